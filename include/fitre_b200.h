@@ -1,0 +1,283 @@
+/*
+ * fitre_b200.h -- C ABI of the B200-native FITRE hot path.
+ *
+ * The library accelerates one path of kylasa/FITRE: the CNN gradient
+ * (forward + backward), the exact Hessian-vector product by Pearlmutter's
+ * R-operator, the one-direction quadratic model, Steihaug-CG driven by that
+ * Hessian-vector product, and KFAC factor accumulation.  Every entry point is
+ * `extern "C"`, takes plain pointers and sizes, and returns an `int` status
+ * (FITRE_OK == 0).  `real` is `double` (reference: core/datadefs.h:5).
+ *
+ * All `real *` arguments are DEVICE pointers unless the name ends in `_host`
+ * or the comment says otherwise.  The caller owns every buffer; the library
+ * never frees or keeps them.  Calls are stream-ordered on the context's
+ * stream; entry points that return a scalar synchronise that stream.
+ *
+ * The model / dataset / scratch structs below are field-for-field compatible
+ * with the reference's (nn/nn_decl.h:64-155, core/structdefs.h:25-83) so a
+ * reference driver can hand its own structs to this library.
+ */
+#ifndef FITRE_B200_H
+#define FITRE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef double real;
+
+#define FITRE_MAX_LAYERS 20 /* reference: nn/nn_decl.h:4 */
+
+/* ---- enum values (binary compatible with nn/nn_decl.h:13-101) ---------- */
+enum { FITRE_NET_LENET = 0, FITRE_NET_ALEXNET = 1, FITRE_NET_VGG11 = 2 };
+enum { FITRE_NO_BATCH_NORM = 0, FITRE_BATCH_NORM = 10, FITRE_BATCH_NORM_TRAINABLE = 20 };
+enum { FITRE_MODEL_TRAIN = 10, FITRE_MODEL_TRAIN_ACCURACY = 20, FITRE_MODEL_TEST_ACCURACY = 30 };
+enum { FITRE_ACT_LINEAR = 3 };
+enum {
+    FITRE_CNN_ACT_NONE = 10,
+    FITRE_CNN_ACT_SOFTPLUS = 11,
+    FITRE_CNN_ACT_ELU = 12,
+    FITRE_CNN_ACT_RELU = 13,
+    FITRE_CNN_ACT_SWISH = 14
+};
+enum { FITRE_MAX_POOL = 0, FITRE_AVG_POOL = 1, FITRE_NO_POOL = 2 };
+enum { FITRE_TRUE_HESSIAN = 0, FITRE_GAUSS_NEWTON = 1 }; /* solvers/params.h:6-9 */
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+    FITRE_OK = 0,
+    FITRE_ERR_BAD_ARG = 1,       /* NULL pointer, negative size, batch mismatch */
+    FITRE_ERR_UNSUPPORTED = 2,   /* layer / activation / pool geometry outside the path */
+    FITRE_ERR_WORKSPACE = 3,     /* scratch smaller than the *_mem_required figure */
+    FITRE_ERR_CUDA = 4,          /* a CUDA runtime call or launch failed */
+    FITRE_ERR_COMM = 5,          /* NCCL error or time-out */
+    FITRE_ERR_NOT_CONVERGED = 6, /* solver hit its iteration limit (informational) */
+    FITRE_ERR_TOO_LARGE = 7      /* size beyond a fixed built-in limit */
+};
+
+/* ---- boundary structs (reference layouts) ------------------------------ */
+typedef struct fitre_conv_layer { /* nn/nn_decl.h:64-95 */
+    int inChannels, outChannels;
+    int width, height, outWidth, outHeight;
+    int kSize, stride, padding;
+    int activationOffset, poolOffset, batchNormOffset, outputOffset;
+    int batchNorm; /* FITRE_NO_BATCH_NORM | FITRE_BATCH_NORM */
+    int meansOffset, variancesOffset;
+    int runningMeansOffset, runningVariancesOffset;
+    int convVolumn, activationVolumn, poolVolumn, batchNormVolumn;
+} CONV_LAYER;
+
+typedef struct fitre_pool_layer { /* nn/nn_decl.h:103-113 */
+    int height, width, outHeight, outWidth;
+    int type; /* FITRE_MAX_POOL | FITRE_AVG_POOL | FITRE_NO_POOL */
+    int pSize, padding, stride;
+} POOL_LAYER;
+
+typedef struct fitre_fc_layer { /* nn/nn_decl.h:115-121 */
+    int in, out, actFun, batchNorm;
+    int offset; /* out * batchSize: where the pre-activation copy lives */
+} FC_LAYER;
+
+typedef struct fitre_cnn_model { /* nn/nn_decl.h:123-155 */
+    CONV_LAYER convLayer[FITRE_MAX_LAYERS];
+    int actFuns[FITRE_MAX_LAYERS];
+    POOL_LAYER poolLayer[FITRE_MAX_LAYERS];
+    int cLayers;
+    int lLayers;
+    FC_LAYER fcLayer[FITRE_MAX_LAYERS];
+    int bias, pSize, zSize, batchSize, maxDeltaSize, name, enableBatchNorm;
+    int wOffsets[FITRE_MAX_LAYERS];
+    int bOffsets[FITRE_MAX_LAYERS];
+    int zOffsets[FITRE_MAX_LAYERS];
+    int zztSize;
+    int zztOffsets[FITRE_MAX_LAYERS];
+    int rZOffsets[FITRE_MAX_LAYERS];
+} CNN_MODEL;
+
+typedef struct fitre_scratch_area { /* core/structdefs.h:25-33 */
+    real *hostWorkspace, *devWorkspace, *pageLckWorkspace;
+    real *nextDevPtr, *nextHostPtr, *nextPageLckPtr;
+} SCRATCH_AREA;
+
+typedef struct fitre_sparse_dataset { /* core/sparsedefs.h:17-29, opaque to this path */
+    int *rowPtr, *colPtr, *rowCsrPtr;
+    real *valPtr;
+    int nnz;
+    real *sortedVals;
+    int *P;
+    void *descr;
+} FITRE_SPARSE_DATASET;
+
+typedef struct fitre_device_dataset { /* core/structdefs.h:55-83 */
+    real *trainSetX, *trainSetY, *testSetX, *testSetY;
+    real *weights; /* flat parameter vector, pSize doubles */
+    int numClasses;
+    int datasetType;
+    int features, height, width;
+    int testSizeX, testSizeY, trainSizeX, trainSizeY;
+    int sampleSize;
+    real *sampledTrainX;
+    real *sampledTrainY; /* labels of the current batch: doubles in 1..numClasses */
+    real *currentBatch;  /* [Cin][N][W][H], h fastest */
+    FITRE_SPARSE_DATASET spSamplingMatrix;
+} DEVICE_DATASET;
+
+/* KFAC block offsets (reference: solvers/kfac_structs.h:12-48, the fields this path uses). */
+typedef struct fitre_kfac_info {
+    int OmegaZOffsets[FITRE_MAX_LAYERS];     /* A-factor block start per layer (doubles) */
+    int LambdaGOffsets[FITRE_MAX_LAYERS];    /* G-factor block start per layer (doubles) */
+    int OmegaZSize, LambdaGSize;
+    real regLambda, dampGamma;
+} FITRE_KFAC_INFO;
+
+/* Steihaug-CG parameters and results (reference: solvers/cg_steihaug.h:10-35). */
+enum {
+    FITRE_CG_CONVERGED = 0,     /* residual below tolerance */
+    FITRE_CG_NEG_CURVATURE = 1, /* d'Hd <= 0, stepped to the boundary */
+    FITRE_CG_HIT_BOUNDARY = 2,  /* iterate left the trust region */
+    FITRE_CG_MAX_ITERS = 3
+};
+typedef struct fitre_cg_params {
+    real delta;     /* trust-region radius */
+    real tolerance; /* stop when ||r||^2 < tolerance */
+    int maxIterations;
+    real weightDecay; /* H + weightDecay * I */
+    /* results */
+    int iterations;
+    int flag;
+    real modelValue; /* 0.5 p'Hp + p'g (+ 0.5 weightDecay p'p) */
+    int hvCalls;
+} FITRE_CG_PARAMS;
+
+typedef struct fitre_context fitre_context; /* one per GPU / host thread */
+
+/* ---- context ------------------------------------------------------------ */
+/* Create a context on CUDA device `device`.  `stream` is a cudaStream_t (NULL = the
+ * legacy default stream).  Replaces the reference's global handles and BLOCK_SIZE
+ * globals (device/handles.h:15-20, drivers/main_driver.c:52-60).  Does not reset the
+ * device and grabs no workspace (contrast device/cuda_environment.c:33,48-66). */
+int fitre_context_create(fitre_context **ctx, int device, void *stream);
+int fitre_context_destroy(fitre_context *ctx);
+/* Last error text of this context (host string, valid until the next call). */
+const char *fitre_last_error(const fitre_context *ctx);
+/* Number of kernels of this library launched through `ctx` since creation. */
+long long fitre_launch_count(const fitre_context *ctx);
+/* 1 = replicate the reference's softmax quirks (max-shift starts at 0 and
+ * probs += 1e-10: functions/softmax_loss.cu:24-27,55); 0 = textbook softmax. Default 1. */
+int fitre_set_reference_softmax(fitre_context *ctx, int on);
+
+/* Data-parallel set-up: `unique_id` is the 128-byte ncclUniqueId obtained on rank 0
+ * (fitre_comm_unique_id) and broadcast by the caller.  After this call every batch
+ * statistic (loss, batch-norm sums, gradient, Hv, KFAC factors, dot products) is
+ * all-reduced over `world` ranks and 1/N uses the global batch world*curBatchSize.
+ * No counterpart in the reference (single GPU). */
+int fitre_comm_unique_id(void *unique_id_128_host);
+int fitre_comm_init(fitre_context *ctx, const void *unique_id_128_host, int rank, int world);
+int fitre_comm_world(const fitre_context *ctx);
+
+/* ---- model builders (nn/read_nn.c:500-725, nn/read_alexnet.c:14-243,
+ *      nn/read_vgg.c:25-120,122-212,216-299, nn/utils.c:19-172) ---------- */
+/* `actFun` overrides the builders' Swish (pass FITRE_CNN_ACT_SWISH to keep it);
+ * `poolType` overrides LeNet's average pooling (FITRE_AVG_POOL to keep it). */
+int fitre_read_lenet_cnn(CNN_MODEL *m, int channels, int width, int height, int batchSize,
+                         int enableBias, int enableBatchNorm, int actFun, int poolType);
+int fitre_read_alexnet_cnn(CNN_MODEL *m, int batchSize, int height, int width, int numClasses,
+                           int enableBias, int enableBatchNorm, int actFun);
+int fitre_read_vgg11(CNN_MODEL *m, int batchSize, int height, int width, int numClasses,
+                     int inChannels, int enableBias, int enableBatchNorm, int actFun);
+int fitre_read_test_vgg(CNN_MODEL *m, int batchSize, int height, int width, int numClasses,
+                        int inChannels, int enableBias, int batchNorm, int actFun);
+/* Generic: the caller fills cLayers/lLayers, per conv layer {inChannels,outChannels,height,
+ * width,kSize,stride,padding,batchNorm}, actFuns[], per pool layer {type,pSize,stride,padding},
+ * per FC layer {in,out,actFun}, bias and batchSize; this fills every derived field
+ * (output sizes, offsets, volumes, pSize, zSize, maxDeltaSize) with the layout of
+ * nn/read_vgg.c:63-101 and nn/utils.c:44-172. */
+int fitre_model_finalize(CNN_MODEL *m);
+/* Checks that the model is inside the supported path (stride-1 square convs, pooling with
+ * ksize - stride == padding, square planes at the conv->FC boundary, known activations). */
+int fitre_model_validate(const CNN_MODEL *m);
+
+/* ---- scratch sizing: element counts of `real` (functions/cnn_forward.cu:16,
+ *      cnn_backward.cu:51, cnn_hv_forward.cu:15, cnn_hv_backward.cu:24) --- */
+long fitre_cnn_forward_mem_required(const CNN_MODEL *m);
+long fitre_cnn_backward_mem_required(const CNN_MODEL *m);
+long fitre_cnn_rop_forward_mem_required(const CNN_MODEL *m);
+long fitre_cnn_rop_backward_mem_required(const CNN_MODEL *m);
+/* Scratch needed behind scratch->nextDevPtr by fitre_compute_cnn_gradient (two delta
+ * buffers + forward/backward scratch) and behind devPtr by fitre_cnn_hv (rz + rError + scratch). */
+long fitre_cnn_gradient_mem_required(const CNN_MODEL *m);
+long fitre_cnn_hv_mem_required(const CNN_MODEL *m);
+
+/* ---- the hot path --------------------------------------------------------- */
+/* functions/cnn_forward.h:11-13.  Writes every intermediate to `z`, the class
+ * probabilities to `probs`, (p - onehot)/N to `errors`, and the mean loss to *loss_host. */
+int fitre_cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                      SCRATCH_AREA *scratch, real *z, real *probs, real *errors, int s,
+                      int curBatchSize, int evalType, real *loss_host);
+/* functions/cnn_backward.h:13-16.  `delta` holds the loss errors on entry and is destroyed. */
+int fitre_cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                       real *devPtr, real *z, real *gradient, real *dx, real *delta,
+                       real *delta_new, int offset, int batchSize, real *hostPtr);
+/* functions/cnn_gradient.h:9-12.  loss -> *loss_host, gradient (+ weightDecay*w) -> gradient. */
+int fitre_compute_cnn_gradient(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                               SCRATCH_AREA *scratch, real *z, real *dx, real *probs,
+                               real *lossFuncErrors, real *gradient, int offset, int curBatchSize,
+                               real weightDecay, real *loss_host);
+/* functions/cnn_hv_forward.h:10-13 */
+int fitre_cnn_rop_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                          SCRATCH_AREA *scratch, real *z, real *vector, real *rz, int s,
+                          int curBatchSize, real *devPtr, real *hostPtr);
+/* functions/cnn_hv_backward.h:12-15 */
+int fitre_cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                           SCRATCH_AREA *scratch, real *z, real *dx, real *lossFuncErrors,
+                           real *rError, real *rz, real *vector, real *hv, int s,
+                           int curBatchSize, real *devPtr, real *hostPtr);
+/* functions/cnn_hessian_vec.h:9-13.  Uses z/probs/lossFuncErrors/dx left by the gradient on
+ * the same batch.  weightDecay is accepted and unused, as in the reference. */
+int fitre_cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, real *z,
+                 real *probs, real *lossFuncErrors, real *dx, real *vector, real *hv, int s,
+                 int curBatchSize, real *devPtr, real *hostPtr, real weightDecay);
+/* functions/model_reduction.cu:20-93.  Scales `vector` in place; model value -> *m_host. */
+int fitre_compute_quadratic_model(fitre_context *ctx, const CNN_MODEL *m,
+                                  const DEVICE_DATASET *data, real *z, real *probs,
+                                  real *lossFuncErrors, real *dx, real *gradient, real *vector,
+                                  real delta, int offset, int curBatchSize, real weightDecay,
+                                  real *devPtr, real *hostPtr, real *pageLckPtr, real *m_host);
+/* Steihaug-CG on the trust-region subproblem min g'p + 0.5 p'Hp, ||p|| <= delta, with
+ * H applied by fitre_cnn_hv (algorithm: solvers/cg_steihaug.c:28-260 and its CNN twin
+ * pytorch/peng/utils.py:104-165).  `p` (pSize) receives the step.  devPtr needs
+ * 4*pSize + fitre_cnn_hv_mem_required doubles. */
+int fitre_cg_steihaug(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                      real *z, real *probs, real *lossFuncErrors, real *dx, real *gradient,
+                      real *p, int curBatchSize, real *devPtr, FITRE_CG_PARAMS *params);
+
+/* ---- KFAC factors (solvers/kfac_utils.cu:7-55, kfac_inverses.cu:450-630,759-857) */
+int fitre_kfac_storage_indices(const CNN_MODEL *m, FITRE_KFAC_INFO *info);
+/* A factors: conv (1/N) P~'P~ with P~ = [im2col(X)/(Ho*Wo), 1]; FC (1/N) z~ z~'.  Raw
+ * (undamped, uninverted) factors are written to omegaZ + OmegaZOffsets[l]. */
+int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                       const real *z, int samples, real *omegaZ, const FITRE_KFAC_INFO *info,
+                       real *devPtr);
+/* G factors: conv (N*Ho*Wo) d'd, FC N d d' from the stored backward errors `dx`. */
+int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, const real *dx, int samples,
+                            real *lambdaG, const FITRE_KFAC_INFO *info, real *devPtr);
+
+/* ---- host-buffer entry point (what a reference driver calls per minibatch) ---- */
+/* One gradient + one Hessian-vector product with HOST inputs and outputs: copies the
+ * batch, labels, weights and `vector` to the device, runs fitre_compute_cnn_gradient and
+ * fitre_cnn_hv, all-reduces when a communicator is set, and copies gradient and hv back.
+ * Device state lives in a workspace the context allocates on first use for this model
+ * and batch size (stream-ordered allocation; reused by later calls). */
+int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *batch_host,
+                           const real *labels_host, const real *weights_host,
+                           const real *vector_host, int curBatchSize, int numClasses,
+                           real weightDecay, real *loss_host, real *gradient_host,
+                           real *hv_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FITRE_B200_H */

@@ -1,0 +1,1306 @@
+/*
+ * fitre_oracle.c -- CPU restatement of FITRE's CNN gradient / Hessian-vector / KFAC-factor
+ * path.  TEST INFRASTRUCTURE ONLY (the checker for the CUDA library; never linked into it).
+ *
+ * Each function names the reference source (path within kylasa/FITRE, file:line) whose
+ * operation order it follows.  GPU kernels and cuBLAS calls become plain loops; results
+ * therefore agree with the reference up to floating-point summation order.
+ *
+ * Pinned against: the reference's batch-norm known-answer vectors
+ * (pytorch/testing/batchnorm_derivative.py + my.out, batchnorm_rop.py), the LeNet offset
+ * table of pytorch/kfac/cifar_kfac_trust_iteration.txt:12-13, and gradient / Hessian-vector
+ * fixtures produced by PyTorch double-backward through the reference's own weight-layout
+ * reader pytorch/testing/readWeights.py (see tests/golden/).
+ *
+ * Deviations from the reference, on purpose:
+ *  - ReLU is differentiated (h' = 1[z>0], h'' = 0); the reference leaves ReLU out of the
+ *    backward and R-op passes (functions/cnn_backward.cu:561-562, cnn_hv_backward.cu:676).
+ *  - the R-op batch-norm backward uses the per-channel scale the reference intends; its
+ *    ker_rI_scale launch indexes past the per-channel buffer (dev_batch_norm.cu:174-183,910).
+ *  - cnnROpForward passes actFuns[0] for every layer (cnn_hv_forward.cu:86,125); here layer
+ *    l uses actFuns[l] (identical for every builder of the reference).
+ *  - the R-op pooling uses the backward pass's arg-max scan order (dev_pool.cu:374-391) for
+ *    both directions; the reference's two scans differ only on exact ties.
+ */
+#include "fitre_oracle.h"
+
+#include <float.h>
+#include <limits.h>
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define BN_EPS 1e-5 /* functions/dev_batch_norm.h:10 */
+
+static double *xmalloc(long n) {
+    if (n < 1) n = 1;
+    double *p = (double *)malloc(sizeof(double) * (size_t)n);
+    if (!p) {
+        fprintf(stderr, "fitre_oracle: out of memory (%ld doubles)\n", n);
+        abort();
+    }
+    return p;
+}
+
+void ora_env_default(ORA_ENV *env) {
+    env->ref_softmax = 1;
+    env->world = 1;
+    env->allreduce = NULL;
+    env->user = NULL;
+}
+
+static void env_allreduce(const ORA_ENV *env, double *buf, long n) {
+    if (env && env->allreduce) env->allreduce(buf, n, env->user);
+}
+static int env_world(const ORA_ENV *env) { return (env && env->world > 0) ? env->world : 1; }
+
+/* ------------------------------------------------------------------------------------ */
+/* Model set-up                                                                          */
+/* ------------------------------------------------------------------------------------ */
+
+/* nn/utils.c:12-17 */
+static void out_dims(int h, int w, int pad, int stride, int k, int *oh, int *ow) {
+    *oh = (h + 2 * pad - k) / stride + 1;
+    *ow = (w + 2 * pad - k) / stride + 1;
+}
+
+/* Per-layer offsets: nn/read_vgg.c:25-120 (makeLayer).  Parameter offsets:
+ * nn/utils.c:19-105.  z offsets: nn/utils.c:107-172. */
+int ora_model_finalize(CNN_MODEL *m) {
+    int B = m->batchSize;
+    if (m->cLayers < 1 || m->cLayers + m->lLayers + 1 >= FITRE_MAX_LAYERS || B < 1) return 1;
+    for (int l = 0; l < m->cLayers; l++) {
+        CONV_LAYER *c = &m->convLayer[l];
+        POOL_LAYER *p = &m->poolLayer[l];
+        out_dims(c->height, c->width, c->padding, c->stride, c->kSize, &c->outHeight,
+                 &c->outWidth);
+        p->height = c->outHeight;
+        p->width = c->outWidth;
+        if (p->type == FITRE_NO_POOL) {
+            p->outHeight = p->height;
+            p->outWidth = p->width;
+        } else {
+            /* functions/dev_pool.cu:226-227 */
+            p->outHeight = (int)floor((double)(p->height - p->pSize + 2 * p->padding) / p->stride + 1.);
+            p->outWidth = (int)floor((double)(p->width - p->pSize + 2 * p->padding) / p->stride + 1.);
+        }
+        long V = (long)c->outHeight * c->outWidth * c->outChannels * B;
+        long P = (long)p->outHeight * p->outWidth * c->outChannels * B;
+        if (3 * V + 4 * c->outChannels + P > INT_MAX) return 2;
+        if (c->batchNorm == FITRE_NO_BATCH_NORM) {
+            c->activationOffset = (int)V;
+            c->batchNormOffset = INT_MAX;
+            c->meansOffset = c->variancesOffset = INT_MAX;
+            c->runningMeansOffset = c->runningVariancesOffset = INT_MAX;
+            if (p->type == FITRE_NO_POOL) {
+                c->poolOffset = INT_MAX;
+                c->outputOffset = c->activationOffset;
+            } else {
+                c->poolOffset = (int)(2 * V);
+                c->outputOffset = c->poolOffset;
+            }
+        } else {
+            c->batchNormOffset = (int)V;
+            c->meansOffset = (int)V; /* relative to the batch-norm output */
+            c->variancesOffset = c->meansOffset + c->outChannels;
+            c->runningMeansOffset = c->variancesOffset + c->outChannels;
+            c->runningVariancesOffset = c->runningMeansOffset + c->outChannels;
+            c->activationOffset = (int)(2 * V + 4 * c->outChannels);
+            if (p->type == FITRE_NO_POOL) {
+                c->poolOffset = INT_MAX;
+                c->outputOffset = c->activationOffset;
+            } else {
+                c->poolOffset = c->activationOffset + (int)V;
+                c->outputOffset = c->poolOffset;
+            }
+        }
+        c->convVolumn = c->outHeight * c->outWidth * c->outChannels;
+        c->activationVolumn = c->convVolumn;
+        c->batchNormVolumn = (c->batchNorm != FITRE_NO_BATCH_NORM) ? INT_MAX : c->convVolumn;
+        c->poolVolumn = (p->type == FITRE_NO_POOL)
+                            ? INT_MAX
+                            : p->outHeight * p->outWidth * c->outChannels;
+    }
+    for (int l = 0; l < m->lLayers; l++) m->fcLayer[l].offset = m->fcLayer[l].out * B;
+
+    /* nn/utils.c:19-42 */
+    long ps = 0;
+    for (int i = 0; i < m->cLayers; i++) {
+        CONV_LAYER *t = &m->convLayer[i];
+        ps += (long)t->outChannels * t->kSize * t->kSize * t->inChannels;
+        if (m->bias >= 1) ps += t->outChannels;
+    }
+    for (int i = 0; i < m->lLayers; i++) {
+        ps += (long)m->fcLayer[i].out * m->fcLayer[i].in;
+        if (m->bias >= 1) ps += m->fcLayer[i].out;
+    }
+    if (ps > INT_MAX) return 2;
+    m->pSize = (int)ps;
+
+    for (int i = 0; i < FITRE_MAX_LAYERS; i++) m->wOffsets[i] = m->bOffsets[i] = m->zOffsets[i] = 0;
+    int L = m->cLayers + m->lLayers;
+    int off = 0;
+    for (int i = 0; i < L; i++) { /* weights then (optionally) bias, layer by layer */
+        int wsz, bsz;
+        if (i < m->cLayers) {
+            CONV_LAYER *t = &m->convLayer[i];
+            wsz = t->outChannels * t->kSize * t->kSize * t->inChannels;
+            bsz = t->outChannels;
+        } else {
+            wsz = m->fcLayer[i - m->cLayers].out * m->fcLayer[i - m->cLayers].in;
+            bsz = m->fcLayer[i - m->cLayers].out;
+        }
+        m->wOffsets[i] = off;
+        off += wsz;
+        if (m->bias != 0) {
+            m->bOffsets[i] = off;
+            off += bsz;
+        } else {
+            m->bOffsets[i] = INT_MAX; /* nn/utils.c:49 */
+        }
+    }
+    if (m->bias == 0) m->wOffsets[L] = off; /* nn/utils.c:60,70 */
+
+    /* nn/utils.c:107-172 */
+    for (int i = 0; i < FITRE_MAX_LAYERS; i++) m->zztOffsets[i] = 0;
+    m->maxDeltaSize = 0;
+    m->zztSize = 0;
+    long zo = 0;
+    m->zOffsets[0] = 0;
+    m->zOffsets[1] = 0;
+    for (int i = 1; i <= m->cLayers; i++) {
+        CONV_LAYER *t = &m->convLayer[i - 1];
+        POOL_LAYER *p = &m->poolLayer[i - 1];
+        long V = (long)B * t->outHeight * t->outWidth * t->outChannels;
+        long sz = 2 * V;
+        if (t->batchNorm != FITRE_NO_BATCH_NORM) sz += V + 4 * t->outChannels;
+        if (p->type != FITRE_NO_POOL) sz += (long)B * p->outHeight * p->outWidth * t->outChannels;
+        zo += sz;
+        if (zo > INT_MAX) return 2;
+        m->zOffsets[i + 1] = (int)zo;
+        m->zztOffsets[i + 1] = m->zztOffsets[i] + (int)V;
+        m->zztSize += (int)V;
+        if (sz > m->maxDeltaSize) m->maxDeltaSize = (int)sz;
+    }
+    for (int i = 1; i <= m->lLayers; i++) {
+        FC_LAYER *t = &m->fcLayer[i - 1];
+        long sz = (long)t->out * B * 2;
+        zo += sz;
+        if (zo > INT_MAX) return 2;
+        m->zOffsets[i + m->cLayers + 1] = (int)zo;
+        m->zztOffsets[i + 1 + m->cLayers] = m->zztOffsets[i + m->cLayers] + t->out * B;
+        m->zztSize += t->out * B;
+        if (sz > m->maxDeltaSize) m->maxDeltaSize = (int)sz;
+    }
+    m->zSize = m->zOffsets[m->cLayers + m->lLayers + 1];
+    return 0;
+}
+
+long ora_model_zsize64(const CNN_MODEL *m) { return m->zSize; }
+
+/* ------------------------------------------------------------------------------------ */
+/* Dense helpers                                                                         */
+/* ------------------------------------------------------------------------------------ */
+
+/* Column-major C = alpha * op(A) * op(B) + beta * C  (cublasDgemm semantics). */
+void ora_gemm(int tA, int tB, long m, long n, long k, double alpha, const double *A, long lda,
+              const double *B, long ldb, double beta, double *C, long ldc) {
+#pragma omp parallel for schedule(static)
+    for (long j = 0; j < n; j++) {
+        double *c = C + j * ldc;
+        if (beta == 0.0)
+            for (long i = 0; i < m; i++) c[i] = 0.0;
+        else if (beta != 1.0)
+            for (long i = 0; i < m; i++) c[i] *= beta;
+        if (!tA) {
+            for (long p = 0; p < k; p++) {
+                double b = alpha * (tB ? B[j + p * ldb] : B[p + j * ldb]);
+                const double *a = A + p * lda;
+                for (long i = 0; i < m; i++) c[i] += a[i] * b;
+            }
+        } else {
+            for (long i = 0; i < m; i++) {
+                const double *a = A + i * lda;
+                double s = 0.0;
+                if (!tB) {
+                    const double *b = B + j * ldb;
+                    for (long p = 0; p < k; p++) s += a[p] * b[p];
+                } else {
+                    for (long p = 0; p < k; p++) s += a[p] * B[j + p * ldb];
+                }
+                c[i] += alpha * s;
+            }
+        }
+    }
+}
+
+static void axpy(long n, double a, const double *x, double *y) {
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < n; i++) y[i] += a * x[i];
+}
+static double dot(long n, const double *x, const double *y) {
+    double s = 0.0;
+#pragma omp parallel for reduction(+ : s) schedule(static)
+    for (long i = 0; i < n; i++) s += x[i] * y[i];
+    return s;
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* im2col: functions/dev_image.cu:12-51                                                  */
+/* ------------------------------------------------------------------------------------ */
+
+/* Source flat index of every im2col element (-1 = zero padding).  Row r = n*Ho*Wo + wo*Ho + ho,
+ * column q = cin*k*k + j*k + i, stored column-major with leading dimension M. */
+void ora_im2col_index(int N, int C, int H, int W, int k, int pad, int stride, long *idx) {
+    int Ho, Wo;
+    out_dims(H, W, pad, stride, k, &Ho, &Wo);
+    long M = (long)N * Ho * Wo;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int cin = 0; cin < C; cin++)
+        for (int n = 0; n < N; n++)
+            for (int wo = 0; wo < Wo; wo++)
+                for (int ho = 0; ho < Ho; ho++) {
+                    int h_in = ho * stride - pad, w_in = wo * stride - pad;
+                    long row = (long)n * Ho * Wo + (long)wo * Ho + ho;
+                    for (int j = 0; j < k; j++)
+                        for (int i = 0; i < k; i++) {
+                            int h = h_in + i, w = w_in + j;
+                            long q = (long)cin * k * k + j * k + i;
+                            long src = -1;
+                            if (h >= 0 && w >= 0 && h < H && w < W)
+                                src = (((long)cin * N + n) * W + w) * H + h;
+                            idx[q * M + row] = src;
+                        }
+                }
+}
+
+void ora_im2col(const double *x, int N, int C, int H, int W, int k, int pad, int stride,
+                double *cols) {
+    int Ho, Wo;
+    out_dims(H, W, pad, stride, k, &Ho, &Wo);
+    long M = (long)N * Ho * Wo;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int cin = 0; cin < C; cin++)
+        for (int n = 0; n < N; n++)
+            for (int wo = 0; wo < Wo; wo++)
+                for (int ho = 0; ho < Ho; ho++) {
+                    int h_in = ho * stride - pad, w_in = wo * stride - pad;
+                    long row = (long)n * Ho * Wo + (long)wo * Ho + ho;
+                    const double *src = x + ((long)cin * N + n) * W * H;
+                    for (int j = 0; j < k; j++)
+                        for (int i = 0; i < k; i++) {
+                            int h = h_in + i, w = w_in + j;
+                            long q = (long)cin * k * k + j * k + i;
+                            cols[q * M + row] =
+                                (h >= 0 && w >= 0 && h < H && w < W) ? src[(long)w * H + h] : 0.0;
+                        }
+                }
+}
+
+/* [right][left][chunk] -> [left][right][chunk]: functions/dev_backprop_convolution.cu:140-156 */
+static void reshape_matrix(const double *in, int right, int left, int chunk, double *out) {
+    long n = (long)right * left * chunk;
+#pragma omp parallel for schedule(static)
+    for (long idx = 0; idx < n; idx++) {
+        long nId = idx / ((long)chunk * left);
+        long nIdx = idx % ((long)chunk * left);
+        long cId = nIdx / chunk;
+        long chunkId = nIdx % chunk;
+        out[cId * ((long)chunk * right) + nId * chunk + chunkId] = in[idx];
+    }
+}
+
+/* Per-plane column-major -> row-major: functions/dev_transpose.cu:8-30 (square planes). */
+static void transpose_planes(const double *in, long count, int height, int width, double *out) {
+    long plane = (long)height * width;
+#pragma omp parallel for schedule(static)
+    for (long idx = 0; idx < count; idx++) {
+        long base = (idx / plane) * plane;
+        long r = idx % plane;
+        long col = r / height, row = r % height;
+        out[base + row * height + col] = in[idx];
+    }
+}
+
+/* conv-layout [C][N][P] -> FC layout (feature c*P + h*Wp + w, sample-major columns):
+ * functions/cnn_forward.cu:237-261 */
+static void conv_to_fc(double *buf, int C, int N, int Hp, int Wp) {
+    long cnt = (long)C * N * Hp * Wp;
+    double *tmp = xmalloc(cnt);
+    reshape_matrix(buf, C, N, Hp * Wp, tmp);
+    transpose_planes(tmp, cnt, Hp, Wp, buf);
+    free(tmp);
+}
+/* inverse direction for the errors: functions/cnn_backward.cu:310-326 */
+static void fc_to_conv(double *buf, int C, int N, int Hp, int Wp) {
+    long cnt = (long)C * N * Hp * Wp;
+    double *tmp = xmalloc(cnt);
+    reshape_matrix(buf, N, C, Hp * Wp, tmp);
+    transpose_planes(tmp, cnt, Hp, Wp, buf);
+    free(tmp);
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Activations: functions/dev_activations.cu:8-39, swish.cu:14-84,                       */
+/* dev_layer_error.cu:34-47, dev_layer_r_error.cu:24-38                                  */
+/* ------------------------------------------------------------------------------------ */
+static int act_known(int a) {
+    return a == FITRE_CNN_ACT_NONE || a == FITRE_ACT_LINEAR || a == FITRE_CNN_ACT_SOFTPLUS ||
+           a == FITRE_CNN_ACT_RELU || a == FITRE_CNN_ACT_SWISH;
+}
+
+void ora_activation(int act, double *x, long n) {
+    if (!act_known(act)) {
+        fprintf(stderr, "fitre_oracle: unknown activation %d\n", act);
+        abort();
+    }
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < n; i++) {
+        double t = x[i];
+        switch (act) {
+            case FITRE_CNN_ACT_RELU: x[i] = t < 0 ? 0 : t; break;
+            case FITRE_CNN_ACT_SOFTPLUS: x[i] = (t < 20) ? log(1 + exp(t)) : t; break;
+            case FITRE_CNN_ACT_SWISH: x[i] = t / (1 + exp(-t)); break;
+            default: break;
+        }
+    }
+}
+
+/* h'(zin) given pre-activation zin and output zout */
+static inline double act_d1(int act, double zin, double zout) {
+    switch (act) {
+        case FITRE_CNN_ACT_RELU: return zin > 0 ? 1.0 : 0.0;
+        case FITRE_CNN_ACT_SOFTPLUS: return 1. / (1. + exp(-zin));
+        case FITRE_CNN_ACT_SWISH: {
+            double t = 1. / (1. + exp(-zin));
+            return zout + t * (1. - zout);
+        }
+        default: return 1.0;
+    }
+}
+/* h''(zin) */
+static inline double act_d2(int act, double zin, double zout) {
+    switch (act) {
+        case FITRE_CNN_ACT_SOFTPLUS: {
+            double tm = exp(-zin);
+            return (1. / (1. + tm)) * (tm / (1. + tm));
+        }
+        case FITRE_CNN_ACT_SWISH: {
+            double t = 1. / (1. + exp(-zin));
+            return (1. - t) * (zout + 2. * t * (1. - zout));
+        }
+        default: return 0.0;
+    }
+}
+
+/* delta *= h'(zin) */
+static void act_backward(int act, double *delta, const double *zin, const double *zout, long n) {
+    if (act == FITRE_CNN_ACT_NONE || act == FITRE_ACT_LINEAR) return;
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < n; i++) delta[i] *= act_d1(act, zin[i], zout[i]);
+}
+/* rdelta = h'(zin) * rdelta + h''(zin) * rzin * delta_in */
+static void act_rop_backward(int act, double *rdelta, const double *delta_in, const double *rzin,
+                             const double *zin, const double *zout, long n) {
+    if (act == FITRE_CNN_ACT_NONE || act == FITRE_ACT_LINEAR) return;
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < n; i++)
+        rdelta[i] = act_d1(act, zin[i], zout[i]) * rdelta[i] +
+                    act_d2(act, zin[i], zout[i]) * rzin[i] * delta_in[i];
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Pooling: functions/dev_pool.cu                                                        */
+/* ------------------------------------------------------------------------------------ */
+
+/* :41-121 (window start (k-1)*stride + ksize - 2*pad, :55,94) */
+void ora_pool_forward(const double *in, int N, int C, int H, int W, int ks, int stride, int pad,
+                      int type, double *out) {
+    int Hp = (int)floor((double)(H - ks + 2 * pad) / stride + 1.);
+    int Wp = (int)floor((double)(W - ks + 2 * pad) / stride + 1.);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int c = 0; c < C; c++)
+        for (int n = 0; n < N; n++)
+            for (int l = 0; l < Wp; l++)
+                for (int k = 0; k < Hp; k++) {
+                    int i = (k - 1) * stride + ks - 2 * pad;
+                    int j = (l - 1) * stride + ks - 2 * pad;
+                    const double *src = in + ((long)c * N + n) * H * W;
+                    double val = (type == FITRE_MAX_POOL) ? -DBL_MAX : 0.0;
+                    for (int r = 0; r < ks; r++)
+                        for (int cc = 0; cc < ks; cc++) {
+                            int fr = i + r, fc = j + cc;
+                            if (fr < 0 || fc < 0 || fr >= H || fc >= W) continue;
+                            double t = src[(long)fc * H + fr];
+                            if (type == FITRE_MAX_POOL) {
+                                if (t > val) val = t;
+                            } else
+                                val += t;
+                        }
+                    if (type != FITRE_MAX_POOL) val = val / (ks * ks);
+                    out[((long)c * N + n) * Hp * Wp + (long)l * Hp + k] = val;
+                }
+}
+
+/* arg-max flat index into the activation tensor per pooled cell, scan order of the
+ * backward kernel (:374-391: column outer, row inner, strict >). */
+void ora_max_pool_argmax(const double *act, int N, int C, int H, int W, int ks, int stride,
+                         int pad, int *argmax) {
+    int Hp = (int)floor((double)(H - ks + 2 * pad) / stride + 1.);
+    int Wp = (int)floor((double)(W - ks + 2 * pad) / stride + 1.);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int c = 0; c < C; c++)
+        for (int n = 0; n < N; n++)
+            for (int l = 0; l < Wp; l++)
+                for (int k = 0; k < Hp; k++) {
+                    int i = (k - 1) * stride + ks - 2 * pad;
+                    int j = (l - 1) * stride + ks - 2 * pad;
+                    long base = ((long)c * N + n) * H * W;
+                    double mv = -DBL_MAX;
+                    long mi = -1;
+                    for (int cc = 0; cc < ks; cc++)
+                        for (int r = 0; r < ks; r++) {
+                            int fc = j + cc, fr = i + r;
+                            if (fc < 0 || fc >= W || fr < 0 || fr >= H) continue;
+                            long tid = base + (long)fc * H + fr;
+                            if (act[tid] > mv) {
+                                mv = act[tid];
+                                mi = tid;
+                            }
+                        }
+                    argmax[((long)c * N + n) * Hp * Wp + (long)l * Hp + k] = (int)mi;
+                }
+}
+
+/* :346-398, :474-497 -- scatter delta to the arg-max (sequential adds, so deterministic) */
+void ora_max_pool_backward(const double *delta, const double *act, int C, int H, int W, int ks,
+                           int stride, int pad, int Hp, int Wp, int N, double *out) {
+    long V = (long)C * N * H * W, P = (long)C * N * Hp * Wp;
+    int *am = (int *)malloc(sizeof(int) * (size_t)(P > 0 ? P : 1));
+    ora_max_pool_argmax(act, N, C, H, W, ks, stride, pad, am);
+    memset(out, 0, sizeof(double) * (size_t)V);
+    for (long i = 0; i < P; i++)
+        if (am[i] >= 0) out[am[i]] += delta[i];
+    free(am);
+}
+
+/* :269-298 with the 1/k^2 scale of functions/cnn_backward.cu:471-473 folded in.
+ * stride == kernel, no padding, square planes (the reference's only form). */
+void ora_avg_pool_backward(const double *delta, int Hp, int C, int ks, int N, double *out) {
+    int inSize = Hp;
+    long n = (long)inSize * inSize * C * N;
+    double sc = 1. / (ks * ks);
+#pragma omp parallel for schedule(static)
+    for (long idx = 0; idx < n; idx++) {
+        long plane = (long)inSize * inSize;
+        long cn = idx / plane; /* c*N + n */
+        long r = idx % plane;
+        long sCol = r / inSize, sRow = r % inSize;
+        double v = delta[idx] * sc;
+        long H = (long)inSize * ks;
+        double *dst = out + cn * H * H;
+        for (int i = 0; i < ks; i++)
+            for (int j = 0; j < ks; j++) dst[(sCol * ks + j) * H + sRow * ks + i] = v;
+    }
+}
+
+/* :123-174 -- R{pool}: pick rz at the arg-max of z */
+void ora_rop_max_pool(const double *rz, const double *zact, int N, int C, int H, int W, int ks,
+                      int stride, int pad, double *out) {
+    int Hp = (int)floor((double)(H - ks + 2 * pad) / stride + 1.);
+    int Wp = (int)floor((double)(W - ks + 2 * pad) / stride + 1.);
+    long P = (long)C * N * Hp * Wp;
+    int *am = (int *)malloc(sizeof(int) * (size_t)(P > 0 ? P : 1));
+    ora_max_pool_argmax(zact, N, C, H, W, ks, stride, pad, am);
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < P; i++) out[i] = am[i] >= 0 ? rz[am[i]] : 0.0;
+    free(am);
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Batch norm: functions/dev_batch_norm.cu                                               */
+/* ------------------------------------------------------------------------------------ */
+
+/* per-channel sum of f(idx) over the (N,H,W) block of channel c; all-reduced over ranks */
+static void channel_sums(const ORA_ENV *env, int C, long rows, const double *a, const double *b,
+                         int mode, const double *p0, const double *p1, double *out) {
+    /* mode 0: sum a ; 1: sum a*b ; 2: sum (a-p0[c])^2 ; 3: sum (a-p0[c])*(b-p1[c]) */
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < C; c++) {
+        const double *ac = a + (long)c * rows;
+        const double *bc = b ? b + (long)c * rows : NULL;
+        double s = 0.0;
+        for (long i = 0; i < rows; i++) {
+            switch (mode) {
+                case 0: s += ac[i]; break;
+                case 1: s += ac[i] * bc[i]; break;
+                case 2: s += (ac[i] - p0[c]) * (ac[i] - p0[c]); break;
+                default: s += (ac[i] - p0[c]) * (bc[i] - p1[c]); break;
+            }
+        }
+        out[c] = s;
+    }
+    env_allreduce(env, out, C);
+}
+
+/* :263-315, :331-393 -- batch mean, biased variance (two passes), zhat */
+void ora_batch_norm_forward(const ORA_ENV *env, const double *in, int H, int W, int C, int N,
+                            double *out, double *mean, double *var, double eps) {
+    long rows = (long)H * W * N;
+    double m = (double)rows * env_world(env);
+    channel_sums(env, C, rows, in, NULL, 0, NULL, NULL, mean);
+    for (int c = 0; c < C; c++) mean[c] *= 1. / m;
+    channel_sums(env, C, rows, in, NULL, 2, mean, NULL, var);
+    for (int c = 0; c < C; c++) var[c] *= 1. / m;
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < C; c++)
+        for (long i = 0; i < rows; i++)
+            out[(long)c * rows + i] = (in[(long)c * rows + i] - mean[c]) / sqrt(var[c] + eps);
+}
+
+/* :398-466, :550-621, kernel :132-150 */
+void ora_batch_norm_backward(const ORA_ENV *env, const double *delta, int H, int W, int C,
+                             int N, const double *var, const double *zhat, double eps,
+                             double *out) {
+    long rows = (long)H * W * N;
+    double m = (double)rows * env_world(env);
+    double *s1 = xmalloc(C), *s2 = xmalloc(C);
+    channel_sums(env, C, rows, delta, NULL, 0, NULL, NULL, s1);
+    channel_sums(env, C, rows, delta, zhat, 1, NULL, NULL, s2);
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < C; c++)
+        for (long i = 0; i < rows; i++) {
+            long id = (long)c * rows + i;
+            double t = delta[id] * m - s1[c] - s2[c] * zhat[id];
+            out[id] = t / (m * sqrt(eps + var[c]));
+        }
+    free(s1);
+    free(s2);
+}
+
+/* :637-770 */
+void ora_rop_batch_norm_forward(const ORA_ENV *env, const double *z, const double *mean,
+                                const double *var, const double *rz_in, double eps, int H,
+                                int W, int C, int N, double *rz_out) {
+    long rows = (long)H * W * N;
+    double m = (double)rows * env_world(env);
+    double *rmean = xmalloc(C), *s = xmalloc(C);
+    channel_sums(env, C, rows, rz_in, NULL, 0, NULL, NULL, rmean);
+    for (int c = 0; c < C; c++) rmean[c] *= 1. / m;
+    channel_sums(env, C, rows, z, rz_in, 3, mean, rmean, s);
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < C; c++)
+        for (long i = 0; i < rows; i++) {
+            long id = (long)c * rows + i;
+            double first = (rz_in[id] - rmean[c]) / sqrt(eps + var[c]);
+            double second = s[c] * (z[id] - mean[c]) / (m * pow(eps + var[c], 1.5));
+            rz_out[id] = first - second;
+        }
+    free(rmean);
+    free(s);
+}
+
+/* :787-960 (helpers :468-529; kernels :92-128,153-183,207-218) */
+void ora_rop_batch_norm_backward(const ORA_ENV *env, const double *z_in, const double *z_out,
+                                 const double *rz_in, const double *rz_out, const double *delta,
+                                 double *rdelta, double eps, const double *mean,
+                                 const double *var, int H, int W, int C, int N) {
+    long rows = (long)H * W * N;
+    double m = (double)rows * env_world(env);
+    double *s1 = xmalloc(C), *s2 = xmalloc(C), *s3 = xmalloc(C), *rmean = xmalloc(C);
+    double *rI = xmalloc(C), *d1 = xmalloc(C);
+    /* R(II): sum Rdelta, sum delta*zhat, sum (delta*Rzhat + zhat*Rdelta) */
+    channel_sums(env, C, rows, rdelta, NULL, 0, NULL, NULL, s1);
+    channel_sums(env, C, rows, delta, z_out, 1, NULL, NULL, s2);
+    {
+        double *t = xmalloc(C);
+        channel_sums(env, C, rows, delta, rz_out, 1, NULL, NULL, s3);
+        channel_sums(env, C, rows, z_out, rdelta, 1, NULL, NULL, t);
+        for (int c = 0; c < C; c++) s3[c] += t[c];
+        free(t);
+    }
+    /* R(I) = -sum[(z-mu)(Rz - mean Rz)] / (m^2 (var+eps)^1.5) */
+    channel_sums(env, C, rows, rz_in, NULL, 0, NULL, NULL, rmean);
+    for (int c = 0; c < C; c++) rmean[c] *= 1. / m;
+    channel_sums(env, C, rows, z_in, rz_in, 3, mean, rmean, rI);
+    for (int c = 0; c < C; c++) rI[c] *= -1. / (m * m * pow(eps + var[c], 1.5));
+    /* II = m*delta - sum delta - zhat * sum(delta*zhat) */
+    channel_sums(env, C, rows, delta, NULL, 0, NULL, NULL, d1);
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < C; c++)
+        for (long i = 0; i < rows; i++) {
+            long id = (long)c * rows + i;
+            double rII = rdelta[id] * m - s1[c] - s2[c] * rz_out[id] - s3[c] * z_out[id];
+            rII /= m * sqrt(eps + var[c]);
+            double II = delta[id] * m - d1[c] - s2[c] * z_out[id];
+            rdelta[id] = rII + II * rI[c];
+        }
+    free(s1); free(s2); free(s3); free(rmean); free(rI); free(d1);
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Convolution data gradient: functions/dev_backprop_convolution.cu:60-97,173-247        */
+/* ------------------------------------------------------------------------------------ */
+void ora_conv_dgrad(const double *delta, int dH, int dW, int dC, const double *filter, int k,
+                    int H, int W, int pad, int C, int N, double *out) {
+    long R = (long)N * H * W, K2 = (long)dC * k * k;
+    double *cols = xmalloc(R * K2);
+    double *wperm = xmalloc(K2 * C);
+    /* transposed im2col of delta, taps enumerated downwards (:86-95) */
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int ch = 0; ch < dC; ch++)
+        for (int n = 0; n < N; n++)
+            for (int col = 0; col < W; col++)
+                for (int row = 0; row < H; row++) {
+                    long r = (long)n * H * W + (long)col * H + row;
+                    const double *src = delta + ((long)ch * N + n) * dH * dW;
+                    long q = (long)ch * k * k;
+                    for (int c = col + pad; c > col + pad - k; c--)
+                        for (int rr = row + pad; rr > row + pad - k; rr--) {
+                            int ok = (c < dW) && (c >= 0) && (rr >= 0) && (rr < dH);
+                            cols[q * R + r] = ok ? src[(long)c * dH + rr] : 0.0;
+                            q++;
+                        }
+                }
+    /* weights [(k*k*C) x dC] -> [(k*k*dC) x C] (:215-217) */
+    reshape_matrix(filter, dC, C, k * k, wperm);
+    ora_gemm(0, 0, R, C, K2, 1.0, cols, R, wperm, K2, 0.0, out, R);
+    free(cols);
+    free(wperm);
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Softmax cross-entropy: functions/softmax_loss.cu:17-79,141-245,251-299                */
+/* ------------------------------------------------------------------------------------ */
+double ora_softmax_loss(const ORA_ENV *env, const double *logits, const double *target, int N,
+                        int classes, double *probs) {
+    int ref = env ? env->ref_softmax : 1;
+    double total = 0.0;
+    for (int r = 0; r < N; r++) {
+        const double *x = logits + (long)r * classes;
+        double *p = probs + (long)r * classes;
+        double mx = ref ? 0.0 : -DBL_MAX;
+        for (int i = 0; i < classes; i++)
+            if (mx < x[i]) mx = x[i];
+        double s = 0.0;
+        for (int i = 0; i < classes; i++) {
+            p[i] = exp(x[i] - mx);
+            s += p[i];
+        }
+        for (int i = 0; i < classes; i++) p[i] = p[i] / s + (ref ? 1e-10 : 0.0);
+        for (int i = 0; i < classes; i++)
+            if ((int)target[r] == i + 1) total += -log(p[i]);
+    }
+    double buf = total;
+    env_allreduce(env, &buf, 1);
+    return buf / ((double)N * env_world(env));
+}
+
+/* (p - onehot) / N_global : :215-245 */
+static void ce_error(const ORA_ENV *env, const double *probs, int N, int classes,
+                     const double *target, double *errors) {
+    double sc = 1. / ((double)N * env_world(env));
+    for (int r = 0; r < N; r++)
+        for (int c = 0; c < classes; c++) {
+            double v = probs[(long)r * classes + c];
+            if ((double)(c + 1) == target[r]) v -= 1.;
+            errors[(long)r * classes + c] = v * sc;
+        }
+}
+/* R{p - y} = p .* (Rz - sum_j p_j Rz_j) / N_global : :251-299 */
+static void ce_rop_error(const ORA_ENV *env, const double *rz, const double *probs, int N,
+                         int classes, double *rError) {
+    double sc = 1. / ((double)N * env_world(env));
+    for (int r = 0; r < N; r++) {
+        double s = 0.0;
+        for (int j = 0; j < classes; j++) s += probs[(long)r * classes + j] * rz[(long)r * classes + j];
+        for (int i = 0; i < classes; i++)
+            rError[(long)r * classes + i] =
+                probs[(long)r * classes + i] * (rz[(long)r * classes + i] - s) * sc;
+    }
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Forward: functions/cnn_forward.cu:48-382, eval_convolution.cu:52-267,                 */
+/* eval_gradient.cu:29-228                                                               */
+/* ------------------------------------------------------------------------------------ */
+static void add_channel_bias(double *x, const double *b, long rows, int C) {
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < C; c++)
+        for (long i = 0; i < rows; i++) x[(long)c * rows + i] += b[c];
+}
+static void add_column_bias(double *x, const double *b, int rows, int cols) {
+    for (int j = 0; j < cols; j++)
+        for (int i = 0; i < rows; i++) x[(long)j * rows + i] += b[i];
+}
+
+static const double *layer_input(const CNN_MODEL *m, const double *batch, const double *z, int l) {
+    if (l == 0) return batch;
+    return z + m->zOffsets[l] + m->convLayer[l - 1].outputOffset;
+}
+
+double ora_cnn_forward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                       const double *labels, const double *weights, int numClasses, double *z,
+                       double *probs, double *errors, int n) {
+    const int *wO = m->wOffsets, *bO = m->bOffsets, *zO = m->zOffsets;
+    for (int l = 0; l < m->cLayers; l++) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        const POOL_LAYER *p = &m->poolLayer[l];
+        const double *in = layer_input(m, batch, z, l);
+        double *out = z + zO[l + 1];
+        long M = (long)n * c->outHeight * c->outWidth;
+        long K = (long)c->kSize * c->kSize * c->inChannels;
+        long V = M * c->outChannels;
+        double *cols = xmalloc(M * K);
+        ora_im2col(in, n, c->inChannels, c->height, c->width, c->kSize, c->padding, c->stride, cols);
+        ora_gemm(0, 0, M, c->outChannels, K, 1.0, cols, M, weights + wO[l], K, 0.0, out, M);
+        free(cols);
+        if (m->bias != 0) add_channel_bias(out, weights + bO[l], M, c->outChannels);
+        double *actOut = out + c->activationOffset;
+        if (c->batchNorm != FITRE_NO_BATCH_NORM) {
+            double *bn = out + c->batchNormOffset;
+            ora_batch_norm_forward(env, out, c->outHeight, c->outWidth, c->outChannels, n, bn,
+                                   bn + c->meansOffset, bn + c->variancesOffset, BN_EPS);
+            memcpy(actOut, bn, sizeof(double) * (size_t)V);
+        } else {
+            memcpy(actOut, out, sizeof(double) * (size_t)V);
+        }
+        ora_activation(m->actFuns[l], actOut, V);
+        if (p->type != FITRE_NO_POOL)
+            ora_pool_forward(actOut, n, c->outChannels, c->outHeight, c->outWidth, p->pSize,
+                             p->stride, p->padding, p->type, out + c->poolOffset);
+    }
+    const CONV_LAYER *lc = &m->convLayer[m->cLayers - 1];
+    const POOL_LAYER *lp = &m->poolLayer[m->cLayers - 1];
+    conv_to_fc(z + zO[m->cLayers] + lc->outputOffset, lc->outChannels, n, lp->outHeight,
+               lp->outWidth);
+    int outputOffset = lc->outputOffset;
+    for (int l = 0; l < m->lLayers; l++) {
+        if (l != 0) outputOffset = 0;
+        const FC_LAYER *f = &m->fcLayer[l];
+        const double *zin = z + zO[l + m->cLayers] + outputOffset;
+        double *out = z + zO[l + 1 + m->cLayers];
+        ora_gemm(0, 0, f->out, n, f->in, 1.0, weights + wO[l + m->cLayers], f->out, zin, f->in,
+                 0.0, out, f->out);
+        if (m->bias != 0) add_column_bias(out, weights + bO[l + m->cLayers], f->out, n);
+        memcpy(out + (long)f->out * n, out, sizeof(double) * (size_t)f->out * n);
+        ora_activation(f->actFun, out, (long)f->out * n);
+    }
+    const double *logits = (m->lLayers == 0) ? z + zO[m->cLayers] + lc->outputOffset
+                                             : z + zO[m->lLayers + m->cLayers];
+    double loss = ora_softmax_loss(env, logits, labels, n, numClasses, probs);
+    ce_error(env, probs, n, numClasses, labels, errors);
+    return loss;
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Backward: functions/cnn_backward.cu:76-857                                            */
+/* ------------------------------------------------------------------------------------ */
+void ora_cnn_backward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                      const double *weights, const double *z, double *gradient, double *dx,
+                      const double *errors, int n) {
+    const int *wO = m->wOffsets, *bO = m->bOffsets, *zO = m->zOffsets;
+    int cL = m->cLayers, lL = m->lLayers;
+    long md = m->maxDeltaSize;
+    { /* the first conv layer's errors can be larger than any z block when its input is wide */
+        for (int l = 0; l < cL; l++) {
+            long v = (long)n * m->convLayer[l].height * m->convLayer[l].width * m->convLayer[l].inChannels;
+            if (v > md) md = v;
+        }
+    }
+    double *delta = xmalloc(md), *delta_new = xmalloc(md), *tmp;
+    const CONV_LAYER *lc = &m->convLayer[cL - 1];
+    const POOL_LAYER *lp = &m->poolLayer[cL - 1];
+    int last_out = (lL > 0) ? m->fcLayer[lL - 1].out : 0;
+    memcpy(delta, errors, sizeof(double) * (size_t)(lL > 0 ? (long)last_out * n
+                              : (long)lc->outChannels * lp->outHeight * lp->outWidth * n));
+
+    for (int f = lL - 1; f >= 0; f--) { /* :111-280 */
+        const FC_LAYER *l = &m->fcLayer[f];
+        const double *zl = z + zO[f + cL + 1];
+        act_backward(l->actFun, delta, zl + (long)l->out * n, zl, (long)l->out * n);
+        const double *zin = z + zO[f + cL] + ((f == 0) ? lc->outputOffset : 0);
+        ora_gemm(0, 1, l->out, l->in, n, 1.0, delta, l->out, zin, l->in, 0.0,
+                 gradient + wO[f + cL], l->out);
+        if (m->bias != 0) {
+            double *db = gradient + bO[f + cL];
+            for (int i = 0; i < l->out; i++) {
+                double s = 0.0;
+                for (int j = 0; j < n; j++) s += delta[(long)j * l->out + i];
+                db[i] = s;
+            }
+        }
+        memcpy(dx + zO[f + cL + 1], delta, sizeof(double) * (size_t)l->out * n);
+        ora_gemm(1, 0, l->in, n, l->out, 1.0, weights + wO[f + cL], l->out, delta, l->out, 0.0,
+                 delta_new, l->in);
+        tmp = delta_new; delta_new = delta; delta = tmp;
+    }
+    if (lL > 0) fc_to_conv(delta, lc->outChannels, n, lp->outHeight, lp->outWidth); /* :310-326 */
+
+    for (int c = cL - 1; c >= 0; c--) { /* :355-852 */
+        const CONV_LAYER *l = &m->convLayer[c];
+        const POOL_LAYER *p = &m->poolLayer[c];
+        const double *zl = z + zO[c + 1];
+        double *dxl = dx + zO[c + 1];
+        long V = (long)n * l->activationVolumn;
+        long M = (long)p->height * p->width * n;
+        switch (p->type) { /* :434-493 */
+            case FITRE_MAX_POOL:
+                ora_max_pool_backward(delta, zl + l->activationOffset, l->outChannels, p->height,
+                                      p->width, p->pSize, p->stride, p->padding, p->outHeight,
+                                      p->outWidth, n, delta_new);
+                break;
+            case FITRE_AVG_POOL:
+                ora_avg_pool_backward(delta, p->outHeight, l->outChannels, p->pSize, n, delta_new);
+                break;
+            default: memcpy(delta_new, delta, sizeof(double) * (size_t)V); break;
+        }
+        memcpy(dxl, delta_new, sizeof(double) * (size_t)V); /* :513 */
+        const double *zin = (l->batchNorm != FITRE_NO_BATCH_NORM) ? zl + l->batchNormOffset : zl;
+        act_backward(m->actFuns[c], delta_new, zin, zl + l->activationOffset, V); /* :523-592 */
+        memcpy(dxl + l->activationOffset, delta_new, sizeof(double) * (size_t)V); /* :605 */
+        if (l->batchNorm != FITRE_NO_BATCH_NORM) { /* :643-659 */
+            const double *bn = zl + l->batchNormOffset;
+            ora_batch_norm_backward(env, delta_new, l->outHeight, l->outWidth, l->outChannels, n,
+                                    bn + l->variancesOffset, bn, BN_EPS, delta);
+            memcpy(dxl + l->batchNormOffset, delta, sizeof(double) * (size_t)V);
+            memcpy(delta_new, delta, sizeof(double) * (size_t)V);
+        }
+        if (m->bias != 0) { /* :662-689 */
+            double *db = gradient + bO[c];
+#pragma omp parallel for schedule(static)
+            for (int ch = 0; ch < l->outChannels; ch++) {
+                double s = 0.0;
+                for (long i = 0; i < M; i++) s += delta_new[(long)ch * M + i];
+                db[ch] = s;
+            }
+        }
+        const double *in = layer_input(m, batch, z, c);
+        long K = (long)l->kSize * l->kSize * l->inChannels;
+        double *cols = xmalloc(M * K);
+        ora_im2col(in, n, l->inChannels, l->height, l->width, l->kSize, l->padding, l->stride, cols);
+        ora_gemm(1, 0, K, l->outChannels, M, 1.0, cols, M, delta_new, M, 0.0, gradient + wO[c], K);
+        free(cols);
+        if (c != 0) /* :803-819 */
+            ora_conv_dgrad(delta_new, p->height, p->width, l->outChannels, weights + wO[c],
+                           l->kSize, l->height, l->width, l->padding, l->inChannels, n, delta);
+    }
+    free(delta);
+    free(delta_new);
+}
+
+/* functions/cnn_gradient.cu:12-63 */
+double ora_cnn_gradient(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                        const double *labels, const double *weights, int numClasses, double *z,
+                        double *dx, double *probs, double *errors, double *gradient, int n,
+                        double weightDecay) {
+    double loss = ora_cnn_forward(env, m, batch, labels, weights, numClasses, z, probs, errors, n);
+    ora_cnn_backward(env, m, batch, weights, z, gradient, dx, errors, n);
+    env_allreduce(env, gradient, m->pSize);
+    axpy(m->pSize, weightDecay, weights, gradient);
+    return loss;
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* R-forward: functions/cnn_hv_forward.cu:53-222, eval_convolution.cu:285-539,           */
+/* rop_fc_layer.cu:34-133                                                                */
+/* ------------------------------------------------------------------------------------ */
+void ora_cnn_rop_forward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                         const double *weights, const double *z, const double *vector,
+                         double *rz, int n) {
+    const int *wO = m->wOffsets, *bO = m->bOffsets, *zO = m->zOffsets;
+    for (int l = 0; l < m->cLayers; l++) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        const POOL_LAYER *p = &m->poolLayer[l];
+        const double *zl = z + zO[l + 1];
+        double *rzl = rz + zO[l + 1];
+        long M = (long)n * c->outHeight * c->outWidth;
+        long K = (long)c->kSize * c->kSize * c->inChannels;
+        long V = M * c->outChannels;
+        const double *in = layer_input(m, batch, z, l);
+        double *cols = xmalloc(M * K);
+        ora_im2col(in, n, c->inChannels, c->height, c->width, c->kSize, c->padding, c->stride, cols);
+        ora_gemm(0, 0, M, c->outChannels, K, 1.0, cols, M, vector + wO[l], K, 0.0, rzl, M);
+        if (l > 0) {
+            const double *rin = rz + zO[l] + m->convLayer[l - 1].outputOffset;
+            ora_im2col(rin, n, c->inChannels, c->height, c->width, c->kSize, c->padding, c->stride, cols);
+            ora_gemm(0, 0, M, c->outChannels, K, 1.0, cols, M, weights + wO[l], K, 1.0, rzl, M);
+        }
+        free(cols);
+        if (m->bias != 0) add_channel_bias(rzl, vector + bO[l], M, c->outChannels);
+        double *actOut = rzl + c->activationOffset;
+        const double *zin = zl;
+        if (c->batchNorm != FITRE_NO_BATCH_NORM) {
+            const double *bn = zl + c->batchNormOffset;
+            ora_rop_batch_norm_forward(env, zl, bn + c->meansOffset, bn + c->variancesOffset, rzl,
+                                       BN_EPS, c->outHeight, c->outWidth, c->outChannels, n,
+                                       rzl + c->batchNormOffset);
+            memcpy(actOut, rzl + c->batchNormOffset, sizeof(double) * (size_t)V);
+            zin = bn;
+        } else {
+            memcpy(actOut, rzl, sizeof(double) * (size_t)V);
+        }
+        act_backward(m->actFuns[l], actOut, zin, zl + c->activationOffset, V);
+        if (p->type == FITRE_MAX_POOL)
+            ora_rop_max_pool(actOut, zl + c->activationOffset, n, c->outChannels, c->outHeight,
+                             c->outWidth, p->pSize, p->stride, p->padding, rzl + c->poolOffset);
+        else if (p->type == FITRE_AVG_POOL)
+            ora_pool_forward(actOut, n, c->outChannels, c->outHeight, c->outWidth, p->pSize,
+                             p->stride, p->padding, FITRE_AVG_POOL, rzl + c->poolOffset);
+    }
+    const CONV_LAYER *lc = &m->convLayer[m->cLayers - 1];
+    const POOL_LAYER *lp = &m->poolLayer[m->cLayers - 1];
+    conv_to_fc(rz + zO[m->cLayers] + lc->outputOffset, lc->outChannels, n, lp->outHeight,
+               lp->outWidth);
+    int outputOffset = lc->outputOffset;
+    for (int l = 0; l < m->lLayers; l++) {
+        if (l > 0) outputOffset = 0;
+        const FC_LAYER *f = &m->fcLayer[l];
+        const double *zin = z + zO[l + m->cLayers] + outputOffset;
+        const double *rzin = rz + zO[l + m->cLayers] + outputOffset;
+        const double *z1 = z + zO[l + 1 + m->cLayers];
+        double *out = rz + zO[l + 1 + m->cLayers];
+        ora_gemm(0, 0, f->out, n, f->in, 1.0, vector + wO[l + m->cLayers], f->out, zin, f->in, 0.0,
+                 out, f->out);
+        ora_gemm(0, 0, f->out, n, f->in, 1.0, weights + wO[l + m->cLayers], f->out, rzin, f->in,
+                 1.0, out, f->out);
+        if (m->bias != 0) add_column_bias(out, vector + bO[l + m->cLayers], f->out, n);
+        memcpy(out + (long)f->out * n, out, sizeof(double) * (size_t)f->out * n);
+        act_backward(f->actFun, out, z1 + (long)f->out * n, z1, (long)f->out * n);
+    }
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* R-backward: functions/cnn_hv_backward.cu:70-912                                       */
+/* ------------------------------------------------------------------------------------ */
+void ora_cnn_rop_backward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                          const double *weights, const double *z, const double *dx,
+                          const double *errors, double *rError, const double *rz,
+                          const double *vector, double *hv, int n) {
+    const int *wO = m->wOffsets, *bO = m->bOffsets, *zO = m->zOffsets;
+    int cL = m->cLayers, lL = m->lLayers;
+    const CONV_LAYER *lc = &m->convLayer[cL - 1];
+    const POOL_LAYER *lp = &m->poolLayer[cL - 1];
+    long md = m->maxDeltaSize;
+    for (int l = 0; l < cL; l++) {
+        long v = (long)n * m->convLayer[l].height * m->convLayer[l].width * m->convLayer[l].inChannels;
+        if (v > md) md = v;
+    }
+    double *t1 = xmalloc(md), *t2 = xmalloc(md);
+
+    for (int f = lL - 1; f >= 0; f--) { /* :153-395 */
+        const FC_LAYER *l = &m->fcLayer[f];
+        int outputOffset = (f == 0) ? lc->outputOffset : 0;
+        const double *zl = z + zO[cL + f + 1];
+        const double *rzl = rz + zO[cL + f + 1];
+        long cnt = (long)l->out * n;
+        if (l->actFun != FITRE_CNN_ACT_NONE && l->actFun != FITRE_ACT_LINEAR) {
+            /* errors entering this activation: loss errors (last layer) or W_{f+1}' dx_{f+1} */
+            const double *din = errors;
+            if (f != lL - 1) {
+                const FC_LAYER *ll = &m->fcLayer[f + 1];
+                ora_gemm(1, 0, ll->in, n, ll->out, 1.0, weights + wO[cL + f + 1], ll->out,
+                         dx + zO[cL + f + 2], ll->out, 0.0, t1, ll->in);
+                din = t1;
+            }
+            act_rop_backward(l->actFun, rError, din, rzl + cnt, zl + cnt, zl, cnt);
+        }
+        /* R dW = Rdelta z' + delta Rz' */
+        ora_gemm(0, 1, l->out, l->in, n, 1.0, rError, l->out, z + zO[cL + f] + outputOffset,
+                 l->in, 0.0, hv + wO[cL + f], l->out);
+        ora_gemm(0, 1, l->out, l->in, n, 1.0, dx + zO[cL + f + 1], l->out,
+                 rz + zO[cL + f] + outputOffset, l->in, 1.0, hv + wO[cL + f], l->out);
+        if (m->bias != 0) {
+            double *db = hv + bO[cL + f];
+            for (int i = 0; i < l->out; i++) {
+                double s = 0.0;
+                for (int j = 0; j < n; j++) s += rError[(long)j * l->out + i];
+                db[i] = s;
+            }
+        }
+        /* Rdelta <- W' Rdelta + V' delta */
+        ora_gemm(1, 0, l->in, n, l->out, 1.0, weights + wO[cL + f], l->out, rError, l->out, 0.0,
+                 t2, l->in);
+        ora_gemm(1, 0, l->in, n, l->out, 1.0, vector + wO[cL + f], l->out, dx + zO[cL + f + 1],
+                 l->out, 1.0, t2, l->in);
+        memcpy(rError, t2, sizeof(double) * (size_t)l->in * n);
+    }
+    if (lL > 0) fc_to_conv(rError, lc->outChannels, n, lp->outHeight, lp->outWidth); /* :414-427 */
+
+    for (int c = cL - 1; c >= 0; c--) { /* :436-907 */
+        const CONV_LAYER *l = &m->convLayer[c];
+        const POOL_LAYER *p = &m->poolLayer[c];
+        const double *zl = z + zO[c + 1], *rzl = rz + zO[c + 1], *dxl = dx + zO[c + 1];
+        long V = (long)n * l->activationVolumn;
+        long M = (long)p->height * p->width * n;
+        long K = (long)l->kSize * l->kSize * l->inChannels;
+        if (p->type == FITRE_MAX_POOL) { /* :498-553 */
+            ora_max_pool_backward(rError, zl + l->activationOffset, l->outChannels, p->height,
+                                  p->width, p->pSize, p->stride, p->padding, p->outHeight,
+                                  p->outWidth, n, t1);
+            memcpy(rError, t1, sizeof(double) * (size_t)V);
+        } else if (p->type == FITRE_AVG_POOL) {
+            ora_avg_pool_backward(rError, p->outHeight, l->outChannels, p->pSize, n, t1);
+            memcpy(rError, t1, sizeof(double) * (size_t)V);
+        }
+        int bn = l->batchNorm != FITRE_NO_BATCH_NORM;
+        const double *zin = bn ? zl + l->batchNormOffset : zl;
+        const double *rzin = bn ? rzl + l->batchNormOffset : rzl;
+        act_rop_backward(m->actFuns[c], rError, dxl, rzin, zin, zl + l->activationOffset, V); /* :566-679 */
+        if (bn) { /* :693-713 */
+            const double *b = zl + l->batchNormOffset;
+            ora_rop_batch_norm_backward(env, zl, b, rzl, rzl + l->batchNormOffset,
+                                        dxl + l->activationOffset, rError, BN_EPS,
+                                        b + l->meansOffset, b + l->variancesOffset, l->outHeight,
+                                        l->outWidth, l->outChannels, n);
+        }
+        const double *dprev = bn ? dxl + l->batchNormOffset : dxl + l->activationOffset;
+        double *cols = xmalloc(M * K);
+        if (c != 0) { /* :727-761 */
+            ora_im2col(rz + zO[c] + m->convLayer[c - 1].outputOffset, n, l->inChannels, l->height,
+                       l->width, l->kSize, l->padding, l->stride, cols);
+            ora_gemm(1, 0, K, l->outChannels, M, 1.0, cols, M, dprev, M, 0.0, hv + wO[c], K);
+        } else {
+            memset(hv + wO[c], 0, sizeof(double) * (size_t)(K * l->outChannels));
+        }
+        ora_im2col(layer_input(m, batch, z, c), n, l->inChannels, l->height, l->width, l->kSize,
+                   l->padding, l->stride, cols);
+        ora_gemm(1, 0, K, l->outChannels, M, 1.0, cols, M, rError, M, 1.0, hv + wO[c], K); /* :776-803 */
+        free(cols);
+        if (m->bias != 0) { /* :821-834 */
+            double *db = hv + bO[c];
+#pragma omp parallel for schedule(static)
+            for (int ch = 0; ch < l->outChannels; ch++) {
+                double s = 0.0;
+                for (long i = 0; i < M; i++) s += rError[(long)ch * M + i];
+                db[ch] = s;
+            }
+        }
+        if (c != 0) { /* :854-898 */
+            long R = (long)l->height * l->width * l->inChannels * n;
+            ora_conv_dgrad(rError, p->height, p->width, l->outChannels, weights + wO[c], l->kSize,
+                           l->height, l->width, l->padding, l->inChannels, n, t1);
+            ora_conv_dgrad(dprev, p->height, p->width, l->outChannels, vector + wO[c], l->kSize,
+                           l->height, l->width, l->padding, l->inChannels, n, rError);
+            axpy(R, 1.0, t1, rError);
+        }
+    }
+    free(t1);
+    free(t2);
+}
+
+/* functions/cnn_hessian_vec.cu:18-122.  `rz` (zSize) is caller scratch. */
+void ora_cnn_hv(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                const double *weights, int numClasses, const double *z, const double *probs,
+                const double *errors, const double *dx, const double *vector, double *hv,
+                double *rz, int n) {
+    long md = m->maxDeltaSize;
+    for (int l = 0; l < m->cLayers; l++) {
+        long v = (long)n * m->convLayer[l].height * m->convLayer[l].width * m->convLayer[l].inChannels;
+        if (v > md) md = v;
+    }
+    double *rError = xmalloc(md);
+    ora_cnn_rop_forward(env, m, batch, weights, z, vector, rz, n);
+    const double *logitsR;
+    if (m->lLayers == 0)
+        logitsR = rz + m->zOffsets[m->cLayers] + m->convLayer[m->cLayers - 1].outputOffset;
+    else
+        logitsR = rz + m->zOffsets[m->cLayers + m->lLayers];
+    ce_rop_error(env, logitsR, probs, n, numClasses, rError);
+    ora_cnn_rop_backward(env, m, batch, weights, z, dx, errors, rError, rz, vector, hv, n);
+    env_allreduce(env, hv, m->pSize);
+    free(rError);
+}
+
+/* functions/model_reduction.cu:20-93; the weight-decay term is weightDecay * vector
+ * (the PyTorch twin pytorch/peng/utils.py:77), identical to the reference at weightDecay 0. */
+double ora_quadratic_model(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                           const double *weights, int numClasses, const double *z,
+                           const double *probs, const double *errors, const double *dx,
+                           const double *gradient, double *vector, double delta, int n,
+                           double weightDecay) {
+    long P = m->pSize;
+    double *hv = xmalloc(P), *rz = xmalloc(m->zSize);
+    ora_cnn_hv(env, m, batch, weights, numClasses, z, probs, errors, dx, vector, hv, rz, n);
+    axpy(P, weightDecay, vector, hv);
+    double vHv = dot(P, hv, vector);
+    double nrm = sqrt(dot(P, vector, vector));
+    double gv = dot(P, gradient, vector);
+    double alpha, val;
+    if (vHv < 0) {
+        alpha = delta / nrm;
+        val = 0.5 * vHv * alpha * alpha - gv * alpha;
+    } else {
+        double step = gv / (vHv + 1e-6);
+        double lim = delta / (nrm + 1e-16);
+        alpha = step < lim ? step : lim;
+        val = vHv * 0.5 * alpha * alpha - gv * alpha;
+    }
+    for (long i = 0; i < P; i++) vector[i] *= alpha;
+    free(hv);
+    free(rz);
+    return val;
+}
+
+/* Steihaug-CG for min g'p + 0.5 p'Hp, ||p|| <= delta.  Algorithm: solvers/cg_steihaug.c:28-260;
+ * constants (the 1e-6 guards, ||r||^2 < tol test) follow its CNN twin
+ * pytorch/peng/utils.py:104-165, which is what the reference runs on CNNs. */
+void ora_cg_steihaug(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                     const double *weights, int numClasses, const double *z,
+                     const double *probs, const double *errors, const double *dx,
+                     const double *gradient, double *p, int n, FITRE_CG_PARAMS *prm) {
+    long P = m->pSize;
+    double *zs = xmalloc(P), *rs = xmalloc(P), *ds = xmalloc(P), *Hd = xmalloc(P);
+    double *rz = xmalloc(m->zSize), *zn = xmalloc(P);
+    double delta = prm->delta, wd = prm->weightDecay;
+    for (long i = 0; i < P; i++) {
+        zs[i] = 0.0;
+        rs[i] = gradient[i];
+        ds[i] = -gradient[i];
+    }
+    int flag = FITRE_CG_MAX_ITERS, it = 0, hvc = 0, done = 0;
+    for (it = 0; it < prm->maxIterations; it++) {
+        ora_cnn_hv(env, m, batch, weights, numClasses, z, probs, errors, dx, ds, Hd, rz, n);
+        hvc++;
+        axpy(P, wd, ds, Hd);
+        double dHd = dot(P, Hd, ds);
+        if (dHd <= 0.0) {
+            double ac = dot(P, ds, ds), bc = 2 * dot(P, zs, ds), cc = dot(P, zs, zs) - delta * delta;
+            double tau = (-bc + sqrt(bc * bc - 4 * ac * cc)) / (2 * ac + 1e-6);
+            for (long i = 0; i < P; i++) p[i] = zs[i] + tau * ds[i];
+            flag = FITRE_CG_NEG_CURVATURE;
+            done = 1;
+            break;
+        }
+        double rr = dot(P, rs, rs);
+        double alpha = rr / (dHd + 1e-6);
+        for (long i = 0; i < P; i++) zn[i] = zs[i] + alpha * ds[i];
+        if (sqrt(dot(P, zn, zn)) >= delta) {
+            double ac = dot(P, ds, ds), bc = 2 * dot(P, zs, ds), cc = dot(P, zs, zs) - delta * delta;
+            double tau = (-bc + sqrt(bc * bc - 4 * ac * cc)) / (2 * ac + 1e-6);
+            for (long i = 0; i < P; i++) p[i] = zs[i] + tau * ds[i];
+            flag = FITRE_CG_HIT_BOUNDARY;
+            done = 1;
+            break;
+        }
+        memcpy(zs, zn, sizeof(double) * (size_t)P);
+        axpy(P, alpha, Hd, rs);
+        double rn = dot(P, rs, rs);
+        if (rn < prm->tolerance) {
+            memcpy(p, zs, sizeof(double) * (size_t)P);
+            flag = FITRE_CG_CONVERGED;
+            done = 1;
+            break;
+        }
+        double beta = rn / (rr + 1e-6);
+        for (long i = 0; i < P; i++) ds[i] = -rs[i] + beta * ds[i];
+    }
+    /* pytorch/peng/utils.py:156-158: an exit taken on the very last iteration is also
+     * reported as "Maximum Iterations" and returns the last accepted iterate. */
+    if (!done) it = prm->maxIterations - 1;
+    if (it == prm->maxIterations - 1) {
+        memcpy(p, zs, sizeof(double) * (size_t)P);
+        flag = FITRE_CG_MAX_ITERS;
+    }
+    ora_cnn_hv(env, m, batch, weights, numClasses, z, probs, errors, dx, p, Hd, rz, n);
+    hvc++;
+    prm->modelValue = 0.5 * dot(P, Hd, p) + dot(P, p, gradient) + 0.5 * wd * dot(P, p, p);
+    prm->iterations = it + 1;
+    prm->flag = flag;
+    prm->hvCalls = hvc;
+    free(zs); free(rs); free(ds); free(Hd); free(rz); free(zn);
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* KFAC factors: solvers/kfac_utils.cu:7-55, kfac_inverses.cu:450-630,759-857            */
+/* ------------------------------------------------------------------------------------ */
+int ora_kfac_storage_indices(const CNN_MODEL *m, FITRE_KFAC_INFO *info) {
+    for (int i = 0; i < FITRE_MAX_LAYERS; i++) info->OmegaZOffsets[i] = info->LambdaGOffsets[i] = 0;
+    long o = 0, g = 0;
+    for (int i = 0; i < m->cLayers; i++) {
+        long K = (long)m->convLayer[i].inChannels * m->convLayer[i].kSize * m->convLayer[i].kSize;
+        o += (K + 1) * (K + 1);
+        g += (long)m->convLayer[i].outChannels * m->convLayer[i].outChannels;
+        if (o > INT_MAX || g > INT_MAX) return 2;
+        info->OmegaZOffsets[i + 1] = (int)o;
+        info->LambdaGOffsets[i + 1] = (int)g;
+    }
+    for (int i = 0; i < m->lLayers; i++) {
+        long in = m->fcLayer[i].in, out = m->fcLayer[i].out;
+        o += (in + 1) * (in + 1);
+        g += out * out;
+        if (o > INT_MAX || g > INT_MAX) return 2;
+        info->OmegaZOffsets[m->cLayers + i + 1] = (int)o;
+        info->LambdaGOffsets[m->cLayers + i + 1] = (int)g;
+    }
+    info->OmegaZSize = (int)o;
+    info->LambdaGSize = (int)g;
+    return 0;
+}
+
+/* A factors, undamped: conv (1/N) P~'P~ with P~ = [im2col(X)/(Ho*Wo), 1] (:515-540);
+ * FC (1/N) z~ z~' with z~ = [z; 1] (:592-622).  N is the global batch. */
+void ora_kfac_omega_z(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                      const double *z, int n, double *omegaZ, const FITRE_KFAC_INFO *info) {
+    double Ng = (double)n * env_world(env);
+    for (int l = 0; l < m->cLayers; l++) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        long M = (long)n * c->outHeight * c->outWidth;
+        long K = (long)c->inChannels * c->kSize * c->kSize;
+        long Kb = K + (m->bias != 0 ? 1 : 0);
+        double *cols = xmalloc(M * Kb);
+        ora_im2col(layer_input(m, batch, z, l), n, c->inChannels, c->height, c->width, c->kSize,
+                   c->padding, c->stride, cols);
+        double sc = 1. / (double)(c->outHeight * c->outWidth);
+        for (long i = 0; i < M * K; i++) cols[i] *= sc;
+        if (m->bias != 0)
+            for (long i = 0; i < M; i++) cols[K * M + i] = 1.0;
+        double *A = omegaZ + info->OmegaZOffsets[l];
+        ora_gemm(1, 0, Kb, Kb, M, 1.0, cols, M, cols, M, 0.0, A, Kb);
+        env_allreduce(env, A, Kb * Kb);
+        for (long i = 0; i < Kb * Kb; i++) A[i] *= 1. / Ng;
+        free(cols);
+    }
+    const CONV_LAYER *lc = &m->convLayer[m->cLayers - 1];
+    for (int l = 0; l < m->lLayers; l++) {
+        const FC_LAYER *f = &m->fcLayer[l];
+        const double *zin = z + m->zOffsets[m->cLayers + l] + (l == 0 ? lc->outputOffset : 0);
+        long R = f->in + (m->bias != 0 ? 1 : 0);
+        double *zm = xmalloc(R * n);
+        for (int j = 0; j < n; j++) {
+            memcpy(zm + (long)j * R, zin + (long)j * f->in, sizeof(double) * (size_t)f->in);
+            if (m->bias != 0) zm[(long)j * R + f->in] = 1.0;
+        }
+        double *A = omegaZ + info->OmegaZOffsets[m->cLayers + l];
+        ora_gemm(0, 1, R, R, n, 1.0, zm, R, zm, R, 0.0, A, R);
+        env_allreduce(env, A, R * R);
+        for (long i = 0; i < R * R; i++) A[i] *= 1. / Ng;
+        free(zm);
+    }
+}
+
+/* G factors, undamped: conv (N*Ho*Wo) d'd (:808-816), FC N d d' (:839-849). */
+void ora_kfac_lambda_delta(const ORA_ENV *env, const CNN_MODEL *m, const double *dx, int n,
+                           double *lambdaG, const FITRE_KFAC_INFO *info) {
+    double Ng = (double)n * env_world(env);
+    for (int l = 0; l < m->cLayers; l++) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        const double *d = dx + m->zOffsets[l + 1] +
+                          (c->batchNorm == FITRE_NO_BATCH_NORM ? c->activationOffset : c->batchNormOffset);
+        long M = (long)n * c->outHeight * c->outWidth;
+        double *G = lambdaG + info->LambdaGOffsets[l];
+        ora_gemm(1, 0, c->outChannels, c->outChannels, M, 1.0, d, M, d, M, 0.0, G, c->outChannels);
+        env_allreduce(env, G, (long)c->outChannels * c->outChannels);
+        double sc = (double)c->outHeight * c->outWidth * Ng;
+        for (long i = 0; i < (long)c->outChannels * c->outChannels; i++) G[i] *= sc;
+    }
+    for (int l = 0; l < m->lLayers; l++) {
+        const FC_LAYER *f = &m->fcLayer[l];
+        const double *d = dx + m->zOffsets[m->cLayers + l + 1];
+        double *G = lambdaG + info->LambdaGOffsets[m->cLayers + l];
+        ora_gemm(0, 1, f->out, f->out, n, 1.0, d, f->out, d, f->out, 0.0, G, f->out);
+        env_allreduce(env, G, (long)f->out * f->out);
+        for (long i = 0; i < (long)f->out * f->out; i++) G[i] *= Ng;
+    }
+}

@@ -1,0 +1,111 @@
+/*
+ * fitre_oracle.h -- CPU restatement of FITRE's CNN gradient / Hessian-vector /
+ * KFAC-factor path.  TEST INFRASTRUCTURE ONLY: it is the checker the CUDA library is
+ * compared against (tests, the smoke check and the benchmark's CPU baseline leg); the
+ * product never links or calls it.
+ *
+ * Every function follows the operation order of the reference's CUDA host code, with
+ * the GPU kernels and cuBLAS calls replaced by plain loops (OpenMP over independent
+ * outputs).  All buffers are HOST memory in the reference's layouts.
+ */
+#ifndef FITRE_ORACLE_H
+#define FITRE_ORACLE_H
+
+#include "../include/fitre_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Sum-all-reduce hook used to emulate data-parallel ranks (NULL = single rank). */
+typedef void (*ora_allreduce_fn)(double *buf, long n, void *user);
+
+typedef struct ora_env {
+    int ref_softmax;        /* 1: max-shift starts at 0 and probs += 1e-10 (softmax_loss.cu:24-27,55) */
+    int world;              /* data-parallel ranks; N_global = world * curBatchSize */
+    ora_allreduce_fn allreduce;
+    void *user;
+} ORA_ENV;
+
+void ora_env_default(ORA_ENV *env);
+
+/* model set-up: nn/utils.c:12-172, nn/read_vgg.c:25-120 */
+int ora_model_finalize(CNN_MODEL *m);
+long ora_model_zsize64(const CNN_MODEL *m);
+
+/* unit operators (each cites its reference source in the .c file) */
+void ora_im2col(const double *x, int N, int C, int H, int W, int k, int pad, int stride,
+                double *cols);
+void ora_im2col_index(int N, int C, int H, int W, int k, int pad, int stride, long *src_index);
+void ora_gemm(int transA, int transB, long m, long n, long k, double alpha, const double *A,
+              long lda, const double *B, long ldb, double beta, double *C, long ldc);
+void ora_pool_forward(const double *in, int N, int C, int H, int W, int ks, int stride, int pad,
+                      int type, double *out);
+void ora_max_pool_argmax(const double *act, int N, int C, int H, int W, int ks, int stride,
+                         int pad, int *argmax);
+void ora_max_pool_backward(const double *delta, const double *act, int C, int H, int W, int ks,
+                           int stride, int pad, int Hp, int Wp, int N, double *out);
+void ora_avg_pool_backward(const double *delta, int Hp, int C, int ks, int N, double *out);
+void ora_rop_max_pool(const double *rz, const double *zact, int N, int C, int H, int W, int ks,
+                      int stride, int pad, double *out);
+void ora_batch_norm_forward(const ORA_ENV *env, const double *in, int H, int W, int C, int N,
+                            double *out, double *mean, double *var, double eps);
+void ora_batch_norm_backward(const ORA_ENV *env, const double *delta, int H, int W, int C,
+                             int N, const double *var, const double *zhat, double eps,
+                             double *out);
+void ora_rop_batch_norm_forward(const ORA_ENV *env, const double *z, const double *mean,
+                                const double *var, const double *rz_in, double eps, int H,
+                                int W, int C, int N, double *rz_out);
+void ora_rop_batch_norm_backward(const ORA_ENV *env, const double *z_in, const double *z_out,
+                                 const double *rz_in, const double *rz_out, const double *delta,
+                                 double *rdelta, double eps, const double *mean,
+                                 const double *var, int H, int W, int C, int N);
+void ora_conv_dgrad(const double *delta, int dH, int dW, int dC, const double *filter, int k,
+                    int H, int W, int pad, int C, int N, double *out);
+void ora_activation(int act, double *x, long n);
+double ora_softmax_loss(const ORA_ENV *env, const double *logits, const double *target, int N,
+                        int classes, double *probs);
+
+/* whole-network passes */
+double ora_cnn_forward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                       const double *labels, const double *weights, int numClasses, double *z,
+                       double *probs, double *errors, int n);
+void ora_cnn_backward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                      const double *weights, const double *z, double *gradient, double *dx,
+                      const double *errors, int n);
+double ora_cnn_gradient(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                        const double *labels, const double *weights, int numClasses, double *z,
+                        double *dx, double *probs, double *errors, double *gradient, int n,
+                        double weightDecay);
+void ora_cnn_rop_forward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                         const double *weights, const double *z, const double *vector,
+                         double *rz, int n);
+void ora_cnn_rop_backward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                          const double *weights, const double *z, const double *dx,
+                          const double *errors, double *rError, const double *rz,
+                          const double *vector, double *hv, int n);
+void ora_cnn_hv(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                const double *weights, int numClasses, const double *z, const double *probs,
+                const double *errors, const double *dx, const double *vector, double *hv,
+                double *rz, int n);
+double ora_quadratic_model(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                           const double *weights, int numClasses, const double *z,
+                           const double *probs, const double *errors, const double *dx,
+                           const double *gradient, double *vector, double delta, int n,
+                           double weightDecay);
+void ora_cg_steihaug(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                     const double *weights, int numClasses, const double *z,
+                     const double *probs, const double *errors, const double *dx,
+                     const double *gradient, double *p, int n, FITRE_CG_PARAMS *params);
+
+/* KFAC factors */
+int ora_kfac_storage_indices(const CNN_MODEL *m, FITRE_KFAC_INFO *info);
+void ora_kfac_omega_z(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
+                      const double *z, int n, double *omegaZ, const FITRE_KFAC_INFO *info);
+void ora_kfac_lambda_delta(const ORA_ENV *env, const CNN_MODEL *m, const double *dx, int n,
+                           double *lambdaG, const FITRE_KFAC_INFO *info);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,113 @@
+"""ctypes binding of the CPU oracle (oracle/libfitre_oracle.so) for the tests.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg may use this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+from fitre_b200 import _structs as S
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ORACLE_DIR = os.path.join(os.path.dirname(_HERE), "oracle")
+_LIB = None
+
+dp = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
+ALLREDUCE_FN = C.CFUNCTYPE(None, C.POINTER(C.c_double), C.c_long, C.c_void_p)
+
+
+class ORA_ENV(C.Structure):
+    _fields_ = [("ref_softmax", C.c_int), ("world", C.c_int),
+                ("allreduce", ALLREDUCE_FN), ("user", C.c_void_p)]
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        so = os.path.join(_ORACLE_DIR, "libfitre_oracle.so")
+        src = os.path.join(_ORACLE_DIR, "fitre_oracle.c")
+        if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+            subprocess.check_call(["make", "-C", _ORACLE_DIR, "libfitre_oracle.so"])
+        L = C.CDLL(so)
+        MP, EP = C.POINTER(S.CNN_MODEL), C.POINTER(ORA_ENV)
+        i, d = C.c_int, C.c_double
+        L.ora_model_finalize.argtypes = [MP]
+        L.ora_model_finalize.restype = i
+        L.ora_cnn_gradient.argtypes = [EP, MP, dp, dp, dp, i, dp, dp, dp, dp, dp, i, d]
+        L.ora_cnn_gradient.restype = d
+        L.ora_cnn_forward.argtypes = [EP, MP, dp, dp, dp, i, dp, dp, dp, i]
+        L.ora_cnn_forward.restype = d
+        L.ora_cnn_hv.argtypes = [EP, MP, dp, dp, i, dp, dp, dp, dp, dp, dp, dp, i]
+        L.ora_cnn_hv.restype = None
+        L.ora_quadratic_model.argtypes = [EP, MP, dp, dp, i, dp, dp, dp, dp, dp, dp, d, i, d]
+        L.ora_quadratic_model.restype = d
+        L.ora_cg_steihaug.argtypes = [EP, MP, dp, dp, i, dp, dp, dp, dp, dp, dp, i,
+                                      C.POINTER(S.CG_PARAMS)]
+        L.ora_cg_steihaug.restype = None
+        L.ora_kfac_storage_indices.argtypes = [MP, C.POINTER(S.KFAC_INFO)]
+        L.ora_kfac_storage_indices.restype = i
+        L.ora_kfac_omega_z.argtypes = [EP, MP, dp, dp, i, dp, C.POINTER(S.KFAC_INFO)]
+        L.ora_kfac_lambda_delta.argtypes = [EP, MP, dp, i, dp, C.POINTER(S.KFAC_INFO)]
+        L.ora_im2col.argtypes = [dp, i, i, i, i, i, i, i, dp]
+        L.ora_im2col_index.argtypes = [i, i, i, i, i, i, i,
+                                       np.ctypeslib.ndpointer(dtype=np.int64, flags="C_CONTIGUOUS")]
+        L.ora_max_pool_argmax.argtypes = [dp, i, i, i, i, i, i, i,
+                                          np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")]
+        L.ora_pool_forward.argtypes = [dp, i, i, i, i, i, i, i, i, dp]
+        L.ora_batch_norm_forward.argtypes = [EP, dp, i, i, i, i, dp, dp, dp, d]
+        L.ora_batch_norm_backward.argtypes = [EP, dp, i, i, i, i, dp, dp, d, dp]
+        L.ora_rop_batch_norm_forward.argtypes = [EP, dp, dp, dp, dp, d, i, i, i, i, dp]
+        L.ora_rop_batch_norm_backward.argtypes = [EP, dp, dp, dp, dp, dp, dp, d, dp, dp, i, i, i, i]
+        L.ora_conv_dgrad.argtypes = [dp, i, i, i, dp, i, i, i, i, i, i, dp]
+        L.ora_gemm.argtypes = [i, i, C.c_long, C.c_long, C.c_long, d, dp, C.c_long, dp, C.c_long,
+                               d, dp, C.c_long]
+        _LIB = L
+    return _LIB
+
+
+def make_env(ref_softmax=1, world=1, allreduce=None):
+    env = ORA_ENV()
+    env.ref_softmax, env.world = int(ref_softmax), int(world)
+    if allreduce is not None:
+        env._cb = ALLREDUCE_FN(allreduce)  # keep alive
+        env.allreduce = env._cb
+    return env
+
+
+def finalize(model):
+    rc = lib().ora_model_finalize(C.byref(model))
+    if rc != 0:
+        raise ValueError("ora_model_finalize failed: %d" % rc)
+    return model
+
+
+class OracleState:
+    """Buffers of one oracle gradient evaluation (z, dx, probs, errors, gradient)."""
+
+    def __init__(self, model, n, num_classes):
+        self.z = np.zeros(model.zSize)
+        self.dx = np.zeros(model.zSize)
+        self.rz = np.zeros(model.zSize)
+        self.probs = np.zeros(n * num_classes)
+        self.errors = np.zeros(max(model.maxDeltaSize, n * num_classes))
+        self.gradient = np.zeros(model.pSize)
+        self.loss = None
+
+
+def gradient(model, batch, labels, weights, num_classes, n, weight_decay=0.0, env=None):
+    env = env or make_env()
+    st = OracleState(model, n, num_classes)
+    st.loss = lib().ora_cnn_gradient(C.byref(env), C.byref(model), batch, labels, weights,
+                                     num_classes, st.z, st.dx, st.probs, st.errors, st.gradient,
+                                     n, weight_decay)
+    return st
+
+
+def hv(model, batch, weights, num_classes, n, st, vector, env=None):
+    env = env or make_env()
+    out = np.zeros(model.pSize)
+    lib().ora_cnn_hv(C.byref(env), C.byref(model), batch, weights, num_classes, st.z, st.probs,
+                     st.errors, st.dx, np.ascontiguousarray(vector), out, st.rz, n)
+    return out
