@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark of the gradient + Hessian-vector hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one computeCNNGradient + one cnnHv on one synthetic batch per GPU:
+VGG-11-BN, fp64, 512 images of 3x32x32 per GPU (weak scaling: at 8 GPUs this is the
+4096-image configuration the metric is quoted on).  Inputs are seeded synthetic data
+(N(0,1) images, uniform labels, He-normal weights, N(0,1) direction).
+
+Prints ONE JSON line: images/s over all GPUs (device-resident inputs, CUDA events, max over
+ranks), the same metric end to end through the host-buffer C-ABI entry point (`e2e`), the
+roofline of the dominant kernel (implicit-GEMM convolution, fp64 tensor path) with its
+duration measured by CUDA events inside the timed region, and on 1 GPU the CPU baseline
+(the oracle port on the host cores, bounded sample).
+
+`--impl reference` times the reference path's CPU restatement (oracle/) with all host
+threads on a bounded sample of the same workload and prints the same line shape.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np  # noqa: E402
+
+PER_GPU_BATCH = 512
+WORKLOAD = "vgg11bn_32x32_fp64_gradient+hv"
+# algorithmic flops per image (2*M*K*Cout products only): gradient 913.1 MF + Hv 1819.1 MF
+CPU_SAMPLE_IMAGES = 64
+
+
+def build_model(n):
+    import nets
+    from fitre_b200 import api
+    m = nets.vgg11(n)
+    api.finalize(m)
+    return m
+
+
+def synth(model, n, seed):
+    from fitre_b200 import layout
+    rng = np.random.default_rng(seed)
+    c0 = model.convLayer[0]
+    x = layout.batch_to_ref(rng.standard_normal((n, c0.inChannels, c0.height, c0.width)))
+    y = rng.integers(1, 11, n).astype(np.float64)
+    w = layout.he_normal_params(model, rng)
+    v = rng.standard_normal(model.pSize)
+    return x, y, w, v
+
+
+def conv_flops_per_image(model):
+    """Algorithmic conv/FC flops of one gradient and one Hv per image."""
+    g = h = 0.0
+    for l in range(model.cLayers):
+        c = model.convLayer[l]
+        mkc = 2.0 * c.outHeight * c.outWidth * c.inChannels * c.kSize ** 2 * c.outChannels
+        g += (2 if l == 0 else 3) * mkc
+        h += (2 if l == 0 else 6) * mkc
+    for l in range(model.lLayers):
+        f = model.fcLayer[l]
+        g += 3 * 2.0 * f.in_ * f.out
+        h += 6 * 2.0 * f.in_ * f.out
+    return g, h
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.QUERY,
+                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.p is None:
+            return out
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.f.read().splitlines():
+            parts = [t.strip() for t in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.f.name)
+        except OSError:
+            pass
+        if sm:
+            # samples under load: the upper half of the clock samples
+            sm_sorted = sorted(sm)
+            out["sm_mhz"] = statistics.median(sm_sorted[len(sm_sorted) // 2:])
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def cpu_oracle_rate(sample_images, threads=None):
+    """images/s of one gradient + one Hv of the oracle port on the host cores."""
+    import oracle_lib as O
+    import nets
+    if threads:
+        os.environ["OMP_NUM_THREADS"] = str(threads)
+    m = nets.vgg11(sample_images)
+    O.finalize(m)
+    x, y, w, v = synth(m, sample_images, 4321)
+    t0 = time.perf_counter()
+    st = O.gradient(m, x, y, w, 10, sample_images)
+    O.hv(m, x, w, 10, sample_images, st, v)
+    dt = time.perf_counter() - t0
+    return sample_images / dt, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    rates = []
+    for i in range(args.warmup + args.steps):
+        r, dt = cpu_oracle_rate(CPU_SAMPLE_IMAGES)
+        if i >= args.warmup:
+            rates.append((r, dt))
+    value = CPU_SAMPLE_IMAGES * len(rates) / sum(dt for _, dt in rates)
+    line = {
+        "impl": "reference", "metric": "gradient+Hv images/sec", "value": value, "unit": "images/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * sum(dt for _, dt in rates) / len(rates),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu_batch": PER_GPU_BATCH,
+                   "note": "CPU restatement of the reference path (oracle/, C + OpenMP); each step "
+                           "is a %d-image sample of the workload" % CPU_SAMPLE_IMAGES},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port",
+                         "sample": "%d images of the VGG-11-BN fp64 gradient+Hv step" % CPU_SAMPLE_IMAGES},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from fitre_b200 import api
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the product path has no CPU fallback)")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.gpus != world and rank == 0:
+        sys.stderr.write("bench.py: --gpus %d but WORLD_SIZE %d; using WORLD_SIZE\n" % (args.gpus, world))
+
+    n = args.per_gpu_batch
+    model = build_model(n)
+    ctx = api.Context(local)
+    if world > 1:
+        ctx.comm_init_from_torch()
+    x, y, w, v = synth(model, n, 3234 + rank)   # each rank holds its own shard of the batch
+    _, _, w, v = synth(model, n, 3234)          # parameters and direction are replicated
+    f64 = dict(dtype=torch.float64, device="cuda")
+    X, Y = torch.tensor(x, **f64), torch.tensor(y, **f64)
+    W, V = torch.tensor(w, **f64), torch.tensor(v, **f64)
+    data = api.make_dataset(W, X, Y, 10)
+    ws = api.Workspace(model, 10)
+
+    def step():
+        api.computeCNNGradient(ctx, model, data, ws.scratch, ws.z, ws.dx, ws.probs, ws.errors,
+                               ws.gradient, 0, n, 0.0)
+        api.cnnHv(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, V, ws.hv, 0, n, ws.dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = ctx.launches
+    ctx.profile_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    ctx.profile_enable(False)
+    launches = ctx.launches - launches0
+    k_ms, k_flops, k_n = ctx.profile_read(0)
+    w_ms, w_flops, w_n = ctx.profile_read(1)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], **f64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = world * n * args.steps / (ms * 1e-3)
+
+    # ---- end to end through the host-buffer C-ABI entry point (pinned host memory)
+    hx = torch.tensor(x).pin_memory()
+    hy = torch.tensor(y).pin_memory()
+    hw = torch.tensor(w).pin_memory()
+    hv_in = torch.tensor(v).pin_memory()
+    hg = torch.zeros(model.pSize, dtype=torch.float64).pin_memory()
+    hh = torch.zeros(model.pSize, dtype=torch.float64).pin_memory()
+    del ws
+    torch.cuda.empty_cache()
+
+    def host_step():
+        return api.gradientHvHost(ctx, model, hx, hy, hw, hv_in, n, 10, 0.0, hg, hh)
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        host_step()
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        host_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], **f64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * n * args.steps / (e2e_ms * 1e-3)
+    h2d = 8 * (x.size + y.size + w.size + v.size)
+    d2h = 8 * 2 * model.pSize
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- fp64 tensor peak: cuBLAS DGEMM 8192^3 measured in this run (burst, best of 5)
+    a = torch.randn(8192, 8192, **f64)
+    b = torch.randn(8192, 8192, **f64)
+    torch.matmul(a, b)
+    best = 1e30
+    for _ in range(5):
+        e0.record()
+        torch.matmul(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    dgemm_tflops = 2.0 * 8192 ** 3 / (best * 1e-3) / 1e12
+    del a, b
+
+    achieved = (k_flops / (k_ms * 1e-3)) / 1e12 if k_ms > 0 else None
+    gpi, hpi = conv_flops_per_image(model)
+    line = {
+        "metric": "gradient+Hv images/sec", "value": value, "unit": "images/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu_batch": n, "global_batch": n * world,
+                   "parallelism": "dp%d" % world, "activation": "swish", "batch_norm": True,
+                   "l2": "inputs larger than L2 (z/dx/rz are 1.85 GiB each per GPU)",
+                   "algorithmic_mflop_per_image": {"gradient": gpi / 1e6, "hv": hpi / 1e6}},
+        "roofline": {"bound": "tensor", "kernel": "conv_fprop_kernel (implicit-GEMM fprop/dgrad, fp64 DMMA)",
+                     "achieved": achieved, "peak": dgemm_tflops, "unit": "TFLOP/s",
+                     "frac": (achieved / dgemm_tflops) if achieved else None,
+                     "peak_source": "cuBLAS DGEMM 8192^3 measured in this run (MEASURED_PEAKS.json has no fp64 figure)",
+                     "launches": k_n, "avg_launch_ms": k_ms / max(k_n, 1),
+                     "share_of_step": k_ms / ms,
+                     "traffic": None,
+                     "wgrad_kernel": {"achieved": (w_flops / (w_ms * 1e-3)) / 1e12 if w_ms > 0 else None,
+                                      "launches": w_n, "share_of_step": w_ms / ms}},
+        "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "per_gpu_algorithmic_tflops": (gpi + hpi) * n * args.steps / (ms * 1e-3) / 1e12,
+    }
+    if world == 1 and not args.skip_cpu:
+        r, dt = cpu_oracle_rate(CPU_SAMPLE_IMAGES)
+        line["cpu_baseline"] = {"value": r, "unit": "images/s", "cores": os.cpu_count() or 1,
+                                "kind": "port",
+                                "sample": "%d images of the same VGG-11-BN fp64 gradient+Hv step "
+                                          "(%.1f s of CPU work)" % (CPU_SAMPLE_IMAGES, dt)}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--per-gpu-batch", type=int, default=PER_GPU_BATCH,
+                    help="images per GPU (default 512, the benchmark shape; smaller values are "
+                         "for profiler captures only)")
+    ap.add_argument("--skip-cpu", action="store_true",
+                    help="leave the CPU baseline leg out (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

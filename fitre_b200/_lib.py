@@ -1,0 +1,87 @@
+"""Loads libfitre_b200.so (built in-tree by fitre_b200.build) and declares its C ABI.
+
+There is no CPU fallback: if the CUDA library is missing the import fails loudly.
+"""
+import ctypes as C
+import os
+
+from . import _structs as S
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfitre_b200.so")
+
+# every symbol include/fitre_b200.h declares
+SYMBOLS = [
+    "fitre_context_create", "fitre_context_destroy", "fitre_last_error", "fitre_launch_count",
+    "fitre_set_reference_softmax", "fitre_set_tma", "fitre_profile_enable", "fitre_profile_read",
+    "fitre_comm_unique_id", "fitre_comm_init", "fitre_comm_world",
+    "fitre_read_lenet_cnn", "fitre_read_alexnet_cnn", "fitre_read_vgg11", "fitre_read_test_vgg",
+    "fitre_model_finalize", "fitre_model_validate",
+    "fitre_cnn_forward_mem_required", "fitre_cnn_backward_mem_required",
+    "fitre_cnn_rop_forward_mem_required", "fitre_cnn_rop_backward_mem_required",
+    "fitre_cnn_gradient_mem_required", "fitre_cnn_hv_mem_required",
+    "fitre_cnn_forward", "fitre_cnn_backward", "fitre_compute_cnn_gradient",
+    "fitre_cnn_rop_forward", "fitre_cnn_rop_backward", "fitre_cnn_hv",
+    "fitre_compute_quadratic_model", "fitre_cg_steihaug",
+    "fitre_kfac_storage_indices", "fitre_kfac_mem_required", "fitre_kfac_omega_z",
+    "fitre_kfac_lambda_delta", "fitre_gradient_hv_host",
+]
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "fitre_b200: %s is missing -- build it with `python -m fitre_b200.build` "
+            "(there is no CPU fallback)" % LIB_PATH)
+    L = C.CDLL(LIB_PATH)
+    vp, i, d, l = C.c_void_p, C.c_int, C.c_double, C.c_long
+    MP = C.POINTER(S.CNN_MODEL)
+    DP = C.POINTER(S.DEVICE_DATASET)
+    SP = C.POINTER(S.SCRATCH_AREA)
+    dbl_p = C.POINTER(C.c_double)
+
+    def sig(name, res, *args):
+        f = getattr(L, name)
+        f.restype = res
+        f.argtypes = list(args)
+
+    sig("fitre_context_create", i, C.POINTER(vp), i, vp)
+    sig("fitre_context_destroy", i, vp)
+    sig("fitre_last_error", C.c_char_p, vp)
+    sig("fitre_launch_count", C.c_longlong, vp)
+    sig("fitre_set_reference_softmax", i, vp, i)
+    sig("fitre_set_tma", i, vp, i)
+    sig("fitre_profile_enable", i, vp, i)
+    sig("fitre_profile_read", i, vp, i, dbl_p, dbl_p, C.POINTER(C.c_long))
+    sig("fitre_comm_unique_id", i, vp)
+    sig("fitre_comm_init", i, vp, vp, i, i)
+    sig("fitre_comm_world", i, vp)
+    sig("fitre_read_lenet_cnn", i, MP, i, i, i, i, i, i, i, i)
+    sig("fitre_read_alexnet_cnn", i, MP, i, i, i, i, i, i, i)
+    sig("fitre_read_vgg11", i, MP, i, i, i, i, i, i, i, i)
+    sig("fitre_read_test_vgg", i, MP, i, i, i, i, i, i, i, i)
+    sig("fitre_model_finalize", i, MP)
+    sig("fitre_model_validate", i, MP)
+    for n in ("forward", "backward", "rop_forward", "rop_backward", "gradient", "hv"):
+        sig("fitre_cnn_%s_mem_required" % n, l, MP)
+    sig("fitre_kfac_mem_required", l, MP)
+    sig("fitre_cnn_forward", i, vp, MP, DP, SP, vp, vp, vp, i, i, i, dbl_p)
+    sig("fitre_cnn_backward", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, i, i, vp)
+    sig("fitre_compute_cnn_gradient", i, vp, MP, DP, SP, vp, vp, vp, vp, vp, i, i, d, dbl_p)
+    sig("fitre_cnn_rop_forward", i, vp, MP, DP, SP, vp, vp, vp, i, i, vp, vp)
+    sig("fitre_cnn_rop_backward", i, vp, MP, DP, SP, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp)
+    sig("fitre_cnn_hv", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, i, i, vp, vp, d)
+    sig("fitre_compute_quadratic_model", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, d, i, i, d,
+        vp, vp, vp, dbl_p)
+    sig("fitre_cg_steihaug", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, i, vp, C.POINTER(S.CG_PARAMS))
+    sig("fitre_kfac_storage_indices", i, MP, C.POINTER(S.KFAC_INFO))
+    sig("fitre_kfac_omega_z", i, vp, MP, DP, vp, i, vp, C.POINTER(S.KFAC_INFO), vp)
+    sig("fitre_kfac_lambda_delta", i, vp, MP, vp, i, vp, C.POINTER(S.KFAC_INFO), vp)
+    sig("fitre_gradient_hv_host", i, vp, MP, vp, vp, vp, vp, i, i, d, dbl_p, vp, vp)
+    _lib = L
+    return L

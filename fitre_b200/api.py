@@ -1,0 +1,282 @@
+"""Host-side mirror of the reference's operator interface for the CNN gradient /
+Hessian-vector path, on top of the C ABI (include/fitre_b200.h).
+
+Function names, argument order and meaning follow the reference:
+  computeCNNGradient  functions/cnn_gradient.h:9-12
+  cnnForward          functions/cnn_forward.h:11-13
+  cnnBackward         functions/cnn_backward.h:13-16
+  cnnHv               functions/cnn_hessian_vec.h:9-13
+  computeQuadraticModel functions/model_reduction.cu:20-93
+Device buffers are torch CUDA tensors of dtype float64 (torch is only the allocator); the
+structs are the ctypes mirrors in _structs.py.  Errors raise FitreError(status, text)
+instead of the reference's print-and-exit (device/cuda_utils.h:28-92).
+"""
+import ctypes as C
+
+from . import _lib
+from . import _structs as S
+
+
+class FitreError(RuntimeError):
+    def __init__(self, status, text):
+        super().__init__("fitre status %d: %s" % (status, text))
+        self.status = status
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return C.c_void_p(t)
+    if hasattr(t, "data_ptr"):
+        import torch
+        if t.dtype != torch.float64 or not t.is_cuda or not t.is_contiguous():
+            raise FitreError(S.ERR_BAD_ARG, "device buffers must be contiguous float64 CUDA tensors")
+        return C.c_void_p(t.data_ptr())
+    raise TypeError(type(t))
+
+
+class Context:
+    """One per GPU (reference: the global handles of device/handles.h:15-20)."""
+
+    def __init__(self, device=0, stream=None):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        sp = C.c_void_p(stream) if stream else None
+        rc = self.lib.fitre_context_create(C.byref(h), int(device), sp)
+        if rc != S.OK:
+            raise FitreError(rc, "fitre_context_create failed (is a CUDA device visible?)")
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.fitre_context_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, rc):
+        if rc != S.OK:
+            raise FitreError(rc, self.lib.fitre_last_error(self.h).decode())
+
+    @property
+    def launches(self):
+        return int(self.lib.fitre_launch_count(self.h))
+
+    def set_reference_softmax(self, on):
+        self.check(self.lib.fitre_set_reference_softmax(self.h, int(bool(on))))
+
+    def set_tma(self, on):
+        self.check(self.lib.fitre_set_tma(self.h, int(bool(on))))
+
+    def profile_enable(self, on):
+        self.check(self.lib.fitre_profile_enable(self.h, int(bool(on))))
+
+    def profile_read(self, kind):
+        """(device ms, algorithmic flops, launches) of kernel class `kind` since the last read."""
+        ms, fl, n = C.c_double(), C.c_double(), C.c_long()
+        self.check(self.lib.fitre_profile_read(self.h, kind, C.byref(ms), C.byref(fl), C.byref(n)))
+        return ms.value, fl.value, n.value
+
+    def comm_init_from_torch(self):
+        """Create the NCCL communicator over torch.distributed's default group (plumbing:
+        the 128-byte unique id is broadcast from rank 0 with the group's own backend)."""
+        import torch
+        import torch.distributed as dist
+        rank, world = dist.get_rank(), dist.get_world_size()
+        buf = (C.c_ubyte * 128)()
+        if rank == 0:
+            rc = self.lib.fitre_comm_unique_id(C.cast(buf, C.c_void_p))
+            if rc != S.OK:
+                raise FitreError(rc, "fitre_comm_unique_id failed")
+        dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+        t = torch.tensor(list(buf), dtype=torch.uint8, device=dev)
+        dist.broadcast(t, src=0)
+        raw = bytes(t.cpu().tolist())
+        idbuf = (C.c_ubyte * 128).from_buffer_copy(raw)
+        self.check(self.lib.fitre_comm_init(self.h, C.cast(idbuf, C.c_void_p), rank, world))
+
+    @property
+    def world(self):
+        return int(self.lib.fitre_comm_world(self.h))
+
+
+def finalize(model):
+    rc = _lib.load().fitre_model_finalize(C.byref(model))
+    if rc != S.OK:
+        raise FitreError(rc, "fitre_model_finalize")
+    return model
+
+
+def readLenetCNN(channels, width, height, batchSize, enableBias, enableBatchNorm,
+                 actFun=S.CNN_ACT_SWISH, poolType=S.AVG_POOL):
+    m = S.CNN_MODEL()
+    rc = _lib.load().fitre_read_lenet_cnn(C.byref(m), channels, width, height, batchSize,
+                                          enableBias, enableBatchNorm, actFun, poolType)
+    if rc != S.OK:
+        raise FitreError(rc, "fitre_read_lenet_cnn")
+    return m
+
+
+def readAlexNetCNN(batchSize, height, width, numClasses, enableBias, enableBatchNorm,
+                   actFun=S.CNN_ACT_SWISH):
+    m = S.CNN_MODEL()
+    rc = _lib.load().fitre_read_alexnet_cnn(C.byref(m), batchSize, height, width, numClasses,
+                                            enableBias, enableBatchNorm, actFun)
+    if rc != S.OK:
+        raise FitreError(rc, "fitre_read_alexnet_cnn")
+    return m
+
+
+def readVGG11(batchSize, height, width, numClasses, inChannels, bias, enableBatchNorm,
+              actFun=S.CNN_ACT_SWISH):
+    m = S.CNN_MODEL()
+    rc = _lib.load().fitre_read_vgg11(C.byref(m), batchSize, height, width, numClasses,
+                                      inChannels, bias, enableBatchNorm, actFun)
+    if rc != S.OK:
+        raise FitreError(rc, "fitre_read_vgg11")
+    return m
+
+
+def readTestVGG(batchSize, height, width, numClasses, inChannels, bias, bn,
+                actFun=S.CNN_ACT_SOFTPLUS):
+    m = S.CNN_MODEL()
+    rc = _lib.load().fitre_read_test_vgg(C.byref(m), batchSize, height, width, numClasses,
+                                         inChannels, bias, bn, actFun)
+    if rc != S.OK:
+        raise FitreError(rc, "fitre_read_test_vgg")
+    return m
+
+
+def make_dataset(weights, currentBatch, sampledTrainY, numClasses):
+    d = S.DEVICE_DATASET()
+    d.weights = weights.data_ptr()
+    d.currentBatch = currentBatch.data_ptr()
+    d.sampledTrainY = sampledTrainY.data_ptr()
+    d.numClasses = int(numClasses)
+    d._keep = (weights, currentBatch, sampledTrainY)
+    return d
+
+
+def make_scratch(dev_tensor):
+    s = S.SCRATCH_AREA()
+    s.devWorkspace = dev_tensor.data_ptr()
+    s.nextDevPtr = dev_tensor.data_ptr()
+    s._keep = dev_tensor
+    return s
+
+
+def mem_required(model, which):
+    return int(getattr(_lib.load(), "fitre_cnn_%s_mem_required" % which)(C.byref(model)))
+
+
+def computeCNNGradient(ctx, model, data, scratch, z, dx, probs, lossFuncErrors, gradient,
+                       offset, curBatchSize, weightDecay):
+    loss = C.c_double()
+    ctx.check(ctx.lib.fitre_compute_cnn_gradient(
+        ctx.h, C.byref(model), C.byref(data), C.byref(scratch), _ptr(z), _ptr(dx), _ptr(probs),
+        _ptr(lossFuncErrors), _ptr(gradient), offset, curBatchSize, float(weightDecay),
+        C.byref(loss)))
+    return loss.value
+
+
+def cnnForward(ctx, model, data, scratch, z, probs, errors, s, curBatchSize, evalType=S.MODEL_TRAIN):
+    loss = C.c_double()
+    ctx.check(ctx.lib.fitre_cnn_forward(ctx.h, C.byref(model), C.byref(data), C.byref(scratch),
+                                        _ptr(z), _ptr(probs), _ptr(errors), s, curBatchSize,
+                                        evalType, C.byref(loss)))
+    return loss.value
+
+
+def cnnBackward(ctx, model, data, devPtr, z, gradient, dx, delta, delta_new, offset, batchSize,
+                hostPtr=None):
+    ctx.check(ctx.lib.fitre_cnn_backward(ctx.h, C.byref(model), C.byref(data), _ptr(devPtr),
+                                         _ptr(z), _ptr(gradient), _ptr(dx), _ptr(delta),
+                                         _ptr(delta_new), offset, batchSize, None))
+
+
+def cnnHv(ctx, model, data, z, probs, lossFuncErrors, dx, vector, hv, s, curBatchSize, devPtr,
+          hostPtr=None, weightDecay=0.0):
+    ctx.check(ctx.lib.fitre_cnn_hv(ctx.h, C.byref(model), C.byref(data), _ptr(z), _ptr(probs),
+                                   _ptr(lossFuncErrors), _ptr(dx), _ptr(vector), _ptr(hv), s,
+                                   curBatchSize, _ptr(devPtr), None, float(weightDecay)))
+
+
+def computeQuadraticModel(ctx, model, data, z, probs, lossFuncErrors, dx, gradient, vector, delta,
+                          offset, curBatchSize, weightDecay, devPtr, hostPtr=None, pageLckPtr=None):
+    val = C.c_double()
+    ctx.check(ctx.lib.fitre_compute_quadratic_model(
+        ctx.h, C.byref(model), C.byref(data), _ptr(z), _ptr(probs), _ptr(lossFuncErrors), _ptr(dx),
+        _ptr(gradient), _ptr(vector), float(delta), offset, curBatchSize, float(weightDecay),
+        _ptr(devPtr), None, None, C.byref(val)))
+    return val.value
+
+
+def cgSteihaug(ctx, model, data, z, probs, lossFuncErrors, dx, gradient, p, curBatchSize, devPtr,
+               params):
+    ctx.check(ctx.lib.fitre_cg_steihaug(ctx.h, C.byref(model), C.byref(data), _ptr(z), _ptr(probs),
+                                        _ptr(lossFuncErrors), _ptr(dx), _ptr(gradient), _ptr(p),
+                                        curBatchSize, _ptr(devPtr), C.byref(params)))
+    return params
+
+
+def computeKFACStorageIndices(model):
+    info = S.KFAC_INFO()
+    rc = _lib.load().fitre_kfac_storage_indices(C.byref(model), C.byref(info))
+    if rc != S.OK:
+        raise FitreError(rc, "fitre_kfac_storage_indices")
+    return info
+
+
+def computeOmegaZ(ctx, model, data, z, samples, omegaZ, info, devPtr):
+    ctx.check(ctx.lib.fitre_kfac_omega_z(ctx.h, C.byref(model), C.byref(data), _ptr(z), samples,
+                                         _ptr(omegaZ), C.byref(info), _ptr(devPtr)))
+
+
+def computeLambdaDelta(ctx, model, dx, samples, lambdaG, info, devPtr):
+    ctx.check(ctx.lib.fitre_kfac_lambda_delta(ctx.h, C.byref(model), _ptr(dx), samples,
+                                              _ptr(lambdaG), C.byref(info), _ptr(devPtr)))
+
+
+def gradientHvHost(ctx, model, batch, labels, weights, vector, curBatchSize, numClasses,
+                   weightDecay, gradient_out, hv_out):
+    """Host-buffer entry point: numpy / pinned torch CPU arrays in and out."""
+    def hp(a):
+        if hasattr(a, "data_ptr"):
+            return C.c_void_p(a.data_ptr())
+        return C.c_void_p(a.ctypes.data)
+    loss = C.c_double()
+    ctx.check(ctx.lib.fitre_gradient_hv_host(ctx.h, C.byref(model), hp(batch), hp(labels),
+                                             hp(weights), hp(vector), curBatchSize, numClasses,
+                                             float(weightDecay), C.byref(loss), hp(gradient_out),
+                                             hp(hv_out)))
+    return loss.value
+
+
+class Workspace:
+    """Every device buffer one model needs for gradient + Hessian-vector calls, sized with the
+    library's *_mem_required figures (the reference carves the same buffers from one big
+    workspace: drivers/cnn_driver.cu:193-209)."""
+
+    def __init__(self, model, num_classes, device="cuda"):
+        import torch
+        L = _lib.load()
+        f64 = dict(dtype=torch.float64, device=device)
+        n = model.batchSize
+        self.model = model
+        self.z = torch.zeros(model.zSize, **f64)
+        self.dx = torch.zeros(model.zSize, **f64)
+        self.probs = torch.zeros(n * num_classes, **f64)
+        self.errors = torch.zeros(n * num_classes, **f64)
+        self.gradient = torch.zeros(model.pSize, **f64)
+        self.hv = torch.zeros(model.pSize, **f64)
+        need = max(L.fitre_cnn_gradient_mem_required(C.byref(model)),
+                   L.fitre_cnn_hv_mem_required(C.byref(model)))
+        self.extra = 4 * (model.pSize + 32) + 64
+        self.dev = torch.zeros(need + self.extra, **f64)
+        self.scratch = make_scratch(self.dev)

@@ -1,0 +1,204 @@
+// Internal declarations shared by the library's translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/fitre_b200.h"
+
+namespace fitre {
+
+constexpr double kBnEps = 1e-5;  // functions/dev_batch_norm.h:10
+
+// Error carrying a C-ABI status code; caught at the extern "C" boundary.
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string &what) : std::runtime_error(what), code(c) {}
+};
+
+#define FITRE_CUDA(call)                                                                   \
+    do {                                                                                   \
+        cudaError_t e_ = (call);                                                           \
+        if (e_ != cudaSuccess)                                                             \
+            throw ::fitre::Error(FITRE_ERR_CUDA, std::string(#call) + ": " +               \
+                                                     cudaGetErrorString(e_));              \
+    } while (0)
+
+#define FITRE_REQUIRE(cond, code, msg)                         \
+    do {                                                       \
+        if (!(cond)) throw ::fitre::Error((code), (msg));      \
+    } while (0)
+
+struct Comm;  // NCCL state (comm.cpp)
+
+}  // namespace fitre
+
+// One context per GPU and host thread.  Owns only small fixed buffers (pinned scalars and a
+// device scalar slab); every tensor-sized buffer belongs to the caller.
+struct fitre_context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    long long launches = 0;
+    std::string err;
+    int ref_softmax = 1;
+    bool use_tma = true;        // TMA-fed convolution kernels where shape and alignment allow
+    double *pinned = nullptr;   // 256 pinned host doubles (scalar read-back)
+    double *dscal = nullptr;    // 4096 device doubles (scalar reductions)
+    fitre::Comm *comm = nullptr;
+    int rank = 0, world = 1;
+    // workspace of the host-buffer entry point (allocated on first use, reused)
+    double *host_ws = nullptr;
+    size_t host_ws_doubles = 0;
+    double *host_pinned = nullptr;
+    size_t host_pinned_doubles = 0;
+    // optional per-kernel timing (CUDA events on the launch stream), see fitre_profile_*
+    bool prof_on = false;
+    struct ProfRec { cudaEvent_t beg, end; int kind; double flops; };
+    std::vector<ProfRec> prof;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_pool;
+};
+
+namespace fitre {
+
+inline void count_launch(fitre_context *ctx, int n = 1) { ctx->launches += n; }
+
+// After a kernel launch: pick up launch-configuration errors.
+inline void check_launch(fitre_context *ctx, const char *name) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        throw Error(FITRE_ERR_CUDA, std::string("launch of ") + name + ": " + cudaGetErrorString(e));
+    ctx->launches += 1;
+}
+
+// Kernel classes the optional event timing distinguishes.
+enum { PROF_CONV_IGEMM = 0, PROF_CONV_WGRAD = 1, PROF_KINDS = 2 };
+// Brackets one launch with events when profiling is on (no-op otherwise).
+struct ProfScope {
+    fitre_context *ctx;
+    int idx = -1;
+    ProfScope(fitre_context *c, int kind, double flops);
+    ~ProfScope();
+};
+
+// ---- comm.cpp: all-reduce hooks (no-ops when world == 1) ----
+void comm_allreduce_sum(fitre_context *ctx, double *dev_buf, size_t n);
+void comm_destroy(fitre_context *ctx);
+
+// ---- model.cpp ----
+struct ConvGeom {
+    int Cin, Cout, H, W, Ho, Wo, k, pad;
+    int bn, act;
+    int poolType, pk, ps, pp, Hp, Wp;
+    long zoff;                      // start of this layer's block in z / dx / rz
+    long actOff, poolOff, bnOff, outOff;  // relative to zoff
+    long meanOff, varOff;           // relative to zoff + bnOff
+};
+ConvGeom conv_geom(const CNN_MODEL *m, int l);
+void model_check_batch(const CNN_MODEL *m, int curBatchSize);
+long max_delta_elems(const CNN_MODEL *m);  // largest errors tensor incl. conv inputs
+
+// ---- gemm.cu ----
+struct ConvSeg {            // one (input tensor, weight matrix) pair of a K-/M-concatenated product
+    const double *x;        // [Cin][N][W][H]
+    const double *w;        // K x Cout column-major
+};
+// Y[M x Cout] (+= bias[c]) = sum_seg im2col(x_seg) * w_seg      (fprop and its R-op form)
+void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
+                int N, int Cin, int H, int W, int k, int pad, int Cout);
+// dX[(N H W) x Cin] = sum_seg im2colT(delta_seg) * perm(w_seg)  (dgrad and its R-op form);
+// `wscratch` receives the permuted weights (nseg * K * Cout doubles).
+void conv_dgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dx, int N, int Cin,
+                int H, int W, int k, int pad, int Cout, double *wscratch);
+// dW[K x Cout] = sum_seg im2col(x_seg)' * delta_seg ; segs[i].w is delta_seg (M x Cout).
+// `partials` needs conv_wgrad_scratch() doubles.
+long conv_wgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
+void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
+                int H, int W, int k, int pad, int Cout, double *partials);
+// C (m x n, ldc) = alpha op(A) op(B) + beta C, column-major (cublasDgemm semantics)
+void dgemm(fitre_context *ctx, bool tA, bool tB, int m, int n, int k, double alpha,
+           const double *A, int lda, const double *B, int ldb, double beta, double *C, int ldc);
+// C (n x n) = alpha * A' A  where A is rows x n column-major (lda); both triangles written.
+long syrk_scratch(long rows, int n);
+void syrk_tn(fitre_context *ctx, long rows, int n, double alpha, const double *A, long lda,
+             double *C, double *partials);
+
+long conv_patch_syrk_scratch(int N, int Cin, int H, int W, int k, int pad, bool bias);
+// A = alpha * S (P~' P~) S over implicit im2col patches P~ = [im2col(x), 1], S = diag(patch_scale.., 1)
+void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int Cin, int H, int W,
+                     int k, int pad, bool bias, double alpha, double patch_scale, double *partials);
+void gemm_init_attributes();
+// conv_tma.cu
+void conv_tma_init_attributes();
+bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias,
+                    double *y, int N, int Cin, int H, int W, int k, int pad, int Cout);
+// Device-side error word (set by a kernel whose bounded wait ran out): dscal[4000] as int.
+void check_device_error(fitre_context *ctx);
+
+// ---- layers.cu ----
+long bn_scratch(int C);   // doubles of scratch any batch-norm / reduction helper may use
+void add_channel_bias(fitre_context *ctx, double *x, const double *bias, long rows, int C);
+void add_column_bias(fitre_context *ctx, double *x, const double *bias, int rows, int cols);
+void apply_activation(fitre_context *ctx, int act, const double *in, double *out, long n);
+// conv-out -> (bn out, mean, var) -> act out [-> pool out]
+void conv_post_forward(fitre_context *ctx, const ConvGeom &g, int N, double *zl, double *scratch);
+// R-op of the same chain: rz conv-out -> R bn -> R act -> R pool
+void conv_post_rop_forward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
+                           double *rzl, double *scratch);
+// pooled errors -> dx_P, dx_A, dx_BN (written into dxl); returns pointer to the errors the
+// convolution consumes (dx_BN or dx_A).  db (may be NULL) receives the bias gradient.
+const double *conv_post_backward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
+                                 double *dxl, const double *delta_pool, double *db,
+                                 double *scratch);
+// R-op of the backward chain: Rdelta_pool -> Rdelta for the convolution (written to `rout`).
+void conv_post_rop_backward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
+                            const double *rzl, const double *dxl, const double *rdelta_pool,
+                            double *rout, double *rdb, double *scratch);
+void conv_to_fc(fitre_context *ctx, double *buf, int C, int N, int Hp, int Wp, double *tmp);
+void fc_to_conv(fitre_context *ctx, double *buf, int C, int N, int Hp, int Wp, double *tmp);
+void act_backward(fitre_context *ctx, int act, double *delta, const double *zin,
+                  const double *zout, long n);
+void act_rop_backward(fitre_context *ctx, int act, double *rdelta, const double *delta_in,
+                      const double *rzin, const double *zin, const double *zout, long n);
+void row_sums(fitre_context *ctx, const double *x, int rows, int cols, double *out);
+// softmax cross-entropy: probs, errors (p - y)/Nglobal; the batch loss sum lands in dscal[0]
+void softmax_loss(fitre_context *ctx, const double *logits, const double *labels, int N,
+                  int classes, double *probs, double *errors, double inv_n_global);
+void softmax_rop_error(fitre_context *ctx, const double *rz, const double *probs, int N,
+                       int classes, double *rerr, double inv_n_global);
+// vector helpers on pSize-long vectors
+void vec_axpy(fitre_context *ctx, long n, double a, const double *x, double *y);
+void vec_scale(fitre_context *ctx, long n, double a, double *x);
+void vec_copy(fitre_context *ctx, long n, const double *x, double *y);
+void vec_axpby(fitre_context *ctx, long n, double a, const double *x, double b, double *y);
+void vec_fill(fitre_context *ctx, long n, double v, double *x);
+// up to 3 dot products in one pass; results in ctx->pinned[0..2] after a stream sync
+void vec_dots(fitre_context *ctx, long n, const double *a0, const double *b0, const double *a1,
+              const double *b1, const double *a2, const double *b2, double *host_out);
+
+// ---- passes.cu ----
+double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                   double *scratch, double *z, double *probs, double *errors, int n,
+                   bool want_loss);
+void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                  double *scratch, double *z, double *gradient, double *dx, double *delta,
+                  double *delta_new, int n);
+void cnn_rop_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                     const double *z, const double *vector, double *rz, int n, double *scratch);
+void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                      const double *z, const double *dx, const double *lossErrors, double *rError,
+                      const double *rz, const double *vector, double *hv, int n, double *scratch);
+void cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, const double *z,
+            const double *probs, const double *lossErrors, const double *dx, const double *vector,
+            double *hv, int n, double *devPtr);
+long forward_scratch(const CNN_MODEL *m);
+long backward_scratch(const CNN_MODEL *m);
+long rop_forward_scratch(const CNN_MODEL *m);
+long rop_backward_scratch(const CNN_MODEL *m);
+
+}  // namespace fitre

@@ -1,0 +1,872 @@
+// fp64 tensor-core (DMMA) GEMM-shaped kernels for sm_100a:
+//   * implicit-GEMM convolution forward / data gradient, with up to two K-concatenated
+//     (input, weight) segments so that an R-op product X*V + RX*W is one launch;
+//   * implicit-GEMM weight gradient with up to two M-concatenated segments and a
+//     deterministic split over the N*Ho*Wo reduction;
+//   * a dense column-major DGEMM for the fully connected layers;
+//   * A'A (SYRK-shaped) for the KFAC G factors.
+// The im2col matrix of the reference (functions/dev_image.cu:12-51) is never materialised:
+// tiles are gathered straight from the [C][N][W][H] tensor with the same index map
+// (row r = n*Ho*Wo + wo*Ho + ho, column q = cin*k*k + j*k + i, zero outside the image).
+// tcgen05 has no fp64 kind, so the fp64 path uses mma.sync m8n8k4 (DMMA).
+#include <algorithm>
+
+#include "common.h"
+
+namespace fitre {
+namespace {
+
+__device__ __forceinline__ void dmma884(double &c0, double &c1, double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
+                 : "+d"(c0), "+d"(c1)
+                 : "d"(a), "d"(b));
+}
+
+// ----------------------------------------------------------------------------------------
+// Implicit-GEMM convolution:  Y[M x Cout] = sum_seg im2col(X_seg)[M x K] * W_seg[K x Cout]
+// ----------------------------------------------------------------------------------------
+struct ConvArgs {
+    const double *x[2];
+    const double *w[2];
+    int nseg;
+    const double *bias;
+    double *y;
+    int N, Cin, H, W, k, pad, Cout, Ho, Wo, K;
+    long M;
+};
+
+constexpr int FP_BM = 128, FP_BN = 64, FP_BK = 16, FP_THREADS = 256;
+constexpr int FP_LDA = FP_BM + 4;  // As[k][m]: (lane%4)*LDA + lane/4 hits 16 distinct 8-byte banks
+constexpr int FP_LDB = FP_BK + 4;  // Bs[n][k]
+constexpr int FP_SMEM = 2 * (FP_BK * FP_LDA + FP_BN * FP_LDB) * (int)sizeof(double);
+
+template <int KS>  // KS = compile-time kernel size (0 = runtime)
+__global__ void __launch_bounds__(FP_THREADS, 2) conv_fprop_kernel(ConvArgs p) {
+    extern __shared__ double smem[];
+    double *As = smem;                           // [2][BK][LDA]
+    double *Bs = smem + 2 * FP_BK * FP_LDA;      // [2][BN][LDB]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_m = warp & 3, warp_n = warp >> 2;
+    const long m0 = (long)blockIdx.x * FP_BM;
+    const int c0 = blockIdx.y * FP_BN;
+    const int k = KS ? KS : p.k, kk2 = k * k;
+
+    // this thread gathers rows mm of the A tile for k-slots a_k0, a_k0 + 2, ...
+    const int a_mm = tid & (FP_BM - 1), a_k0 = tid >> 7;
+    const long am = m0 + a_mm;
+    const bool a_mvalid = am < p.M;
+    int a_ho = 0, a_wo = 0;
+    long a_base = 0;
+    if (a_mvalid) {
+        const int howo = p.Ho * p.Wo;
+        const int n = (int)(am / howo);
+        const int r = (int)(am - (long)n * howo);
+        a_wo = r / p.Ho;
+        a_ho = r - a_wo * p.Ho;
+        a_base = ((long)n * p.W + (a_wo - p.pad)) * p.H + (a_ho - p.pad);
+    }
+    const long chan_stride = (long)p.N * p.W * p.H;
+    // B tile: thread loads 4 consecutive k of column b_nn
+    const int b_nn = tid >> 2, b_k0 = (tid & 3) * 4;
+    const bool b_cvalid = (c0 + b_nn) < p.Cout;
+
+    const int nk = (p.K + FP_BK - 1) / FP_BK;
+    const int iters = nk * p.nseg;
+
+    double ra[8], rb[4];
+    auto gload = [&](int it) {
+        const int seg = it / nk, kt = it - seg * nk;
+        const double *x = p.x[seg];
+        const double *w = p.w[seg];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const int q = kt * FP_BK + a_k0 + 2 * r;
+            double v = 0.0;
+            if (a_mvalid && q < p.K) {
+                const int cin = q / kk2;
+                const int rem = q - cin * kk2;
+                const int j = rem / k, i = rem - j * k;
+                const int h = a_ho - p.pad + i, wv = a_wo - p.pad + j;
+                if (h >= 0 && h < p.H && wv >= 0 && wv < p.W)
+                    v = __ldg(x + a_base + cin * chan_stride + (long)j * p.H + i);
+            }
+            ra[r] = v;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int q = kt * FP_BK + b_k0 + e;
+            rb[e] = (b_cvalid && q < p.K) ? __ldg(w + (long)(c0 + b_nn) * p.K + q) : 0.0;
+        }
+    };
+    auto sstore = [&](int buf) {
+        double *a = As + buf * FP_BK * FP_LDA;
+        double *b = Bs + buf * FP_BN * FP_LDB;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) a[(a_k0 + 2 * r) * FP_LDA + a_mm] = ra[r];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) b[b_nn * FP_LDB + b_k0 + e] = rb[e];
+    };
+
+    double acc[4][4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+    gload(0);
+    sstore(0);
+    __syncthreads();
+    const int lr = lane >> 2, lc = lane & 3;
+    for (int it = 0; it < iters; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < iters) gload(it + 1);
+        const double *a = As + buf * FP_BK * FP_LDA + warp_m * 32 + lr;
+        const double *b = Bs + buf * FP_BN * FP_LDB + (warp_n * 32 + lr) * FP_LDB;
+#pragma unroll
+        for (int k4 = 0; k4 < FP_BK / 4; ++k4) {
+            double fa[4], fb[4];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) fa[mi] = a[(k4 * 4 + lc) * FP_LDA + mi * 8];
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) fb[ni] = b[ni * 8 * FP_LDB + k4 * 4 + lc];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 4; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+        }
+        if (it + 1 < iters) {
+            sstore(buf ^ 1);
+            __syncthreads();
+        }
+    }
+
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int col = c0 + warp_n * 32 + ni * 8 + 2 * lc + e;
+            if (col >= p.Cout) continue;
+            const double bv = p.bias ? p.bias[col] : 0.0;
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) {
+                const long row = m0 + warp_m * 32 + mi * 8 + lr;
+                if (row < p.M) p.y[(long)col * p.M + row] = acc[mi][ni][e] + bv;
+            }
+        }
+}
+
+// Weights for the data gradient: Wd[(cout*k*k + j'*k + i') + cin*(Cout*k*k)] =
+// W[cout][cin][k-1-j'][k-1-i'] (functions/dev_backprop_convolution.cu:86-95,140-156,215-217).
+__global__ void dgrad_weight_perm_kernel(const double *w, double *wd, int Cin, int Cout, int k) {
+    const long n = (long)Cin * Cout * k * k;
+    const int kk2 = k * k;
+    for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < n;
+         idx += (long)gridDim.x * blockDim.x) {
+        const int cin = (int)(idx / ((long)Cout * kk2));
+        const long r = idx - (long)cin * Cout * kk2;
+        const int cout = (int)(r / kk2);
+        const int t = (int)(r - (long)cout * kk2);
+        const int jp = t / k, ip = t - jp * k;
+        wd[idx] = w[(long)cout * Cin * kk2 + (long)cin * kk2 + (k - 1 - jp) * k + (k - 1 - ip)];
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// Implicit-GEMM weight gradient: dW[K x Cout] = sum_seg im2col(X_seg)' [K x M] * D_seg[M x Cout]
+// ----------------------------------------------------------------------------------------
+struct WgradArgs {
+    const double *x[2];
+    const double *d[2];
+    int nseg;
+    double *out;      // dW when splits == 1, else partial slabs [split][K*Cout]
+    int N, Cin, H, W, k, pad, Cout, Ho, Wo, K;
+    long M;
+    long chunk;       // rows of M per split (multiple of WG_BK)
+};
+
+constexpr int WG_BQ = 64, WG_BN = 64, WG_BK = 16, WG_THREADS = 256;
+constexpr int WG_LD = WG_BK + 4;  // Sa[q][m], Sb[c][m]: (lane/4)*LD + lane%4 is conflict-free
+constexpr int WG_SMEM = 2 * (WG_BQ + WG_BN) * WG_LD * (int)sizeof(double);
+
+template <int KS>
+__global__ void __launch_bounds__(WG_THREADS, 2) conv_wgrad_kernel(WgradArgs p) {
+    extern __shared__ double smem[];
+    double *Sa = smem;                          // [2][BQ][LD]
+    double *Sb = smem + 2 * WG_BQ * WG_LD;      // [2][BN][LD]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_q = warp & 1, warp_n = warp >> 1;  // warp tile 32 (q) x 16 (c)
+    const int q0 = blockIdx.x * WG_BQ, c0 = blockIdx.y * WG_BN;
+    const long mbeg = (long)blockIdx.z * p.chunk;
+    const long mend = min(p.M, mbeg + p.chunk);
+    const int k = KS ? KS : p.k, kk2 = k * k;
+    const long chan_stride = (long)p.N * p.W * p.H;
+    const int howo = p.Ho * p.Wo;
+
+    // gather roles: element (qq = t_q + 16 r, mm = t_m)
+    const int t_m = tid & 15, t_q = tid >> 4;
+    long q_off[4];
+    int q_i[4], q_j[4];
+    bool q_ok[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int q = q0 + t_q + 16 * r;
+        q_ok[r] = q < p.K;
+        const int cin = q_ok[r] ? q / kk2 : 0;
+        const int rem = q_ok[r] ? q - cin * kk2 : 0;
+        q_j[r] = rem / k;
+        q_i[r] = rem - q_j[r] * k;
+        q_off[r] = cin * chan_stride + (long)q_j[r] * p.H + q_i[r];
+    }
+    bool c_ok[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) c_ok[r] = (c0 + t_q + 16 * r) < p.Cout;
+
+    const long span = mend > mbeg ? mend - mbeg : 0;
+    const int nk = (int)((span + WG_BK - 1) / WG_BK);
+    const int iters = nk * p.nseg;
+
+    double ra[4], rb[4];
+    auto gload = [&](int it) {
+        const int seg = it / nk, kt = it - seg * nk;
+        const double *x = p.x[seg];
+        const double *d = p.d[seg];
+        const long m = mbeg + (long)kt * WG_BK + t_m;
+        const bool mv = m < mend;
+        int ho = 0, wo = 0;
+        long base = 0;
+        if (mv) {
+            const int n = (int)(m / howo);
+            const int r = (int)(m - (long)n * howo);
+            wo = r / p.Ho;
+            ho = r - wo * p.Ho;
+            base = ((long)n * p.W + (wo - p.pad)) * p.H + (ho - p.pad);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            double v = 0.0;
+            if (mv && q_ok[r]) {
+                const int h = ho - p.pad + q_i[r], wv = wo - p.pad + q_j[r];
+                if (h >= 0 && h < p.H && wv >= 0 && wv < p.W) v = __ldg(x + base + q_off[r]);
+            }
+            ra[r] = v;
+            rb[r] = (mv && c_ok[r]) ? __ldg(d + (long)(c0 + t_q + 16 * r) * p.M + m) : 0.0;
+        }
+    };
+    auto sstore = [&](int buf) {
+        double *a = Sa + buf * WG_BQ * WG_LD;
+        double *b = Sb + buf * WG_BN * WG_LD;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            a[(t_q + 16 * r) * WG_LD + t_m] = ra[r];
+            b[(t_q + 16 * r) * WG_LD + t_m] = rb[r];
+        }
+    };
+
+    double acc[4][2][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+    const int lr = lane >> 2, lc = lane & 3;
+    if (iters > 0) {
+        gload(0);
+        sstore(0);
+    }
+    __syncthreads();
+    for (int it = 0; it < iters; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < iters) gload(it + 1);
+        const double *a = Sa + buf * WG_BQ * WG_LD + (warp_q * 32 + lr) * WG_LD + lc;
+        const double *b = Sb + buf * WG_BN * WG_LD + (warp_n * 16 + lr) * WG_LD + lc;
+#pragma unroll
+        for (int k4 = 0; k4 < WG_BK / 4; ++k4) {
+            double fa[4], fb[2];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) fa[mi] = a[mi * 8 * WG_LD + k4 * 4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) fb[ni] = b[ni * 8 * WG_LD + k4 * 4];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+        }
+        if (it + 1 < iters) {
+            sstore(buf ^ 1);
+            __syncthreads();
+        }
+    }
+    double *out = p.out + (long)blockIdx.z * p.K * p.Cout;
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int col = c0 + warp_n * 16 + ni * 8 + 2 * lc + e;
+            if (col >= p.Cout) continue;
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) {
+                const int row = q0 + warp_q * 32 + mi * 8 + lr;
+                if (row < p.K) out[(long)col * p.K + row] = acc[mi][ni][e];
+            }
+        }
+}
+
+// out[i] = alpha * sum_s partial[s][i], s ascending (deterministic)
+__global__ void reduce_slabs_kernel(const double *partial, double *out, long n, int slabs,
+                                    double alpha) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n;
+         i += (long)gridDim.x * blockDim.x) {
+        double s = 0.0;
+        for (int k = 0; k < slabs; ++k) s += partial[(long)k * n + i];
+        out[i] = alpha * s;
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// Dense DGEMM (fully connected layers): C = alpha op(A) op(B) + beta C, column-major
+// ----------------------------------------------------------------------------------------
+constexpr int DG_BM = 64, DG_BN = 64, DG_BK = 16, DG_THREADS = 256;
+constexpr int DG_LDA = DG_BM + 4, DG_LDB = DG_BN + 4;  // As[k][m], Bs[k][n]
+
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(DG_THREADS) dgemm_kernel(int m, int n, int k, double alpha,
+                                                          const double *A, int lda,
+                                                          const double *B, int ldb, double beta,
+                                                          double *C, int ldc) {
+    __shared__ double As[2][DG_BK * DG_LDA];
+    __shared__ double Bs[2][DG_BK * DG_LDB];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_m = warp & 1, warp_n = warp >> 1;  // warp tile 32 x 16
+    const int m0 = blockIdx.x * DG_BM, n0 = blockIdx.y * DG_BN;
+    const int nk = (k + DG_BK - 1) / DG_BK;
+    // loader roles: 1024 elements per operand tile, 4 per thread.  The fast thread index
+    // follows the contiguous direction of the operand in memory.
+    double ra[4], rb[4];
+    auto gload = [&](int kt) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int mm, kk;
+            if (!TA) { mm = tid & 63; kk = (tid >> 6) + 4 * r; }
+            else     { kk = tid & 15; mm = (tid >> 4) + 16 * r; }
+            const int gi = m0 + mm, gp = kt * DG_BK + kk;
+            double v = 0.0;
+            if (gi < m && gp < k) v = TA ? A[gp + (long)gi * lda] : A[gi + (long)gp * lda];
+            ra[r] = v;
+            int nn, kb;
+            if (!TB) { kb = tid & 15; nn = (tid >> 4) + 16 * r; }
+            else     { nn = tid & 63; kb = (tid >> 6) + 4 * r; }
+            const int gj = n0 + nn, gq = kt * DG_BK + kb;
+            double u = 0.0;
+            if (gj < n && gq < k) u = TB ? B[gj + (long)gq * ldb] : B[gq + (long)gj * ldb];
+            rb[r] = u;
+        }
+    };
+    auto sstore = [&](int buf) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int mm, kk;
+            if (!TA) { mm = tid & 63; kk = (tid >> 6) + 4 * r; }
+            else     { kk = tid & 15; mm = (tid >> 4) + 16 * r; }
+            As[buf][kk * DG_LDA + mm] = ra[r];
+            int nn, kb;
+            if (!TB) { kb = tid & 15; nn = (tid >> 4) + 16 * r; }
+            else     { nn = tid & 63; kb = (tid >> 6) + 4 * r; }
+            Bs[buf][kb * DG_LDB + nn] = rb[r];
+        }
+    };
+    double acc[4][2][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+    const int lr = lane >> 2, lc = lane & 3;
+    if (nk > 0) {
+        gload(0);
+        sstore(0);
+    }
+    __syncthreads();
+    for (int kt = 0; kt < nk; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < nk) gload(kt + 1);
+        const double *a = As[buf] + warp_m * 32 + lr;
+        const double *b = Bs[buf] + warp_n * 16 + lr;
+#pragma unroll
+        for (int k4 = 0; k4 < DG_BK / 4; ++k4) {
+            double fa[4], fb[2];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) fa[mi] = a[(k4 * 4 + lc) * DG_LDA + mi * 8];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) fb[ni] = b[(k4 * 4 + lc) * DG_LDB + ni * 8];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+        }
+        if (kt + 1 < nk) {
+            sstore(buf ^ 1);
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int col = n0 + warp_n * 16 + ni * 8 + 2 * lc + e;
+            if (col >= n) continue;
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) {
+                const int row = m0 + warp_m * 32 + mi * 8 + lr;
+                if (row >= m) continue;
+                double *c = C + (long)col * ldc + row;
+                const double v = alpha * acc[mi][ni][e];
+                *c = (beta == 0.0) ? v : v + beta * (*c);
+            }
+        }
+}
+
+// ----------------------------------------------------------------------------------------
+// C[n x n] = alpha * A' A with A rows x n column-major; split over rows, both triangles.
+// ----------------------------------------------------------------------------------------
+struct SyrkArgs {
+    const double *A;
+    long lda, rows, chunk;
+    int n;
+    double *out;
+};
+
+__global__ void __launch_bounds__(WG_THREADS, 2) syrk_tn_kernel(SyrkArgs p) {
+    extern __shared__ double smem[];
+    double *Sa = smem;
+    double *Sb = smem + 2 * WG_BQ * WG_LD;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_q = warp & 1, warp_n = warp >> 1;
+    const int q0 = blockIdx.x * WG_BQ, c0 = blockIdx.y * WG_BN;
+    if (c0 > q0 + WG_BQ - 1) return;  // lower-triangular tiles only; mirrored by the reducer
+    const long mbeg = (long)blockIdx.z * p.chunk;
+    const long mend = min(p.rows, mbeg + p.chunk);
+    const int t_m = tid & 15, t_q = tid >> 4;
+    const long span = mend > mbeg ? mend - mbeg : 0;
+    const int nk = (int)((span + WG_BK - 1) / WG_BK);
+    double ra[4], rb[4];
+    auto gload = [&](int kt) {
+        const long m = mbeg + (long)kt * WG_BK + t_m;
+        const bool mv = m < mend;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int qa = q0 + t_q + 16 * r, qb = c0 + t_q + 16 * r;
+            ra[r] = (mv && qa < p.n) ? __ldg(p.A + (long)qa * p.lda + m) : 0.0;
+            rb[r] = (mv && qb < p.n) ? __ldg(p.A + (long)qb * p.lda + m) : 0.0;
+        }
+    };
+    auto sstore = [&](int buf) {
+        double *a = Sa + buf * WG_BQ * WG_LD;
+        double *b = Sb + buf * WG_BN * WG_LD;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            a[(t_q + 16 * r) * WG_LD + t_m] = ra[r];
+            b[(t_q + 16 * r) * WG_LD + t_m] = rb[r];
+        }
+    };
+    double acc[4][2][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+    const int lr = lane >> 2, lc = lane & 3;
+    if (nk > 0) {
+        gload(0);
+        sstore(0);
+    }
+    __syncthreads();
+    for (int kt = 0; kt < nk; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < nk) gload(kt + 1);
+        const double *a = Sa + buf * WG_BQ * WG_LD + (warp_q * 32 + lr) * WG_LD + lc;
+        const double *b = Sb + buf * WG_BN * WG_LD + (warp_n * 16 + lr) * WG_LD + lc;
+#pragma unroll
+        for (int k4 = 0; k4 < WG_BK / 4; ++k4) {
+            double fa[4], fb[2];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) fa[mi] = a[mi * 8 * WG_LD + k4 * 4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) fb[ni] = b[ni * 8 * WG_LD + k4 * 4];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+        }
+        if (kt + 1 < nk) {
+            sstore(buf ^ 1);
+            __syncthreads();
+        }
+    }
+    double *out = p.out + (long)blockIdx.z * p.n * p.n;
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int col = c0 + warp_n * 16 + ni * 8 + 2 * lc + e;
+            if (col >= p.n) continue;
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) {
+                const int row = q0 + warp_q * 32 + mi * 8 + lr;
+                if (row < p.n) out[(long)col * p.n + row] = acc[mi][ni][e];
+            }
+        }
+}
+
+// out = alpha * sum of slabs; entries above the diagonal are taken from their mirror image
+// (tiles strictly above the diagonal are not computed).
+__global__ void syrk_reduce_kernel(const double *partial, double *out, int n, int slabs,
+                                   double alpha) {
+    const long nn = (long)n * n;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nn;
+         i += (long)gridDim.x * blockDim.x) {
+        int col = (int)(i / n), row = (int)(i - (long)col * n);
+        // tile (row/64, col/64) is computed iff col_tile <= row_tile
+        long src = (col / WG_BN <= row / WG_BQ) ? i : (long)row * n + col;
+        double s = 0.0;
+        for (int k = 0; k < slabs; ++k) s += partial[(long)k * nn + src];
+        out[i] = alpha * s;
+    }
+}
+
+
+// ----------------------------------------------------------------------------------------
+// KFAC A factor of a convolution: A = (1/N) P~' P~ with P~ = [im2col(X) / (Ho*Wo), 1]
+// (solvers/kfac_inverses.cu:515-540), as a tensor-core SYRK over implicit patches: both
+// operands are gathered from X, only lower-triangular tiles are computed, the scaling and
+// the mirror image are applied by the slab reducer.
+// ----------------------------------------------------------------------------------------
+struct PatchSyrkArgs {
+    const double *x;
+    double *out;
+    int N, Cin, H, W, k, pad, Ho, Wo, K, Kb;  // Kb = K + (bias column ? 1 : 0)
+    long M, chunk;
+};
+
+template <int KS>
+__global__ void __launch_bounds__(WG_THREADS, 2) patch_syrk_kernel(PatchSyrkArgs p) {
+    extern __shared__ double smem[];
+    double *Sa = smem;
+    double *Sb = smem + 2 * WG_BQ * WG_LD;
+    const int q0 = blockIdx.x * WG_BQ, c0 = blockIdx.y * WG_BN;
+    if (c0 > q0 + WG_BQ - 1) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_q = warp & 1, warp_n = warp >> 1;
+    const long mbeg = (long)blockIdx.z * p.chunk;
+    const long mend = min(p.M, mbeg + p.chunk);
+    const int k = KS ? KS : p.k, kk2 = k * k;
+    const long chan_stride = (long)p.N * p.W * p.H;
+    const int howo = p.Ho * p.Wo;
+    const int t_m = tid & 15, t_q = tid >> 4;
+    // per-thread column descriptors for both operands: kind 0 = outside, 1 = patch, 2 = ones
+    long off[2][4];
+    int qi[2][4], qj[2][4], kind[2][4];
+#pragma unroll
+    for (int o = 0; o < 2; ++o)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int q = (o == 0 ? q0 : c0) + t_q + 16 * r;
+            kind[o][r] = q < p.K ? 1 : (q < p.Kb ? 2 : 0);
+            const int cin = kind[o][r] == 1 ? q / kk2 : 0;
+            const int rem = kind[o][r] == 1 ? q - cin * kk2 : 0;
+            qj[o][r] = rem / k;
+            qi[o][r] = rem - qj[o][r] * k;
+            off[o][r] = cin * chan_stride + (long)qj[o][r] * p.H + qi[o][r];
+        }
+    const long span = mend > mbeg ? mend - mbeg : 0;
+    const int nk = (int)((span + WG_BK - 1) / WG_BK);
+    double rr[2][4];
+    auto gload = [&](int kt) {
+        const long m = mbeg + (long)kt * WG_BK + t_m;
+        const bool mv = m < mend;
+        int ho = 0, wo = 0;
+        long base = 0;
+        if (mv) {
+            const int n = (int)(m / howo);
+            const int r = (int)(m - (long)n * howo);
+            wo = r / p.Ho;
+            ho = r - wo * p.Ho;
+            base = ((long)n * p.W + (wo - p.pad)) * p.H + (ho - p.pad);
+        }
+#pragma unroll
+        for (int o = 0; o < 2; ++o)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                double v = 0.0;
+                if (mv && kind[o][r] == 1) {
+                    const int h = ho - p.pad + qi[o][r], wv = wo - p.pad + qj[o][r];
+                    if (h >= 0 && h < p.H && wv >= 0 && wv < p.W) v = __ldg(p.x + base + off[o][r]);
+                } else if (mv && kind[o][r] == 2) {
+                    v = 1.0;
+                }
+                rr[o][r] = v;
+            }
+    };
+    auto sstore = [&](int buf) {
+        double *a = Sa + buf * WG_BQ * WG_LD;
+        double *b = Sb + buf * WG_BN * WG_LD;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            a[(t_q + 16 * r) * WG_LD + t_m] = rr[0][r];
+            b[(t_q + 16 * r) * WG_LD + t_m] = rr[1][r];
+        }
+    };
+    double acc[4][2][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+    const int lr = lane >> 2, lc = lane & 3;
+    if (nk > 0) {
+        gload(0);
+        sstore(0);
+    }
+    __syncthreads();
+    for (int kt = 0; kt < nk; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < nk) gload(kt + 1);
+        const double *a = Sa + buf * WG_BQ * WG_LD + (warp_q * 32 + lr) * WG_LD + lc;
+        const double *b = Sb + buf * WG_BN * WG_LD + (warp_n * 16 + lr) * WG_LD + lc;
+#pragma unroll
+        for (int k4 = 0; k4 < WG_BK / 4; ++k4) {
+            double fa[4], fb[2];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) fa[mi] = a[mi * 8 * WG_LD + k4 * 4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) fb[ni] = b[ni * 8 * WG_LD + k4 * 4];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+        }
+        if (kt + 1 < nk) {
+            sstore(buf ^ 1);
+            __syncthreads();
+        }
+    }
+    double *out = p.out + (long)blockIdx.z * p.Kb * p.Kb;
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int col = c0 + warp_n * 16 + ni * 8 + 2 * lc + e;
+            if (col >= p.Kb) continue;
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) {
+                const int row = q0 + warp_q * 32 + mi * 8 + lr;
+                if (row < p.Kb) out[(long)col * p.Kb + row] = acc[mi][ni][e];
+            }
+        }
+}
+
+// A[i][j] = alpha * s_i * s_j * sum of slabs, s = patch_scale for patch columns (< K) and 1 for
+// the ones column; upper triangle mirrored from the computed lower tiles.
+__global__ void patch_syrk_reduce_kernel(const double *partial, double *out, int Kb, int K,
+                                         int slabs, double alpha, double patch_scale) {
+    const long nn = (long)Kb * Kb;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nn;
+         i += (long)gridDim.x * blockDim.x) {
+        const int col = (int)(i / Kb), row = (int)(i - (long)col * Kb);
+        const long src = (col / WG_BN <= row / WG_BQ) ? i : (long)row * Kb + col;
+        double s = 0.0;
+        for (int k = 0; k < slabs; ++k) s += partial[(long)k * nn + src];
+        const double sc = (row < K ? patch_scale : 1.0) * (col < K ? patch_scale : 1.0);
+        out[i] = alpha * sc * s;
+    }
+}
+
+int split_count(long tiles, long reduce_len, long min_len) {
+    long want = (2L * 148 * 2 + tiles - 1) / tiles;  // about two waves of 2 CTAs per SM
+    long cap = std::max(1L, reduce_len / min_len);
+    return (int)std::max(1L, std::min(want, cap));
+}
+
+}  // namespace
+
+void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
+                int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    if (ctx->use_tma && conv_fprop_tma(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout)) return;
+    ConvArgs a{};
+    for (int s = 0; s < nseg; ++s) {
+        a.x[s] = segs[s].x;
+        a.w[s] = segs[s].w;
+    }
+    a.nseg = nseg;
+    a.bias = bias;
+    a.y = y;
+    a.N = N; a.Cin = Cin; a.H = H; a.W = W; a.k = k; a.pad = pad; a.Cout = Cout;
+    a.Ho = H + 2 * pad - k + 1;
+    a.Wo = W + 2 * pad - k + 1;
+    a.K = Cin * k * k;
+    a.M = (long)N * a.Ho * a.Wo;
+    dim3 grid((unsigned)((a.M + FP_BM - 1) / FP_BM), (unsigned)((Cout + FP_BN - 1) / FP_BN));
+    ProfScope prof(ctx, PROF_CONV_IGEMM, 2.0 * (double)a.M * a.K * Cout * nseg);
+    if (k == 3) {
+        conv_fprop_kernel<3><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+    } else if (k == 5) {
+        conv_fprop_kernel<5><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+    } else {
+        conv_fprop_kernel<0><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+    }
+    check_launch(ctx, "conv_fprop_kernel");
+}
+
+void conv_dgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dx, int N, int Cin,
+                int H, int W, int k, int pad, int Cout, double *wscratch) {
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    const long wsz = (long)Cin * Cout * k * k;
+    ConvSeg t[2];
+    for (int s = 0; s < nseg; ++s) {
+        double *wd = wscratch + s * wsz;
+        int blocks = (int)std::min<long>((wsz + 255) / 256, 1184);
+        dgrad_weight_perm_kernel<<<blocks, 256, 0, ctx->stream>>>(segs[s].w, wd, Cin, Cout, k);
+        check_launch(ctx, "dgrad_weight_perm_kernel");
+        t[s].x = segs[s].x;
+        t[s].w = wd;
+    }
+    // a convolution of the errors ([Cout][N][Wo][Ho]) with flipped taps and pad k-1-pad
+    conv_fprop(ctx, nseg, t, nullptr, dx, N, Cout, Ho, Wo, k, k - 1 - pad, Cin);
+}
+
+long conv_wgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    const long M = (long)N * Ho * Wo;
+    const int K = Cin * k * k;
+    const long tiles = (long)((K + WG_BQ - 1) / WG_BQ) * ((Cout + WG_BN - 1) / WG_BN);
+    const int S = split_count(tiles, M, 512);
+    return S > 1 ? (long)S * K * Cout : 0;
+}
+
+void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
+                int H, int W, int k, int pad, int Cout, double *partials) {
+    WgradArgs a{};
+    for (int s = 0; s < nseg; ++s) {
+        a.x[s] = segs[s].x;
+        a.d[s] = segs[s].w;
+    }
+    a.nseg = nseg;
+    a.N = N; a.Cin = Cin; a.H = H; a.W = W; a.k = k; a.pad = pad; a.Cout = Cout;
+    a.Ho = H + 2 * pad - k + 1;
+    a.Wo = W + 2 * pad - k + 1;
+    a.K = Cin * k * k;
+    a.M = (long)N * a.Ho * a.Wo;
+    const int tq = (a.K + WG_BQ - 1) / WG_BQ, tn = (Cout + WG_BN - 1) / WG_BN;
+    const int S = split_count((long)tq * tn, a.M, 512);
+    a.chunk = ((a.M + S - 1) / S + WG_BK - 1) / WG_BK * WG_BK;
+    a.out = S > 1 ? partials : dw;
+    dim3 grid(tq, tn, S);
+    ProfScope prof(ctx, PROF_CONV_WGRAD, 2.0 * (double)a.M * a.K * Cout * nseg);
+    if (k == 3) {
+        conv_wgrad_kernel<3><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+    } else if (k == 5) {
+        conv_wgrad_kernel<5><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+    } else {
+        conv_wgrad_kernel<0><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+    }
+    check_launch(ctx, "conv_wgrad_kernel");
+    if (S > 1) {
+        const long n = (long)a.K * Cout;
+        int blocks = (int)std::min<long>((n + 255) / 256, 1184);
+        reduce_slabs_kernel<<<blocks, 256, 0, ctx->stream>>>(partials, dw, n, S, 1.0);
+        check_launch(ctx, "reduce_slabs_kernel");
+    }
+}
+
+void dgemm(fitre_context *ctx, bool tA, bool tB, int m, int n, int k, double alpha,
+           const double *A, int lda, const double *B, int ldb, double beta, double *C, int ldc) {
+    if (m <= 0 || n <= 0) return;
+    dim3 grid((m + DG_BM - 1) / DG_BM, (n + DG_BN - 1) / DG_BN);
+    if (!tA && !tB)
+        dgemm_kernel<false, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+    else if (!tA && tB)
+        dgemm_kernel<false, true><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+    else if (tA && !tB)
+        dgemm_kernel<true, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+    else
+        dgemm_kernel<true, true><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+    check_launch(ctx, "dgemm_kernel");
+}
+
+static int syrk_splits(long rows, int n) {
+    const long t = (n + WG_BQ - 1) / WG_BQ;
+    return split_count(t * (t + 1) / 2, rows, 512);
+}
+
+long syrk_scratch(long rows, int n) { return (long)syrk_splits(rows, n) * n * n; }
+
+void syrk_tn(fitre_context *ctx, long rows, int n, double alpha, const double *A, long lda,
+             double *C, double *partials) {
+    SyrkArgs a{};
+    a.A = A; a.lda = lda; a.rows = rows; a.n = n;
+    const int S = syrk_splits(rows, n);
+    a.chunk = ((rows + S - 1) / S + WG_BK - 1) / WG_BK * WG_BK;
+    a.out = partials;
+    const int t = (n + WG_BQ - 1) / WG_BQ;
+    dim3 grid(t, t, S);
+    syrk_tn_kernel<<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+    check_launch(ctx, "syrk_tn_kernel");
+    const long nn = (long)n * n;
+    int blocks = (int)std::min<long>((nn + 255) / 256, 1184);
+    syrk_reduce_kernel<<<blocks, 256, 0, ctx->stream>>>(partials, C, n, S, alpha);
+    check_launch(ctx, "syrk_reduce_kernel");
+}
+
+static int patch_syrk_splits(long M, int Kb) {
+    const long t = (Kb + WG_BQ - 1) / WG_BQ;
+    return split_count(t * (t + 1) / 2, M, 512);
+}
+
+long conv_patch_syrk_scratch(int N, int Cin, int H, int W, int k, int pad, bool bias) {
+    const long M = (long)N * (H + 2 * pad - k + 1) * (W + 2 * pad - k + 1);
+    const int Kb = Cin * k * k + (bias ? 1 : 0);
+    return (long)patch_syrk_splits(M, Kb) * Kb * Kb;
+}
+
+void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int Cin, int H, int W,
+                     int k, int pad, bool bias, double alpha, double patch_scale,
+                     double *partials) {
+    PatchSyrkArgs a{};
+    a.x = x;
+    a.out = partials;
+    a.N = N; a.Cin = Cin; a.H = H; a.W = W; a.k = k; a.pad = pad;
+    a.Ho = H + 2 * pad - k + 1;
+    a.Wo = W + 2 * pad - k + 1;
+    a.K = Cin * k * k;
+    a.Kb = a.K + (bias ? 1 : 0);
+    a.M = (long)N * a.Ho * a.Wo;
+    const int S = patch_syrk_splits(a.M, a.Kb);
+    a.chunk = ((a.M + S - 1) / S + WG_BK - 1) / WG_BK * WG_BK;
+    const int t = (a.Kb + WG_BQ - 1) / WG_BQ;
+    dim3 grid(t, t, S);
+    if (k == 3)
+        patch_syrk_kernel<3><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+    else if (k == 5)
+        patch_syrk_kernel<5><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+    else
+        patch_syrk_kernel<0><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+    check_launch(ctx, "patch_syrk_kernel");
+    const long nn = (long)a.Kb * a.Kb;
+    int blocks = (int)std::min<long>((nn + 255) / 256, 1184);
+    patch_syrk_reduce_kernel<<<blocks, 256, 0, ctx->stream>>>(partials, A, a.Kb, a.K, S, alpha,
+                                                              patch_scale);
+    check_launch(ctx, "patch_syrk_reduce_kernel");
+}
+
+void gemm_init_attributes() {
+    conv_tma_init_attributes();
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(syrk_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+}
+
+}  // namespace fitre

@@ -1,0 +1,281 @@
+// Whole-network passes: forward, backward (gradient), R-forward, R-backward (Hessian-vector).
+// They follow the reference's state contract -- every intermediate lands in `z`, the backward
+// errors in `dx`, the R-forward values in `rz`, all with the offsets of CNN_MODEL -- so that a
+// Hessian-vector call can consume what the gradient call left behind
+// (functions/cnn_hessian_vec.cu:18-22).
+// Reference: functions/cnn_forward.cu:48-382, cnn_backward.cu:76-857, cnn_hv_forward.cu:53-222,
+// eval_convolution.cu:52-267,285-539, rop_fc_layer.cu:34-133, cnn_hv_backward.cu:70-912.
+#include <algorithm>
+
+#include "common.h"
+
+namespace fitre {
+namespace {
+
+long align32(long n) { return (n + 31) / 32 * 32; }
+
+long last_pool_elems(const CNN_MODEL *m) {
+    const CONV_LAYER &c = m->convLayer[m->cLayers - 1];
+    const POOL_LAYER &p = m->poolLayer[m->cLayers - 1];
+    return (long)c.outChannels * p.outHeight * p.outWidth * m->batchSize;
+}
+long max_conv_volume(const CNN_MODEL *m) {
+    long v = 0;
+    for (int l = 0; l < m->cLayers; ++l)
+        v = std::max(v, (long)m->convLayer[l].convVolumn * m->batchSize);
+    return v;
+}
+long max_wgrad_scratch(const CNN_MODEL *m) {
+    long v = 0;
+    for (int l = 0; l < m->cLayers; ++l) {
+        const CONV_LAYER &c = m->convLayer[l];
+        v = std::max(v, conv_wgrad_scratch(m->batchSize, c.inChannels, c.height, c.width, c.kSize,
+                                           c.padding, c.outChannels));
+    }
+    return v;
+}
+long max_weight_elems(const CNN_MODEL *m) {
+    long v = 0;
+    for (int l = 0; l < m->cLayers; ++l) {
+        const CONV_LAYER &c = m->convLayer[l];
+        v = std::max(v, (long)c.outChannels * c.inChannels * c.kSize * c.kSize);
+    }
+    return v;
+}
+long max_fc_elems(const CNN_MODEL *m) {
+    long v = 0;
+    for (int l = 0; l < m->lLayers; ++l)
+        v = std::max(v, (long)std::max(m->fcLayer[l].in, m->fcLayer[l].out) * m->batchSize);
+    return v;
+}
+
+const double *layer_input(const CNN_MODEL *m, const DEVICE_DATASET *data, const double *z, int l) {
+    if (l == 0) return data->currentBatch;
+    return z + m->zOffsets[l] + m->convLayer[l - 1].outputOffset;
+}
+
+}  // namespace
+
+long forward_scratch(const CNN_MODEL *m) { return bn_scratch(0) + align32(last_pool_elems(m)); }
+long rop_forward_scratch(const CNN_MODEL *m) { return forward_scratch(m); }
+long backward_scratch(const CNN_MODEL *m) {
+    return bn_scratch(0) + align32(last_pool_elems(m)) + align32(max_wgrad_scratch(m)) +
+           align32(max_weight_elems(m));
+}
+long rop_backward_scratch(const CNN_MODEL *m) {
+    return bn_scratch(0) + align32(last_pool_elems(m)) + align32(max_wgrad_scratch(m)) +
+           2 * align32(max_weight_elems(m)) + align32(max_conv_volume(m)) +
+           2 * align32(max_fc_elems(m));
+}
+
+// ---------------------------------------------------------------------------------------------
+double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                   double *scratch, double *z, double *probs, double *errors, int n,
+                   bool want_loss) {
+    const double *weights = data->weights;
+    double *bnws = scratch;
+    double *tmp = scratch + bn_scratch(0);
+    for (int l = 0; l < m->cLayers; ++l) {
+        const ConvGeom g = conv_geom(m, l);
+        double *zl = z + g.zoff;
+        ConvSeg seg{layer_input(m, data, z, l), weights + m->wOffsets[l]};
+        conv_fprop(ctx, 1, &seg, m->bias ? weights + m->bOffsets[l] : nullptr, zl, n, g.Cin, g.H,
+                   g.W, g.k, g.pad, g.Cout);
+        conv_post_forward(ctx, g, n, zl, bnws);
+    }
+    const ConvGeom lg = conv_geom(m, m->cLayers - 1);
+    // the last convolution block's output is rewritten in the FC layout, as the reference does
+    conv_to_fc(ctx, z + lg.zoff + lg.outOff, lg.Cout, n, lg.Hp, lg.Wp, tmp);
+    long in_off = lg.zoff + lg.outOff;
+    for (int l = 0; l < m->lLayers; ++l) {
+        const FC_LAYER &f = m->fcLayer[l];
+        double *out = z + m->zOffsets[m->cLayers + l + 1];
+        dgemm(ctx, false, false, f.out, n, f.in, 1.0, weights + m->wOffsets[m->cLayers + l], f.out,
+              z + in_off, f.in, 0.0, out + (long)f.out * n, f.out);
+        if (m->bias) add_column_bias(ctx, out + (long)f.out * n, weights + m->bOffsets[m->cLayers + l], f.out, n);
+        apply_activation(ctx, f.actFun, out + (long)f.out * n, out, (long)f.out * n);
+        in_off = m->zOffsets[m->cLayers + l + 1];
+    }
+    const double *logits = z + m->zOffsets[m->cLayers + m->lLayers];
+    const int classes = m->fcLayer[m->lLayers - 1].out;
+    const double inv_ng = 1.0 / ((double)n * ctx->world);
+    softmax_loss(ctx, logits, data->sampledTrainY, n, classes, probs, errors, inv_ng);
+    if (!want_loss) return 0.0;
+    comm_allreduce_sum(ctx, ctx->dscal, 1);
+    FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost,
+                               ctx->stream));
+    FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+    return ctx->pinned[0] * inv_ng;
+}
+
+// ---------------------------------------------------------------------------------------------
+void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                  double *scratch, double *z, double *gradient, double *dx, double *delta,
+                  double *delta_new, int n) {
+    const double *weights = data->weights;
+    const int cL = m->cLayers, lL = m->lLayers;
+    double *bnws = scratch;
+    double *tmp = bnws + bn_scratch(0);
+    double *wg = tmp + align32(last_pool_elems(m));
+    double *wperm = wg + align32(max_wgrad_scratch(m));
+    const ConvGeom lg = conv_geom(m, cL - 1);
+
+    for (int f = lL - 1; f >= 0; --f) {  // functions/cnn_backward.cu:111-280
+        const FC_LAYER &l = m->fcLayer[f];
+        const double *zl = z + m->zOffsets[cL + f + 1];
+        act_backward(ctx, l.actFun, delta, zl + (long)l.out * n, zl, (long)l.out * n);
+        const double *zin = (f == 0) ? z + lg.zoff + lg.outOff : z + m->zOffsets[cL + f];
+        dgemm(ctx, false, true, l.out, l.in, n, 1.0, delta, l.out, zin, l.in, 0.0,
+              gradient + m->wOffsets[cL + f], l.out);
+        if (m->bias) row_sums(ctx, delta, l.out, n, gradient + m->bOffsets[cL + f]);
+        vec_copy(ctx, (long)l.out * n, delta, dx + m->zOffsets[cL + f + 1]);
+        dgemm(ctx, true, false, l.in, n, l.out, 1.0, weights + m->wOffsets[cL + f], l.out, delta,
+              l.out, 0.0, delta_new, l.in);
+        std::swap(delta, delta_new);
+    }
+    fc_to_conv(ctx, delta, lg.Cout, n, lg.Hp, lg.Wp, tmp);  // :310-326
+
+    for (int c = cL - 1; c >= 0; --c) {  // :355-852
+        const ConvGeom g = conv_geom(m, c);
+        const double *zl = z + g.zoff;
+        double *dxl = dx + g.zoff;
+        const double *dconv = conv_post_backward(ctx, g, n, zl, dxl, delta,
+                                                 m->bias ? gradient + m->bOffsets[c] : nullptr, bnws);
+        ConvSeg wseg{layer_input(m, data, z, c), dconv};
+        conv_wgrad(ctx, 1, &wseg, gradient + m->wOffsets[c], n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wg);
+        if (c != 0) {
+            ConvSeg dseg{dconv, weights + m->wOffsets[c]};
+            conv_dgrad(ctx, 1, &dseg, delta_new, n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wperm);
+            std::swap(delta, delta_new);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+void cnn_rop_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                     const double *z, const double *vector, double *rz, int n, double *scratch) {
+    const double *weights = data->weights;
+    double *bnws = scratch;
+    double *tmp = scratch + bn_scratch(0);
+    for (int l = 0; l < m->cLayers; ++l) {
+        const ConvGeom g = conv_geom(m, l);
+        double *rzl = rz + g.zoff;
+        // R{conv} = im2col(X) V + im2col(RX) W + Vb  (functions/eval_convolution.cu:339-381)
+        ConvSeg segs[2];
+        segs[0] = ConvSeg{layer_input(m, data, z, l), vector + m->wOffsets[l]};
+        int nseg = 1;
+        if (l > 0) {
+            segs[1] = ConvSeg{rz + m->zOffsets[l] + m->convLayer[l - 1].outputOffset,
+                              weights + m->wOffsets[l]};
+            nseg = 2;
+        }
+        conv_fprop(ctx, nseg, segs, m->bias ? vector + m->bOffsets[l] : nullptr, rzl, n, g.Cin, g.H,
+                   g.W, g.k, g.pad, g.Cout);
+        conv_post_rop_forward(ctx, g, n, z + g.zoff, rzl, bnws);
+    }
+    const ConvGeom lg = conv_geom(m, m->cLayers - 1);
+    conv_to_fc(ctx, rz + lg.zoff + lg.outOff, lg.Cout, n, lg.Hp, lg.Wp, tmp);
+    long in_off = lg.zoff + lg.outOff;
+    for (int l = 0; l < m->lLayers; ++l) {  // functions/rop_fc_layer.cu:34-133
+        const FC_LAYER &f = m->fcLayer[l];
+        const long cnt = (long)f.out * n;
+        const double *z1 = z + m->zOffsets[m->cLayers + l + 1];
+        double *out = rz + m->zOffsets[m->cLayers + l + 1];
+        double *pre = out + cnt;
+        dgemm(ctx, false, false, f.out, n, f.in, 1.0, vector + m->wOffsets[m->cLayers + l], f.out,
+              z + in_off, f.in, 0.0, pre, f.out);
+        dgemm(ctx, false, false, f.out, n, f.in, 1.0, weights + m->wOffsets[m->cLayers + l], f.out,
+              rz + in_off, f.in, 1.0, pre, f.out);
+        if (m->bias) add_column_bias(ctx, pre, vector + m->bOffsets[m->cLayers + l], f.out, n);
+        vec_copy(ctx, cnt, pre, out);
+        act_backward(ctx, f.actFun, out, z1 + cnt, z1, cnt);
+        in_off = m->zOffsets[m->cLayers + l + 1];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                      const double *z, const double *dx, const double *lossErrors, double *rError,
+                      const double *rz, const double *vector, double *hv, int n, double *scratch) {
+    const double *weights = data->weights;
+    const int cL = m->cLayers, lL = m->lLayers;
+    double *bnws = scratch;
+    double *tmp = bnws + bn_scratch(0);
+    double *wg = tmp + align32(last_pool_elems(m));
+    double *wperm = wg + align32(max_wgrad_scratch(m));
+    double *rout = wperm + 2 * align32(max_weight_elems(m));
+    double *t1 = rout + align32(max_conv_volume(m));
+    double *t2 = t1 + align32(max_fc_elems(m));
+    const ConvGeom lg = conv_geom(m, cL - 1);
+
+    for (int f = lL - 1; f >= 0; --f) {  // functions/cnn_hv_backward.cu:153-395
+        const FC_LAYER &l = m->fcLayer[f];
+        const long cnt = (long)l.out * n;
+        const double *zl = z + m->zOffsets[cL + f + 1];
+        const double *rzl = rz + m->zOffsets[cL + f + 1];
+        const double *dxl = dx + m->zOffsets[cL + f + 1];
+        if (l.actFun != FITRE_CNN_ACT_NONE && l.actFun != FITRE_ACT_LINEAR) {
+            // errors that entered this activation in the backward pass
+            const double *din = lossErrors;
+            if (f != lL - 1) {
+                const FC_LAYER &ll = m->fcLayer[f + 1];
+                dgemm(ctx, true, false, ll.in, n, ll.out, 1.0, weights + m->wOffsets[cL + f + 1],
+                      ll.out, dx + m->zOffsets[cL + f + 2], ll.out, 0.0, t1, ll.in);
+                din = t1;
+            }
+            act_rop_backward(ctx, l.actFun, rError, din, rzl + cnt, zl + cnt, zl, cnt);
+        }
+        const double *zin = (f == 0) ? z + lg.zoff + lg.outOff : z + m->zOffsets[cL + f];
+        const double *rzin = (f == 0) ? rz + lg.zoff + lg.outOff : rz + m->zOffsets[cL + f];
+        double *hw = hv + m->wOffsets[cL + f];
+        dgemm(ctx, false, true, l.out, l.in, n, 1.0, rError, l.out, zin, l.in, 0.0, hw, l.out);
+        dgemm(ctx, false, true, l.out, l.in, n, 1.0, dxl, l.out, rzin, l.in, 1.0, hw, l.out);
+        if (m->bias) row_sums(ctx, rError, l.out, n, hv + m->bOffsets[cL + f]);
+        dgemm(ctx, true, false, l.in, n, l.out, 1.0, weights + m->wOffsets[cL + f], l.out, rError,
+              l.out, 0.0, t2, l.in);
+        dgemm(ctx, true, false, l.in, n, l.out, 1.0, vector + m->wOffsets[cL + f], l.out, dxl,
+              l.out, 1.0, t2, l.in);
+        vec_copy(ctx, (long)l.in * n, t2, rError);
+    }
+    fc_to_conv(ctx, rError, lg.Cout, n, lg.Hp, lg.Wp, tmp);  // :414-427
+
+    for (int c = cL - 1; c >= 0; --c) {  // :436-907
+        const ConvGeom g = conv_geom(m, c);
+        const double *zl = z + g.zoff, *rzl = rz + g.zoff, *dxl = dx + g.zoff;
+        conv_post_rop_backward(ctx, g, n, zl, rzl, dxl, rError, rout,
+                               m->bias ? hv + m->bOffsets[c] : nullptr, bnws);
+        const double *dprev = g.bn ? dxl + g.bnOff : dxl + g.actOff;
+        // R dW = im2col(X)' Rdelta + im2col(RX)' delta  (:727-803)
+        ConvSeg ws[2];
+        ws[0] = ConvSeg{layer_input(m, data, z, c), rout};
+        int nseg = 1;
+        if (c != 0) {
+            ws[1] = ConvSeg{rz + m->zOffsets[c] + m->convLayer[c - 1].outputOffset, dprev};
+            nseg = 2;
+        }
+        conv_wgrad(ctx, nseg, ws, hv + m->wOffsets[c], n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wg);
+        if (c != 0) {  // Rdelta <- dgrad(Rdelta, W) + dgrad(delta, V)  (:854-898)
+            ConvSeg ds[2] = {ConvSeg{rout, weights + m->wOffsets[c]},
+                             ConvSeg{dprev, vector + m->wOffsets[c]}};
+            conv_dgrad(ctx, 2, ds, rError, n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wperm);
+        }
+    }
+}
+
+// functions/cnn_hessian_vec.cu:18-122: devPtr = [rz (zSize) | rError (maxDelta) | scratch]
+void cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, const double *z,
+            const double *probs, const double *lossErrors, const double *dx, const double *vector,
+            double *hv, int n, double *devPtr) {
+    double *rz = devPtr;
+    double *rError = rz + align32(m->zSize);
+    double *scratch = rError + align32(max_delta_elems(m));
+    cnn_rop_forward(ctx, m, data, z, vector, rz, n, scratch);
+    const int classes = m->fcLayer[m->lLayers - 1].out;
+    const double inv_ng = 1.0 / ((double)n * ctx->world);
+    softmax_rop_error(ctx, rz + m->zOffsets[m->cLayers + m->lLayers], probs, n, classes, rError,
+                      inv_ng);
+    cnn_rop_backward(ctx, m, data, z, dx, lossErrors, rError, rz, vector, hv, n, scratch);
+    comm_allreduce_sum(ctx, hv, m->pSize);
+}
+
+}  // namespace fitre

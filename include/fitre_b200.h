@@ -169,6 +169,20 @@ long long fitre_launch_count(const fitre_context *ctx);
  * probs += 1e-10: functions/softmax_loss.cu:24-27,55); 0 = textbook softmax. Default 1. */
 int fitre_set_reference_softmax(fitre_context *ctx, int on);
 
+/* 1 (default) = use the TMA-fed convolution kernels wherever shape and alignment allow;
+ * 0 = always use the gather kernels (same results; kept for comparison and as the path
+ * for odd shapes).  No counterpart in the reference. */
+int fitre_set_tma(fitre_context *ctx, int on);
+
+/* Optional per-kernel timing.  While enabled, every launch of the two convolution kernel
+ * classes (0 = implicit-GEMM forward / data-gradient kernel, 1 = weight-gradient kernel) is
+ * bracketed by CUDA events on the context's stream.  fitre_profile_read synchronises the
+ * stream, returns the summed device time (ms), algorithmic flops (2*M*K*Cout per product)
+ * and launch count of one class since the last read, and clears them.  No counterpart in
+ * the reference (its timers are gettimeofday around whole phases, utilities/utils.c:16-33). */
+int fitre_profile_enable(fitre_context *ctx, int on);
+int fitre_profile_read(fitre_context *ctx, int kind, double *ms, double *flops, long *launches);
+
 /* Data-parallel set-up: `unique_id` is the 128-byte ncclUniqueId obtained on rank 0
  * (fitre_comm_unique_id) and broadcast by the caller.  After this call every batch
  * statistic (loss, batch-norm sums, gradient, Hv, KFAC factors, dot products) is
@@ -256,6 +270,8 @@ int fitre_cg_steihaug(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
 
 /* ---- KFAC factors (solvers/kfac_utils.cu:7-55, kfac_inverses.cu:450-630,759-857) */
 int fitre_kfac_storage_indices(const CNN_MODEL *m, FITRE_KFAC_INFO *info);
+/* Scratch (doubles) the two factor routines below need behind devPtr. */
+long fitre_kfac_mem_required(const CNN_MODEL *m);
 /* A factors: conv (1/N) P~'P~ with P~ = [im2col(X)/(Ho*Wo), 1]; FC (1/N) z~ z~'.  Raw
  * (undamped, uninverted) factors are written to omegaZ + OmegaZOffsets[l]. */
 int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,

@@ -1,0 +1,250 @@
+"""GPU parity tests: the CUDA library (through the C ABI) against the committed golden
+fixtures and against the CPU oracle on the same seeded inputs.  Tolerance: 1e-10 relative
+(fp64), both norm-wise and max-wise; integer artefacts (arg-max routing) show up as exact
+agreement of the routed tensors."""
+import ctypes as C
+import glob
+import json
+import os
+
+import numpy as np
+import pytest
+
+import nets
+import oracle_lib as O
+from fitre_b200 import _structs as S
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-10
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+FLAGS = {"Small Residue": S.CG_CONVERGED, "Negative Curvature": S.CG_NEG_CURVATURE,
+         "Hit Boundary": S.CG_HIT_BOUNDARY, "Maximum Iterations": S.CG_MAX_ITERS}
+
+
+def load_case(path):
+    d = np.load(path, allow_pickle=False)
+    spec = json.loads(str(d["spec"]))
+    model = getattr(nets, spec["builder"])(spec["batch"], **spec["kwargs"])
+    return d, spec, model
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_cuda_matches_golden(path):
+    import gpu_util as G
+    d, spec, model = load_case(path)
+    run = G.GpuRun(model, d["batch"], d["labels"], d["weights"], spec["classes"], ref_softmax=0)
+    assert abs(run.loss - float(d["loss"])) <= TOL * abs(float(d["loss"]))
+    assert G.rel(run.gradient, d["gradient"]) < TOL
+    assert G.relmax(run.gradient, d["gradient"]) < TOL
+    hv = run.hv(d["vector"])
+    assert G.rel(hv, d["hv"]) < TOL
+    assert G.relmax(hv, d["hv"]) < TOL
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_cuda_quadratic_model_and_cg_match_golden(path):
+    import gpu_util as G
+    from fitre_b200 import api
+    d, spec, model = load_case(path)
+    run = G.GpuRun(model, d["batch"], d["labels"], d["weights"], spec["classes"], ref_softmax=0)
+    ws = run.ws
+    g = ws.gradient.clone()
+    v = G.dev(d["vector"])
+    mval = api.computeQuadraticModel(run.c, model, run.data, ws.z, ws.probs, ws.errors, ws.dx, g, v,
+                                     float(d["clip_delta"]), 0, run.n, 0.0, ws.dev)
+    assert abs(mval - float(d["clip_model"])) <= 1e-9 * abs(float(d["clip_model"]))
+    assert G.rel(v.cpu().numpy(), d["clip_vector"]) < 1e-9
+    for tag in ("cg", "cgb", "cgw"):
+        prm = S.CG_PARAMS()
+        prm.delta = float(d[tag + "_delta"])
+        prm.tolerance = 1e-30
+        prm.maxIterations = 10
+        prm.weightDecay = float(d["cgw_weight"]) if tag == "cgw" else 0.0
+        p = G.dev(np.zeros(model.pSize))
+        api.cgSteihaug(run.c, model, run.data, ws.z, ws.probs, ws.errors, ws.dx, g, p, run.n,
+                       ws.dev, prm)
+        assert prm.flag == FLAGS[str(d[tag + "_flag"])], tag
+        assert prm.iterations == int(d[tag + "_iters"]), tag
+        assert G.rel(p.cpu().numpy(), d[tag + "_p"]) < 1e-7, tag
+        assert abs(prm.modelValue - float(d[tag + "_model"])) <= 1e-7 * abs(float(d[tag + "_model"])), tag
+
+
+CASES = [
+    ("test_vgg", dict(), 7),
+    ("test_vgg", dict(bn=True, act=S.CNN_ACT_SWISH), 5),
+    ("lenet_small", dict(), 9),
+    ("lenet_small", dict(act=S.CNN_ACT_RELU, pool=S.MAX_POOL), 9),
+    ("lenet_small", dict(act=S.CNN_ACT_SOFTPLUS, bias=False), 3),
+    ("alexnet_small", dict(), 8),
+    ("alexnet_small", dict(bn=False, bias=True, ch=5, hw=12), 6),
+    ("vgg_small", dict(), 6),
+    ("vgg_small", dict(act=S.CNN_ACT_RELU, bias=True), 4),
+    ("vgg_small", dict(act=S.CNN_ACT_SOFTPLUS, bn=False, hw=16), 3),
+    ("lenet", dict(), 16),
+    ("lenet", dict(act=S.CNN_ACT_RELU, pool=S.MAX_POOL), 16),
+]
+
+
+@pytest.mark.parametrize("builder,kwargs,n", CASES,
+                         ids=["%s-%d" % (c[0], i) for i, c in enumerate(CASES)])
+def test_cuda_matches_oracle(builder, kwargs, n):
+    """Same seeded inputs through the CUDA path and the oracle, reference-exact softmax;
+    compares loss, gradient, Hv and the whole z / dx state (arg-max routing included)."""
+    import gpu_util as G
+    model = getattr(nets, builder)(n, **kwargs)
+    O.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=100 + n)
+    st = O.gradient(model, x, y, w, ncls, n, weight_decay=1e-3)
+    hv_o = O.hv(model, x, w, ncls, n, st, v)
+    run = G.GpuRun(model, x, y, w, ncls, ref_softmax=1, weight_decay=1e-3)
+    assert abs(run.loss - st.loss) <= TOL * abs(st.loss)
+    assert G.rel(run.gradient, st.gradient) < TOL
+    assert G.relmax(run.gradient, st.gradient) < TOL
+    hv = run.hv(v)
+    assert G.rel(hv, hv_o) < TOL
+    assert G.relmax(hv, hv_o) < TOL
+    # stored state: everything except the running batch-norm statistics (uninitialised input)
+    z = run.ws.z.cpu().numpy()
+    dx = run.ws.dx.cpu().numpy()
+    mask = np.ones(model.zSize, dtype=bool)
+    for l in range(model.cLayers):
+        c = model.convLayer[l]
+        if c.batchNorm != S.NO_BATCH_NORM:
+            b = model.zOffsets[l + 1] + c.batchNormOffset
+            mask[b + c.runningMeansOffset:b + c.runningVariancesOffset + c.outChannels] = False
+    assert G.relmax(z[mask], st.z[mask]) < TOL
+    # dx: compare the slots the backward pass defines
+    for l in range(model.cLayers):
+        c = model.convLayer[l]
+        V = c.convVolumn * n
+        b = model.zOffsets[l + 1]
+        for off in (0, c.activationOffset) + ((c.batchNormOffset,) if c.batchNorm else ()):
+            assert G.relmax(dx[b + off:b + off + V], st.dx[b + off:b + off + V]) < TOL
+
+
+def test_cuda_midsize_alexnet_and_vgg11_vs_oracle():
+    import gpu_util as G
+    for model, n in ((nets.alexnet(16), 16), (nets.vgg11(8), 8)):
+        O.finalize(model)
+        x, y, w, v, ncls = G.synth(model, n, seed=7)
+        st = O.gradient(model, x, y, w, ncls, n)
+        hv_o = O.hv(model, x, w, ncls, n, st, v)
+        run = G.GpuRun(model, x, y, w, ncls)
+        assert abs(run.loss - st.loss) <= TOL * abs(st.loss)
+        assert G.rel(run.gradient, st.gradient) < TOL
+        assert G.rel(run.hv(v), hv_o) < TOL
+
+
+def test_cuda_kfac_factors_vs_oracle():
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    for builder, kwargs, n in (("vgg_small", dict(), 6), ("lenet_small", dict(), 5),
+                               ("alexnet_small", dict(bias=True), 4)):
+        model = getattr(nets, builder)(n, **kwargs)
+        O.finalize(model)
+        x, y, w, v, ncls = G.synth(model, n, seed=31)
+        st = O.gradient(model, x, y, w, ncls, n)
+        info = S.KFAC_INFO()
+        assert O.lib().ora_kfac_storage_indices(C.byref(model), C.byref(info)) == 0
+        A_o = np.zeros(info.OmegaZSize)
+        G_o = np.zeros(info.LambdaGSize)
+        env = O.make_env()
+        O.lib().ora_kfac_omega_z(C.byref(env), C.byref(model), x, st.z, n, A_o, C.byref(info))
+        O.lib().ora_kfac_lambda_delta(C.byref(env), C.byref(model), st.dx, n, G_o, C.byref(info))
+        run = G.GpuRun(model, x, y, w, ncls)
+        info2 = api.computeKFACStorageIndices(model)
+        assert list(info2.OmegaZOffsets) == list(info.OmegaZOffsets)
+        assert list(info2.LambdaGOffsets) == list(info.LambdaGOffsets)
+        need = _lib.load().fitre_kfac_mem_required(C.byref(model))
+        scratch = G.dev(np.zeros(need))
+        A = G.dev(np.zeros(info.OmegaZSize))
+        Gm = G.dev(np.zeros(info.LambdaGSize))
+        api.computeOmegaZ(run.c, model, run.data, run.ws.z, n, A, info2, scratch)
+        api.computeLambdaDelta(run.c, model, run.ws.dx, n, Gm, info2, scratch)
+        A, Gm = A.cpu().numpy(), Gm.cpu().numpy()
+        L = model.cLayers + model.lLayers
+        for l in range(L):
+            # used part of each A block: K' x K' with K' = K + bias
+            if l < model.cLayers:
+                c = model.convLayer[l]
+                kb = c.inChannels * c.kSize ** 2 + (1 if model.bias else 0)
+            else:
+                kb = model.fcLayer[l - model.cLayers].in_ + (1 if model.bias else 0)
+            a0 = info.OmegaZOffsets[l]
+            assert G.relmax(A[a0:a0 + kb * kb], A_o[a0:a0 + kb * kb]) < TOL, l
+            g0, g1 = info.LambdaGOffsets[l], info.LambdaGOffsets[l + 1]
+            assert G.relmax(Gm[g0:g1], G_o[g0:g1]) < TOL, l
+
+
+def test_cuda_host_entry_point():
+    import gpu_util as G
+    from fitre_b200 import api
+    n = 6
+    model = nets.vgg_small(n)
+    O.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=77)
+    st = O.gradient(model, x, y, w, ncls, n)
+    hv_o = O.hv(model, x, w, ncls, n, st, v)
+    g, hv = np.zeros(model.pSize), np.zeros(model.pSize)
+    c = G.ctx(1)
+    for _ in range(2):  # second call reuses the context workspace
+        loss = api.gradientHvHost(c, model, x, y, w, v, n, ncls, 0.0, g, hv)
+        assert abs(loss - st.loss) <= TOL * abs(st.loss)
+        assert G.rel(g, st.gradient) < TOL and G.rel(hv, hv_o) < TOL
+
+
+def test_cuda_rejects_bad_arguments():
+    import gpu_util as G
+    from fitre_b200 import api
+    model = nets.vgg_small(4)
+    api.finalize(model)
+    x, y, w, v, ncls = G.synth(model, 4, seed=1)
+    run = G.GpuRun(model, x, y, w, ncls)
+    with pytest.raises(api.FitreError) as e:  # partial batches are outside the path
+        api.computeCNNGradient(run.c, model, run.data, run.ws.scratch, run.ws.z, run.ws.dx,
+                               run.ws.probs, run.ws.errors, run.ws.gradient, 0, 3, 0.0)
+    assert e.value.status == S.ERR_BAD_ARG
+    bad = nets.vgg_small(4)
+    bad.convLayer[0].stride = 2
+    api.finalize(bad)
+    with pytest.raises(api.FitreError) as e:
+        G.GpuRun(bad, x, y, w, ncls)
+    assert e.value.status == S.ERR_UNSUPPORTED
+
+
+def test_cuda_full_size_properties_vgg11():
+    """VGG-11-BN at 512 images (the benchmark shape), where the oracle is too slow:
+    Hv is linear and symmetric, and gradient / Hv agree with central differences of the
+    loss / gradient along a random direction."""
+    import torch
+    import gpu_util as G
+    n = 512
+    model = nets.vgg11(n)
+    O.finalize(model)
+    x, y, w, v1, ncls = G.synth(model, n, seed=3234)
+    v2 = np.random.default_rng(9).standard_normal(model.pSize)
+    run = G.GpuRun(model, x, y, w, ncls, ref_softmax=0)
+    h1, h2 = run.hv(v1), run.hv(v2)
+    h12 = run.hv(0.3 * v1 - 1.7 * v2)
+    assert G.rel(h12, 0.3 * h1 - 1.7 * h2) < 1e-9
+    s12, s21 = v1.dot(h2), v2.dot(h1)
+    assert abs(s12 - s21) <= 1e-8 * max(abs(s12), abs(s21))
+    g = run.gradient.copy()
+    d = g / np.linalg.norm(g)          # steepest-ascent direction: g.d = |g| is well scaled
+    hd = run.hv(d)
+    del run
+    torch.cuda.empty_cache()
+    h = 1e-3
+    rp = G.GpuRun(model, x, y, w + h * d, ncls, ref_softmax=0)
+    fp, gp = rp.loss, rp.gradient.copy()
+    del rp
+    torch.cuda.empty_cache()
+    rm = G.GpuRun(model, x, y, w - h * d, ncls, ref_softmax=0)
+    fm, gm = rm.loss, rm.gradient.copy()
+    del rm
+    torch.cuda.empty_cache()
+    fd_g = (fp - fm) / (2 * h)
+    assert abs(fd_g - g.dot(d)) <= 1e-4 * abs(g.dot(d)), (fd_g, g.dot(d))
+    fd_h = (gp - gm) / (2 * h)
+    assert G.rel(fd_h, hd) < 1e-2, G.rel(fd_h, hd)
