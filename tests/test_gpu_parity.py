@@ -215,8 +215,8 @@ def test_cuda_rejects_bad_arguments():
 
 def test_cuda_full_size_properties_vgg11():
     """VGG-11-BN at 512 images (the benchmark shape), where the oracle is too slow:
-    Hv is linear and symmetric, and gradient / Hv agree with central differences of the
-    loss / gradient along a random direction."""
+    Hv is linear and symmetric, and the directional derivative and curvature along the
+    gradient direction agree with central differences of the loss."""
     import torch
     import gpu_util as G
     n = 512
@@ -230,21 +230,23 @@ def test_cuda_full_size_properties_vgg11():
     assert G.rel(h12, 0.3 * h1 - 1.7 * h2) < 1e-9
     s12, s21 = v1.dot(h2), v2.dot(h1)
     assert abs(s12 - s21) <= 1e-8 * max(abs(s12), abs(s21))
-    g = run.gradient.copy()
+    g, f0 = run.gradient.copy(), run.loss
     d = g / np.linalg.norm(g)          # steepest-ascent direction: g.d = |g| is well scaled
-    hd = run.hv(d)
+    dHd = d.dot(run.hv(d))
     del run
     torch.cuda.empty_cache()
-    h = 1e-3
+    h = 1e-4
     rp = G.GpuRun(model, x, y, w + h * d, ncls, ref_softmax=0)
-    fp, gp = rp.loss, rp.gradient.copy()
+    fp = rp.loss
     del rp
     torch.cuda.empty_cache()
     rm = G.GpuRun(model, x, y, w - h * d, ncls, ref_softmax=0)
-    fm, gm = rm.loss, rm.gradient.copy()
+    fm = rm.loss
     del rm
     torch.cuda.empty_cache()
     fd_g = (fp - fm) / (2 * h)
     assert abs(fd_g - g.dot(d)) <= 1e-4 * abs(g.dot(d)), (fd_g, g.dot(d))
-    fd_h = (gp - gm) / (2 * h)
-    assert G.rel(fd_h, hd) < 1e-2, G.rel(fd_h, hd)
+    # curvature along d from the loss alone (a component-wise difference of gradients is
+    # dominated by max-pool arg-max switches at this size and is not a usable check)
+    fd_h = (fp - 2 * f0 + fm) / (h * h)
+    assert abs(fd_h - dHd) <= 2e-2 * abs(dHd), (fd_h, dHd)
