@@ -10,6 +10,7 @@
 // (row r = n*Ho*Wo + wo*Ho + ho, column q = cin*k*k + j*k + i, zero outside the image).
 // tcgen05 has no fp64 kind, so the fp64 path uses mma.sync m8n8k4 (DMMA).
 #include <algorithm>
+#include <mutex>
 
 #include "common.h"
 
@@ -870,3 +871,81 @@ void gemm_init_attributes() {
 }
 
 }  // namespace fitre
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the A'A product (the KFAC G-factor kernel).
+//
+// Some callers cannot allocate device memory at all: a driver that has already handed every
+// free byte to its own bump-pointer workspace (the reference does exactly that,
+// device/cuda_environment.c:48-66), code running between the capture calls of a stream, or a
+// host thread that is not allowed to take the allocator's lock.  For them the split-sum slabs
+// of the product live in the fixed device array below instead of caller-provided scratch.
+// Every GPU that loads this library holds the array (8 MiB) until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace fitre {
+namespace {
+constexpr long kStaticSlabDoubles = 1L << 20;  // 8 MiB: the stated maximum of the entry point
+static __device__ __align__(256) double g_static_slabs[kStaticSlabDoubles];
+constexpr int kMaxDevices = 64;
+double *g_static_slabs_addr[kMaxDevices];  // device address per device, resolved on first use
+std::mutex g_static_slabs_mutex;
+}  // namespace
+}  // namespace fitre
+
+// C (n x n, column-major, both triangles) = alpha * A' A, A rows x n column-major with leading
+// dimension lda.  Same kernels and the same arithmetic as the G-factor blocks of
+// fitre_kfac_lambda_delta; the only difference is where the split-sum slabs live.
+//   * allocates nothing: no cudaMalloc / cudaFree, no allocating library call, no context;
+//   * the first call on a device looks the array's device address up (cudaGetSymbolAddress on
+//     the current device); make that first call before starting any stream capture;
+//   * limit: splits * n * n <= 2^20 doubles, so n <= 1024; larger n returns
+//     FITRE_ERR_TOO_LARGE and prints the limit;
+//   * every call on a device shares the one array and leaves its slabs behind; the kernels
+//     overwrite every slab entry they later read, so nothing needs clearing, but two calls
+//     whose kernels overlap on the GPU (different streams) race on it: serialise them.
+extern "C" int fitre_syrk_tn_static_scratch(const real *A, long rows, int n, long lda, real alpha,
+                                            real *C, void *stream) {
+    using namespace fitre;
+    if (!A || !C || rows < 1 || n < 1 || lda < rows) return FITRE_ERR_BAD_ARG;
+    const long nn = (long)n * n;
+    if (nn > kStaticSlabDoubles) {
+        std::fprintf(stderr,
+                     "fitre_syrk_tn_static_scratch: n = %d needs %ld doubles of slab space, the "
+                     "built-in array holds %ld (n <= 1024)\n", n, nn, kStaticSlabDoubles);
+        return FITRE_ERR_TOO_LARGE;
+    }
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FITRE_ERR_CUDA;
+    double *slabs = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_slabs_mutex);
+        if (!g_static_slabs_addr[dev]) {
+            // In host code the array's name is only a handle; the kernels need this address.
+            void *p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_static_slabs) != cudaSuccess || !p) {
+                cudaGetLastError();
+                return FITRE_ERR_CUDA;
+            }
+            g_static_slabs_addr[dev] = (double *)p;
+        }
+        slabs = g_static_slabs_addr[dev];
+    }
+    const long t = (n + WG_BQ - 1) / WG_BQ;
+    long S = split_count(t * (t + 1) / 2, rows, 512);
+    S = std::max(1L, std::min(S, kStaticSlabDoubles / nn));  // fewer splits rather than more space
+    SyrkArgs a{};
+    a.A = A;
+    a.lda = lda;
+    a.rows = rows;
+    a.n = n;
+    a.chunk = ((rows + S - 1) / S + WG_BK - 1) / WG_BK * WG_BK;
+    a.out = slabs;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((unsigned)t, (unsigned)t, (unsigned)S);
+    syrk_tn_kernel<<<grid, WG_THREADS, WG_SMEM, st>>>(a);
+    if (cudaGetLastError() != cudaSuccess) return FITRE_ERR_CUDA;
+    const int blocks = (int)std::min<long>((nn + 255) / 256, 1184);
+    syrk_reduce_kernel<<<blocks, 256, 0, st>>>(slabs, C, n, (int)S, alpha);
+    if (cudaGetLastError() != cudaSuccess) return FITRE_ERR_CUDA;
+    return FITRE_OK;
+}

@@ -281,6 +281,17 @@ int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATA
 int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, const real *dx, int samples,
                             real *lambdaG, const FITRE_KFAC_INFO *info, real *devPtr);
 
+/* C (n x n, both triangles) = alpha * A'A with A rows x n column-major (lda), the product behind
+ * every G-factor block above, for callers that cannot allocate device memory (a driver whose
+ * workspace already owns all of it, code between stream-capture calls, threads barred from the
+ * allocator): it needs no context and no scratch argument because its split-sum slabs live in
+ * an 8 MiB array built into the library (held on every GPU that loads it).  Limit n <= 1024
+ * (FITRE_ERR_TOO_LARGE beyond).  The first call on a device resolves the array's address and
+ * should precede any stream capture; calls that overlap on the GPU race on the shared array.
+ * `stream` is a cudaStream_t.  This entry point has no counterpart in the reference. */
+int fitre_syrk_tn_static_scratch(const real *A, long rows, int n, long lda, real alpha, real *C,
+                                 void *stream);
+
 /* ---- host-buffer entry point (what a reference driver calls per minibatch) ---- */
 /* One gradient + one Hessian-vector product with HOST inputs and outputs: copies the
  * batch, labels, weights and `vector` to the device, runs fitre_compute_cnn_gradient and
