@@ -137,6 +137,9 @@ void gemm_init_attributes();
 void conv_tma_init_attributes();
 bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias,
                     double *y, int N, int Cin, int H, int W, int k, int pad, int Cout);
+long conv_wgrad_tma_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
+bool conv_wgrad_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
+                    int H, int W, int k, int pad, int Cout, double *partials);
 // Device-side error word (set by a kernel whose bounded wait ran out): dscal[4000] as int.
 void check_device_error(fitre_context *ctx);
 

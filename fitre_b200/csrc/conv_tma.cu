@@ -195,6 +195,161 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
         }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// TMA-fed weight gradient: dW[K x Cout] = sum_seg im2col(X_seg)' * D_seg, reduction over
+// M = N*Ho*Wo split across blockIdx.z (slabs summed afterwards in fixed order).
+// CTA tile: 128 rows of q = (cin, j, i) x 64 output channels.  Per step of BMT output positions
+// (a box: all Ho rows x TW columns x TN images, contiguous in M) TMA brings
+//   * the raw input patch of that box for the <= CBW input channels the 128 q-rows touch, and
+//   * the BMT x 64 slab of the errors as BMT/16 boxes with the 128-byte swizzle, so that the
+//     DMMA B fragments (4 consecutive m x 8 channels) are read without bank conflicts.
+// A fragments come straight from the patch: element (q, m) = patch[rowbase(m) + qofs(q)].
+// ---------------------------------------------------------------------------------------------
+constexpr int W_BQ = 128, W_BN = 64;
+
+struct alignas(64) TmaWgradArgs {
+    CUtensorMap xmap[2];
+    CUtensorMap dmap[2];
+    double *out;   // dW (splits == 1) or slabs [split][K*Cout]
+    int *err;
+    long M;
+    int nseg, N, K, Cout, Ho, Wo, pad, TW, TN, HB, WB, xoff, x0, CBW, stages, tilesW;
+    int tiles_total, tiles_per_split, patchBytes;
+};
+
+template <int KS, int BMT>
+__global__ void __launch_bounds__(T_THREADS, 2)
+wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
+    extern __shared__ unsigned char smraw[];
+    unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 1023) & ~(uintptr_t)1023);
+    constexpr int dBytes = BMT * W_BN * 8;           // BMT/16 swizzled boxes of 16 x 64 doubles
+    const int stageBytes = dBytes + p.patchBytes;    // [errors | patch], both 1024-aligned
+    int *rowbase_s = (int *)(sm + (size_t)p.stages * stageBytes);
+    unsigned long long *bars = (unsigned long long *)(rowbase_s + BMT);
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_q = warp & 3, warp_n = warp >> 2;
+    const int lr = lane >> 2, lc = lane & 3;
+    const int q0 = blockIdx.x * W_BQ, c0 = blockIdx.y * W_BN;
+    const int c_lo = q0 / (KS * KS);
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) mbar_init(smem_u32(bars + s), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int ml = tid; ml < BMT; ml += T_THREADS) {
+        const int ho = ml % p.Ho, r = ml / p.Ho;
+        const int wl = r % p.TW, nl = r / p.TW;
+        rowbase_s[ml] = (nl * p.WB + wl) * p.HB + ho + p.xoff;
+    }
+    __syncthreads();
+
+    int qofs[4];
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi) {
+        const int q = q0 + warp_q * 32 + mi * 8 + lr;
+        const int c = q / (KS * KS), rem = q - c * (KS * KS);
+        const int j = rem / KS, i = rem - j * KS;
+        // rows beyond K fall on channels >= Cin, which TMA zero-fills; clamp keeps the address
+        // inside the patch for the last tile
+        const int cl = min(c - c_lo, p.CBW - 1);
+        qofs[mi] = (q < p.K) ? (cl * p.TN * p.WB + j) * p.HB + i : -1;
+    }
+    // swizzled B addressing: channel row r = warp_n*32 + (ni>>1)*16 + 2*lr + (ni&1); within a
+    // 16-double box row the 16-byte chunk index is XORed with (r & 7)
+    int brow[4];
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni) brow[ni] = warp_n * 32 + (ni >> 1) * 16 + 2 * lr + (ni & 1);
+
+    const int t_beg = blockIdx.z * p.tiles_per_split;
+    const int t_end = min(p.tiles_total, t_beg + p.tiles_per_split);
+    const int ntile = max(0, t_end - t_beg);
+    const int iters = ntile * p.nseg;
+    const uint32_t txBytes = (uint32_t)(p.HB * p.WB * p.TN * p.CBW * 8 + dBytes);
+    auto issue = [&](int it) {
+        const int seg = it / ntile, t = t_beg + (it - seg * ntile);
+        const int wt = t % p.tilesW, nt = t / p.tilesW;
+        const int s = it % p.stages;
+        const uint32_t bar = smem_u32(bars + s);
+        unsigned char *dst = sm + (size_t)s * stageBytes;
+        mbar_expect_tx(bar, txBytes);
+        const int mstart = t * BMT;
+#pragma unroll
+        for (int b = 0; b < BMT / 16; ++b)
+            tma_load_2d(smem_u32(dst + b * (16 * W_BN * 8)), &p.dmap[seg], bar, mstart + 16 * b, c0);
+        tma_load_4d(smem_u32(dst + dBytes), &p.xmap[seg], bar, p.x0, wt * p.TW - p.pad, nt * p.TN, c_lo);
+    };
+    if (tid == 0)
+        for (int it = 0; it < p.stages - 1 && it < iters; ++it) issue(it);
+
+    double acc[4][4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+    for (int it = 0; it < iters; ++it) {
+        const int s = it % p.stages;
+        if (tid == 0 && it + p.stages - 1 < iters) issue(it + p.stages - 1);
+        const bool ready = mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1));
+        if (!ready) {
+            abort_flag = 1;
+        } else {
+            const double *dS = (const double *)(sm + (size_t)s * stageBytes);
+            const double *patch = (const double *)(sm + (size_t)s * stageBytes + dBytes);
+#pragma unroll
+            for (int k4 = 0; k4 < BMT / 4; ++k4) {
+                const int rb = rowbase_s[k4 * 4 + lc];
+                const double *box = dS + (k4 >> 2) * (16 * W_BN);
+                const int chunk = (k4 & 3) * 2 + (lc >> 1);
+                double fa[4], fb[4];
+#pragma unroll
+                for (int mi = 0; mi < 4; ++mi) fa[mi] = qofs[mi] >= 0 ? patch[rb + qofs[mi]] : 0.0;
+#pragma unroll
+                for (int ni = 0; ni < 4; ++ni)
+                    fb[ni] = box[brow[ni] * 16 + ((chunk ^ (brow[ni] & 7)) << 1) + (lc & 1)];
+#pragma unroll
+                for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                    for (int ni = 0; ni < 4; ++ni)
+                        dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+            }
+        }
+        __syncthreads();
+        if (abort_flag) {
+            if (tid == 0) atomicExch(p.err, 1);
+            return;
+        }
+    }
+
+    double *out = p.out + (long)blockIdx.z * p.K * p.Cout;
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            // mma column 2*lc+e of tile ni is channel row warp_n*32 + (ni>>1)*16 + 2*(2*lc+e) + (ni&1)
+            const int col = c0 + warp_n * 32 + (ni >> 1) * 16 + 2 * (2 * lc + e) + (ni & 1);
+            if (col >= p.Cout) continue;
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) {
+                const int row = q0 + warp_q * 32 + mi * 8 + lr;
+                if (row < p.K) out[(long)col * p.K + row] = acc[mi][ni][e];
+            }
+        }
+}
+
+__global__ void reduce_slabs_tma_kernel(const double *partial, double *out, long n, int slabs) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n;
+         i += (long)gridDim.x * blockDim.x) {
+        double s = 0.0;
+        for (int k = 0; k < slabs; ++k) s += partial[(long)k * n + i];
+        out[i] = s;
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -215,18 +370,80 @@ EncodeTiledFn encode_fn() {
 }
 
 bool encode(CUtensorMap *map, const void *base, int rank, const cuuint64_t *dims,
-            const cuuint64_t *strides_bytes, const cuuint32_t *box) {
+            const cuuint64_t *strides_bytes, const cuuint32_t *box,
+            CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_NONE) {
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, (cuuint32_t)rank, (void *)base, dims,
                              strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
+}
+
+// Tiling plan of the TMA weight-gradient kernel; ok == false when shape/alignment rule it out.
+struct WgradPlan {
+    bool ok = false;
+    int BMT = 0, TW = 0, TN = 0, HB = 0, WB = 0, x0 = 0, xoff = 0, CBW = 0, patchBytes = 0;
+    int stages = 0, tiles_total = 0, splits = 1, tiles_per_split = 0, tq = 0, tn = 0, smem = 0;
+};
+
+WgradPlan wgrad_plan(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    WgradPlan pl;
+    if (!encode_fn() || (k != 3 && k != 5)) return pl;
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    const long M = (long)N * Ho * Wo;
+    if (Ho < 1 || Wo < 1 || (H & 1) || (M & 1)) return pl;
+    const int padE = pad + (pad & 1);
+    pl.x0 = -padE;
+    pl.xoff = padE - pad;
+    pl.HB = (H + pad + padE + 1) & ~1;
+    pl.CBW = (k == 3) ? 16 : 8;  // input channels a 128-row q tile can touch
+    for (int bmt : {64, 32}) {
+        int TW, TN;
+        if (Ho * Wo >= bmt) {
+            if (bmt % Ho) continue;
+            TW = bmt / Ho;
+            TN = 1;
+            if (Wo % TW) continue;
+        } else {
+            if (bmt % (Ho * Wo)) continue;
+            TW = Wo;
+            TN = bmt / (Ho * Wo);
+        }
+        const int WB = TW + k - 1;
+        if (pl.HB > 256 || WB > 256 || TN > 256) continue;
+        const int patchBytes = (pl.HB * WB * TN * pl.CBW * 8 + 1023) & ~1023;
+        const int stageBytes = bmt * W_BN * 8 + patchBytes;
+        const int fixed = 1024 + bmt * 4 + 8 * 8;
+        int stages = (kSmemBudget - fixed) / stageBytes;
+        if (stages < 2) continue;
+        pl.BMT = bmt; pl.TW = TW; pl.TN = TN; pl.WB = WB; pl.patchBytes = patchBytes;
+        pl.stages = std::min(stages, 4);
+        pl.smem = pl.stages * stageBytes + fixed;
+        pl.ok = true;
+        break;
+    }
+    if (!pl.ok) return pl;
+    const int K = Cin * k * k;
+    pl.tq = (K + W_BQ - 1) / W_BQ;
+    pl.tn = (Cout + W_BN - 1) / W_BN;
+    pl.tiles_total = (int)((M + pl.BMT - 1) / pl.BMT);
+    const long tiles = (long)pl.tq * pl.tn;
+    long want = (2L * 148 * 2 + tiles - 1) / tiles;           // about two waves of 2 CTAs per SM
+    long cap = std::max(1L, (long)pl.tiles_total / 8);         // at least 8 steps per CTA
+    pl.splits = (int)std::max(1L, std::min(want, cap));
+    pl.tiles_per_split = (pl.tiles_total + pl.splits - 1) / pl.splits;
+    pl.splits = (pl.tiles_total + pl.tiles_per_split - 1) / pl.tiles_per_split;
+    return pl;
 }
 
 }  // namespace
 
 void conv_tma_init_attributes() {
+    FITRE_CUDA(cudaFuncSetAttribute(wgrad_tma_kernel<3, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    FITRE_CUDA(cudaFuncSetAttribute(wgrad_tma_kernel<3, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    FITRE_CUDA(cudaFuncSetAttribute(wgrad_tma_kernel<5, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    FITRE_CUDA(cudaFuncSetAttribute(wgrad_tma_kernel<5, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     FITRE_CUDA(cudaFuncSetAttribute(conv_tma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     kSmemBudget));
     FITRE_CUDA(cudaFuncSetAttribute(conv_tma_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -295,6 +512,58 @@ bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const dou
     else
         conv_tma_kernel<5><<<grid, T_THREADS, smem, ctx->stream>>>(a);
     check_launch(ctx, "conv_tma_kernel");
+    return true;
+}
+
+long conv_wgrad_tma_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    const WgradPlan pl = wgrad_plan(N, Cin, H, W, k, pad, Cout);
+    if (!pl.ok || pl.splits <= 1) return 0;
+    return (long)pl.splits * Cin * k * k * Cout;
+}
+
+// dW = sum_seg im2col(x_seg)' * d_seg (segs[i].w is the errors tensor, M x Cout).  Returns
+// false when the TMA kernel cannot take the shape; the caller then uses the gather kernel.
+bool conv_wgrad_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
+                    int H, int W, int k, int pad, int Cout, double *partials) {
+    const WgradPlan pl = wgrad_plan(N, Cin, H, W, k, pad, Cout);
+    if (!pl.ok) return false;
+    for (int s = 0; s < nseg; ++s)
+        if (((uintptr_t)segs[s].x & 15) || ((uintptr_t)segs[s].w & 15)) return false;
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    TmaWgradArgs a{};
+    a.M = (long)N * Ho * Wo;
+    a.nseg = nseg; a.N = N; a.K = Cin * k * k; a.Cout = Cout; a.Ho = Ho; a.Wo = Wo; a.pad = pad;
+    a.TW = pl.TW; a.TN = pl.TN; a.HB = pl.HB; a.WB = pl.WB; a.xoff = pl.xoff; a.x0 = pl.x0;
+    a.CBW = pl.CBW; a.stages = pl.stages; a.tilesW = Wo / pl.TW;
+    a.tiles_total = pl.tiles_total; a.tiles_per_split = pl.tiles_per_split;
+    a.patchBytes = pl.patchBytes;
+    a.out = pl.splits > 1 ? partials : dw;
+    a.err = (int *)(ctx->dscal + 4000);
+    for (int s = 0; s < nseg; ++s) {
+        cuuint64_t xd[4] = {(cuuint64_t)H, (cuuint64_t)W, (cuuint64_t)N, (cuuint64_t)Cin};
+        cuuint64_t xs[3] = {(cuuint64_t)H * 8, (cuuint64_t)H * W * 8, (cuuint64_t)H * W * N * 8};
+        cuuint32_t xb[4] = {(cuuint32_t)pl.HB, (cuuint32_t)pl.WB, (cuuint32_t)pl.TN, (cuuint32_t)pl.CBW};
+        if (!encode(&a.xmap[s], segs[s].x, 4, xd, xs, xb)) return false;
+        cuuint64_t dd[2] = {(cuuint64_t)a.M, (cuuint64_t)Cout};
+        cuuint64_t ds[1] = {(cuuint64_t)a.M * 8};
+        cuuint32_t db[2] = {16u, (cuuint32_t)W_BN};
+        if (!encode(&a.dmap[s], segs[s].w, 2, dd, ds, db, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    }
+    dim3 grid(pl.tq, pl.tn, pl.splits);
+    {
+        ProfScope prof(ctx, PROF_CONV_WGRAD, 2.0 * (double)a.M * a.K * Cout * nseg);
+        if (k == 3 && pl.BMT == 64) wgrad_tma_kernel<3, 64><<<grid, T_THREADS, pl.smem, ctx->stream>>>(a);
+        else if (k == 3) wgrad_tma_kernel<3, 32><<<grid, T_THREADS, pl.smem, ctx->stream>>>(a);
+        else if (pl.BMT == 64) wgrad_tma_kernel<5, 64><<<grid, T_THREADS, pl.smem, ctx->stream>>>(a);
+        else wgrad_tma_kernel<5, 32><<<grid, T_THREADS, pl.smem, ctx->stream>>>(a);
+        check_launch(ctx, "wgrad_tma_kernel");
+    }
+    if (pl.splits > 1) {
+        const long n = (long)a.K * Cout;
+        const int blocks = (int)std::min<long>((n + 255) / 256, 1184);
+        reduce_slabs_tma_kernel<<<blocks, 256, 0, ctx->stream>>>(partials, dw, n, pl.splits);
+        check_launch(ctx, "reduce_slabs_tma_kernel");
+    }
     return true;
 }
 

@@ -738,11 +738,13 @@ long conv_wgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) 
     const int K = Cin * k * k;
     const long tiles = (long)((K + WG_BQ - 1) / WG_BQ) * ((Cout + WG_BN - 1) / WG_BN);
     const int S = split_count(tiles, M, 512);
-    return S > 1 ? (long)S * K * Cout : 0;
+    const long gather = S > 1 ? (long)S * K * Cout : 0;
+    return std::max(gather, conv_wgrad_tma_scratch(N, Cin, H, W, k, pad, Cout));
 }
 
 void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
                 int H, int W, int k, int pad, int Cout, double *partials) {
+    if (ctx->use_tma && conv_wgrad_tma(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout, partials)) return;
     WgradArgs a{};
     for (int s = 0; s < nseg; ++s) {
         a.x[s] = segs[s].x;
