@@ -390,6 +390,7 @@ struct WgradPlan {
 WgradPlan wgrad_plan(int N, int Cin, int H, int W, int k, int pad, int Cout) {
     WgradPlan pl;
     if (!encode_fn() || (k != 3 && k != 5)) return pl;
+    if (Cin * k * k <= 64) return pl;  // a 128-row q tile would be mostly empty: gather kernel
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
     const long M = (long)N * Ho * Wo;
     if (Ho < 1 || Wo < 1 || (H & 1) || (M & 1)) return pl;

@@ -1,0 +1,81 @@
+"""Worker used by the multi-rank tests: each rank evaluates its shard of one batch and the
+per-rank results are combined by sum all-reduce (gloo + the CPU oracle, or NCCL + the CUDA
+library).  Run as a child process: python multirank_worker.py <backend> <rank> <world> <port> <out.npz>
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+for p in (ROOT, HERE):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+N_GLOBAL = 8
+
+
+def make_case(builder="vgg_small"):
+    import nets
+    import oracle_lib as O
+    from fitre_b200 import layout
+    rng = np.random.default_rng(2024)
+    model_full = getattr(nets, builder)(N_GLOBAL)
+    O.finalize(model_full)
+    c0 = model_full.convLayer[0]
+    ncls = model_full.fcLayer[model_full.lLayers - 1].out
+    x = layout.batch_to_ref(rng.standard_normal((N_GLOBAL, c0.inChannels, c0.height, c0.width)))
+    y = rng.integers(1, ncls + 1, N_GLOBAL).astype(np.float64)
+    w = layout.he_normal_params(model_full, rng)
+    v = rng.standard_normal(model_full.pSize)
+    return model_full, x, y, w, v, ncls
+
+
+def main():
+    backend, rank, world, port, out = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4], sys.argv[5]
+    builder = sys.argv[6] if len(sys.argv) > 6 else "vgg_small"
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=port, RANK=str(rank), WORLD_SIZE=str(world))
+    import torch
+    import torch.distributed as dist
+    import nets
+    import oracle_lib as O
+    from fitre_b200 import layout
+    model_full, x, y, w, v, ncls = make_case(builder)
+    c0 = model_full.convLayer[0]
+    per = N_GLOBAL // world
+    xs = layout.shard_batch(x, N_GLOBAL, c0.inChannels, c0.height, c0.width, rank, world)
+    ys = np.ascontiguousarray(y[rank * per:(rank + 1) * per])
+    model = getattr(nets, builder)(per)
+    O.finalize(model)
+    if backend == "gloo":
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+        def allreduce(buf, n, user):
+            a = np.ctypeslib.as_array(buf, shape=(n,))
+            t = torch.from_numpy(a)
+            dist.all_reduce(t)
+
+        env = O.make_env(ref_softmax=1, world=world, allreduce=allreduce)
+        st = O.gradient(model, xs, ys, w, ncls, per, env=env)
+        hv = O.hv(model, xs, w, ncls, per, st, v, env=env)
+        np.savez(out, loss=st.loss, gradient=st.gradient, hv=hv)
+    else:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank))
+        import gpu_util as G
+        from fitre_b200 import api
+        ctx = api.Context(rank)
+        ctx.comm_init_from_torch()
+        G._CTX["c"] = ctx
+        run = G.GpuRun(model, xs, ys, w, ncls, ref_softmax=1)
+        hv = run.hv(v)
+        np.savez(out, loss=run.loss, gradient=run.gradient, hv=hv)
+        torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
