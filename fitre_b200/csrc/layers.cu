@@ -78,17 +78,48 @@ __device__ __forceinline__ void block_reduce_store(double (&acc)[NS], double *ds
     }
 }
 
-template <int NS, class Op>
-__global__ void __launch_bounds__(kThreads) channel_pass_kernel(Op op, long rows, int S,
+// V consecutive doubles moved with one instruction (V = 2: 16-byte accesses)
+template <int V>
+struct Pk {
+    double v[V];
+};
+template <int V>
+__device__ __forceinline__ Pk<V> ldp(const double *p) {
+    Pk<V> r;
+    if (V == 2) {
+        const double2 t = *reinterpret_cast<const double2 *>(p);
+        r.v[0] = t.x;
+        r.v[V - 1] = t.y;
+    } else {
+        r.v[0] = *p;
+    }
+    return r;
+}
+template <int V>
+__device__ __forceinline__ void stp(double *p, const Pk<V> &a) {
+    if (V == 2)
+        *reinterpret_cast<double2 *>(p) = make_double2(a.v[0], a.v[V - 1]);
+    else
+        *p = a.v[0];
+}
+
+// Block (c, s) walks slice s of channel c.  Op::chan(c) hoists everything that depends only
+// on the channel (base pointers, 1/sigma, the finished sums); Op::run<V> handles V
+// consecutive rows.  Row indices are 32-bit (one channel of one shard is far below 2^31
+// elements), which keeps the index arithmetic off the 64-bit divider.
+template <int NS, int V, class Op>
+__global__ void __launch_bounds__(kThreads) channel_pass_kernel(Op op, unsigned rows, int S,
                                                                 double *partials) {
     const int c = blockIdx.x, s = blockIdx.y;
-    const long per = (rows + S - 1) / S;
-    const long beg = (long)s * per;
-    const long end = min(rows, beg + per);
+    unsigned per = (rows + S - 1) / S;
+    per = (per + V - 1) / V * V;
+    const unsigned beg = min(rows, (unsigned)s * per);
+    const unsigned end = min(rows, beg + per);
+    const typename Op::Chan ch = op.chan(c);
     double acc[NS > 0 ? NS : 1];
 #pragma unroll
     for (int k = 0; k < (NS > 0 ? NS : 1); ++k) acc[k] = 0.0;
-    for (long r = beg + threadIdx.x; r < end; r += kThreads) op(c, r, acc);
+    for (unsigned r = beg + V * threadIdx.x; r < end; r += V * kThreads) op.template run<V>(ch, r, acc);
     if (NS > 0) block_reduce_store<(NS > 0 ? NS : 1)>(acc, partials + ((long)c * S + s) * NS);
 }
 
@@ -106,8 +137,8 @@ int slices_for(int C, long rows) {
     long want = (148L * 8 + C - 1) / C;
     long cap = std::max(1L, rows / 2048);
     long S = std::max(1L, std::min(want, cap));
-    // scratch holds C*S*NS partials + C*NS sums, NS <= 7
-    while (S > 1 && (long)C * (S + 1) * 7 > kScratchDoubles) --S;
+    // scratch holds C*S*NS partials + C*NS sums + a parked copy of C*NS sums, NS <= 7
+    while (S > 1 && (long)C * (S + 2) * 7 > kScratchDoubles) --S;
     return (int)S;
 }
 
@@ -115,13 +146,17 @@ int slices_for(int C, long rows) {
 // channel) at `sums` (= scratch) and, when `sync`, all-reduces them over the ranks.
 template <int NS, class Op>
 double *channel_pass(fitre_context *ctx, const Op &op, int C, long rows, double *scratch,
-                     bool sync, const char *name) {
-    FITRE_REQUIRE((long)C * 2 * 7 <= kScratchDoubles, FITRE_ERR_TOO_LARGE, "too many channels");
+                     bool sync, const char *name, bool vec2) {
+    FITRE_REQUIRE((long)C * 3 * 7 <= kScratchDoubles, FITRE_ERR_TOO_LARGE, "too many channels");
+    FITRE_REQUIRE(rows < (1L << 31), FITRE_ERR_TOO_LARGE, "channel block beyond 2^31 elements");
     const int S = slices_for(C, rows);
     double *sums = scratch;
     double *partials = scratch + (long)C * (NS > 0 ? NS : 1);
     dim3 grid(C, S);
-    channel_pass_kernel<NS, Op><<<grid, kThreads, 0, ctx->stream>>>(op, rows, S, partials);
+    if (vec2 && (rows & 1) == 0)
+        channel_pass_kernel<NS, 2, Op><<<grid, kThreads, 0, ctx->stream>>>(op, (unsigned)rows, S, partials);
+    else
+        channel_pass_kernel<NS, 1, Op><<<grid, kThreads, 0, ctx->stream>>>(op, (unsigned)rows, S, partials);
     check_launch(ctx, name);
     if (NS > 0) {
         const int n = C * NS;
@@ -136,15 +171,29 @@ double *channel_pass(fitre_context *ctx, const Op &op, int C, long rows, double 
 struct SumOp {  // sum x
     const double *x;
     long rows;
-    __device__ void operator()(int c, long r, double (&a)[1]) const { a[0] += x[(long)c * rows + r]; }
+    struct Chan { const double *x; };
+    __device__ Chan chan(int c) const { return Chan{x + (long)c * rows}; }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&a)[1]) const {
+        const Pk<V> p = ldp<V>(ch.x + r);
+#pragma unroll
+        for (int e = 0; e < V; ++e) a[0] += p.v[e];
+    }
 };
 struct VarOp {  // sum (x - mean)^2, mean = sums[c] * inv_m
     const double *x, *sum;
     long rows;
     double inv_m;
-    __device__ void operator()(int c, long r, double (&a)[1]) const {
-        const double d = x[(long)c * rows + r] - sum[c] * inv_m;
-        a[0] += d * d;
+    struct Chan { const double *x; double mean; };
+    __device__ Chan chan(int c) const { return Chan{x + (long)c * rows, sum[c] * inv_m}; }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&a)[1]) const {
+        const Pk<V> p = ldp<V>(ch.x + r);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const double d = p.v[e] - ch.mean;
+            a[0] += d * d;
+        }
     }
 };
 __global__ void bn_stats_store_kernel(const double *sum, const double *ssq, double inv_m, int C,
@@ -164,14 +213,22 @@ struct NormActOp {  // bn out (optional) and activation out
     double *bn, *actout;
     long rows;
     int act, has_bn;
-    __device__ void operator()(int c, long r, double (&)[1]) const {
-        const long i = (long)c * rows + r;
-        double v = x[i];
-        if (has_bn) {
-            v = (v - mean[c]) / sqrt(var[c] + kBnEps);
-            bn[i] = v;
+    struct Chan { const double *x; double *bn, *actout; double mean, sd; };
+    __device__ Chan chan(int c) const {
+        const long b = (long)c * rows;
+        return Chan{x + b, has_bn ? bn + b : nullptr, actout + b, has_bn ? mean[c] : 0.0,
+                    has_bn ? 1.0 / sqrt(var[c] + kBnEps) : 1.0};
+    }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&)[1]) const {
+        Pk<V> p = ldp<V>(ch.x + r), o;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            if (has_bn) p.v[e] = (p.v[e] - ch.mean) * ch.sd;  // sd holds 1/sigma
+            o.v[e] = act_fwd(act, p.v[e]);
         }
-        actout[i] = act_fwd(act, v);
+        if (has_bn) stp<V>(ch.bn + r, p);
+        stp<V>(ch.actout + r, o);
     }
 };
 
@@ -225,6 +282,51 @@ __device__ __forceinline__ double pool_gather(const double *dpool_plane, const d
     return s;
 }
 
+// Pooled errors for V consecutive rows (h, h+1, same column w) of one plane.  `a` holds the
+// activations of those rows.  The 2x2/stride-2 max pool with V == 2 (both rows in one window)
+// is resolved from the two window columns directly; everything else takes the general gather.
+template <int V>
+__device__ __forceinline__ Pk<V> pool_gather_v(const double *dpool_plane, const double *act_plane,
+                                               const PoolGeom &g, int h, int w, const Pk<V> &a) {
+    Pk<V> out;
+    if (V == 2 && g.type == FITRE_MAX_POOL && g.pk == 2 && g.ps == 2 && g.pp == 0 &&
+        !(g.H & 1) && !(g.W & 1)) {
+        const Pk<V> b = ldp<V>(act_plane + (w ^ 1) * g.H + h);  // the window's other column
+        const bool first = !(w & 1);                             // is our column scanned first?
+        const double c0 = first ? a.v[0] : b.v[0], c1 = first ? a.v[V - 1] : b.v[V - 1];
+        const double c2 = first ? b.v[0] : a.v[0], c3 = first ? b.v[V - 1] : a.v[V - 1];
+        int win = 0;
+        double best = c0;
+        if (c1 > best) { best = c1; win = 1; }
+        if (c2 > best) { best = c2; win = 2; }
+        if (c3 > best) { best = c3; win = 3; }
+        const double d = dpool_plane[(w >> 1) * g.Hp + (h >> 1)];
+        const int mine = first ? 0 : 2;
+        out.v[0] = (win == mine) ? d : 0.0;
+        out.v[V - 1] = (win == mine + 1) ? d : 0.0;
+        return out;
+    }
+    if (g.type == FITRE_NO_POOL) return ldp<V>(dpool_plane + w * g.H + h);
+#pragma unroll
+    for (int e = 0; e < V; ++e) out.v[e] = pool_gather(dpool_plane, act_plane, g, h + e, w);
+    return out;
+}
+
+struct PlaneChan {   // per-channel bases shared by the pool/activation functors
+    long cbase;      // c * rows
+    long pbase;      // start of channel c in the pooled tensor
+    unsigned hw, H, pw;
+};
+__device__ __forceinline__ PlaneChan plane_chan(int c, long rows, const PoolGeom &g) {
+    PlaneChan p;
+    p.hw = (unsigned)(g.H * g.W);
+    p.H = (unsigned)g.H;
+    p.pw = (unsigned)(g.Hp * g.Wp);
+    p.cbase = (long)c * rows;
+    p.pbase = g.type == FITRE_NO_POOL ? p.cbase : (long)c * (rows / p.hw) * p.pw;
+    return p;
+}
+
 template <int NS>
 struct PoolActBwdOp {  // dxP, dxA (+ sums: dA [, dA*zhat])
     const double *dpool, *actv, *zin;
@@ -232,23 +334,26 @@ struct PoolActBwdOp {  // dxP, dxA (+ sums: dA [, dA*zhat])
     long rows;
     PoolGeom g;
     int act;
-    __device__ void operator()(int c, long r, double (&a)[NS > 0 ? NS : 1]) const {
-        const int hw = g.H * g.W;
-        const long n = r / hw;
-        const int rem = (int)(r - n * hw);
-        const int w = rem / g.H, h = rem - w * g.H;
-        const long i = (long)c * rows + r;
-        const long plane = (long)c * rows + n * hw;
-        const long pplane = g.type == FITRE_NO_POOL
-                                ? plane
-                                : ((long)c * (rows / hw) + n) * (g.Hp * g.Wp);
-        const double dP = pool_gather(dpool + pplane, actv + plane, g, h, w);
-        dxP[i] = dP;
-        const double zi = zin[i];
-        const double dA = dP * act_d1(act, zi, actv[i]);
-        dxA[i] = dA;
-        if (NS >= 1) a[0] += dA;
-        if (NS >= 2) a[1] += dA * zi;
+    typedef PlaneChan Chan;
+    __device__ Chan chan(int c) const { return plane_chan(c, rows, g); }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&a)[NS > 0 ? NS : 1]) const {
+        const unsigned n = r / ch.hw, rem = r - n * ch.hw;
+        const unsigned w = rem / ch.H, h = rem - w * ch.H;
+        const long i = ch.cbase + r;
+        const double *aplane = actv + ch.cbase + (long)n * ch.hw;
+        const double *pplane = dpool + ch.pbase + (long)n * (g.type == FITRE_NO_POOL ? ch.hw : ch.pw);
+        const Pk<V> av = ldp<V>(actv + i), zi = ldp<V>(zin + i);
+        const Pk<V> dP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av);
+        Pk<V> dA;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            dA.v[e] = dP.v[e] * act_d1(act, zi.v[e], av.v[e]);
+            if (NS >= 1) a[0] += dA.v[e];
+            if (NS >= 2) a[1] += dA.v[e] * zi.v[e];
+        }
+        stp<V>(dxP + i, dP);
+        stp<V>(dxA + i, dA);
     }
 };
 
@@ -258,24 +363,40 @@ struct BnBwdApplyOp {  // dBN = (m dA - s1 - zhat s2) / (m sigma)   (+ sum dBN)
     double *out;
     long rows;
     double m;
-    __device__ void operator()(int c, long r, double (&a)[NS > 0 ? NS : 1]) const {
-        const long i = (long)c * rows + r;
-        const double v = (dA[i] * m - sums[2 * c] - sums[2 * c + 1] * zhat[i]) /
-                         (m * sqrt(kBnEps + var[c]));
-        out[i] = v;
-        if (NS >= 1) a[0] += v;
+    struct Chan { long b; double s1, s2, den; };
+    __device__ Chan chan(int c) const {
+        return Chan{(long)c * rows, sums[2 * c], sums[2 * c + 1], 1.0 / (m * sqrt(kBnEps + var[c]))};
+    }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&a)[NS > 0 ? NS : 1]) const {
+        const long i = ch.b + r;
+        const Pk<V> d = ldp<V>(dA + i), zh = ldp<V>(zhat + i);
+        Pk<V> o;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            o.v[e] = (d.v[e] * m - ch.s1 - ch.s2 * zh.v[e]) * ch.den;  // den holds 1/(m sigma)
+            if (NS >= 1) a[0] += o.v[e];
+        }
+        stp<V>(out + i, o);
     }
 };
 
 struct RbnSumsOp {  // sum Rz, sum (z-mu) Rz, sum (z-mu)
     const double *z, *rz, *mean;
     long rows;
-    __device__ void operator()(int c, long r, double (&a)[3]) const {
-        const long i = (long)c * rows + r;
-        const double d = z[i] - mean[c], t = rz[i];
-        a[0] += t;
-        a[1] += d * t;
-        a[2] += d;
+    struct Chan { long b; double mean; };
+    __device__ Chan chan(int c) const { return Chan{(long)c * rows, mean[c]}; }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&a)[3]) const {
+        const long i = ch.b + r;
+        const Pk<V> zz = ldp<V>(z + i), t = ldp<V>(rz + i);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const double d = zz.v[e] - ch.mean;
+            a[0] += t.v[e];
+            a[1] += d * t.v[e];
+            a[2] += d;
+        }
     }
 };
 struct RNormActOp {  // R bn-out, R act-out
@@ -284,18 +405,36 @@ struct RNormActOp {  // R bn-out, R act-out
     long rows;
     double m;
     int act, has_bn;
-    __device__ void operator()(int c, long r, double (&)[1]) const {
-        const long i = (long)c * rows + r;
-        double v = rz[i];
+    struct Chan { long b; double mean, rmean, sd, coef; };
+    __device__ Chan chan(int c) const {
+        Chan ch{(long)c * rows, 0.0, 0.0, 1.0, 0.0};
         if (has_bn) {
-            const double rmean = sums[3 * c] / m;
+            ch.mean = mean[c];
+            ch.rmean = sums[3 * c] / m;
             // sum (z-mu)(Rz - mean Rz) = sum (z-mu) Rz - mean Rz * sum (z-mu)
-            const double s = sums[3 * c + 1] - rmean * sums[3 * c + 2];
-            const double ve = var[c] + kBnEps, sd = sqrt(ve);
-            v = (v - rmean) / sd - s * (z[i] - mean[c]) / (m * ve * sd);
-            rbn[i] = v;
+            const double s = sums[3 * c + 1] - ch.rmean * sums[3 * c + 2];
+            const double ve = var[c] + kBnEps;
+            const double sd = sqrt(ve);
+            ch.sd = 1.0 / sd;  // 1/sigma
+            ch.coef = s / (m * ve * sd);
         }
-        ract[i] = v * act_d1(act, zin[i], actv[i]);
+        return ch;
+    }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&)[1]) const {
+        const long i = ch.b + r;
+        Pk<V> v = ldp<V>(rz + i), o;
+        const Pk<V> zi = ldp<V>(zin + i), av = ldp<V>(actv + i);
+        if (has_bn) {
+            const Pk<V> zz = ldp<V>(z + i);
+#pragma unroll
+            for (int e = 0; e < V; ++e)
+                v.v[e] = (v.v[e] - ch.rmean) * ch.sd - ch.coef * (zz.v[e] - ch.mean);
+            stp<V>(rbn + i, v);
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) o.v[e] = v.v[e] * act_d1(act, zi.v[e], av.v[e]);
+        stp<V>(ract + i, o);
     }
 };
 
@@ -306,31 +445,42 @@ struct RPoolActBwdOp {  // RdA = h' RdP + h'' Rzin dxP   (+ sums, see conv_post_
     long rows;
     PoolGeom g;
     int act;
-    __device__ void operator()(int c, long r, double (&a)[NS > 0 ? NS : 1]) const {
-        const int hw = g.H * g.W;
-        const long n = r / hw;
-        const int rem = (int)(r - n * hw);
-        const int w = rem / g.H, h = rem - w * g.H;
-        const long i = (long)c * rows + r;
-        const long plane = (long)c * rows + n * hw;
-        const long pplane = g.type == FITRE_NO_POOL
-                                ? plane
-                                : ((long)c * (rows / hw) + n) * (g.Hp * g.Wp);
-        const double RdP = pool_gather(rdpool + pplane, actv + plane, g, h, w);
-        const double zi = zin[i], zo = actv[i];
-        const double RdA = act_d1(act, zi, zo) * RdP + act_d2(act, zi, zo) * rzin[i] * dxP[i];
-        rout[i] = RdA;
-        if (NS == 1) a[0] += RdA;
+    struct Chan { PlaneChan p; double mean; };
+    __device__ Chan chan(int c) const { return Chan{plane_chan(c, rows, g), NS == 7 ? mean[c] : 0.0}; }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&a)[NS > 0 ? NS : 1]) const {
+        const PlaneChan &pc = ch.p;
+        const unsigned n = r / pc.hw, rem = r - n * pc.hw;
+        const unsigned w = rem / pc.H, h = rem - w * pc.H;
+        const long i = pc.cbase + r;
+        const double *aplane = actv + pc.cbase + (long)n * pc.hw;
+        const double *pplane = rdpool + pc.pbase + (long)n * (g.type == FITRE_NO_POOL ? pc.hw : pc.pw);
+        const Pk<V> av = ldp<V>(actv + i), zi = ldp<V>(zin + i), rzh = ldp<V>(rzin + i);
+        const Pk<V> dp = ldp<V>(dxP + i);
+        const Pk<V> RdP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av);
+        Pk<V> RdA;
+#pragma unroll
+        for (int e = 0; e < V; ++e)
+            RdA.v[e] = act_d1(act, zi.v[e], av.v[e]) * RdP.v[e] +
+                       act_d2(act, zi.v[e], av.v[e]) * rzh.v[e] * dp.v[e];
+        stp<V>(rout + i, RdA);
+        if (NS == 1) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) a[0] += RdA.v[e];
+        }
         if (NS == 7) {
-            const double dA = dxA[i], rzh = rzin[i];
-            const double d = zconv[i] - mean[c], rzc = rzconv[i];
-            a[0] += RdA;
-            a[1] += dA * zi;
-            a[2] += dA * rzh + zi * RdA;
-            a[3] += dA;
-            a[4] += rzc;
-            a[5] += d * rzc;
-            a[6] += d;
+            const Pk<V> dA = ldp<V>(dxA + i), zc = ldp<V>(zconv + i), rzc = ldp<V>(rzconv + i);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const double d = zc.v[e] - ch.mean;
+                a[0] += RdA.v[e];
+                a[1] += dA.v[e] * zi.v[e];
+                a[2] += dA.v[e] * rzh.v[e] + zi.v[e] * RdA.v[e];
+                a[3] += dA.v[e];
+                a[4] += rzc.v[e];
+                a[5] += d * rzc.v[e];
+                a[6] += d;
+            }
         }
     }
 };
@@ -341,18 +491,28 @@ struct RBnBwdApplyOp {
     double *rout;
     long rows;
     double m;
-    __device__ void operator()(int c, long r, double (&a)[NS > 0 ? NS : 1]) const {
-        const long i = (long)c * rows + r;
+    struct Chan { long b; double s0, s1, s2, s3, den, rI; };
+    __device__ Chan chan(int c) const {
         const double *s = sums + 7 * c;
         const double ve = var[c] + kBnEps, sd = sqrt(ve);
-        const double zh = zhat[i];
-        const double rII = (rout[i] * m - s[0] - s[1] * rzhat[i] - s[2] * zh) / (m * sd);
-        const double II = dA[i] * m - s[3] - s[1] * zh;
         const double rmean = s[4] / m;
-        const double rI = -(s[5] - rmean * s[6]) / (m * m * ve * sd);
-        const double v = rII + II * rI;
-        rout[i] = v;
-        if (NS >= 1) a[0] += v;
+        return Chan{(long)c * rows, s[0], s[1], s[2], s[3], 1.0 / (m * sd),
+                    -(s[5] - rmean * s[6]) / (m * m * ve * sd)};
+    }
+    template <int V>
+    __device__ void run(const Chan &ch, unsigned r, double (&a)[NS > 0 ? NS : 1]) const {
+        const long i = ch.b + r;
+        const Pk<V> rd = ldp<V>(rout + i), d = ldp<V>(dA + i), zh = ldp<V>(zhat + i),
+                    rzh = ldp<V>(rzhat + i);
+        Pk<V> o;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const double rII = (rd.v[e] * m - ch.s0 - ch.s1 * rzh.v[e] - ch.s2 * zh.v[e]) * ch.den;
+            const double II = d.v[e] * m - ch.s3 - ch.s1 * zh.v[e];
+            o.v[e] = rII + II * ch.rI;
+            if (NS >= 1) a[0] += o.v[e];
+        }
+        stp<V>(rout + i, o);
     }
 };
 
@@ -551,6 +711,16 @@ __global__ void dots_final_kernel(const double *partials, int blocks, double *ou
 
 int grid_for(long n) { return (int)std::max<long>(1, std::min<long>((n + kThreads - 1) / kThreads, 148 * 8)); }
 
+// 16-byte accesses need every tensor of the pass on a 16-byte boundary and an even plane height
+// (so that a pair of rows never straddles a column or a plane).
+bool vec2_ok(const ConvGeom &g, int N, std::initializer_list<const void *> ptrs) {
+    if ((g.Ho & 1) || (((long)N * g.Ho * g.Wo) & 1)) return false;
+    if ((g.actOff | (g.bn ? g.bnOff : 0)) & 1) return false;
+    for (const void *p : ptrs)
+        if (p && ((uintptr_t)p & 15)) return false;
+    return true;
+}
+
 PoolGeom pool_geom(const ConvGeom &g) {
     PoolGeom p;
     p.type = g.poolType;
@@ -598,20 +768,21 @@ void conv_post_forward(fitre_context *ctx, const ConvGeom &g, int N, double *zl,
     double *bn = g.bn ? zl + g.bnOff : nullptr;
     double *mean = g.bn ? bn + g.meanOff : nullptr;
     double *var = g.bn ? bn + g.varOff : nullptr;
+    const bool v2 = vec2_ok(g, N, {zl});
     if (g.bn) {
         // two-pass batch statistics (functions/dev_batch_norm.cu:263-315)
-        double *sum = channel_pass<1>(ctx, SumOp{zl, rows}, g.Cout, rows, scratch, true, "bn_sum");
+        double *sum = channel_pass<1>(ctx, SumOp{zl, rows}, g.Cout, rows, scratch, true, "bn_sum", v2);
         double *sum_keep = scratch + kScratchDoubles - g.Cout;  // parked above the partials
         FITRE_CUDA(cudaMemcpyAsync(sum_keep, sum, sizeof(double) * g.Cout, cudaMemcpyDeviceToDevice,
                                    ctx->stream));
         double *ssq = channel_pass<1>(ctx, VarOp{zl, sum_keep, rows, 1.0 / m}, g.Cout, rows, scratch,
-                                      true, "bn_var");
+                                      true, "bn_var", v2);
         bn_stats_store_kernel<<<(g.Cout + 127) / 128, 128, 0, ctx->stream>>>(
             sum_keep, ssq, 1.0 / m, g.Cout, mean, var, var + g.Cout, var + 2 * g.Cout);
         check_launch(ctx, "bn_stats_store_kernel");
     }
     NormActOp op{zl, mean, var, bn, zl + g.actOff, rows, g.act, g.bn};
-    channel_pass<0>(ctx, op, g.Cout, rows, scratch, false, "bn_norm_act");
+    channel_pass<0>(ctx, op, g.Cout, rows, scratch, false, "bn_norm_act", v2);
     if (g.poolType != FITRE_NO_POOL) {
         const long planes = (long)g.Cout * N;
         pool_forward_kernel<<<grid_for(planes * g.Hp * g.Wp), kThreads, 0, ctx->stream>>>(
@@ -628,9 +799,10 @@ void conv_post_rop_forward(fitre_context *ctx, const ConvGeom &g, int N, const d
     const double *mean = g.bn ? bn + g.meanOff : nullptr;
     const double *var = g.bn ? bn + g.varOff : nullptr;
     double *sums = nullptr;
+    const bool v2 = vec2_ok(g, N, {zl, rzl});
     if (g.bn)
         sums = channel_pass<3>(ctx, RbnSumsOp{zl, rzl, mean, rows}, g.Cout, rows, scratch, true,
-                               "rbn_sums");
+                               "rbn_sums", v2);
     double *sums_keep = nullptr;
     if (g.bn) {
         sums_keep = scratch + kScratchDoubles - 3 * g.Cout;
@@ -639,7 +811,7 @@ void conv_post_rop_forward(fitre_context *ctx, const ConvGeom &g, int N, const d
     }
     RNormActOp op{zl, rzl, mean, var, sums_keep, g.bn ? bn : zl, zl + g.actOff,
                   g.bn ? rzl + g.bnOff : nullptr, rzl + g.actOff, rows, m, g.act, g.bn};
-    channel_pass<0>(ctx, op, g.Cout, rows, scratch, false, "rbn_norm_act");
+    channel_pass<0>(ctx, op, g.Cout, rows, scratch, false, "rbn_norm_act", v2);
     const long planes = (long)g.Cout * N;
     if (g.poolType == FITRE_MAX_POOL) {
         rop_max_pool_kernel<<<grid_for(planes * g.Hp * g.Wp), kThreads, 0, ctx->stream>>>(
@@ -659,32 +831,33 @@ const double *conv_post_backward(fitre_context *ctx, const ConvGeom &g, int N, c
     const double m = (double)rows * ctx->world;
     const double *zin = g.bn ? zl + g.bnOff : zl;
     const PoolGeom pg = pool_geom(g);
+    const bool v2 = vec2_ok(g, N, {zl, dxl, g.poolType == FITRE_NO_POOL ? delta_pool : nullptr});
     if (g.bn) {
         PoolActBwdOp<2> op{delta_pool, zl + g.actOff, zin, dxl, dxl + g.actOff, rows, pg, g.act};
-        double *sums = channel_pass<2>(ctx, op, g.Cout, rows, scratch, true, "pool_act_bwd");
+        double *sums = channel_pass<2>(ctx, op, g.Cout, rows, scratch, true, "pool_act_bwd", v2);
         double *keep = scratch + kScratchDoubles - 2 * g.Cout;
         FITRE_CUDA(cudaMemcpyAsync(keep, sums, sizeof(double) * 2 * g.Cout, cudaMemcpyDeviceToDevice,
                                    ctx->stream));
         const double *var = zl + g.bnOff + g.varOff;
         if (db) {
             BnBwdApplyOp<1> ap{dxl + g.actOff, zin, var, keep, dxl + g.bnOff, rows, m};
-            double *s = channel_pass<1>(ctx, ap, g.Cout, rows, scratch, false, "bn_bwd_apply");
+            double *s = channel_pass<1>(ctx, ap, g.Cout, rows, scratch, false, "bn_bwd_apply", v2);
             FITRE_CUDA(cudaMemcpyAsync(db, s, sizeof(double) * g.Cout, cudaMemcpyDeviceToDevice,
                                        ctx->stream));
         } else {
             BnBwdApplyOp<0> ap{dxl + g.actOff, zin, var, keep, dxl + g.bnOff, rows, m};
-            channel_pass<0>(ctx, ap, g.Cout, rows, scratch, false, "bn_bwd_apply");
+            channel_pass<0>(ctx, ap, g.Cout, rows, scratch, false, "bn_bwd_apply", v2);
         }
         return dxl + g.bnOff;
     }
     if (db) {
         PoolActBwdOp<1> op{delta_pool, zl + g.actOff, zin, dxl, dxl + g.actOff, rows, pg, g.act};
-        double *s = channel_pass<1>(ctx, op, g.Cout, rows, scratch, false, "pool_act_bwd");
+        double *s = channel_pass<1>(ctx, op, g.Cout, rows, scratch, false, "pool_act_bwd", v2);
         FITRE_CUDA(cudaMemcpyAsync(db, s, sizeof(double) * g.Cout, cudaMemcpyDeviceToDevice,
                                    ctx->stream));
     } else {
         PoolActBwdOp<0> op{delta_pool, zl + g.actOff, zin, dxl, dxl + g.actOff, rows, pg, g.act};
-        channel_pass<0>(ctx, op, g.Cout, rows, scratch, false, "pool_act_bwd");
+        channel_pass<0>(ctx, op, g.Cout, rows, scratch, false, "pool_act_bwd", v2);
     }
     return dxl + g.actOff;
 }
@@ -698,35 +871,36 @@ void conv_post_rop_backward(fitre_context *ctx, const ConvGeom &g, int N, const 
     const double *zin = g.bn ? zl + g.bnOff : zl;
     const double *rzin = g.bn ? rzl + g.bnOff : rzl;
     const double *mean = g.bn ? zl + g.bnOff + g.meanOff : nullptr;
+    const bool v2 = vec2_ok(g, N, {zl, rzl, dxl, rout, g.poolType == FITRE_NO_POOL ? rdelta_pool : nullptr});
     if (g.bn) {
         RPoolActBwdOp<7> op{rdelta_pool, zl + g.actOff, zin, rzin, dxl, dxl + g.actOff, zl, rzl,
                             mean, rout, rows, pg, g.act};
-        double *sums = channel_pass<7>(ctx, op, g.Cout, rows, scratch, true, "rop_pool_act_bwd");
+        double *sums = channel_pass<7>(ctx, op, g.Cout, rows, scratch, true, "rop_pool_act_bwd", v2);
         double *keep = scratch + kScratchDoubles - 7 * g.Cout;
         FITRE_CUDA(cudaMemcpyAsync(keep, sums, sizeof(double) * 7 * g.Cout, cudaMemcpyDeviceToDevice,
                                    ctx->stream));
         const double *var = zl + g.bnOff + g.varOff;
         if (rdb) {
             RBnBwdApplyOp<1> ap{dxl + g.actOff, zin, rzin, var, keep, rout, rows, m};
-            double *s = channel_pass<1>(ctx, ap, g.Cout, rows, scratch, false, "rbn_bwd_apply");
+            double *s = channel_pass<1>(ctx, ap, g.Cout, rows, scratch, false, "rbn_bwd_apply", v2);
             FITRE_CUDA(cudaMemcpyAsync(rdb, s, sizeof(double) * g.Cout, cudaMemcpyDeviceToDevice,
                                        ctx->stream));
         } else {
             RBnBwdApplyOp<0> ap{dxl + g.actOff, zin, rzin, var, keep, rout, rows, m};
-            channel_pass<0>(ctx, ap, g.Cout, rows, scratch, false, "rbn_bwd_apply");
+            channel_pass<0>(ctx, ap, g.Cout, rows, scratch, false, "rbn_bwd_apply", v2);
         }
         return;
     }
     if (rdb) {
         RPoolActBwdOp<1> op{rdelta_pool, zl + g.actOff, zin, rzin, dxl, dxl + g.actOff, zl, rzl,
                             mean, rout, rows, pg, g.act};
-        double *s = channel_pass<1>(ctx, op, g.Cout, rows, scratch, false, "rop_pool_act_bwd");
+        double *s = channel_pass<1>(ctx, op, g.Cout, rows, scratch, false, "rop_pool_act_bwd", v2);
         FITRE_CUDA(cudaMemcpyAsync(rdb, s, sizeof(double) * g.Cout, cudaMemcpyDeviceToDevice,
                                    ctx->stream));
     } else {
         RPoolActBwdOp<0> op{rdelta_pool, zl + g.actOff, zin, rzin, dxl, dxl + g.actOff, zl, rzl,
                             mean, rout, rows, pg, g.act};
-        channel_pass<0>(ctx, op, g.Cout, rows, scratch, false, "rop_pool_act_bwd");
+        channel_pass<0>(ctx, op, g.Cout, rows, scratch, false, "rop_pool_act_bwd", v2);
     }
 }
 
