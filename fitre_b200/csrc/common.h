@@ -109,12 +109,15 @@ struct ConvSeg {            // one (input tensor, weight matrix) pair of a K-/M-
     const double *w;        // K x Cout column-major
 };
 // Y[M x Cout] (+= bias[c]) = sum_seg im2col(x_seg) * w_seg      (fprop and its R-op form)
+// `split` = conv_fprop_scratch() doubles of scratch for split-K slabs (may be NULL).
+long conv_fprop_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
 void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
-                int N, int Cin, int H, int W, int k, int pad, int Cout);
+                int N, int Cin, int H, int W, int k, int pad, int Cout, double *split);
 // dX[(N H W) x Cin] = sum_seg im2colT(delta_seg) * perm(w_seg)  (dgrad and its R-op form);
 // `wscratch` receives the permuted weights (nseg * K * Cout doubles).
+long conv_dgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
 void conv_dgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dx, int N, int Cin,
-                int H, int W, int k, int pad, int Cout, double *wscratch);
+                int H, int W, int k, int pad, int Cout, double *wscratch, double *split);
 // dW[K x Cout] = sum_seg im2col(x_seg)' * delta_seg ; segs[i].w is delta_seg (M x Cout).
 // `partials` needs conv_wgrad_scratch() doubles.
 long conv_wgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
@@ -135,8 +138,10 @@ void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int 
 void gemm_init_attributes();
 // conv_tma.cu
 void conv_tma_init_attributes();
+long conv_fprop_tma_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
 bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias,
-                    double *y, int N, int Cin, int H, int W, int k, int pad, int Cout);
+                    double *y, int N, int Cin, int H, int W, int k, int pad, int Cout,
+                    double *split_scratch);
 long conv_wgrad_tma_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
 bool conv_wgrad_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
                     int H, int W, int k, int pad, int Cout, double *partials);

@@ -36,6 +36,7 @@ struct alignas(64) TmaConvArgs {
     long M;
     int nseg, N, Cout, Ho, Wo, pad, TW, TN, HB, WB, xoff, x0, nchunks, stages, tilesW;
     int patchBytes;
+    int iters_per_split;  // K-chunk iterations per blockIdx.z slice (split-K: slabs in y)
 };
 
 __device__ __forceinline__ void dmma884(double &c0, double &c1, double a, double b) {
@@ -129,10 +130,13 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
         grow[mi] = ok ? ((long)(n0 + nl) * p.Wo + (w0 + wl)) * p.Ho + ho : -1;
     }
 
-    const int iters = p.nseg * p.nchunks;
+    // split-K: slice blockIdx.z owns iterations [it0, it0 + iters) of the flattened
+    // (segment, K-chunk) sequence and writes its own output slab
+    const int it0 = blockIdx.z * p.iters_per_split;
+    const int iters = max(0, min(p.nseg * p.nchunks - it0, p.iters_per_split));
     const uint32_t txBytes = (uint32_t)(p.HB * p.WB * p.TN * T_CB * 8 + KCH * T_BN * 8);
     auto issue = [&](int it) {
-        const int seg = it / p.nchunks, ch = it - seg * p.nchunks;
+        const int seg = (it0 + it) / p.nchunks, ch = (it0 + it) - seg * p.nchunks;
         const int s = it % p.stages;
         const uint32_t bar = smem_u32(bars + s);
         unsigned char *dst = sm + (size_t)s * stageBytes;
@@ -182,6 +186,7 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
         }
     }
 
+    double *y = p.y + (long)blockIdx.z * p.M * p.Cout;
 #pragma unroll
     for (int ni = 0; ni < 4; ++ni)
 #pragma unroll
@@ -191,8 +196,21 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
             const double bv = p.bias ? p.bias[col] : 0.0;
 #pragma unroll
             for (int mi = 0; mi < 4; ++mi)
-                if (grow[mi] >= 0) p.y[(long)col * p.M + grow[mi]] = acc[mi][ni][e] + bv;
+                if (grow[mi] >= 0) y[(long)col * p.M + grow[mi]] = acc[mi][ni][e] + bv;
         }
+}
+
+// y[c][m] = sum over split-K slabs (fixed order) + bias[c]
+__global__ void reduce_out_slabs_kernel(const double *slabs, double *y, long M, int Cout, int SK,
+                                        const double *bias) {
+    const long n = M * Cout;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n;
+         i += (long)gridDim.x * blockDim.x) {
+        double s = 0.0;
+        for (int k = 0; k < SK; ++k) s += slabs[(long)k * n + i];
+        if (bias) s += bias[i / M];
+        y[i] = s;
+    }
 }
 
 
@@ -451,10 +469,33 @@ void conv_tma_init_attributes() {
                                     kSmemBudget));
 }
 
+namespace {
+// Split-K factor: small grids (late layers with few output positions) are cut along K so that
+// about 3.5 waves of CTAs exist; each slice keeps at least 8 K-chunks.
+int fprop_split(int N, int Cin, int H, int W, int k, int pad, int Cout, int nseg) {
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    const long tiles = (((long)N * Ho * Wo + T_BM - 1) / T_BM) * ((Cout + T_BN - 1) / T_BN);
+    const int iters = nseg * ((Cin + T_CB - 1) / T_CB);
+    if (tiles >= 900) return 1;
+    long sk = (1000 + tiles - 1) / tiles;
+    sk = std::min<long>(sk, iters / 8);
+    return (int)std::max<long>(1, std::min<long>(sk, 16));
+}
+}  // namespace
+
+long conv_fprop_tma_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    const int sk = std::max(fprop_split(N, Cin, H, W, k, pad, Cout, 1),
+                            fprop_split(N, Cin, H, W, k, pad, Cout, 2));
+    return sk > 1 ? (long)sk * N * Ho * Wo * Cout : 0;
+}
+
 // Returns false when the shape or the alignment is outside what the TMA kernel handles; the
-// caller then uses the gather kernel.
+// caller then uses the gather kernel.  `split_scratch` (conv_fprop_tma_scratch doubles, may be
+// NULL) enables split-K.
 bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias,
-                    double *y, int N, int Cin, int H, int W, int k, int pad, int Cout) {
+                    double *y, int N, int Cin, int H, int W, int k, int pad, int Cout,
+                    double *split_scratch) {
     if (!encode_fn()) return false;
     if (k != 3 && k != 5) return false;
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
@@ -505,7 +546,15 @@ bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const dou
         if (!encode(&a.wmap[s], segs[s].w, 2, wd, wsb, wb)) return false;
     }
     const int tilesN = (N + TN - 1) / TN;
-    dim3 grid((unsigned)(a.tilesW * tilesN), (unsigned)((Cout + T_BN - 1) / T_BN));
+    int SK = split_scratch ? fprop_split(N, Cin, H, W, k, pad, Cout, nseg) : 1;
+    const int iters = nseg * a.nchunks;
+    a.iters_per_split = (iters + SK - 1) / SK;
+    SK = (iters + a.iters_per_split - 1) / a.iters_per_split;
+    if (SK > 1) {
+        a.y = split_scratch;
+        a.bias = nullptr;
+    }
+    dim3 grid((unsigned)(a.tilesW * tilesN), (unsigned)((Cout + T_BN - 1) / T_BN), (unsigned)SK);
     const int smem = a.stages * stageBytes + fixed;
     ProfScope prof(ctx, PROF_CONV_IGEMM, 2.0 * (double)a.M * K * Cout * nseg);
     if (k == 3)
@@ -513,6 +562,12 @@ bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const dou
     else
         conv_tma_kernel<5><<<grid, T_THREADS, smem, ctx->stream>>>(a);
     check_launch(ctx, "conv_tma_kernel");
+    if (SK > 1) {
+        const long n = a.M * Cout;
+        const int blocks = (int)std::min<long>((n + 255) / 256, 148 * 8);
+        reduce_out_slabs_kernel<<<blocks, 256, 0, ctx->stream>>>(split_scratch, y, a.M, Cout, SK, bias);
+        check_launch(ctx, "reduce_out_slabs_kernel");
+    }
     return true;
 }
 

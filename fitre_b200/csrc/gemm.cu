@@ -687,9 +687,18 @@ int split_count(long tiles, long reduce_len, long min_len) {
 
 }  // namespace
 
+long conv_fprop_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    return conv_fprop_tma_scratch(N, Cin, H, W, k, pad, Cout);
+}
+long conv_dgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    // the data gradient is a convolution of the errors: Cout input channels, Cin outputs
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    return conv_fprop_tma_scratch(N, Cout, Ho, Wo, k, k - 1 - pad, Cin);
+}
+
 void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
-                int N, int Cin, int H, int W, int k, int pad, int Cout) {
-    if (ctx->use_tma && conv_fprop_tma(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout)) return;
+                int N, int Cin, int H, int W, int k, int pad, int Cout, double *split) {
+    if (ctx->use_tma && conv_fprop_tma(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout, split)) return;
     ConvArgs a{};
     for (int s = 0; s < nseg; ++s) {
         a.x[s] = segs[s].x;
@@ -716,7 +725,7 @@ void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double 
 }
 
 void conv_dgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dx, int N, int Cin,
-                int H, int W, int k, int pad, int Cout, double *wscratch) {
+                int H, int W, int k, int pad, int Cout, double *wscratch, double *split) {
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
     const long wsz = (long)Cin * Cout * k * k;
     ConvSeg t[2];
@@ -729,7 +738,7 @@ void conv_dgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dx, i
         t[s].w = wd;
     }
     // a convolution of the errors ([Cout][N][Wo][Ho]) with flipped taps and pad k-1-pad
-    conv_fprop(ctx, nseg, t, nullptr, dx, N, Cout, Ho, Wo, k, k - 1 - pad, Cin);
+    conv_fprop(ctx, nseg, t, nullptr, dx, N, Cout, Ho, Wo, k, k - 1 - pad, Cin, split);
 }
 
 long conv_wgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {

@@ -42,6 +42,18 @@ long max_weight_elems(const CNN_MODEL *m) {
     }
     return v;
 }
+long max_split_scratch(const CNN_MODEL *m) {
+    long v = 0;
+    for (int l = 0; l < m->cLayers; ++l) {
+        const CONV_LAYER &c = m->convLayer[l];
+        v = std::max(v, conv_fprop_scratch(m->batchSize, c.inChannels, c.height, c.width, c.kSize,
+                                           c.padding, c.outChannels));
+        if (l > 0)
+            v = std::max(v, conv_dgrad_scratch(m->batchSize, c.inChannels, c.height, c.width,
+                                               c.kSize, c.padding, c.outChannels));
+    }
+    return v;
+}
 long max_fc_elems(const CNN_MODEL *m) {
     long v = 0;
     for (int l = 0; l < m->lLayers; ++l)
@@ -56,16 +68,18 @@ const double *layer_input(const CNN_MODEL *m, const DEVICE_DATASET *data, const 
 
 }  // namespace
 
-long forward_scratch(const CNN_MODEL *m) { return bn_scratch(0) + align32(last_pool_elems(m)); }
+long forward_scratch(const CNN_MODEL *m) {
+    return bn_scratch(0) + align32(last_pool_elems(m)) + align32(max_split_scratch(m));
+}
 long rop_forward_scratch(const CNN_MODEL *m) { return forward_scratch(m); }
 long backward_scratch(const CNN_MODEL *m) {
     return bn_scratch(0) + align32(last_pool_elems(m)) + align32(max_wgrad_scratch(m)) +
-           align32(max_weight_elems(m));
+           align32(max_weight_elems(m)) + align32(max_split_scratch(m));
 }
 long rop_backward_scratch(const CNN_MODEL *m) {
     return bn_scratch(0) + align32(last_pool_elems(m)) + align32(max_wgrad_scratch(m)) +
            2 * align32(max_weight_elems(m)) + align32(max_conv_volume(m)) +
-           2 * align32(max_fc_elems(m));
+           2 * align32(max_fc_elems(m)) + align32(max_split_scratch(m));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -75,12 +89,13 @@ double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET 
     const double *weights = data->weights;
     double *bnws = scratch;
     double *tmp = scratch + bn_scratch(0);
+    double *split = tmp + align32(last_pool_elems(m));
     for (int l = 0; l < m->cLayers; ++l) {
         const ConvGeom g = conv_geom(m, l);
         double *zl = z + g.zoff;
         ConvSeg seg{layer_input(m, data, z, l), weights + m->wOffsets[l]};
         conv_fprop(ctx, 1, &seg, m->bias ? weights + m->bOffsets[l] : nullptr, zl, n, g.Cin, g.H,
-                   g.W, g.k, g.pad, g.Cout);
+                   g.W, g.k, g.pad, g.Cout, split);
         conv_post_forward(ctx, g, n, zl, bnws);
     }
     const ConvGeom lg = conv_geom(m, m->cLayers - 1);
@@ -118,6 +133,7 @@ void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *
     double *tmp = bnws + bn_scratch(0);
     double *wg = tmp + align32(last_pool_elems(m));
     double *wperm = wg + align32(max_wgrad_scratch(m));
+    double *split = wperm + align32(max_weight_elems(m));
     const ConvGeom lg = conv_geom(m, cL - 1);
 
     for (int f = lL - 1; f >= 0; --f) {  // functions/cnn_backward.cu:111-280
@@ -145,7 +161,7 @@ void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *
         conv_wgrad(ctx, 1, &wseg, gradient + m->wOffsets[c], n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wg);
         if (c != 0) {
             ConvSeg dseg{dconv, weights + m->wOffsets[c]};
-            conv_dgrad(ctx, 1, &dseg, delta_new, n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wperm);
+            conv_dgrad(ctx, 1, &dseg, delta_new, n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wperm, split);
             std::swap(delta, delta_new);
         }
     }
@@ -157,6 +173,7 @@ void cnn_rop_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASE
     const double *weights = data->weights;
     double *bnws = scratch;
     double *tmp = scratch + bn_scratch(0);
+    double *split = tmp + align32(last_pool_elems(m));
     for (int l = 0; l < m->cLayers; ++l) {
         const ConvGeom g = conv_geom(m, l);
         double *rzl = rz + g.zoff;
@@ -170,7 +187,7 @@ void cnn_rop_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASE
             nseg = 2;
         }
         conv_fprop(ctx, nseg, segs, m->bias ? vector + m->bOffsets[l] : nullptr, rzl, n, g.Cin, g.H,
-                   g.W, g.k, g.pad, g.Cout);
+                   g.W, g.k, g.pad, g.Cout, split);
         conv_post_rop_forward(ctx, g, n, z + g.zoff, rzl, bnws);
     }
     const ConvGeom lg = conv_geom(m, m->cLayers - 1);
@@ -206,6 +223,7 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
     double *rout = wperm + 2 * align32(max_weight_elems(m));
     double *t1 = rout + align32(max_conv_volume(m));
     double *t2 = t1 + align32(max_fc_elems(m));
+    double *split = t2 + align32(max_fc_elems(m));
     const ConvGeom lg = conv_geom(m, cL - 1);
 
     for (int f = lL - 1; f >= 0; --f) {  // functions/cnn_hv_backward.cu:153-395
@@ -257,7 +275,7 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
         if (c != 0) {  // Rdelta <- dgrad(Rdelta, W) + dgrad(delta, V)  (:854-898)
             ConvSeg ds[2] = {ConvSeg{rout, weights + m->wOffsets[c]},
                              ConvSeg{dprev, vector + m->wOffsets[c]}};
-            conv_dgrad(ctx, 2, ds, rError, n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wperm);
+            conv_dgrad(ctx, 2, ds, rError, n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wperm, split);
         }
     }
 }
