@@ -398,6 +398,28 @@ bool encode(CUtensorMap *map, const void *base, int rank, const cuuint64_t *dims
     return r == CUDA_SUCCESS;
 }
 
+// Picks the split count that minimises a simple time model: waves of 296 CTAs (2 per SM) times
+// the steps each CTA runs, plus the slab write/read traffic a split adds.
+int best_split(long tiles, int steps, int max_split, int min_steps, double step_us, double slab_bytes) {
+    int best = 1;
+    double best_t = 1e300;
+    for (int s = 1; s <= max_split; ++s) {
+        const int per = (steps + s - 1) / s;
+        if (s > 1 && per < min_steps) break;
+        const long ctas = tiles * s;
+        const long waves = (ctas + 295) / 296;
+        // a last wave that fills less than half of the slots runs with one CTA per SM, i.e. faster
+        const double tail = (ctas - (waves - 1) * 296 <= 148) ? 0.55 : 1.0;
+        double t = ((waves - 1) + tail) * per * step_us;
+        if (s > 1) t += (s + 2) * slab_bytes / 5.0e6;  // bytes / (5 TB/s) in microseconds
+        if (t < best_t * 0.98) {
+            best_t = t;
+            best = s;
+        }
+    }
+    return best;
+}
+
 // Tiling plan of the TMA weight-gradient kernel; ok == false when shape/alignment rule it out.
 struct WgradPlan {
     bool ok = false;
@@ -448,9 +470,8 @@ WgradPlan wgrad_plan(int N, int Cin, int H, int W, int k, int pad, int Cout) {
     pl.tn = (Cout + W_BN - 1) / W_BN;
     pl.tiles_total = (int)((M + pl.BMT - 1) / pl.BMT);
     const long tiles = (long)pl.tq * pl.tn;
-    long want = (2L * 148 * 2 + tiles - 1) / tiles;           // about two waves of 2 CTAs per SM
-    long cap = std::max(1L, (long)pl.tiles_total / 8);         // at least 8 steps per CTA
-    pl.splits = (int)std::max(1L, std::min(want, cap));
+    const double step_us = 8.3 * pl.BMT / 64.0;  // one BMT x 128 x 64 step with two CTAs per SM
+    pl.splits = best_split(tiles, pl.tiles_total, 256, 8, step_us, (double)K * Cout * 8);
     pl.tiles_per_split = (pl.tiles_total + pl.splits - 1) / pl.splits;
     pl.splits = (pl.tiles_total + pl.tiles_per_split - 1) / pl.tiles_per_split;
     return pl;
@@ -474,12 +495,11 @@ namespace {
 // about 3.5 waves of CTAs exist; each slice keeps at least 8 K-chunks.
 int fprop_split(int N, int Cin, int H, int W, int k, int pad, int Cout, int nseg) {
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
-    const long tiles = (((long)N * Ho * Wo + T_BM - 1) / T_BM) * ((Cout + T_BN - 1) / T_BN);
+    const long M = (long)N * Ho * Wo;
+    const long tiles = ((M + T_BM - 1) / T_BM) * ((Cout + T_BN - 1) / T_BN);
     const int iters = nseg * ((Cin + T_CB - 1) / T_CB);
-    if (tiles >= 900) return 1;
-    long sk = (1000 + tiles - 1) / tiles;
-    sk = std::min<long>(sk, iters / 8);
-    return (int)std::max<long>(1, std::min<long>(sk, 16));
+    const double step_us = 4.7 * (k * k) / 9.0;  // one 128x64x(4 k^2) chunk with two CTAs per SM
+    return best_split(tiles, iters, 16, 8, step_us, (double)M * Cout * 8);
 }
 }  // namespace
 
