@@ -295,13 +295,17 @@ def run_ours(args):
                    "parallelism": "dp%d" % world, "activation": "swish", "batch_norm": True,
                    "l2": "inputs larger than L2 (z/dx/rz are 1.85 GiB each per GPU)",
                    "algorithmic_mflop_per_image": {"gradient": gpi / 1e6, "hv": hpi / 1e6}},
-        "roofline": {"bound": "tensor", "kernel": "conv_fprop_kernel (implicit-GEMM fprop/dgrad, fp64 DMMA)",
+        "roofline": {"bound": "tensor", "kernel": "conv_tma_kernel (TMA-fed implicit-GEMM fprop/dgrad, fp64 DMMA; gather kernel for layer 0)",
                      "achieved": achieved, "peak": dgemm_tflops, "unit": "TFLOP/s",
                      "frac": (achieved / dgemm_tflops) if achieved else None,
                      "peak_source": "cuBLAS DGEMM 8192^3 measured in this run (MEASURED_PEAKS.json has no fp64 figure)",
                      "launches": k_n, "avg_launch_ms": k_ms / max(k_n, 1),
                      "share_of_step": k_ms / ms,
-                     "traffic": None,
+                     # dram__bytes_read+write of the layer-3 forward launch, ncu capture at 256
+                     # images scaled by 2 (profiles/conv_tma_kernel_vgg11bn_n256.md); its
+                     # algorithmic bytes (input + weights + output) are 138.9 MB
+                     "traffic": 116.8e6 if n == PER_GPU_BATCH else None,
+                     "traffic_launch": "layer 3 forward (M 32768, K 2304, Cout 256)",
                      "wgrad_kernel": {"achieved": (w_flops / (w_ms * 1e-3)) / 1e12 if w_ms > 0 else None,
                                       "launches": w_n, "share_of_step": w_ms / ms}},
         "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d,
