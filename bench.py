@@ -36,7 +36,8 @@ import numpy as np  # noqa: E402
 PER_GPU_BATCH = 512
 WORKLOAD = "vgg11bn_32x32_fp64_gradient+hv"
 # algorithmic flops per image (2*M*K*Cout products only): gradient 913.1 MF + Hv 1819.1 MF
-CPU_SAMPLE_IMAGES = 64
+CPU_SAMPLE_IMAGES = 256      # cpu_baseline leg of the default run: one pass, ~15 s on 16 cores
+REF_SAMPLE_IMAGES = 64       # --impl reference: per timed step
 
 
 def build_model(n):
@@ -150,10 +151,10 @@ def run_reference(args):
     cores = os.cpu_count() or 1
     rates = []
     for i in range(args.warmup + args.steps):
-        r, dt = cpu_oracle_rate(CPU_SAMPLE_IMAGES)
+        r, dt = cpu_oracle_rate(REF_SAMPLE_IMAGES)
         if i >= args.warmup:
             rates.append((r, dt))
-    value = CPU_SAMPLE_IMAGES * len(rates) / sum(dt for _, dt in rates)
+    value = REF_SAMPLE_IMAGES * len(rates) / sum(dt for _, dt in rates)
     line = {
         "impl": "reference", "metric": "gradient+Hv images/sec", "value": value, "unit": "images/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -162,9 +163,9 @@ def run_reference(args):
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "per_gpu_batch": PER_GPU_BATCH,
                    "note": "CPU restatement of the reference path (oracle/, C + OpenMP); each step "
-                           "is a %d-image sample of the workload" % CPU_SAMPLE_IMAGES},
+                           "is a %d-image sample of the workload" % REF_SAMPLE_IMAGES},
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port",
-                         "sample": "%d images of the VGG-11-BN fp64 gradient+Hv step" % CPU_SAMPLE_IMAGES},
+                         "sample": "%d images of the VGG-11-BN fp64 gradient+Hv step" % REF_SAMPLE_IMAGES},
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -325,12 +326,110 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_extra(args):
+    """Secondary workloads (the other configurations of the path): one JSON line each, device
+    timing only.  alexnet: gradient+Hv, AlexNet-BN, 1024 images over the ranks; lenet: gradient,
+    Hv and 10 Steihaug-CG iterations at 256 images; kfac: VGG-11-BN KFAC factor step (gradient,
+    sampled-label backward, A and G factors), 256 images per GPU."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    import nets
+    from fitre_b200 import _lib, api
+    from fitre_b200 import _structs as S
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = api.Context(local)
+    if world > 1:
+        ctx.comm_init_from_torch()
+    wl = args.workload
+    n = {"alexnet": 1024 // world, "lenet": 256, "kfac": 256}[wl]
+    model = {"alexnet": nets.alexnet, "lenet": nets.lenet, "kfac": nets.vgg11}[wl](n)
+    api.finalize(model)
+    x, y, w, v = synth(model, n, 2234 + rank)
+    _, _, w, v = synth(model, n, 2234)
+    f64 = dict(dtype=torch.float64, device="cuda")
+    X, Y, W, V = (torch.tensor(a, **f64) for a in (x, y, w, v))
+    data = api.make_dataset(W, X, Y, 10)
+    ws = api.Workspace(model, 10)
+    extra = {}
+    if wl == "kfac":
+        info = api.computeKFACStorageIndices(model)
+        need = _lib.load().fitre_kfac_mem_required(C.byref(model))
+        kscr = torch.zeros(max(need, ws.dev.numel()), **f64)
+        A = torch.zeros(info.OmegaZSize, **f64)
+        G = torch.zeros(info.LambdaGSize, **f64)
+        U = torch.rand(n, **f64)
+        tgt = torch.zeros(n, **f64)
+        md = model.maxDeltaSize + 32
+        e1b, e2b = torch.zeros(md, **f64), torch.zeros(md, **f64)
+        dgrad, ddx = torch.zeros(model.pSize, **f64), torch.zeros(model.zSize, **f64)
+
+    def step():
+        api.computeCNNGradient(ctx, model, data, ws.scratch, ws.z, ws.dx, ws.probs, ws.errors,
+                               ws.gradient, 0, n, 0.0)
+        if wl == "alexnet":
+            api.cnnHv(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, V, ws.hv, 0, n, ws.dev)
+        elif wl == "lenet":
+            api.cnnHv(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, V, ws.hv, 0, n, ws.dev)
+            prm = S.CG_PARAMS()
+            prm.delta, prm.tolerance, prm.maxIterations, prm.weightDecay = 1e3, 1e-30, 10, 1.0
+            api.cgSteihaug(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, ws.gradient, ws.hv,
+                           n, ws.dev, prm)
+            extra["cg_iterations"], extra["cg_hv_calls"] = prm.iterations, prm.hvCalls
+        else:
+            api.computeDistributionErrors(ctx, ws.probs, U, tgt, e1b, n, 10)
+            api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
+            api.computeOmegaZ(ctx, model, data, ws.z, n, A, info, kscr)
+            api.computeLambdaDelta(ctx, model, ddx, n, G, info, kscr)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    l0 = ctx.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], **f64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.destroy_process_group()
+    if rank == 0:
+        names = {"alexnet": "alexnetbn_32x32_fp64_gradient+hv",
+                 "lenet": "lenet_32x32_fp64_gradient+hv+cg10",
+                 "kfac": "vgg11bn_32x32_fp64_kfac_factor_step"}
+        print(json.dumps({
+            "metric": "images/sec", "value": world * n * args.steps / (ms * 1e-3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if wl == "alexnet" else "weak", "dtype": "f64", "data": "synthetic",
+            "config": dict({"workload": names[wl], "per_gpu_batch": n}, **extra),
+            "gpu_launches": ctx.launches - l0}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="vgg11", choices=["vgg11", "alexnet", "lenet", "kfac"],
+                    help="vgg11 = the benchmark (default); the others print a device-timed line "
+                         "for the path's other configurations")
     ap.add_argument("--per-gpu-batch", type=int, default=PER_GPU_BATCH,
                     help="images per GPU (default 512, the benchmark shape; smaller values are "
                          "for profiler captures only)")
@@ -339,6 +438,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "vgg11":
+        run_extra(args)
     else:
         run_ours(args)
 

@@ -23,7 +23,7 @@ SYMBOLS = [
     "fitre_cnn_forward", "fitre_cnn_backward", "fitre_compute_cnn_gradient",
     "fitre_cnn_rop_forward", "fitre_cnn_rop_backward", "fitre_cnn_hv",
     "fitre_compute_quadratic_model", "fitre_cg_steihaug",
-    "fitre_kfac_storage_indices", "fitre_kfac_mem_required", "fitre_kfac_omega_z",
+    "fitre_compute_distribution_errors", "fitre_kfac_storage_indices", "fitre_kfac_mem_required", "fitre_kfac_omega_z",
     "fitre_kfac_lambda_delta", "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host",
 ]
 
@@ -79,6 +79,7 @@ def load():
     sig("fitre_compute_quadratic_model", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, d, i, i, d,
         vp, vp, vp, dbl_p)
     sig("fitre_cg_steihaug", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, i, vp, C.POINTER(S.CG_PARAMS))
+    sig("fitre_compute_distribution_errors", i, vp, vp, vp, vp, vp, i, i)
     sig("fitre_kfac_storage_indices", i, MP, C.POINTER(S.KFAC_INFO))
     sig("fitre_kfac_omega_z", i, vp, MP, DP, vp, i, vp, C.POINTER(S.KFAC_INFO), vp)
     sig("fitre_kfac_lambda_delta", i, vp, MP, vp, i, vp, C.POINTER(S.KFAC_INFO), vp)

@@ -225,6 +225,13 @@ def cgSteihaug(ctx, model, data, z, probs, lossFuncErrors, dx, gradient, p, curB
     return params
 
 
+def computeDistributionErrors(ctx, probs, uniforms, distTarget, distError, rows, num_classes):
+    """functions/softmax_loss.cu:104-136 with injected uniforms."""
+    ctx.check(ctx.lib.fitre_compute_distribution_errors(ctx.h, _ptr(probs), _ptr(uniforms),
+                                                        _ptr(distTarget), _ptr(distError), rows,
+                                                        num_classes))
+
+
 def computeKFACStorageIndices(model):
     info = S.KFAC_INFO()
     rc = _lib.load().fitre_kfac_storage_indices(C.byref(model), C.byref(info))

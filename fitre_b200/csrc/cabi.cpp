@@ -114,6 +114,9 @@ int fitre_context_destroy(fitre_context *ctx) {
     if (ctx->dscal) cudaFree(ctx->dscal);
     if (ctx->host_ws) cudaFree(ctx->host_ws);
     if (ctx->host_pinned) cudaFreeHost(ctx->host_pinned);
+    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+    if (ctx->ev_up) cudaEventDestroy(ctx->ev_up);
+    if (ctx->ev_down) cudaEventDestroy(ctx->ev_down);
     for (auto &r : ctx->prof) {
         cudaEventDestroy(r.beg);
         cudaEventDestroy(r.end);
@@ -428,11 +431,20 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         double *x = ctx->host_ws, *y = x + X, *w = y + Y, *v = w + P, *g = v + P, *hv = g + P;
         double *z = hv + P, *dx = z + Z, *probs = dx + Z, *errs = probs + PR, *ws = errs + PR;
         cudaStream_t st = ctx->stream;
+        if (!ctx->copy_stream) {
+            FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+            FITRE_CUDA(cudaEventCreateWithFlags(&ctx->ev_up, cudaEventDisableTiming));
+            FITRE_CUDA(cudaEventCreateWithFlags(&ctx->ev_down, cudaEventDisableTiming));
+        }
+        cudaStream_t cs = ctx->copy_stream;
+        // the direction vector is not needed before the Hessian-vector product: its upload runs
+        // on the copy stream underneath the gradient
+        FITRE_CUDA(cudaMemcpyAsync(v, vector_host, sizeof(double) * m->pSize, cudaMemcpyHostToDevice, cs));
+        FITRE_CUDA(cudaEventRecord(ctx->ev_up, cs));
         FITRE_CUDA(cudaMemcpyAsync(x, batch_host, sizeof(double) * (long)n * c0.inChannels * c0.height * c0.width,
                                    cudaMemcpyHostToDevice, st));
         FITRE_CUDA(cudaMemcpyAsync(y, labels_host, sizeof(double) * n, cudaMemcpyHostToDevice, st));
         FITRE_CUDA(cudaMemcpyAsync(w, weights_host, sizeof(double) * m->pSize, cudaMemcpyHostToDevice, st));
-        FITRE_CUDA(cudaMemcpyAsync(v, vector_host, sizeof(double) * m->pSize, cudaMemcpyHostToDevice, st));
         DEVICE_DATASET data;
         std::memset(&data, 0, sizeof(data));
         data.weights = w;
@@ -446,11 +458,16 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         int rc = fitre_compute_cnn_gradient(ctx, m, &data, &sa, z, dx, probs, errs, g, 0, n,
                                             weightDecay, &loss);
         FITRE_REQUIRE(rc == FITRE_OK, rc, ctx->err);
+        // the gradient call returned after a stream sync (loss read-back): g is complete and
+        // travels back on the copy stream while the Hessian-vector product runs
+        FITRE_CUDA(cudaMemcpyAsync(gradient_host, g, sizeof(double) * m->pSize, cudaMemcpyDeviceToHost, cs));
+        FITRE_CUDA(cudaEventRecord(ctx->ev_down, cs));
+        FITRE_CUDA(cudaStreamWaitEvent(st, ctx->ev_up, 0));
         rc = fitre_cnn_hv(ctx, m, &data, z, probs, errs, dx, v, hv, 0, n, ws, nullptr, weightDecay);
         FITRE_REQUIRE(rc == FITRE_OK, rc, ctx->err);
-        FITRE_CUDA(cudaMemcpyAsync(gradient_host, g, sizeof(double) * m->pSize, cudaMemcpyDeviceToHost, st));
         FITRE_CUDA(cudaMemcpyAsync(hv_host, hv, sizeof(double) * m->pSize, cudaMemcpyDeviceToHost, st));
         FITRE_CUDA(cudaStreamSynchronize(st));
+        FITRE_CUDA(cudaEventSynchronize(ctx->ev_down));
         if (loss_host) *loss_host = loss;
     });
 }

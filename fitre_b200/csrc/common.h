@@ -57,6 +57,8 @@ struct fitre_context {
     size_t host_ws_doubles = 0;
     double *host_pinned = nullptr;
     size_t host_pinned_doubles = 0;
+    cudaStream_t copy_stream = nullptr;   // second stream of the host-buffer entry point
+    cudaEvent_t ev_up = nullptr, ev_down = nullptr;
     // optional per-kernel timing (CUDA events on the launch stream), see fitre_profile_*
     bool prof_on = false;
     struct ProfRec { cudaEvent_t beg, end; int kind; double flops; };
@@ -179,6 +181,8 @@ void softmax_loss(fitre_context *ctx, const double *logits, const double *labels
                   int classes, double *probs, double *errors, double inv_n_global);
 void softmax_rop_error(fitre_context *ctx, const double *rz, const double *probs, int N,
                        int classes, double *rerr, double inv_n_global);
+void distribution_errors(fitre_context *ctx, const double *probs, const double *uniforms, int N,
+                         int classes, double *target, double *errors, double inv_n_global);
 // vector helpers on pSize-long vectors
 void vec_axpy(fitre_context *ctx, long n, double a, const double *x, double *y);
 void vec_scale(fitre_context *ctx, long n, double a, double *x);

@@ -66,6 +66,23 @@ extern "C" long fitre_kfac_mem_required(const CNN_MODEL *m) {
     return align32(need);
 }
 
+extern "C" int fitre_compute_distribution_errors(fitre_context *ctx, const real *probs,
+                                                 const real *uniforms, real *distTarget,
+                                                 real *distError, int rows, int numClasses) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    try {
+        FITRE_CUDA(cudaSetDevice(ctx->device));
+        FITRE_REQUIRE(probs && uniforms && distTarget && distError && rows > 0 && numClasses > 0,
+                      FITRE_ERR_BAD_ARG, "bad argument");
+        distribution_errors(ctx, probs, uniforms, rows, numClasses, distTarget, distError,
+                            1.0 / ((double)rows * ctx->world));
+        return FITRE_OK;
+    } catch (const Error &e) {
+        ctx->err = e.what();
+        return e.code;
+    }
+}
+
 extern "C" int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m,
                                   const DEVICE_DATASET *data, const real *z, int samples,
                                   real *omegaZ, const FITRE_KFAC_INFO *info, real *devPtr) {

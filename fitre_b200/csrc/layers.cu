@@ -678,6 +678,28 @@ __global__ void softmax_rop_error_kernel(const double *rz, const double *probs, 
             probs[(long)r * classes + i] * (rz[(long)r * classes + i] - s) * inv_ng;
 }
 
+// inverse-CDF label sampling + (p - onehot(label)) / N  (functions/dev_dist_errors.cu:12-29,
+// functions/softmax_loss.cu:104-136,215-245)
+__global__ void distribution_errors_kernel(const double *probs, const double *uniforms, int N,
+                                           int classes, double *target, double *errors,
+                                           double inv_ng) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= N) return;
+    double c = 0.0;
+    int label = -1;
+    for (int i = 0; i < classes; ++i) {
+        c += probs[(long)r * classes + i];
+        if (c >= uniforms[r]) {
+            label = i + 1;
+            break;
+        }
+    }
+    if (label == -1) label = classes + 1;
+    target[r] = (double)label;
+    for (int i = 0; i < classes; ++i)
+        errors[(long)r * classes + i] = (probs[(long)r * classes + i] - (i + 1 == label ? 1.0 : 0.0)) * inv_ng;
+}
+
 __global__ void axpby_kernel(long n, double a, const double *x, double b, double *y) {
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n;
          i += (long)gridDim.x * blockDim.x)
@@ -933,6 +955,13 @@ void softmax_rop_error(fitre_context *ctx, const double *rz, const double *probs
     softmax_rop_error_kernel<<<(N + 127) / 128, 128, 0, ctx->stream>>>(rz, probs, N, classes, rerr,
                                                                        inv_n_global);
     check_launch(ctx, "softmax_rop_error_kernel");
+}
+
+void distribution_errors(fitre_context *ctx, const double *probs, const double *uniforms, int N,
+                         int classes, double *target, double *errors, double inv_n_global) {
+    distribution_errors_kernel<<<(N + 127) / 128, 128, 0, ctx->stream>>>(probs, uniforms, N, classes,
+                                                                         target, errors, inv_n_global);
+    check_launch(ctx, "distribution_errors_kernel");
 }
 
 void vec_axpby(fitre_context *ctx, long n, double a, const double *x, double b, double *y) {

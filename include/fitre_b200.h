@@ -270,6 +270,12 @@ int fitre_cg_steihaug(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
 
 /* ---- KFAC factors (solvers/kfac_utils.cu:7-55, kfac_inverses.cu:450-630,759-857) */
 int fitre_kfac_storage_indices(const CNN_MODEL *m, FITRE_KFAC_INFO *info);
+/* functions/softmax_loss.cu:104-136 (computeDistributionErrors): sample one label per image from
+ * `probs` by inverse CDF (functions/dev_dist_errors.cu:12-29) and form (p - onehot(label))/N for
+ * the second backward pass of the KFAC step.  `uniforms` (rows doubles in [0,1), device) replaces
+ * the reference's time-seeded cuRAND draw so that results are reproducible. */
+int fitre_compute_distribution_errors(fitre_context *ctx, const real *probs, const real *uniforms,
+                                      real *distTarget, real *distError, int rows, int numClasses);
 /* Scratch (doubles) the two factor routines below need behind devPtr. */
 long fitre_kfac_mem_required(const CNN_MODEL *m);
 /* A factors: conv (1/N) P~'P~ with P~ = [im2col(X)/(Ho*Wo), 1]; FC (1/N) z~ z~'.  Raw

@@ -708,6 +708,33 @@ static void ce_error(const ORA_ENV *env, const double *probs, int N, int classes
             errors[(long)r * classes + c] = v * sc;
         }
 }
+/* Labels sampled from the model's own distribution (KFAC), then (p - onehot(label)) / N_global.
+ * functions/dev_dist_errors.cu:12-50 (inverse CDF: first class whose running sum reaches the
+ * uniform; classes+1 if none does), functions/softmax_loss.cu:104-136.  The reference draws the
+ * uniforms from a time-seeded cuRAND stream; here they are an input. */
+void ora_distribution_errors(const ORA_ENV *env, const double *probs, const double *uniforms,
+                             int N, int classes, double *distTarget, double *distError) {
+    for (int r = 0; r < N; r++) {
+        double c = 0.0;
+        distTarget[r] = -1;
+        for (int i = 0; i < classes; i++) {
+            c += probs[(long)r * classes + i];
+            if (c >= uniforms[r]) {
+                distTarget[r] = i + 1;
+                break;
+            }
+        }
+        if (distTarget[r] == -1) distTarget[r] = classes + 1;
+    }
+    double sc = 1. / ((double)N * env_world(env));
+    for (int r = 0; r < N; r++)
+        for (int c = 0; c < classes; c++) {
+            double v = probs[(long)r * classes + c];
+            if ((double)(c + 1) == distTarget[r]) v -= 1.;
+            distError[(long)r * classes + c] = v * sc;
+        }
+}
+
 /* R{p - y} = p .* (Rz - sum_j p_j Rz_j) / N_global : :251-299 */
 static void ce_rop_error(const ORA_ENV *env, const double *rz, const double *probs, int N,
                          int classes, double *rError) {

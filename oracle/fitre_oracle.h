@@ -66,6 +66,9 @@ void ora_activation(int act, double *x, long n);
 double ora_softmax_loss(const ORA_ENV *env, const double *logits, const double *target, int N,
                         int classes, double *probs);
 
+void ora_distribution_errors(const ORA_ENV *env, const double *probs, const double *uniforms,
+                             int N, int classes, double *distTarget, double *distError);
+
 /* whole-network passes */
 double ora_cnn_forward(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
                        const double *labels, const double *weights, int numClasses, double *z,

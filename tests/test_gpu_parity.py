@@ -250,3 +250,32 @@ def test_cuda_full_size_properties_vgg11():
     # dominated by max-pool arg-max switches at this size and is not a usable check)
     fd_h = (fp - 2 * f0 + fm) / (h * h)
     assert abs(fd_h - dHd) <= 2e-2 * abs(dHd), (fd_h, dHd)
+
+
+def test_cuda_distribution_errors_and_sampled_backward_vs_oracle():
+    """KFAC's second backward pass: labels sampled from the model's distribution (injected
+    uniforms), errors, then cnnBackward on them; sampled labels must be identical."""
+    import gpu_util as G
+    from fitre_b200 import api
+    n = 12
+    model = nets.vgg_small(n)
+    O.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=41)
+    u = np.random.default_rng(4238).random(n)
+    u[0], u[1] = 0.0, 1.0 - 1e-16  # edges of the inverse CDF
+    st = O.gradient(model, x, y, w, ncls, n)
+    env = O.make_env()
+    t_o, e_o = np.zeros(n), np.zeros(n * ncls)
+    O.lib().ora_distribution_errors(C.byref(env), st.probs, u, n, ncls, t_o, e_o)
+    g_o, dx_o = np.zeros(model.pSize), np.zeros(model.zSize)
+    O.lib().ora_cnn_backward(C.byref(env), C.byref(model), x, w, st.z, g_o, dx_o, e_o, n)
+    run = G.GpuRun(model, x, y, w, ncls)
+    ws = run.ws
+    t_d, e_d = G.dev(np.zeros(n)), G.dev(np.zeros(model.maxDeltaSize + n * ncls))
+    e2 = G.dev(np.zeros(model.maxDeltaSize + n * ncls))
+    api.computeDistributionErrors(run.c, ws.probs, G.dev(u), t_d, e_d, n, ncls)
+    assert np.array_equal(t_d.cpu().numpy(), t_o)
+    assert G.relmax(e_d.cpu().numpy()[:n * ncls], e_o) < TOL
+    g_d, dx_d = G.dev(np.zeros(model.pSize)), G.dev(np.zeros(model.zSize))
+    api.cnnBackward(run.c, model, run.data, ws.dev, ws.z, g_d, dx_d, e_d, e2, 0, n)
+    assert G.rel(g_d.cpu().numpy(), g_o) < TOL
