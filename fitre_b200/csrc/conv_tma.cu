@@ -54,6 +54,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 // Bounded wait: gives up after ~2^31 clock ticks and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     const long long t0 = clock64();
@@ -105,9 +108,13 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
     const int w0 = wt * p.TW, n0 = nt * p.TN;
     const int c0 = blockIdx.y * T_BN;
 
+    // bars[s]: "full" (TMA bytes landed); bars[4 + s]: "empty" (all 8 warps done reading)
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < p.stages; ++s) mbar_init(smem_u32(bars + s), 1);
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(bars + s), 1);
+            mbar_init(smem_u32(bars + 4 + s), T_THREADS / 32);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int q = tid; q < KCH; q += T_THREADS) {
@@ -153,14 +160,23 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
+    // Warps run decoupled: a stage is refilled once every warp has arrived on its "empty"
+    // barrier; only the issuing thread waits for that, the others go on to the next stage.
+    volatile int *vabort = &abort_flag;
     for (int it = 0; it < iters; ++it) {
         const int s = it % p.stages;
-        // stage (it-1) % stages was released by the barrier that ended the previous iteration
-        if (tid == 0 && it + p.stages - 1 < iters) issue(it + p.stages - 1);
-        const bool ready = mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1));
-        if (!ready) {
-            abort_flag = 1;
-        } else {
+        if (tid == 0 && it + p.stages - 1 < iters) {
+            const int nit = it + p.stages - 1, use = nit / p.stages;
+            if (use > 0 && !mbar_wait(smem_u32(bars + 4 + nit % p.stages), (uint32_t)((use - 1) & 1)))
+                *vabort = 1;
+            else
+                issue(nit);
+        }
+        if (*vabort || !mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1))) {
+            *vabort = 1;
+            break;
+        }
+        {
             const double *patch = (const double *)(sm + (size_t)s * stageBytes);
             const double *Bs = (const double *)(sm + (size_t)s * stageBytes + p.patchBytes) +
                                (warp_n * 32 + lr) * KCH + lc;
@@ -179,11 +195,13 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
                         dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
             }
         }
-        __syncthreads();
-        if (abort_flag) {
-            if (tid == 0) atomicExch(p.err, 1);
-            return;
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bars + 4 + s));
+    }
+    __syncthreads();
+    if (abort_flag) {
+        if (tid == 0) atomicExch(p.err, 1);
+        return;
     }
 
     double *y = p.y + (long)blockIdx.z * p.M * p.Cout;
@@ -255,7 +273,10 @@ wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < p.stages; ++s) mbar_init(smem_u32(bars + s), 1);
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(bars + s), 1);                  // full
+            mbar_init(smem_u32(bars + 4 + s), T_THREADS / 32);  // empty
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int ml = tid; ml < BMT; ml += T_THREADS) {
@@ -265,22 +286,20 @@ wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
     }
     __syncthreads();
 
+    // Rows q >= K of the last tile fall on channels >= Cin, which TMA zero-fills; a 128-row tile
+    // never spans more than CBW channels, so every offset stays inside the patch.
     int qofs[4];
 #pragma unroll
     for (int mi = 0; mi < 4; ++mi) {
         const int q = q0 + warp_q * 32 + mi * 8 + lr;
         const int c = q / (KS * KS), rem = q - c * (KS * KS);
         const int j = rem / KS, i = rem - j * KS;
-        // rows beyond K fall on channels >= Cin, which TMA zero-fills; clamp keeps the address
-        // inside the patch for the last tile
-        const int cl = min(c - c_lo, p.CBW - 1);
-        qofs[mi] = (q < p.K) ? (cl * p.TN * p.WB + j) * p.HB + i : -1;
+        qofs[mi] = ((c - c_lo) * p.TN * p.WB + j) * p.HB + i;
     }
     // swizzled B addressing: channel row r = warp_n*32 + (ni>>1)*16 + 2*lr + (ni&1); within a
-    // 16-double box row the 16-byte chunk index is XORed with (r & 7)
-    int brow[4];
-#pragma unroll
-    for (int ni = 0; ni < 4; ++ni) brow[ni] = warp_n * 32 + (ni >> 1) * 16 + 2 * lr + (ni & 1);
+    // 16-double box row the 16-byte chunk index is XORed with (r & 7) = (2*lr + (ni&1)) & 7
+    const int boff0 = (warp_n * 32 + 2 * lr) * 16 + (lc & 1);
+    const int bx0 = (2 * lr) & 7, bx1 = (2 * lr + 1) & 7;
 
     const int t_beg = blockIdx.z * p.tiles_per_split;
     const int t_end = min(p.tiles_total, t_beg + p.tiles_per_split);
@@ -309,13 +328,21 @@ wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
+    volatile int *vabort = &abort_flag;
     for (int it = 0; it < iters; ++it) {
         const int s = it % p.stages;
-        if (tid == 0 && it + p.stages - 1 < iters) issue(it + p.stages - 1);
-        const bool ready = mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1));
-        if (!ready) {
-            abort_flag = 1;
-        } else {
+        if (tid == 0 && it + p.stages - 1 < iters) {
+            const int nit = it + p.stages - 1, use = nit / p.stages;
+            if (use > 0 && !mbar_wait(smem_u32(bars + 4 + nit % p.stages), (uint32_t)((use - 1) & 1)))
+                *vabort = 1;
+            else
+                issue(nit);
+        }
+        if (*vabort || !mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1))) {
+            *vabort = 1;
+            break;
+        }
+        {
             const double *dS = (const double *)(sm + (size_t)s * stageBytes);
             const double *patch = (const double *)(sm + (size_t)s * stageBytes + dBytes);
 #pragma unroll
@@ -325,10 +352,11 @@ wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
                 const int chunk = (k4 & 3) * 2 + (lc >> 1);
                 double fa[4], fb[4];
 #pragma unroll
-                for (int mi = 0; mi < 4; ++mi) fa[mi] = qofs[mi] >= 0 ? patch[rb + qofs[mi]] : 0.0;
+                for (int mi = 0; mi < 4; ++mi) fa[mi] = patch[rb + qofs[mi]];
 #pragma unroll
                 for (int ni = 0; ni < 4; ++ni)
-                    fb[ni] = box[brow[ni] * 16 + ((chunk ^ (brow[ni] & 7)) << 1) + (lc & 1)];
+                    fb[ni] = box[boff0 + ((ni >> 1) * 16 + (ni & 1)) * 16 +
+                                 ((chunk ^ ((ni & 1) ? bx1 : bx0)) << 1)];
 #pragma unroll
                 for (int mi = 0; mi < 4; ++mi)
 #pragma unroll
@@ -336,11 +364,13 @@ wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
                         dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
             }
         }
-        __syncthreads();
-        if (abort_flag) {
-            if (tid == 0) atomicExch(p.err, 1);
-            return;
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bars + 4 + s));
+    }
+    __syncthreads();
+    if (abort_flag) {
+        if (tid == 0) atomicExch(p.err, 1);
+        return;
     }
 
     double *out = p.out + (long)blockIdx.z * p.K * p.Cout;
