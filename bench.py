@@ -368,6 +368,21 @@ def run_extra(args):
         md = model.maxDeltaSize + 32
         e1b, e2b = torch.zeros(md, **f64), torch.zeros(md, **f64)
         dgrad, ddx = torch.zeros(model.pSize, **f64), torch.zeros(model.zSize, **f64)
+        Ai, Gi = torch.zeros(info.OmegaZSize, **f64), torch.zeros(info.LambdaGSize, **f64)
+        ngrad = torch.zeros(model.pSize, **f64)
+        L = _lib.load()
+        iscr = torch.zeros(max(L.fitre_kfac_inverse_mem_required(4609),
+                               L.fitre_kfac_natural_gradient_mem_required(C.byref(model))), **f64)
+        blocks = []
+        for l in range(model.cLayers + model.lLayers):
+            if l < model.cLayers:
+                c = model.convLayer[l]
+                kb, co = c.inChannels * c.kSize ** 2 + model.bias, c.outChannels
+            else:
+                f = model.fcLayer[l - model.cLayers]
+                kb, co = f.in_ + model.bias, f.out
+            blocks.append((kb, info.OmegaZOffsets[l], A, Ai))
+            blocks.append((co, info.LambdaGOffsets[l], G, Gi))
 
     def step():
         api.computeCNNGradient(ctx, model, data, ws.scratch, ws.z, ws.dx, ws.probs, ws.errors,
@@ -386,6 +401,10 @@ def run_extra(args):
             api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
             api.computeOmegaZ(ctx, model, data, ws.z, n, A, info, kscr)
             api.computeLambdaDelta(ctx, model, ddx, n, G, info, kscr)
+            for size, off, src, dst in blocks:  # damped Cholesky inverse of every factor
+                api.computeMatrixInverse(ctx, src[off:off + size * size], dst[off:off + size * size],
+                                         size, iscr, 1e-3, 0.0)
+            api.computeNaturalGradient(ctx, model, info, Ai, Gi, ws.gradient, ngrad, iscr)
 
     def barrier():
         if world > 1:
@@ -411,7 +430,7 @@ def run_extra(args):
     if rank == 0:
         names = {"alexnet": "alexnetbn_32x32_fp64_gradient+hv",
                  "lenet": "lenet_32x32_fp64_gradient+hv+cg10",
-                 "kfac": "vgg11bn_32x32_fp64_kfac_factor_step"}
+                 "kfac": "vgg11bn_32x32_fp64_kfac_step(grad,sampled bwd,A/G factors,inverses,natural gradient)"}
         print(json.dumps({
             "metric": "images/sec", "value": world * n * args.steps / (ms * 1e-3), "unit": "images/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

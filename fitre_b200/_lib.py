@@ -24,7 +24,9 @@ SYMBOLS = [
     "fitre_cnn_rop_forward", "fitre_cnn_rop_backward", "fitre_cnn_hv",
     "fitre_compute_quadratic_model", "fitre_cg_steihaug",
     "fitre_compute_distribution_errors", "fitre_kfac_storage_indices", "fitre_kfac_mem_required", "fitre_kfac_omega_z",
-    "fitre_kfac_lambda_delta", "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host",
+    "fitre_kfac_lambda_delta", "fitre_kfac_inverse_mem_required", "fitre_kfac_matrix_inverse",
+    "fitre_kfac_natural_gradient_mem_required", "fitre_compute_natural_gradient",
+    "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host",
 ]
 
 _lib = None
@@ -83,6 +85,10 @@ def load():
     sig("fitre_kfac_storage_indices", i, MP, C.POINTER(S.KFAC_INFO))
     sig("fitre_kfac_omega_z", i, vp, MP, DP, vp, i, vp, C.POINTER(S.KFAC_INFO), vp)
     sig("fitre_kfac_lambda_delta", i, vp, MP, vp, i, vp, C.POINTER(S.KFAC_INFO), vp)
+    sig("fitre_kfac_inverse_mem_required", l, i)
+    sig("fitre_kfac_matrix_inverse", i, vp, vp, vp, i, vp, d, d)
+    sig("fitre_kfac_natural_gradient_mem_required", l, MP)
+    sig("fitre_compute_natural_gradient", i, vp, MP, C.POINTER(S.KFAC_INFO), vp, vp, vp, vp, vp)
     sig("fitre_syrk_tn_static_scratch", i, vp, l, i, l, d, vp, vp)
     sig("fitre_gradient_hv_host", i, vp, MP, vp, vp, vp, vp, i, i, d, dbl_p, vp, vp)
     _lib = L

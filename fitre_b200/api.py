@@ -250,6 +250,19 @@ def computeLambdaDelta(ctx, model, dx, samples, lambdaG, info, devPtr):
                                               _ptr(lambdaG), C.byref(info), _ptr(devPtr)))
 
 
+def computeMatrixInverse(ctx, matrix, inverse, n, devPtr, lam, dampGamma):
+    """solvers/kfac_inverses.cu:133-186: inverse = (matrix + (lam + dampGamma) I)^-1."""
+    ctx.check(ctx.lib.fitre_kfac_matrix_inverse(ctx.h, _ptr(matrix), _ptr(inverse), n, _ptr(devPtr),
+                                                float(lam), float(dampGamma)))
+
+
+def computeNaturalGradient(ctx, model, info, omegaZInv, lambdaGInv, gradient, nGradient, devPtr):
+    """solvers/kfac_natural_gradient.cu:36-241."""
+    ctx.check(ctx.lib.fitre_compute_natural_gradient(ctx.h, C.byref(model), C.byref(info),
+                                                     _ptr(omegaZInv), _ptr(lambdaGInv),
+                                                     _ptr(gradient), _ptr(nGradient), _ptr(devPtr)))
+
+
 def gradientHvHost(ctx, model, batch, labels, weights, vector, curBatchSize, numClasses,
                    weightDecay, gradient_out, hv_out):
     """Host-buffer entry point: numpy / pinned torch CPU arrays in and out."""

@@ -6,6 +6,8 @@
 // the data-parallel ranks before the 1/N (A) or N (G) scaling with the global batch.
 #include <algorithm>
 #include <climits>
+#include <cstring>
+#include <string>
 
 #include "common.h"
 
@@ -166,6 +168,244 @@ extern "C" int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, c
                 comm_allreduce_sum(ctx, G, (size_t)f.out * f.out);
                 vec_scale(ctx, (long)f.out * f.out, Ng, G);
             }
+        }
+        return FITRE_OK;
+    } catch (const Error &e) {
+        ctx->err = e.what();
+        return e.code;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Damped factor inverses and the natural gradient.
+// Reference: computeMatrixInverseCusolver (solvers/kfac_inverses.cu:133-186: add (lambda+gamma)
+// to the diagonal, cusolverDnDpotrf, cusolverDnDpotrs against the identity) and
+// computeNaturalGradient (solvers/kfac_natural_gradient.cu:36-241: G^-1 [W|b] A^-1 per layer).
+// Here the Cholesky factorisation is a right-looking blocked one whose panel solves and
+// trailing updates are DMMA GEMMs, the triangular inverse is recursive (two GEMMs per level)
+// and the final L^-T L^-1 is the A'A kernel; only the 64x64 diagonal blocks are handled by a
+// small shared-memory kernel.  No cuSOLVER / cuBLAS.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr int NB = 64;
+
+// In place: A (nb x nb, lower, leading dim lda) <- its Cholesky factor L (upper part zeroed);
+// Linv (nb x nb, ld NB, dense lower) <- L^-1.  *fail is set to 1 + column on a pivot <= 0.
+__global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, int nb, double *Linv,
+                                                         int *fail, int col0) {
+    // lower triangle: L; strictly upper triangle: (L^-1)' off-diagonal; xd: diagonal of L^-1
+    __shared__ double L[NB][NB + 1];
+    __shared__ double xd[NB];
+    __shared__ int bad;
+    const int tid = threadIdx.x;
+    if (tid == 0) bad = 0;
+    for (int e = tid; e < NB * NB; e += 256) {
+        const int r = e % NB, c = e / NB;
+        L[r][c] = (r < nb && c < nb && r >= c) ? A[(long)c * lda + r] : 0.0;
+    }
+    __syncthreads();
+    for (int j = 0; j < nb; ++j) {
+        if (tid == 0) {
+            const double d = L[j][j];
+            if (!(d > 0.0)) {
+                bad = j + 1;
+                L[j][j] = 1.0;
+            } else {
+                L[j][j] = sqrt(d);
+            }
+        }
+        __syncthreads();
+        const double dj = L[j][j];
+        for (int r = j + 1 + tid; r < nb; r += 256) L[r][j] /= dj;
+        __syncthreads();
+        // trailing update of the lower triangle: L[r][c] -= L[r][j] * L[c][j], j < c <= r
+        const int rem = nb - j - 1;
+        for (int e = tid; e < rem * rem; e += 256) {
+            const int r = j + 1 + e % rem, c = j + 1 + e / rem;
+            if (r >= c) L[r][c] -= L[r][j] * L[c][j];
+        }
+        __syncthreads();
+    }
+    // X = L^-1 by forward substitution, one column per thread; X[r][c] (r > c) lives at L[c][r]
+    if (tid < nb) {
+        const int c = tid;
+        xd[c] = 1.0 / L[c][c];
+        for (int r = c + 1; r < nb; ++r) {
+            double s = -L[r][c] * xd[c];
+            for (int k = c + 1; k < r; ++k) s -= L[r][k] * L[c][k];
+            L[c][r] = s / L[r][r];
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < NB * NB; e += 256) {
+        const int r = e % NB, c = e / NB;
+        if (r < nb && c < nb && r >= c) A[(long)c * lda + r] = L[r][c];
+        double x = 0.0;
+        if (r < nb && c < nb) x = (r == c) ? xd[c] : (r > c ? L[c][r] : 0.0);
+        Linv[(long)c * NB + r] = x;
+    }
+    if (tid == 0 && bad) atomicCAS(fail, 0, col0 + bad);
+}
+
+__global__ void add_diagonal_kernel(double *A, int n, double v) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) A[(long)i * n + i] += v;
+}
+__global__ void zero_upper_kernel(double *A, int n) {  // strictly upper triangle <- 0
+    const long nn = (long)n * n;
+    for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < nn; e += (long)gridDim.x * blockDim.x) {
+        const int c = (int)(e / n), r = (int)(e - (long)c * n);
+        if (r < c) A[e] = 0.0;
+    }
+}
+// conv weights (K x Cout) + bias -> wb (K' x Cout): solvers/kfac_natural_gradient.cu:79-94
+__global__ void pack_wb_kernel(const double *w, const double *b, double *wb, int K, int Kb, int Cout) {
+    const long total = (long)Kb * Cout;
+    for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+        const int o = (int)(e / Kb), r = (int)(e - (long)o * Kb);
+        wb[e] = r < K ? w[(long)o * K + r] : b[o];
+    }
+}
+// ng (Cout x K', col-major) -> weights (K x Cout col-major) and bias (Cout): :166-173
+__global__ void unpack_ng_kernel(const double *t, double *w, double *b, int K, int Kb, int Cout) {
+    const long total = (long)Kb * Cout;
+    for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+        const int r = (int)(e / Cout), o = (int)(e - (long)r * Cout);  // t[o + r*Cout]
+        if (r < K) w[(long)o * K + r] = t[e];
+        else b[o] = t[e];
+    }
+}
+int blocks_for(long n) { return (int)std::max<long>(1, std::min<long>((n + 255) / 256, 1184)); }
+
+// Y (n x n, ld n) holds L on entry (lower, upper zero); on exit L^-1.  dinv = the NB x NB inverses
+// of the diagonal blocks.  Recursive: inv([L11 0; L21 L22]) = [L11^-1 0; -L22^-1 L21 L11^-1  L22^-1].
+void trtri_recursive(fitre_context *ctx, double *Y, long ld, int n, int off, const double *dinv,
+                     double *tmp) {
+    if (n <= NB) {
+        FITRE_CUDA(cudaMemcpy2DAsync(Y, ld * sizeof(double), dinv + (long)(off / NB) * NB * NB,
+                                     NB * sizeof(double), n * sizeof(double), n,
+                                     cudaMemcpyDeviceToDevice, ctx->stream));
+        return;
+    }
+    const int n1 = ((n / 2 + NB - 1) / NB) * NB, n2 = n - n1;
+    double *Y11 = Y, *Y21 = Y + n1, *Y22 = Y + (long)n1 * ld + n1;
+    trtri_recursive(ctx, Y11, ld, n1, off, dinv, tmp);
+    trtri_recursive(ctx, Y22, ld, n2, off + n1, dinv, tmp);
+    // tmp (n2 x n1) = L21 * Y11 ; Y21 = -Y22 * tmp
+    dgemm(ctx, false, false, n2, n1, n1, 1.0, Y21, (int)ld, Y11, (int)ld, 0.0, tmp, n2);
+    dgemm(ctx, false, false, n2, n1, n2, -1.0, Y22, (int)ld, tmp, n2, 0.0, Y21, (int)ld);
+}
+}  // namespace
+
+extern "C" long fitre_kfac_inverse_mem_required(int n) {
+    if (n < 1) return -1;
+    const long nn = (long)n * n;
+    const long nblk = (n + NB - 1) / NB;
+    return align32(nn) + align32(nblk * NB * NB) + align32(nn / 2 + (long)n * NB) +
+           align32(syrk_scratch(n, n)) + 64;
+}
+
+// inverse = (matrix + (lambda + dampGamma) I)^-1, both n x n column-major.
+extern "C" int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix, real *inverse, int n,
+                                         real *devPtr, real lambda, real dampGamma) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    try {
+        FITRE_CUDA(cudaSetDevice(ctx->device));
+        FITRE_REQUIRE(matrix && inverse && devPtr && n > 0, FITRE_ERR_BAD_ARG, "bad argument");
+        const long nn = (long)n * n;
+        const int nblk = (n + NB - 1) / NB;
+        double *Lm = devPtr;                                   // factor, then L^-1
+        double *dinv = Lm + align32(nn);                       // inverses of the diagonal blocks
+        double *tmp = dinv + align32((long)nblk * NB * NB);    // panel / recursion scratch
+        double *slabs = tmp + align32(nn / 2 + (long)n * NB);
+        int *fail = (int *)(ctx->dscal + 4002);
+        FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), ctx->stream));
+        vec_copy(ctx, nn, matrix, Lm);
+        add_diagonal_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(Lm, n, lambda + dampGamma);
+        check_launch(ctx, "add_diagonal_kernel");
+        for (int j = 0; j < n; j += NB) {
+            const int nb = std::min(NB, n - j), rows = n - j - nb;
+            double *A11 = Lm + (long)j * n + j;
+            double *Dj = dinv + (long)(j / NB) * NB * NB;
+            chol_block_kernel<<<1, 256, 0, ctx->stream>>>(A11, n, nb, Dj, fail, j);
+            check_launch(ctx, "chol_block_kernel");
+            if (rows > 0) {
+                double *A21 = A11 + nb, *A22 = A11 + (long)nb * n + nb;
+                // L21 = A21 * L11^-T ; A22 -= L21 L21'
+                dgemm(ctx, false, true, rows, nb, nb, 1.0, A21, n, Dj, NB, 0.0, tmp, rows);
+                FITRE_CUDA(cudaMemcpy2DAsync(A21, (size_t)n * sizeof(double), tmp, (size_t)rows * sizeof(double),
+                                             (size_t)rows * sizeof(double), nb, cudaMemcpyDeviceToDevice,
+                                             ctx->stream));
+                dgemm(ctx, false, true, rows, rows, nb, -1.0, tmp, rows, tmp, rows, 1.0, A22, n);
+            }
+        }
+        zero_upper_kernel<<<blocks_for(nn), 256, 0, ctx->stream>>>(Lm, n);
+        check_launch(ctx, "zero_upper_kernel");
+        trtri_recursive(ctx, Lm, n, n, 0, dinv, tmp);
+        syrk_tn(ctx, n, n, 1.0, Lm, n, inverse, slabs);        // (L^-1)' L^-1
+        FITRE_CUDA(cudaMemcpyAsync(ctx->pinned + 202, fail, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
+        FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+        int f;
+        std::memcpy(&f, ctx->pinned + 202, sizeof(int));
+        FITRE_REQUIRE(f == 0, FITRE_ERR_NOT_CONVERGED,
+                      "Cholesky pivot <= 0 at column " + std::to_string(f - 1) + " (matrix not positive definite)");
+        return FITRE_OK;
+    } catch (const Error &e) {
+        ctx->err = e.what();
+        return e.code;
+    }
+}
+
+extern "C" long fitre_kfac_natural_gradient_mem_required(const CNN_MODEL *m) {
+    if (!m) return -1;
+    long need = 0;
+    for (int l = 0; l < m->cLayers; ++l) {
+        const CONV_LAYER &c = m->convLayer[l];
+        const long Kb = (long)c.inChannels * c.kSize * c.kSize + 1;
+        need = std::max(need, 3 * align32(Kb * c.outChannels));
+    }
+    for (int l = 0; l < m->lLayers; ++l)
+        need = std::max(need, align32((long)m->fcLayer[l].out * (m->fcLayer[l].in + 1)));
+    return need;
+}
+
+// nGradient = G^-1 [W|b] A^-1 per layer, in the flat gradient layout.
+extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODEL *m,
+                                              const FITRE_KFAC_INFO *info, const real *omegaZInv,
+                                              const real *lambdaGInv, const real *gradient,
+                                              real *nGradient, real *devPtr) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    try {
+        FITRE_CUDA(cudaSetDevice(ctx->device));
+        FITRE_REQUIRE(m && info && omegaZInv && lambdaGInv && gradient && nGradient && devPtr,
+                      FITRE_ERR_BAD_ARG, "NULL pointer argument");
+        const int hasb = m->bias ? 1 : 0;
+        for (int c = 0; c < m->cLayers; ++c) {
+            const CONV_LAYER &L = m->convLayer[c];
+            const int K = L.inChannels * L.kSize * L.kSize, Kb = K + hasb, Co = L.outChannels;
+            const double *Ai = omegaZInv + info->OmegaZOffsets[c];
+            const double *Gi = lambdaGInv + info->LambdaGOffsets[c];
+            const long sz = align32((long)Kb * Co);
+            double *wb = devPtr, *t1 = wb + sz, *t2 = t1 + sz;
+            pack_wb_kernel<<<blocks_for((long)Kb * Co), 256, 0, ctx->stream>>>(
+                gradient + m->wOffsets[c], hasb ? gradient + m->bOffsets[c] : nullptr, wb, K, Kb, Co);
+            check_launch(ctx, "pack_wb_kernel");
+            dgemm(ctx, false, true, Co, Kb, Co, 1.0, Gi, Co, wb, Kb, 0.0, t1, Co);   // G^-1 wb'
+            dgemm(ctx, false, false, Co, Kb, Kb, 1.0, t1, Co, Ai, Kb, 0.0, t2, Co);  // ... A^-1
+            unpack_ng_kernel<<<blocks_for((long)Kb * Co), 256, 0, ctx->stream>>>(
+                t2, nGradient + m->wOffsets[c], hasb ? nGradient + m->bOffsets[c] : nullptr, K, Kb, Co);
+            check_launch(ctx, "unpack_ng_kernel");
+        }
+        for (int l = 0; l < m->lLayers; ++l) {
+            const FC_LAYER &F = m->fcLayer[l];
+            const int li = m->cLayers + l, in = F.in + hasb;
+            const double *Ai = omegaZInv + info->OmegaZOffsets[li];
+            const double *Gi = lambdaGInv + info->LambdaGOffsets[li];
+            // [W | b] is contiguous in the flat layout: out x (in + bias), column-major
+            dgemm(ctx, false, false, F.out, in, F.out, 1.0, Gi, F.out, gradient + m->wOffsets[li], F.out,
+                  0.0, devPtr, F.out);
+            dgemm(ctx, false, false, F.out, in, in, 1.0, devPtr, F.out, Ai, in, 0.0,
+                  nGradient + m->wOffsets[li], F.out);
         }
         return FITRE_OK;
     } catch (const Error &e) {

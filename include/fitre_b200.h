@@ -287,6 +287,22 @@ int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATA
 int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, const real *dx, int samples,
                             real *lambdaG, const FITRE_KFAC_INFO *info, real *devPtr);
 
+/* solvers/kfac_inverses.cu:133-186 (computeMatrixInverseCusolver): inverse = (matrix +
+ * (lambda + dampGamma) I)^-1 for a symmetric positive definite n x n factor, by blocked Cholesky
+ * and triangular inversion on the device.  devPtr needs fitre_kfac_inverse_mem_required(n)
+ * doubles.  A non-positive pivot returns FITRE_ERR_NOT_CONVERGED (the reference exits). */
+long fitre_kfac_inverse_mem_required(int n);
+int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix, real *inverse, int n,
+                              real *devPtr, real lambda, real dampGamma);
+/* solvers/kfac_natural_gradient.cu:36-241 (computeNaturalGradient): nGradient = G^-1 [W|b] A^-1
+ * per layer, in the flat layout of `gradient`.  omegaZInv / lambdaGInv hold the inverted factors
+ * at the offsets of `info` (A blocks K' x K' with K' = K + bias). */
+long fitre_kfac_natural_gradient_mem_required(const CNN_MODEL *m);
+int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODEL *m,
+                                   const FITRE_KFAC_INFO *info, const real *omegaZInv,
+                                   const real *lambdaGInv, const real *gradient, real *nGradient,
+                                   real *devPtr);
+
 /* C (n x n, both triangles) = alpha * A'A with A rows x n column-major (lda), the product behind
  * every G-factor block above, for callers that cannot allocate device memory (a driver whose
  * workspace already owns all of it, code between stream-capture calls, threads barred from the

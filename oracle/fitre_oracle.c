@@ -1331,3 +1331,81 @@ void ora_kfac_lambda_delta(const ORA_ENV *env, const CNN_MODEL *m, const double 
         for (long i = 0; i < (long)f->out * f->out; i++) G[i] *= Ng;
     }
 }
+
+/* inverse = (matrix + (lambda + gamma) I)^-1 by Cholesky factorisation and two triangular solves
+ * against the identity: solvers/kfac_inverses.cu:133-186 (cusolverDnDpotrf + cusolverDnDpotrs).
+ * Returns 0, or 1 + the column of a non-positive pivot. */
+int ora_kfac_matrix_inverse(const double *matrix, double *inverse, int n, double lambda,
+                            double gamma) {
+    long nn = (long)n * n;
+    double *L = xmalloc(nn);
+    memcpy(L, matrix, sizeof(double) * (size_t)nn);
+    for (int i = 0; i < n; i++) L[(long)i * n + i] += lambda + gamma;
+    for (int j = 0; j < n; j++) { /* column-major lower Cholesky, left-looking */
+        double d = L[(long)j * n + j];
+        for (int k = 0; k < j; k++) d -= L[(long)k * n + j] * L[(long)k * n + j];
+        if (!(d > 0)) {
+            free(L);
+            return j + 1;
+        }
+        d = sqrt(d);
+        L[(long)j * n + j] = d;
+#pragma omp parallel for schedule(static)
+        for (int i = j + 1; i < n; i++) {
+            double s = L[(long)j * n + i];
+            for (int k = 0; k < j; k++) s -= L[(long)k * n + i] * L[(long)k * n + j];
+            L[(long)j * n + i] = s / d;
+        }
+    }
+#pragma omp parallel for schedule(dynamic)
+    for (int c = 0; c < n; c++) { /* solve L L' x = e_c */
+        double *x = inverse + (long)c * n;
+        for (int i = 0; i < n; i++) x[i] = (i == c) ? 1.0 : 0.0;
+        for (int i = c; i < n; i++) {
+            double s = x[i];
+            for (int k = c; k < i; k++) s -= L[(long)k * n + i] * x[k];
+            x[i] = s / L[(long)i * n + i];
+        }
+        for (int i = n - 1; i >= 0; i--) {
+            double s = x[i];
+            for (int k = i + 1; k < n; k++) s -= L[(long)i * n + k] * x[k];
+            x[i] = s / L[(long)i * n + i];
+        }
+    }
+    free(L);
+    return 0;
+}
+
+/* nGradient = G^-1 [W|b] A^-1 per layer in the flat gradient layout:
+ * solvers/kfac_natural_gradient.cu:36-241. */
+void ora_natural_gradient(const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const double *omegaZInv,
+                          const double *lambdaGInv, const double *gradient, double *nGradient) {
+    int hasb = m->bias != 0;
+    for (int c = 0; c < m->cLayers; c++) {
+        const CONV_LAYER *L = &m->convLayer[c];
+        long K = (long)L->inChannels * L->kSize * L->kSize, Kb = K + hasb, Co = L->outChannels;
+        const double *Ai = omegaZInv + info->OmegaZOffsets[c], *Gi = lambdaGInv + info->LambdaGOffsets[c];
+        double *wb = xmalloc(Kb * Co), *t1 = xmalloc(Kb * Co), *t2 = xmalloc(Kb * Co);
+        for (long o = 0; o < Co; o++) {
+            memcpy(wb + o * Kb, gradient + m->wOffsets[c] + o * K, sizeof(double) * (size_t)K);
+            if (hasb) wb[o * Kb + K] = gradient[m->bOffsets[c] + o];
+        }
+        ora_gemm(0, 1, Co, Kb, Co, 1.0, Gi, Co, wb, Kb, 0.0, t1, Co);
+        ora_gemm(0, 0, Co, Kb, Kb, 1.0, t1, Co, Ai, Kb, 0.0, t2, Co);
+        for (long o = 0; o < Co; o++) {
+            for (long r = 0; r < K; r++) nGradient[m->wOffsets[c] + o * K + r] = t2[o + r * Co];
+            if (hasb) nGradient[m->bOffsets[c] + o] = t2[o + K * Co];
+        }
+        free(wb); free(t1); free(t2);
+    }
+    for (int l = 0; l < m->lLayers; l++) {
+        const FC_LAYER *F = &m->fcLayer[l];
+        int li = m->cLayers + l;
+        long in = F->in + hasb;
+        const double *Ai = omegaZInv + info->OmegaZOffsets[li], *Gi = lambdaGInv + info->LambdaGOffsets[li];
+        double *t = xmalloc((long)F->out * in);
+        ora_gemm(0, 0, F->out, in, F->out, 1.0, Gi, F->out, gradient + m->wOffsets[li], F->out, 0.0, t, F->out);
+        ora_gemm(0, 0, F->out, in, in, 1.0, t, F->out, Ai, in, 0.0, nGradient + m->wOffsets[li], F->out);
+        free(t);
+    }
+}

@@ -108,6 +108,11 @@ void ora_kfac_omega_z(const ORA_ENV *env, const CNN_MODEL *m, const double *batc
 void ora_kfac_lambda_delta(const ORA_ENV *env, const CNN_MODEL *m, const double *dx, int n,
                            double *lambdaG, const FITRE_KFAC_INFO *info);
 
+int ora_kfac_matrix_inverse(const double *matrix, double *inverse, int n, double lambda,
+                            double gamma);
+void ora_natural_gradient(const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const double *omegaZInv,
+                          const double *lambdaGInv, const double *gradient, double *nGradient);
+
 #ifdef __cplusplus
 }
 #endif

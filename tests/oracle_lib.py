@@ -50,6 +50,9 @@ def lib():
         L.ora_kfac_storage_indices.restype = i
         L.ora_kfac_omega_z.argtypes = [EP, MP, dp, dp, i, dp, C.POINTER(S.KFAC_INFO)]
         L.ora_kfac_lambda_delta.argtypes = [EP, MP, dp, i, dp, C.POINTER(S.KFAC_INFO)]
+        L.ora_kfac_matrix_inverse.argtypes = [dp, dp, i, d, d]
+        L.ora_kfac_matrix_inverse.restype = i
+        L.ora_natural_gradient.argtypes = [MP, C.POINTER(S.KFAC_INFO), dp, dp, dp, dp]
         L.ora_cnn_backward.argtypes = [EP, MP, dp, dp, dp, dp, dp, dp, i]
         L.ora_distribution_errors.argtypes = [EP, dp, dp, i, i, dp, dp]
         L.ora_im2col.argtypes = [dp, i, i, i, i, i, i, i, dp]

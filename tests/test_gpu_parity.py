@@ -279,3 +279,75 @@ def test_cuda_distribution_errors_and_sampled_backward_vs_oracle():
     g_d, dx_d = G.dev(np.zeros(model.pSize)), G.dev(np.zeros(model.zSize))
     api.cnnBackward(run.c, model, run.data, ws.dev, ws.z, g_d, dx_d, e_d, e2, 0, n)
     assert G.rel(g_d.cpu().numpy(), g_o) < TOL
+
+
+def test_cuda_kfac_inverse_and_natural_gradient_vs_oracle():
+    """Damped Cholesky inverses of every factor and the natural gradient G^-1 [W|b] A^-1.
+    The inverse is compared to the oracle's and by its residual; tolerance 1e-9 (two different
+    factorisation orders on matrices with condition number up to ~1e4)."""
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    L = _lib.load()
+    lam, gamma = 1e-3, 1e-2
+    for builder, kwargs, n in (("vgg_small", dict(), 6), ("alexnet_small", dict(bias=True, ch=6), 4)):
+        model = getattr(nets, builder)(n, **kwargs)
+        O.finalize(model)
+        x, y, w, v, ncls = G.synth(model, n, seed=55)
+        run = G.GpuRun(model, x, y, w, ncls)
+        info = api.computeKFACStorageIndices(model)
+        need = max(L.fitre_kfac_mem_required(C.byref(model)), L.fitre_kfac_inverse_mem_required(512),
+                   L.fitre_kfac_natural_gradient_mem_required(C.byref(model)))
+        scratch = G.dev(np.zeros(need))
+        A, Gm = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+        api.computeOmegaZ(run.c, model, run.data, run.ws.z, n, A, info, scratch)
+        api.computeLambdaDelta(run.c, model, run.ws.dx, n, Gm, info, scratch)
+        Ai, Gi = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+        A_h, G_h = A.cpu().numpy(), Gm.cpu().numpy()
+        Ai_o, Gi_o = np.zeros(info.OmegaZSize), np.zeros(info.LambdaGSize)
+        nl = model.cLayers + model.lLayers
+        for l in range(nl):
+            if l < model.cLayers:
+                c = model.convLayer[l]
+                kb, co = c.inChannels * c.kSize ** 2 + (1 if model.bias else 0), c.outChannels
+            else:
+                f = model.fcLayer[l - model.cLayers]
+                kb, co = f.in_ + (1 if model.bias else 0), f.out
+            for size, off, src, dst, dst_o, src_h in ((kb, info.OmegaZOffsets[l], A, Ai, Ai_o, A_h),
+                                                      (co, info.LambdaGOffsets[l], Gm, Gi, Gi_o, G_h)):
+                api.computeMatrixInverse(run.c, src[off:off + size * size], dst[off:off + size * size],
+                                         size, scratch, lam, gamma)
+                blk = np.ascontiguousarray(src_h[off:off + size * size])
+                out = np.zeros(size * size)
+                assert O.lib().ora_kfac_matrix_inverse(blk, out, size, lam, gamma) == 0
+                dst_o[off:off + size * size] = out
+                got = dst[off:off + size * size].cpu().numpy()
+                assert G.relmax(got, out) < 1e-9, (builder, l, size)
+                M = blk.reshape(size, size) + (lam + gamma) * np.eye(size)
+                assert np.abs(M @ got.reshape(size, size) - np.eye(size)).max() < 1e-9
+        ng = G.dev(np.zeros(model.pSize))
+        api.computeNaturalGradient(run.c, model, info, Ai, Gi, run.ws.gradient, ng, scratch)
+        ng_o = np.zeros(model.pSize)
+        O.lib().ora_natural_gradient(C.byref(model), C.byref(info), Ai_o, Gi_o, run.gradient, ng_o)
+        assert G.rel(ng.cpu().numpy(), ng_o) < 1e-8
+
+
+def test_cuda_matrix_inverse_blocked_sizes_and_failure():
+    """Sizes that exercise the blocked path (several 64-blocks, ragged last block) and the
+    not-positive-definite status."""
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    L = _lib.load()
+    c = G.ctx()
+    rng = np.random.default_rng(3)
+    for n in (1, 64, 65, 200, 333):
+        B = rng.standard_normal((n, n + 8))
+        F = B @ B.T / n
+        scratch = G.dev(np.zeros(L.fitre_kfac_inverse_mem_required(n)))
+        out = G.dev(np.zeros(n * n))
+        api.computeMatrixInverse(c, G.dev(F.reshape(-1)), out, n, scratch, 1e-3, 0.1)
+        ref = np.linalg.inv(F + 0.101 * np.eye(n))
+        assert G.relmax(out.cpu().numpy().reshape(n, n), ref) < 1e-9, n
+    with pytest.raises(api.FitreError) as e:
+        api.computeMatrixInverse(c, G.dev(-np.eye(70).reshape(-1)), G.dev(np.zeros(4900)), 70,
+                                 G.dev(np.zeros(L.fitre_kfac_inverse_mem_required(70))), 0.0, 0.0)
+    assert e.value.status == S.ERR_NOT_CONVERGED

@@ -243,3 +243,37 @@ def test_reference_softmax_quirk_is_small_but_present():
     r = rel(a.gradient, b.gradient)
     assert 0 < r < 1e-8
     assert np.all(a.probs >= 1e-10)
+
+
+def test_kfac_inverse_and_natural_gradient_host():
+    """(F + damping)^-1 against numpy, and G^-1 [W|b] A^-1 against a direct numpy statement."""
+    import ctypes as C
+    rng = np.random.default_rng(8)
+    n = 37
+    B = rng.standard_normal((n, 2 * n))
+    F = B @ B.T / (2 * n)
+    inv = np.zeros(n * n)
+    assert O.lib().ora_kfac_matrix_inverse(np.ascontiguousarray(F.T).reshape(-1), inv, n, 1e-3, 0.05) == 0
+    ref = np.linalg.inv(F + (1e-3 + 0.05) * np.eye(n))
+    assert np.allclose(inv.reshape(n, n).T, ref, rtol=1e-10, atol=1e-12)
+    bad = -np.eye(n)
+    assert O.lib().ora_kfac_matrix_inverse(bad.reshape(-1).copy(), inv, n, 0.0, 0.0) == 1
+    model = nets.lenet_small(4)
+    O.finalize(model)
+    info = S.KFAC_INFO()
+    O.lib().ora_kfac_storage_indices(C.byref(model), C.byref(info))
+    Ainv = rng.standard_normal(info.OmegaZSize)
+    Ginv = rng.standard_normal(info.LambdaGSize)
+    g = rng.standard_normal(model.pSize)
+    ng = np.zeros(model.pSize)
+    O.lib().ora_natural_gradient(C.byref(model), C.byref(info), Ainv, Ginv, g, ng)
+    # layer 1 (conv 6->16, 5x5, with bias): W is K x Cout column-major, bias follows
+    c = model.convLayer[1]
+    K, Co = c.inChannels * 25, c.outChannels
+    Wm = g[model.wOffsets[1]:model.wOffsets[1] + K * Co].reshape(Co, K)      # [o][q]
+    Wb = np.concatenate([Wm, g[model.bOffsets[1]:model.bOffsets[1] + Co][:, None]], axis=1)
+    A = Ainv[info.OmegaZOffsets[1]:info.OmegaZOffsets[1] + (K + 1) ** 2].reshape(K + 1, K + 1).T
+    Gm = Ginv[info.LambdaGOffsets[1]:info.LambdaGOffsets[1] + Co * Co].reshape(Co, Co).T
+    exp = Gm @ Wb @ A
+    assert np.allclose(ng[model.wOffsets[1]:model.wOffsets[1] + K * Co].reshape(Co, K), exp[:, :K])
+    assert np.allclose(ng[model.bOffsets[1]:model.bOffsets[1] + Co], exp[:, K])
