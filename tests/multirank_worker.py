@@ -57,9 +57,16 @@ def main():
             dist.all_reduce(t)
 
         env = O.make_env(ref_softmax=1, world=world, allreduce=allreduce)
+        import ctypes as C
+        from fitre_b200 import _structs as S
         st = O.gradient(model, xs, ys, w, ncls, per, env=env)
         hv = O.hv(model, xs, w, ncls, per, st, v, env=env)
-        np.savez(out, loss=st.loss, gradient=st.gradient, hv=hv)
+        info = S.KFAC_INFO()
+        O.lib().ora_kfac_storage_indices(C.byref(model), C.byref(info))
+        A, G = np.zeros(info.OmegaZSize), np.zeros(info.LambdaGSize)
+        O.lib().ora_kfac_omega_z(C.byref(env), C.byref(model), xs, st.z, per, A, C.byref(info))
+        O.lib().ora_kfac_lambda_delta(C.byref(env), C.byref(model), st.dx, per, G, C.byref(info))
+        np.savez(out, loss=st.loss, gradient=st.gradient, hv=hv, A=A, G=G)
     else:
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world,
@@ -69,9 +76,17 @@ def main():
         ctx = api.Context(rank)
         ctx.comm_init_from_torch()
         G._CTX["c"] = ctx
+        import ctypes as C
+        from fitre_b200 import _lib
         run = G.GpuRun(model, xs, ys, w, ncls, ref_softmax=1)
         hv = run.hv(v)
-        np.savez(out, loss=run.loss, gradient=run.gradient, hv=hv)
+        info = api.computeKFACStorageIndices(model)
+        scr = G.dev(np.zeros(_lib.load().fitre_kfac_mem_required(C.byref(model))))
+        A, Gm = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+        api.computeOmegaZ(ctx, model, run.data, run.ws.z, per, A, info, scr)
+        api.computeLambdaDelta(ctx, model, run.ws.dx, per, Gm, info, scr)
+        np.savez(out, loss=run.loss, gradient=run.gradient, hv=hv, A=A.cpu().numpy(),
+                 G=Gm.cpu().numpy())
         torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

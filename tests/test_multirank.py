@@ -38,7 +38,15 @@ def full_batch_reference(builder):
     model, x, y, w, v, ncls = W.make_case(builder)
     st = O.gradient(model, x, y, w, ncls, W.N_GLOBAL)
     hv = O.hv(model, x, w, ncls, W.N_GLOBAL, st, v)
-    return st.loss, st.gradient, hv
+    import ctypes as C
+    from fitre_b200 import _structs as S
+    info = S.KFAC_INFO()
+    O.lib().ora_kfac_storage_indices(C.byref(model), C.byref(info))
+    A, G = np.zeros(info.OmegaZSize), np.zeros(info.LambdaGSize)
+    env = O.make_env()
+    O.lib().ora_kfac_omega_z(C.byref(env), C.byref(model), x, st.z, W.N_GLOBAL, A, C.byref(info))
+    O.lib().ora_kfac_lambda_delta(C.byref(env), C.byref(model), st.dx, W.N_GLOBAL, G, C.byref(info))
+    return st.loss, st.gradient, hv, A, G
 
 
 def rel(a, b):
@@ -47,11 +55,12 @@ def rel(a, b):
 
 @pytest.mark.parametrize("builder", ["vgg_small", "lenet_small"])
 def test_two_rank_oracle_matches_full_batch(tmp_path, builder):
-    loss, g, hv = full_batch_reference(builder)
+    loss, g, hv, A, G = full_batch_reference(builder)
     for res in run_ranks("gloo", 2, tmp_path, builder):
         assert abs(float(res["loss"]) - loss) <= 1e-12 * abs(loss)
         assert rel(res["gradient"], g) < 1e-12
         assert rel(res["hv"], hv) < 1e-12
+        assert rel(res["A"], A) < 1e-12 and rel(res["G"], G) < 1e-12
 
 
 @pytest.mark.gpu
@@ -60,8 +69,9 @@ def test_two_gpu_cuda_matches_full_batch(tmp_path, builder):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    loss, g, hv = full_batch_reference(builder)
+    loss, g, hv, A, G = full_batch_reference(builder)
     for res in run_ranks("nccl", 2, tmp_path, builder):
         assert abs(float(res["loss"]) - loss) <= 1e-10 * abs(loss)
         assert rel(res["gradient"], g) < 1e-10
         assert rel(res["hv"], hv) < 1e-10
+        assert rel(res["A"], A) < 1e-10 and rel(res["G"], G) < 1e-10
