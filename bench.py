@@ -193,6 +193,8 @@ def run_ours(args):
     ctx = api.Context(local)
     if world > 1:
         ctx.comm_init_from_torch()
+    if args.precision != "fp64":
+        ctx.set_precision({"tf32": 1, "tf32x3": 2}[args.precision])
     x, y, w, v = synth(model, n, 3234 + rank)   # each rank holds its own shard of the batch
     _, _, w, v = synth(model, n, 3234)          # parameters and direction are replicated
     f64 = dict(dtype=torch.float64, device="cuda")
@@ -291,12 +293,17 @@ def run_ours(args):
         "metric": "gradient+Hv images/sec", "value": value, "unit": "images/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f64" if args.precision == "fp64" else args.precision, "data": "synthetic",
         "config": {"workload": WORKLOAD, "per_gpu_batch": n, "global_batch": n * world,
                    "parallelism": "dp%d" % world, "activation": "swish", "batch_norm": True,
                    "l2": "inputs larger than L2 (z/dx/rz are 1.85 GiB each per GPU)",
                    "algorithmic_mflop_per_image": {"gradient": gpi / 1e6, "hv": hpi / 1e6}},
-        "roofline": {"bound": "tensor", "kernel": "conv_tma_kernel (TMA-fed implicit-GEMM fprop/dgrad, fp64 DMMA; gather kernel for layer 0)",
+        "roofline": {"bound": "tensor",
+                     "kernel": "conv_tma_kernel (TMA-fed implicit-GEMM fprop/dgrad, fp64 DMMA; gather kernel for layer 0)"
+                     if args.precision == "fp64" else
+                     "conv_tf32_kernel (tcgen05 %s fprop/dgrad; fp64 kernels for layer 0 and the weight "
+                     "gradients; shown against the fp64 DGEMM peak for comparison with the default mode)"
+                     % args.precision,
                      "achieved": achieved, "peak": dgemm_tflops, "unit": "TFLOP/s",
                      "frac": (achieved / dgemm_tflops) if achieved else None,
                      "peak_source": "cuBLAS DGEMM 8192^3 measured in this run (MEASURED_PEAKS.json has no fp64 figure)",
@@ -452,6 +459,10 @@ def main():
     ap.add_argument("--per-gpu-batch", type=int, default=PER_GPU_BATCH,
                     help="images per GPU (default 512, the benchmark shape; smaller values are "
                          "for profiler captures only)")
+    ap.add_argument("--precision", default="fp64", choices=["fp64", "tf32", "tf32x3"],
+                    help="fp64 = the reference's arithmetic (default, the benchmark); tf32 / tf32x3 = "
+                         "the opt-in tcgen05 modes (one TF32 product / error-compensated three), "
+                         "reported under their own dtype and never as the headline")
     ap.add_argument("--skip-cpu", action="store_true",
                     help="leave the CPU baseline leg out (profiling runs)")
     args = ap.parse_args()

@@ -71,6 +71,12 @@ class Context:
     def set_reference_softmax(self, on):
         self.check(self.lib.fitre_set_reference_softmax(self.h, int(bool(on))))
 
+    def set_precision(self, precision):
+        """0 = fp64 (reference arithmetic); opt-in tcgen05 modes for the convolution products:
+        1 = one TF32 product (loss within 1e-3, deep-net gradients only within 1e-1),
+        2 = error-compensated 3 x TF32 (gradient and Hv within 1e-3 of fp64)."""
+        self.check(self.lib.fitre_set_precision(self.h, int(precision)))
+
     def set_tma(self, on):
         self.check(self.lib.fitre_set_tma(self.h, int(bool(on))))
 

@@ -137,6 +137,14 @@ int fitre_set_reference_softmax(fitre_context *ctx, int on) {
     return FITRE_OK;
 }
 
+int fitre_set_precision(fitre_context *ctx, int precision) {
+    if (!ctx || (precision != FITRE_PRECISION_FP64 && precision != FITRE_PRECISION_TF32 &&
+                 precision != FITRE_PRECISION_TF32X3))
+        return FITRE_ERR_BAD_ARG;
+    ctx->precision = precision;
+    return FITRE_OK;
+}
+
 int fitre_set_tma(fitre_context *ctx, int on) {
     if (!ctx) return FITRE_ERR_BAD_ARG;
     ctx->use_tma = on != 0;

@@ -47,6 +47,7 @@ struct fitre_context {
     long long launches = 0;
     std::string err;
     int ref_softmax = 1;
+    int precision = 0;          // FITRE_PRECISION_* (convolution products)
     bool use_tma = true;        // TMA-fed convolution kernels where shape and alignment allow
     double *pinned = nullptr;   // 256 pinned host doubles (scalar read-back)
     double *dscal = nullptr;    // 4096 device doubles (scalar reductions)
@@ -147,6 +148,11 @@ bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const dou
 long conv_wgrad_tma_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
 bool conv_wgrad_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
                     int H, int W, int k, int pad, int Cout, double *partials);
+// conv_tf32.cu
+void conv_tf32_init_attributes();
+long conv_fprop_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
+bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
+                     int N, int Cin, int H, int W, int k, int pad, int Cout, double *scratch);
 // Device-side error word (set by a kernel whose bounded wait ran out): dscal[4000] as int.
 void check_device_error(fitre_context *ctx);
 

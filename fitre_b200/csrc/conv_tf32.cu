@@ -1,0 +1,419 @@
+// Opt-in reduced-precision convolution (forward / data-gradient shape): TF32 operands, FP32
+// accumulation on the 5th-generation tensor cores (tcgen05.mma, accumulator in TMEM).
+//
+// The tensors stay fp64 in HBM (the reference's `real`); precision is reduced only inside the
+// product:
+//   * warp 0 (one lane) is the TMA producer: per K-chunk of 32 im2col columns it fetches the raw
+//     fp64 input patch of the CTA's 128 output positions (same box as the fp64 kernel) and the
+//     32 x 64 slab of the weight matrix, which a small pre-pass has rounded to TF32 and which
+//     lands in shared memory in the 128-byte-swizzled K-major layout tcgen05 reads;
+//   * warps 2-9 expand the patch into the A operand: each thread owns half an output position's row,
+//     gathers its 16 im2col values from the patch (rowbase(m) + offset(q)), rounds them to TF32
+//     and writes them into the same swizzled K-major layout (fence.proxy.async, then arrive);
+//   * warp 1 (one lane) issues tcgen05.mma (M 128, N 64, K 8; four per chunk) and commits each
+//     stage back to the producer; the last commit releases the epilogue;
+//   * warps 2-9 read the 128 x 64 fp32 accumulator with tcgen05.ld, widen to fp64, add the bias
+//     and store (or write a split-K slab).
+// X3 = true is the error-compensated variant: every operand is split into a TF32 head and a TF32
+// tail (x = hi + lo, about 22 mantissa bits together) and the product is accumulated as
+// lo*hi + hi*lo + hi*hi, three tensor-core products per K step.  A single TF32 product carries a
+// relative error near 3e-4 per convolution, which batch normalisation and the backward sweep of a
+// deep net amplify a hundredfold; the compensated form stays near 1e-6 per convolution.
+// Every mbarrier wait is bounded; on a time-out the CTA sets the error word, still frees its
+// TMEM columns and returns.  No cluster launch, no multicast.
+#include <algorithm>
+
+#include "common.h"
+#include "tma_util.cuh"
+
+namespace fitre {
+namespace {
+
+constexpr int F_BM = 128, F_BN = 64, F_KC = 32, F_THREADS = 320, F_STAGES_MAX = 4;
+constexpr int F_ABYTES = F_BM * F_KC * 4, F_BBYTES = F_BN * F_KC * 4;
+constexpr int F_TMEM_COLS = 64;
+constexpr int kSmemHalf = 100 * 1024;   // two CTAs per SM
+constexpr int kSmemFull = 200 * 1024;   // one CTA per SM
+
+struct alignas(64) Tf32ConvArgs {
+    CUtensorMap xmap[2];
+    CUtensorMap wmap[2];
+    const double *bias;
+    double *y;
+    int *err;
+    long M;
+    int nseg, N, Cout, CoutPad, K, Ho, Wo, pad, TW, TN, HB, WB, xoff, x0, CBP, nchunks, stages, tilesW;
+    int patchBytes, iters_per_split;
+};
+
+__device__ __forceinline__ uint32_t f32_to_tf32(float f) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(f));
+    return r;
+}
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused here)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset
+    d |= (uint64_t)1 << 46;                               // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+    return d;
+}
+// instruction descriptor: D fp32, A/B tf32, both K-major, N = 64, M = 128
+constexpr uint32_t kIdescTf32 = (1u << 4) | (2u << 7) | (2u << 10) | ((F_BN >> 3) << 17) | ((F_BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int KS, bool X3>
+__global__ void __launch_bounds__(F_THREADS, X3 ? 1 : 2)
+conv_tf32_kernel(const __grid_constant__ Tf32ConvArgs p) {
+    constexpr int KK = KS * KS;
+    constexpr int NP = X3 ? 2 : 1;                       // operand parts: head (and tail)
+    constexpr int OPBYTES = NP * (F_ABYTES + F_BBYTES);  // A head [A tail] B head [B tail]
+    extern __shared__ unsigned char smraw[];
+    unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 1023) & ~(uintptr_t)1023);
+    const int stageBytes = OPBYTES + p.patchBytes;   // all multiples of 1024
+    unsigned long long *bars = (unsigned long long *)(sm + (size_t)p.stages * stageBytes);
+    // bars: [0,4) patch full, [4,8) weights full, [8,12) A ready, [12,16) stage consumed, [16] accumulator
+    uint32_t *tmem_slot = (uint32_t *)(bars + 17);
+    __shared__ int abort_flag;
+    volatile int *vabort = &abort_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wt = blockIdx.x % p.tilesW, nt = blockIdx.x / p.tilesW;
+    const int w0 = wt * p.TW, n0 = nt * p.TN;
+    const int c0 = blockIdx.y * F_BN;
+    const int it0 = blockIdx.z * p.iters_per_split;
+    const int iters = max(0, min(p.nseg * p.nchunks - it0, p.iters_per_split));
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(bars + s), 1);
+            mbar_init(smem_u32(bars + 4 + s), 1);
+            mbar_init(smem_u32(bars + 8 + s), 256);
+            mbar_init(smem_u32(bars + 12 + s), 1);
+        }
+        mbar_init(smem_u32(bars + 16), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)), "r"(F_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const uint32_t patchTx = (uint32_t)(p.HB * p.WB * p.TN * p.CBP * 8);
+            for (int it = 0; it < iters; ++it) {
+                const int s = it % p.stages, fill = it / p.stages;
+                if (fill > 0 && !mbar_wait(smem_u32(bars + 12 + s), (uint32_t)((fill - 1) & 1))) {
+                    *vabort = 1;
+                    break;
+                }
+                if (*vabort) break;
+                const int g = it0 + it, seg = g / p.nchunks, ch = g - seg * p.nchunks;
+                unsigned char *st = sm + (size_t)s * stageBytes;
+                const uint32_t bp = smem_u32(bars + s), bw = smem_u32(bars + 4 + s);
+                mbar_expect_tx(bp, patchTx);
+                tma_load_4d(smem_u32(st + OPBYTES), &p.xmap[seg], bp, p.x0, w0 - p.pad, n0,
+                            (ch * F_KC) / KK);
+                mbar_expect_tx(bw, NP * F_BBYTES);
+                // head and tail of the weights are stacked along the channel axis of one map
+                for (int part = 0; part < NP; ++part)
+                    tma_load_2d(smem_u32(st + NP * F_ABYTES + part * F_BBYTES), &p.wmap[seg], bw, ch * F_KC,
+                                c0 + part * p.CoutPad);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            for (int it = 0; it < iters; ++it) {
+                const int s = it % p.stages;
+                const uint32_t par = (uint32_t)((it / p.stages) & 1);
+                if (*vabort || !mbar_wait(smem_u32(bars + 4 + s), par) ||
+                    !mbar_wait(smem_u32(bars + 8 + s), par)) {
+                    *vabort = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char *st = sm + (size_t)s * stageBytes;
+                const uint64_t da = umma_desc_sw128(smem_u32(st));
+                const uint64_t db = umma_desc_sw128(smem_u32(st + NP * F_ABYTES));
+                constexpr uint64_t kATail = F_ABYTES >> 4, kBTail = F_BBYTES >> 4;
+#pragma unroll
+                for (int k = 0; k < F_KC / 8; ++k) {  // 8 tf32 = 32 bytes = 2 descriptor units per step
+                    const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+                    if (X3) {
+                        umma_tf32(tmem_base, da + kATail + 2 * k, db + 2 * k, kIdescTf32, acc);   // lo * hi
+                        umma_tf32(tmem_base, da + 2 * k, db + kBTail + 2 * k, kIdescTf32, 1u);    // hi * lo
+                        umma_tf32(tmem_base, da + 2 * k, db + 2 * k, kIdescTf32, 1u);             // hi * hi
+                    } else {
+                        umma_tf32(tmem_base, da + 2 * k, db + 2 * k, kIdescTf32, acc);
+                    }
+                }
+                umma_commit(smem_u32(bars + 12 + s));
+            }
+            if (!*vabort) umma_commit(smem_u32(bars + 16));
+        }
+    } else {
+        // ---------------- expanders (A operand) and epilogue: 256 threads, half a row each ----------------
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const int hf = (warp - 2) >> 2;         // which half of the chunk's columns / of the 64 channels
+        const int ml = q * 32 + lane;           // row of the tile = output position
+        const int ho = ml % p.Ho, r = ml / p.Ho;
+        const int wl = r % p.TW, nl = r / p.TW;
+        const int rowbase = (nl * p.WB + wl) * p.HB + ho + p.xoff;
+        const int chanStride = p.TN * p.WB * p.HB;
+        const uint32_t a_row = (uint32_t)((ml >> 3) * 1024 + (ml & 7) * 128);
+        for (int it = 0; it < iters; ++it) {
+            const int s = it % p.stages;
+            if (*vabort || !mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1))) {
+                *vabort = 1;
+                break;
+            }
+            unsigned char *st = sm + (size_t)s * stageBytes;
+            const double *patch = (const double *)(st + OPBYTES) + rowbase;
+            const int g = it0 + it, ch = g % p.nchunks;
+            const int qq = ch * F_KC;
+            const int cbase = qq / KK;           // first channel of the chunk = channel 0 of the patch
+            const int q0 = qq + hf * (F_KC / 2); // this thread's first im2col column
+            int cc = q0 / KK, rem = q0 - cc * KK;
+            cc -= cbase;
+            int j = rem / KS, i = rem - j * KS;
+#pragma unroll
+            for (int grp = 0; grp < F_KC / 8; ++grp) {
+                uint32_t v[4], t[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const double x = patch[cc * chanStride + j * p.HB + i];
+                    v[e] = f32_to_tf32(__double2float_rn(x));
+                    if (X3) t[e] = f32_to_tf32(__double2float_rn(x - (double)__uint_as_float(v[e])));
+                    if (++i == KS) {
+                        i = 0;
+                        if (++j == KS) {
+                            j = 0;
+                            ++cc;
+                        }
+                    }
+                }
+                const uint32_t off = a_row + (uint32_t)(((hf * 4 + grp) ^ (ml & 7)) << 4);
+                *reinterpret_cast<uint4 *>(st + off) = make_uint4(v[0], v[1], v[2], v[3]);
+                if (X3) *reinterpret_cast<uint4 *>(st + F_ABYTES + off) = make_uint4(t[0], t[1], t[2], t[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(bars + 8 + s));
+        }
+        // ---------------- epilogue ----------------
+        if (!*vabort && iters > 0 && mbar_wait(smem_u32(bars + 16), 0)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool ok = (n0 + nl) < p.N && (w0 + wl) < p.Wo && nl < p.TN;
+            const long grow = ok ? ((long)(n0 + nl) * p.Wo + (w0 + wl)) * p.Ho + ho : -1;
+            double *y = p.y + (long)blockIdx.z * p.M * p.Cout;
+            uint32_t rr[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(hf * 32), rr);
+            if (grow >= 0) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int col = c0 + hf * 32 + c;
+                    if (col < p.Cout)
+                        y[(long)col * p.M + grow] =
+                            (double)__uint_as_float(rr[c]) + (p.bias ? p.bias[col] : 0.0);
+                }
+            }
+        } else if (iters > 0) {
+            *vabort = 1;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(F_TMEM_COLS)
+                     : "memory");
+    }
+    if (tid == 0 && abort_flag) atomicExch(p.err, 2);
+}
+
+// fp64 weights (K x Cout column-major = K contiguous per channel) -> TF32-rounded fp32 in the same
+// element order; with parts == 2 the TF32 tails follow at channel offset CoutPad, and the padding
+// channels of both halves are zero.
+__global__ void split_weights_tf32_kernel(const double *in, float *out, int K, int Cout, int CoutPad,
+                                          int parts) {
+    const long n = (long)K * (parts == 2 ? CoutPad : Cout);
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const bool live = i < (long)K * Cout;
+        const double w = live ? in[i] : 0.0;
+        const float hi = __uint_as_float(f32_to_tf32(__double2float_rn(w)));
+        out[i] = hi;
+        if (parts == 2)
+            out[(long)K * CoutPad + i] = __uint_as_float(f32_to_tf32(__double2float_rn(w - (double)hi)));
+    }
+}
+
+__global__ void reduce_out_slabs_tf32_kernel(const double *slabs, double *y, long M, int Cout, int SK,
+                                             const double *bias) {
+    const long n = M * Cout;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        double s = 0.0;
+        for (int k = 0; k < SK; ++k) s += slabs[(long)k * n + i];
+        if (bias) s += bias[i / M];
+        y[i] = s;
+    }
+}
+
+}  // namespace
+
+void conv_tf32_init_attributes() {
+    FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_kernel<5, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+}
+
+namespace {
+int tf32_split(long M, int Cout, int iters) {
+    const long tiles = ((M + F_BM - 1) / F_BM) * ((Cout + F_BN - 1) / F_BN);
+    if (tiles >= 296) return 1;
+    return (int)std::max<long>(1, std::min<long>(std::min<long>((592 + tiles - 1) / tiles, 8), iters / 8));
+}
+inline long cout_pad(int Cout) { return ((long)Cout + F_BN - 1) / F_BN * F_BN; }
+}  // namespace
+
+// doubles of scratch: split-K slabs (small grids only) + the TF32 heads and tails of two weight
+// matrices (2 segments x 2 parts x K x CoutPad floats)
+long conv_fprop_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    const long K = (long)Cin * k * k, M = (long)N * Ho * Wo;
+    const int sk = tf32_split(M, Cout, 2 * (int)((K + F_KC - 1) / F_KC));
+    return (sk > 1 ? sk * M * Cout : 0) + 2 * K * cout_pad(Cout) + 64;
+}
+
+bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
+                     int N, int Cin, int H, int W, int k, int pad, int Cout, double *scratch) {
+    if (!encode_fn() || !scratch) return false;
+    if (k != 3 && k != 5) return false;
+    const bool x3 = ctx->precision == FITRE_PRECISION_TF32X3;
+    const int parts = x3 ? 2 : 1;
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    const int K = Cin * k * k;
+    if (Ho < 1 || Wo < 1 || (H & 1) || (K & 3) || K < F_KC) return false;
+    for (int s = 0; s < nseg; ++s)
+        if ((uintptr_t)segs[s].x & 15) return false;
+    int TW, TN;
+    if (Ho * Wo >= F_BM) {
+        if (F_BM % Ho) return false;
+        TW = F_BM / Ho;
+        TN = 1;
+    } else {
+        if (F_BM % (Ho * Wo)) return false;
+        TW = Wo;
+        TN = F_BM / (Ho * Wo);
+    }
+    Tf32ConvArgs a{};
+    const int padE = pad + (pad & 1);
+    a.x0 = -padE;
+    a.xoff = padE - pad;
+    a.HB = (H + pad + padE + 1) & ~1;
+    a.WB = TW + k - 1;
+    a.CBP = (k == 3) ? 5 : 3;  // channels a run of 32 im2col columns can touch
+    if (a.HB > 256 || a.WB > 256 || TN > 256) return false;
+    a.patchBytes = (a.HB * a.WB * TN * a.CBP * 8 + 1023) & ~1023;
+    const int stageBytes = parts * (F_ABYTES + F_BBYTES) + a.patchBytes;
+    const int fixed = 1024 + 17 * 8 + 16;
+    int stages = x3 ? 0 : (kSmemHalf - fixed) / stageBytes;     // two CTAs per SM when they fit
+    if (stages < 2) stages = (kSmemFull - fixed) / stageBytes;  // else one
+    if (stages < 2) return false;
+    a.stages = std::min(stages, F_STAGES_MAX);
+    a.nchunks = (K + F_KC - 1) / F_KC;
+    a.nseg = nseg;
+    a.N = N; a.Cout = Cout; a.K = K; a.Ho = Ho; a.Wo = Wo; a.pad = pad; a.TW = TW; a.TN = TN;
+    a.CoutPad = (int)cout_pad(Cout);
+    a.tilesW = (Wo + TW - 1) / TW;
+    a.M = (long)N * Ho * Wo;
+    a.err = (int *)(ctx->dscal + 4000);
+    // split-K for small grids (same rule of thumb as the fp64 kernel, fewer CTAs needed)
+    const int iters = nseg * a.nchunks;
+    const int sk_max = tf32_split(a.M, Cout, 2 * a.nchunks);   // what the scratch was sized for
+    int SK = std::min(sk_max, tf32_split(a.M, Cout, iters));
+    a.iters_per_split = (iters + SK - 1) / SK;
+    SK = (iters + a.iters_per_split - 1) / a.iters_per_split;
+    double *slabs = scratch;
+    float *w32 = (float *)(scratch + (sk_max > 1 ? (long)sk_max * a.M * Cout : 0));
+    a.y = SK > 1 ? slabs : y;
+    a.bias = SK > 1 ? nullptr : bias;
+    for (int s = 0; s < nseg; ++s) {
+        float *ws = w32 + (long)s * 2 * K * a.CoutPad;
+        const long n = (long)K * a.CoutPad;
+        split_weights_tf32_kernel<<<(int)std::min<long>((n + 255) / 256, 1184), 256, 0, ctx->stream>>>(
+            segs[s].w, ws, K, Cout, a.CoutPad, parts);
+        check_launch(ctx, "split_weights_tf32_kernel");
+        cuuint64_t xd[4] = {(cuuint64_t)H, (cuuint64_t)W, (cuuint64_t)N, (cuuint64_t)Cin};
+        cuuint64_t xs[3] = {(cuuint64_t)H * 8, (cuuint64_t)H * W * 8, (cuuint64_t)H * W * N * 8};
+        cuuint32_t xb[4] = {(cuuint32_t)a.HB, (cuuint32_t)a.WB, (cuuint32_t)TN, (cuuint32_t)a.CBP};
+        if (!encode(&a.xmap[s], segs[s].x, 4, xd, xs, xb)) return false;
+        cuuint64_t wd[2] = {(cuuint64_t)K, (cuuint64_t)(x3 ? 2 * a.CoutPad : Cout)};
+        cuuint64_t wsb[1] = {(cuuint64_t)K * 4};
+        cuuint32_t wb[2] = {(cuuint32_t)F_KC, (cuuint32_t)F_BN};
+        if (!encode(&a.wmap[s], ws, 2, wd, wsb, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_DATA_TYPE_FLOAT32))
+            return false;
+    }
+    const int tilesN = (N + TN - 1) / TN;
+    dim3 grid((unsigned)(a.tilesW * tilesN), (unsigned)((Cout + F_BN - 1) / F_BN), (unsigned)SK);
+    const int smem = a.stages * stageBytes + fixed;
+    {
+        ProfScope prof(ctx, PROF_CONV_IGEMM, 2.0 * (double)a.M * K * Cout * nseg);
+        if (k == 3 && x3)
+            conv_tf32_kernel<3, true><<<grid, F_THREADS, smem, ctx->stream>>>(a);
+        else if (k == 3)
+            conv_tf32_kernel<3, false><<<grid, F_THREADS, smem, ctx->stream>>>(a);
+        else if (x3)
+            conv_tf32_kernel<5, true><<<grid, F_THREADS, smem, ctx->stream>>>(a);
+        else
+            conv_tf32_kernel<5, false><<<grid, F_THREADS, smem, ctx->stream>>>(a);
+        check_launch(ctx, "conv_tf32_kernel");
+        if (SK > 1) {
+            const long n = a.M * Cout;
+            reduce_out_slabs_tf32_kernel<<<(int)std::min<long>((n + 255) / 256, 1184), 256, 0, ctx->stream>>>(
+                slabs, y, a.M, Cout, SK, bias);
+            check_launch(ctx, "reduce_out_slabs_tf32_kernel");
+        }
+    }
+    return true;
+}
+
+}  // namespace fitre

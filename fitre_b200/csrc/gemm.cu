@@ -688,16 +688,20 @@ int split_count(long tiles, long reduce_len, long min_len) {
 }  // namespace
 
 long conv_fprop_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
-    return conv_fprop_tma_scratch(N, Cin, H, W, k, pad, Cout);
+    return std::max(conv_fprop_tma_scratch(N, Cin, H, W, k, pad, Cout),
+                    conv_fprop_tf32_scratch(N, Cin, H, W, k, pad, Cout));
 }
 long conv_dgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
     // the data gradient is a convolution of the errors: Cout input channels, Cin outputs
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
-    return conv_fprop_tma_scratch(N, Cout, Ho, Wo, k, k - 1 - pad, Cin);
+    return conv_fprop_scratch(N, Cout, Ho, Wo, k, k - 1 - pad, Cin);
 }
 
 void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
                 int N, int Cin, int H, int W, int k, int pad, int Cout, double *split) {
+    if (ctx->precision != FITRE_PRECISION_FP64 &&
+        conv_fprop_tf32(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout, split))
+        return;
     if (ctx->use_tma && conv_fprop_tma(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout, split)) return;
     ConvArgs a{};
     for (int s = 0; s < nseg; ++s) {
@@ -869,6 +873,7 @@ void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int 
 
 void gemm_init_attributes() {
     conv_tma_init_attributes();
+    conv_tf32_init_attributes();
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));

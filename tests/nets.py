@@ -68,13 +68,13 @@ def vgg_small(batch, act=S.CNN_ACT_SWISH, bn=True, bias=False, hw=8, classes=10)
     return S.describe_model(convs, fcs, batch, bias)
 
 
-def vgg11(batch, act=S.CNN_ACT_SWISH, bn=True, bias=False, hw=32, classes=10):
+def vgg11(batch, act=S.CNN_ACT_SWISH, bn=True, bias=False, hw=32, classes=10, pool=S.MAX_POOL):
     chans = [(3, 64, True), (64, 128, True), (128, 256, False), (256, 256, True),
              (256, 512, False), (512, 512, True), (512, 512, False), (512, 512, True)]
     convs, s = [], hw
     for cin, cout, pooled in chans:
         convs.append(dict(cin=cin, cout=cout, h=s, w=s, k=3, pad=1, bn=bn, act=act,
-                          pool=(S.MAX_POOL, 2, 2, 0) if pooled else None))
+                          pool=(pool, 2, 2, 0) if pooled else None))
         if pooled:
             s //= 2
     fcs = [(512 * s * s, classes, S.CNN_ACT_NONE)]

@@ -351,3 +351,35 @@ def test_cuda_matrix_inverse_blocked_sizes_and_failure():
         api.computeMatrixInverse(c, G.dev(-np.eye(70).reshape(-1)), G.dev(np.zeros(4900)), 70,
                                  G.dev(np.zeros(L.fitre_kfac_inverse_mem_required(70))), 0.0, 0.0)
     assert e.value.status == S.ERR_NOT_CONVERGED
+
+
+def test_cuda_reduced_precision_modes_within_stated_tolerance():
+    """Opt-in modes: convolution forward / data-gradient products on the tcgen05 tensor cores
+    (fp32 accumulation), everything else fp64.  Stated tolerances against the fp64 oracle,
+    relative and norm-wise:
+      mode 2 (error-compensated 3 x TF32): 1e-3 for loss, gradient and Hessian-vector product;
+      mode 1 (one TF32 product): 1e-3 for the loss, 1e-1 for gradient and Hessian-vector
+      product (batch norm and the backward sweep amplify the 3e-4 rounding of each product)."""
+    import gpu_util as G
+    TOL = {2: (1e-3, 1e-3), 1: (1e-3, 1e-1)}
+    c = G.ctx()
+    try:
+        for model, n in ((nets.vgg_small(6), 6), (nets.alexnet_small(8, ch=8), 8), (nets.vgg11(8), 8)):
+            O.finalize(model)
+            x, y, w, v, ncls = G.synth(model, n, seed=17)
+            st = O.gradient(model, x, y, w, ncls, n)
+            hv_o = O.hv(model, x, w, ncls, n, st, v)
+            for mode in (2, 1):
+                tol_loss, tol_grad = TOL[mode]
+                c.set_precision(mode)
+                run = G.GpuRun(model, x, y, w, ncls)
+                hv = run.hv(v)
+                eg, eh = G.rel(run.gradient, st.gradient), G.rel(hv, hv_o)
+                assert abs(run.loss - st.loss) <= tol_loss * abs(st.loss), (mode, run.loss, st.loss)
+                assert eg < tol_grad and eh < tol_grad, (mode, eg, eh)
+                # the mode really is reduced precision on these nets (not a silent fp64 fallback)
+                assert eg > 1e-11, (mode, eg)
+                c.set_precision(0)
+                del run
+    finally:
+        c.set_precision(0)
