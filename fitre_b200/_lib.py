@@ -27,6 +27,10 @@ SYMBOLS = [
     "fitre_kfac_lambda_delta", "fitre_kfac_inverse_mem_required", "fitre_kfac_matrix_inverse",
     "fitre_kfac_natural_gradient_mem_required", "fitre_compute_natural_gradient",
     "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host",
+    "fitre_init_batch_norm_data", "fitre_evaluate_cnn_model", "fitre_compute_accuracy",
+    "fitre_prepare_minibatch", "fitre_generalization_mem_required",
+    "fitre_compute_generalization_errors", "fitre_trust_region_kfac_mem_required",
+    "fitre_subsampled_trust_region_kfac", "fitre_write_vector", "fitre_read_vector",
 ]
 
 _lib = None
@@ -92,5 +96,17 @@ def load():
     sig("fitre_compute_natural_gradient", i, vp, MP, C.POINTER(S.KFAC_INFO), vp, vp, vp, vp, vp)
     sig("fitre_syrk_tn_static_scratch", i, vp, l, i, l, d, vp, vp)
     sig("fitre_gradient_hv_host", i, vp, MP, vp, vp, vp, vp, i, i, d, dbl_p, vp, vp)
+    sig("fitre_init_batch_norm_data", i, vp, MP, vp)
+    sig("fitre_evaluate_cnn_model", i, vp, MP, DP, SP, vp, vp, vp, i, i, dbl_p)
+    sig("fitre_compute_accuracy", i, vp, vp, vp, i, i, dbl_p, dbl_p)
+    sig("fitre_prepare_minibatch", i, vp, MP, DP, vp, vp, vp, l, i, vp)
+    sig("fitre_generalization_mem_required", l, MP)
+    sig("fitre_compute_generalization_errors", i, vp, MP, DP, SP, vp, vp, vp, i, dbl_p, dbl_p)
+    sig("fitre_trust_region_kfac_mem_required", l, MP, DP)
+    sig("fitre_subsampled_trust_region_kfac", i, vp, MP, DP, C.POINTER(S.KFAC_INFO),
+        C.POINTER(S.TRUST_REGION_PARAMS), SP, C.c_ulonglong, i, i, C.POINTER(S.TR_STEP), i,
+        C.POINTER(S.TR_EPOCH))
+    sig("fitre_write_vector", i, C.c_char_p, vp, l, i)
+    sig("fitre_read_vector", i, C.c_char_p, vp, l, C.POINTER(C.c_long))
     _lib = L
     return L

@@ -95,6 +95,34 @@ class KFAC_INFO(C.Structure):
         ("LambdaGOffsets", C.c_int * MAX_LAYERS),
         ("OmegaZSize", C.c_int), ("LambdaGSize", C.c_int),
         ("regLambda", C.c_double), ("dampGamma", C.c_double),
+        ("stats_decay", C.c_double), ("momentum", C.c_double),
+        ("checkGrad", C.c_int), ("inverseFreq", C.c_int),
+    ]
+
+
+class TRUST_REGION_PARAMS(C.Structure):  # solvers/params.h:11-33
+    _fields_ = [
+        ("delta", C.c_double), ("minDelta", C.c_double), ("maxDelta", C.c_double),
+        ("eta1", C.c_double), ("eta2", C.c_double), ("gamma1", C.c_double), ("gamma2", C.c_double),
+        ("maxProps", C.c_ulong), ("maxMatVecs", C.c_int), ("maxEpochs", C.c_int),
+        ("maxIters", C.c_int), ("hessianType", C.c_int), ("alpha", C.c_double),
+        ("curIteration", C.c_int), ("hs", C.c_double), ("lambda_", C.c_double),
+    ]
+
+
+class TR_STEP(C.Structure):
+    _fields_ = [
+        ("trainLikelihood", C.c_double), ("newTrainLikelihood", C.c_double),
+        ("newTrainAccuracy", C.c_double), ("modelKfac", C.c_double), ("modelGradient", C.c_double),
+        ("rho", C.c_double), ("delta", C.c_double), ("usedKfac", C.c_int), ("reverted", C.c_int),
+    ]
+
+
+class TR_EPOCH(C.Structure):
+    _fields_ = [
+        ("testLikelihood", C.c_double), ("testAccuracy", C.c_double),
+        ("trainLikelihood", C.c_double), ("trainAccuracy", C.c_double),
+        ("seconds", C.c_double), ("miniBatches", C.c_int),
     ]
 
 

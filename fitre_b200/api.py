@@ -306,3 +306,103 @@ class Workspace:
         self.extra = 4 * (model.pSize + 32) + 64
         self.dev = torch.zeros(need + self.extra, **f64)
         self.scratch = make_scratch(self.dev)
+
+
+# ---- training-loop pieces either side of the path -------------------------------------------
+
+def make_full_dataset(weights, trainX, trainY, testX, testY, numClasses, features, batchSize,
+                      datasetType=10):
+    """DEVICE_DATASET over whole train / test sets (features x samples, column per image, as the
+    reference stores them) with the sampled-batch buffers allocSampledDataset would provide."""
+    import torch
+    d = S.DEVICE_DATASET()
+    d.weights = weights.data_ptr()
+    d.trainSetX, d.trainSetY = trainX.data_ptr(), trainY.data_ptr()
+    d.trainSizeX = d.trainSizeY = int(trainY.numel())
+    if testX is not None:
+        d.testSetX, d.testSetY = testX.data_ptr(), testY.data_ptr()
+        d.testSizeX = d.testSizeY = int(testY.numel())
+    d.numClasses, d.features, d.datasetType = int(numClasses), int(features), int(datasetType)
+    sx = torch.zeros(2 * batchSize * features, dtype=torch.float64, device=weights.device)
+    sy = torch.zeros(batchSize, dtype=torch.float64, device=weights.device)
+    d.sampledTrainX, d.sampledTrainY = sx.data_ptr(), sy.data_ptr()
+    d.currentBatch = sx.data_ptr()
+    d.sampleSize = int(batchSize)
+    d._keep = (weights, trainX, trainY, testX, testY, sx, sy)
+    return d
+
+
+def initBatchNormData(ctx, model, z):
+    ctx.check(ctx.lib.fitre_init_batch_norm_data(ctx.h, C.byref(model), z.data_ptr()))
+
+
+def cnnForwardEval(ctx, model, data, scratch, z, probs, errors, curBatchSize, evalType):
+    """cnnForward with an explicit EVAL_TYPE (10 train, 20 / 30 accuracy modes)."""
+    loss = C.c_double()
+    ctx.check(ctx.lib.fitre_cnn_forward(ctx.h, C.byref(model), C.byref(data), C.byref(scratch),
+                                        z.data_ptr(), probs.data_ptr(), errors.data_ptr(), 0,
+                                        int(curBatchSize), int(evalType), C.byref(loss)))
+    return loss.value
+
+
+def evaluateCNNModel(ctx, model, data, scratch, z, probs, lossFuncErrors, offset, curBatchSize):
+    loss = C.c_double()
+    ctx.check(ctx.lib.fitre_evaluate_cnn_model(ctx.h, C.byref(model), C.byref(data), C.byref(scratch),
+                                               z.data_ptr(), probs.data_ptr(),
+                                               lossFuncErrors.data_ptr(), int(offset),
+                                               int(curBatchSize), C.byref(loss)))
+    return loss.value
+
+
+def computeAccuracy(ctx, probs, target, rows, numClasses):
+    """Returns (hits, percent)."""
+    hits, acc = C.c_double(), C.c_double()
+    ctx.check(ctx.lib.fitre_compute_accuracy(ctx.h, probs.data_ptr(), target.data_ptr(), int(rows),
+                                             int(numClasses), C.byref(hits), C.byref(acc)))
+    return hits.value, acc.value
+
+
+def prepareMinibatch(ctx, model, data, setX, setY, indices, offset, n, uniforms=None):
+    ctx.check(ctx.lib.fitre_prepare_minibatch(
+        ctx.h, C.byref(model), C.byref(data), setX.data_ptr(), setY.data_ptr(),
+        indices.data_ptr() if indices is not None else None, int(offset), int(n),
+        uniforms.data_ptr() if uniforms is not None else None))
+
+
+def computeGeneralizationErrors(ctx, model, data, scratch, z, probs, errors, evalType):
+    """Returns (likelihood, accuracy percent) over the test (30) or train (20) set."""
+    lik, acc = C.c_double(), C.c_double()
+    ctx.check(ctx.lib.fitre_compute_generalization_errors(
+        ctx.h, C.byref(model), C.byref(data), C.byref(scratch), z.data_ptr(), probs.data_ptr(),
+        errors.data_ptr(), int(evalType), C.byref(lik), C.byref(acc)))
+    return lik.value, acc.value
+
+
+def subsampledTrustRegionKFAC(ctx, model, data, kfacInfo, trParams, scratch, seed=1, enableDA=1,
+                              maxMiniBatches=0, stepsCap=0):
+    """Runs the FITRE loop; returns (steps, epochs) as lists of TR_STEP / TR_EPOCH."""
+    steps = (S.TR_STEP * max(stepsCap, 1))()
+    epochs = (S.TR_EPOCH * max(trParams.maxIters, 1))()
+    ctx.check(ctx.lib.fitre_subsampled_trust_region_kfac(
+        ctx.h, C.byref(model), C.byref(data), C.byref(kfacInfo), C.byref(trParams), C.byref(scratch),
+        int(seed), int(enableDA), int(maxMiniBatches), steps, int(stepsCap), epochs))
+    n = min(stepsCap, trParams.curIteration)
+    return list(steps[:n]), list(epochs[:trParams.maxIters])
+
+
+def writeVector(path, host_array, referenceFormat=0):
+    import numpy as np
+    a = np.ascontiguousarray(host_array, dtype=np.float64)
+    rc = _lib.load().fitre_write_vector(str(path).encode(), a.ctypes.data, a.size, int(referenceFormat))
+    if rc:
+        raise OSError("fitre_write_vector failed for %s" % path)
+
+
+def readVector(path, n):
+    import numpy as np
+    a = np.zeros(n)
+    got = C.c_long()
+    rc = _lib.load().fitre_read_vector(str(path).encode(), a.ctypes.data, n, C.byref(got))
+    if rc:
+        raise OSError("fitre_read_vector failed for %s" % path)
+    return a[:got.value]

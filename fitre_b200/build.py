@@ -11,7 +11,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["gemm.cu", "conv_tma.cu", "conv_tf32.cu", "layers.cu", "passes.cu", "kfac.cu", "model.cpp", "comm.cpp", "cabi.cpp"]
+SOURCES = ["gemm.cu", "conv_tma.cu", "conv_tf32.cu", "layers.cu", "passes.cu", "kfac.cu", "training.cu", "model.cpp", "comm.cpp", "cabi.cpp"]
 LIB = os.path.join(HERE, "libfitre_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

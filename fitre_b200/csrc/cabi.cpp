@@ -221,10 +221,13 @@ int fitre_cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
     return guarded(ctx, [&] {
         require_ptrs({m, data, scratch, z, probs, errors});
         require_ptrs({data->weights, data->currentBatch, data->sampledTrainY, scratch->nextDevPtr});
-        FITRE_REQUIRE(evalType == FITRE_MODEL_TRAIN, FITRE_ERR_UNSUPPORTED,
-                      "only MODEL_TRAIN (batch statistics) is on this path");
+        FITRE_REQUIRE(evalType == FITRE_MODEL_TRAIN || evalType == FITRE_MODEL_TRAIN_ACCURACY ||
+                          evalType == FITRE_MODEL_TEST_ACCURACY,
+                      FITRE_ERR_BAD_ARG, "unknown EVAL_TYPE");
         model_check_batch(m, curBatchSize);
-        double loss = cnn_forward(ctx, m, data, scratch->nextDevPtr, z, probs, errors, curBatchSize, true);
+        // the two accuracy modes normalise with the running statistics (functions/dev_batch_norm.cu:386-392)
+        double loss = cnn_forward(ctx, m, data, scratch->nextDevPtr, z, probs, errors, curBatchSize, true,
+                                  evalType != FITRE_MODEL_TRAIN);
         if (loss_host) *loss_host = loss;
     });
 }

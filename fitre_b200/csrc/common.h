@@ -162,7 +162,8 @@ void add_channel_bias(fitre_context *ctx, double *x, const double *bias, long ro
 void add_column_bias(fitre_context *ctx, double *x, const double *bias, int rows, int cols);
 void apply_activation(fitre_context *ctx, int act, const double *in, double *out, long n);
 // conv-out -> (bn out, mean, var) -> act out [-> pool out]
-void conv_post_forward(fitre_context *ctx, const ConvGeom &g, int N, double *zl, double *scratch);
+void conv_post_forward(fitre_context *ctx, const ConvGeom &g, int N, double *zl, double *scratch,
+                       bool running_stats = false);
 // R-op of the same chain: rz conv-out -> R bn -> R act -> R pool
 void conv_post_rop_forward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
                            double *rzl, double *scratch);
@@ -202,7 +203,7 @@ void vec_dots(fitre_context *ctx, long n, const double *a0, const double *b0, co
 // ---- passes.cu ----
 double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
                    double *scratch, double *z, double *probs, double *errors, int n,
-                   bool want_loss);
+                   bool want_loss, bool running_stats = false);
 void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
                   double *scratch, double *z, double *gradient, double *dx, double *delta,
                   double *delta_new, int n);

@@ -20,7 +20,7 @@
 // relative error near 3e-4 per convolution, which batch normalisation and the backward sweep of a
 // deep net amplify a hundredfold; the compensated form stays near 1e-6 per convolution.
 // Every mbarrier wait is bounded; on a time-out the CTA sets the error word, still frees its
-// TMEM columns and returns.  No cluster launch, no multicast.
+// TMEM columns and returns.  Plain one-CTA launches; every CTA fetches its own tiles.
 #include <algorithm>
 
 #include "common.h"

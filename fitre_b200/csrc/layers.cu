@@ -205,8 +205,8 @@ __global__ void bn_stats_store_kernel(const double *sum, const double *ssq, doub
     mean[c] = mu;
     var[c] = v;
     // running statistics, momentum 0.9 (functions/dev_batch_norm.cu:307-314)
-    run_mean[c] = 0.9 * run_mean[c] + 0.1 * mu;
-    run_var[c] = 0.9 * run_var[c] + 0.1 * v;
+    run_mean[c] = 0.9 * run_mean[c] + (1. - 0.9) * mu;
+    run_var[c] = 0.9 * run_var[c] + (1. - 0.9) * v;
 }
 struct NormActOp {  // bn out (optional) and activation out
     const double *x, *mean, *var;
@@ -784,14 +784,20 @@ void act_rop_backward(fitre_context *ctx, int act, double *rdelta, const double 
     check_launch(ctx, "act_rop_backward_kernel");
 }
 
-void conv_post_forward(fitre_context *ctx, const ConvGeom &g, int N, double *zl, double *scratch) {
+void conv_post_forward(fitre_context *ctx, const ConvGeom &g, int N, double *zl, double *scratch,
+                       bool running_stats) {
     const long rows = (long)N * g.Ho * g.Wo;
     const double m = (double)rows * ctx->world;
     double *bn = g.bn ? zl + g.bnOff : nullptr;
     double *mean = g.bn ? bn + g.meanOff : nullptr;
     double *var = g.bn ? bn + g.varOff : nullptr;
     const bool v2 = vec2_ok(g, N, {zl});
-    if (g.bn) {
+    if (g.bn && running_stats) {
+        // accuracy evaluation: normalise with the running statistics, leave every statistic as it
+        // is (functions/dev_batch_norm.cu:386-392)
+        mean = var + g.Cout;
+        var = var + 2 * g.Cout;
+    } else if (g.bn) {
         // two-pass batch statistics (functions/dev_batch_norm.cu:263-315)
         double *sum = channel_pass<1>(ctx, SumOp{zl, rows}, g.Cout, rows, scratch, true, "bn_sum", v2);
         double *sum_keep = scratch + kScratchDoubles - g.Cout;  // parked above the partials

@@ -85,7 +85,7 @@ long rop_backward_scratch(const CNN_MODEL *m) {
 // ---------------------------------------------------------------------------------------------
 double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
                    double *scratch, double *z, double *probs, double *errors, int n,
-                   bool want_loss) {
+                   bool want_loss, bool running_stats) {
     const double *weights = data->weights;
     double *bnws = scratch;
     double *tmp = scratch + bn_scratch(0);
@@ -96,7 +96,7 @@ double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET 
         ConvSeg seg{layer_input(m, data, z, l), weights + m->wOffsets[l]};
         conv_fprop(ctx, 1, &seg, m->bias ? weights + m->bOffsets[l] : nullptr, zl, n, g.Cin, g.H,
                    g.W, g.k, g.pad, g.Cout, split);
-        conv_post_forward(ctx, g, n, zl, bnws);
+        conv_post_forward(ctx, g, n, zl, bnws, running_stats);
     }
     const ConvGeom lg = conv_geom(m, m->cLayers - 1);
     // the last convolution block's output is rewritten in the FC layout, as the reference does

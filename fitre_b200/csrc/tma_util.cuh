@@ -1,5 +1,5 @@
 // Device and host helpers shared by the TMA-fed kernels: mbarrier primitives with bounded
-// waits, cp.async.bulk.tensor loads (never with cluster multicast), tensor-map encoding through
+// waits, plain per-CTA tensor loads (each CTA fetches its own tiles), tensor-map encoding through
 // the driver entry point (no link-time dependency on libcuda).
 #pragma once
 

@@ -131,7 +131,40 @@ typedef struct fitre_kfac_info {
     int LambdaGOffsets[FITRE_MAX_LAYERS];    /* G-factor block start per layer (doubles) */
     int OmegaZSize, LambdaGSize;
     real regLambda, dampGamma;
+    /* knobs of the training loop (same names as the reference's struct) */
+    real stats_decay, momentum;
+    int checkGrad;   /* 1: also evaluate the quadratic model along the gradient and take the better */
+    int inverseFreq; /* factors are inverted every inverseFreq minibatches; this library: 1 only */
 } FITRE_KFAC_INFO;
+
+/* solvers/params.h:11-33, field for field. */
+typedef struct fitre_trust_region_params {
+    real delta, minDelta, maxDelta;
+    real eta1, eta2, gamma1, gamma2;
+    unsigned long int maxProps;
+    int maxMatVecs, maxEpochs, maxIters;
+    int hessianType;
+    real alpha;
+    int curIteration;
+    real hs;
+    real lambda;
+} TRUST_REGION_PARAMS;
+
+/* What fitre_subsampled_trust_region_kfac records per minibatch / per epoch (caller-owned
+ * arrays; the reference prints these values to stderr). */
+typedef struct fitre_tr_step {
+    real trainLikelihood;    /* loss of the minibatch before the step */
+    real newTrainLikelihood; /* loss after the step (batch statistics) */
+    real newTrainAccuracy;   /* percent, after the step */
+    real modelKfac, modelGradient; /* quadratic-model values of the two directions */
+    real rho, delta;         /* reduction ratio; radius after the update */
+    int usedKfac, reverted;
+} FITRE_TR_STEP;
+typedef struct fitre_tr_epoch {
+    real testLikelihood, testAccuracy, trainLikelihood, trainAccuracy;
+    real seconds; /* wall time of the minibatch sweep (without the two evaluation sweeps) */
+    int miniBatches;
+} FITRE_TR_EPOCH;
 
 /* Steihaug-CG parameters and results (reference: solvers/cg_steihaug.h:10-35). */
 enum {
@@ -331,6 +364,68 @@ int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODEL *m,
  * `stream` is a cudaStream_t.  This entry point has no counterpart in the reference. */
 int fitre_syrk_tn_static_scratch(const real *A, long rows, int n, long lda, real alpha, real *C,
                                  void *stream);
+
+/* ---- training loop pieces either side of the path ------------------------------------- */
+/* solvers/kfac_trust_region.cu:66-77 (initBatchNormData): running mean 0 / variance 1 in the
+ * running-statistics slots of `z` for every batch-normalised layer. */
+int fitre_init_batch_norm_data(fitre_context *ctx, const CNN_MODEL *m, real *z);
+/* functions/cnn_eval_model.cu:7-13 (evaluateCNNModel): a MODEL_TRAIN forward, loss -> *loss_host. */
+int fitre_evaluate_cnn_model(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                             SCRATCH_AREA *scratch, real *z, real *probs, real *lossFuncErrors,
+                             int offset, int curBatchSize, real *loss_host);
+/* functions/cnn_accuracy.cu:16-59 (computeAccuracy): predicted class = first class whose
+ * probability strictly exceeds the running maximum (starting at 0); *hits_host = number of hits
+ * and *accuracy_host = percentage, both over the global batch when a communicator is set. */
+int fitre_compute_accuracy(fitre_context *ctx, const real *probs, const real *target, int rows,
+                           int numClasses, real *hits_host, real *accuracy_host);
+/* Minibatch assembly in one kernel: utilities/sample_matrix.cu:70-92 (selectColumnMatrix: gather
+ * images `indices[offset..offset+n)` -- or offset..offset+n when indices is NULL -- and their
+ * labels from the features x samples matrix setX / setY), solvers/kfac_da.cu:22-89 (augmentData:
+ * per-image [C][W][H] -> batch [C][N][W][H]; when `uniforms` is given, random crop with padding 4
+ * then random horizontal flip, augmentation/dev_crop.cu, dev_flip.cu) and
+ * augmentation/dev_normalize.cu (v/255, minus channel mean, over channel deviation, chosen by
+ * data->datasetType).  `uniforms` = 3n device doubles in [0,1): row shifts, column shifts, flips
+ * (replaces the reference's cuRAND draws).  Writes data->sampledTrainY and the second half of
+ * data->sampledTrainX (2n*features doubles, as allocSampledDataset sizes it) and points
+ * data->currentBatch there. */
+int fitre_prepare_minibatch(fitre_context *ctx, const CNN_MODEL *m, DEVICE_DATASET *data,
+                            const real *setX, const real *setY, const int *indices, long offset,
+                            int n, const real *uniforms);
+/* functions/cnn_accuracy.cu:61-174 (computeTestGeneralizationErrors for evalType =
+ * FITRE_MODEL_TEST_ACCURACY, computeTrainGeneralizationErrors for FITRE_MODEL_TRAIN_ACCURACY):
+ * mean loss and accuracy (percent) over the whole set in minibatches of model->batchSize,
+ * batch norm with the running statistics of `z`, no augmentation.  Loop bounds follow the
+ * reference: the test sweep includes the partial last batch, the train sweep stops before the
+ * last batch; both divide by the set size.  With a communicator each global batch is split
+ * over the ranks and what does not fill a global batch is evaluated redundantly by every rank.
+ * Scratch behind scratch->nextDevPtr: fitre_generalization_mem_required doubles. */
+long fitre_generalization_mem_required(const CNN_MODEL *m);
+int fitre_compute_generalization_errors(fitre_context *ctx, const CNN_MODEL *m, DEVICE_DATASET *data,
+                                        SCRATCH_AREA *scratch, real *z, real *probs, real *errors,
+                                        int evalType, real *likelihood, real *accuracy);
+/* solvers/kfac_trust_region.cu:94-661 (subsampledTrustRegionKFAC), inverseFreq == 1: per epoch a
+ * shuffled sweep over the training set; per minibatch gradient, sampled-label backward, A and G
+ * factors with damped inverses, natural gradient, quadratic model of the KFAC direction (and of
+ * the gradient when checkGrad), momentum, weight update, re-evaluation, reduction ratio, radius
+ * update and the reference's revert rule; after each epoch the two generalisation sweeps.
+ * trParams->maxIters epochs; `maxMiniBatches` > 0 stops each epoch early (tests).  Random draws
+ * (shuffle, augmentation, sampled labels) come from a counter-based generator seeded with `seed`,
+ * identical on every rank.  `steps` (capacity stepsCap) and `epochs` (capacity maxIters) may be
+ * NULL.  All device memory comes from scratch->nextDevPtr: fitre_trust_region_kfac_mem_required
+ * doubles.  data->weights is updated in place; data->sampledTrainX/Y must hold 2*batch*features
+ * and batch doubles. */
+long fitre_trust_region_kfac_mem_required(const CNN_MODEL *m, const DEVICE_DATASET *data);
+int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL *m, DEVICE_DATASET *data,
+                                       FITRE_KFAC_INFO *kfacInfo, TRUST_REGION_PARAMS *trParams,
+                                       SCRATCH_AREA *scratch, unsigned long long seed, int enableDA,
+                                       int maxMiniBatches, FITRE_TR_STEP *steps, int stepsCap,
+                                       FITRE_TR_EPOCH *epochs);
+/* utilities/print_utils.c:136-186 (writeVector / readVector): the `.params` text format, one
+ * value per line.  referenceFormat = 1 writes the reference's "%6.10f" (byte-identical files,
+ * 10 decimals); 0 writes "%.17g" (round-trips every double).  The reader takes either (atof per
+ * line, stops at `n` values or end of file) and returns the count in *read_out.  Host pointers. */
+int fitre_write_vector(const char *path, const real *host, long n, int referenceFormat);
+int fitre_read_vector(const char *path, real *host, long n, long *read_out);
 
 /* ---- host-buffer entry point (what a reference driver calls per minibatch) ---- */
 /* One gradient + one Hessian-vector product with HOST inputs and outputs: copies the

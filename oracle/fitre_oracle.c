@@ -48,6 +48,7 @@ void ora_env_default(ORA_ENV *env) {
     env->world = 1;
     env->allreduce = NULL;
     env->user = NULL;
+    env->eval_type = FITRE_MODEL_TRAIN;
 }
 
 static void env_allreduce(const ORA_ENV *env, double *buf, long n) {
@@ -787,8 +788,27 @@ double ora_cnn_forward(const ORA_ENV *env, const CNN_MODEL *m, const double *bat
         double *actOut = out + c->activationOffset;
         if (c->batchNorm != FITRE_NO_BATCH_NORM) {
             double *bn = out + c->batchNormOffset;
-            ora_batch_norm_forward(env, out, c->outHeight, c->outWidth, c->outChannels, n, bn,
-                                   bn + c->meansOffset, bn + c->variancesOffset, BN_EPS);
+            double *run_mean = bn + c->runningMeansOffset, *run_var = bn + c->runningVariancesOffset;
+            if (env && env->eval_type != FITRE_MODEL_TRAIN && env->eval_type != 0) {
+                /* accuracy modes: dataset statistics, nothing updated (dev_batch_norm.cu:386-392) */
+                long rows = (long)c->outHeight * c->outWidth * n;
+#pragma omp parallel for schedule(static)
+                for (int ch = 0; ch < c->outChannels; ch++)
+                    for (long i = 0; i < rows; i++)
+                        bn[(long)ch * rows + i] =
+                            (out[(long)ch * rows + i] - run_mean[ch]) / sqrt(run_var[ch] + BN_EPS);
+            } else {
+                double *mean = bn + c->meansOffset, *var = bn + c->variancesOffset;
+                ora_batch_norm_forward(env, out, c->outHeight, c->outWidth, c->outChannels, n, bn,
+                                       mean, var, BN_EPS);
+                /* running statistics, momentum 0.9 (dev_batch_norm.cu:307-314): Dscal then Daxpy */
+                for (int ch = 0; ch < c->outChannels; ch++) {
+                    run_mean[ch] = 0.9 * run_mean[ch];
+                    run_var[ch] = 0.9 * run_var[ch];
+                    run_mean[ch] += (1. - 0.9) * mean[ch];
+                    run_var[ch] += (1. - 0.9) * var[ch];
+                }
+            }
             memcpy(actOut, bn, sizeof(double) * (size_t)V);
         } else {
             memcpy(actOut, out, sizeof(double) * (size_t)V);
@@ -1408,4 +1428,285 @@ void ora_natural_gradient(const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const
         ora_gemm(0, 0, F->out, in, in, 1.0, t, F->out, Ai, in, 0.0, nGradient + m->wOffsets[li], F->out);
         free(t);
     }
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Evaluation pass and input pipeline                                                     */
+/* ------------------------------------------------------------------------------------ */
+
+/* solvers/kfac_trust_region.cu:66-77 with functions/dev_batch_norm.cu:235-255: running mean 0,
+ * running variance 1 for every batch-normalised layer. */
+void ora_init_batch_norm_data(const CNN_MODEL *m, double *z) {
+    for (int l = 0; l < m->cLayers; l++) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        if (c->batchNorm == FITRE_NO_BATCH_NORM) continue;
+        double *bn = z + m->zOffsets[l + 1] + c->batchNormOffset;
+        for (int ch = 0; ch < c->outChannels; ch++) {
+            bn[c->runningMeansOffset + ch] = 0.;
+            bn[c->runningVariancesOffset + ch] = 1.;
+        }
+    }
+}
+
+/* functions/cnn_accuracy.cu:16-59: predicted class = first class whose probability strictly
+ * exceeds the running maximum (which starts at 0); a hit when class + 1 equals the label.
+ * Returns the percentage over the (global) batch, *hits_out the hit count. */
+double ora_compute_accuracy(const ORA_ENV *env, const double *probs, const double *target, int rows,
+                            int classes, double *hits_out) {
+    double hits = 0;
+    for (int i = 0; i < rows; i++) {
+        double best = 0;
+        int cls = 0;
+        for (int c = 0; c < classes; c++)
+            if (best < probs[(long)i * classes + c]) {
+                best = probs[(long)i * classes + c];
+                cls = c;
+            }
+        if ((double)(cls + 1) == target[i]) hits += 1;
+    }
+    env_allreduce(env, &hits, 1);
+    if (hits_out) *hits_out = hits;
+    return hits * 100. / ((double)rows * env_world(env));
+}
+
+/* Minibatch assembly: utilities/sample_matrix.cu:70-92 (column gather of images and labels),
+ * solvers/kfac_da.cu:22-89 (per-image [C][W][H] -> batch [C][N][W][H]; with augmentation: random
+ * crop with padding 4 then random horizontal flip), augmentation/dev_crop.cu:14-62 (shift =
+ * trunc(u*100) % 9 - 4 per axis, zero outside), augmentation/dev_flip.cu:61-92 (mirror the
+ * columns when u < 0.5), augmentation/dev_normalize.cu:12-100 (v/255, minus mean, over std).
+ * `indices` NULL = images offset .. offset+n-1; `uniforms` NULL = no augmentation, else
+ * [row shifts n][column shifts n][flip n] in [0,1). */
+static const double k_norm_mean[3][3] = {{0.4914, 0.4822, 0.4465}, {0.5071, 0.4865, 0.4409},
+                                         {0.4799, 0.4478, 0.3972}};
+static const double k_norm_std[3][3] = {{0.2470, 0.2435, 0.2616}, {0.2673, 0.2564, 0.2762},
+                                        {0.2769, 0.2690, 0.2820}};
+
+void ora_prepare_minibatch(const double *setX, const double *setY, const int *indices, long offset,
+                           int n, int C, int H, int W, int datasetType, const double *uniforms,
+                           double *batch, double *labels) {
+    const long plane = (long)H * W, feat = plane * C;
+    /* DATASET_TYPE: CIFAR10 = 10, CIFAR100 = 20, IMAGENET = 30 (core/structdefs.h:17-21) */
+    const int di = datasetType == 20 ? 1 : datasetType == 30 ? 2 : 0;
+    const double *mean = k_norm_mean[di], *sd = k_norm_std[di];
+    for (int im = 0; im < n; im++) {
+        const long src = indices ? indices[offset + im] : offset + im;
+        labels[im] = setY[src];
+        int dr = 0, dc = 0, flip = 0;
+        if (uniforms) {
+            dr = (int)(uniforms[im] * 100.) % 9 - 4;
+            dc = (int)(uniforms[n + im] * 100.) % 9 - 4;
+            flip = uniforms[2 * n + im] < 0.5;
+        }
+        for (int c = 0; c < C; c++)
+            for (int col = 0; col < W; col++)
+                for (int row = 0; row < H; row++) {
+                    /* flipped output column col holds cropped column W-1-col */
+                    const int ccol = flip ? W - 1 - col : col;
+                    const int sr = row + dr, sc = ccol + dc;
+                    double v = 0.;
+                    if (sr >= 0 && sc >= 0 && sr < H && sc < W)
+                        v = setX[src * feat + c * plane + (long)sc * H + sr];
+                    v /= 255.;
+                    v = (v - mean[c % 3]) / sd[c % 3];
+                    batch[((long)c * n + im) * plane + (long)col * H + row] = v;
+                }
+    }
+}
+
+/* functions/cnn_accuracy.cu:61-174: mean loss / accuracy over a whole set in minibatches of
+ * model->batchSize with the running batch-norm statistics of `z`.  test != 0: the partial last
+ * batch is included; test == 0: the loop leaves before the last batch; both divide by the set
+ * size.  A partial batch is run on the same net laid out for that many images, the running
+ * statistics carried over (every other part of z is scratch during an evaluation). */
+static long move_running_stats(const CNN_MODEL *m, double *z, double *packed, int to_packed) {
+    long o = 0;
+    for (int l = 0; l < m->cLayers; l++) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        if (c->batchNorm == FITRE_NO_BATCH_NORM) continue;
+        double *bn = z + m->zOffsets[l + 1] + c->batchNormOffset;
+        for (int ch = 0; ch < c->outChannels; ch++) {
+            if (to_packed) {
+                packed[o + ch] = bn[c->runningMeansOffset + ch];
+                packed[o + c->outChannels + ch] = bn[c->runningVariancesOffset + ch];
+            } else {
+                bn[c->runningMeansOffset + ch] = packed[o + ch];
+                bn[c->runningVariancesOffset + ch] = packed[o + c->outChannels + ch];
+            }
+        }
+        o += 2L * c->outChannels;
+    }
+    return o;
+}
+
+void ora_generalization_errors(const ORA_ENV *env_in, const CNN_MODEL *m, const double *setX,
+                               const double *setY, long size, int datasetType,
+                               const double *weights, int numClasses, double *z, int test,
+                               double *likelihood, double *accuracy) {
+    ORA_ENV env = *env_in;
+    env.eval_type = test ? FITRE_MODEL_TEST_ACCURACY : FITRE_MODEL_TRAIN_ACCURACY;
+    env.world = 1;
+    env.allreduce = NULL;
+    const CONV_LAYER *c0 = &m->convLayer[0];
+    const int C = c0->inChannels, H = c0->height, W = c0->width, B = m->batchSize;
+    const long feat = (long)C * H * W;
+    double *batch = xmalloc(feat * B), *labels = xmalloc(B), *probs = xmalloc((long)B * numClasses);
+    double *errors = xmalloc((long)B * numClasses), *packed = xmalloc(2L * FITRE_MAX_LAYERS * 4096);
+    double lik = 0, hits = 0;
+    long cur_idx = 0;
+    int cur = B;
+    while (cur_idx < size) {
+        const CNN_MODEL *mm = m;
+        CNN_MODEL tail;
+        if (cur != B) {
+            tail = *m;
+            tail.batchSize = cur;
+            ora_model_finalize(&tail);
+            move_running_stats(m, z, packed, 1);
+            move_running_stats(&tail, z, packed, 0);
+            mm = &tail;
+        }
+        ora_prepare_minibatch(setX, setY, NULL, cur_idx, cur, C, H, W, datasetType, NULL, batch, labels);
+        double l = ora_cnn_forward(&env, mm, batch, labels, weights, numClasses, z, probs, errors, cur);
+        double h = 0;
+        ora_compute_accuracy(&env, probs, labels, cur, numClasses, &h);
+        if (cur != B) move_running_stats(m, z, packed, 0);
+        lik += l * cur;
+        hits += h;
+        cur_idx += cur;
+        if (cur_idx + B < size) {
+            cur = B;
+        } else {
+            cur = (int)(size - cur_idx);
+            if (!test) break;
+        }
+    }
+    *accuracy = hits * 100. / (double)size;
+    *likelihood = lik / (double)size;
+    free(batch); free(labels); free(probs); free(errors); free(packed);
+}
+
+/* solvers/kfac_trust_region.cu:94-661 with inverseFreq == 1, single rank over the global batch.
+ * Random draws: splitmix64 seeded with `seed`; per epoch a Fisher-Yates shuffle of the training
+ * indices, per minibatch 4*B uniforms [row shifts | column shifts | flips | sampled labels]. */
+static unsigned long long sm64_next(unsigned long long *s) {
+    unsigned long long z = (*s += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+static void layer_block_sizes(const CNN_MODEL *m, int l, int *a, int *g) {
+    if (l < m->cLayers) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        *a = c->inChannels * c->kSize * c->kSize + (m->bias ? 1 : 0);
+        *g = c->outChannels;
+    } else {
+        const FC_LAYER *f = &m->fcLayer[l - m->cLayers];
+        *a = f->in + (m->bias ? 1 : 0);
+        *g = f->out;
+    }
+}
+
+int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, const double *trainX,
+                                     const double *trainY, long trainN, const double *testX,
+                                     const double *testY, long testN, int datasetType,
+                                     double *weights, int numClasses, FITRE_KFAC_INFO *info,
+                                     TRUST_REGION_PARAMS *tr, unsigned long long seed, int enableDA,
+                                     int maxMiniBatches, FITRE_TR_STEP *steps, int stepsCap,
+                                     FITRE_TR_EPOCH *epochs) {
+    ora_kfac_storage_indices(m, info);
+    const CONV_LAYER *c0 = &m->convLayer[0];
+    const int C = c0->inChannels, H = c0->height, W = c0->width, B = m->batchSize;
+    const long feat = (long)C * H * W, P = m->pSize, Z = m->zSize;
+    const long md = (m->maxDeltaSize > (long)B * numClasses ? m->maxDeltaSize : (long)B * numClasses) + 32;
+    const int layers = m->cLayers + m->lLayers;
+    double *batch = xmalloc(feat * B), *labels = xmalloc(B), *u = xmalloc(4L * B);
+    double *z = xmalloc(Z), *dx = xmalloc(Z), *distDX = xmalloc(Z);
+    double *probs = xmalloc((long)B * numClasses), *errors = xmalloc(md), *dist1 = xmalloc(md);
+    double *distTarget = xmalloc(B);
+    double *gradient = xmalloc(P), *distGradient = xmalloc(P), *prev = xmalloc(P), *ngrad = xmalloc(P);
+    double *A = xmalloc(info->OmegaZSize), *Ai = xmalloc(info->OmegaZSize);
+    double *G = xmalloc(info->LambdaGSize), *Gi = xmalloc(info->LambdaGSize);
+    int *idx = (int *)malloc(sizeof(int) * (size_t)trainN);
+    memset(z, 0, sizeof(double) * (size_t)Z);
+    memset(prev, 0, sizeof(double) * (size_t)P);
+    ora_init_batch_norm_data(m, z);
+    unsigned long long s = seed;
+    int step_no = 0, rc = 0;
+    for (int iter = 0; iter < tr->maxIters && rc == 0; iter++) {
+        for (long i = 0; i < trainN; i++) idx[i] = (int)i;
+        for (long i = trainN - 1; i > 0; i--) {
+            long j = (long)(sm64_next(&s) % (unsigned long long)(i + 1));
+            int t = idx[i]; idx[i] = idx[j]; idx[j] = t;
+        }
+        long offset = 0;
+        int mb = 0;
+        while (offset + B < trainN && (maxMiniBatches <= 0 || mb < maxMiniBatches)) {
+            for (long i = 0; i < 4L * B; i++) u[i] = (double)(sm64_next(&s) >> 11) * (1.0 / 9007199254740992.0);
+            ora_prepare_minibatch(trainX, trainY, idx, offset, B, C, H, W, datasetType,
+                                  enableDA ? u : NULL, batch, labels);
+            double lik = ora_cnn_forward(env, m, batch, labels, weights, numClasses, z, probs, errors, B);
+            memcpy(dist1, errors, sizeof(double) * (size_t)B * numClasses);
+            ora_cnn_backward(env, m, batch, weights, z, gradient, dx, dist1, B);
+            axpy(P, info->regLambda, weights, gradient);
+            ora_distribution_errors(env, probs, u + 3L * B, B, numClasses, distTarget, dist1);
+            ora_cnn_backward(env, m, batch, weights, z, distGradient, distDX, dist1, B);
+            ora_kfac_omega_z(env, m, batch, z, B, A, info);
+            ora_kfac_lambda_delta(env, m, distDX, B, G, info);
+            for (int l = 0; l < layers && rc == 0; l++) {
+                int a, g;
+                layer_block_sizes(m, l, &a, &g);
+                rc |= ora_kfac_matrix_inverse(A + info->OmegaZOffsets[l], Ai + info->OmegaZOffsets[l], a,
+                                              info->regLambda, info->dampGamma);
+                rc |= ora_kfac_matrix_inverse(G + info->LambdaGOffsets[l], Gi + info->LambdaGOffsets[l], g,
+                                              info->regLambda, info->dampGamma);
+            }
+            if (rc) break;
+            ora_natural_gradient(m, info, Ai, Gi, gradient, ngrad);
+            double mK = ora_quadratic_model(env, m, batch, weights, numClasses, z, probs, errors, dx,
+                                            gradient, ngrad, tr->delta, B, info->regLambda);
+            double mG = 0;
+            if (info->checkGrad)
+                mG = ora_quadratic_model(env, m, batch, weights, numClasses, z, probs, errors, dx,
+                                         gradient, gradient, tr->delta, B, info->regLambda);
+            int use_kfac = !info->checkGrad || mK < mG;
+            double *dir = use_kfac ? ngrad : gradient;
+            axpy(P, info->momentum, prev, dir);
+            axpy(P, -1.0, dir, weights);
+            memcpy(prev, dir, sizeof(double) * (size_t)P);
+            double nlik = ora_cnn_forward(env, m, batch, labels, weights, numClasses, z, probs, errors, B);
+            double hits = 0;
+            double acc = ora_compute_accuracy(env, probs, labels, B, numClasses, &hits);
+            double rho = (nlik - lik) / ((use_kfac ? mK : mG) - 1e-16);
+            if (rho > 0.75) tr->delta = tr->maxDelta < 2. * tr->delta ? tr->maxDelta : 2. * tr->delta;
+            if (rho < 0.25) tr->delta = tr->minDelta > 0.5 * tr->delta ? tr->minDelta : 0.5 * tr->delta;
+            int reverted = 0;
+            if (rho < 1e-4 || nlik > 10. * lik) {
+                axpy(P, 1.0, prev, weights);
+                reverted = 1;
+            }
+            if (steps && step_no < stepsCap) {
+                FITRE_TR_STEP st = {lik, nlik, acc, mK, mG, rho, tr->delta, use_kfac, reverted};
+                steps[step_no] = st;
+            }
+            step_no++;
+            offset += B;
+            mb++;
+        }
+        if (rc) break;
+        FITRE_TR_EPOCH ep;
+        memset(&ep, 0, sizeof ep);
+        ep.miniBatches = mb;
+        if (testX && testN > 0)
+            ora_generalization_errors(env, m, testX, testY, testN, datasetType, weights, numClasses, z, 1,
+                                      &ep.testLikelihood, &ep.testAccuracy);
+        ora_generalization_errors(env, m, trainX, trainY, trainN, datasetType, weights, numClasses, z, 0,
+                                  &ep.trainLikelihood, &ep.trainAccuracy);
+        if (epochs) epochs[iter] = ep;
+    }
+    tr->curIteration = step_no;
+    free(batch); free(labels); free(u); free(z); free(dx); free(distDX); free(probs); free(errors);
+    free(dist1); free(distTarget); free(gradient); free(distGradient); free(prev); free(ngrad);
+    free(A); free(Ai); free(G); free(Gi); free(idx);
+    return rc;
 }

@@ -25,6 +25,9 @@ typedef struct ora_env {
     int world;              /* data-parallel ranks; N_global = world * curBatchSize */
     ora_allreduce_fn allreduce;
     void *user;
+    int eval_type;          /* FITRE_MODEL_TRAIN (default): batch statistics, running statistics
+                             * updated; the two *_ACCURACY values: normalise with the running
+                             * statistics (functions/dev_batch_norm.cu:331-393) */
 } ORA_ENV;
 
 void ora_env_default(ORA_ENV *env);
@@ -50,6 +53,12 @@ void ora_rop_max_pool(const double *rz, const double *zact, int N, int C, int H,
                       int stride, int pad, double *out);
 void ora_batch_norm_forward(const ORA_ENV *env, const double *in, int H, int W, int C, int N,
                             double *out, double *mean, double *var, double eps);
+void ora_init_batch_norm_data(const CNN_MODEL *m, double *z);
+double ora_compute_accuracy(const ORA_ENV *env, const double *probs, const double *target, int rows,
+                            int classes, double *hits_out);
+void ora_prepare_minibatch(const double *setX, const double *setY, const int *indices, long offset,
+                           int n, int C, int H, int W, int datasetType, const double *uniforms,
+                           double *batch, double *labels);
 void ora_batch_norm_backward(const ORA_ENV *env, const double *delta, int H, int W, int C,
                              int N, const double *var, const double *zhat, double eps,
                              double *out);
@@ -112,6 +121,19 @@ int ora_kfac_matrix_inverse(const double *matrix, double *inverse, int n, double
                             double gamma);
 void ora_natural_gradient(const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const double *omegaZInv,
                           const double *lambdaGInv, const double *gradient, double *nGradient);
+
+/* evaluation sweeps and the FITRE outer loop (single rank over the global batch) */
+void ora_generalization_errors(const ORA_ENV *env, const CNN_MODEL *m, const double *setX,
+                               const double *setY, long size, int datasetType,
+                               const double *weights, int numClasses, double *z, int test,
+                               double *likelihood, double *accuracy);
+int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, const double *trainX,
+                                     const double *trainY, long trainN, const double *testX,
+                                     const double *testY, long testN, int datasetType,
+                                     double *weights, int numClasses, FITRE_KFAC_INFO *info,
+                                     TRUST_REGION_PARAMS *tr, unsigned long long seed, int enableDA,
+                                     int maxMiniBatches, FITRE_TR_STEP *steps, int stepsCap,
+                                     FITRE_TR_EPOCH *epochs);
 
 #ifdef __cplusplus
 }

@@ -20,7 +20,7 @@ ALLREDUCE_FN = C.CFUNCTYPE(None, C.POINTER(C.c_double), C.c_long, C.c_void_p)
 
 class ORA_ENV(C.Structure):
     _fields_ = [("ref_softmax", C.c_int), ("world", C.c_int),
-                ("allreduce", ALLREDUCE_FN), ("user", C.c_void_p)]
+                ("allreduce", ALLREDUCE_FN), ("user", C.c_void_p), ("eval_type", C.c_int)]
 
 
 def lib():
@@ -68,13 +68,27 @@ def lib():
         L.ora_conv_dgrad.argtypes = [dp, i, i, i, dp, i, i, i, i, i, i, dp]
         L.ora_gemm.argtypes = [i, i, C.c_long, C.c_long, C.c_long, d, dp, C.c_long, dp, C.c_long,
                                d, dp, C.c_long]
+        ip = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+        L.ora_init_batch_norm_data.argtypes = [MP, dp]
+        L.ora_compute_accuracy.argtypes = [EP, dp, dp, i, i, C.POINTER(C.c_double)]
+        L.ora_compute_accuracy.restype = d
+        L.ora_prepare_minibatch.argtypes = [dp, dp, C.c_void_p, C.c_long, i, i, i, i, i, C.c_void_p,
+                                            dp, dp]
+        L.ora_generalization_errors.argtypes = [EP, MP, dp, dp, C.c_long, i, dp, i, dp, i,
+                                                C.POINTER(C.c_double), C.POINTER(C.c_double)]
+        L.ora_subsampled_trust_region_kfac.argtypes = [
+            EP, MP, dp, dp, C.c_long, C.c_void_p, C.c_void_p, C.c_long, i, dp, i,
+            C.POINTER(S.KFAC_INFO), C.POINTER(S.TRUST_REGION_PARAMS), C.c_ulonglong, i, i,
+            C.POINTER(S.TR_STEP), i, C.POINTER(S.TR_EPOCH)]
+        L.ora_subsampled_trust_region_kfac.restype = i
         _LIB = L
     return _LIB
 
 
-def make_env(ref_softmax=1, world=1, allreduce=None):
+def make_env(ref_softmax=1, world=1, allreduce=None, eval_type=10):
     env = ORA_ENV()
     env.ref_softmax, env.world = int(ref_softmax), int(world)
+    env.eval_type = int(eval_type)
     if allreduce is not None:
         env._cb = ALLREDUCE_FN(allreduce)  # keep alive
         env.allreduce = env._cb
@@ -116,3 +130,36 @@ def hv(model, batch, weights, num_classes, n, st, vector, env=None):
     lib().ora_cnn_hv(C.byref(env), C.byref(model), batch, weights, num_classes, st.z, st.probs,
                      st.errors, st.dx, np.ascontiguousarray(vector), out, st.rz, n)
     return out
+
+
+def prepare_minibatch(setX, setY, indices, offset, n, C_, H, W, dataset_type=10, uniforms=None):
+    """Oracle minibatch assembly; returns (batch [C][N][W][H] flat, labels)."""
+    batch = np.zeros(n * C_ * H * W)
+    labels = np.zeros(n)
+    idx = None if indices is None else np.ascontiguousarray(indices, dtype=np.int32)
+    u = None if uniforms is None else np.ascontiguousarray(uniforms, dtype=np.float64)
+    lib().ora_prepare_minibatch(np.ascontiguousarray(setX), np.ascontiguousarray(setY),
+                                None if idx is None else idx.ctypes.data, int(offset), int(n), C_, H,
+                                W, int(dataset_type), None if u is None else u.ctypes.data, batch,
+                                labels)
+    return batch, labels
+
+
+def trust_region_kfac(model, trainX, trainY, testX, testY, weights, num_classes, info, tr, seed=1,
+                      enable_da=1, max_mini_batches=0, steps_cap=0, dataset_type=10, env=None):
+    """Oracle FITRE loop; updates `weights` in place, returns (steps, epochs)."""
+    env = env or make_env()
+    steps = (S.TR_STEP * max(steps_cap, 1))()
+    epochs = (S.TR_EPOCH * max(tr.maxIters, 1))()
+    tX = None if testX is None else np.ascontiguousarray(testX)
+    tY = None if testY is None else np.ascontiguousarray(testY)
+    rc = lib().ora_subsampled_trust_region_kfac(
+        C.byref(env), C.byref(model), np.ascontiguousarray(trainX), np.ascontiguousarray(trainY),
+        int(trainY.size), None if tX is None else tX.ctypes.data,
+        None if tY is None else tY.ctypes.data, 0 if tY is None else int(tY.size),
+        int(dataset_type), weights, int(num_classes), C.byref(info), C.byref(tr), int(seed),
+        int(enable_da), int(max_mini_batches), steps, int(steps_cap), epochs)
+    if rc:
+        raise RuntimeError("oracle loop: a factor was not positive definite")
+    n = min(steps_cap, tr.curIteration)
+    return list(steps[:n]), list(epochs[:tr.maxIters])
