@@ -28,7 +28,7 @@ SYMBOLS = [
     "fitre_kfac_natural_gradient_mem_required", "fitre_compute_natural_gradient",
     "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host",
     "fitre_init_batch_norm_data", "fitre_evaluate_cnn_model", "fitre_compute_accuracy",
-    "fitre_prepare_minibatch", "fitre_generalization_mem_required",
+    "fitre_select_column_matrix", "fitre_prepare_minibatch", "fitre_generalization_mem_required",
     "fitre_compute_generalization_errors", "fitre_trust_region_kfac_mem_required",
     "fitre_subsampled_trust_region_kfac", "fitre_write_vector", "fitre_read_vector",
 ]
@@ -99,6 +99,7 @@ def load():
     sig("fitre_init_batch_norm_data", i, vp, MP, vp)
     sig("fitre_evaluate_cnn_model", i, vp, MP, DP, SP, vp, vp, vp, i, i, dbl_p)
     sig("fitre_compute_accuracy", i, vp, vp, vp, i, i, dbl_p, dbl_p)
+    sig("fitre_select_column_matrix", i, vp, DP, i, vp, i)
     sig("fitre_prepare_minibatch", i, vp, MP, DP, vp, vp, vp, l, i, vp)
     sig("fitre_generalization_mem_required", l, MP)
     sig("fitre_compute_generalization_errors", i, vp, MP, DP, SP, vp, vp, vp, i, dbl_p, dbl_p)

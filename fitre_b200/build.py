@@ -13,6 +13,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SOURCES = ["gemm.cu", "conv_tma.cu", "conv_tf32.cu", "layers.cu", "passes.cu", "kfac.cu", "training.cu", "model.cpp", "comm.cpp", "cabi.cpp"]
 LIB = os.path.join(HERE, "libfitre_b200.so")
+# C++ functions with the reference's own (mangled) names on top of the C ABI
+SHIM_SRC = os.path.join(HERE, "csrc", "reference_shim.cpp")
+SHIM_LIB = os.path.join(HERE, "libfitre_reference_shim.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--use_fast_math=false"]
@@ -48,6 +51,11 @@ def build(verbose=False, force=False):
         raise RuntimeError("nvcc failed")
     if procs or not os.path.exists(LIB):
         cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcudart", "-ldl"]
+        subprocess.check_call(cmd)
+    if force or _stale(SHIM_LIB, SHIM_SRC) or os.path.getmtime(SHIM_LIB) < os.path.getmtime(LIB):
+        inc = os.path.join(os.path.dirname(HERE), "include")
+        cmd = [NVCC, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-I", inc, "-shared", "-o", SHIM_LIB,
+               SHIM_SRC, "-L", HERE, "-lfitre_b200", "-lcudart", "-Xlinker", "-rpath=$ORIGIN"]
         subprocess.check_call(cmd)
     return LIB
 

@@ -95,6 +95,16 @@ __global__ void prepare_minibatch_kernel(const double *__restrict__ setX, const 
     }
 }
 
+// utilities/sample_matrix.cu:12-30 (kerExtractColumns): dst column j = src column indices[j]
+__global__ void select_columns_kernel(const double *__restrict__ src, const int *__restrict__ indices,
+                                      long rows, long total, double *__restrict__ dst) {
+    for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long)gridDim.x * blockDim.x) {
+        const long col = idx / rows, r = idx - col * rows;
+        dst[idx] = src[(long)indices[col] * rows + r];
+    }
+}
+
 NormConst norm_constants(int datasetType) {
     // augmentation/dev_normalize.cu:52-83; DATASET_TYPE values core/structdefs.h:17-21
     switch (datasetType) {
@@ -176,6 +186,23 @@ extern "C" int fitre_compute_accuracy(fitre_context *ctx, const real *probs, con
     const double hits = compute_hits(ctx, probs, target, rows, numClasses);
     if (hits_host) *hits_host = hits;
     if (accuracy_host) *accuracy_host = hits * 100. / ((double)rows * ctx->world);
+    FITRE_ENTRY_END
+}
+
+extern "C" int fitre_select_column_matrix(fitre_context *ctx, DEVICE_DATASET *data, int sampleSize,
+                                          const int *indices, int offset) {
+    FITRE_ENTRY_BEGIN
+    FITRE_REQUIRE(data && indices && sampleSize > 0 && offset >= 0 && data->trainSetX && data->trainSetY &&
+                      data->sampledTrainX && data->sampledTrainY && data->features > 0,
+                  FITRE_ERR_BAD_ARG, "bad argument");
+    const long total = (long)sampleSize * data->features;
+    select_columns_kernel<<<(int)std::min<long>((total + kThreads - 1) / kThreads, 148 * 16), kThreads, 0,
+                            ctx->stream>>>(data->trainSetX, indices + offset, data->features, total,
+                                           data->sampledTrainX);
+    check_launch(ctx, "select_columns_kernel");
+    select_columns_kernel<<<(sampleSize + kThreads - 1) / kThreads, kThreads, 0, ctx->stream>>>(
+        data->trainSetY, indices + offset, 1, sampleSize, data->sampledTrainY);
+    check_launch(ctx, "select_columns_kernel");
     FITRE_ENTRY_END
 }
 

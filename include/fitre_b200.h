@@ -388,6 +388,12 @@ int fitre_compute_accuracy(fitre_context *ctx, const real *probs, const real *ta
  * (replaces the reference's cuRAND draws).  Writes data->sampledTrainY and the second half of
  * data->sampledTrainX (2n*features doubles, as allocSampledDataset sizes it) and points
  * data->currentBatch there. */
+/* utilities/sample_matrix.cu:70-92 (selectColumnMatrix) on its own: images and labels
+ * indices[offset .. offset+sampleSize) of the training set -> data->sampledTrainX / sampledTrainY,
+ * no layout change.  fitre_prepare_minibatch does this and the rest of the pipeline in one
+ * kernel; this entry point exists for callers that keep the reference's two-step sequence. */
+int fitre_select_column_matrix(fitre_context *ctx, DEVICE_DATASET *data, int sampleSize,
+                               const int *indices, int offset);
 int fitre_prepare_minibatch(fitre_context *ctx, const CNN_MODEL *m, DEVICE_DATASET *data,
                             const real *setX, const real *setY, const int *indices, long offset,
                             int n, const real *uniforms);

@@ -49,6 +49,7 @@ void ora_env_default(ORA_ENV *env) {
     env->allreduce = NULL;
     env->user = NULL;
     env->eval_type = FITRE_MODEL_TRAIN;
+    env->rank = 0;
 }
 
 static void env_allreduce(const ORA_ENV *env, double *buf, long n) {
@@ -1585,9 +1586,10 @@ void ora_generalization_errors(const ORA_ENV *env_in, const CNN_MODEL *m, const 
     free(batch); free(labels); free(probs); free(errors); free(packed);
 }
 
-/* solvers/kfac_trust_region.cu:94-661 with inverseFreq == 1, single rank over the global batch.
- * Random draws: splitmix64 seeded with `seed`; per epoch a Fisher-Yates shuffle of the training
- * indices, per minibatch 4*B uniforms [row shifts | column shifts | flips | sampled labels]. */
+/* solvers/kfac_trust_region.cu:94-661 with inverseFreq == 1.  Random draws: splitmix64 seeded
+ * with `seed`, the same stream on every rank; per epoch a Fisher-Yates shuffle of the training
+ * indices, per global minibatch of GB = world * B images 4*GB uniforms [row shifts | column
+ * shifts | flips | sampled labels], of which rank r uses entries r*B .. r*B+B-1 of each part. */
 static unsigned long long sm64_next(unsigned long long *s) {
     unsigned long long z = (*s += 0x9E3779B97F4A7C15ull);
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -1620,7 +1622,9 @@ int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, con
     const long feat = (long)C * H * W, P = m->pSize, Z = m->zSize;
     const long md = (m->maxDeltaSize > (long)B * numClasses ? m->maxDeltaSize : (long)B * numClasses) + 32;
     const int layers = m->cLayers + m->lLayers;
-    double *batch = xmalloc(feat * B), *labels = xmalloc(B), *u = xmalloc(4L * B);
+    const int Wn = env_world(env), rank = env ? env->rank : 0;
+    const long GB = (long)B * Wn;
+    double *batch = xmalloc(feat * B), *labels = xmalloc(B), *u = xmalloc(4L * B), *ug = xmalloc(4L * GB);
     double *z = xmalloc(Z), *dx = xmalloc(Z), *distDX = xmalloc(Z);
     double *probs = xmalloc((long)B * numClasses), *errors = xmalloc(md), *dist1 = xmalloc(md);
     double *distTarget = xmalloc(B);
@@ -1641,13 +1645,16 @@ int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, con
         }
         long offset = 0;
         int mb = 0;
-        while (offset + B < trainN && (maxMiniBatches <= 0 || mb < maxMiniBatches)) {
-            for (long i = 0; i < 4L * B; i++) u[i] = (double)(sm64_next(&s) >> 11) * (1.0 / 9007199254740992.0);
-            ora_prepare_minibatch(trainX, trainY, idx, offset, B, C, H, W, datasetType,
+        while (offset + GB < trainN && (maxMiniBatches <= 0 || mb < maxMiniBatches)) {
+            for (long i = 0; i < 4L * GB; i++) ug[i] = (double)(sm64_next(&s) >> 11) * (1.0 / 9007199254740992.0);
+            for (int part = 0; part < 4; part++)
+                memcpy(u + (long)part * B, ug + part * GB + (long)rank * B, sizeof(double) * (size_t)B);
+            ora_prepare_minibatch(trainX, trainY, idx, offset + (long)rank * B, B, C, H, W, datasetType,
                                   enableDA ? u : NULL, batch, labels);
             double lik = ora_cnn_forward(env, m, batch, labels, weights, numClasses, z, probs, errors, B);
             memcpy(dist1, errors, sizeof(double) * (size_t)B * numClasses);
             ora_cnn_backward(env, m, batch, weights, z, gradient, dx, dist1, B);
+            env_allreduce(env, gradient, P);
             axpy(P, info->regLambda, weights, gradient);
             ora_distribution_errors(env, probs, u + 3L * B, B, numClasses, distTarget, dist1);
             ora_cnn_backward(env, m, batch, weights, z, distGradient, distDX, dist1, B);
@@ -1690,7 +1697,7 @@ int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, con
                 steps[step_no] = st;
             }
             step_no++;
-            offset += B;
+            offset += GB;
             mb++;
         }
         if (rc) break;
@@ -1705,7 +1712,7 @@ int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, con
         if (epochs) epochs[iter] = ep;
     }
     tr->curIteration = step_no;
-    free(batch); free(labels); free(u); free(z); free(dx); free(distDX); free(probs); free(errors);
+    free(batch); free(labels); free(u); free(ug); free(z); free(dx); free(distDX); free(probs); free(errors);
     free(dist1); free(distTarget); free(gradient); free(distGradient); free(prev); free(ngrad);
     free(A); free(Ai); free(G); free(Gi); free(idx);
     return rc;

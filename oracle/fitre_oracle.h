@@ -28,6 +28,8 @@ typedef struct ora_env {
     int eval_type;          /* FITRE_MODEL_TRAIN (default): batch statistics, running statistics
                              * updated; the two *_ACCURACY values: normalise with the running
                              * statistics (functions/dev_batch_norm.cu:331-393) */
+    int rank;               /* this rank's index among `world` (outer loop: which slice of each
+                             * global minibatch it assembles) */
 } ORA_ENV;
 
 void ora_env_default(ORA_ENV *env);

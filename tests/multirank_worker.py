@@ -32,10 +32,67 @@ def make_case(builder="vgg_small"):
     return model_full, x, y, w, v, ncls
 
 
+def loop_case(per_rank_batch):
+    """Inputs of the outer-loop test: a small image set and a vgg_small laid out for one rank."""
+    from test_training_oracle import loop_params, small_problem
+    rng = np.random.default_rng(77)
+    model, trainX, trainY, testX, testY, w = small_problem(rng, n_train=60, n_test=21,
+                                                          batch=per_rank_batch)
+    info, tr = loop_params()
+    return model, trainX, trainY, testX, testY, w, info, tr
+
+
+def pack_loop(steps, epochs, w):
+    f = lambda rows, names: np.array([[getattr(r, n) for n in names] for r in rows], dtype=np.float64)
+    return dict(steps=f(steps, ["trainLikelihood", "newTrainLikelihood", "newTrainAccuracy", "modelKfac",
+                                "modelGradient", "rho", "delta", "usedKfac", "reverted"]),
+                epochs=f(epochs, ["testLikelihood", "testAccuracy", "trainLikelihood", "trainAccuracy",
+                                  "miniBatches"]), w=w)
+
+
+def run_loop(backend, rank, world, out):
+    """Each rank runs the FITRE loop on its slices of every global minibatch."""
+    import torch
+    import torch.distributed as dist
+    import oracle_lib as O
+    model, trainX, trainY, testX, testY, w, info, tr = loop_case(8 // world)
+    if backend == "gloo":
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+        def allreduce(buf, n, user):
+            dist.all_reduce(torch.from_numpy(np.ctypeslib.as_array(buf, shape=(n,))))
+
+        env = O.make_env(world=world, allreduce=allreduce, rank=rank)
+        steps, epochs = O.trust_region_kfac(model, trainX, trainY, testX, testY, w, 10, info, tr, seed=5,
+                                            steps_cap=64, env=env)
+        np.savez(out, **pack_loop(steps, epochs, w))
+    else:
+        import ctypes as C
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import gpu_util as G
+        from fitre_b200 import api, _lib
+        ctx = api.Context(rank)
+        ctx.comm_init_from_torch()
+        c0 = model.convLayer[0]
+        W = G.dev(w)
+        data = api.make_full_dataset(W, G.dev(trainX), G.dev(trainY), G.dev(testX), G.dev(testY), 10,
+                                     c0.inChannels * c0.height * c0.width, model.batchSize)
+        need = _lib.load().fitre_trust_region_kfac_mem_required(C.byref(model), C.byref(data))
+        scr = api.make_scratch(torch.zeros(need, dtype=torch.float64, device="cuda"))
+        steps, epochs = api.subsampledTrustRegionKFAC(ctx, model, data, info, tr, scr, seed=5, stepsCap=64)
+        np.savez(out, **pack_loop(steps, epochs, W.cpu().numpy()))
+        torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     backend, rank, world, port, out = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4], sys.argv[5]
     builder = sys.argv[6] if len(sys.argv) > 6 else "vgg_small"
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=port, RANK=str(rank), WORLD_SIZE=str(world))
+    if builder == "loop":
+        return run_loop(backend, rank, world, out)
     import torch
     import torch.distributed as dist
     import nets

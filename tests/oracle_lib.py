@@ -20,7 +20,8 @@ ALLREDUCE_FN = C.CFUNCTYPE(None, C.POINTER(C.c_double), C.c_long, C.c_void_p)
 
 class ORA_ENV(C.Structure):
     _fields_ = [("ref_softmax", C.c_int), ("world", C.c_int),
-                ("allreduce", ALLREDUCE_FN), ("user", C.c_void_p), ("eval_type", C.c_int)]
+                ("allreduce", ALLREDUCE_FN), ("user", C.c_void_p), ("eval_type", C.c_int),
+                ("rank", C.c_int)]
 
 
 def lib():
@@ -85,8 +86,9 @@ def lib():
     return _LIB
 
 
-def make_env(ref_softmax=1, world=1, allreduce=None, eval_type=10):
+def make_env(ref_softmax=1, world=1, allreduce=None, eval_type=10, rank=0):
     env = ORA_ENV()
+    env.rank = int(rank)
     env.ref_softmax, env.world = int(ref_softmax), int(world)
     env.eval_type = int(eval_type)
     if allreduce is not None:

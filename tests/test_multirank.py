@@ -26,8 +26,11 @@ def free_port():
 def run_ranks(backend, world, tmp_path, builder):
     port = free_port()
     outs = [str(tmp_path / ("r%d.npz" % r)) for r in range(world)]
+    # ranks share the host cores: a few OpenMP threads each, sleeping (not spinning) at barriers
+    env = dict(os.environ, OMP_NUM_THREADS="4", OMP_WAIT_POLICY="passive")
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "multirank_worker.py"), backend,
-                               str(r), str(world), port, outs[r], builder]) for r in range(world)]
+                               str(r), str(world), port, outs[r], builder], env=env)
+             for r in range(world)]
     for p in procs:
         assert p.wait(timeout=600) == 0
     return [np.load(o) for o in outs]
@@ -75,3 +78,40 @@ def test_two_gpu_cuda_matches_full_batch(tmp_path, builder):
         assert rel(res["gradient"], g) < 1e-10
         assert rel(res["hv"], hv) < 1e-10
         assert rel(res["A"], A) < 1e-10 and rel(res["G"], G) < 1e-10
+
+
+def single_rank_loop():
+    import multirank_worker as W
+    model, trainX, trainY, testX, testY, w, info, tr = W.loop_case(8)
+    steps, epochs = O.trust_region_kfac(model, trainX, trainY, testX, testY, w, 10, info, tr, seed=5,
+                                        steps_cap=64)
+    return W.pack_loop(steps, epochs, w)
+
+
+def check_loop(res, ref, tol):
+    assert res["steps"].shape == ref["steps"].shape and ref["steps"].shape[0] == 14
+    # flags, accuracies and radii are exact; likelihoods, models and rho within tolerance
+    assert np.array_equal(res["steps"][:, [2, 6, 7, 8]], ref["steps"][:, [2, 6, 7, 8]])
+    assert np.allclose(res["steps"][:, [0, 1]], ref["steps"][:, [0, 1]], rtol=tol, atol=0)
+    assert np.allclose(res["steps"][:, [3, 4, 5]], ref["steps"][:, [3, 4, 5]], rtol=100 * tol, atol=1e-12)
+    assert np.array_equal(res["epochs"][:, [1, 3, 4]], ref["epochs"][:, [1, 3, 4]])
+    assert np.allclose(res["epochs"][:, [0, 2]], ref["epochs"][:, [0, 2]], rtol=tol, atol=0)
+    assert rel(res["w"], ref["w"]) < 10 * tol
+
+
+def test_two_rank_oracle_loop_matches_single_rank(tmp_path):
+    """Host-side sharding of the outer loop: two ranks with 4 images each reproduce one rank
+    with 8 (same shuffle, each rank assembling its slice of every global minibatch)."""
+    ref = single_rank_loop()
+    for res in run_ranks("gloo", 2, tmp_path, "loop"):
+        check_loop(res, ref, 1e-9)
+
+
+@pytest.mark.gpu
+def test_two_gpu_cuda_loop_matches_single_rank_oracle(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ref = single_rank_loop()
+    for res in run_ranks("nccl", 2, tmp_path, "loop"):
+        check_loop(res, ref, 1e-8)
