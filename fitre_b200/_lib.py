@@ -22,7 +22,7 @@ SYMBOLS = [
     "fitre_cnn_gradient_mem_required", "fitre_cnn_hv_mem_required",
     "fitre_cnn_forward", "fitre_cnn_backward", "fitre_compute_cnn_gradient",
     "fitre_cnn_rop_forward", "fitre_cnn_rop_backward", "fitre_cnn_hv",
-    "fitre_compute_quadratic_model", "fitre_cg_steihaug",
+    "fitre_quadratic_model_mem_required", "fitre_compute_quadratic_model", "fitre_cg_steihaug",
     "fitre_compute_distribution_errors", "fitre_kfac_storage_indices", "fitre_kfac_mem_required", "fitre_kfac_omega_z",
     "fitre_kfac_lambda_delta", "fitre_kfac_inverse_mem_required", "fitre_kfac_matrix_inverse",
     "fitre_kfac_natural_gradient_mem_required", "fitre_compute_natural_gradient",
@@ -83,6 +83,7 @@ def load():
     sig("fitre_cnn_rop_forward", i, vp, MP, DP, SP, vp, vp, vp, i, i, vp, vp)
     sig("fitre_cnn_rop_backward", i, vp, MP, DP, SP, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp)
     sig("fitre_cnn_hv", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, i, i, vp, vp, d)
+    sig("fitre_quadratic_model_mem_required", l, MP)
     sig("fitre_compute_quadratic_model", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, d, i, i, d,
         vp, vp, vp, dbl_p)
     sig("fitre_cg_steihaug", i, vp, MP, DP, vp, vp, vp, vp, vp, vp, i, vp, C.POINTER(S.CG_PARAMS))

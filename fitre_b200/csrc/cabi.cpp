@@ -309,6 +309,11 @@ int fitre_cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *d
 // functions/model_reduction.cu:20-93.  The damping term is weightDecay * vector (what the
 // reference's PyTorch twin adds, pytorch/peng/utils.py:77); the C reference adds
 // weightDecay * weights (model_reduction.cu:50-52); both vanish at weightDecay == 0.
+long fitre_quadratic_model_mem_required(const CNN_MODEL *m) {
+    if (!m) return -1;
+    return align32(m->pSize) + fitre_cnn_hv_mem_required(m);
+}
+
 int fitre_compute_quadratic_model(fitre_context *ctx, const CNN_MODEL *m,
                                   const DEVICE_DATASET *data, real *z, real *probs,
                                   real *lossFuncErrors, real *dx, real *gradient, real *vector,

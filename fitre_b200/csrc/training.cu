@@ -451,7 +451,7 @@ TrLayout tr_layout(const CNN_MODEL *m, const DEVICE_DATASET *data, const FITRE_K
         const LayerBlock b = layer_block(m, l);
         maxblock = std::max(maxblock, std::max(b.a, b.g));
     }
-    long need = std::max(fitre_cnn_gradient_mem_required(m), fitre_cnn_hv_mem_required(m));
+    long need = std::max(fitre_cnn_gradient_mem_required(m), fitre_quadratic_model_mem_required(m));
     need = std::max(need, fitre_kfac_mem_required(m));
     need = std::max(need, fitre_kfac_inverse_mem_required(maxblock));
     need = std::max(need, fitre_kfac_natural_gradient_mem_required(m));

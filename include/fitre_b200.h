@@ -305,7 +305,10 @@ int fitre_cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_
 int fitre_cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, real *z,
                  real *probs, real *lossFuncErrors, real *dx, real *vector, real *hv, int s,
                  int curBatchSize, real *devPtr, real *hostPtr, real weightDecay);
-/* functions/model_reduction.cu:20-93.  Scales `vector` in place; model value -> *m_host. */
+/* functions/model_reduction.cu:20-93.  Scales `vector` in place; model value -> *m_host.
+ * devPtr needs fitre_quadratic_model_mem_required doubles (one pSize vector for the Hessian-vector
+ * product in front of fitre_cnn_hv_mem_required). */
+long fitre_quadratic_model_mem_required(const CNN_MODEL *m);
 int fitre_compute_quadratic_model(fitre_context *ctx, const CNN_MODEL *m,
                                   const DEVICE_DATASET *data, real *z, real *probs,
                                   real *lossFuncErrors, real *dx, real *gradient, real *vector,
