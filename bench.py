@@ -378,8 +378,9 @@ def run_extra(args):
         Ai, Gi = torch.zeros(info.OmegaZSize, **f64), torch.zeros(info.LambdaGSize, **f64)
         ngrad = torch.zeros(model.pSize, **f64)
         L = _lib.load()
-        iscr = torch.zeros(max(L.fitre_kfac_inverse_mem_required(4609),
+        iscr = torch.zeros(max(L.fitre_kfac_invert_factors_mem_required(C.byref(model)),
                                L.fitre_kfac_natural_gradient_mem_required(C.byref(model))), **f64)
+        info.regLambda, info.dampGamma = 1e-3, 0.0
         blocks = []
         for l in range(model.cLayers + model.lLayers):
             if l < model.cLayers:
@@ -408,9 +409,7 @@ def run_extra(args):
             api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
             api.computeOmegaZ(ctx, model, data, ws.z, n, A, info, kscr)
             api.computeLambdaDelta(ctx, model, ddx, n, G, info, kscr)
-            for size, off, src, dst in blocks:  # damped Cholesky inverse of every factor
-                api.computeMatrixInverse(ctx, src[off:off + size * size], dst[off:off + size * size],
-                                         size, iscr, 1e-3, 0.0)
+            api.invertFactors(ctx, model, info, A, Ai, G, Gi, iscr)  # 22 damped Cholesky inverses
             api.computeNaturalGradient(ctx, model, info, Ai, Gi, ws.gradient, ngrad, iscr)
 
     def barrier():

@@ -25,6 +25,7 @@ SYMBOLS = [
     "fitre_quadratic_model_mem_required", "fitre_compute_quadratic_model", "fitre_cg_steihaug",
     "fitre_compute_distribution_errors", "fitre_kfac_storage_indices", "fitre_kfac_mem_required", "fitre_kfac_omega_z",
     "fitre_kfac_lambda_delta", "fitre_kfac_inverse_mem_required", "fitre_kfac_matrix_inverse",
+    "fitre_kfac_invert_factors_mem_required", "fitre_kfac_invert_factors",
     "fitre_kfac_natural_gradient_mem_required", "fitre_compute_natural_gradient",
     "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host",
     "fitre_init_batch_norm_data", "fitre_evaluate_cnn_model", "fitre_compute_accuracy",
@@ -93,6 +94,8 @@ def load():
     sig("fitre_kfac_lambda_delta", i, vp, MP, vp, i, vp, C.POINTER(S.KFAC_INFO), vp)
     sig("fitre_kfac_inverse_mem_required", l, i)
     sig("fitre_kfac_matrix_inverse", i, vp, vp, vp, i, vp, d, d)
+    sig("fitre_kfac_invert_factors_mem_required", l, MP)
+    sig("fitre_kfac_invert_factors", i, vp, MP, C.POINTER(S.KFAC_INFO), vp, vp, vp, vp, vp)
     sig("fitre_kfac_natural_gradient_mem_required", l, MP)
     sig("fitre_compute_natural_gradient", i, vp, MP, C.POINTER(S.KFAC_INFO), vp, vp, vp, vp, vp)
     sig("fitre_syrk_tn_static_scratch", i, vp, l, i, l, d, vp, vp)

@@ -332,6 +332,13 @@ def make_full_dataset(weights, trainX, trainY, testX, testY, numClasses, feature
     return d
 
 
+def invertFactors(ctx, model, info, omegaZ, omegaZInv, lambdaG, lambdaGInv, devPtr):
+    """All damped factor inverses of one KFAC step (several streams, divided among ranks)."""
+    ctx.check(ctx.lib.fitre_kfac_invert_factors(ctx.h, C.byref(model), C.byref(info), omegaZ.data_ptr(),
+                                                omegaZInv.data_ptr(), lambdaG.data_ptr(),
+                                                lambdaGInv.data_ptr(), devPtr.data_ptr()))
+
+
 def initBatchNormData(ctx, model, z):
     ctx.check(ctx.lib.fitre_init_batch_norm_data(ctx.h, C.byref(model), z.data_ptr()))
 

@@ -115,6 +115,11 @@ int fitre_context_destroy(fitre_context *ctx) {
     if (ctx->host_ws) cudaFree(ctx->host_ws);
     if (ctx->host_pinned) cudaFreeHost(ctx->host_pinned);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+    for (int s = 0; s < 4; ++s) {
+        if (ctx->inv_streams[s]) cudaStreamDestroy(ctx->inv_streams[s]);
+        if (ctx->inv_join[s]) cudaEventDestroy(ctx->inv_join[s]);
+    }
+    if (ctx->inv_fork) cudaEventDestroy(ctx->inv_fork);
     if (ctx->ev_up) cudaEventDestroy(ctx->ev_up);
     if (ctx->ev_down) cudaEventDestroy(ctx->ev_down);
     for (auto &r : ctx->prof) {

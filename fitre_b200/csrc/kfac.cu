@@ -8,6 +8,7 @@
 #include <climits>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "common.h"
 
@@ -189,10 +190,10 @@ extern "C" int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, c
 namespace {
 constexpr int NB = 64;
 
-// In place: A (nb x nb, lower, leading dim lda) <- its Cholesky factor L (upper part zeroed);
-// Linv (nb x nb, ld NB, dense lower) <- L^-1.  *fail is set to 1 + column on a pivot <= 0.
+// In place: A (nb x nb, lower, leading dim lda) <- its Cholesky factor L;
+// Linv (nb x nb, leading dim ldi, upper part zero) <- L^-1.  *fail is set to 1 + column on a pivot <= 0.
 __global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, int nb, double *Linv,
-                                                         int *fail, int col0) {
+                                                         long ldi, int *fail, int col0) {
     // lower triangle: L; strictly upper triangle: (L^-1)' off-diagonal; xd: diagonal of L^-1
     __shared__ double L[NB][NB + 1];
     __shared__ double xd[NB];
@@ -240,9 +241,7 @@ __global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, in
     for (int e = tid; e < NB * NB; e += 256) {
         const int r = e % NB, c = e / NB;
         if (r < nb && c < nb && r >= c) A[(long)c * lda + r] = L[r][c];
-        double x = 0.0;
-        if (r < nb && c < nb) x = (r == c) ? xd[c] : (r > c ? L[c][r] : 0.0);
-        Linv[(long)c * NB + r] = x;
+        if (r < nb && c < nb) Linv[(long)c * ldi + r] = (r == c) ? xd[c] : (r > c ? L[c][r] : 0.0);
     }
     if (tid == 0 && bad) atomicCAS(fail, 0, col0 + bad);
 }
@@ -277,32 +276,63 @@ __global__ void unpack_ng_kernel(const double *t, double *w, double *b, int K, i
 }
 int blocks_for(long n) { return (int)std::max<long>(1, std::min<long>((n + 255) / 256, 1184)); }
 
-// Y (n x n, ld n) holds L on entry (lower, upper zero); on exit L^-1.  dinv = the NB x NB inverses
-// of the diagonal blocks.  Recursive: inv([L11 0; L21 L22]) = [L11^-1 0; -L22^-1 L21 L11^-1  L22^-1].
-void trtri_recursive(fitre_context *ctx, double *Y, long ld, int n, int off, const double *dinv,
-                     double *tmp) {
+// Factor and invert in one recursion.  A (n x n, leading dim ld, lower triangle read, destroyed)
+// is symmetric positive definite; on exit Y (same shape, zero on entry) holds L^-1 with
+// A = L L'.  For A = [A11 .; A21 A22]:  L11, Y11 from A11;  L21 = A21 Y11';  A22 -= L21 L21';
+// L22, Y22 from the updated A22;  Y21 = -Y22 L21 Y11.  Every product is a plain GEMM with large
+// inner dimensions; only the NB x NB leaves run in the small shared-memory kernel.  `tmp` is a
+// bump region of at most n*n/2 doubles.
+void factor_invert(fitre_context *ctx, double *A, double *Y, long ld, int n, int col0, int *fail,
+                   double *tmp) {
     if (n <= NB) {
-        FITRE_CUDA(cudaMemcpy2DAsync(Y, ld * sizeof(double), dinv + (long)(off / NB) * NB * NB,
-                                     NB * sizeof(double), n * sizeof(double), n,
-                                     cudaMemcpyDeviceToDevice, ctx->stream));
+        chol_block_kernel<<<1, 256, 0, ctx->stream>>>(A, ld, n, Y, ld, fail, col0);
+        check_launch(ctx, "chol_block_kernel");
         return;
     }
     const int n1 = ((n / 2 + NB - 1) / NB) * NB, n2 = n - n1;
-    double *Y11 = Y, *Y21 = Y + n1, *Y22 = Y + (long)n1 * ld + n1;
-    trtri_recursive(ctx, Y11, ld, n1, off, dinv, tmp);
-    trtri_recursive(ctx, Y22, ld, n2, off + n1, dinv, tmp);
-    // tmp (n2 x n1) = L21 * Y11 ; Y21 = -Y22 * tmp
-    dgemm(ctx, false, false, n2, n1, n1, 1.0, Y21, (int)ld, Y11, (int)ld, 0.0, tmp, n2);
-    dgemm(ctx, false, false, n2, n1, n2, -1.0, Y22, (int)ld, tmp, n2, 0.0, Y21, (int)ld);
+    double *A21 = A + n1, *A22 = A + (long)n1 * ld + n1;
+    double *Y21 = Y + n1, *Y22 = Y + (long)n1 * ld + n1;
+    double *L21 = tmp, *next = tmp + (long)n2 * n1;
+    factor_invert(ctx, A, Y, ld, n1, col0, fail, next);
+    dgemm(ctx, false, true, n2, n1, n1, 1.0, A21, (int)ld, Y, (int)ld, 0.0, L21, n2);
+    dgemm(ctx, false, true, n2, n2, n1, -1.0, L21, n2, L21, n2, 1.0, A22, (int)ld);
+    factor_invert(ctx, A22, Y22, ld, n2, col0 + n1, fail, next);
+    double *T = next;  // free again after the recursion: L21 * Y11
+    dgemm(ctx, false, false, n2, n1, n1, 1.0, L21, n2, Y, (int)ld, 0.0, T, n2);
+    dgemm(ctx, false, false, n2, n1, n2, -1.0, Y22, (int)ld, T, n2, 0.0, Y21, (int)ld);
+}
+
+// inverse <- (matrix + damp I)^-1 on ctx->stream, no host synchronisation; a pivot <= 0 is
+// recorded in *fail.  scratch: fitre_kfac_inverse_mem_required(n) doubles.
+void invert_spd(fitre_context *ctx, const double *matrix, double *inverse, int n, double damp,
+                double *scratch, int *fail) {
+    const long nn = (long)n * n;
+    double *Am = scratch;                    // damped copy, destroyed by the factorisation
+    double *Y = Am + align32(nn);            // L^-1
+    double *tmp = Y + align32(nn);           // recursion scratch
+    double *slabs = tmp + align32(nn / 2 + (long)n * NB);
+    vec_copy(ctx, nn, matrix, Am);
+    add_diagonal_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(Am, n, damp);
+    check_launch(ctx, "add_diagonal_kernel");
+    vec_fill(ctx, nn, 0.0, Y);
+    factor_invert(ctx, Am, Y, n, n, 0, fail, tmp);
+    syrk_tn(ctx, n, n, 1.0, Y, n, inverse, slabs);  // (L^-1)' L^-1
+}
+
+void check_fail_word(fitre_context *ctx, int *fail) {
+    FITRE_CUDA(cudaMemcpyAsync(ctx->pinned + 202, fail, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
+    FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+    int f;
+    std::memcpy(&f, ctx->pinned + 202, sizeof(int));
+    FITRE_REQUIRE(f == 0, FITRE_ERR_NOT_CONVERGED,
+                  "Cholesky pivot <= 0 at column " + std::to_string(f - 1) + " (matrix not positive definite)");
 }
 }  // namespace
 
 extern "C" long fitre_kfac_inverse_mem_required(int n) {
     if (n < 1) return -1;
     const long nn = (long)n * n;
-    const long nblk = (n + NB - 1) / NB;
-    return align32(nn) + align32(nblk * NB * NB) + align32(nn / 2 + (long)n * NB) +
-           align32(syrk_scratch(n, n)) + 64;
+    return 2 * align32(nn) + align32(nn / 2 + (long)n * NB) + align32(syrk_scratch(n, n)) + 64;
 }
 
 // inverse = (matrix + (lambda + dampGamma) I)^-1, both n x n column-major.
@@ -312,43 +342,124 @@ extern "C" int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix,
     try {
         FITRE_CUDA(cudaSetDevice(ctx->device));
         FITRE_REQUIRE(matrix && inverse && devPtr && n > 0, FITRE_ERR_BAD_ARG, "bad argument");
-        const long nn = (long)n * n;
-        const int nblk = (n + NB - 1) / NB;
-        double *Lm = devPtr;                                   // factor, then L^-1
-        double *dinv = Lm + align32(nn);                       // inverses of the diagonal blocks
-        double *tmp = dinv + align32((long)nblk * NB * NB);    // panel / recursion scratch
-        double *slabs = tmp + align32(nn / 2 + (long)n * NB);
         int *fail = (int *)(ctx->dscal + 4002);
         FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), ctx->stream));
-        vec_copy(ctx, nn, matrix, Lm);
-        add_diagonal_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(Lm, n, lambda + dampGamma);
-        check_launch(ctx, "add_diagonal_kernel");
-        for (int j = 0; j < n; j += NB) {
-            const int nb = std::min(NB, n - j), rows = n - j - nb;
-            double *A11 = Lm + (long)j * n + j;
-            double *Dj = dinv + (long)(j / NB) * NB * NB;
-            chol_block_kernel<<<1, 256, 0, ctx->stream>>>(A11, n, nb, Dj, fail, j);
-            check_launch(ctx, "chol_block_kernel");
-            if (rows > 0) {
-                double *A21 = A11 + nb, *A22 = A11 + (long)nb * n + nb;
-                // L21 = A21 * L11^-T ; A22 -= L21 L21'
-                dgemm(ctx, false, true, rows, nb, nb, 1.0, A21, n, Dj, NB, 0.0, tmp, rows);
-                FITRE_CUDA(cudaMemcpy2DAsync(A21, (size_t)n * sizeof(double), tmp, (size_t)rows * sizeof(double),
-                                             (size_t)rows * sizeof(double), nb, cudaMemcpyDeviceToDevice,
-                                             ctx->stream));
-                dgemm(ctx, false, true, rows, rows, nb, -1.0, tmp, rows, tmp, rows, 1.0, A22, n);
-            }
+        invert_spd(ctx, matrix, inverse, n, lambda + dampGamma, devPtr, fail);
+        check_fail_word(ctx, fail);
+        return FITRE_OK;
+    } catch (const Error &e) {
+        ctx->err = e.what();
+        return e.code;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// All 2L factor inverses of one KFAC step.  The matrices are independent: they are spread over a
+// few streams of this GPU (the leaves of the factorisation occupy one SM, so concurrent matrices
+// fill the rest), and over the ranks of the communicator when there is one (largest first onto
+// the least loaded rank; every rank then receives the others' inverses by one sum all-reduce over
+// buffers that hold zeros where a rank did no work).
+namespace {
+constexpr int kInvStreams = 4;
+struct InvJob {
+    const double *src;
+    double *dst;
+    int n;
+    double cost;
+};
+std::vector<InvJob> inverse_jobs(const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const double *A,
+                                 double *Ainv, const double *G, double *Ginv) {
+    std::vector<InvJob> jobs;
+    for (int l = 0; l < m->cLayers + m->lLayers; ++l) {
+        int a, g;
+        if (l < m->cLayers) {
+            const CONV_LAYER &c = m->convLayer[l];
+            a = c.inChannels * c.kSize * c.kSize + (m->bias ? 1 : 0);
+            g = c.outChannels;
+        } else {
+            a = m->fcLayer[l - m->cLayers].in + (m->bias ? 1 : 0);
+            g = m->fcLayer[l - m->cLayers].out;
         }
-        zero_upper_kernel<<<blocks_for(nn), 256, 0, ctx->stream>>>(Lm, n);
-        check_launch(ctx, "zero_upper_kernel");
-        trtri_recursive(ctx, Lm, n, n, 0, dinv, tmp);
-        syrk_tn(ctx, n, n, 1.0, Lm, n, inverse, slabs);        // (L^-1)' L^-1
-        FITRE_CUDA(cudaMemcpyAsync(ctx->pinned + 202, fail, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
-        FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
-        int f;
-        std::memcpy(&f, ctx->pinned + 202, sizeof(int));
-        FITRE_REQUIRE(f == 0, FITRE_ERR_NOT_CONVERGED,
-                      "Cholesky pivot <= 0 at column " + std::to_string(f - 1) + " (matrix not positive definite)");
+        jobs.push_back({A + info->OmegaZOffsets[l], Ainv + info->OmegaZOffsets[l], a, (double)a * a * a});
+        jobs.push_back({G + info->LambdaGOffsets[l], Ginv + info->LambdaGOffsets[l], g, (double)g * g * g});
+    }
+    std::stable_sort(jobs.begin(), jobs.end(), [](const InvJob &x, const InvJob &y) { return x.cost > y.cost; });
+    return jobs;
+}
+int max_block(const CNN_MODEL *m) {
+    int mx = 1;
+    for (int l = 0; l < m->cLayers; ++l)
+        mx = std::max(mx, std::max(m->convLayer[l].inChannels * m->convLayer[l].kSize * m->convLayer[l].kSize + 1,
+                                   m->convLayer[l].outChannels));
+    for (int l = 0; l < m->lLayers; ++l) mx = std::max(mx, std::max(m->fcLayer[l].in + 1, m->fcLayer[l].out));
+    return mx;
+}
+}  // namespace
+
+extern "C" long fitre_kfac_invert_factors_mem_required(const CNN_MODEL *m) {
+    if (!m) return -1;
+    return kInvStreams * align32(fitre_kfac_inverse_mem_required(max_block(m)));
+}
+
+extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m, const FITRE_KFAC_INFO *info,
+                                         const real *omegaZ, real *omegaZInv, const real *lambdaG,
+                                         real *lambdaGInv, real *devPtr) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    try {
+        FITRE_CUDA(cudaSetDevice(ctx->device));
+        FITRE_REQUIRE(m && info && omegaZ && omegaZInv && lambdaG && lambdaGInv && devPtr, FITRE_ERR_BAD_ARG,
+                      "NULL pointer argument");
+        const double damp = info->regLambda + info->dampGamma;
+        std::vector<InvJob> jobs = inverse_jobs(m, info, omegaZ, omegaZInv, lambdaG, lambdaGInv);
+        const int W = ctx->world;
+        std::vector<double> load(W, 0.0);
+        std::vector<InvJob> mine;
+        for (const InvJob &j : jobs) {
+            const int r = (int)(std::min_element(load.begin(), load.end()) - load.begin());
+            load[r] += j.cost;
+            if (r == ctx->rank) mine.push_back(j);
+        }
+        int *fail = (int *)(ctx->dscal + 4002);
+        FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), ctx->stream));
+        if (W > 1) {
+            vec_fill(ctx, info->OmegaZSize, 0.0, omegaZInv);
+            vec_fill(ctx, info->LambdaGSize, 0.0, lambdaGInv);
+        }
+        // fork: the side streams start after everything queued on the context's stream
+        if (!ctx->inv_streams[0]) {
+            for (int s = 0; s < kInvStreams; ++s)
+                FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->inv_streams[s], cudaStreamNonBlocking));
+            FITRE_CUDA(cudaEventCreateWithFlags(&ctx->inv_fork, cudaEventDisableTiming));
+            for (int s = 0; s < kInvStreams; ++s)
+                FITRE_CUDA(cudaEventCreateWithFlags(&ctx->inv_join[s], cudaEventDisableTiming));
+        }
+        cudaStream_t main_stream = ctx->stream;
+        FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
+        const long per = align32(fitre_kfac_inverse_mem_required(max_block(m)));
+        std::vector<double> sload(kInvStreams, 0.0);
+        try {
+            for (int s = 0; s < kInvStreams; ++s) FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
+            for (const InvJob &j : mine) {
+                const int s = (int)(std::min_element(sload.begin(), sload.end()) - sload.begin());
+                sload[s] += j.cost;
+                ctx->stream = ctx->inv_streams[s];
+                invert_spd(ctx, j.src, j.dst, j.n, damp, devPtr + (long)s * per, fail);
+            }
+        } catch (...) {
+            ctx->stream = main_stream;
+            throw;
+        }
+        ctx->stream = main_stream;
+        for (int s = 0; s < kInvStreams; ++s) {
+            FITRE_CUDA(cudaEventRecord(ctx->inv_join[s], ctx->inv_streams[s]));
+            FITRE_CUDA(cudaStreamWaitEvent(main_stream, ctx->inv_join[s], 0));
+        }
+        if (W > 1) {
+            comm_allreduce_sum(ctx, omegaZInv, info->OmegaZSize);
+            comm_allreduce_sum(ctx, lambdaGInv, info->LambdaGSize);
+            comm_allreduce_sum(ctx, ctx->dscal + 4002, 1);  // a failure on any rank is seen by all
+        }
+        check_fail_word(ctx, fail);
         return FITRE_OK;
     } catch (const Error &e) {
         ctx->err = e.what();

@@ -403,18 +403,6 @@ struct Rng {
     double uniform() { return (double)(next() >> 11) * (1.0 / 9007199254740992.0); }  // [0,1)
 };
 
-struct LayerBlock {
-    int a, g;  // used sizes of the A block (K + bias) and the G block
-};
-LayerBlock layer_block(const CNN_MODEL *m, int l) {
-    if (l < m->cLayers) {
-        const CONV_LAYER &c = m->convLayer[l];
-        return {c.inChannels * c.kSize * c.kSize + (m->bias ? 1 : 0), c.outChannels};
-    }
-    const FC_LAYER &f = m->fcLayer[l - m->cLayers];
-    return {f.in + (m->bias ? 1 : 0), f.out};
-}
-
 struct TrLayout {
     long indices, uniforms, A, Ainv, G, Ginv, gradient, distGradient, prevWeights, nGradient, z, dx,
         distDX, probs, errors, dist1, dist2, distTarget, scratch, total;
@@ -446,14 +434,9 @@ TrLayout tr_layout(const CNN_MODEL *m, const DEVICE_DATASET *data, const FITRE_K
     L.dist1 = take(md);
     L.dist2 = take(md);
     L.distTarget = take(B);
-    int maxblock = 1;
-    for (int l = 0; l < m->cLayers + m->lLayers; ++l) {
-        const LayerBlock b = layer_block(m, l);
-        maxblock = std::max(maxblock, std::max(b.a, b.g));
-    }
     long need = std::max(fitre_cnn_gradient_mem_required(m), fitre_quadratic_model_mem_required(m));
     need = std::max(need, fitre_kfac_mem_required(m));
-    need = std::max(need, fitre_kfac_inverse_mem_required(maxblock));
+    need = std::max(need, fitre_kfac_invert_factors_mem_required(m));
     need = std::max(need, fitre_kfac_natural_gradient_mem_required(m));
     need = std::max(need, fitre_generalization_mem_required(m));
     L.scratch = take(need);
@@ -501,8 +484,7 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
     const int B = m->batchSize, W = ctx->world, P = m->pSize, classes = data->numClasses;
     const long trainN = data->trainSizeX;
     const long GB = (long)B * W;  // images per global minibatch
-    const int layers = m->cLayers + m->lLayers;
-    const double damp_l = kfacInfo->regLambda, damp_g = kfacInfo->dampGamma;
+    const double damp_l = kfacInfo->regLambda;
     Rng rng{seed};
     std::vector<int> host_idx(trainN);
     std::vector<double> host_u(4 * GB);
@@ -545,13 +527,7 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
             // factors and their damped inverses (:404-411, solvers/kfac_inverses.cu:450-630,759-857)
             FITRE_RC(fitre_kfac_omega_z(ctx, m, data, z, B, A, kfacInfo, work));
             FITRE_RC(fitre_kfac_lambda_delta(ctx, m, distDX, B, G, kfacInfo, work));
-            for (int l = 0; l < layers; ++l) {
-                const LayerBlock b = layer_block(m, l);
-                FITRE_RC(fitre_kfac_matrix_inverse(ctx, A + kfacInfo->OmegaZOffsets[l], Ainv + kfacInfo->OmegaZOffsets[l],
-                                                   b.a, work, damp_l, damp_g));
-                FITRE_RC(fitre_kfac_matrix_inverse(ctx, G + kfacInfo->LambdaGOffsets[l], Ginv + kfacInfo->LambdaGOffsets[l],
-                                                   b.g, work, damp_l, damp_g));
-            }
+            FITRE_RC(fitre_kfac_invert_factors(ctx, m, kfacInfo, A, Ainv, G, Ginv, work));
             FITRE_RC(fitre_compute_natural_gradient(ctx, m, kfacInfo, Ainv, Ginv, gradient, nGradient, work));
 
             // quadratic models of the two candidate steps (:452-470); each call scales its direction

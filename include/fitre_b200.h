@@ -348,6 +348,18 @@ int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, const real *
 long fitre_kfac_inverse_mem_required(int n);
 int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix, real *inverse, int n,
                               real *devPtr, real lambda, real dampGamma);
+/* Every damped inverse of one KFAC step in one call: omegaZInv / lambdaGInv <- the inverses of
+ * all A blocks (K' x K', K' = K + bias) and G blocks of omegaZ / lambdaG at the offsets of `info`,
+ * damping info->regLambda + info->dampGamma (what the reference does block by block inside
+ * computeOmegaZ / computeLambdaDelta, solvers/kfac_inverses.cu:542-544,624-627,822-824,852-855).
+ * The independent matrices run on several streams of the GPU and, with a communicator, are
+ * divided among the ranks (largest first onto the least loaded rank) and exchanged by one sum
+ * all-reduce, which replaces the reference's dormant second-GPU inverse thread
+ * (solvers/kfac_thread.cu:77-204).  devPtr: fitre_kfac_invert_factors_mem_required doubles. */
+long fitre_kfac_invert_factors_mem_required(const CNN_MODEL *m);
+int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m, const FITRE_KFAC_INFO *info,
+                              const real *omegaZ, real *omegaZInv, const real *lambdaG,
+                              real *lambdaGInv, real *devPtr);
 /* solvers/kfac_natural_gradient.cu:36-241 (computeNaturalGradient): nGradient = G^-1 [W|b] A^-1
  * per layer, in the flat layout of `gradient`.  omegaZInv / lambdaGInv hold the inverted factors
  * at the offsets of `info` (A blocks K' x K' with K' = K + bias). */

@@ -142,8 +142,13 @@ def main():
         A, Gm = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
         api.computeOmegaZ(ctx, model, run.data, run.ws.z, per, A, info, scr)
         api.computeLambdaDelta(ctx, model, run.ws.dx, per, Gm, info, scr)
+        # the factor inverses, divided among the ranks and exchanged
+        info.regLambda, info.dampGamma = 1e-3, 1e-2
+        Ai, Gi = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+        iscr = G.dev(np.zeros(_lib.load().fitre_kfac_invert_factors_mem_required(C.byref(model))))
+        api.invertFactors(ctx, model, info, A, Ai, Gm, Gi, iscr)
         np.savez(out, loss=run.loss, gradient=run.gradient, hv=hv, A=A.cpu().numpy(),
-                 G=Gm.cpu().numpy())
+                 G=Gm.cpu().numpy(), Ainv=Ai.cpu().numpy(), Ginv=Gi.cpu().numpy())
         torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

@@ -324,6 +324,13 @@ def test_cuda_kfac_inverse_and_natural_gradient_vs_oracle():
                 assert G.relmax(got, out) < 1e-9, (builder, l, size)
                 M = blk.reshape(size, size) + (lam + gamma) * np.eye(size)
                 assert np.abs(M @ got.reshape(size, size) - np.eye(size)).max() < 1e-9
+        # the same inverses in one call (several streams)
+        info.regLambda, info.dampGamma = lam, gamma
+        Ai2, Gi2 = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+        scr2 = G.dev(np.zeros(L.fitre_kfac_invert_factors_mem_required(C.byref(model))))
+        api.invertFactors(run.c, model, info, A, Ai2, Gm, Gi2, scr2)
+        assert np.array_equal(Ai2.cpu().numpy(), Ai.cpu().numpy())
+        assert np.array_equal(Gi2.cpu().numpy(), Gi.cpu().numpy())
         ng = G.dev(np.zeros(model.pSize))
         api.computeNaturalGradient(run.c, model, info, Ai, Gi, run.ws.gradient, ng, scratch)
         ng_o = np.zeros(model.pSize)
@@ -339,7 +346,7 @@ def test_cuda_matrix_inverse_blocked_sizes_and_failure():
     L = _lib.load()
     c = G.ctx()
     rng = np.random.default_rng(3)
-    for n in (1, 64, 65, 200, 333):
+    for n in (1, 64, 65, 128, 200, 333, 1000):
         B = rng.standard_normal((n, n + 8))
         F = B @ B.T / n
         scratch = G.dev(np.zeros(L.fitre_kfac_inverse_mem_required(n)))

@@ -56,6 +56,30 @@ def rel(a, b):
     return np.linalg.norm(a - b) / np.linalg.norm(b)
 
 
+def full_batch_inverses(builder, A, G):
+    """Oracle inverses (damping 1e-3 + 1e-2) of every used factor block, in the flat layouts."""
+    import ctypes as C
+    import multirank_worker as W
+    from fitre_b200 import _structs as S
+    model = W.make_case(builder)[0]
+    info = S.KFAC_INFO()
+    O.lib().ora_kfac_storage_indices(C.byref(model), C.byref(info))
+    Ai, Gi = np.zeros_like(A), np.zeros_like(G)
+    for l in range(model.cLayers + model.lLayers):
+        if l < model.cLayers:
+            c = model.convLayer[l]
+            kb, co = c.inChannels * c.kSize ** 2 + (1 if model.bias else 0), c.outChannels
+        else:
+            f = model.fcLayer[l - model.cLayers]
+            kb, co = f.in_ + (1 if model.bias else 0), f.out
+        for size, off, src, dst in ((kb, info.OmegaZOffsets[l], A, Ai), (co, info.LambdaGOffsets[l], G, Gi)):
+            out = np.zeros(size * size)
+            assert O.lib().ora_kfac_matrix_inverse(np.ascontiguousarray(src[off:off + size * size]), out,
+                                                   size, 1e-3, 1e-2) == 0
+            dst[off:off + size * size] = out
+    return Ai, Gi
+
+
 @pytest.mark.parametrize("builder", ["vgg_small", "lenet_small"])
 def test_two_rank_oracle_matches_full_batch(tmp_path, builder):
     loss, g, hv, A, G = full_batch_reference(builder)
@@ -73,11 +97,14 @@ def test_two_gpu_cuda_matches_full_batch(tmp_path, builder):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     loss, g, hv, A, G = full_batch_reference(builder)
+    Ainv, Ginv = full_batch_inverses(builder, A, G)
     for res in run_ranks("nccl", 2, tmp_path, builder):
         assert abs(float(res["loss"]) - loss) <= 1e-10 * abs(loss)
         assert rel(res["gradient"], g) < 1e-10
         assert rel(res["hv"], hv) < 1e-10
         assert rel(res["A"], A) < 1e-10 and rel(res["G"], G) < 1e-10
+        # every rank holds every inverse although each computed only its share
+        assert rel(res["Ainv"], Ainv) < 1e-8 and rel(res["Ginv"], Ginv) < 1e-8
 
 
 def single_rank_loop():
