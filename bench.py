@@ -479,7 +479,7 @@ def run_fitre(args):
     trainY = torch.tensor(rng.integers(1, 11, n_train).astype(np.float64), **f64)
     W = torch.tensor(layout.he_normal_params(model, rng), **f64)
     data = api.make_full_dataset(W, trainX, trainY, None, None, 10, 3072, n)
-    need = _lib.load().fitre_trust_region_kfac_mem_required(C.byref(model), C.byref(data))
+    need = _lib.load().fitre_trust_region_kfac_mem_required(C.byref(model), C.byref(data), None)
     scr = api.make_scratch(torch.zeros(need, **f64))
 
     def run(count):

@@ -25,6 +25,8 @@ SYMBOLS = [
     "fitre_quadratic_model_mem_required", "fitre_compute_quadratic_model", "fitre_cg_steihaug",
     "fitre_compute_distribution_errors", "fitre_kfac_storage_indices", "fitre_kfac_mem_required", "fitre_kfac_omega_z",
     "fitre_kfac_lambda_delta", "fitre_kfac_inverse_mem_required", "fitre_kfac_matrix_inverse",
+    "fitre_update_running_stats", "fitre_kfac_speedup_omega_z", "fitre_kfac_speedup_lambda_delta",
+    "fitre_kfac_omega_z_damped", "fitre_kfac_lambda_delta_damped",
     "fitre_kfac_invert_factors_mem_required", "fitre_kfac_invert_factors",
     "fitre_kfac_natural_gradient_mem_required", "fitre_compute_natural_gradient",
     "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host",
@@ -94,6 +96,12 @@ def load():
     sig("fitre_kfac_lambda_delta", i, vp, MP, vp, i, vp, C.POINTER(S.KFAC_INFO), vp)
     sig("fitre_kfac_inverse_mem_required", l, i)
     sig("fitre_kfac_matrix_inverse", i, vp, vp, vp, i, vp, d, d)
+    KP = C.POINTER(S.KFAC_INFO)
+    sig("fitre_update_running_stats", i, vp, vp, vp, l, d)
+    sig("fitre_kfac_speedup_omega_z", i, vp, KP, MP, DP, i, vp, vp, vp, i)
+    sig("fitre_kfac_speedup_lambda_delta", i, vp, KP, MP, i, vp, vp, i)
+    sig("fitre_kfac_omega_z_damped", i, vp, MP, vp, vp, i, vp, KP, vp)
+    sig("fitre_kfac_lambda_delta_damped", i, vp, MP, vp, i, vp, KP, vp)
     sig("fitre_kfac_invert_factors_mem_required", l, MP)
     sig("fitre_kfac_invert_factors", i, vp, MP, C.POINTER(S.KFAC_INFO), vp, vp, vp, vp, vp)
     sig("fitre_kfac_natural_gradient_mem_required", l, MP)
@@ -107,7 +115,7 @@ def load():
     sig("fitre_prepare_minibatch", i, vp, MP, DP, vp, vp, vp, l, i, vp)
     sig("fitre_generalization_mem_required", l, MP)
     sig("fitre_compute_generalization_errors", i, vp, MP, DP, SP, vp, vp, vp, i, dbl_p, dbl_p)
-    sig("fitre_trust_region_kfac_mem_required", l, MP, DP)
+    sig("fitre_trust_region_kfac_mem_required", l, MP, DP, C.POINTER(S.KFAC_INFO))
     sig("fitre_subsampled_trust_region_kfac", i, vp, MP, DP, C.POINTER(S.KFAC_INFO),
         C.POINTER(S.TRUST_REGION_PARAMS), SP, C.c_ulonglong, i, i, C.POINTER(S.TR_STEP), i,
         C.POINTER(S.TR_EPOCH))

@@ -6,6 +6,7 @@
 // the data-parallel ranks before the 1/N (A) or N (G) scaling with the global batch.
 #include <algorithm>
 #include <climits>
+#include <cmath>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -86,95 +87,204 @@ extern "C" int fitre_compute_distribution_errors(fitre_context *ctx, const real 
     }
 }
 
-extern "C" int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m,
-                                  const DEVICE_DATASET *data, const real *z, int samples,
-                                  real *omegaZ, const FITRE_KFAC_INFO *info, real *devPtr) {
-    if (!ctx) return FITRE_ERR_BAD_ARG;
-    try {
-        FITRE_CUDA(cudaSetDevice(ctx->device));
-        FITRE_REQUIRE(m && data && z && omegaZ && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
-        model_check_batch(m, samples);
-        const double Ng = (double)samples * ctx->world;
-        for (int l = 0; l < m->cLayers; ++l) {
-            const ConvGeom g = conv_geom(m, l);
-            const double *x = (l == 0) ? data->currentBatch
-                                       : z + m->zOffsets[l] + m->convLayer[l - 1].outputOffset;
-            double *A = omegaZ + info->OmegaZOffsets[l];
-            const int Kb = g.Cin * g.k * g.k + (m->bias ? 1 : 0);
-            // sum over ranks first, then 1/N: with world == 1 the scale is applied directly
-            const double alpha = ctx->world > 1 ? 1.0 : 1.0 / Ng;
-            conv_patch_syrk(ctx, x, A, samples, g.Cin, g.H, g.W, g.k, g.pad, m->bias != 0, alpha,
-                            1.0 / (double)(g.Ho * g.Wo), devPtr);
-            if (ctx->world > 1) {
-                comm_allreduce_sum(ctx, A, (size_t)Kb * Kb);
-                vec_scale(ctx, (long)Kb * Kb, 1.0 / Ng, A);
-            }
+namespace {
+// Layer inputs come either from the live state (x0 = the batch, zbase = z with the model's z
+// offsets) or, packed == true, from the running averages of the "speed-up" variant (x0 =
+// dampedInput, zbase = dampedZ with the model's zzt offsets: solvers/kfac_inverses.cu:479-489,553-575).
+void omega_z_impl(fitre_context *ctx, const CNN_MODEL *m, const double *x0, const double *zbase, bool packed,
+                  int samples, double *omegaZ, const FITRE_KFAC_INFO *info, double *devPtr) {
+    const double Ng = (double)samples * ctx->world;
+    for (int l = 0; l < m->cLayers; ++l) {
+        const ConvGeom g = conv_geom(m, l);
+        const double *x = (l == 0) ? x0
+                          : packed ? zbase + m->zztOffsets[l]
+                                   : zbase + m->zOffsets[l] + m->convLayer[l - 1].outputOffset;
+        double *A = omegaZ + info->OmegaZOffsets[l];
+        const int Kb = g.Cin * g.k * g.k + (m->bias ? 1 : 0);
+        // sum over ranks first, then 1/N: with world == 1 the scale is applied directly
+        const double alpha = ctx->world > 1 ? 1.0 : 1.0 / Ng;
+        conv_patch_syrk(ctx, x, A, samples, g.Cin, g.H, g.W, g.k, g.pad, m->bias != 0, alpha,
+                        1.0 / (double)(g.Ho * g.Wo), devPtr);
+        if (ctx->world > 1) {
+            comm_allreduce_sum(ctx, A, (size_t)Kb * Kb);
+            vec_scale(ctx, (long)Kb * Kb, 1.0 / Ng, A);
         }
-        const ConvGeom lg = conv_geom(m, m->cLayers - 1);
-        for (int l = 0; l < m->lLayers; ++l) {
-            const FC_LAYER &f = m->fcLayer[l];
-            const double *zin = (l == 0) ? z + lg.zoff + lg.outOff : z + m->zOffsets[m->cLayers + l];
-            double *A = omegaZ + info->OmegaZOffsets[m->cLayers + l];
-            int R = f.in;
-            const double *zm = zin;
-            if (m->bias) {
-                R = f.in + 1;
-                const long total = (long)R * samples;
-                int blocks = (int)std::min<long>((total + 255) / 256, 1184);
-                fc_augment_kernel<<<blocks, 256, 0, ctx->stream>>>(zin, devPtr, f.in, samples);
-                check_launch(ctx, "fc_augment_kernel");
-                zm = devPtr;
-            }
-            dgemm(ctx, false, true, R, R, samples, ctx->world > 1 ? 1.0 : 1.0 / Ng, zm, R, zm, R, 0.0, A, R);
-            if (ctx->world > 1) {
-                comm_allreduce_sum(ctx, A, (size_t)R * R);
-                vec_scale(ctx, (long)R * R, 1.0 / Ng, A);
-            }
+    }
+    const ConvGeom lg = conv_geom(m, m->cLayers - 1);
+    for (int l = 0; l < m->lLayers; ++l) {
+        const FC_LAYER &f = m->fcLayer[l];
+        const double *zin = packed ? zbase + m->zztOffsets[m->cLayers + l]
+                            : (l == 0) ? zbase + lg.zoff + lg.outOff
+                                       : zbase + m->zOffsets[m->cLayers + l];
+        double *A = omegaZ + info->OmegaZOffsets[m->cLayers + l];
+        int R = f.in;
+        const double *zm = zin;
+        if (m->bias) {
+            R = f.in + 1;
+            const long total = (long)R * samples;
+            int blocks = (int)std::min<long>((total + 255) / 256, 1184);
+            fc_augment_kernel<<<blocks, 256, 0, ctx->stream>>>(zin, devPtr, f.in, samples);
+            check_launch(ctx, "fc_augment_kernel");
+            zm = devPtr;
         }
-        return FITRE_OK;
-    } catch (const Error &e) {
-        ctx->err = e.what();
-        return e.code;
+        dgemm(ctx, false, true, R, R, samples, ctx->world > 1 ? 1.0 : 1.0 / Ng, zm, R, zm, R, 0.0, A, R);
+        if (ctx->world > 1) {
+            comm_allreduce_sum(ctx, A, (size_t)R * R);
+            vec_scale(ctx, (long)R * R, 1.0 / Ng, A);
+        }
     }
 }
 
-extern "C" int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, const real *dx,
-                                       int samples, real *lambdaG, const FITRE_KFAC_INFO *info,
-                                       real *devPtr) {
-    if (!ctx) return FITRE_ERR_BAD_ARG;
-    try {
-        FITRE_CUDA(cudaSetDevice(ctx->device));
-        FITRE_REQUIRE(m && dx && lambdaG && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
-        model_check_batch(m, samples);
-        const double Ng = (double)samples * ctx->world;
-        for (int l = 0; l < m->cLayers; ++l) {
-            const ConvGeom g = conv_geom(m, l);
-            const double *d = dx + g.zoff + (g.bn ? g.bnOff : g.actOff);
-            const long M = (long)samples * g.Ho * g.Wo;
-            double *G = lambdaG + info->LambdaGOffsets[l];
-            const double sc = (double)g.Ho * g.Wo * Ng;  // solvers/kfac_inverses.cu:815-816
-            syrk_tn(ctx, M, g.Cout, ctx->world > 1 ? 1.0 : sc, d, M, G, devPtr);
-            if (ctx->world > 1) {
-                comm_allreduce_sum(ctx, G, (size_t)g.Cout * g.Cout);
-                vec_scale(ctx, (long)g.Cout * g.Cout, sc, G);
-            }
+void lambda_delta_impl(fitre_context *ctx, const CNN_MODEL *m, const double *dbase, bool packed, int samples,
+                       double *lambdaG, const FITRE_KFAC_INFO *info, double *devPtr) {
+    const double Ng = (double)samples * ctx->world;
+    for (int l = 0; l < m->cLayers; ++l) {
+        const ConvGeom g = conv_geom(m, l);
+        const double *d = packed ? dbase + m->zztOffsets[l + 1] : dbase + g.zoff + (g.bn ? g.bnOff : g.actOff);
+        const long M = (long)samples * g.Ho * g.Wo;
+        double *G = lambdaG + info->LambdaGOffsets[l];
+        const double sc = (double)g.Ho * g.Wo * Ng;  // solvers/kfac_inverses.cu:815-816
+        syrk_tn(ctx, M, g.Cout, ctx->world > 1 ? 1.0 : sc, d, M, G, devPtr);
+        if (ctx->world > 1) {
+            comm_allreduce_sum(ctx, G, (size_t)g.Cout * g.Cout);
+            vec_scale(ctx, (long)g.Cout * g.Cout, sc, G);
         }
-        for (int l = 0; l < m->lLayers; ++l) {
-            const FC_LAYER &f = m->fcLayer[l];
-            const double *d = dx + m->zOffsets[m->cLayers + l + 1];
-            double *G = lambdaG + info->LambdaGOffsets[m->cLayers + l];
-            dgemm(ctx, false, true, f.out, f.out, samples, ctx->world > 1 ? 1.0 : Ng, d, f.out, d,
-                  f.out, 0.0, G, f.out);
-            if (ctx->world > 1) {
-                comm_allreduce_sum(ctx, G, (size_t)f.out * f.out);
-                vec_scale(ctx, (long)f.out * f.out, Ng, G);
-            }
-        }
-        return FITRE_OK;
-    } catch (const Error &e) {
-        ctx->err = e.what();
-        return e.code;
     }
+    for (int l = 0; l < m->lLayers; ++l) {
+        const FC_LAYER &f = m->fcLayer[l];
+        const double *d = packed ? dbase + m->zztOffsets[m->cLayers + l + 1] : dbase + m->zOffsets[m->cLayers + l + 1];
+        double *G = lambdaG + info->LambdaGOffsets[m->cLayers + l];
+        dgemm(ctx, false, true, f.out, f.out, samples, ctx->world > 1 ? 1.0 : Ng, d, f.out, d,
+              f.out, 0.0, G, f.out);
+        if (ctx->world > 1) {
+            comm_allreduce_sum(ctx, G, (size_t)f.out * f.out);
+            vec_scale(ctx, (long)f.out * f.out, Ng, G);
+        }
+    }
+}
+
+// theta <- m * theta + (1 - m) * update, in the reference's operation order
+// (solvers/kfac_inverses.cu:106-126: scale by m/(1-m), add, scale by 1-m); m == 0 copies.
+__global__ void running_stats_kernel(double *theta, const double *update, long n, double mom) {
+    const double a = mom / (1. - mom), b = 1. - mom;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+        theta[i] = (theta[i] * a + update[i]) * b;
+}
+void update_running(fitre_context *ctx, double *theta, const double *update, long n, double mom, bool first) {
+    if (first || mom == 0.0) {
+        vec_copy(ctx, n, update, theta);
+        return;
+    }
+    running_stats_kernel<<<(int)std::min<long>((n + 255) / 256, 2368), 256, 0, ctx->stream>>>(theta, update, n, mom);
+    check_launch(ctx, "running_stats_kernel");
+}
+}  // namespace
+
+#define KFAC_ENTRY_BEGIN               \
+    if (!ctx) return FITRE_ERR_BAD_ARG; \
+    try {                               \
+        FITRE_CUDA(cudaSetDevice(ctx->device));
+#define KFAC_ENTRY_END       \
+    return FITRE_OK;         \
+    }                        \
+    catch (const Error &e) { \
+        ctx->err = e.what(); \
+        return e.code;       \
+    }
+
+extern "C" int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
+                                  const real *z, int samples, real *omegaZ, const FITRE_KFAC_INFO *info,
+                                  real *devPtr) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(m && data && z && omegaZ && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    model_check_batch(m, samples);
+    omega_z_impl(ctx, m, data->currentBatch, z, false, samples, omegaZ, info, devPtr);
+    KFAC_ENTRY_END
+}
+
+extern "C" int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, const real *dx, int samples,
+                                       real *lambdaG, const FITRE_KFAC_INFO *info, real *devPtr) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(m && dx && lambdaG && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    model_check_batch(m, samples);
+    lambda_delta_impl(ctx, m, dx, false, samples, lambdaG, info, devPtr);
+    KFAC_ENTRY_END
+}
+
+// The "speed-up" variant (factors refreshed every inverseFreq minibatches from running averages of
+// the layer inputs and errors): solvers/kfac_inverses.cu:106-126 (updateRunningStats), :386-447
+// (computeSpeedUpOmegaZ), :699-755 (computeSpeedUpLambdaDelta), and the dampedInput / dampedZ /
+// dampedLambda branches of computeOmegaZ / computeLambdaDelta.
+extern "C" int fitre_update_running_stats(fitre_context *ctx, real *src, const real *update, long numElements,
+                                          real momentum) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(src && update && numElements >= 0 && momentum >= 0 && momentum < 1, FITRE_ERR_BAD_ARG,
+                  "bad argument");
+    update_running(ctx, src, update, numElements, momentum, false);
+    KFAC_ENTRY_END
+}
+
+extern "C" int fitre_kfac_speedup_omega_z(fitre_context *ctx, const FITRE_KFAC_INFO *info, const CNN_MODEL *m,
+                                          const DEVICE_DATASET *data, int samples, const real *z,
+                                          real *dampedInput, real *dampedZ, int iterCount) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(info && m && data && data->currentBatch && z && dampedInput && dampedZ, FITRE_ERR_BAD_ARG,
+                  "NULL pointer argument");
+    model_check_batch(m, samples);
+    const bool first = iterCount == 0;
+    const double mom = std::sqrt(info->stats_decay);
+    update_running(ctx, dampedInput, data->currentBatch, (long)data->features * samples, mom, first);
+    for (int l = 0; l < m->cLayers; ++l) {
+        const CONV_LAYER &c = m->convLayer[l];
+        const POOL_LAYER &p = m->poolLayer[l];
+        const long vol = (p.type == FITRE_NO_POOL ? (long)c.outHeight * c.outWidth : (long)p.outHeight * p.outWidth) *
+                         c.outChannels * samples;
+        update_running(ctx, dampedZ + m->zztOffsets[l + 1], z + m->zOffsets[l + 1] + c.outputOffset, vol, mom, first);
+    }
+    for (int l = 0; l < m->lLayers; ++l)
+        update_running(ctx, dampedZ + m->zztOffsets[l + 1 + m->cLayers], z + m->zOffsets[l + 1 + m->cLayers],
+                       (long)m->fcLayer[l].out * samples, mom, first);
+    KFAC_ENTRY_END
+}
+
+extern "C" int fitre_kfac_speedup_lambda_delta(fitre_context *ctx, const FITRE_KFAC_INFO *info, const CNN_MODEL *m,
+                                               int samples, const real *dx, real *dampedLambda, int iterCount) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(info && m && dx && dampedLambda, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    model_check_batch(m, samples);
+    const bool first = iterCount == 0;
+    const double mom = std::sqrt(info->stats_decay);
+    for (int l = 0; l < m->cLayers; ++l) {
+        const CONV_LAYER &c = m->convLayer[l];
+        const real *delta = dx + m->zOffsets[l + 1] +
+                            (c.batchNorm == FITRE_NO_BATCH_NORM ? c.activationOffset : c.batchNormOffset);
+        update_running(ctx, dampedLambda + m->zztOffsets[l + 1], delta,
+                       (long)c.outChannels * c.outHeight * c.outWidth * samples, mom, first);
+    }
+    for (int l = 0; l < m->lLayers; ++l)
+        update_running(ctx, dampedLambda + m->zztOffsets[l + 1 + m->cLayers], dx + m->zOffsets[l + 1 + m->cLayers],
+                       (long)m->fcLayer[l].out * samples, mom, first);
+    KFAC_ENTRY_END
+}
+
+extern "C" int fitre_kfac_omega_z_damped(fitre_context *ctx, const CNN_MODEL *m, const real *dampedInput,
+                                         const real *dampedZ, int samples, real *omegaZ,
+                                         const FITRE_KFAC_INFO *info, real *devPtr) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(m && dampedInput && dampedZ && omegaZ && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    model_check_batch(m, samples);
+    omega_z_impl(ctx, m, dampedInput, dampedZ, true, samples, omegaZ, info, devPtr);
+    KFAC_ENTRY_END
+}
+
+extern "C" int fitre_kfac_lambda_delta_damped(fitre_context *ctx, const CNN_MODEL *m, const real *dampedLambda,
+                                              int samples, real *lambdaG, const FITRE_KFAC_INFO *info,
+                                              real *devPtr) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(m && dampedLambda && lambdaG && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    model_check_batch(m, samples);
+    lambda_delta_impl(ctx, m, dampedLambda, true, samples, lambdaG, info, devPtr);
+    KFAC_ENTRY_END
 }
 
 // ---------------------------------------------------------------------------------------------

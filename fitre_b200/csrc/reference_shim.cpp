@@ -251,8 +251,8 @@ void computeOmegaZ(kfac_curvature *kfac_info, cnn *model, dev_dataset *data, int
                    real *dampedZ, real *omegaZInv, int *zOffsets, int *zztOffsets, real *devPtr, real *pageLckPtr,
                    cublasContext *blasHandle, CUstream_st *curStream, cusolverDnContext *curHandle) {
     (void)zOffsets; (void)zztOffsets; (void)pageLckPtr; (void)blasHandle; (void)curStream; (void)curHandle;
-    if (!data || dampedInput || !dampedZ) {
-        fprintf(stderr, "fitre shim: computeOmegaZ on running-average inputs (inverseFreq != 1) is not built\n");
+    if (!dampedZ || (!data && !dampedInput)) {
+        fprintf(stderr, "fitre shim: computeOmegaZ needs the batch and z, or dampedInput and dampedZ\n");
         exit(-1);
     }
     const CNN_MODEL *m = M(model);
@@ -260,7 +260,10 @@ void computeOmegaZ(kfac_curvature *kfac_info, cnn *model, dev_dataset *data, int
     fill_info(m, kfac_info, &info);
     // factors into the head of the scratch, inverses block by block behind them
     real *A = devPtr, *work = devPtr + ((info.OmegaZSize + 31) / 32) * 32;
-    die(fitre_kfac_omega_z(ctx(), m, D(data), dampedZ, samples, A, &info, work), "computeOmegaZ");
+    if (dampedInput)  // running averages (solvers/kfac_inverses.cu:479-489)
+        die(fitre_kfac_omega_z_damped(ctx(), m, dampedInput, dampedZ, samples, A, &info, work), "computeOmegaZ");
+    else
+        die(fitre_kfac_omega_z(ctx(), m, D(data), dampedZ, samples, A, &info, work), "computeOmegaZ");
     for (int l = 0; l < m->cLayers + m->lLayers; ++l) {
         int a, g;
         block_sizes(m, l, &a, &g);
@@ -274,15 +277,18 @@ void computeLambdaDelta(kfac_curvature *kfac_info, cnn *model, int samples, real
                         real *lambdaGInv, int *zOffsets, int *zztOffsets, real *devPtr, real *pageLckPtr,
                         cublasContext *blasHandle, CUstream_st *curStream, cusolverDnContext *curHandle) {
     (void)zOffsets; (void)zztOffsets; (void)pageLckPtr; (void)blasHandle; (void)curStream; (void)curHandle;
-    if (!dx || dampedLambda) {
-        fprintf(stderr, "fitre shim: computeLambdaDelta on running-average inputs (inverseFreq != 1) is not built\n");
+    if (!dx && !dampedLambda) {
+        fprintf(stderr, "fitre shim: computeLambdaDelta needs dx or dampedLambda\n");
         exit(-1);
     }
     const CNN_MODEL *m = M(model);
     FITRE_KFAC_INFO info{};
     fill_info(m, kfac_info, &info);
     real *G = devPtr, *work = devPtr + ((info.LambdaGSize + 31) / 32) * 32;
-    die(fitre_kfac_lambda_delta(ctx(), m, dx, samples, G, &info, work), "computeLambdaDelta");
+    if (dampedLambda)
+        die(fitre_kfac_lambda_delta_damped(ctx(), m, dampedLambda, samples, G, &info, work), "computeLambdaDelta");
+    else
+        die(fitre_kfac_lambda_delta(ctx(), m, dx, samples, G, &info, work), "computeLambdaDelta");
     for (int l = 0; l < m->cLayers + m->lLayers; ++l) {
         int a, g;
         block_sizes(m, l, &a, &g);
@@ -290,6 +296,31 @@ void computeLambdaDelta(kfac_curvature *kfac_info, cnn *model, int samples, real
                                       info.regLambda, info.dampGamma),
             "computeLambdaDelta (inverse)");
     }
+    cudaDeviceSynchronize();
+}
+// solvers/kfac_inverses.h: the running-average variant
+void updateRunningStats(real *src, real *update, int numElements, real momentum) {
+    die(fitre_update_running_stats(ctx(), src, update, numElements, momentum), "updateRunningStats");
+    cudaDeviceSynchronize();
+}
+void computeSpeedUpOmegaZ(kfac_curvature *kfac_info, cnn *model, dev_dataset *data, int samples, real *z,
+                          int *zOffsets, real *dampedInput, real *dampedZ, int *zztOffsets, int iterCount) {
+    (void)zOffsets; (void)zztOffsets;
+    const CNN_MODEL *m = M(model);
+    FITRE_KFAC_INFO info{};
+    fill_info(m, kfac_info, &info);
+    die(fitre_kfac_speedup_omega_z(ctx(), &info, m, D(data), samples, z, dampedInput, dampedZ, iterCount),
+        "computeSpeedUpOmegaZ");
+    cudaDeviceSynchronize();
+}
+void computeSpeedUpLambdaDelta(kfac_curvature *kfac_info, cnn *model, int samples, real *dx, real *dampedLambda,
+                               int *zOffsets, int *zztOffsets, int iterCount) {
+    (void)zOffsets; (void)zztOffsets;
+    const CNN_MODEL *m = M(model);
+    FITRE_KFAC_INFO info{};
+    fill_info(m, kfac_info, &info);
+    die(fitre_kfac_speedup_lambda_delta(ctx(), &info, m, samples, dx, dampedLambda, iterCount),
+        "computeSpeedUpLambdaDelta");
     cudaDeviceSynchronize();
 }
 void computeNaturalGradient(cnn *model, kfac_curvature *kfacInfo, real *devPtr, real *hostPtr) {

@@ -405,7 +405,7 @@ struct Rng {
 
 struct TrLayout {
     long indices, uniforms, A, Ainv, G, Ginv, gradient, distGradient, prevWeights, nGradient, z, dx,
-        distDX, probs, errors, dist1, dist2, distTarget, scratch, total;
+        distDX, probs, errors, dist1, dist2, distTarget, dInput, dZ, dLambda, scratch, total;
 };
 TrLayout tr_layout(const CNN_MODEL *m, const DEVICE_DATASET *data, const FITRE_KFAC_INFO &info) {
     TrLayout L{};
@@ -434,6 +434,11 @@ TrLayout tr_layout(const CNN_MODEL *m, const DEVICE_DATASET *data, const FITRE_K
     L.dist1 = take(md);
     L.dist2 = take(md);
     L.distTarget = take(B);
+    if (info.inverseFreq > 1) {  // running averages of the "speed-up" variant
+        L.dInput = take(B * data->features);
+        L.dZ = take(m->zztSize);
+        L.dLambda = take(m->zztSize);
+    }
     long need = std::max(fitre_cnn_gradient_mem_required(m), fitre_quadratic_model_mem_required(m));
     need = std::max(need, fitre_kfac_mem_required(m));
     need = std::max(need, fitre_kfac_invert_factors_mem_required(m));
@@ -447,9 +452,11 @@ TrLayout tr_layout(const CNN_MODEL *m, const DEVICE_DATASET *data, const FITRE_K
 }  // namespace
 }  // namespace fitre
 
-extern "C" long fitre_trust_region_kfac_mem_required(const CNN_MODEL *m, const DEVICE_DATASET *data) {
+extern "C" long fitre_trust_region_kfac_mem_required(const CNN_MODEL *m, const DEVICE_DATASET *data,
+                                                     const FITRE_KFAC_INFO *kfacInfo) {
     if (!m || !data) return -1;
     FITRE_KFAC_INFO info{};
+    if (kfacInfo) info = *kfacInfo;
     if (fitre_kfac_storage_indices(m, &info) != FITRE_OK) return -1;
     return tr_layout(m, data, info).total;
 }
@@ -465,8 +472,6 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
     FITRE_REQUIRE(data->trainSetX && data->trainSetY && data->weights && data->sampledTrainX &&
                       data->sampledTrainY,
                   FITRE_ERR_BAD_ARG, "data set pointers missing");
-    FITRE_REQUIRE(kfacInfo->inverseFreq <= 1, FITRE_ERR_UNSUPPORTED,
-                  "only inverseFreq == 1 (factors inverted every minibatch) is built");
     FITRE_RC(fitre_model_validate(m));
     FITRE_RC(fitre_kfac_storage_indices(m, kfacInfo));
     const TrLayout L = tr_layout(m, data, *kfacInfo);
@@ -478,6 +483,10 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
            *dx = base + L.dx, *distDX = base + L.distDX, *probs = base + L.probs,
            *errors = base + L.errors, *dist1 = base + L.dist1, *dist2 = base + L.dist2,
            *distTarget = base + L.distTarget, *work = base + L.scratch;
+    const int invFreq = kfacInfo->inverseFreq > 1 ? kfacInfo->inverseFreq : 1;
+    double *dInput = invFreq > 1 ? base + L.dInput : nullptr, *dZ = invFreq > 1 ? base + L.dZ : nullptr,
+           *dLambda = invFreq > 1 ? base + L.dLambda : nullptr;
+    int total_mb = 0;
     SCRATCH_AREA inner = *scratch;
     inner.nextDevPtr = work;
 
@@ -525,9 +534,24 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
             cnn_backward(ctx, m, data, work, z, distGradient, distDX, dist1, dist2, B);
 
             // factors and their damped inverses (:404-411, solvers/kfac_inverses.cu:450-630,759-857)
-            FITRE_RC(fitre_kfac_omega_z(ctx, m, data, z, B, A, kfacInfo, work));
-            FITRE_RC(fitre_kfac_lambda_delta(ctx, m, distDX, B, G, kfacInfo, work));
-            FITRE_RC(fitre_kfac_invert_factors(ctx, m, kfacInfo, A, Ainv, G, Ginv, work));
+            // with inverseFreq > 1: running averages every minibatch, factors on the very first minibatch from
+            // the live state and then every inverseFreq minibatches from the averages (:392-411)
+            bool refresh = true, from_avg = false;
+            if (invFreq > 1) {
+                FITRE_RC(fitre_kfac_speedup_omega_z(ctx, kfacInfo, m, data, B, z, dInput, dZ, iter + (int)offset));
+                FITRE_RC(fitre_kfac_speedup_lambda_delta(ctx, kfacInfo, m, B, distDX, dLambda, iter + (int)offset));
+                if (iter == 0 && total_mb == 0) from_avg = false;
+                else if (total_mb % invFreq == 0) from_avg = true;
+                else refresh = false;
+            }
+            if (refresh && from_avg) {
+                FITRE_RC(fitre_kfac_omega_z_damped(ctx, m, dInput, dZ, B, A, kfacInfo, work));
+                FITRE_RC(fitre_kfac_lambda_delta_damped(ctx, m, dLambda, B, G, kfacInfo, work));
+            } else if (refresh) {
+                FITRE_RC(fitre_kfac_omega_z(ctx, m, data, z, B, A, kfacInfo, work));
+                FITRE_RC(fitre_kfac_lambda_delta(ctx, m, distDX, B, G, kfacInfo, work));
+            }
+            if (refresh) FITRE_RC(fitre_kfac_invert_factors(ctx, m, kfacInfo, A, Ainv, G, Ginv, work));
             FITRE_RC(fitre_compute_natural_gradient(ctx, m, kfacInfo, Ainv, Ginv, gradient, nGradient, work));
 
             // quadratic models of the two candidate steps (:452-470); each call scales its direction
@@ -562,6 +586,7 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
             ++step_no;
             offset += GB;
             ++mb;
+            ++total_mb;
         }
         FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
         const double secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();

@@ -134,7 +134,7 @@ typedef struct fitre_kfac_info {
     /* knobs of the training loop (same names as the reference's struct) */
     real stats_decay, momentum;
     int checkGrad;   /* 1: also evaluate the quadratic model along the gradient and take the better */
-    int inverseFreq; /* factors are inverted every inverseFreq minibatches; this library: 1 only */
+    int inverseFreq; /* factors are refreshed and inverted every inverseFreq minibatches (<= 1: every one) */
 } FITRE_KFAC_INFO;
 
 /* solvers/params.h:11-33, field for field. */
@@ -348,6 +348,26 @@ int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, const real *
 long fitre_kfac_inverse_mem_required(int n);
 int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix, real *inverse, int n,
                               real *devPtr, real lambda, real dampGamma);
+/* The running-average ("speed-up") variant, solvers/kfac_inverses.cu:106-126 (updateRunningStats:
+ * theta <- m*theta + (1-m)*update in the reference's operation order, m == 0 copies), :386-447
+ * (computeSpeedUpOmegaZ: averages of the batch into dampedInput and of every layer's output into
+ * dampedZ at the model's zzt offsets; iterCount == 0 copies), :699-755
+ * (computeSpeedUpLambdaDelta: the same for the layer errors), and the dampedInput / dampedZ /
+ * dampedLambda branches of computeOmegaZ / computeLambdaDelta (factors from those averages).
+ * dampedInput: features*samples doubles; dampedZ, dampedLambda: model->zztSize doubles. */
+int fitre_update_running_stats(fitre_context *ctx, real *src, const real *update, long numElements,
+                               real momentum);
+int fitre_kfac_speedup_omega_z(fitre_context *ctx, const FITRE_KFAC_INFO *info, const CNN_MODEL *m,
+                               const DEVICE_DATASET *data, int samples, const real *z,
+                               real *dampedInput, real *dampedZ, int iterCount);
+int fitre_kfac_speedup_lambda_delta(fitre_context *ctx, const FITRE_KFAC_INFO *info, const CNN_MODEL *m,
+                                    int samples, const real *dx, real *dampedLambda, int iterCount);
+int fitre_kfac_omega_z_damped(fitre_context *ctx, const CNN_MODEL *m, const real *dampedInput,
+                              const real *dampedZ, int samples, real *omegaZ,
+                              const FITRE_KFAC_INFO *info, real *devPtr);
+int fitre_kfac_lambda_delta_damped(fitre_context *ctx, const CNN_MODEL *m, const real *dampedLambda,
+                                   int samples, real *lambdaG, const FITRE_KFAC_INFO *info,
+                                   real *devPtr);
 /* Every damped inverse of one KFAC step in one call: omegaZInv / lambdaGInv <- the inverses of
  * all A blocks (K' x K', K' = K + bias) and G blocks of omegaZ / lambdaG at the offsets of `info`,
  * damping info->regLambda + info->dampGamma (what the reference does block by block inside
@@ -424,18 +444,22 @@ long fitre_generalization_mem_required(const CNN_MODEL *m);
 int fitre_compute_generalization_errors(fitre_context *ctx, const CNN_MODEL *m, DEVICE_DATASET *data,
                                         SCRATCH_AREA *scratch, real *z, real *probs, real *errors,
                                         int evalType, real *likelihood, real *accuracy);
-/* solvers/kfac_trust_region.cu:94-661 (subsampledTrustRegionKFAC), inverseFreq == 1: per epoch a
+/* solvers/kfac_trust_region.cu:94-661 (subsampledTrustRegionKFAC): per epoch a
  * shuffled sweep over the training set; per minibatch gradient, sampled-label backward, A and G
  * factors with damped inverses, natural gradient, quadratic model of the KFAC direction (and of
  * the gradient when checkGrad), momentum, weight update, re-evaluation, reduction ratio, radius
  * update and the reference's revert rule; after each epoch the two generalisation sweeps.
+ * kfacInfo->inverseFreq > 1 selects the running-average variant: factors and inverses on the
+ * very first minibatch, then every inverseFreq minibatches from running averages of the layer
+ * inputs and errors (decay sqrt(stats_decay)); the natural gradient uses the latest inverses.
  * trParams->maxIters epochs; `maxMiniBatches` > 0 stops each epoch early (tests).  Random draws
  * (shuffle, augmentation, sampled labels) come from a counter-based generator seeded with `seed`,
  * identical on every rank.  `steps` (capacity stepsCap) and `epochs` (capacity maxIters) may be
  * NULL.  All device memory comes from scratch->nextDevPtr: fitre_trust_region_kfac_mem_required
- * doubles.  data->weights is updated in place; data->sampledTrainX/Y must hold 2*batch*features
+ * doubles (kfacInfo may be NULL there for inverseFreq <= 1).  data->weights is updated in place; data->sampledTrainX/Y must hold 2*batch*features
  * and batch doubles. */
-long fitre_trust_region_kfac_mem_required(const CNN_MODEL *m, const DEVICE_DATASET *data);
+long fitre_trust_region_kfac_mem_required(const CNN_MODEL *m, const DEVICE_DATASET *data,
+                                          const FITRE_KFAC_INFO *kfacInfo);
 int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL *m, DEVICE_DATASET *data,
                                        FITRE_KFAC_INFO *kfacInfo, TRUST_REGION_PARAMS *trParams,
                                        SCRATCH_AREA *scratch, unsigned long long seed, int enableDA,

@@ -1289,8 +1289,20 @@ int ora_kfac_storage_indices(const CNN_MODEL *m, FITRE_KFAC_INFO *info) {
 
 /* A factors, undamped: conv (1/N) P~'P~ with P~ = [im2col(X)/(Ho*Wo), 1] (:515-540);
  * FC (1/N) z~ z~' with z~ = [z; 1] (:592-622).  N is the global batch. */
+static void omega_z_impl(const ORA_ENV *env, const CNN_MODEL *m, const double *batch, const double *z,
+                         int packed, int n, double *omegaZ, const FITRE_KFAC_INFO *info);
 void ora_kfac_omega_z(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
                       const double *z, int n, double *omegaZ, const FITRE_KFAC_INFO *info) {
+    omega_z_impl(env, m, batch, z, 0, n, omegaZ, info);
+}
+/* packed != 0: inputs are the running averages of the speed-up variant, layer l reading
+ * dampedZ + zztOffsets[l] (solvers/kfac_inverses.cu:479-489,553-575) */
+void ora_kfac_omega_z_damped(const ORA_ENV *env, const CNN_MODEL *m, const double *dampedInput,
+                             const double *dampedZ, int n, double *omegaZ, const FITRE_KFAC_INFO *info) {
+    omega_z_impl(env, m, dampedInput, dampedZ, 1, n, omegaZ, info);
+}
+static void omega_z_impl(const ORA_ENV *env, const CNN_MODEL *m, const double *batch, const double *z,
+                         int packed, int n, double *omegaZ, const FITRE_KFAC_INFO *info) {
     double Ng = (double)n * env_world(env);
     for (int l = 0; l < m->cLayers; l++) {
         const CONV_LAYER *c = &m->convLayer[l];
@@ -1298,8 +1310,8 @@ void ora_kfac_omega_z(const ORA_ENV *env, const CNN_MODEL *m, const double *batc
         long K = (long)c->inChannels * c->kSize * c->kSize;
         long Kb = K + (m->bias != 0 ? 1 : 0);
         double *cols = xmalloc(M * Kb);
-        ora_im2col(layer_input(m, batch, z, l), n, c->inChannels, c->height, c->width, c->kSize,
-                   c->padding, c->stride, cols);
+        const double *xin = (packed && l > 0) ? z + m->zztOffsets[l] : layer_input(m, batch, z, l);
+        ora_im2col(xin, n, c->inChannels, c->height, c->width, c->kSize, c->padding, c->stride, cols);
         double sc = 1. / (double)(c->outHeight * c->outWidth);
         for (long i = 0; i < M * K; i++) cols[i] *= sc;
         if (m->bias != 0)
@@ -1313,7 +1325,8 @@ void ora_kfac_omega_z(const ORA_ENV *env, const CNN_MODEL *m, const double *batc
     const CONV_LAYER *lc = &m->convLayer[m->cLayers - 1];
     for (int l = 0; l < m->lLayers; l++) {
         const FC_LAYER *f = &m->fcLayer[l];
-        const double *zin = z + m->zOffsets[m->cLayers + l] + (l == 0 ? lc->outputOffset : 0);
+        const double *zin = packed ? z + m->zztOffsets[m->cLayers + l]
+                                   : z + m->zOffsets[m->cLayers + l] + (l == 0 ? lc->outputOffset : 0);
         long R = f->in + (m->bias != 0 ? 1 : 0);
         double *zm = xmalloc(R * n);
         for (int j = 0; j < n; j++) {
@@ -1329,13 +1342,24 @@ void ora_kfac_omega_z(const ORA_ENV *env, const CNN_MODEL *m, const double *batc
 }
 
 /* G factors, undamped: conv (N*Ho*Wo) d'd (:808-816), FC N d d' (:839-849). */
+static void lambda_delta_impl(const ORA_ENV *env, const CNN_MODEL *m, const double *dx, int packed, int n,
+                              double *lambdaG, const FITRE_KFAC_INFO *info);
 void ora_kfac_lambda_delta(const ORA_ENV *env, const CNN_MODEL *m, const double *dx, int n,
                            double *lambdaG, const FITRE_KFAC_INFO *info) {
+    lambda_delta_impl(env, m, dx, 0, n, lambdaG, info);
+}
+void ora_kfac_lambda_delta_damped(const ORA_ENV *env, const CNN_MODEL *m, const double *dampedLambda, int n,
+                                  double *lambdaG, const FITRE_KFAC_INFO *info) {
+    lambda_delta_impl(env, m, dampedLambda, 1, n, lambdaG, info);
+}
+static void lambda_delta_impl(const ORA_ENV *env, const CNN_MODEL *m, const double *dx, int packed, int n,
+                              double *lambdaG, const FITRE_KFAC_INFO *info) {
     double Ng = (double)n * env_world(env);
     for (int l = 0; l < m->cLayers; l++) {
         const CONV_LAYER *c = &m->convLayer[l];
-        const double *d = dx + m->zOffsets[l + 1] +
-                          (c->batchNorm == FITRE_NO_BATCH_NORM ? c->activationOffset : c->batchNormOffset);
+        const double *d = packed ? dx + m->zztOffsets[l + 1]
+                                 : dx + m->zOffsets[l + 1] + (c->batchNorm == FITRE_NO_BATCH_NORM
+                                                                  ? c->activationOffset : c->batchNormOffset);
         long M = (long)n * c->outHeight * c->outWidth;
         double *G = lambdaG + info->LambdaGOffsets[l];
         ora_gemm(1, 0, c->outChannels, c->outChannels, M, 1.0, d, M, d, M, 0.0, G, c->outChannels);
@@ -1345,12 +1369,60 @@ void ora_kfac_lambda_delta(const ORA_ENV *env, const CNN_MODEL *m, const double 
     }
     for (int l = 0; l < m->lLayers; l++) {
         const FC_LAYER *f = &m->fcLayer[l];
-        const double *d = dx + m->zOffsets[m->cLayers + l + 1];
+        const double *d = packed ? dx + m->zztOffsets[m->cLayers + l + 1] : dx + m->zOffsets[m->cLayers + l + 1];
         double *G = lambdaG + info->LambdaGOffsets[m->cLayers + l];
         ora_gemm(0, 1, f->out, f->out, n, 1.0, d, f->out, d, f->out, 0.0, G, f->out);
         env_allreduce(env, G, (long)f->out * f->out);
         for (long i = 0; i < (long)f->out * f->out; i++) G[i] *= Ng;
     }
+}
+
+/* solvers/kfac_inverses.cu:106-126 (updateRunningStats): theta *= m/(1-m); theta += update;
+ * theta *= 1-m; momentum 0 copies. */
+void ora_update_running_stats(double *src, const double *update, long n, double momentum) {
+    if (momentum != 0) {
+        double a = momentum / (1. - momentum), b = 1. - momentum;
+        for (long i = 0; i < n; i++) src[i] = (src[i] * a + update[i]) * b;
+    } else {
+        memcpy(src, update, sizeof(double) * (size_t)n);
+    }
+}
+static void running_or_copy(double *dst, const double *src, long n, double mom, int first) {
+    if (first) memcpy(dst, src, sizeof(double) * (size_t)n);
+    else ora_update_running_stats(dst, src, n, mom);
+}
+/* :386-447 (computeSpeedUpOmegaZ): running averages of the batch and of every layer's output */
+void ora_kfac_speedup_omega_z(const FITRE_KFAC_INFO *info, const CNN_MODEL *m, const double *batch, long features,
+                              int n, const double *z, double *dampedInput, double *dampedZ, int iterCount) {
+    double mom = sqrt(info->stats_decay);
+    int first = iterCount == 0;
+    running_or_copy(dampedInput, batch, features * n, mom, first);
+    for (int l = 0; l < m->cLayers; l++) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        const POOL_LAYER *p = &m->poolLayer[l];
+        long vol = (p->type == FITRE_NO_POOL ? (long)c->outHeight * c->outWidth : (long)p->outHeight * p->outWidth) *
+                   c->outChannels * n;
+        running_or_copy(dampedZ + m->zztOffsets[l + 1], z + m->zOffsets[l + 1] + c->outputOffset, vol, mom, first);
+    }
+    for (int l = 0; l < m->lLayers; l++)
+        running_or_copy(dampedZ + m->zztOffsets[l + 1 + m->cLayers], z + m->zOffsets[l + 1 + m->cLayers],
+                        (long)m->fcLayer[l].out * n, mom, first);
+}
+/* :699-755 (computeSpeedUpLambdaDelta): running averages of every layer's errors */
+void ora_kfac_speedup_lambda_delta(const FITRE_KFAC_INFO *info, const CNN_MODEL *m, int n, const double *dx,
+                                   double *dampedLambda, int iterCount) {
+    double mom = sqrt(info->stats_decay);
+    int first = iterCount == 0;
+    for (int l = 0; l < m->cLayers; l++) {
+        const CONV_LAYER *c = &m->convLayer[l];
+        const double *delta = dx + m->zOffsets[l + 1] +
+                              (c->batchNorm == FITRE_NO_BATCH_NORM ? c->activationOffset : c->batchNormOffset);
+        running_or_copy(dampedLambda + m->zztOffsets[l + 1], delta,
+                        (long)c->outChannels * c->outHeight * c->outWidth * n, mom, first);
+    }
+    for (int l = 0; l < m->lLayers; l++)
+        running_or_copy(dampedLambda + m->zztOffsets[l + 1 + m->cLayers], dx + m->zOffsets[l + 1 + m->cLayers],
+                        (long)m->fcLayer[l].out * n, mom, first);
 }
 
 /* inverse = (matrix + (lambda + gamma) I)^-1 by Cholesky factorisation and two triangular solves
@@ -1636,7 +1708,13 @@ int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, con
     memset(prev, 0, sizeof(double) * (size_t)P);
     ora_init_batch_norm_data(m, z);
     unsigned long long s = seed;
-    int step_no = 0, rc = 0;
+    int step_no = 0, rc = 0, total_mb = 0;
+    double *dInput = NULL, *dZ = NULL, *dLambda = NULL;
+    if (info->inverseFreq > 1) {
+        dInput = xmalloc(feat * B);
+        dZ = xmalloc(m->zztSize);
+        dLambda = xmalloc(m->zztSize);
+    }
     for (int iter = 0; iter < tr->maxIters && rc == 0; iter++) {
         for (long i = 0; i < trainN; i++) idx[i] = (int)i;
         for (long i = trainN - 1; i > 0; i--) {
@@ -1658,9 +1736,24 @@ int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, con
             axpy(P, info->regLambda, weights, gradient);
             ora_distribution_errors(env, probs, u + 3L * B, B, numClasses, distTarget, dist1);
             ora_cnn_backward(env, m, batch, weights, z, distGradient, distDX, dist1, B);
-            ora_kfac_omega_z(env, m, batch, z, B, A, info);
-            ora_kfac_lambda_delta(env, m, distDX, B, G, info);
-            for (int l = 0; l < layers && rc == 0; l++) {
+            /* :392-411: running averages every minibatch; factors and inverses on the very first
+             * minibatch from the live state, afterwards every inverseFreq minibatches from the averages */
+            int refresh = 1, from_avg = 0;
+            if (info->inverseFreq > 1) {
+                ora_kfac_speedup_omega_z(info, m, batch, feat, B, z, dInput, dZ, iter + (int)offset);
+                ora_kfac_speedup_lambda_delta(info, m, B, distDX, dLambda, iter + (int)offset);
+                if (iter == 0 && total_mb == 0) from_avg = 0;
+                else if (total_mb % info->inverseFreq == 0) from_avg = 1;
+                else refresh = 0;
+            }
+            if (refresh && from_avg) {
+                ora_kfac_omega_z_damped(env, m, dInput, dZ, B, A, info);
+                ora_kfac_lambda_delta_damped(env, m, dLambda, B, G, info);
+            } else if (refresh) {
+                ora_kfac_omega_z(env, m, batch, z, B, A, info);
+                ora_kfac_lambda_delta(env, m, distDX, B, G, info);
+            }
+            for (int l = 0; refresh && l < layers && rc == 0; l++) {
                 int a, g;
                 layer_block_sizes(m, l, &a, &g);
                 rc |= ora_kfac_matrix_inverse(A + info->OmegaZOffsets[l], Ai + info->OmegaZOffsets[l], a,
@@ -1699,6 +1792,7 @@ int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, con
             step_no++;
             offset += GB;
             mb++;
+            total_mb++;
         }
         if (rc) break;
         FITRE_TR_EPOCH ep;
@@ -1715,5 +1809,6 @@ int ora_subsampled_trust_region_kfac(const ORA_ENV *env, const CNN_MODEL *m, con
     free(batch); free(labels); free(u); free(ug); free(z); free(dx); free(distDX); free(probs); free(errors);
     free(dist1); free(distTarget); free(gradient); free(distGradient); free(prev); free(ngrad);
     free(A); free(Ai); free(G); free(Gi); free(idx);
+    free(dInput); free(dZ); free(dLambda);
     return rc;
 }

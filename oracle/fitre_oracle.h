@@ -119,6 +119,17 @@ void ora_kfac_omega_z(const ORA_ENV *env, const CNN_MODEL *m, const double *batc
 void ora_kfac_lambda_delta(const ORA_ENV *env, const CNN_MODEL *m, const double *dx, int n,
                            double *lambdaG, const FITRE_KFAC_INFO *info);
 
+/* the running-average ("speed-up") variant: solvers/kfac_inverses.cu:106-126,386-447,699-755 */
+void ora_update_running_stats(double *src, const double *update, long n, double momentum);
+void ora_kfac_speedup_omega_z(const FITRE_KFAC_INFO *info, const CNN_MODEL *m, const double *batch, long features,
+                              int n, const double *z, double *dampedInput, double *dampedZ, int iterCount);
+void ora_kfac_speedup_lambda_delta(const FITRE_KFAC_INFO *info, const CNN_MODEL *m, int n, const double *dx,
+                                   double *dampedLambda, int iterCount);
+void ora_kfac_omega_z_damped(const ORA_ENV *env, const CNN_MODEL *m, const double *dampedInput,
+                             const double *dampedZ, int n, double *omegaZ, const FITRE_KFAC_INFO *info);
+void ora_kfac_lambda_delta_damped(const ORA_ENV *env, const CNN_MODEL *m, const double *dampedLambda, int n,
+                                  double *lambdaG, const FITRE_KFAC_INFO *info);
+
 int ora_kfac_matrix_inverse(const double *matrix, double *inverse, int n, double lambda,
                             double gamma);
 void ora_natural_gradient(const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const double *omegaZInv,

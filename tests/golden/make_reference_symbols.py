@@ -18,7 +18,8 @@ FUNCTIONS = ["computeCNNGradient", "cnnForwardMemRequired", "cnnForward", "cnnBa
              "cnnROpBackwardMemRequired", "cnnROpBackward", "computeQuadraticModel", "evaluateCNNModel",
              "computeAccuracy", "computeTestGeneralizationErrors", "computeTrainGeneralizationErrors",
              "computeDistributionErrors", "augmentData", "selectColumnMatrix",
-             "computeKFACStorageIndices", "computeOmegaZ", "computeLambdaDelta", "computeNaturalGradient"]
+             "computeKFACStorageIndices", "computeOmegaZ", "computeLambdaDelta", "computeNaturalGradient",
+             "updateRunningStats", "computeSpeedUpOmegaZ", "computeSpeedUpLambdaDelta"]
 
 
 def main():

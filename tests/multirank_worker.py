@@ -78,7 +78,7 @@ def run_loop(backend, rank, world, out):
         W = G.dev(w)
         data = api.make_full_dataset(W, G.dev(trainX), G.dev(trainY), G.dev(testX), G.dev(testY), 10,
                                      c0.inChannels * c0.height * c0.width, model.batchSize)
-        need = _lib.load().fitre_trust_region_kfac_mem_required(C.byref(model), C.byref(data))
+        need = _lib.load().fitre_trust_region_kfac_mem_required(C.byref(model), C.byref(data), None)
         scr = api.make_scratch(torch.zeros(need, dtype=torch.float64, device="cuda"))
         steps, epochs = api.subsampledTrustRegionKFAC(ctx, model, data, info, tr, scr, seed=5, stepsCap=64)
         np.savez(out, **pack_loop(steps, epochs, W.cpu().numpy()))

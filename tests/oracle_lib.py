@@ -75,6 +75,12 @@ def lib():
         L.ora_compute_accuracy.restype = d
         L.ora_prepare_minibatch.argtypes = [dp, dp, C.c_void_p, C.c_long, i, i, i, i, i, C.c_void_p,
                                             dp, dp]
+        KP = C.POINTER(S.KFAC_INFO)
+        L.ora_update_running_stats.argtypes = [dp, dp, C.c_long, d]
+        L.ora_kfac_speedup_omega_z.argtypes = [KP, MP, dp, C.c_long, i, dp, dp, dp, i]
+        L.ora_kfac_speedup_lambda_delta.argtypes = [KP, MP, i, dp, dp, i]
+        L.ora_kfac_omega_z_damped.argtypes = [EP, MP, dp, dp, i, dp, KP]
+        L.ora_kfac_lambda_delta_damped.argtypes = [EP, MP, dp, i, dp, KP]
         L.ora_generalization_errors.argtypes = [EP, MP, dp, dp, C.c_long, i, dp, i, dp, i,
                                                 C.POINTER(C.c_double), C.POINTER(C.c_double)]
         L.ora_subsampled_trust_region_kfac.argtypes = [

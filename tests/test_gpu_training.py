@@ -143,8 +143,8 @@ def test_cuda_generalization_errors_vs_oracle():
     assert np.array_equal(ws.z.cpu().numpy()[bo:bo + 2 * cl.outChannels], zo[bo:bo + 2 * cl.outChannels])
 
 
-@pytest.mark.parametrize("check_grad,enable_da", [(1, 1), (0, 0)])
-def test_cuda_trust_region_loop_vs_oracle(check_grad, enable_da):
+@pytest.mark.parametrize("check_grad,enable_da,inverse_freq", [(1, 1, 1), (0, 0, 1), (1, 1, 3)])
+def test_cuda_trust_region_loop_vs_oracle(check_grad, enable_da, inverse_freq):
     import torch
     import gpu_util as G
     from fitre_b200 import api, _lib
@@ -152,14 +152,14 @@ def test_cuda_trust_region_loop_vs_oracle(check_grad, enable_da):
     model, trainX, trainY, testX, testY, w = small_problem(rng)
     c = G.ctx()
     info_o, tr_o = loop_params()
-    info_o.checkGrad = check_grad
+    info_o.checkGrad, info_o.inverseFreq, info_o.stats_decay = check_grad, inverse_freq, 0.81
     wo = w.copy()
     steps_o, epochs_o = O.trust_region_kfac(model, trainX, trainY, testX, testY, wo, 10, info_o, tr_o,
                                             seed=7, enable_da=enable_da, steps_cap=64)
     info_g, tr_g = loop_params()
-    info_g.checkGrad = check_grad
+    info_g.checkGrad, info_g.inverseFreq, info_g.stats_decay = check_grad, inverse_freq, 0.81
     data, W = full_dataset(G, api, model, trainX, trainY, testX, testY, w, model.batchSize)
-    need = _lib.load().fitre_trust_region_kfac_mem_required(C.byref(model), C.byref(data))
+    need = _lib.load().fitre_trust_region_kfac_mem_required(C.byref(model), C.byref(data), C.byref(info_g))
     scr = api.make_scratch(torch.zeros(need, dtype=torch.float64, device="cuda"))
     steps_g, epochs_g = api.subsampledTrustRegionKFAC(c, model, data, info_g, tr_g, scr, seed=7,
                                                       enableDA=enable_da, stepsCap=64)
@@ -177,3 +177,53 @@ def test_cuda_trust_region_loop_vs_oracle(check_grad, enable_da):
         assert eg.testAccuracy == eo_.testAccuracy and eg.trainAccuracy == eo_.trainAccuracy
     assert G.rel(W.cpu().numpy(), wo) < 1e-7
     assert tr_g.delta == tr_o.delta
+
+
+def test_cuda_running_average_factors_vs_oracle():
+    """The speed-up variant's pieces one by one: running averages of inputs / outputs / errors over
+    three minibatches and the factors computed from them."""
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    L = _lib.load()
+    n = 6
+    for builder, kwargs in (("vgg_small", dict()), ("alexnet_small", dict(bias=True))):
+        model = getattr(nets, builder)(n, **kwargs)
+        O.finalize(model)
+        info = S.KFAC_INFO()
+        O.lib().ora_kfac_storage_indices(C.byref(model), C.byref(info))
+        info.stats_decay = 0.49
+        c0 = model.convLayer[0]
+        feat = c0.inChannels * c0.height * c0.width
+        dI_o, dZ_o, dL_o = np.zeros(feat * n), np.zeros(model.zztSize), np.zeros(model.zztSize)
+        dI, dZ, dL = G.dev(dI_o), G.dev(dZ_o), G.dev(dL_o)
+        c = G.ctx()
+        for it in range(3):
+            x, y, w, v, ncls = G.synth(model, n, seed=60 + it)
+            st = O.gradient(model, x, y, w, ncls, n)
+            run = G.GpuRun(model, x, y, w, ncls)
+            O.lib().ora_kfac_speedup_omega_z(C.byref(info), C.byref(model), x, feat, n, st.z, dI_o, dZ_o, it)
+            O.lib().ora_kfac_speedup_lambda_delta(C.byref(info), C.byref(model), n, st.dx, dL_o, it)
+            run.data.features = feat
+            c.check(L.fitre_kfac_speedup_omega_z(c.h, C.byref(info), C.byref(model), C.byref(run.data), n,
+                                                 run.ws.z.data_ptr(), dI.data_ptr(), dZ.data_ptr(), it))
+            c.check(L.fitre_kfac_speedup_lambda_delta(c.h, C.byref(info), C.byref(model), n,
+                                                      run.ws.dx.data_ptr(), dL.data_ptr(), it))
+        assert G.relmax(dI.cpu().numpy(), dI_o) < TOL and G.relmax(dZ.cpu().numpy(), dZ_o) < TOL
+        assert G.relmax(dL.cpu().numpy(), dL_o) < TOL
+        A_o, G_o = np.zeros(info.OmegaZSize), np.zeros(info.LambdaGSize)
+        env = O.make_env()
+        O.lib().ora_kfac_omega_z_damped(C.byref(env), C.byref(model), dI_o, dZ_o, n, A_o, C.byref(info))
+        O.lib().ora_kfac_lambda_delta_damped(C.byref(env), C.byref(model), dL_o, n, G_o, C.byref(info))
+        scr = G.dev(np.zeros(L.fitre_kfac_mem_required(C.byref(model))))
+        A, Gm = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+        c.check(L.fitre_kfac_omega_z_damped(c.h, C.byref(model), dI.data_ptr(), dZ.data_ptr(), n, A.data_ptr(),
+                                            C.byref(info), scr.data_ptr()))
+        c.check(L.fitre_kfac_lambda_delta_damped(c.h, C.byref(model), dL.data_ptr(), n, Gm.data_ptr(),
+                                                 C.byref(info), scr.data_ptr()))
+        assert G.rel(A.cpu().numpy(), A_o) < TOL and G.rel(Gm.cpu().numpy(), G_o) < TOL
+        # updateRunningStats on its own
+        a, b = np.arange(10.) + 1, np.arange(10.) * 0.5
+        A1 = G.dev(a)
+        c.check(L.fitre_update_running_stats(c.h, A1.data_ptr(), G.dev(b).data_ptr(), 10, 0.7))
+        O.lib().ora_update_running_stats(a, b, 10, 0.7)
+        assert np.array_equal(A1.cpu().numpy(), a)

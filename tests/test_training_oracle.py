@@ -236,3 +236,23 @@ def test_vector_files_round_trip(tmp_path):
     lines = open(p).read().split("\n")
     assert lines[0] == "%6.10f" % v[0] and len(lines) == 258
     assert np.allclose(api.readVector(p, 257), v, atol=5.1e-11, rtol=0)
+
+
+def test_outer_loop_running_average_variant():
+    """inverseFreq 3: factors are refreshed on minibatches 0, 3, 6, ...; the run differs from the
+    every-minibatch loop after the first minibatch and equals it on the first."""
+    rng = np.random.default_rng(12)
+    model, trainX, trainY, testX, testY, w = small_problem(rng)
+    runs = []
+    for freq in (1, 3):
+        info, tr = loop_params()
+        info.inverseFreq, info.stats_decay = freq, 0.81
+        wi = w.copy()
+        steps, _ = O.trust_region_kfac(model, trainX, trainY, testX, testY, wi, 10, info, tr, seed=7,
+                                       steps_cap=64)
+        runs.append((steps, wi))
+    (s1, w1), (s3, w3) = runs
+    assert len(s1) == len(s3) == 12
+    assert abs(s1[0].modelKfac - s3[0].modelKfac) <= 1e-9 * abs(s1[0].modelKfac)
+    assert any(abs(a.modelKfac - b.modelKfac) > 1e-6 * abs(a.modelKfac) for a, b in zip(s1[1:], s3[1:]))
+    assert np.all(np.isfinite(w3))
