@@ -296,6 +296,209 @@ __global__ void reduce_out_slabs_tf32_kernel(const double *slabs, double *y, lon
     }
 }
 
+
+// =============================================================================================
+// Second form, used whenever the input channel count is a multiple of 32: no thread ever touches
+// an operand.  A pre-pass rewrites the fp64 input [C][N][W][H] as fp32 planes with the channel
+// innermost ([N][W][H][C]; TF32 head and, when compensated, tail), so that for one filter tap and
+// 32 consecutive channels the 128 rows of the im2col tile are 128-byte runs of memory: one 4-D
+// tiled TMA load (box 32 channels x TH x TW x TN positions, shifted by the tap, halo zero-filled)
+// lands them in shared memory already in the 128-byte-swizzled K-major layout tcgen05.mma reads.
+// The weight matrix is reordered to the same K order (tap-major) by its own pre-pass.  Warp 0
+// issues the TMA loads, warp 1 the MMAs (accumulator 128 x BN fp32 in TMEM), warps 2-5 only run
+// the epilogue.
+// =============================================================================================
+struct alignas(64) Tf32DirectArgs {
+    CUtensorMap amap[2][2];   // [segment][head / tail]
+    CUtensorMap wmap[2];      // [segment]; the tail rows follow at row CoutPad
+    const double *bias;
+    double *y;
+    int *err;
+    long M;
+    int nseg, N, Cout, CoutPad, Ho, Wo, pad, k, TH, TW, TN, tilesW, cchunks, nchunks, stages;
+    int iters_per_split;
+};
+
+constexpr int D_THREADS = 192;
+
+template <int BN, bool X3>
+__global__ void __launch_bounds__(D_THREADS, 1)
+conv_tf32_direct_kernel(const __grid_constant__ Tf32DirectArgs p) {
+    constexpr int NP = X3 ? 2 : 1;
+    constexpr int ABYTES = F_BM * F_KC * 4, BBYTES = BN * F_KC * 4;
+    constexpr int STAGE = NP * (ABYTES + BBYTES);
+    extern __shared__ unsigned char smraw[];
+    unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 1023) & ~(uintptr_t)1023);
+    unsigned long long *bars = (unsigned long long *)(sm + (size_t)p.stages * STAGE);
+    // bars: [0,8) stage full, [8,16) stage consumed, [16] accumulator complete
+    uint32_t *tmem_slot = (uint32_t *)(bars + 17);
+    __shared__ int abort_flag;
+    volatile int *vabort = &abort_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wt = blockIdx.x % p.tilesW, nt = blockIdx.x / p.tilesW;
+    const int w0 = wt * p.TW, n0 = nt * p.TN;
+    const int c0 = blockIdx.y * BN;
+    const int it0 = blockIdx.z * p.iters_per_split;
+    const int iters = max(0, min(p.nseg * p.nchunks - it0, p.iters_per_split));
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(bars + s), 1);
+            mbar_init(smem_u32(bars + 8 + s), 1);
+        }
+        mbar_init(smem_u32(bars + 16), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)), "r"(BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < iters; ++it) {
+                const int s = it % p.stages, fill = it / p.stages;
+                if (fill > 0 && !mbar_wait(smem_u32(bars + 8 + s), (uint32_t)((fill - 1) & 1))) {
+                    *vabort = 1;
+                    break;
+                }
+                if (*vabort) break;
+                const int g = it0 + it, seg = g / p.nchunks, ch = g - seg * p.nchunks;
+                const int tap = ch / p.cchunks, cc = ch - tap * p.cchunks;
+                const int tj = tap / p.k, ti = tap - tj * p.k;   // kernel column, kernel row
+                unsigned char *st = sm + (size_t)s * STAGE;
+                const uint32_t bar = smem_u32(bars + s);
+                mbar_expect_tx(bar, STAGE);
+                for (int part = 0; part < NP; ++part) {
+                    tma_load_4d(smem_u32(st + part * ABYTES), &p.amap[seg][part], bar, cc * F_KC, ti - p.pad,
+                                w0 + tj - p.pad, n0);
+                    tma_load_2d(smem_u32(st + NP * ABYTES + part * BBYTES), &p.wmap[seg], bar, ch * F_KC,
+                                c0 + part * p.CoutPad);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)(F_BM >> 4) << 24);
+            constexpr uint64_t kATail = ABYTES >> 4, kBTail = BBYTES >> 4;
+            for (int it = 0; it < iters; ++it) {
+                const int s = it % p.stages;
+                if (*vabort || !mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1))) {
+                    *vabort = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char *st = sm + (size_t)s * STAGE;
+                const uint64_t da = umma_desc_sw128(smem_u32(st));
+                const uint64_t db = umma_desc_sw128(smem_u32(st + NP * ABYTES));
+#pragma unroll
+                for (int k = 0; k < F_KC / 8; ++k) {
+                    const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+                    if (X3) {
+                        umma_tf32(tmem_base, da + kATail + 2 * k, db + 2 * k, idesc, acc);
+                        umma_tf32(tmem_base, da + 2 * k, db + kBTail + 2 * k, idesc, 1u);
+                        umma_tf32(tmem_base, da + 2 * k, db + 2 * k, idesc, 1u);
+                    } else {
+                        umma_tf32(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+                    }
+                }
+                umma_commit(smem_u32(bars + 8 + s));
+            }
+            if (!*vabort) umma_commit(smem_u32(bars + 16));
+        }
+    } else {
+        const int q = warp & 3;
+        const int ml = q * 32 + lane;
+        const int hl = ml % p.TH, r = ml / p.TH;
+        const int wl = r % p.TW, nl = r / p.TW;
+        if (iters > 0 && mbar_wait(smem_u32(bars + 16), 0) && !*vabort) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool ok = (n0 + nl) < p.N && (w0 + wl) < p.Wo && hl < p.Ho;
+            const long grow = ok ? ((long)(n0 + nl) * p.Wo + (w0 + wl)) * p.Ho + hl : -1;
+            double *y = p.y + (long)blockIdx.z * p.M * p.Cout;
+#pragma unroll 1
+            for (int cb = 0; cb < BN / 32; ++cb) {
+                uint32_t rr[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), rr);
+                if (grow >= 0) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int col = c0 + cb * 32 + c;
+                        if (col < p.Cout)
+                            y[(long)col * p.M + grow] =
+                                (double)__uint_as_float(rr[c]) + (p.bias ? p.bias[col] : 0.0);
+                    }
+                }
+            }
+        } else if (iters > 0) {
+            *vabort = 1;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN)
+                     : "memory");
+    }
+    if (tid == 0 && abort_flag) atomicExch(p.err, 2);
+}
+
+// in[c][p] fp64 (p = position within the channel plane, contiguous) -> hi[p][c] (and lo[p][c]) fp32,
+// TF32-rounded; 32 x 32 tiles through shared memory so that reads and writes both coalesce.
+template <bool X3>
+__global__ void split_channels_last_kernel(const double *__restrict__ in, float *__restrict__ hi,
+                                           float *__restrict__ lo, int C, long P) {
+    __shared__ double tile[32][33];
+    const long ptiles = (P + 31) / 32;
+    const long ntiles = ptiles * (C / 32);
+    for (long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const long pt = t % ptiles;
+        const int ct = (int)(t / ptiles);
+        const long p0 = pt * 32;
+        const int cbase = ct * 32;
+        for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+            const long pp = p0 + threadIdx.x;
+            tile[r][threadIdx.x] = pp < P ? in[(long)(cbase + r) * P + pp] : 0.0;
+        }
+        __syncthreads();
+        for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+            const long pp = p0 + r;
+            if (pp < P) {
+                const double x = tile[threadIdx.x][r];
+                const float h = __uint_as_float(f32_to_tf32(__double2float_rn(x)));
+                hi[pp * C + cbase + threadIdx.x] = h;
+                if (X3) lo[pp * C + cbase + threadIdx.x] = __uint_as_float(f32_to_tf32(__double2float_rn(x - (double)h)));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// weights W[cout][c*kk + tap] fp64 -> out[cout][tap*Cin + c] fp32 (TF32 head; tail rows at
+// cout + CoutPad when parts == 2; padding rows zero)
+__global__ void split_weights_tap_major_kernel(const double *__restrict__ in, float *__restrict__ out, int Cin,
+                                               int kk, int Cout, int CoutPad, int parts) {
+    const long K = (long)Cin * kk;
+    const long n = K * (parts == 2 ? CoutPad : Cout);
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const long co = i / K, q = i - co * K;          // q = tap * Cin + c in the output
+        const int tap = (int)(q / Cin), c = (int)(q - (long)tap * Cin);
+        const double w = co < Cout ? in[co * K + (long)c * kk + tap] : 0.0;
+        const float h = __uint_as_float(f32_to_tf32(__double2float_rn(w)));
+        out[i] = h;
+        if (parts == 2) out[K * CoutPad + i] = __uint_as_float(f32_to_tf32(__double2float_rn(w - (double)h)));
+    }
+}
+
 }  // namespace
 
 void conv_tf32_init_attributes() {
@@ -303,30 +506,144 @@ void conv_tf32_init_attributes() {
     FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_kernel<5, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
     FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
     FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_direct_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_direct_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_direct_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_direct_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
 }
 
 namespace {
-int tf32_split(long M, int Cout, int iters) {
-    const long tiles = ((M + F_BM - 1) / F_BM) * ((Cout + F_BN - 1) / F_BN);
+int tf32_split_bn(long M, int Cout, int iters, int bn) {
+    const long tiles = ((M + F_BM - 1) / F_BM) * ((Cout + bn - 1) / bn);
     if (tiles >= 296) return 1;
     return (int)std::max<long>(1, std::min<long>(std::min<long>((592 + tiles - 1) / tiles, 8), iters / 8));
 }
-inline long cout_pad(int Cout) { return ((long)Cout + F_BN - 1) / F_BN * F_BN; }
-}  // namespace
+int tf32_split(long M, int Cout, int iters) { return tf32_split_bn(M, Cout, iters, F_BN); }
+inline long cout_pad(int Cout) { return ((long)Cout + 127) / 128 * 128; }
+inline long up32(long n) { return (n + 31) / 32 * 32; }
 
-// doubles of scratch: split-K slabs (small grids only) + the TF32 heads and tails of two weight
-// matrices (2 segments x 2 parts x K x CoutPad floats)
-long conv_fprop_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+struct Tf32Scratch {
+    long slabs, weights, inputs, total;   // offsets in doubles
+    int sk_max;
+};
+// split-K slabs (small grids only) | TF32 heads and tails of two weight matrices | fp32
+// channels-last heads and tails of two inputs (direct kernel only)
+Tf32Scratch tf32_scratch_layout(int N, int Cin, int H, int W, int k, int pad, int Cout) {
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
     const long K = (long)Cin * k * k, M = (long)N * Ho * Wo;
-    const int sk = tf32_split(M, Cout, 2 * (int)((K + F_KC - 1) / F_KC));
-    return (sk > 1 ? sk * M * Cout : 0) + 2 * K * cout_pad(Cout) + 64;
+    Tf32Scratch L{};
+    const int iters = 2 * (int)((K + F_KC - 1) / F_KC);
+    L.sk_max = std::max(tf32_split_bn(M, Cout, iters, 64), tf32_split_bn(M, Cout, iters, 128));
+    L.slabs = 0;
+    L.weights = up32(L.sk_max > 1 ? (long)L.sk_max * M * Cout : 0);
+    L.inputs = L.weights + up32(2 * K * cout_pad(Cout));
+    L.total = L.inputs + ((Cin % 32 == 0) ? up32(2L * Cin * N * H * W) : 0) + 64;
+    return L;
 }
+}  // namespace
+
+long conv_fprop_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    return tf32_scratch_layout(N, Cin, H, W, k, pad, Cout).total;
+}
+
+namespace {
+// The expander-free form; false when the shape does not fit it (the caller then tries the other).
+bool conv_fprop_tf32_direct(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
+                            int N, int Cin, int H, int W, int k, int pad, int Cout, double *scratch) {
+    if (Cin % 32 != 0 || k < 1 || k > 7) return false;
+    const bool x3 = ctx->precision == FITRE_PRECISION_TF32X3;
+    const int parts = x3 ? 2 : 1;
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    if (Ho < 1 || Wo < 1 || Ho > F_BM || F_BM % Ho) return false;
+    const int TH = Ho;
+    const int TW = std::min(Wo, F_BM / TH);
+    if (Wo % TW || F_BM % (TH * TW)) return false;
+    const int TN = F_BM / (TH * TW);
+    if (TH > 256 || TW > 256 || TN > 256) return false;
+    const Tf32Scratch L = tf32_scratch_layout(N, Cin, H, W, k, pad, Cout);
+    const int BN = (Cout % 128 == 0) ? 128 : 64;
+    const int K = Cin * k * k;
+    Tf32DirectArgs a{};
+    a.nseg = nseg; a.N = N; a.Cout = Cout; a.Ho = Ho; a.Wo = Wo; a.pad = pad; a.k = k;
+    a.TH = TH; a.TW = TW; a.TN = TN;
+    a.CoutPad = (int)cout_pad(Cout);
+    a.tilesW = Wo / TW;
+    a.cchunks = Cin / F_KC;
+    a.nchunks = k * k * a.cchunks;
+    a.M = (long)N * Ho * Wo;
+    a.err = (int *)(ctx->dscal + 4000);
+    const int stageBytes = parts * (F_BM * F_KC * 4 + BN * F_KC * 4);
+    const int fixed = 1024 + 17 * 8 + 16;
+    a.stages = std::min((kSmemFull - fixed) / stageBytes, 6);
+    if (a.stages < 2) return false;
+    const int iters = nseg * a.nchunks;
+    int SK = std::min(L.sk_max, tf32_split_bn(a.M, Cout, iters, BN));
+    a.iters_per_split = (iters + SK - 1) / SK;
+    SK = (iters + a.iters_per_split - 1) / a.iters_per_split;
+    double *slabs = scratch + L.slabs;
+    a.y = SK > 1 ? slabs : y;
+    a.bias = SK > 1 ? nullptr : bias;
+    const long P = (long)N * W * H;
+    for (int s = 0; s < nseg; ++s) {
+        float *ws = (float *)(scratch + L.weights) + (long)s * 2 * K * a.CoutPad;
+        const long nw = (long)K * a.CoutPad;
+        split_weights_tap_major_kernel<<<(int)std::min<long>((nw + 255) / 256, 1184), 256, 0, ctx->stream>>>(
+            segs[s].w, ws, Cin, k * k, Cout, a.CoutPad, parts);
+        check_launch(ctx, "split_weights_tap_major_kernel");
+        float *xh = (float *)(scratch + L.inputs) + (long)s * 2 * Cin * P, *xl = xh + (long)Cin * P;
+        const long ntiles = ((P + 31) / 32) * (Cin / 32);
+        const int blocks = (int)std::min<long>(ntiles, 148 * 16);
+        if (x3)
+            split_channels_last_kernel<true><<<blocks, dim3(32, 8), 0, ctx->stream>>>(segs[s].x, xh, xl, Cin, P);
+        else
+            split_channels_last_kernel<false><<<blocks, dim3(32, 8), 0, ctx->stream>>>(segs[s].x, xh, xl, Cin, P);
+        check_launch(ctx, "split_channels_last_kernel");
+        cuuint64_t xd[4] = {(cuuint64_t)Cin, (cuuint64_t)H, (cuuint64_t)W, (cuuint64_t)N};
+        cuuint64_t xs[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)H * Cin * 4, (cuuint64_t)W * H * Cin * 4};
+        cuuint32_t xb[4] = {(cuuint32_t)F_KC, (cuuint32_t)TH, (cuuint32_t)TW, (cuuint32_t)TN};
+        for (int part = 0; part < parts; ++part)
+            if (!encode(&a.amap[s][part], part ? xl : xh, 4, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_DATA_TYPE_FLOAT32))
+                return false;
+        cuuint64_t wd[2] = {(cuuint64_t)K, (cuuint64_t)(x3 ? 2 * a.CoutPad : Cout)};
+        cuuint64_t wsb[1] = {(cuuint64_t)K * 4};
+        cuuint32_t wb[2] = {(cuuint32_t)F_KC, (cuuint32_t)BN};
+        if (!encode(&a.wmap[s], ws, 2, wd, wsb, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_DATA_TYPE_FLOAT32))
+            return false;
+    }
+    const int tilesN = (N + TN - 1) / TN;
+    dim3 grid((unsigned)(a.tilesW * tilesN), (unsigned)((Cout + BN - 1) / BN), (unsigned)SK);
+    const int smem = a.stages * stageBytes + fixed;
+    {
+        ProfScope prof(ctx, PROF_CONV_IGEMM, 2.0 * (double)a.M * K * Cout * nseg);
+        if (BN == 128 && x3)
+            conv_tf32_direct_kernel<128, true><<<grid, D_THREADS, smem, ctx->stream>>>(a);
+        else if (BN == 128)
+            conv_tf32_direct_kernel<128, false><<<grid, D_THREADS, smem, ctx->stream>>>(a);
+        else if (x3)
+            conv_tf32_direct_kernel<64, true><<<grid, D_THREADS, smem, ctx->stream>>>(a);
+        else
+            conv_tf32_direct_kernel<64, false><<<grid, D_THREADS, smem, ctx->stream>>>(a);
+        check_launch(ctx, "conv_tf32_direct_kernel");
+        if (SK > 1) {
+            const long n = a.M * Cout;
+            reduce_out_slabs_tf32_kernel<<<(int)std::min<long>((n + 255) / 256, 1184), 256, 0, ctx->stream>>>(
+                slabs, y, a.M, Cout, SK, bias);
+            check_launch(ctx, "reduce_out_slabs_tf32_kernel");
+        }
+    }
+    return true;
+}
+}  // namespace
 
 bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
                      int N, int Cin, int H, int W, int k, int pad, int Cout, double *scratch) {
     if (!encode_fn() || !scratch) return false;
+    for (int s = 0; s < nseg; ++s)
+        if ((uintptr_t)segs[s].x & 15) return false;
+    if (conv_fprop_tf32_direct(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout, scratch)) return true;
     if (k != 3 && k != 5) return false;
+    const Tf32Scratch L = tf32_scratch_layout(N, Cin, H, W, k, pad, Cout);
     const bool x3 = ctx->precision == FITRE_PRECISION_TF32X3;
     const int parts = x3 ? 2 : 1;
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
@@ -368,12 +685,11 @@ bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const do
     a.err = (int *)(ctx->dscal + 4000);
     // split-K for small grids (same rule of thumb as the fp64 kernel, fewer CTAs needed)
     const int iters = nseg * a.nchunks;
-    const int sk_max = tf32_split(a.M, Cout, 2 * a.nchunks);   // what the scratch was sized for
-    int SK = std::min(sk_max, tf32_split(a.M, Cout, iters));
+    int SK = std::min(L.sk_max, tf32_split(a.M, Cout, iters));   // L.sk_max: what the scratch was sized for
     a.iters_per_split = (iters + SK - 1) / SK;
     SK = (iters + a.iters_per_split - 1) / a.iters_per_split;
-    double *slabs = scratch;
-    float *w32 = (float *)(scratch + (sk_max > 1 ? (long)sk_max * a.M * Cout : 0));
+    double *slabs = scratch + L.slabs;
+    float *w32 = (float *)(scratch + L.weights);
     a.y = SK > 1 ? slabs : y;
     a.bias = SK > 1 ? nullptr : bias;
     for (int s = 0; s < nseg; ++s) {
