@@ -153,6 +153,9 @@ bool conv_wgrad_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, double *d
 // conv_tf32.cu
 void conv_tf32_init_attributes();
 long conv_fprop_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
+long conv_wgrad_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
+bool conv_wgrad_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin, int H,
+                     int W, int k, int pad, int Cout, double *scratch);
 bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
                      int N, int Cin, int H, int W, int k, int pad, int Cout, double *scratch);
 // Device-side error word (set by a kernel whose bounded wait ran out): dscal[4000] as int.

@@ -499,6 +499,184 @@ __global__ void split_weights_tap_major_kernel(const double *__restrict__ in, fl
     }
 }
 
+
+// =============================================================================================
+// Weight gradient on the same tensor cores: dW[q, cout] = sum_m patch[m, q] * err[m, cout], a plain
+// GEMM whose reduction runs over the output positions m.  Both operands are wanted K-major with m
+// contiguous.  The errors [Cout][M] already are (A tile: 2-D box 32 x 128).  The patches are written
+// once per call by a pre-pass as an fp32 matrix [K][M] (row q = (channel, tap), TF32 head and, when
+// compensated, tail), so the B tile is a 2-D box 32 x BNQ as well and every TMA load is a full
+// 128-byte-wide box starting on a 128-byte boundary.  (Reading the taps straight from the image
+// would need loads that start at h - 1, which a TMA load cannot: its innermost coordinate must sit
+// on a 16-byte boundary.)  The positions are split over blockIdx.z into slabs that a reducer sums in
+// fixed order.  Warp roles as in the forward kernel.
+// =============================================================================================
+struct alignas(64) Tf32WgradArgs {
+    CUtensorMap dmap[2][2];   // errors  [segment][head / tail]: (M, Cout)
+    CUtensorMap pmap[2][2];   // patches [segment][head / tail]: (M, K)
+    double *out;              // slabs (or dW itself when there is one split)
+    int *err;
+    int nseg, Cout, K, chunks, chunks_per_split, stages;
+};
+
+template <int BNQ, bool X3>
+__global__ void __launch_bounds__(D_THREADS, 1)
+wgrad_tf32_kernel(const __grid_constant__ Tf32WgradArgs p) {
+    constexpr int NP = X3 ? 2 : 1;
+    constexpr int ABYTES = F_BM * F_KC * 4, BBYTES = BNQ * F_KC * 4;
+    constexpr int STAGE = NP * (ABYTES + BBYTES);
+    extern __shared__ unsigned char smraw[];
+    unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 1023) & ~(uintptr_t)1023);
+    unsigned long long *bars = (unsigned long long *)(sm + (size_t)p.stages * STAGE);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 17);
+    __shared__ int abort_flag;
+    volatile int *vabort = &abort_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q0 = blockIdx.x * BNQ, co0 = blockIdx.y * F_BM;
+    const int g0 = blockIdx.z * p.chunks_per_split;
+    const int per_seg = max(0, min(p.chunks - g0, p.chunks_per_split));
+    const int iters = per_seg * p.nseg;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(bars + s), 1);
+            mbar_init(smem_u32(bars + 8 + s), 1);
+        }
+        mbar_init(smem_u32(bars + 16), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)), "r"(BNQ)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < iters; ++it) {
+                const int s = it % p.stages, fill = it / p.stages;
+                if (fill > 0 && !mbar_wait(smem_u32(bars + 8 + s), (uint32_t)((fill - 1) & 1))) {
+                    *vabort = 1;
+                    break;
+                }
+                if (*vabort) break;
+                const int seg = it / per_seg, g = g0 + (it - seg * per_seg);
+                unsigned char *st = sm + (size_t)s * STAGE;
+                const uint32_t bar = smem_u32(bars + s);
+                mbar_expect_tx(bar, STAGE);
+                for (int part = 0; part < NP; ++part) {
+                    tma_load_2d(smem_u32(st + part * ABYTES), &p.dmap[seg][part], bar, g * F_KC, co0);
+                    tma_load_2d(smem_u32(st + NP * ABYTES + part * BBYTES), &p.pmap[seg][part], bar, g * F_KC, q0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNQ >> 3) << 17) |
+                                       ((uint32_t)(F_BM >> 4) << 24);
+            constexpr uint64_t kATail = ABYTES >> 4, kBTail = BBYTES >> 4;
+            for (int it = 0; it < iters; ++it) {
+                const int s = it % p.stages;
+                if (*vabort || !mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1))) {
+                    *vabort = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char *st = sm + (size_t)s * STAGE;
+                const uint64_t da = umma_desc_sw128(smem_u32(st));
+                const uint64_t db = umma_desc_sw128(smem_u32(st + NP * ABYTES));
+#pragma unroll
+                for (int k = 0; k < F_KC / 8; ++k) {
+                    const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+                    if (X3) {
+                        umma_tf32(tmem_base, da + kATail + 2 * k, db + 2 * k, idesc, acc);
+                        umma_tf32(tmem_base, da + 2 * k, db + kBTail + 2 * k, idesc, 1u);
+                        umma_tf32(tmem_base, da + 2 * k, db + 2 * k, idesc, 1u);
+                    } else {
+                        umma_tf32(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+                    }
+                }
+                umma_commit(smem_u32(bars + 8 + s));
+            }
+            if (!*vabort) umma_commit(smem_u32(bars + 16));
+        }
+    } else {
+        const int q = warp & 3;
+        const int co = co0 + q * 32 + lane;           // this thread's output channel (tile row)
+        if (iters > 0 && mbar_wait(smem_u32(bars + 16), 0) && !*vabort) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            double *out = p.out + (long)blockIdx.z * p.K * p.Cout;
+#pragma unroll 1
+            for (int cb = 0; cb < BNQ / 32; ++cb) {
+                uint32_t rr[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), rr);
+                if (co < p.Cout) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int col = q0 + cb * 32 + c;
+                        if (col < p.K) out[(long)co * p.K + col] = (double)__uint_as_float(rr[c]);
+                    }
+                }
+            }
+        } else if (iters > 0) {
+            *vabort = 1;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BNQ)
+                     : "memory");
+    }
+    if (tid == 0 && abort_flag) atomicExch(p.err, 2);
+}
+
+// x fp64 [C][N][W][H] -> patches [K][M] fp32 (row q = c*k*k + j*k + i, column m = (n, wo, ho), the
+// reference's im2col indexing, functions/dev_image.cu:20-49), TF32 head (and tail)
+template <bool X3>
+__global__ void im2col_split_kernel(const double *__restrict__ x, float *__restrict__ hi, float *__restrict__ lo,
+                                    int N, int H, int W, int k, int pad, int Ho, int Wo, long M, long total) {
+    const int kk = k * k;
+    for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+        const long q = idx / M, m = idx - q * M;
+        const int c = (int)(q / kk), tap = (int)(q - (long)c * kk);
+        const int j = tap / k, i = tap - j * k;
+        const int ho = (int)(m % Ho);
+        const long t = m / Ho;
+        const int wo = (int)(t % Wo), n = (int)(t / Wo);
+        const int h = ho + i - pad, w = wo + j - pad;
+        const double v = (h >= 0 && h < H && w >= 0 && w < W) ? x[(((long)c * N + n) * W + w) * H + h] : 0.0;
+        const float hv = __uint_as_float(f32_to_tf32(__double2float_rn(v)));
+        hi[idx] = hv;
+        if (X3) lo[idx] = __uint_as_float(f32_to_tf32(__double2float_rn(v - (double)hv)));
+    }
+}
+// fp64 -> fp32 TF32 head (and tail), same element order
+template <bool X3>
+__global__ void split_same_layout_kernel(const double *__restrict__ in, float *__restrict__ hi,
+                                         float *__restrict__ lo, long n) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const double x = in[i];
+        const float h = __uint_as_float(f32_to_tf32(__double2float_rn(x)));
+        hi[i] = h;
+        if (X3) lo[i] = __uint_as_float(f32_to_tf32(__double2float_rn(x - (double)h)));
+    }
+}
+__global__ void sum_slabs_tf32_kernel(const double *slabs, double *out, long n, int S) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        double s = 0.0;
+        for (int k = 0; k < S; ++k) s += slabs[(long)k * n + i];
+        out[i] = s;
+    }
+}
+
 }  // namespace
 
 void conv_tf32_init_attributes() {
@@ -510,6 +688,10 @@ void conv_tf32_init_attributes() {
     FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_direct_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
     FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_direct_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
     FITRE_CUDA(cudaFuncSetAttribute(conv_tf32_direct_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(wgrad_tf32_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(wgrad_tf32_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(wgrad_tf32_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
+    FITRE_CUDA(cudaFuncSetAttribute(wgrad_tf32_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFull));
 }
 
 namespace {
@@ -728,6 +910,105 @@ bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const do
                 slabs, y, a.M, Cout, SK, bias);
             check_launch(ctx, "reduce_out_slabs_tf32_kernel");
         }
+    }
+    return true;
+}
+
+
+namespace {
+struct WgradTf32Plan {
+    bool ok;
+    int Ho, Wo, BNQ, S, chunks;
+    long M, K, slabs, errs, patches, total;   // scratch offsets in doubles
+};
+WgradTf32Plan wgrad_tf32_plan(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    WgradTf32Plan P{};
+    P.Ho = H + 2 * pad - k + 1;
+    P.Wo = W + 2 * pad - k + 1;
+    P.K = (long)Cin * k * k;
+    P.M = (long)N * P.Ho * P.Wo;
+    // row strides of both fp32 matrices are M * 4 bytes and must be multiples of 16
+    if (P.Ho < 1 || P.Wo < 1 || P.K % 64 != 0 || (P.M & 3) || P.M < 256) return P;
+    P.BNQ = (P.K % 128 == 0) ? 128 : 64;
+    P.chunks = (int)((P.M + F_KC - 1) / F_KC);
+    const long tiles = (P.K / P.BNQ) * ((Cout + F_BM - 1) / F_BM);
+    P.S = (int)std::max<long>(1, std::min<long>(std::min<long>((2 * 148 + tiles - 1) / tiles, 64), P.chunks / 8));
+    P.slabs = 0;
+    P.errs = up32(P.S > 1 ? (long)P.S * P.K * Cout : 0);
+    P.patches = P.errs + up32(2 * P.M * Cout);        // two segments x head/tail, fp32
+    P.total = P.patches + up32(2 * P.K * P.M) + 64;
+    P.ok = true;
+    return P;
+}
+}  // namespace
+
+long conv_wgrad_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
+    const WgradTf32Plan P = wgrad_tf32_plan(N, Cin, H, W, k, pad, Cout);
+    return P.ok ? P.total : 0;
+}
+
+// dW = sum_seg im2col(x_seg)' * err_seg on the tensor cores; false when the shape does not fit.
+bool conv_wgrad_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin, int H,
+                     int W, int k, int pad, int Cout, double *scratch) {
+    if (!encode_fn() || !scratch) return false;
+    const WgradTf32Plan P = wgrad_tf32_plan(N, Cin, H, W, k, pad, Cout);
+    if (!P.ok) return false;
+    const bool x3 = ctx->precision == FITRE_PRECISION_TF32X3;
+    const int parts = x3 ? 2 : 1;
+    Tf32WgradArgs a{};
+    a.nseg = nseg; a.Cout = Cout; a.K = (int)P.K;
+    a.chunks = P.chunks;
+    a.chunks_per_split = (P.chunks + P.S - 1) / P.S;
+    const int S = (P.chunks + a.chunks_per_split - 1) / a.chunks_per_split;
+    a.err = (int *)(ctx->dscal + 4000);
+    a.out = S > 1 ? scratch + P.slabs : dw;
+    const int stageBytes = parts * (F_BM * F_KC * 4 + P.BNQ * F_KC * 4);
+    const int fixed = 1024 + 17 * 8 + 16;
+    a.stages = std::min((kSmemFull - fixed) / stageBytes, 6);
+    if (a.stages < 2) return false;
+    const long EP = P.M * Cout, PP = P.K * P.M;
+    for (int s = 0; s < nseg; ++s) {
+        float *eh = (float *)(scratch + P.errs) + (long)s * 2 * EP, *el = eh + EP;
+        float *ph = (float *)(scratch + P.patches) + (long)s * 2 * PP, *pl = ph + PP;
+        const int be = (int)std::min<long>((EP + 255) / 256, 2368), bp = (int)std::min<long>((PP + 255) / 256, 4736);
+        if (x3) {
+            split_same_layout_kernel<true><<<be, 256, 0, ctx->stream>>>(segs[s].w, eh, el, EP);
+            im2col_split_kernel<true><<<bp, 256, 0, ctx->stream>>>(segs[s].x, ph, pl, N, H, W, k, pad, P.Ho, P.Wo, P.M, PP);
+        } else {
+            split_same_layout_kernel<false><<<be, 256, 0, ctx->stream>>>(segs[s].w, eh, el, EP);
+            im2col_split_kernel<false><<<bp, 256, 0, ctx->stream>>>(segs[s].x, ph, pl, N, H, W, k, pad, P.Ho, P.Wo, P.M, PP);
+        }
+        check_launch(ctx, "im2col_split_kernel");
+        cuuint64_t dd[2] = {(cuuint64_t)P.M, (cuuint64_t)Cout};
+        cuuint64_t pd[2] = {(cuuint64_t)P.M, (cuuint64_t)P.K};
+        cuuint64_t st[1] = {(cuuint64_t)P.M * 4};
+        cuuint32_t db[2] = {(cuuint32_t)F_KC, (cuuint32_t)F_BM};
+        cuuint32_t pb[2] = {(cuuint32_t)F_KC, (cuuint32_t)P.BNQ};
+        for (int part = 0; part < parts; ++part) {
+            if (!encode(&a.dmap[s][part], part ? el : eh, 2, dd, st, db, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_DATA_TYPE_FLOAT32))
+                return false;
+            if (!encode(&a.pmap[s][part], part ? pl : ph, 2, pd, st, pb, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_DATA_TYPE_FLOAT32))
+                return false;
+        }
+    }
+    dim3 grid((unsigned)(P.K / P.BNQ), (unsigned)((Cout + F_BM - 1) / F_BM), (unsigned)S);
+    const int smem = a.stages * stageBytes + fixed;
+    ProfScope prof(ctx, PROF_CONV_WGRAD, 2.0 * (double)P.M * P.K * Cout * nseg);
+    if (P.BNQ == 128 && x3)
+        wgrad_tf32_kernel<128, true><<<grid, D_THREADS, smem, ctx->stream>>>(a);
+    else if (P.BNQ == 128)
+        wgrad_tf32_kernel<128, false><<<grid, D_THREADS, smem, ctx->stream>>>(a);
+    else if (x3)
+        wgrad_tf32_kernel<64, true><<<grid, D_THREADS, smem, ctx->stream>>>(a);
+    else
+        wgrad_tf32_kernel<64, false><<<grid, D_THREADS, smem, ctx->stream>>>(a);
+    check_launch(ctx, "wgrad_tf32_kernel");
+    if (S > 1) {
+        const long n = P.K * Cout;
+        sum_slabs_tf32_kernel<<<(int)std::min<long>((n + 255) / 256, 1184), 256, 0, ctx->stream>>>(a.out, dw, n, S);
+        check_launch(ctx, "sum_slabs_tf32_kernel");
     }
     return true;
 }

@@ -752,11 +752,15 @@ long conv_wgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) 
     const long tiles = (long)((K + WG_BQ - 1) / WG_BQ) * ((Cout + WG_BN - 1) / WG_BN);
     const int S = split_count(tiles, M, 512);
     const long gather = S > 1 ? (long)S * K * Cout : 0;
-    return std::max(gather, conv_wgrad_tma_scratch(N, Cin, H, W, k, pad, Cout));
+    return std::max(std::max(gather, conv_wgrad_tma_scratch(N, Cin, H, W, k, pad, Cout)),
+                    conv_wgrad_tf32_scratch(N, Cin, H, W, k, pad, Cout));
 }
 
 void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
                 int H, int W, int k, int pad, int Cout, double *partials) {
+    if (ctx->precision != FITRE_PRECISION_FP64 &&
+        conv_wgrad_tf32(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout, partials))
+        return;
     if (ctx->use_tma && conv_wgrad_tma(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout, partials)) return;
     WgradArgs a{};
     for (int s = 0; s < nseg; ++s) {

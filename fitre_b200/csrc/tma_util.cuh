@@ -87,7 +87,7 @@ bool encode(CUtensorMap *map, const void *base, int rank, const cuuint64_t *dims
             const cuuint64_t *strides_bytes, const cuuint32_t *box,
             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_NONE,
             CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_FLOAT64) {
-    cuuint32_t estr[4] = {1, 1, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUresult r = encode_fn()(map, dtype, (cuuint32_t)rank, (void *)base, dims,
                              strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
