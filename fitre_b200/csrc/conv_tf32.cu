@@ -639,23 +639,31 @@ wgrad_tf32_kernel(const __grid_constant__ Tf32WgradArgs p) {
 }
 
 // x fp64 [C][N][W][H] -> patches [K][M] fp32 (row q = c*k*k + j*k + i, column m = (n, wo, ho), the
-// reference's im2col indexing, functions/dev_image.cu:20-49), TF32 head (and tail)
+// reference's im2col indexing, functions/dev_image.cu:20-49), TF32 head (and tail).  blockIdx.y is
+// the row q; each thread converts four consecutive positions and stores them as one float4.
 template <bool X3>
 __global__ void im2col_split_kernel(const double *__restrict__ x, float *__restrict__ hi, float *__restrict__ lo,
-                                    int N, int H, int W, int k, int pad, int Ho, int Wo, long M, long total) {
-    const int kk = k * k;
-    for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-        const long q = idx / M, m = idx - q * M;
-        const int c = (int)(q / kk), tap = (int)(q - (long)c * kk);
-        const int j = tap / k, i = tap - j * k;
-        const int ho = (int)(m % Ho);
-        const long t = m / Ho;
-        const int wo = (int)(t % Wo), n = (int)(t / Wo);
-        const int h = ho + i - pad, w = wo + j - pad;
-        const double v = (h >= 0 && h < H && w >= 0 && w < W) ? x[(((long)c * N + n) * W + w) * H + h] : 0.0;
-        const float hv = __uint_as_float(f32_to_tf32(__double2float_rn(v)));
-        hi[idx] = hv;
-        if (X3) lo[idx] = __uint_as_float(f32_to_tf32(__double2float_rn(v - (double)hv)));
+                                    int N, int H, int W, int k, int pad, int Ho, int Wo, int M) {
+    const int q = blockIdx.y, kk = k * k;
+    const int c = q / kk, tap = q - c * kk;
+    const int j = tap / k, i = tap - j * k;
+    const double *xc = x + (long)c * N * W * H;
+    float *hq = hi + (long)q * M, *lq = lo + (long)q * M;
+    for (int m4 = (blockIdx.x * blockDim.x + threadIdx.x) * 4; m4 < M; m4 += gridDim.x * blockDim.x * 4) {
+        float vh[4], vl[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int m = m4 + e;
+            const int ho = m % Ho, t = m / Ho;
+            const int wo = t % Wo, n = t / Wo;
+            const int h = ho + i - pad, w = wo + j - pad;
+            const double v = (m < M && h >= 0 && h < H && w >= 0 && w < W) ? xc[((long)n * W + w) * H + h] : 0.0;
+            vh[e] = __uint_as_float(f32_to_tf32(__double2float_rn(v)));
+            if (X3) vl[e] = __uint_as_float(f32_to_tf32(__double2float_rn(v - (double)vh[e])));
+        }
+        // M is a multiple of 4 (checked by the planner), so the four stay inside the row
+        *reinterpret_cast<float4 *>(hq + m4) = make_float4(vh[0], vh[1], vh[2], vh[3]);
+        if (X3) *reinterpret_cast<float4 *>(lq + m4) = make_float4(vl[0], vl[1], vl[2], vl[3]);
     }
 }
 // fp64 -> fp32 TF32 head (and tail), same element order
@@ -928,7 +936,7 @@ WgradTf32Plan wgrad_tf32_plan(int N, int Cin, int H, int W, int k, int pad, int 
     P.K = (long)Cin * k * k;
     P.M = (long)N * P.Ho * P.Wo;
     // row strides of both fp32 matrices are M * 4 bytes and must be multiples of 16
-    if (P.Ho < 1 || P.Wo < 1 || P.K % 64 != 0 || (P.M & 3) || P.M < 256) return P;
+    if (P.Ho < 1 || P.Wo < 1 || P.K % 64 != 0 || P.K > 65535 || (P.M & 3) || P.M < 256 || P.M > (1L << 30)) return P;
     P.BNQ = (P.K % 128 == 0) ? 128 : 64;
     P.chunks = (int)((P.M + F_KC - 1) / F_KC);
     const long tiles = (P.K / P.BNQ) * ((Cout + F_BM - 1) / F_BM);
@@ -970,13 +978,14 @@ bool conv_wgrad_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, double *
     for (int s = 0; s < nseg; ++s) {
         float *eh = (float *)(scratch + P.errs) + (long)s * 2 * EP, *el = eh + EP;
         float *ph = (float *)(scratch + P.patches) + (long)s * 2 * PP, *pl = ph + PP;
-        const int be = (int)std::min<long>((EP + 255) / 256, 2368), bp = (int)std::min<long>((PP + 255) / 256, 4736);
+        const int be = (int)std::min<long>((EP + 255) / 256, 2368);
+        const dim3 gp((unsigned)std::min<long>((P.M / 4 + 255) / 256, 64), (unsigned)P.K);
         if (x3) {
             split_same_layout_kernel<true><<<be, 256, 0, ctx->stream>>>(segs[s].w, eh, el, EP);
-            im2col_split_kernel<true><<<bp, 256, 0, ctx->stream>>>(segs[s].x, ph, pl, N, H, W, k, pad, P.Ho, P.Wo, P.M, PP);
+            im2col_split_kernel<true><<<gp, 256, 0, ctx->stream>>>(segs[s].x, ph, pl, N, H, W, k, pad, P.Ho, P.Wo, (int)P.M);
         } else {
             split_same_layout_kernel<false><<<be, 256, 0, ctx->stream>>>(segs[s].w, eh, el, EP);
-            im2col_split_kernel<false><<<bp, 256, 0, ctx->stream>>>(segs[s].x, ph, pl, N, H, W, k, pad, P.Ho, P.Wo, P.M, PP);
+            im2col_split_kernel<false><<<gp, 256, 0, ctx->stream>>>(segs[s].x, ph, pl, N, H, W, k, pad, P.Ho, P.Wo, (int)P.M);
         }
         check_launch(ctx, "im2col_split_kernel");
         cuuint64_t dd[2] = {(cuuint64_t)P.M, (cuuint64_t)Cout};
