@@ -202,21 +202,22 @@ long long fitre_launch_count(const fitre_context *ctx);
  * probs += 1e-10: functions/softmax_loss.cu:24-27,55); 0 = textbook softmax. Default 1. */
 int fitre_set_reference_softmax(fitre_context *ctx, int on);
 
-/* Arithmetic of the convolution forward / data-gradient products (and of the R-operator's
- * convolutions).  FITRE_PRECISION_FP64 (default) is the reference's arithmetic.  The two other
+/* Arithmetic of the convolution products: forward, data gradient, weight gradient and their
+ * R-operator forms.  FITRE_PRECISION_FP64 (default) is the reference's arithmetic.  The two other
  * values are opt-in reduced-precision modes on the tcgen05 tensor cores with fp32 accumulation in
- * tensor memory; batch norm, activations, pooling, weight gradients, FC layers and all stored
- * tensors stay fp64 in both.
+ * tensor memory; batch norm, activations, pooling, FC layers and all stored tensors stay fp64.
  *   FITRE_PRECISION_TF32X3: every operand is split into a TF32 head and tail and each product is
  *     three tensor-core products (lo*hi + hi*lo + hi*hi), about 22 mantissa bits.  Stated
  *     tolerance of loss, gradient and Hessian-vector product against the fp64 result: 1e-3
- *     relative (measured: about 1e-5 on VGG-11-BN).
+ *     relative (measured about 1e-5 on VGG-11-BN; on max-pooling nets at batch sizes in the
+ *     hundreds a few arg-max decisions of near-tied pooling windows flip under any rounding and
+ *     move the gradient by up to 3e-3).
  *   FITRE_PRECISION_TF32: one product on TF32-rounded operands.  Each convolution is within 5e-4
  *     relative of fp64 and the loss within 1e-3, but batch normalisation and the backward sweep
  *     amplify the rounding: gradients and Hessian-vector products of deep nets are only within
  *     1e-1 relative (measured 3e-2 / 5e-2 on VGG-11-BN), so this mode does not meet 1e-3.
- * Layers the tensor-core kernel does not cover (first layer, odd input heights, kernels other than
- * 3x3 / 5x5) use the fp64 kernels in every mode.  No counterpart in the reference (fp64 only). */
+ * Shapes the tensor-core kernels do not cover (the 3-channel first layer, odd input heights, ...)
+ * use the fp64 kernels in every mode.  No counterpart in the reference (fp64 only). */
 enum { FITRE_PRECISION_FP64 = 0, FITRE_PRECISION_TF32 = 1, FITRE_PRECISION_TF32X3 = 2 };
 int fitre_set_precision(fitre_context *ctx, int precision);
 

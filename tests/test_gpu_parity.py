@@ -361,8 +361,8 @@ def test_cuda_matrix_inverse_blocked_sizes_and_failure():
 
 
 def test_cuda_reduced_precision_modes_within_stated_tolerance():
-    """Opt-in modes: convolution forward / data-gradient products on the tcgen05 tensor cores
-    (fp32 accumulation), everything else fp64.  Stated tolerances against the fp64 oracle,
+    """Opt-in modes: convolution forward / data-gradient / weight-gradient products on the tcgen05
+    tensor cores (fp32 accumulation), everything else fp64.  Stated tolerances against the fp64 oracle,
     relative and norm-wise:
       mode 2 (error-compensated 3 x TF32): 1e-3 for loss, gradient and Hessian-vector product;
       mode 1 (one TF32 product): 1e-3 for the loss, 1e-1 for gradient and Hessian-vector
@@ -371,7 +371,14 @@ def test_cuda_reduced_precision_modes_within_stated_tolerance():
     TOL = {2: (1e-3, 1e-3), 1: (1e-3, 1e-1)}
     c = G.ctx()
     try:
-        for model, n in ((nets.vgg_small(6), 6), (nets.alexnet_small(8, ch=8), 8), (nets.vgg11(8), 8)):
+        # a net whose layers exercise the expander-free kernel with 64-wide and ragged channel tiles
+        # and the tensor-core weight gradient (channels 32 / 64 / 96, average pooling, 5x5 and 3x3)
+        wide = S.describe_model(
+            [dict(cin=3, cout=32, h=8, w=8, k=3, pad=1, bn=True, act=S.CNN_ACT_SWISH, pool=None),
+             dict(cin=32, cout=64, h=8, w=8, k=5, pad=2, bn=True, act=S.CNN_ACT_SWISH, pool=(S.AVG_POOL, 2, 2, 0)),
+             dict(cin=64, cout=96, h=4, w=4, k=3, pad=1, bn=True, act=S.CNN_ACT_SOFTPLUS, pool=(S.AVG_POOL, 2, 2, 0))],
+            [(96 * 2 * 2, 10, S.CNN_ACT_NONE)], 16, True)
+        for model, n in ((nets.vgg_small(6), 6), (nets.alexnet_small(8, ch=8), 8), (nets.vgg11(8), 8), (wide, 16)):
             O.finalize(model)
             x, y, w, v, ncls = G.synth(model, n, seed=17)
             st = O.gradient(model, x, y, w, ncls, n)
