@@ -427,6 +427,106 @@ __global__ void __launch_bounds__(DG_THREADS) dgemm_kernel(int m, int n, int k, 
 }
 
 // ----------------------------------------------------------------------------------------
+// The same product on 128 x 128 tiles for large shapes (the GEMMs of the factor inversion and
+// the natural gradient): 8 warps as 2 x 4, each 64 x 32, so 12 shared-memory fragment loads feed
+// 32 DMMAs per 4-deep k step (the 64 x 64 kernel above: 6 loads for 8).  Double-buffered
+// register-staged loads as above; shared memory is dynamic (two 16 x 132 tiles per operand).
+// ----------------------------------------------------------------------------------------
+constexpr int DL_BM = 128, DL_BN = 128, DL_LD = 128 + 4;
+constexpr int DL_SMEM = 2 * 2 * DG_BK * DL_LD * (int)sizeof(double);
+
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(DG_THREADS) dgemm_large_kernel(int m, int n, int k, double alpha,
+                                                                const double *A, int lda,
+                                                                const double *B, int ldb, double beta,
+                                                                double *C, int ldc) {
+    extern __shared__ double dl_smem[];
+    double *As = dl_smem;                          // [2][DG_BK * DL_LD], As[k][m]
+    double *Bs = dl_smem + 2 * DG_BK * DL_LD;      // [2][DG_BK * DL_LD], Bs[k][n]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_m = warp & 1, warp_n = warp >> 1;  // warp tile 64 x 32
+    const int m0 = blockIdx.x * DL_BM, n0 = blockIdx.y * DL_BN;
+    const int nk = (k + DG_BK - 1) / DG_BK;
+    double ra[8], rb[8];
+    auto gload = [&](int kt) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            int mm, kk;
+            if (!TA) { mm = tid & 127; kk = (tid >> 7) + 2 * r; }
+            else     { kk = tid & 15; mm = (tid >> 4) + 16 * r; }
+            const int gi = m0 + mm, gp = kt * DG_BK + kk;
+            ra[r] = (gi < m && gp < k) ? (TA ? A[gp + (long)gi * lda] : A[gi + (long)gp * lda]) : 0.0;
+            int nn, kb;
+            if (!TB) { kb = tid & 15; nn = (tid >> 4) + 16 * r; }
+            else     { nn = tid & 127; kb = (tid >> 7) + 2 * r; }
+            const int gj = n0 + nn, gq = kt * DG_BK + kb;
+            rb[r] = (gj < n && gq < k) ? (TB ? B[gj + (long)gq * ldb] : B[gq + (long)gj * ldb]) : 0.0;
+        }
+    };
+    auto sstore = [&](int buf) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            int mm, kk;
+            if (!TA) { mm = tid & 127; kk = (tid >> 7) + 2 * r; }
+            else     { kk = tid & 15; mm = (tid >> 4) + 16 * r; }
+            As[buf * DG_BK * DL_LD + kk * DL_LD + mm] = ra[r];
+            int nn, kb;
+            if (!TB) { kb = tid & 15; nn = (tid >> 4) + 16 * r; }
+            else     { nn = tid & 127; kb = (tid >> 7) + 2 * r; }
+            Bs[buf * DG_BK * DL_LD + kb * DL_LD + nn] = rb[r];
+        }
+    };
+    double acc[8][4][2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+    const int lr = lane >> 2, lc = lane & 3;
+    if (nk > 0) {
+        gload(0);
+        sstore(0);
+    }
+    __syncthreads();
+    for (int kt = 0; kt < nk; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < nk) gload(kt + 1);
+        const double *a = As + buf * DG_BK * DL_LD + warp_m * 64 + lr;
+        const double *b = Bs + buf * DG_BK * DL_LD + warp_n * 32 + lr;
+#pragma unroll
+        for (int k4 = 0; k4 < DG_BK / 4; ++k4) {
+            double fa[8], fb[4];
+#pragma unroll
+            for (int mi = 0; mi < 8; ++mi) fa[mi] = a[(k4 * 4 + lc) * DL_LD + mi * 8];
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) fb[ni] = b[(k4 * 4 + lc) * DL_LD + ni * 8];
+#pragma unroll
+            for (int mi = 0; mi < 8; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 4; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+        }
+        if (kt + 1 < nk) {
+            sstore(buf ^ 1);
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int col = n0 + warp_n * 32 + ni * 8 + 2 * lc + e;
+            if (col >= n) continue;
+#pragma unroll
+            for (int mi = 0; mi < 8; ++mi) {
+                const int row = m0 + warp_m * 64 + mi * 8 + lr;
+                if (row >= m) continue;
+                double *c = C + (long)col * ldc + row;
+                const double v = alpha * acc[mi][ni][e];
+                *c = (beta == 0.0) ? v : v + beta * (*c);
+            }
+        }
+}
+
+// ----------------------------------------------------------------------------------------
 // C[n x n] = alpha * A' A with A rows x n column-major; split over rows, both triangles.
 // ----------------------------------------------------------------------------------------
 struct SyrkArgs {
@@ -798,6 +898,20 @@ void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, i
 void dgemm(fitre_context *ctx, bool tA, bool tB, int m, int n, int k, double alpha,
            const double *A, int lda, const double *B, int ldb, double beta, double *C, int ldc) {
     if (m <= 0 || n <= 0) return;
+    // large shapes: 128 x 128 tiles once they still fill the GPU
+    if ((long)((m + DL_BM - 1) / DL_BM) * ((n + DL_BN - 1) / DL_BN) >= 96 && k >= 64) {
+        dim3 gl((m + DL_BM - 1) / DL_BM, (n + DL_BN - 1) / DL_BN);
+        if (!tA && !tB)
+            dgemm_large_kernel<false, false><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        else if (!tA && tB)
+            dgemm_large_kernel<false, true><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        else if (tA && !tB)
+            dgemm_large_kernel<true, false><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        else
+            dgemm_large_kernel<true, true><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        check_launch(ctx, "dgemm_large_kernel");
+        return;
+    }
     dim3 grid((m + DG_BM - 1) / DG_BM, (n + DG_BN - 1) / DG_BN);
     if (!tA && !tB)
         dgemm_kernel<false, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
@@ -888,6 +1002,10 @@ void gemm_init_attributes() {
     FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(syrk_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(dgemm_large_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DL_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(dgemm_large_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DL_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(dgemm_large_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DL_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(dgemm_large_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DL_SMEM));
 }
 
 }  // namespace fitre

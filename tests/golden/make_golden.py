@@ -1,8 +1,9 @@
 """Generates the committed golden fixtures tests/golden/*.npz.
 
-Run once in a container that has the reference checkout (default /root/reference):
+Run once where the reference checkout is available (default: a `reference` directory beside
+this repository):
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <path to the reference checkout>]
 
 What comes from the reference itself:
   * the flat-vector <-> tensor mapping: pytorch/testing/readWeights.py (get4DMatrix,
@@ -65,7 +66,9 @@ def unpack_with_reference(readWeights, model, flat):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    here = os.path.dirname(os.path.abspath(__file__))
+    beside = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(here))), "reference")
+    ap.add_argument("--reference", default=beside)
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "pytorch", "testing"))
     sys.path.insert(0, os.path.join(args.reference, "pytorch", "peng"))
