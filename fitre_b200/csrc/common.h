@@ -131,6 +131,11 @@ void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, i
 // C (m x n, ldc) = alpha op(A) op(B) + beta C, column-major (cublasDgemm semantics)
 void dgemm(fitre_context *ctx, bool tA, bool tB, int m, int n, int k, double alpha,
            const double *A, int lda, const double *B, int ldb, double beta, double *C, int ldc);
+// the same with a structure hint (see gemm.cu): terms known to be zero are skipped
+enum { GEMM_FULL = 0, GEMM_K_LE_COL = 1, GEMM_K_GE_COL = 2, GEMM_K_LE_ROW = 3, GEMM_LOWER_C = 4 };
+void dgemm_structured(fitre_context *ctx, bool tA, bool tB, int m, int n, int k, double alpha,
+                      const double *A, int lda, const double *B, int ldb, double beta, double *C, int ldc,
+                      int kmode);
 // C (n x n) = alpha * A' A  where A is rows x n column-major (lda); both triangles written.
 long syrk_scratch(long rows, int n);
 void syrk_tn(fitre_context *ctx, long rows, int n, double alpha, const double *A, long lda,

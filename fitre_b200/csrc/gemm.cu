@@ -328,19 +328,36 @@ __global__ void reduce_slabs_kernel(const double *partial, double *out, long n, 
 // Dense DGEMM (fully connected layers): C = alpha op(A) op(B) + beta C, column-major
 // ----------------------------------------------------------------------------------------
 constexpr int DG_BM = 64, DG_BN = 64, DG_BK = 16, DG_THREADS = 256;
+// Structure hints for products with a triangular operand (the factor inversion): which k blocks of
+// a C tile can be non-zero, or that only tiles touching the lower triangle of C are wanted.
+//   GEMM_K_LE_COL: terms with k <= column only  (B' lower triangular:  C = A * L')
+//   GEMM_K_GE_COL: terms with k >= column only  (B lower triangular:   C = A * L)
+//   GEMM_K_LE_ROW: terms with k <= row only     (A lower triangular:   C = L * B)
+//   GEMM_LOWER_C:  tiles strictly above the diagonal of C are skipped (C symmetric, lower wanted)
+// The skipped terms are exact zeros, so results equal the plain product.
+__device__ __forceinline__ bool gemm_k_range(int kmode, int m0, int n0, int bm, int bn, int k, int &kt0, int &nk) {
+    kt0 = 0;
+    nk = (k + DG_BK - 1) / DG_BK;
+    if (kmode == GEMM_K_LE_COL) nk = min(nk, (min(n0 + bn, k) + DG_BK - 1) / DG_BK);
+    else if (kmode == GEMM_K_GE_COL) kt0 = n0 / DG_BK;
+    else if (kmode == GEMM_K_LE_ROW) nk = min(nk, (min(m0 + bm, k) + DG_BK - 1) / DG_BK);
+    else if (kmode == GEMM_LOWER_C && n0 >= m0 + bm) return false;
+    return true;
+}
 constexpr int DG_LDA = DG_BM + 4, DG_LDB = DG_BN + 4;  // As[k][m], Bs[k][n]
 
 template <bool TA, bool TB>
 __global__ void __launch_bounds__(DG_THREADS) dgemm_kernel(int m, int n, int k, double alpha,
                                                           const double *A, int lda,
                                                           const double *B, int ldb, double beta,
-                                                          double *C, int ldc) {
+                                                          double *C, int ldc, int kmode) {
     __shared__ double As[2][DG_BK * DG_LDA];
     __shared__ double Bs[2][DG_BK * DG_LDB];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int warp_m = warp & 1, warp_n = warp >> 1;  // warp tile 32 x 16
     const int m0 = blockIdx.x * DG_BM, n0 = blockIdx.y * DG_BN;
-    const int nk = (k + DG_BK - 1) / DG_BK;
+    int kt0, nk;
+    if (!gemm_k_range(kmode, m0, n0, DG_BM, DG_BN, k, kt0, nk)) return;
     // loader roles: 1024 elements per operand tile, 4 per thread.  The fast thread index
     // follows the contiguous direction of the operand in memory.
     double ra[4], rb[4];
@@ -382,12 +399,12 @@ __global__ void __launch_bounds__(DG_THREADS) dgemm_kernel(int m, int n, int k, 
 #pragma unroll
         for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
     const int lr = lane >> 2, lc = lane & 3;
-    if (nk > 0) {
-        gload(0);
-        sstore(0);
+    if (nk > kt0) {
+        gload(kt0);
+        sstore(kt0 & 1);
     }
     __syncthreads();
-    for (int kt = 0; kt < nk; ++kt) {
+    for (int kt = kt0; kt < nk; ++kt) {
         const int buf = kt & 1;
         if (kt + 1 < nk) gload(kt + 1);
         const double *a = As[buf] + warp_m * 32 + lr;
@@ -439,14 +456,15 @@ template <bool TA, bool TB>
 __global__ void __launch_bounds__(DG_THREADS) dgemm_large_kernel(int m, int n, int k, double alpha,
                                                                 const double *A, int lda,
                                                                 const double *B, int ldb, double beta,
-                                                                double *C, int ldc) {
+                                                                double *C, int ldc, int kmode) {
     extern __shared__ double dl_smem[];
     double *As = dl_smem;                          // [2][DG_BK * DL_LD], As[k][m]
     double *Bs = dl_smem + 2 * DG_BK * DL_LD;      // [2][DG_BK * DL_LD], Bs[k][n]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int warp_m = warp & 1, warp_n = warp >> 1;  // warp tile 64 x 32
     const int m0 = blockIdx.x * DL_BM, n0 = blockIdx.y * DL_BN;
-    const int nk = (k + DG_BK - 1) / DG_BK;
+    int kt0, nk;
+    if (!gemm_k_range(kmode, m0, n0, DL_BM, DL_BN, k, kt0, nk)) return;
     double ra[8], rb[8];
     auto gload = [&](int kt) {
 #pragma unroll
@@ -482,12 +500,12 @@ __global__ void __launch_bounds__(DG_THREADS) dgemm_large_kernel(int m, int n, i
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
     const int lr = lane >> 2, lc = lane & 3;
-    if (nk > 0) {
-        gload(0);
-        sstore(0);
+    if (nk > kt0) {
+        gload(kt0);
+        sstore(kt0 & 1);
     }
     __syncthreads();
-    for (int kt = 0; kt < nk; ++kt) {
+    for (int kt = kt0; kt < nk; ++kt) {
         const int buf = kt & 1;
         if (kt + 1 < nk) gload(kt + 1);
         const double *a = As + buf * DG_BK * DL_LD + warp_m * 64 + lr;
@@ -897,30 +915,36 @@ void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, i
 
 void dgemm(fitre_context *ctx, bool tA, bool tB, int m, int n, int k, double alpha,
            const double *A, int lda, const double *B, int ldb, double beta, double *C, int ldc) {
+    dgemm_structured(ctx, tA, tB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, GEMM_FULL);
+}
+
+void dgemm_structured(fitre_context *ctx, bool tA, bool tB, int m, int n, int k, double alpha,
+                      const double *A, int lda, const double *B, int ldb, double beta, double *C, int ldc,
+                      int kmode) {
     if (m <= 0 || n <= 0) return;
     // large shapes: 128 x 128 tiles once they still fill the GPU
     if ((long)((m + DL_BM - 1) / DL_BM) * ((n + DL_BN - 1) / DL_BN) >= 96 && k >= 64) {
         dim3 gl((m + DL_BM - 1) / DL_BM, (n + DL_BN - 1) / DL_BN);
         if (!tA && !tB)
-            dgemm_large_kernel<false, false><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+            dgemm_large_kernel<false, false><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
         else if (!tA && tB)
-            dgemm_large_kernel<false, true><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+            dgemm_large_kernel<false, true><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
         else if (tA && !tB)
-            dgemm_large_kernel<true, false><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+            dgemm_large_kernel<true, false><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
         else
-            dgemm_large_kernel<true, true><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+            dgemm_large_kernel<true, true><<<gl, DG_THREADS, DL_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
         check_launch(ctx, "dgemm_large_kernel");
         return;
     }
     dim3 grid((m + DG_BM - 1) / DG_BM, (n + DG_BN - 1) / DG_BN);
     if (!tA && !tB)
-        dgemm_kernel<false, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        dgemm_kernel<false, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
     else if (!tA && tB)
-        dgemm_kernel<false, true><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        dgemm_kernel<false, true><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
     else if (tA && !tB)
-        dgemm_kernel<true, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        dgemm_kernel<true, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
     else
-        dgemm_kernel<true, true><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        dgemm_kernel<true, true><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
     check_launch(ctx, "dgemm_kernel");
 }
 

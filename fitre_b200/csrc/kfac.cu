@@ -404,12 +404,14 @@ void factor_invert(fitre_context *ctx, double *A, double *Y, long ld, int n, int
     double *Y21 = Y + n1, *Y22 = Y + (long)n1 * ld + n1;
     double *L21 = tmp, *next = tmp + (long)n2 * n1;
     factor_invert(ctx, A, Y, ld, n1, col0, fail, next);
-    dgemm(ctx, false, true, n2, n1, n1, 1.0, A21, (int)ld, Y, (int)ld, 0.0, L21, n2);
-    dgemm(ctx, false, true, n2, n2, n1, -1.0, L21, n2, L21, n2, 1.0, A22, (int)ld);
+    // Y11 and Y22 are lower triangular and only the lower triangle of A22 is ever read again, so
+    // each product skips the blocks that are zero or unused
+    dgemm_structured(ctx, false, true, n2, n1, n1, 1.0, A21, (int)ld, Y, (int)ld, 0.0, L21, n2, GEMM_K_LE_COL);
+    dgemm_structured(ctx, false, true, n2, n2, n1, -1.0, L21, n2, L21, n2, 1.0, A22, (int)ld, GEMM_LOWER_C);
     factor_invert(ctx, A22, Y22, ld, n2, col0 + n1, fail, next);
     double *T = next;  // free again after the recursion: L21 * Y11
-    dgemm(ctx, false, false, n2, n1, n1, 1.0, L21, n2, Y, (int)ld, 0.0, T, n2);
-    dgemm(ctx, false, false, n2, n1, n2, -1.0, Y22, (int)ld, T, n2, 0.0, Y21, (int)ld);
+    dgemm_structured(ctx, false, false, n2, n1, n1, 1.0, L21, n2, Y, (int)ld, 0.0, T, n2, GEMM_K_GE_COL);
+    dgemm_structured(ctx, false, false, n2, n1, n2, -1.0, Y22, (int)ld, T, n2, 0.0, Y21, (int)ld, GEMM_K_LE_ROW);
 }
 
 // inverse <- (matrix + damp I)^-1 on ctx->stream, no host synchronisation; a pivot <= 0 is
