@@ -36,6 +36,7 @@ import numpy as np  # noqa: E402
 PER_GPU_BATCH = 512
 WORKLOAD = "vgg11bn_32x32_fp64_gradient+hv"
 # algorithmic flops per image (2*M*K*Cout products only): gradient 913.1 MF + Hv 1819.1 MF
+TORCH_SAMPLE_IMAGES = 64     # PyTorch-on-CPU leg beside it
 CPU_SAMPLE_IMAGES = 256      # cpu_baseline leg of the default run: one pass, ~15 s on 16 cores
 REF_SAMPLE_IMAGES = 64       # --impl reference: per timed step
 
@@ -140,6 +141,24 @@ def cpu_oracle_rate(sample_images, threads=None):
     t0 = time.perf_counter()
     st = O.gradient(m, x, y, w, 10, sample_images)
     O.hv(m, x, w, 10, sample_images, st, v)
+    dt = time.perf_counter() - t0
+    return sample_images / dt, dt
+
+
+def cpu_pytorch_rate(sample_images):
+    """images/s of the same step as PyTorch runs it on the host cores: fp64 autograd gradient and
+    Hessian-vector product by double backward, the operator of the reference's pytorch/ path
+    (pytorch/kfac/alexnet_cifar.py:297-324), all threads."""
+    import torch
+    import nets
+    import oracle_lib as O
+    import torch_ref
+    torch.set_num_threads(os.cpu_count() or 1)
+    m = nets.vgg11(sample_images)
+    O.finalize(m)
+    x, y, w, v = synth(m, sample_images, 4321)
+    t0 = time.perf_counter()
+    torch_ref.loss_grad_hv(m, w, x, y, sample_images, vectors=(v,))
     dt = time.perf_counter() - t0
     return sample_images / dt, dt
 
@@ -328,6 +347,14 @@ def run_ours(args):
                                 "kind": "port",
                                 "sample": "%d images of the same VGG-11-BN fp64 gradient+Hv step "
                                           "(%.1f s of CPU work)" % (CPU_SAMPLE_IMAGES, dt)}
+        try:  # the same step in PyTorch on the host cores, reported beside the port
+            rt, dtt = cpu_pytorch_rate(TORCH_SAMPLE_IMAGES)
+            line["cpu_baseline_pytorch"] = {
+                "value": rt, "unit": "images/s", "cores": os.cpu_count() or 1,
+                "sample": "%d images, fp64 autograd gradient + double-backward Hv (%.1f s)"
+                          % (TORCH_SAMPLE_IMAGES, dtt)}
+        except Exception as e:  # noqa: BLE001 -- a missing or failing torch CPU path must not fail the bench
+            line["cpu_baseline_pytorch"] = {"unavailable": str(e)[:200]}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
