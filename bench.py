@@ -36,7 +36,7 @@ import numpy as np  # noqa: E402
 PER_GPU_BATCH = 512
 WORKLOAD = "vgg11bn_32x32_fp64_gradient+hv"
 # algorithmic flops per image (2*M*K*Cout products only): gradient 913.1 MF + Hv 1819.1 MF
-TORCH_SAMPLE_IMAGES = 64     # PyTorch-on-CPU leg beside it
+TORCH_SAMPLE_IMAGES = 256    # PyTorch-on-CPU leg beside it
 CPU_SAMPLE_IMAGES = 256      # cpu_baseline leg of the default run: one pass, ~15 s on 16 cores
 REF_SAMPLE_IMAGES = 64       # --impl reference: per timed step
 
@@ -539,6 +539,9 @@ def run_fitre(args):
             "first_loss": steps[0].trainLikelihood, "last_loss": steps[-1].newTrainLikelihood,
             "kfac_steps": sum(s.usedKfac for s in steps), "reverted": sum(s.reverted for s in steps),
             "gpu_launches": launches}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main():
