@@ -11,7 +11,7 @@ MAX_LAYERS = 20
 # enum values (nn/nn_decl.h:13-101)
 NO_BATCH_NORM, BATCH_NORM = 0, 10
 MODEL_TRAIN = 10
-ACT_LINEAR = 3
+ACT_LOGISTIC, ACT_TANH, ACT_LINEAR = 1, 2, 3
 CNN_ACT_NONE, CNN_ACT_SOFTPLUS, CNN_ACT_ELU, CNN_ACT_RELU, CNN_ACT_SWISH = 10, 11, 12, 13, 14
 MAX_POOL, AVG_POOL, NO_POOL = 0, 1, 2
 

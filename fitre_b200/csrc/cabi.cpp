@@ -114,6 +114,7 @@ int fitre_context_destroy(fitre_context *ctx) {
     if (ctx->dscal) cudaFree(ctx->dscal);
     if (ctx->host_ws) cudaFree(ctx->host_ws);
     if (ctx->host_pinned) cudaFreeHost(ctx->host_pinned);
+    if (ctx->tf32_buf) cudaFree(ctx->tf32_buf);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
     for (int s = 0; s < 4; ++s) {
         if (ctx->inv_streams[s]) cudaStreamDestroy(ctx->inv_streams[s]);

@@ -60,6 +60,8 @@ struct fitre_context {
     size_t host_pinned_doubles = 0;
     cudaStream_t copy_stream = nullptr;   // second stream of the host-buffer entry point
     cudaEvent_t ev_up = nullptr, ev_down = nullptr;
+    double *tf32_buf = nullptr;           // staging of the opt-in tensor-core modes (fp32 operand copies,
+    long tf32_cap = 0;                    // split slabs), owned by the context, grown on demand
     cudaStream_t inv_streams[4] = {};     // side streams of the batched factor inversion
     cudaEvent_t inv_fork = nullptr, inv_join[4] = {};
     // optional per-kernel timing (CUDA events on the launch stream), see fitre_profile_*

@@ -732,14 +732,27 @@ Tf32Scratch tf32_scratch_layout(int N, int Cin, int H, int W, int k, int pad, in
 }
 }  // namespace
 
-long conv_fprop_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
-    return tf32_scratch_layout(N, Cin, H, W, k, pad, Cout).total;
+// The reduced-precision modes have no counterpart in the reference, so their staging does not
+// come out of the caller's scratch (whose size is the fp64 path's): the context owns one buffer,
+// allocated and grown in stream order on first need.
+double *tf32_workspace(fitre_context *ctx, long doubles) {
+    if (doubles > ctx->tf32_cap) {
+        if (ctx->tf32_buf) FITRE_CUDA(cudaFreeAsync(ctx->tf32_buf, ctx->stream));
+        ctx->tf32_buf = nullptr;
+        ctx->tf32_cap = 0;
+        const long cap = doubles + doubles / 8;
+        FITRE_CUDA(cudaMallocAsync((void **)&ctx->tf32_buf, sizeof(double) * (size_t)cap, ctx->stream));
+        ctx->tf32_cap = cap;
+    }
+    return ctx->tf32_buf;
 }
+
+long conv_fprop_tf32_scratch(int, int, int, int, int, int, int) { return 0; }
 
 namespace {
 // The expander-free form; false when the shape does not fit it (the caller then tries the other).
 bool conv_fprop_tf32_direct(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
-                            int N, int Cin, int H, int W, int k, int pad, int Cout, double *scratch) {
+                            int N, int Cin, int H, int W, int k, int pad, int Cout) {
     if (Cin % 32 != 0 || k < 1 || k > 7) return false;
     const bool x3 = ctx->precision == FITRE_PRECISION_TF32X3;
     const int parts = x3 ? 2 : 1;
@@ -751,6 +764,7 @@ bool conv_fprop_tf32_direct(fitre_context *ctx, int nseg, const ConvSeg *segs, c
     const int TN = F_BM / (TH * TW);
     if (TH > 256 || TW > 256 || TN > 256) return false;
     const Tf32Scratch L = tf32_scratch_layout(N, Cin, H, W, k, pad, Cout);
+    double *scratch = tf32_workspace(ctx, L.total);
     const int BN = (Cout % 128 == 0) ? 128 : 64;
     const int K = Cin * k * k;
     Tf32DirectArgs a{};
@@ -827,11 +841,12 @@ bool conv_fprop_tf32_direct(fitre_context *ctx, int nseg, const ConvSeg *segs, c
 }  // namespace
 
 bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
-                     int N, int Cin, int H, int W, int k, int pad, int Cout, double *scratch) {
-    if (!encode_fn() || !scratch) return false;
+                     int N, int Cin, int H, int W, int k, int pad, int Cout, double *caller_scratch) {
+    (void)caller_scratch;
+    if (!encode_fn()) return false;
     for (int s = 0; s < nseg; ++s)
         if ((uintptr_t)segs[s].x & 15) return false;
-    if (conv_fprop_tf32_direct(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout, scratch)) return true;
+    if (conv_fprop_tf32_direct(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout)) return true;
     if (k != 3 && k != 5) return false;
     const Tf32Scratch L = tf32_scratch_layout(N, Cin, H, W, k, pad, Cout);
     const bool x3 = ctx->precision == FITRE_PRECISION_TF32X3;
@@ -878,6 +893,7 @@ bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const do
     int SK = std::min(L.sk_max, tf32_split(a.M, Cout, iters));   // L.sk_max: what the scratch was sized for
     a.iters_per_split = (iters + SK - 1) / SK;
     SK = (iters + a.iters_per_split - 1) / a.iters_per_split;
+    double *scratch = tf32_workspace(ctx, L.total);
     double *slabs = scratch + L.slabs;
     float *w32 = (float *)(scratch + L.weights);
     a.y = SK > 1 ? slabs : y;
@@ -950,17 +966,16 @@ WgradTf32Plan wgrad_tf32_plan(int N, int Cin, int H, int W, int k, int pad, int 
 }
 }  // namespace
 
-long conv_wgrad_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) {
-    const WgradTf32Plan P = wgrad_tf32_plan(N, Cin, H, W, k, pad, Cout);
-    return P.ok ? P.total : 0;
-}
+long conv_wgrad_tf32_scratch(int, int, int, int, int, int, int) { return 0; }  // staged in the context's buffer
 
 // dW = sum_seg im2col(x_seg)' * err_seg on the tensor cores; false when the shape does not fit.
 bool conv_wgrad_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin, int H,
-                     int W, int k, int pad, int Cout, double *scratch) {
-    if (!encode_fn() || !scratch) return false;
+                     int W, int k, int pad, int Cout, double *caller_scratch) {
+    (void)caller_scratch;
+    if (!encode_fn()) return false;
     const WgradTf32Plan P = wgrad_tf32_plan(N, Cin, H, W, k, pad, Cout);
     if (!P.ok) return false;
+    double *scratch = tf32_workspace(ctx, P.total);
     const bool x3 = ctx->precision == FITRE_PRECISION_TF32X3;
     const int parts = x3 ? 2 : 1;
     Tf32WgradArgs a{};

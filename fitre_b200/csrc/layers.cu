@@ -29,6 +29,8 @@ __device__ __forceinline__ double act_fwd(int act, double x) {
         case FITRE_CNN_ACT_RELU: return x < 0 ? 0.0 : x;
         case FITRE_CNN_ACT_SOFTPLUS: return x < 20 ? log(1 + exp(x)) : x;
         case FITRE_CNN_ACT_SWISH: return x / (1 + exp(-x));
+        case FITRE_ACT_LOGISTIC: return 1. / (1. + exp(-x));
+        case FITRE_ACT_TANH: return tanh(x);
         default: return x;
     }
 }
@@ -40,6 +42,9 @@ __device__ __forceinline__ double act_d1(int act, double zin, double zout) {
             const double t = 1. / (1. + exp(-zin));
             return zout + t * (1. - zout);
         }
+        // logistic and tanh from the output, as functions/dev_layer_error.cu:13-29
+        case FITRE_ACT_LOGISTIC: return zout * (1.0 - zout);
+        case FITRE_ACT_TANH: return (1.0 + zout) * (1.0 - zout);
         default: return 1.0;
     }
 }
@@ -53,6 +58,8 @@ __device__ __forceinline__ double act_d2(int act, double zin, double zout) {
             const double t = 1. / (1. + exp(-zin));
             return (1. - t) * (zout + 2. * t * (1. - zout));
         }
+        case FITRE_ACT_LOGISTIC: return zout * (1.0 - zout) * (1.0 - 2.0 * zout);
+        case FITRE_ACT_TANH: return -2.0 * zout * (1.0 + zout) * (1.0 - zout);
         default: return 0.0;
     }
 }

@@ -52,7 +52,8 @@ void set_fc(CNN_MODEL *m, int l, int in, int out, int act) {
 
 bool act_supported(int a) {
     return a == FITRE_CNN_ACT_NONE || a == FITRE_ACT_LINEAR || a == FITRE_CNN_ACT_SOFTPLUS ||
-           a == FITRE_CNN_ACT_RELU || a == FITRE_CNN_ACT_SWISH;
+           a == FITRE_CNN_ACT_RELU || a == FITRE_CNN_ACT_SWISH || a == FITRE_ACT_LOGISTIC ||
+           a == FITRE_ACT_TANH;
 }
 
 }  // namespace

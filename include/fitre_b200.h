@@ -35,7 +35,7 @@ typedef double real;
 enum { FITRE_NET_LENET = 0, FITRE_NET_ALEXNET = 1, FITRE_NET_VGG11 = 2 };
 enum { FITRE_NO_BATCH_NORM = 0, FITRE_BATCH_NORM = 10, FITRE_BATCH_NORM_TRAINABLE = 20 };
 enum { FITRE_MODEL_TRAIN = 10, FITRE_MODEL_TRAIN_ACCURACY = 20, FITRE_MODEL_TEST_ACCURACY = 30 };
-enum { FITRE_ACT_LINEAR = 3 };
+enum { FITRE_ACT_LOGISTIC = 1, FITRE_ACT_TANH = 2, FITRE_ACT_LINEAR = 3 }; /* FC layers */
 enum {
     FITRE_CNN_ACT_NONE = 10,
     FITRE_CNN_ACT_SOFTPLUS = 11,

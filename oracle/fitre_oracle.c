@@ -344,12 +344,16 @@ static void fc_to_conv(double *buf, int C, int N, int Hp, int Wp) {
 }
 
 /* ------------------------------------------------------------------------------------ */
-/* Activations: functions/dev_activations.cu:8-39, swish.cu:14-84,                       */
-/* dev_layer_error.cu:34-47, dev_layer_r_error.cu:24-38                                  */
+/* Activations: functions/dev_activations.cu:8-77, swish.cu:14-84,                       */
+/* dev_layer_error.cu:13-47, dev_layer_r_error.cu:24-38.  Logistic and tanh (FC layers,  */
+/* functions/eval_gradient.cu:142-157, cnn_backward.cu:121-136) are differentiated from  */
+/* their output as the reference does: y(1-y) and (1+y)(1-y); their second derivatives   */
+/* y(1-y)(1-2y) and -2y(1+y)(1-y) complete the R-operator, which the reference lacks.    */
 /* ------------------------------------------------------------------------------------ */
 static int act_known(int a) {
     return a == FITRE_CNN_ACT_NONE || a == FITRE_ACT_LINEAR || a == FITRE_CNN_ACT_SOFTPLUS ||
-           a == FITRE_CNN_ACT_RELU || a == FITRE_CNN_ACT_SWISH;
+           a == FITRE_CNN_ACT_RELU || a == FITRE_CNN_ACT_SWISH || a == FITRE_ACT_LOGISTIC ||
+           a == FITRE_ACT_TANH;
 }
 
 void ora_activation(int act, double *x, long n) {
@@ -364,6 +368,8 @@ void ora_activation(int act, double *x, long n) {
             case FITRE_CNN_ACT_RELU: x[i] = t < 0 ? 0 : t; break;
             case FITRE_CNN_ACT_SOFTPLUS: x[i] = (t < 20) ? log(1 + exp(t)) : t; break;
             case FITRE_CNN_ACT_SWISH: x[i] = t / (1 + exp(-t)); break;
+            case FITRE_ACT_LOGISTIC: x[i] = 1. / (1. + exp(-t)); break;
+            case FITRE_ACT_TANH: x[i] = tanh(t); break;
             default: break;
         }
     }
@@ -378,6 +384,8 @@ static inline double act_d1(int act, double zin, double zout) {
             double t = 1. / (1. + exp(-zin));
             return zout + t * (1. - zout);
         }
+        case FITRE_ACT_LOGISTIC: return zout * (1.0 - zout);
+        case FITRE_ACT_TANH: return (1.0 + zout) * (1.0 - zout);
         default: return 1.0;
     }
 }
@@ -392,6 +400,8 @@ static inline double act_d2(int act, double zin, double zout) {
             double t = 1. / (1. + exp(-zin));
             return (1. - t) * (zout + 2. * t * (1. - zout));
         }
+        case FITRE_ACT_LOGISTIC: return zout * (1.0 - zout) * (1.0 - 2.0 * zout);
+        case FITRE_ACT_TANH: return -2.0 * zout * (1.0 + zout) * (1.0 - zout);
         default: return 0.0;
     }
 }

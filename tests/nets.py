@@ -13,8 +13,9 @@ def test_vgg(batch, h=4, w=4, act=S.CNN_ACT_SOFTPLUS, bn=False, bias=True, class
     return S.describe_model(convs, fcs, batch, bias)
 
 
-def lenet_small(batch, act=S.CNN_ACT_SWISH, pool=S.AVG_POOL, bias=True, hw=16, classes=10):
-    """LeNet topology (conv5, pool2, conv5, pool2, 3 FC) on a 16x16 input."""
+def lenet_small(batch, act=S.CNN_ACT_SWISH, pool=S.AVG_POOL, bias=True, hw=16, classes=10, fc_act=None):
+    """LeNet topology (conv5, pool2, conv5, pool2, 3 FC) on a 16x16 input; fc_act gives the two
+    hidden FC layers their own activation (logistic / tanh of the reference's FC path)."""
     h1 = hw - 4
     h2 = h1 // 2 - 4
     convs = [
@@ -22,7 +23,8 @@ def lenet_small(batch, act=S.CNN_ACT_SWISH, pool=S.AVG_POOL, bias=True, hw=16, c
         dict(cin=6, cout=16, h=h1 // 2, w=h1 // 2, k=5, pad=0, bn=False, act=act, pool=(pool, 2, 2, 0)),
     ]
     fin = 16 * (h2 // 2) ** 2
-    fcs = [(fin, 12, act), (12, 11, act), (11, classes, S.CNN_ACT_NONE)]
+    fa = act if fc_act is None else fc_act
+    fcs = [(fin, 12, fa), (12, 11, fa), (11, classes, S.CNN_ACT_NONE)]
     return S.describe_model(convs, fcs, batch, bias)
 
 

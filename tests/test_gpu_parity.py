@@ -83,6 +83,8 @@ CASES = [
     ("vgg_small", dict(act=S.CNN_ACT_SOFTPLUS, bn=False, hw=16), 3),
     ("lenet", dict(), 16),
     ("lenet", dict(act=S.CNN_ACT_RELU, pool=S.MAX_POOL), 16),
+    ("lenet_small", dict(fc_act=S.ACT_LOGISTIC), 7),
+    ("lenet_small", dict(fc_act=S.ACT_TANH, act=S.CNN_ACT_SOFTPLUS), 5),
 ]
 
 

@@ -197,6 +197,7 @@ def test_layout_round_trip():
 @pytest.mark.parametrize("builder,kwargs", [
     ("lenet_small", {}), ("vgg_small", {}), ("alexnet_small", {}),
     ("vgg_small", dict(act=S.CNN_ACT_SOFTPLUS, bias=True)),
+    ("lenet_small", dict(fc_act=S.ACT_LOGISTIC)), ("lenet_small", dict(fc_act=S.ACT_TANH)),
 ])
 def test_taylor_derivative(builder, kwargs):
     # utilities/cnn_derivative_test.cu:48-235: first-order remainder O(|d|^2),
