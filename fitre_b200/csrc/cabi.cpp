@@ -122,6 +122,9 @@ int fitre_context_destroy(fitre_context *ctx) {
     }
     if (ctx->inv_fork) cudaEventDestroy(ctx->inv_fork);
     if (ctx->ev_up) cudaEventDestroy(ctx->ev_up);
+    if (ctx->ev_w2) cudaEventDestroy(ctx->ev_w2);
+    for (int i = 0; i < 24; ++i)
+        if (ctx->chunk_ev[i]) cudaEventDestroy(ctx->chunk_ev[i]);
     if (ctx->ev_down) cudaEventDestroy(ctx->ev_down);
     for (auto &r : ctx->prof) {
         cudaEventDestroy(r.beg);
@@ -459,14 +462,31 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
             FITRE_CUDA(cudaEventCreateWithFlags(&ctx->ev_down, cudaEventDisableTiming));
         }
         cudaStream_t cs = ctx->copy_stream;
-        // the direction vector is not needed before the Hessian-vector product: its upload runs
-        // on the copy stream underneath the gradient
-        FITRE_CUDA(cudaMemcpyAsync(v, vector_host, sizeof(double) * m->pSize, cudaMemcpyHostToDevice, cs));
-        FITRE_CUDA(cudaEventRecord(ctx->ev_up, cs));
+        if (!ctx->ev_w2) FITRE_CUDA(cudaEventCreateWithFlags(&ctx->ev_w2, cudaEventDisableTiming));
+        // Uploads.  The forward pass needs the batch and the first layers' weights at once; the late
+        // layers' weights (most of the vector) and the direction vector travel on the copy stream
+        // underneath the first layers' compute, in that order so that they do not share the link
+        // with what the forward pass is waiting for.
+        int split_layer = -1;
+        for (int l = 1; l < m->cLayers; ++l)
+            if ((long)m->wOffsets[l] * 8 >= (4L << 20)) {
+                split_layer = l;
+                break;
+            }
+        const long head = split_layer > 0 ? m->wOffsets[split_layer] : m->pSize;
         FITRE_CUDA(cudaMemcpyAsync(x, batch_host, sizeof(double) * (long)n * c0.inChannels * c0.height * c0.width,
                                    cudaMemcpyHostToDevice, st));
         FITRE_CUDA(cudaMemcpyAsync(y, labels_host, sizeof(double) * n, cudaMemcpyHostToDevice, st));
-        FITRE_CUDA(cudaMemcpyAsync(w, weights_host, sizeof(double) * m->pSize, cudaMemcpyHostToDevice, st));
+        FITRE_CUDA(cudaMemcpyAsync(w, weights_host, sizeof(double) * head, cudaMemcpyHostToDevice, st));
+        if (head < m->pSize) {
+            FITRE_CUDA(cudaMemcpyAsync(w + head, weights_host + head, sizeof(double) * (m->pSize - head),
+                                       cudaMemcpyHostToDevice, cs));
+            FITRE_CUDA(cudaEventRecord(ctx->ev_w2, cs));
+            ctx->fwd_wait_event = ctx->ev_w2;
+            ctx->fwd_wait_layer = split_layer;
+        }
+        FITRE_CUDA(cudaMemcpyAsync(v, vector_host, sizeof(double) * m->pSize, cudaMemcpyHostToDevice, cs));
+        FITRE_CUDA(cudaEventRecord(ctx->ev_up, cs));
         DEVICE_DATASET data;
         std::memset(&data, 0, sizeof(data));
         data.weights = w;
@@ -479,15 +499,24 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         double loss = 0.0;
         int rc = fitre_compute_cnn_gradient(ctx, m, &data, &sa, z, dx, probs, errs, g, 0, n,
                                             weightDecay, &loss);
+        ctx->fwd_wait_event = nullptr;
+        ctx->fwd_wait_layer = -1;
         FITRE_REQUIRE(rc == FITRE_OK, rc, ctx->err);
         // the gradient call returned after a stream sync (loss read-back): g is complete and
         // travels back on the copy stream while the Hessian-vector product runs
         FITRE_CUDA(cudaMemcpyAsync(gradient_host, g, sizeof(double) * m->pSize, cudaMemcpyDeviceToHost, cs));
-        FITRE_CUDA(cudaEventRecord(ctx->ev_down, cs));
         FITRE_CUDA(cudaStreamWaitEvent(st, ctx->ev_up, 0));
+        // single rank: finished slices of hv follow the gradient on the copy stream as the backward
+        // sweep completes its layers; with several ranks hv is only final after the all-reduce
+        ctx->hv_host_dst = ctx->world == 1 ? hv_host : nullptr;
+        ctx->hv_sent_from = m->pSize;
         rc = fitre_cnn_hv(ctx, m, &data, z, probs, errs, dx, v, hv, 0, n, ws, nullptr, weightDecay);
+        const long sent_from = ctx->hv_host_dst ? ctx->hv_sent_from : m->pSize;
+        ctx->hv_host_dst = nullptr;
         FITRE_REQUIRE(rc == FITRE_OK, rc, ctx->err);
-        FITRE_CUDA(cudaMemcpyAsync(hv_host, hv, sizeof(double) * m->pSize, cudaMemcpyDeviceToHost, st));
+        if (sent_from > 0)
+            FITRE_CUDA(cudaMemcpyAsync(hv_host, hv, sizeof(double) * sent_from, cudaMemcpyDeviceToHost, st));
+        FITRE_CUDA(cudaEventRecord(ctx->ev_down, cs));
         FITRE_CUDA(cudaStreamSynchronize(st));
         FITRE_CUDA(cudaEventSynchronize(ctx->ev_down));
         if (loss_host) *loss_host = loss;

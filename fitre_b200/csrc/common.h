@@ -60,6 +60,13 @@ struct fitre_context {
     size_t host_pinned_doubles = 0;
     cudaStream_t copy_stream = nullptr;   // second stream of the host-buffer entry point
     cudaEvent_t ev_up = nullptr, ev_down = nullptr;
+    // hooks of the host-buffer entry point: the forward pass waits for `fwd_wait_event` before conv
+    // layer `fwd_wait_layer` (late weights still uploading), and the R-backward pass sends finished
+    // slices of hv to `hv_host_dst` on the copy stream as the layers complete
+    cudaEvent_t fwd_wait_event = nullptr, ev_w2 = nullptr, chunk_ev[24] = {};
+    int fwd_wait_layer = -1;
+    double *hv_host_dst = nullptr;
+    long hv_sent_from = 0;
     double *tf32_buf = nullptr;           // staging of the opt-in tensor-core modes (fp32 operand copies,
     long tf32_cap = 0;                    // split slabs), owned by the context, grown on demand
     cudaStream_t inv_streams[4] = {};     // side streams of the batched factor inversion

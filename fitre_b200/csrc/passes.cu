@@ -91,6 +91,8 @@ double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET 
     double *tmp = scratch + bn_scratch(0);
     double *split = tmp + align32(last_pool_elems(m));
     for (int l = 0; l < m->cLayers; ++l) {
+        if (ctx->fwd_wait_event && l == ctx->fwd_wait_layer)
+            FITRE_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->fwd_wait_event, 0));
         const ConvGeom g = conv_geom(m, l);
         double *zl = z + g.zoff;
         ConvSeg seg{layer_input(m, data, z, l), weights + m->wOffsets[l]};
@@ -211,6 +213,20 @@ void cnn_rop_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASE
 }
 
 // ---------------------------------------------------------------------------------------------
+// Host-buffer entry point only (single rank): everything of hv at or beyond `from` is final once
+// the layers processed so far are done (the backward sweep runs from the last layer to the first),
+// so that slice goes to the host on the copy stream while the earlier layers are still computed.
+static void send_finished_hv(fitre_context *ctx, const double *hv, long from, int slot) {
+    if (!ctx->hv_host_dst || ctx->world > 1 || !ctx->copy_stream || from >= ctx->hv_sent_from) return;
+    cudaEvent_t &ev = ctx->chunk_ev[slot % 24];
+    if (!ev) FITRE_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    FITRE_CUDA(cudaEventRecord(ev, ctx->stream));
+    FITRE_CUDA(cudaStreamWaitEvent(ctx->copy_stream, ev, 0));
+    FITRE_CUDA(cudaMemcpyAsync(ctx->hv_host_dst + from, hv + from, sizeof(double) * (size_t)(ctx->hv_sent_from - from),
+                               cudaMemcpyDeviceToHost, ctx->copy_stream));
+    ctx->hv_sent_from = from;
+}
+
 void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data,
                       const double *z, const double *dx, const double *lossErrors, double *rError,
                       const double *rz, const double *vector, double *hv, int n, double *scratch) {
@@ -256,6 +272,7 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
         vec_copy(ctx, (long)l.in * n, t2, rError);
     }
     fc_to_conv(ctx, rError, lg.Cout, n, lg.Hp, lg.Wp, tmp);  // :414-427
+    send_finished_hv(ctx, hv, m->wOffsets[cL], cL);
 
     for (int c = cL - 1; c >= 0; --c) {  // :436-907
         const ConvGeom g = conv_geom(m, c);
@@ -277,6 +294,7 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
                              ConvSeg{dprev, vector + m->wOffsets[c]}};
             conv_dgrad(ctx, 2, ds, rError, n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wperm, split);
         }
+        send_finished_hv(ctx, hv, m->wOffsets[c], c);
     }
 }
 
