@@ -188,6 +188,12 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    try:  # the same step as PyTorch runs it on the host cores, for comparison with the port
+        rt, dtt = cpu_pytorch_rate(TORCH_SAMPLE_IMAGES)
+        line["cpu_baseline_pytorch"] = {"value": rt, "unit": "images/s", "cores": cores,
+                                        "sample": "%d images (%.1f s)" % (TORCH_SAMPLE_IMAGES, dtt)}
+    except Exception as e:  # noqa: BLE001
+        line["cpu_baseline_pytorch"] = {"unavailable": str(e)[:200]}
     print(json.dumps(line), flush=True)
 
 

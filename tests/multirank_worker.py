@@ -147,8 +147,17 @@ def main():
         Ai, Gi = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
         iscr = G.dev(np.zeros(_lib.load().fitre_kfac_invert_factors_mem_required(C.byref(model))))
         api.invertFactors(ctx, model, info, A, Ai, Gm, Gi, iscr)
-        np.savez(out, loss=run.loss, gradient=run.gradient, hv=hv, A=A.cpu().numpy(),
-                 G=Gm.cpu().numpy(), Ainv=Ai.cpu().numpy(), Ginv=Gi.cpu().numpy())
+        # the same gradient and Hv in the compensated tensor-core mode (sharded batch-norm statistics
+        # and all-reduces around the tcgen05 kernels)
+        g64, loss64 = run.gradient.copy(), run.loss
+        del run
+        ctx.set_precision(2)
+        run3 = G.GpuRun(model, xs, ys, w, ncls, ref_softmax=1)
+        hv3 = run3.hv(v)
+        ctx.set_precision(0)
+        np.savez(out, loss=loss64, gradient=g64, hv=hv, A=A.cpu().numpy(),
+                 G=Gm.cpu().numpy(), Ainv=Ai.cpu().numpy(), Ginv=Gi.cpu().numpy(),
+                 gradient_x3=run3.gradient, hv_x3=hv3)
         torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
