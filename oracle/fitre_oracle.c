@@ -206,35 +206,81 @@ long ora_model_zsize64(const CNN_MODEL *m) { return m->zSize; }
 /* ------------------------------------------------------------------------------------ */
 
 /* Column-major C = alpha * op(A) * op(B) + beta * C  (cublasDgemm semantics). */
+/* C = alpha op(A) op(B) + beta C, column-major (the cublasDgemm calls of the reference).  Plain
+ * loops, blocked so that operands are reused from cache and registers: every C element is still
+ * the sum over p in ascending order. */
+#define GEMM_MB 256
+#define GEMM_NB 8
 void ora_gemm(int tA, int tB, long m, long n, long k, double alpha, const double *A, long lda,
               const double *B, long ldb, double beta, double *C, long ldc) {
-#pragma omp parallel for schedule(static)
-    for (long j = 0; j < n; j++) {
-        double *c = C + j * ldc;
-        if (beta == 0.0)
-            for (long i = 0; i < m; i++) c[i] = 0.0;
-        else if (beta != 1.0)
-            for (long i = 0; i < m; i++) c[i] *= beta;
-        if (!tA) {
-            for (long p = 0; p < k; p++) {
-                double b = alpha * (tB ? B[j + p * ldb] : B[p + j * ldb]);
-                const double *a = A + p * lda;
-                for (long i = 0; i < m; i++) c[i] += a[i] * b;
-            }
-        } else {
-            for (long i = 0; i < m; i++) {
-                const double *a = A + i * lda;
-                double s = 0.0;
-                if (!tB) {
-                    const double *b = B + j * ldb;
-                    for (long p = 0; p < k; p++) s += a[p] * b[p];
-                } else {
-                    for (long p = 0; p < k; p++) s += a[p] * B[j + p * ldb];
+    if (!tA) {
+        const long mblocks = (m + GEMM_MB - 1) / GEMM_MB, nblocks = (n + GEMM_NB - 1) / GEMM_NB;
+#pragma omp parallel for collapse(2) schedule(static)
+        for (long jb = 0; jb < nblocks; jb++)
+            for (long ib = 0; ib < mblocks; ib++) {
+                const long i0 = ib * GEMM_MB, j0 = jb * GEMM_NB;
+                const long mb = (m - i0 < GEMM_MB) ? m - i0 : GEMM_MB;
+                const long nb = (n - j0 < GEMM_NB) ? n - j0 : GEMM_NB;
+                double acc[GEMM_NB][GEMM_MB];
+                for (long j = 0; j < nb; j++)
+                    for (long i = 0; i < mb; i++) acc[j][i] = 0.0;
+                for (long p = 0; p < k; p++) {
+                    const double *a = A + p * lda + i0;
+                    for (long j = 0; j < nb; j++) {
+                        const double bv = alpha * (tB ? B[(j0 + j) + p * ldb] : B[p + (j0 + j) * ldb]);
+                        double *c = acc[j];
+                        for (long i = 0; i < mb; i++) c[i] += a[i] * bv;
+                    }
                 }
-                c[i] += alpha * s;
+                for (long j = 0; j < nb; j++) {
+                    double *c = C + (j0 + j) * ldc + i0;
+                    if (beta == 0.0)
+                        for (long i = 0; i < mb; i++) c[i] = acc[j][i];
+                    else
+                        for (long i = 0; i < mb; i++) c[i] = beta * c[i] + acc[j][i];
+                }
             }
-        }
+        return;
     }
+    /* op(A) = A': rows of op(A) are contiguous columns of A; 4 x 4 register blocks of dot products */
+    const long iblocks = (m + 3) / 4, jblocks = (n + 3) / 4;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (long jb = 0; jb < jblocks; jb++)
+        for (long ib = 0; ib < iblocks; ib++) {
+            const long i0 = ib * 4, j0 = jb * 4;
+            const long mb = (m - i0 < 4) ? m - i0 : 4, nb = (n - j0 < 4) ? n - j0 : 4;
+            double s[4][4] = {{0}};
+            if (mb == 4 && nb == 4 && !tB) {
+                const double *a0 = A + i0 * lda, *a1 = a0 + lda, *a2 = a1 + lda, *a3 = a2 + lda;
+                const double *b0 = B + j0 * ldb, *b1 = b0 + ldb, *b2 = b1 + ldb, *b3 = b2 + ldb;
+                for (long p = 0; p < k; p++) {
+                    const double x0 = a0[p], x1 = a1[p], x2 = a2[p], x3 = a3[p];
+                    const double y0 = b0[p], y1 = b1[p], y2 = b2[p], y3 = b3[p];
+                    s[0][0] += x0 * y0; s[0][1] += x0 * y1; s[0][2] += x0 * y2; s[0][3] += x0 * y3;
+                    s[1][0] += x1 * y0; s[1][1] += x1 * y1; s[1][2] += x1 * y2; s[1][3] += x1 * y3;
+                    s[2][0] += x2 * y0; s[2][1] += x2 * y1; s[2][2] += x2 * y2; s[2][3] += x2 * y3;
+                    s[3][0] += x3 * y0; s[3][1] += x3 * y1; s[3][2] += x3 * y2; s[3][3] += x3 * y3;
+                }
+            } else {
+                for (long i = 0; i < mb; i++)
+                    for (long j = 0; j < nb; j++) {
+                        const double *a = A + (i0 + i) * lda;
+                        double t = 0.0;
+                        if (!tB) {
+                            const double *bb = B + (j0 + j) * ldb;
+                            for (long p = 0; p < k; p++) t += a[p] * bb[p];
+                        } else {
+                            for (long p = 0; p < k; p++) t += a[p] * B[(j0 + j) + p * ldb];
+                        }
+                        s[i][j] = t;
+                    }
+            }
+            for (long i = 0; i < mb; i++)
+                for (long j = 0; j < nb; j++) {
+                    double *c = C + (j0 + j) * ldc + (i0 + i);
+                    *c = (beta == 0.0 ? 0.0 : beta * *c) + alpha * s[i][j];
+                }
+        }
 }
 
 static void axpy(long n, double a, const double *x, double *y) {
