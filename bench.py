@@ -219,7 +219,7 @@ def run_ours(args):
     if world > 1:
         ctx.comm_init_from_torch()
     if args.precision != "fp64":
-        ctx.set_precision({"tf32": 1, "tf32x3": 2}[args.precision])
+        ctx.set_precision({"tf32": 1, "tf32x3": 2, "fp64i8": 3}[args.precision])
     x, y, w, v = synth(model, n, 3234 + rank)   # each rank holds its own shard of the batch
     _, _, w, v = synth(model, n, 3234)          # parameters and direction are replicated
     f64 = dict(dtype=torch.float64, device="cuda")
@@ -562,7 +562,7 @@ def main():
     ap.add_argument("--per-gpu-batch", type=int, default=PER_GPU_BATCH,
                     help="images per GPU (default 512, the benchmark shape; smaller values are "
                          "for profiler captures only)")
-    ap.add_argument("--precision", default="fp64", choices=["fp64", "tf32", "tf32x3"],
+    ap.add_argument("--precision", default="fp64", choices=["fp64", "tf32", "tf32x3", "fp64i8"],
                     help="fp64 = the reference's arithmetic (default, the benchmark); tf32 / tf32x3 = "
                          "the opt-in tcgen05 modes (one TF32 product / error-compensated three), "
                          "reported under their own dtype and never as the headline")

@@ -93,6 +93,7 @@ int fitre_context_create(fitre_context **out, int device, void *stream) {
         FITRE_CUDA(cudaMalloc((void **)&ctx->dscal, 4096 * sizeof(double)));
         FITRE_CUDA(cudaMemsetAsync(ctx->dscal, 0, 4096 * sizeof(double), ctx->stream));
         gemm_init_attributes();
+        if (const char *e = std::getenv("FITRE_I8_WGRAD")) ctx->i8_wgrad = std::atoi(e);
     });
     if (rc != FITRE_OK) {
         fitre_context_destroy(ctx);
@@ -148,7 +149,7 @@ int fitre_set_reference_softmax(fitre_context *ctx, int on) {
 
 int fitre_set_precision(fitre_context *ctx, int precision) {
     if (!ctx || (precision != FITRE_PRECISION_FP64 && precision != FITRE_PRECISION_TF32 &&
-                 precision != FITRE_PRECISION_TF32X3))
+                 precision != FITRE_PRECISION_TF32X3 && precision != FITRE_PRECISION_FP64_I8))
         return FITRE_ERR_BAD_ARG;
     ctx->precision = precision;
     return FITRE_OK;

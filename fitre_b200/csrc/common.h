@@ -47,6 +47,7 @@ struct fitre_context {
     long long launches = 0;
     std::string err;
     int ref_softmax = 1;
+    int i8_wgrad = 1;           // FITRE_PRECISION_FP64_I8: weight gradients through the int8 kernel too
     int precision = 0;          // FITRE_PRECISION_* (convolution products)
     bool use_tma = true;        // TMA-fed convolution kernels where shape and alignment allow
     double *pinned = nullptr;   // 256 pinned host doubles (scalar read-back)
@@ -167,6 +168,12 @@ bool conv_wgrad_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, double *d
 // conv_tf32.cu
 void conv_tf32_init_attributes();
 long conv_fprop_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
+// conv_i8.cu
+void conv_i8_init_attributes();
+bool conv_fprop_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y, int N,
+                   int Cin, int H, int W, int k, int pad, int Cout);
+bool conv_wgrad_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin, int H, int W,
+                   int k, int pad, int Cout);
 long conv_wgrad_tf32_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);
 bool conv_wgrad_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin, int H,
                      int W, int k, int pad, int Cout, double *scratch);

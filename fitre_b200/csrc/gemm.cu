@@ -817,9 +817,12 @@ long conv_dgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) 
 
 void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double *bias, double *y,
                 int N, int Cin, int H, int W, int k, int pad, int Cout, double *split) {
-    if (ctx->precision != FITRE_PRECISION_FP64 &&
-        conv_fprop_tf32(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout, split))
+    if (ctx->precision == FITRE_PRECISION_FP64_I8) {
+        if (conv_fprop_i8(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout)) return;
+    } else if (ctx->precision != FITRE_PRECISION_FP64 &&
+               conv_fprop_tf32(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout, split)) {
         return;
+    }
     if (ctx->use_tma && conv_fprop_tma(ctx, nseg, segs, bias, y, N, Cin, H, W, k, pad, Cout, split)) return;
     ConvArgs a{};
     for (int s = 0; s < nseg; ++s) {
@@ -876,8 +879,11 @@ long conv_wgrad_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout) 
 
 void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, int N, int Cin,
                 int H, int W, int k, int pad, int Cout, double *partials) {
-    if (ctx->precision != FITRE_PRECISION_FP64 &&
+    if ((ctx->precision == FITRE_PRECISION_TF32 || ctx->precision == FITRE_PRECISION_TF32X3) &&
         conv_wgrad_tf32(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout, partials))
+        return;
+    if (ctx->precision == FITRE_PRECISION_FP64_I8 && ctx->i8_wgrad &&
+        conv_wgrad_i8(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout))
         return;
     if (ctx->use_tma && conv_wgrad_tma(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout, partials)) return;
     WgradArgs a{};
@@ -1016,6 +1022,7 @@ void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int 
 void gemm_init_attributes() {
     conv_tma_init_attributes();
     conv_tf32_init_attributes();
+    conv_i8_init_attributes();
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));

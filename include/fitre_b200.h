@@ -216,9 +216,14 @@ int fitre_set_reference_softmax(fitre_context *ctx, int on);
  *     relative of fp64 and the loss within 1e-3, but batch normalisation and the backward sweep
  *     amplify the rounding: gradients and Hessian-vector products of deep nets are only within
  *     1e-1 relative (measured 3e-2 / 5e-2 on VGG-11-BN), so this mode does not meet 1e-3.
+ *   FITRE_PRECISION_FP64_I8: fp64-class results from the integer tensor cores: operands in fixed
+ *     point (power-of-two scale per channel), six signed base-128 digits each, the digit
+ *     products summed exactly in int32 (tcgen05.mma.kind::i8) and recombined in fp64; terms below
+ *     128^-7 of full scale are dropped.  Stated tolerance against the fp64 result: 1e-10
+ *     relative, the same as the default mode's against the reference.
  * Shapes the tensor-core kernels do not cover (the 3-channel first layer, odd input heights, ...)
  * use the fp64 kernels in every mode.  No counterpart in the reference (fp64 only). */
-enum { FITRE_PRECISION_FP64 = 0, FITRE_PRECISION_TF32 = 1, FITRE_PRECISION_TF32X3 = 2 };
+enum { FITRE_PRECISION_FP64 = 0, FITRE_PRECISION_TF32 = 1, FITRE_PRECISION_TF32X3 = 2, FITRE_PRECISION_FP64_I8 = 3 };
 int fitre_set_precision(fitre_context *ctx, int precision);
 
 /* 1 (default) = use the TMA-fed convolution kernels wherever shape and alignment allow;
