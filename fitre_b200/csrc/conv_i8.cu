@@ -516,33 +516,47 @@ __global__ void slice_rows_kernel(const double *__restrict__ e, const double *__
         }
     }
 }
-// x [C][N][W][H] fp64 -> patch digit planes [plane][K][M] int8 (row q = c*kk + j*k + i, column
-// m = (n, wo, ho)) of the patch value over the channel's scale; four positions per thread
-__global__ void im2col_slice_kernel(const double *__restrict__ x, const double *__restrict__ chmax,
-                                    signed char *__restrict__ planes, int N, int H, int W, int k, int pad,
-                                    int Ho, int Wo, int M, int K) {
-    const int q = blockIdx.y, kk = k * k;
-    const int c = q / kk, tap = q - c * kk;
-    const int j = tap / k, i = tap - j * k;
+// x [C][P] fp64 -> digit planes [plane][C][P] int8 of x / scale(channel), same element order; four
+// elements per thread
+__global__ void slice_same_layout_kernel(const double *__restrict__ x, const double *__restrict__ chmax,
+                                         signed char *__restrict__ planes, int C, long P) {
+    const int c = blockIdx.y;
     const double inv = 1.0 / pow2_scale(chmax[c]);
-    const double *xc = x + (long)c * N * W * H;
-    for (int m4 = (blockIdx.x * blockDim.x + threadIdx.x) * 4; m4 < M; m4 += gridDim.x * blockDim.x * 4) {
+    const double *xc = x + (long)c * P;
+    for (long p4 = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4; p4 < P; p4 += (long)gridDim.x * blockDim.x * 4) {
         signed char d[4][I_S];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const int m = m4 + t;
-            const int ho = m % Ho, u = m / Ho;
-            const int wo = u % Wo, n = u / Wo;
-            const int h = ho + i - pad, w = wo + j - pad;
-            const double v = (m < M && h >= 0 && h < H && w >= 0 && w < W) ? xc[((long)n * W + w) * H + h] : 0.0;
-            digits128(v * inv, d[t]);
-        }
+        for (int t = 0; t < 4; ++t) digits128(p4 + t < P ? xc[p4 + t] * inv : 0.0, d[t]);
 #pragma unroll
         for (int pl = 0; pl < I_S; ++pl) {
             char4 v;
             v.x = d[0][pl]; v.y = d[1][pl]; v.z = d[2][pl]; v.w = d[3][pl];
-            *reinterpret_cast<char4 *>(planes + ((long)pl * K + q) * M + m4) = v;
+            *reinterpret_cast<char4 *>(planes + ((long)pl * C + c) * P + p4) = v;
         }
+    }
+}
+// digit planes of the input [plane][C][N][W][H] -> patch digit planes [plane][K][M] (row q = c*kk +
+// j*k + i, column m = (n, wo, ho), zero outside the image): a byte gather, the digits of an input
+// element being the same in all k*k patches it appears in.  blockIdx.y = q, blockIdx.z = plane;
+// sixteen positions per thread, one 16-byte store.
+__global__ void im2col_bytes_kernel(const signed char *__restrict__ xin, signed char *__restrict__ planes,
+                                    int C, int N, int H, int W, int k, int pad, int Ho, int Wo, int M, int K) {
+    const int q = blockIdx.y, pl = blockIdx.z, kk = k * k;
+    const int c = q / kk, tap = q - c * kk;
+    const int j = tap / k, i = tap - j * k;
+    const signed char *xc = xin + ((long)pl * C + c) * N * W * H;
+    signed char *out = planes + ((long)pl * K + q) * M;
+    for (int m16 = (blockIdx.x * blockDim.x + threadIdx.x) * 16; m16 < M; m16 += gridDim.x * blockDim.x * 16) {
+        alignas(16) signed char v[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+            const int m = m16 + t;
+            const int ho = m % Ho, u = m / Ho;
+            const int wo = u % Wo, n = u / Wo;
+            const int h = ho + i - pad, w = wo + j - pad;
+            v[t] = (m < M && h >= 0 && h < H && w >= 0 && w < W) ? xc[((long)n * W + w) * H + h] : (signed char)0;
+        }
+        *reinterpret_cast<int4 *>(out + m16) = *reinterpret_cast<const int4 *>(v);
     }
 }
 // dW = sum over splits and segments of the slabs, fixed order
@@ -667,7 +681,9 @@ bool conv_wgrad_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
     const long K = (long)Cin * k * k, M = (long)N * Ho * Wo;
     // row strides of both int8 matrices are M bytes and must be multiples of 16
-    if (Ho < 1 || Wo < 1 || K % I_BN != 0 || K > 65535 || (M & 15) || M < 256 || M > (1L << 30)) return false;
+    if (Ho < 1 || Wo < 1 || K % I_BN != 0 || K > 65535 || (M & 15) || M < 256 || M > (1L << 30) ||
+        (((long)N * W * H) & 3))
+        return false;
     I8WgradArgs a{};
     a.nseg = nseg; a.Cout = Cout; a.K = (int)K; a.kk = k * k;
     a.CoutPad = (Cout + I_BM - 1) / I_BM * I_BM;
@@ -685,7 +701,9 @@ bool conv_wgrad_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw
     // workspace (doubles): slabs (S x nseg) | per segment: error scales, channel maxima, error planes, patch planes
     const long o_seg = up32((long)S * nseg * K * Cout);
     const long e_bytes = (long)I_S * a.CoutPad * M, p_bytes = (long)I_S * K * M;
-    const long seg_doubles = up32(a.CoutPad) + up32(Cin) + up32((e_bytes + 7) / 8) + up32((p_bytes + 7) / 8);
+    const long x_bytes = (long)I_S * Cin * N * W * H;
+    const long seg_doubles = up32(a.CoutPad) + up32(Cin) + up32((e_bytes + 7) / 8) + up32((p_bytes + 7) / 8) +
+                             up32((x_bytes + 7) / 8);
     double *ws = tf32_workspace(ctx, o_seg + 2 * seg_doubles + 64);
     a.out = ws;
     for (int s = 0; s < nseg; ++s) {
@@ -694,6 +712,7 @@ bool conv_wgrad_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw
         double *chmax = escale + up32(a.CoutPad);
         signed char *ep = (signed char *)(chmax + up32(Cin));
         signed char *pp = ep + up32((e_bytes + 7) / 8) * 8;
+        signed char *xq = pp + up32((p_bytes + 7) / 8) * 8;
         FITRE_CUDA(cudaMemsetAsync(escale, 0, sizeof(double) * (up32(a.CoutPad) + up32(Cin)), ctx->stream));
         const unsigned gx = (unsigned)std::min<long>((M + 1023) / 1024, 64);
         row_absmax_kernel<<<dim3(gx, (unsigned)Cout), 256, 0, ctx->stream>>>(segs[s].w, M, (unsigned long long *)escale);
@@ -709,9 +728,12 @@ bool conv_wgrad_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw
         slice_rows_kernel<<<dim3((unsigned)std::min<long>((M / 4 + 255) / 256, 64), (unsigned)Cout), 256, 0,
                             ctx->stream>>>(segs[s].w, escale, ep, a.CoutPad, M);
         check_launch(ctx, "slice_rows_kernel");
-        im2col_slice_kernel<<<dim3((unsigned)std::min<long>((M / 4 + 255) / 256, 64), (unsigned)K), 256, 0,
-                              ctx->stream>>>(segs[s].x, chmax, pp, N, H, W, k, pad, Ho, Wo, (int)M, (int)K);
-        check_launch(ctx, "im2col_slice_kernel");
+        slice_same_layout_kernel<<<dim3((unsigned)std::min<long>((P / 4 + 255) / 256, 64), (unsigned)Cin), 256, 0,
+                                   ctx->stream>>>(segs[s].x, chmax, xq, Cin, P);
+        check_launch(ctx, "slice_same_layout_kernel");
+        im2col_bytes_kernel<<<dim3((unsigned)std::min<long>((M / 16 + 127) / 128, 64), (unsigned)K, I_S), 128, 0,
+                              ctx->stream>>>(xq, pp, Cin, N, H, W, k, pad, Ho, Wo, (int)M, (int)K);
+        check_launch(ctx, "im2col_bytes_kernel");
         a.escale[s] = escale;
         a.chmax[s] = chmax;
         cuuint64_t dd[2] = {(cuuint64_t)M, (cuuint64_t)I_S * a.CoutPad};

@@ -399,3 +399,35 @@ def test_cuda_reduced_precision_modes_within_stated_tolerance():
                 del run
     finally:
         c.set_precision(0)
+
+
+def test_cuda_int8_tensor_core_fp64_mode_within_1e_10():
+    """Opt-in mode 3: convolution products from base-128 digit planes on the int8 tensor cores with
+    exact int32 digit sums, recombined in fp64.  Stated tolerance against the fp64 oracle: the
+    default mode's own 1e-10, norm-wise and max-wise."""
+    import gpu_util as G
+    wide = S.describe_model(
+        [dict(cin=3, cout=64, h=8, w=8, k=3, pad=1, bn=True, act=S.CNN_ACT_SWISH, pool=None),
+         dict(cin=64, cout=64, h=8, w=8, k=5, pad=2, bn=True, act=S.CNN_ACT_SWISH, pool=(S.MAX_POOL, 2, 2, 0)),
+         dict(cin=64, cout=96, h=4, w=4, k=3, pad=1, bn=True, act=S.CNN_ACT_SOFTPLUS, pool=(S.AVG_POOL, 2, 2, 0))],
+        [(96 * 2 * 2, 10, S.CNN_ACT_NONE)], 16, True)
+    c = G.ctx()
+    try:
+        for model, n in ((nets.vgg11(8), 8), (wide, 16)):
+            O.finalize(model)
+            x, y, w, v, ncls = G.synth(model, n, seed=23)
+            st = O.gradient(model, x, y, w, ncls, n)
+            hv_o = O.hv(model, x, w, ncls, n, st, v)
+            c.set_precision(3)
+            run = G.GpuRun(model, x, y, w, ncls)
+            hv = run.hv(v)
+            c.set_precision(0)
+            assert abs(run.loss - st.loss) <= TOL * abs(st.loss)
+            eg, eh = G.rel(run.gradient, st.gradient), G.rel(hv, hv_o)
+            assert eg < TOL and eh < TOL, (eg, eh)
+            assert G.relmax(run.gradient, st.gradient) < TOL and G.relmax(hv, hv_o) < TOL
+            # the integer path really ran (the fp64 kernels agree with the oracle to ~1e-14)
+            assert eg > 2e-13, eg
+            del run
+    finally:
+        c.set_precision(0)
