@@ -537,26 +537,41 @@ __global__ void slice_same_layout_kernel(const double *__restrict__ x, const dou
 }
 // digit planes of the input [plane][C][N][W][H] -> patch digit planes [plane][K][M] (row q = c*kk +
 // j*k + i, column m = (n, wo, ho), zero outside the image): a byte gather, the digits of an input
-// element being the same in all k*k patches it appears in.  blockIdx.y = q, blockIdx.z = plane;
-// sixteen positions per thread, one 16-byte store.
+// element being the same in all k*k patches it appears in.  blockIdx.y = q; a thread resolves the
+// source offsets of sixteen consecutive positions once (walking (ho, wo, n) incrementally) and
+// reuses them for all six planes, one 16-byte store per plane.
 __global__ void im2col_bytes_kernel(const signed char *__restrict__ xin, signed char *__restrict__ planes,
                                     int C, int N, int H, int W, int k, int pad, int Ho, int Wo, int M, int K) {
-    const int q = blockIdx.y, pl = blockIdx.z, kk = k * k;
+    const int q = blockIdx.y, kk = k * k;
     const int c = q / kk, tap = q - c * kk;
     const int j = tap / k, i = tap - j * k;
-    const signed char *xc = xin + ((long)pl * C + c) * N * W * H;
-    signed char *out = planes + ((long)pl * K + q) * M;
+    const long plane_in = (long)C * N * W * H, plane_out = (long)K * M;
+    const signed char *xc = xin + (long)c * N * W * H;
+    signed char *out = planes + (long)q * M;
     for (int m16 = (blockIdx.x * blockDim.x + threadIdx.x) * 16; m16 < M; m16 += gridDim.x * blockDim.x * 16) {
-        alignas(16) signed char v[16];
+        int off[16];
+        int ho = m16 % Ho, u = m16 / Ho;
+        int wo = u % Wo, n = u / Wo;
 #pragma unroll
         for (int t = 0; t < 16; ++t) {
-            const int m = m16 + t;
-            const int ho = m % Ho, u = m / Ho;
-            const int wo = u % Wo, n = u / Wo;
             const int h = ho + i - pad, w = wo + j - pad;
-            v[t] = (m < M && h >= 0 && h < H && w >= 0 && w < W) ? xc[((long)n * W + w) * H + h] : (signed char)0;
+            off[t] = (m16 + t < M && h >= 0 && h < H && w >= 0 && w < W) ? (n * W + w) * H + h : -1;
+            if (++ho == Ho) {
+                ho = 0;
+                if (++wo == Wo) {
+                    wo = 0;
+                    ++n;
+                }
+            }
         }
-        *reinterpret_cast<int4 *>(out + m16) = *reinterpret_cast<const int4 *>(v);
+#pragma unroll 1
+        for (int pl = 0; pl < I_S; ++pl) {
+            const signed char *xp = xc + pl * plane_in;
+            alignas(16) signed char v[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t) v[t] = off[t] >= 0 ? xp[off[t]] : (signed char)0;
+            *reinterpret_cast<int4 *>(out + pl * plane_out + m16) = *reinterpret_cast<const int4 *>(v);
+        }
     }
 }
 // dW = sum over splits and segments of the slabs, fixed order
@@ -731,7 +746,7 @@ bool conv_wgrad_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw
         slice_same_layout_kernel<<<dim3((unsigned)std::min<long>((P / 4 + 255) / 256, 64), (unsigned)Cin), 256, 0,
                                    ctx->stream>>>(segs[s].x, chmax, xq, Cin, P);
         check_launch(ctx, "slice_same_layout_kernel");
-        im2col_bytes_kernel<<<dim3((unsigned)std::min<long>((M / 16 + 127) / 128, 64), (unsigned)K, I_S), 128, 0,
+        im2col_bytes_kernel<<<dim3((unsigned)std::min<long>((M / 16 + 127) / 128, 64), (unsigned)K), 128, 0,
                               ctx->stream>>>(xq, pp, Cin, N, H, W, k, pad, Ho, Wo, (int)M, (int)K);
         check_launch(ctx, "im2col_bytes_kernel");
         a.escale[s] = escale;
