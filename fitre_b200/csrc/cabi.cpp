@@ -93,7 +93,6 @@ int fitre_context_create(fitre_context **out, int device, void *stream) {
         FITRE_CUDA(cudaMalloc((void **)&ctx->dscal, 4096 * sizeof(double)));
         FITRE_CUDA(cudaMemsetAsync(ctx->dscal, 0, 4096 * sizeof(double), ctx->stream));
         gemm_init_attributes();
-        if (const char *e = std::getenv("FITRE_I8_WGRAD")) ctx->i8_wgrad = std::atoi(e);
     });
     if (rc != FITRE_OK) {
         fitre_context_destroy(ctx);
@@ -115,7 +114,7 @@ int fitre_context_destroy(fitre_context *ctx) {
     if (ctx->dscal) cudaFree(ctx->dscal);
     if (ctx->host_ws) cudaFree(ctx->host_ws);
     if (ctx->host_pinned) cudaFreeHost(ctx->host_pinned);
-    if (ctx->tf32_buf) cudaFree(ctx->tf32_buf);
+    if (ctx->staging_buf) cudaFree(ctx->staging_buf);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
     for (int s = 0; s < 4; ++s) {
         if (ctx->inv_streams[s]) cudaStreamDestroy(ctx->inv_streams[s]);

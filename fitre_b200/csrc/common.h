@@ -47,7 +47,6 @@ struct fitre_context {
     long long launches = 0;
     std::string err;
     int ref_softmax = 1;
-    int i8_wgrad = 1;           // FITRE_PRECISION_FP64_I8: weight gradients through the int8 kernel too
     int precision = 0;          // FITRE_PRECISION_* (convolution products)
     bool use_tma = true;        // TMA-fed convolution kernels where shape and alignment allow
     double *pinned = nullptr;   // 256 pinned host doubles (scalar read-back)
@@ -68,8 +67,8 @@ struct fitre_context {
     int fwd_wait_layer = -1;
     double *hv_host_dst = nullptr;
     long hv_sent_from = 0;
-    double *tf32_buf = nullptr;           // staging of the opt-in tensor-core modes (fp32 operand copies,
-    long tf32_cap = 0;                    // split slabs), owned by the context, grown on demand
+    double *staging_buf = nullptr;        // staging of the opt-in tensor-core modes (operand copies, digit
+    long staging_cap = 0;                 // planes, split slabs), owned by the context, grown on demand
     cudaStream_t inv_streams[4] = {};     // side streams of the batched factor inversion
     cudaEvent_t inv_fork = nullptr, inv_join[4] = {};
     // optional per-kernel timing (CUDA events on the launch stream), see fitre_profile_*

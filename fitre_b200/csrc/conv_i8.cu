@@ -597,7 +597,7 @@ void conv_i8_init_attributes() {
     FITRE_CUDA(cudaFuncSetAttribute(wgrad_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemI8));
 }
 
-double *tf32_workspace(fitre_context *ctx, long doubles);   // the context-owned staging buffer (conv_tf32.cu)
+double *staging_workspace(fitre_context *ctx, long doubles);   // the context-owned staging buffer (conv_tf32.cu)
 
 // Y = sum_seg im2col(x_seg) * w_seg (+ bias) through int8 digit planes; false when the shape does
 // not fit (channel count not a multiple of 64, tile shape), the caller then uses the fp64 kernels.
@@ -634,7 +634,7 @@ bool conv_fprop_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, const doub
     const long o_scale = up32(SK > 1 ? (long)SK * M * Cout : 0);
     const long o_seg = o_scale + up32(Cout);
     const long seg_doubles = up32(Cin) + up32((I_S * P * Cin + 7) / 8) + up32((I_S * K * a.CoutPad + 7) / 8);
-    double *ws = tf32_workspace(ctx, o_seg + 2 * seg_doubles + 64);
+    double *ws = staging_workspace(ctx, o_seg + 2 * seg_doubles + 64);
     double *slabs = ws, *colscale = ws + o_scale;
     a.colscale = colscale;
     a.y = SK > 1 ? slabs : y;
@@ -719,7 +719,7 @@ bool conv_wgrad_i8(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw
     const long x_bytes = (long)I_S * Cin * N * W * H;
     const long seg_doubles = up32(a.CoutPad) + up32(Cin) + up32((e_bytes + 7) / 8) + up32((p_bytes + 7) / 8) +
                              up32((x_bytes + 7) / 8);
-    double *ws = tf32_workspace(ctx, o_seg + 2 * seg_doubles + 64);
+    double *ws = staging_workspace(ctx, o_seg + 2 * seg_doubles + 64);
     a.out = ws;
     for (int s = 0; s < nseg; ++s) {
         if (((uintptr_t)segs[s].x & 15) || ((uintptr_t)segs[s].w & 15)) return false;

@@ -735,16 +735,16 @@ Tf32Scratch tf32_scratch_layout(int N, int Cin, int H, int W, int k, int pad, in
 // The reduced-precision modes have no counterpart in the reference, so their staging does not
 // come out of the caller's scratch (whose size is the fp64 path's): the context owns one buffer,
 // allocated and grown in stream order on first need.
-double *tf32_workspace(fitre_context *ctx, long doubles) {
-    if (doubles > ctx->tf32_cap) {
-        if (ctx->tf32_buf) FITRE_CUDA(cudaFreeAsync(ctx->tf32_buf, ctx->stream));
-        ctx->tf32_buf = nullptr;
-        ctx->tf32_cap = 0;
+double *staging_workspace(fitre_context *ctx, long doubles) {
+    if (doubles > ctx->staging_cap) {
+        if (ctx->staging_buf) FITRE_CUDA(cudaFreeAsync(ctx->staging_buf, ctx->stream));
+        ctx->staging_buf = nullptr;
+        ctx->staging_cap = 0;
         const long cap = doubles + doubles / 8;
-        FITRE_CUDA(cudaMallocAsync((void **)&ctx->tf32_buf, sizeof(double) * (size_t)cap, ctx->stream));
-        ctx->tf32_cap = cap;
+        FITRE_CUDA(cudaMallocAsync((void **)&ctx->staging_buf, sizeof(double) * (size_t)cap, ctx->stream));
+        ctx->staging_cap = cap;
     }
-    return ctx->tf32_buf;
+    return ctx->staging_buf;
 }
 
 long conv_fprop_tf32_scratch(int, int, int, int, int, int, int) { return 0; }
@@ -764,7 +764,7 @@ bool conv_fprop_tf32_direct(fitre_context *ctx, int nseg, const ConvSeg *segs, c
     const int TN = F_BM / (TH * TW);
     if (TH > 256 || TW > 256 || TN > 256) return false;
     const Tf32Scratch L = tf32_scratch_layout(N, Cin, H, W, k, pad, Cout);
-    double *scratch = tf32_workspace(ctx, L.total);
+    double *scratch = staging_workspace(ctx, L.total);
     const int BN = (Cout % 128 == 0) ? 128 : 64;
     const int K = Cin * k * k;
     Tf32DirectArgs a{};
@@ -893,7 +893,7 @@ bool conv_fprop_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, const do
     int SK = std::min(L.sk_max, tf32_split(a.M, Cout, iters));   // L.sk_max: what the scratch was sized for
     a.iters_per_split = (iters + SK - 1) / SK;
     SK = (iters + a.iters_per_split - 1) / a.iters_per_split;
-    double *scratch = tf32_workspace(ctx, L.total);
+    double *scratch = staging_workspace(ctx, L.total);
     double *slabs = scratch + L.slabs;
     float *w32 = (float *)(scratch + L.weights);
     a.y = SK > 1 ? slabs : y;
@@ -975,7 +975,7 @@ bool conv_wgrad_tf32(fitre_context *ctx, int nseg, const ConvSeg *segs, double *
     if (!encode_fn()) return false;
     const WgradTf32Plan P = wgrad_tf32_plan(N, Cin, H, W, k, pad, Cout);
     if (!P.ok) return false;
-    double *scratch = tf32_workspace(ctx, P.total);
+    double *scratch = staging_workspace(ctx, P.total);
     const bool x3 = ctx->precision == FITRE_PRECISION_TF32X3;
     const int parts = x3 ? 2 : 1;
     Tf32WgradArgs a{};

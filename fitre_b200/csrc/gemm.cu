@@ -882,7 +882,7 @@ void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, i
     if ((ctx->precision == FITRE_PRECISION_TF32 || ctx->precision == FITRE_PRECISION_TF32X3) &&
         conv_wgrad_tf32(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout, partials))
         return;
-    if (ctx->precision == FITRE_PRECISION_FP64_I8 && ctx->i8_wgrad &&
+    if (ctx->precision == FITRE_PRECISION_FP64_I8 &&
         conv_wgrad_i8(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout))
         return;
     if (ctx->use_tma && conv_wgrad_tma(ctx, nseg, segs, dw, N, Cin, H, W, k, pad, Cout, partials)) return;
