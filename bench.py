@@ -398,6 +398,8 @@ def run_extra(args):
     ws = api.Workspace(model, 10)
     extra = {}
     if wl == "kfac":
+        ctx.set_kfac_solver(1 if args.kfac_solver == "cholesky" else 0)
+        extra["kfac_solver"] = args.kfac_solver
         info = api.computeKFACStorageIndices(model)
         need = _lib.load().fitre_kfac_mem_required(C.byref(model))
         kscr = torch.zeros(max(need, ws.dev.numel()), **f64)
@@ -442,7 +444,7 @@ def run_extra(args):
             api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
             api.computeOmegaZ(ctx, model, data, ws.z, n, A, info, kscr)
             api.computeLambdaDelta(ctx, model, ddx, n, G, info, kscr)
-            api.invertFactors(ctx, model, info, A, Ai, G, Gi, iscr)  # 22 damped Cholesky inverses
+            api.invertFactors(ctx, model, info, A, Ai, G, Gi, iscr)  # 22 damped factors: inverses or Cholesky
             api.computeNaturalGradient(ctx, model, info, Ai, Gi, ws.gradient, ngrad, iscr)
 
     def barrier():
@@ -501,6 +503,7 @@ def run_fitre(args):
     ctx = api.Context(local)
     if world > 1:
         ctx.comm_init_from_torch()
+    ctx.set_kfac_solver(1 if args.kfac_solver == "cholesky" else 0)
     n = 256
     model = nets.vgg11(n)
     api.finalize(model)
@@ -541,6 +544,7 @@ def run_fitre(args):
             "steps": ep.miniBatches, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "dtype": "f64", "data": "synthetic",
             "config": {"workload": "vgg11bn_32x32_fp64_fitre_loop_minibatch", "per_gpu_batch": n,
+                       "kfac_solver": args.kfac_solver,
                        "timing": "host clock around the minibatch sweep inside the library call, max over ranks"},
             "first_loss": steps[0].trainLikelihood, "last_loss": steps[-1].newTrainLikelihood,
             "kfac_steps": sum(s.usedKfac for s in steps), "reverted": sum(s.reverted for s in steps),
@@ -566,6 +570,9 @@ def main():
                     help="fp64 = the reference's arithmetic (default, the benchmark); tf32 / tf32x3 = "
                          "the opt-in tcgen05 modes (one TF32 product / error-compensated three), "
                          "reported under their own dtype and never as the headline")
+    ap.add_argument("--kfac-solver", default="cholesky", choices=["inverse", "cholesky"],
+                    help="kfac / fitre workloads: explicit damped inverses of the A blocks (the "
+                         "reference's form) or Cholesky factors applied by triangular solves")
     ap.add_argument("--skip-cpu", action="store_true",
                     help="leave the CPU baseline leg out (profiling runs)")
     args = ap.parse_args()

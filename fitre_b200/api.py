@@ -77,6 +77,11 @@ class Context:
         2 = error-compensated 3 x TF32 (gradient and Hv within 1e-3 of fp64)."""
         self.check(self.lib.fitre_set_precision(self.h, int(precision)))
 
+    def set_kfac_solver(self, solver):
+        """0 = explicit damped inverses of the A blocks (reference form); 1 = Cholesky factors in
+        the same slots, applied by two triangular solves in the natural gradient."""
+        self.check(self.lib.fitre_set_kfac_solver(self.h, int(solver)))
+
     def set_tma(self, on):
         self.check(self.lib.fitre_set_tma(self.h, int(bool(on))))
 

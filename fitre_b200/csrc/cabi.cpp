@@ -154,6 +154,13 @@ int fitre_set_precision(fitre_context *ctx, int precision) {
     return FITRE_OK;
 }
 
+int fitre_set_kfac_solver(fitre_context *ctx, int solver) {
+    if (!ctx || (solver != FITRE_KFAC_SOLVER_INVERSE && solver != FITRE_KFAC_SOLVER_CHOLESKY))
+        return FITRE_ERR_BAD_ARG;
+    ctx->kfac_solver = solver;
+    return FITRE_OK;
+}
+
 int fitre_set_tma(fitre_context *ctx, int on) {
     if (!ctx) return FITRE_ERR_BAD_ARG;
     ctx->use_tma = on != 0;

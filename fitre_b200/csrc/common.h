@@ -48,6 +48,7 @@ struct fitre_context {
     std::string err;
     int ref_softmax = 1;
     int precision = 0;          // FITRE_PRECISION_* (convolution products)
+    int kfac_solver = 0;        // FITRE_KFAC_SOLVER_* (what the A-factor slots hold)
     bool use_tma = true;        // TMA-fed convolution kernels where shape and alignment allow
     double *pinned = nullptr;   // 256 pinned host doubles (scalar read-back)
     double *dscal = nullptr;    // 4096 device doubles (scalar reductions)

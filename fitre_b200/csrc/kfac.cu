@@ -8,6 +8,7 @@
 #include <climits>
 #include <cmath>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -302,56 +303,94 @@ constexpr int NB = 64;
 
 // In place: A (nb x nb, lower, leading dim lda) <- its Cholesky factor L;
 // Linv (nb x nb, leading dim ldi, upper part zero) <- L^-1.  *fail is set to 1 + column on a pivot <= 0.
+// With Linv == nullptr the inverse is packed into the block itself: the strictly upper triangle
+// of A receives (L^-1)' (element (a, b), a < b, holds L^-1[b][a]; the diagonal of L^-1 is the
+// reciprocal of the diagonal of L), which is what trsm_small_kernel reads.
 __global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, int nb, double *Linv,
                                                          long ldi, int *fail, int col0) {
-    // lower triangle: L; strictly upper triangle: (L^-1)' off-diagonal; xd: diagonal of L^-1
+    // staging for the coalesced write-out: lower triangle L; strictly upper triangle (L^-1)'
+    // off-diagonal; xd: diagonal of L^-1
     __shared__ double L[NB][NB + 1];
     __shared__ double xd[NB];
-    __shared__ int bad;
-    const int tid = threadIdx.x;
-    if (tid == 0) bad = 0;
-    for (int e = tid; e < NB * NB; e += 256) {
-        const int r = e % NB, c = e / NB;
-        L[r][c] = (r < nb && c < nb && r >= c) ? A[(long)c * lda + r] : 0.0;
+    __shared__ double lcol[2][NB], wrow[2][NB], piv[2];
+    const int tid = threadIdx.x, ty = tid & 15, tx = tid >> 4;
+    // Right-looking elimination with the block in registers: thread (ty, tx) owns the cyclic 4 x 4
+    // sub-tile rows ty + 16 i, columns tx + 16 jj of the block (a) and of W, which starts as the
+    // identity and receives the same row operations, so that W ends as L^-1.  One barrier per
+    // column: the owners publish column j of a, row j of W and the pivot unscaled, everybody
+    // forms 1/sqrt(pivot) for itself.
+    double a[4][4], w[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int r = ty + 16 * i, c = tx + 16 * jj;
+            a[i][jj] = (r < nb && c < nb) ? (r >= c ? A[(long)c * lda + r] : 0.0) : (r == c ? 1.0 : 0.0);
+            w[i][jj] = r == c ? 1.0 : 0.0;
+        }
     }
-    __syncthreads();
-    for (int j = 0; j < nb; ++j) {
-        if (tid == 0) {
-            const double d = L[j][j];
-            if (!(d > 0.0)) {
-                bad = j + 1;
-                L[j][j] = 1.0;
-            } else {
-                L[j][j] = sqrt(d);
+    int bad = 0;
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+        const int jq = j >> 4, jr = j & 15, b = j & 1;
+        if (tx == jr) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) lcol[b][ty + 16 * i] = a[i][jq];
+            if (ty == jr) piv[b] = a[jq][jq];
+        }
+        if (ty == jr) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) wrow[b][tx + 16 * jj] = w[jq][jj];
+        }
+        __syncthreads();
+        const double p = piv[b];
+        double rinv = 1.0;
+        if (p > 0.0) rinv = rsqrt(p);
+        else if (!bad) bad = j + 1;
+        double lr[4], lc[4], wr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) lr[i] = lcol[b][ty + 16 * i] * rinv;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            lc[jj] = lcol[b][tx + 16 * jj] * rinv;
+            wr[jj] = wrow[b][tx + 16 * jj] * rinv;
+        }
+        if (tx == jr) {  // column j of L is final
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i][jq] = (ty + 16 * i == j) ? p * rinv : lr[i];
+        }
+        if (ty == jr) {  // row j of L^-1 is final
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) w[jq][jj] = wr[jj];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                if (tx + 16 * jj > j) a[i][jj] -= lr[i] * lc[jj];
+                if (ty + 16 * i > j) w[i][jj] -= lr[i] * wr[jj];
             }
         }
-        __syncthreads();
-        const double dj = L[j][j];
-        for (int r = j + 1 + tid; r < nb; r += 256) L[r][j] /= dj;
-        __syncthreads();
-        // trailing update of the lower triangle: L[r][c] -= L[r][j] * L[c][j], j < c <= r
-        const int rem = nb - j - 1;
-        for (int e = tid; e < rem * rem; e += 256) {
-            const int r = j + 1 + e % rem, c = j + 1 + e / rem;
-            if (r >= c) L[r][c] -= L[r][j] * L[c][j];
-        }
-        __syncthreads();
     }
-    // X = L^-1 by forward substitution, one column per thread; X[r][c] (r > c) lives at L[c][r]
-    if (tid < nb) {
-        const int c = tid;
-        xd[c] = 1.0 / L[c][c];
-        for (int r = c + 1; r < nb; ++r) {
-            double s = -L[r][c] * xd[c];
-            for (int k = c + 1; k < r; ++k) s -= L[r][k] * L[c][k];
-            L[c][r] = s / L[r][r];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int r = ty + 16 * i, c = tx + 16 * jj;
+            if (r > c) {
+                L[r][c] = a[i][jj];
+                L[c][r] = w[i][jj];
+            } else if (r == c) {
+                L[r][r] = a[i][jj];
+                xd[r] = w[i][jj];
+            }
         }
     }
     __syncthreads();
     for (int e = tid; e < NB * NB; e += 256) {
         const int r = e % NB, c = e / NB;
-        if (r < nb && c < nb && r >= c) A[(long)c * lda + r] = L[r][c];
-        if (r < nb && c < nb) Linv[(long)c * ldi + r] = (r == c) ? xd[c] : (r > c ? L[c][r] : 0.0);
+        if (r < nb && c < nb && (r >= c || !Linv)) A[(long)c * lda + r] = L[r][c];
+        if (Linv && r < nb && c < nb) Linv[(long)c * ldi + r] = (r == c) ? xd[c] : (r > c ? L[c][r] : 0.0);
     }
     if (tid == 0 && bad) atomicCAS(fail, 0, col0 + bad);
 }
@@ -412,6 +451,183 @@ void factor_invert(fitre_context *ctx, double *A, double *Y, long ld, int n, int
     double *T = next;  // free again after the recursion: L21 * Y11
     dgemm_structured(ctx, false, false, n2, n1, n1, 1.0, L21, n2, Y, (int)ld, 0.0, T, n2, GEMM_K_GE_COL);
     dgemm_structured(ctx, false, false, n2, n1, n2, -1.0, Y22, (int)ld, T, n2, 0.0, Y21, (int)ld, GEMM_K_LE_ROW);
+}
+
+
+// ---- Cholesky without the explicit inverse --------------------------------------------------
+// Triangular solves from the right for a chunk of TR_ROWS rows of B (rows are independent):
+//   trans != 0:  X L' = B   (block columns ascending:  X_j = (B_j - sum_{k<j} X_k L_jk') L_jj^-T)
+//   trans == 0:  X L  = B   (block columns descending: X_j = (B_j - sum_{k>j} X_k L_kj ) L_jj^-1)
+// L is t x t (t <= TR_MAX), lower, with the inverse of every NB x NB diagonal block packed in that
+// block's upper triangle by chol_block_kernel.  B is overwritten by X.
+constexpr int TR_ROWS = 16, TR_MAX = 256;
+constexpr int TR_SMEM = (TR_MAX * TR_ROWS + 2 * NB * (NB + 1)) * (int)sizeof(double);
+
+// The NB x NB tile of step (s, s2) of the sweep, 16 elements per thread, still in registers: s2 < s
+// is the coupling tile of block column j with an already solved block k, s2 == s the diagonal
+// block (lower = L_jj, strictly upper = packed inverse; identity outside a ragged block).
+__device__ __forceinline__ void trsm_tile_load(double (&reg)[16], const double *L, long ldl, int t, int nblk,
+                                               int trans, int s, int s2, int tid) {
+    const int j = trans ? s : nblk - 1 - s;
+    const int jb = min(NB, t - j * NB);
+    if (s2 == s) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int e = tid + u * 256, rr = e % NB, cc = e / NB;
+            reg[u] = (rr < jb && cc < jb) ? L[(long)(j * NB + cc) * ldl + j * NB + rr] : (rr == cc ? 1.0 : 0.0);
+        }
+        return;
+    }
+    const int k = trans ? s2 : nblk - 1 - s2;
+    const int kb = min(NB, t - k * NB);
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+        const int e = tid + u * 256, lo = e % NB, hi = e / NB;  // global reads run along a column
+        if (trans) reg[u] = (lo < jb && hi < kb) ? L[(long)(k * NB + hi) * ldl + j * NB + lo] : 0.0;
+        else reg[u] = (lo < kb && hi < jb) ? L[(long)(j * NB + hi) * ldl + k * NB + lo] : 0.0;
+    }
+}
+
+__global__ void __launch_bounds__(256) trsm_small_kernel(double *B, long ldb, int r, const double *L, long ldl,
+                                                         int t, int trans) {
+    extern __shared__ __align__(16) double tr_sm[];
+    double (*xs)[TR_ROWS] = reinterpret_cast<double (*)[TR_ROWS]>(tr_sm);
+    typedef double Tile[NB][NB + 1];
+    Tile *tiles = reinterpret_cast<Tile *>(tr_sm + TR_MAX * TR_ROWS);
+    const int tid = threadIdx.x;
+    const long row0 = (long)blockIdx.x * TR_ROWS;
+    const int nrows = (int)min((long)TR_ROWS, r - row0);
+    const int nblk = (t + NB - 1) / NB;
+    double reg[16];
+    trsm_tile_load(reg, L, ldl, t, nblk, trans, 0, 0, tid);
+    for (int e = tid; e < TR_MAX * TR_ROWS; e += 256) {
+        const int i = e % TR_ROWS, c = e / TR_ROWS;
+        xs[c][i] = (i < nrows && c < t) ? B[(long)c * ldb + row0 + i] : 0.0;
+    }
+    __syncthreads();
+    const int c = tid % NB, r4 = (tid / NB) * 4;
+    int buf = 0;
+    for (int s = 0; s < nblk; ++s) {
+        const int j = trans ? s : nblk - 1 - s;
+        const int jb = min(NB, t - j * NB);
+        double acc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = xs[j * NB + c][r4 + i];
+        for (int s2 = 0; s2 <= s; ++s2) {
+            Tile &tl = tiles[buf];
+            // tl[q][cc]: coupling tiles hold L[j*NB+cc][k*NB+q] (trans) or L[k*NB+q][j*NB+cc];
+            // the diagonal tile is stored as it lies, tl[row][col]
+            const bool flip = trans && s2 < s;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int e = tid + u * 256, lo = e % NB, hi = e / NB;
+                if (flip) tl[hi][lo] = reg[u];
+                else tl[lo][hi] = reg[u];
+            }
+            __syncthreads();
+            // the next tile travels while this one is used
+            if (s2 < s) trsm_tile_load(reg, L, ldl, t, nblk, trans, s, s2 + 1, tid);
+            else if (s + 1 < nblk) trsm_tile_load(reg, L, ldl, t, nblk, trans, s + 1, 0, tid);
+            if (s2 < s) {
+                const int k = trans ? s2 : nblk - 1 - s2;
+#pragma unroll 8
+                for (int q = 0; q < NB; ++q) {
+                    const double l = tl[q][c];
+                    const double2 x01 = *reinterpret_cast<const double2 *>(&xs[k * NB + q][r4]);
+                    const double2 x23 = *reinterpret_cast<const double2 *>(&xs[k * NB + q][r4 + 2]);
+                    acc[0] -= x01.x * l;
+                    acc[1] -= x01.y * l;
+                    acc[2] -= x23.x * l;
+                    acc[3] -= x23.y * l;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) xs[j * NB + c][r4 + i] = acc[i];
+                __syncthreads();
+                double out[4];
+                const double dinv = 1.0 / tl[c][c];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) out[i] = acc[i] * dinv;
+                if (trans) {
+                    for (int k = 0; k < c; ++k) {
+                        const double w = tl[k][c];  // L^-1[c][k]
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) out[i] += xs[j * NB + k][r4 + i] * w;
+                    }
+                } else {
+                    for (int k = c + 1; k < jb; ++k) {
+                        const double w = tl[c][k];  // L^-1[k][c]
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) out[i] += xs[j * NB + k][r4 + i] * w;
+                    }
+                }
+                __syncthreads();
+#pragma unroll
+                for (int i = 0; i < 4; ++i) xs[j * NB + c][r4 + i] = out[i];
+            }
+            buf ^= 1;
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < t * TR_ROWS; e += 256) {
+        const int i = e % TR_ROWS, cc = e / TR_ROWS;
+        if (i < nrows) B[(long)cc * ldb + row0 + i] = xs[cc][i];
+    }
+}
+
+// B (r x t, leading dim ldb) <- B L^-T (trans) or B L^-1, L as left by chol_factor.  Above TR_MAX
+// the triangle is halved and the coupling term is one GEMM; splits fall on multiples of NB so
+// that the packed diagonal blocks line up.
+void trsm_right(fitre_context *ctx, double *B, long ldb, int r, const double *L, long ldl, int t, bool trans) {
+    if (t <= TR_MAX) {
+        static std::once_flag once;
+        std::call_once(once, [] {
+            cudaFuncSetAttribute(trsm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM);
+        });
+        trsm_small_kernel<<<(r + TR_ROWS - 1) / TR_ROWS, 256, TR_SMEM, ctx->stream>>>(B, ldb, r, L, ldl, t,
+                                                                                      trans ? 1 : 0);
+        check_launch(ctx, "trsm_small_kernel");
+        return;
+    }
+    const int t1 = ((t / 2 + NB - 1) / NB) * NB, t2 = t - t1;
+    const double *L21 = L + t1, *L22 = L + (long)t1 * ldl + t1;
+    double *B2 = B + (long)t1 * ldb;
+    if (trans) {
+        trsm_right(ctx, B, ldb, r, L, ldl, t1, true);
+        dgemm(ctx, false, true, r, t2, t1, -1.0, B, (int)ldb, L21, (int)ldl, 1.0, B2, (int)ldb);
+        trsm_right(ctx, B2, ldb, r, L22, ldl, t2, true);
+    } else {
+        trsm_right(ctx, B2, ldb, r, L22, ldl, t2, false);
+        dgemm(ctx, false, false, r, t1, t2, -1.0, B2, (int)ldb, L21, (int)ldl, 1.0, B, (int)ldb);
+        trsm_right(ctx, B, ldb, r, L, ldl, t1, false);
+    }
+}
+
+// In place: the lower triangle of A (n x n, leading dim ld, symmetric positive definite) <- L with
+// A = L L'; the upper triangles of the NB x NB diagonal blocks <- their packed inverses.  The rest
+// of the upper triangle keeps whatever it held.  No scratch: the panel solve and the trailing
+// update work inside A.
+void chol_factor(fitre_context *ctx, double *A, long ld, int n, int col0, int *fail) {
+    if (n <= NB) {
+        chol_block_kernel<<<1, 256, 0, ctx->stream>>>(A, ld, n, nullptr, 0, fail, col0);
+        check_launch(ctx, "chol_block_kernel");
+        return;
+    }
+    const int n1 = ((n / 2 + NB - 1) / NB) * NB, n2 = n - n1;
+    double *A21 = A + n1, *A22 = A + (long)n1 * ld + n1;
+    chol_factor(ctx, A, ld, n1, col0, fail);
+    trsm_right(ctx, A21, ld, n2, A, ld, n1, true);  // L21 = A21 L11^-T
+    dgemm_structured(ctx, false, true, n2, n2, n1, -1.0, A21, (int)ld, A21, (int)ld, 1.0, A22, (int)ld,
+                     GEMM_LOWER_C);
+    chol_factor(ctx, A22, ld, n2, col0 + n1, fail);
+}
+
+// factor <- Cholesky factor of (matrix + damp I), packed as chol_factor leaves it
+void factor_spd(fitre_context *ctx, const double *matrix, double *factor, int n, double damp, int *fail) {
+    vec_copy(ctx, (long)n * n, matrix, factor);
+    add_diagonal_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(factor, n, damp);
+    check_launch(ctx, "add_diagonal_kernel");
+    chol_factor(ctx, factor, n, n, 0, fail);
 }
 
 // inverse <- (matrix + damp I)^-1 on ctx->stream, no host synchronisation; a pivot <= 0 is
@@ -478,9 +694,10 @@ struct InvJob {
     double *dst;
     int n;
     double cost;
+    bool factor_only;  // Cholesky factor instead of the inverse
 };
 std::vector<InvJob> inverse_jobs(const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const double *A,
-                                 double *Ainv, const double *G, double *Ginv) {
+                                 double *Ainv, const double *G, double *Ginv, bool chol) {
     std::vector<InvJob> jobs;
     for (int l = 0; l < m->cLayers + m->lLayers; ++l) {
         int a, g;
@@ -492,11 +709,20 @@ std::vector<InvJob> inverse_jobs(const CNN_MODEL *m, const FITRE_KFAC_INFO *info
             a = m->fcLayer[l - m->cLayers].in + (m->bias ? 1 : 0);
             g = m->fcLayer[l - m->cLayers].out;
         }
-        jobs.push_back({A + info->OmegaZOffsets[l], Ainv + info->OmegaZOffsets[l], a, (double)a * a * a});
-        jobs.push_back({G + info->LambdaGOffsets[l], Ginv + info->LambdaGOffsets[l], g, (double)g * g * g});
+        jobs.push_back({A + info->OmegaZOffsets[l], Ainv + info->OmegaZOffsets[l], a,
+                        (double)a * a * a / (chol ? 3.0 : 1.0), chol});
+        jobs.push_back({G + info->LambdaGOffsets[l], Ginv + info->LambdaGOffsets[l], g, (double)g * g * g, false});
     }
     std::stable_sort(jobs.begin(), jobs.end(), [](const InvJob &x, const InvJob &y) { return x.cost > y.cost; });
     return jobs;
+}
+void ensure_side_streams(fitre_context *ctx) {
+    if (ctx->inv_streams[0]) return;
+    for (int s = 0; s < kInvStreams; ++s)
+        FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->inv_streams[s], cudaStreamNonBlocking));
+    FITRE_CUDA(cudaEventCreateWithFlags(&ctx->inv_fork, cudaEventDisableTiming));
+    for (int s = 0; s < kInvStreams; ++s)
+        FITRE_CUDA(cudaEventCreateWithFlags(&ctx->inv_join[s], cudaEventDisableTiming));
 }
 int max_block(const CNN_MODEL *m) {
     int mx = 1;
@@ -522,7 +748,8 @@ extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m,
         FITRE_REQUIRE(m && info && omegaZ && omegaZInv && lambdaG && lambdaGInv && devPtr, FITRE_ERR_BAD_ARG,
                       "NULL pointer argument");
         const double damp = info->regLambda + info->dampGamma;
-        std::vector<InvJob> jobs = inverse_jobs(m, info, omegaZ, omegaZInv, lambdaG, lambdaGInv);
+        std::vector<InvJob> jobs = inverse_jobs(m, info, omegaZ, omegaZInv, lambdaG, lambdaGInv,
+                                                ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY);
         const int W = ctx->world;
         std::vector<double> load(W, 0.0);
         std::vector<InvJob> mine;
@@ -538,13 +765,7 @@ extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m,
             vec_fill(ctx, info->LambdaGSize, 0.0, lambdaGInv);
         }
         // fork: the side streams start after everything queued on the context's stream
-        if (!ctx->inv_streams[0]) {
-            for (int s = 0; s < kInvStreams; ++s)
-                FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->inv_streams[s], cudaStreamNonBlocking));
-            FITRE_CUDA(cudaEventCreateWithFlags(&ctx->inv_fork, cudaEventDisableTiming));
-            for (int s = 0; s < kInvStreams; ++s)
-                FITRE_CUDA(cudaEventCreateWithFlags(&ctx->inv_join[s], cudaEventDisableTiming));
-        }
+        ensure_side_streams(ctx);
         cudaStream_t main_stream = ctx->stream;
         FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
         const long per = align32(fitre_kfac_inverse_mem_required(max_block(m)));
@@ -555,7 +776,8 @@ extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m,
                 const int s = (int)(std::min_element(sload.begin(), sload.end()) - sload.begin());
                 sload[s] += j.cost;
                 ctx->stream = ctx->inv_streams[s];
-                invert_spd(ctx, j.src, j.dst, j.n, damp, devPtr + (long)s * per, fail);
+                if (j.factor_only) factor_spd(ctx, j.src, j.dst, j.n, damp, fail);
+                else invert_spd(ctx, j.src, j.dst, j.n, damp, devPtr + (long)s * per, fail);
             }
         } catch (...) {
             ctx->stream = main_stream;
@@ -579,8 +801,8 @@ extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m,
     }
 }
 
-extern "C" long fitre_kfac_natural_gradient_mem_required(const CNN_MODEL *m) {
-    if (!m) return -1;
+namespace {
+long natural_gradient_layer_scratch(const CNN_MODEL *m) {
     long need = 0;
     for (int l = 0; l < m->cLayers; ++l) {
         const CONV_LAYER &c = m->convLayer[l];
@@ -591,8 +813,15 @@ extern "C" long fitre_kfac_natural_gradient_mem_required(const CNN_MODEL *m) {
         need = std::max(need, align32((long)m->fcLayer[l].out * (m->fcLayer[l].in + 1)));
     return need;
 }
+}  // namespace
 
-// nGradient = G^-1 [W|b] A^-1 per layer, in the flat gradient layout.
+extern "C" long fitre_kfac_natural_gradient_mem_required(const CNN_MODEL *m) {
+    if (!m) return -1;
+    return kInvStreams * natural_gradient_layer_scratch(m);
+}
+
+// nGradient = G^-1 [W|b] A^-1 per layer, in the flat gradient layout.  The layers are independent
+// and their products are small next to the GPU, so they are spread over the side streams.
 extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODEL *m,
                                               const FITRE_KFAC_INFO *info, const real *omegaZInv,
                                               const real *lambdaGInv, const real *gradient,
@@ -603,32 +832,80 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
         FITRE_REQUIRE(m && info && omegaZInv && lambdaGInv && gradient && nGradient && devPtr,
                       FITRE_ERR_BAD_ARG, "NULL pointer argument");
         const int hasb = m->bias ? 1 : 0;
-        for (int c = 0; c < m->cLayers; ++c) {
-            const CONV_LAYER &L = m->convLayer[c];
-            const int K = L.inChannels * L.kSize * L.kSize, Kb = K + hasb, Co = L.outChannels;
-            const double *Ai = omegaZInv + info->OmegaZOffsets[c];
-            const double *Gi = lambdaGInv + info->LambdaGOffsets[c];
-            const long sz = align32((long)Kb * Co);
-            double *wb = devPtr, *t1 = wb + sz, *t2 = t1 + sz;
-            pack_wb_kernel<<<blocks_for((long)Kb * Co), 256, 0, ctx->stream>>>(
-                gradient + m->wOffsets[c], hasb ? gradient + m->bOffsets[c] : nullptr, wb, K, Kb, Co);
-            check_launch(ctx, "pack_wb_kernel");
-            dgemm(ctx, false, true, Co, Kb, Co, 1.0, Gi, Co, wb, Kb, 0.0, t1, Co);   // G^-1 wb'
-            dgemm(ctx, false, false, Co, Kb, Kb, 1.0, t1, Co, Ai, Kb, 0.0, t2, Co);  // ... A^-1
-            unpack_ng_kernel<<<blocks_for((long)Kb * Co), 256, 0, ctx->stream>>>(
-                t2, nGradient + m->wOffsets[c], hasb ? nGradient + m->bOffsets[c] : nullptr, K, Kb, Co);
-            check_launch(ctx, "unpack_ng_kernel");
+        const bool chol = ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY;
+        const long per = natural_gradient_layer_scratch(m);
+        ensure_side_streams(ctx);
+        cudaStream_t main_stream = ctx->stream;
+        FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
+        for (int s = 0; s < kInvStreams; ++s) FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
+        std::vector<double> sload(kInvStreams, 0.0);
+        auto pick_stream = [&](double cost) {
+            const int s = (int)(std::min_element(sload.begin(), sload.end()) - sload.begin());
+            sload[s] += cost;
+            ctx->stream = ctx->inv_streams[s];
+            return devPtr + (long)s * per;
+        };
+        try {
+            // largest layers first, so that the long chains start early
+            std::vector<int> order(m->cLayers + m->lLayers);
+            std::vector<double> cost(order.size());
+            for (int l = 0; l < (int)order.size(); ++l) {
+                order[l] = l;
+                const double kb = l < m->cLayers ? (double)m->convLayer[l].inChannels * m->convLayer[l].kSize *
+                                                       m->convLayer[l].kSize
+                                                 : (double)m->fcLayer[l - m->cLayers].in;
+                const double co = l < m->cLayers ? m->convLayer[l].outChannels : m->fcLayer[l - m->cLayers].out;
+                cost[l] = co * kb * (kb + co);
+            }
+            std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return cost[x] > cost[y]; });
+            for (int li : order) {
+                double *work = pick_stream(cost[li]);
+                const double *Ai = omegaZInv + info->OmegaZOffsets[li];
+                const double *Gi = lambdaGInv + info->LambdaGOffsets[li];
+                if (li < m->cLayers) {
+                    const CONV_LAYER &L = m->convLayer[li];
+                    const int K = L.inChannels * L.kSize * L.kSize, Kb = K + hasb, Co = L.outChannels;
+                    const long sz = align32((long)Kb * Co);
+                    double *wb = work, *t1 = wb + sz, *t2 = t1 + sz;
+                    pack_wb_kernel<<<blocks_for((long)Kb * Co), 256, 0, ctx->stream>>>(
+                        gradient + m->wOffsets[li], hasb ? gradient + m->bOffsets[li] : nullptr, wb, K, Kb, Co);
+                    check_launch(ctx, "pack_wb_kernel");
+                    dgemm(ctx, false, true, Co, Kb, Co, 1.0, Gi, Co, wb, Kb, 0.0, t1, Co);  // G^-1 wb'
+                    if (chol) {  // ... A^-1 = L^-T L^-1 by two solves in place
+                        trsm_right(ctx, t1, Co, Co, Ai, Kb, Kb, true);
+                        trsm_right(ctx, t1, Co, Co, Ai, Kb, Kb, false);
+                        t2 = t1;
+                    } else {
+                        dgemm(ctx, false, false, Co, Kb, Kb, 1.0, t1, Co, Ai, Kb, 0.0, t2, Co);  // ... A^-1
+                    }
+                    unpack_ng_kernel<<<blocks_for((long)Kb * Co), 256, 0, ctx->stream>>>(
+                        t2, nGradient + m->wOffsets[li], hasb ? nGradient + m->bOffsets[li] : nullptr, K, Kb, Co);
+                    check_launch(ctx, "unpack_ng_kernel");
+                } else {
+                    const FC_LAYER &F = m->fcLayer[li - m->cLayers];
+                    const int in = F.in + hasb;
+                    // [W | b] is contiguous in the flat layout: out x (in + bias), column-major
+                    double *ng = nGradient + m->wOffsets[li];
+                    if (chol) {
+                        dgemm(ctx, false, false, F.out, in, F.out, 1.0, Gi, F.out, gradient + m->wOffsets[li],
+                              F.out, 0.0, ng, F.out);
+                        trsm_right(ctx, ng, F.out, F.out, Ai, in, in, true);
+                        trsm_right(ctx, ng, F.out, F.out, Ai, in, in, false);
+                    } else {
+                        dgemm(ctx, false, false, F.out, in, F.out, 1.0, Gi, F.out, gradient + m->wOffsets[li],
+                              F.out, 0.0, work, F.out);
+                        dgemm(ctx, false, false, F.out, in, in, 1.0, work, F.out, Ai, in, 0.0, ng, F.out);
+                    }
+                }
+            }
+        } catch (...) {
+            ctx->stream = main_stream;
+            throw;
         }
-        for (int l = 0; l < m->lLayers; ++l) {
-            const FC_LAYER &F = m->fcLayer[l];
-            const int li = m->cLayers + l, in = F.in + hasb;
-            const double *Ai = omegaZInv + info->OmegaZOffsets[li];
-            const double *Gi = lambdaGInv + info->LambdaGOffsets[li];
-            // [W | b] is contiguous in the flat layout: out x (in + bias), column-major
-            dgemm(ctx, false, false, F.out, in, F.out, 1.0, Gi, F.out, gradient + m->wOffsets[li], F.out,
-                  0.0, devPtr, F.out);
-            dgemm(ctx, false, false, F.out, in, in, 1.0, devPtr, F.out, Ai, in, 0.0,
-                  nGradient + m->wOffsets[li], F.out);
+        ctx->stream = main_stream;
+        for (int s = 0; s < kInvStreams; ++s) {
+            FITRE_CUDA(cudaEventRecord(ctx->inv_join[s], ctx->inv_streams[s]));
+            FITRE_CUDA(cudaStreamWaitEvent(main_stream, ctx->inv_join[s], 0));
         }
         return FITRE_OK;
     } catch (const Error &e) {

@@ -226,6 +226,22 @@ int fitre_set_reference_softmax(fitre_context *ctx, int on);
 enum { FITRE_PRECISION_FP64 = 0, FITRE_PRECISION_TF32 = 1, FITRE_PRECISION_TF32X3 = 2, FITRE_PRECISION_FP64_I8 = 3 };
 int fitre_set_precision(fitre_context *ctx, int precision);
 
+/* How the KFAC A-factor blocks are applied (the G blocks, at most a few hundred rows, are always
+ * inverted):
+ *   FITRE_KFAC_SOLVER_INVERSE (default): fitre_kfac_invert_factors writes the explicit inverses
+ *     (F + (lambda+gamma) I)^-1, as computeMatrixInverseCusolver does
+ *     (solvers/kfac_inverses.cu:133-186), and fitre_compute_natural_gradient multiplies by them.
+ *   FITRE_KFAC_SOLVER_CHOLESKY: fitre_kfac_invert_factors writes into the same slots the Cholesky
+ *     factor L of each damped A block (lower triangle; the upper triangles of the 64 x 64
+ *     diagonal blocks hold those blocks' inverses) and fitre_compute_natural_gradient applies
+ *     A^-1 = L^-T L^-1 to G^-1 [W|b] by two triangular solves.  One third of the factorisation
+ *     work and no triangular inversion or L^-T L^-1 product; the natural gradient agrees with the
+ *     explicit-inverse form to rounding (about cond(A) * 1e-16 relative).  The slots are then
+ *     only meaningful to these two calls.  fitre_subsampled_trust_region_kfac follows the
+ *     setting.  No counterpart in the reference. */
+enum { FITRE_KFAC_SOLVER_INVERSE = 0, FITRE_KFAC_SOLVER_CHOLESKY = 1 };
+int fitre_set_kfac_solver(fitre_context *ctx, int solver);
+
 /* 1 (default) = use the TMA-fed convolution kernels wherever shape and alignment allow;
  * 0 = always use the gather kernels (same results; kept for comparison and as the path
  * for odd shapes).  No counterpart in the reference. */

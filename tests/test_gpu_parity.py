@@ -338,6 +338,67 @@ def test_cuda_kfac_inverse_and_natural_gradient_vs_oracle():
         ng_o = np.zeros(model.pSize)
         O.lib().ora_natural_gradient(C.byref(model), C.byref(info), Ai_o, Gi_o, run.gradient, ng_o)
         assert G.rel(ng.cpu().numpy(), ng_o) < 1e-8
+        # Cholesky-solve form: factors instead of inverses in the A slots, same natural gradient
+        run.c.set_kfac_solver(1)
+        try:
+            Ac, Gi3 = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+            api.invertFactors(run.c, model, info, A, Ac, Gm, Gi3, scr2)
+            assert np.array_equal(Gi3.cpu().numpy(), Gi.cpu().numpy())
+            ng_c = G.dev(np.zeros(model.pSize))
+            api.computeNaturalGradient(run.c, model, info, Ac, Gi3, run.ws.gradient, ng_c, scratch)
+        finally:
+            run.c.set_kfac_solver(0)
+        assert G.rel(ng_c.cpu().numpy(), ng_o) < 1e-8
+
+
+def test_cuda_cholesky_solve_natural_gradient_large_blocks():
+    """The Cholesky-solve form on VGG-11's factor sizes (27 ... 4608: every level of the blocked
+    factorisation and of the recursive triangular solves).  Checked three ways: L L' reproduces the
+    damped factor; the natural gradient equals LAPACK's solves on the host (1e-9); and it equals
+    the explicit-inverse form of the same library (1e-9)."""
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    L = _lib.load()
+    n = 2
+    model = nets.vgg11(n)
+    O.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=77)
+    run = G.GpuRun(model, x, y, w, ncls)
+    info = api.computeKFACStorageIndices(model)
+    info.regLambda, info.dampGamma = 1e-3, 1e-2
+    damp = info.regLambda + info.dampGamma
+    scratch = G.dev(np.zeros(max(L.fitre_kfac_mem_required(C.byref(model)),
+                                 L.fitre_kfac_invert_factors_mem_required(C.byref(model)),
+                                 L.fitre_kfac_natural_gradient_mem_required(C.byref(model)))))
+    A, Gm = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+    api.computeOmegaZ(run.c, model, run.data, run.ws.z, n, A, info, scratch)
+    api.computeLambdaDelta(run.c, model, run.ws.dx, n, Gm, info, scratch)
+    Ai, Gi = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+    api.invertFactors(run.c, model, info, A, Ai, Gm, Gi, scratch)
+    ng_inv = G.dev(np.zeros(model.pSize))
+    api.computeNaturalGradient(run.c, model, info, Ai, Gi, run.ws.gradient, ng_inv, scratch)
+    run.c.set_kfac_solver(1)
+    try:
+        Ac, Gi2 = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+        api.invertFactors(run.c, model, info, A, Ac, Gm, Gi2, scratch)
+        ng = G.dev(np.zeros(model.pSize))
+        api.computeNaturalGradient(run.c, model, info, Ac, Gi2, run.ws.gradient, ng, scratch)
+    finally:
+        run.c.set_kfac_solver(0)
+    g_h, ng_h = run.ws.gradient.cpu().numpy(), ng.cpu().numpy()
+    for l in range(model.cLayers):
+        c = model.convLayer[l]
+        K, co = c.inChannels * c.kSize ** 2, c.outChannels
+        a0, g0 = info.OmegaZOffsets[l], info.LambdaGOffsets[l]
+        Al = A[a0:a0 + K * K].cpu().numpy().reshape(K, K) + damp * np.eye(K)
+        Lc = np.tril(Ac[a0:a0 + K * K].cpu().numpy().reshape(K, K).T)  # column-major slot
+        assert np.abs(Lc @ Lc.T - Al).max() <= 1e-12 * np.abs(Al).max() * K, l
+        Gl = Gm[g0:g0 + co * co].cpu().numpy().reshape(co, co) + damp * np.eye(co)
+        Wg = g_h[model.wOffsets[l]:model.wOffsets[l] + K * co].reshape(co, K)  # row o = column o of K x Cout
+        ref = np.linalg.solve(Gl, np.linalg.solve(Al, Wg.T).T)
+        got = ng_h[model.wOffsets[l]:model.wOffsets[l] + K * co].reshape(co, K)
+        assert G.rel(got, ref) < 1e-9, l
+    assert G.rel(ng_h, ng_inv.cpu().numpy()) < 1e-9
 
 
 def test_cuda_matrix_inverse_blocked_sizes_and_failure():

@@ -143,8 +143,9 @@ def test_cuda_generalization_errors_vs_oracle():
     assert np.array_equal(ws.z.cpu().numpy()[bo:bo + 2 * cl.outChannels], zo[bo:bo + 2 * cl.outChannels])
 
 
-@pytest.mark.parametrize("check_grad,enable_da,inverse_freq", [(1, 1, 1), (0, 0, 1), (1, 1, 3)])
-def test_cuda_trust_region_loop_vs_oracle(check_grad, enable_da, inverse_freq):
+@pytest.mark.parametrize("check_grad,enable_da,inverse_freq,solver",
+                         [(1, 1, 1, 0), (0, 0, 1, 0), (1, 1, 3, 0), (1, 1, 1, 1), (1, 0, 3, 1)])
+def test_cuda_trust_region_loop_vs_oracle(check_grad, enable_da, inverse_freq, solver):
     import torch
     import gpu_util as G
     from fitre_b200 import api, _lib
@@ -161,8 +162,12 @@ def test_cuda_trust_region_loop_vs_oracle(check_grad, enable_da, inverse_freq):
     data, W = full_dataset(G, api, model, trainX, trainY, testX, testY, w, model.batchSize)
     need = _lib.load().fitre_trust_region_kfac_mem_required(C.byref(model), C.byref(data), C.byref(info_g))
     scr = api.make_scratch(torch.zeros(need, dtype=torch.float64, device="cuda"))
-    steps_g, epochs_g = api.subsampledTrustRegionKFAC(c, model, data, info_g, tr_g, scr, seed=7,
-                                                      enableDA=enable_da, stepsCap=64)
+    c.set_kfac_solver(solver)  # 1: Cholesky factors + triangular solves instead of explicit inverses
+    try:
+        steps_g, epochs_g = api.subsampledTrustRegionKFAC(c, model, data, info_g, tr_g, scr, seed=7,
+                                                          enableDA=enable_da, stepsCap=64)
+    finally:
+        c.set_kfac_solver(0)
     assert len(steps_g) == len(steps_o) == 12 and tr_g.curIteration == tr_o.curIteration
     close = lambda a, b, t=1e-7: abs(a - b) <= t * max(abs(b), 1e-12)
     for sg, so in zip(steps_g, steps_o):
