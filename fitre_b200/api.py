@@ -82,6 +82,10 @@ class Context:
         the same slots, applied by two triangular solves in the natural gradient."""
         self.check(self.lib.fitre_set_kfac_solver(self.h, int(solver)))
 
+    def set_graphs(self, on):
+        """CUDA-graph replay of the factor-inverse and natural-gradient launch sequences (default on)."""
+        self.check(self.lib.fitre_set_graphs(self.h, int(bool(on))))
+
     def set_tma(self, on):
         self.check(self.lib.fitre_set_tma(self.h, int(bool(on))))
 

@@ -116,11 +116,14 @@ int fitre_context_destroy(fitre_context *ctx) {
     if (ctx->host_pinned) cudaFreeHost(ctx->host_pinned);
     if (ctx->staging_buf) cudaFree(ctx->staging_buf);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
-    for (int s = 0; s < 4; ++s) {
+    for (int s = 0; s < 8; ++s) {
         if (ctx->inv_streams[s]) cudaStreamDestroy(ctx->inv_streams[s]);
         if (ctx->inv_join[s]) cudaEventDestroy(ctx->inv_join[s]);
     }
     if (ctx->inv_fork) cudaEventDestroy(ctx->inv_fork);
+    if (ctx->graph_invert.exec) cudaGraphExecDestroy(ctx->graph_invert.exec);
+    if (ctx->graph_natgrad.exec) cudaGraphExecDestroy(ctx->graph_natgrad.exec);
+    if (ctx->graph_stream) cudaStreamDestroy(ctx->graph_stream);
     if (ctx->ev_up) cudaEventDestroy(ctx->ev_up);
     if (ctx->ev_w2) cudaEventDestroy(ctx->ev_w2);
     for (int i = 0; i < 24; ++i)
@@ -158,6 +161,12 @@ int fitre_set_kfac_solver(fitre_context *ctx, int solver) {
     if (!ctx || (solver != FITRE_KFAC_SOLVER_INVERSE && solver != FITRE_KFAC_SOLVER_CHOLESKY))
         return FITRE_ERR_BAD_ARG;
     ctx->kfac_solver = solver;
+    return FITRE_OK;
+}
+
+int fitre_set_graphs(fitre_context *ctx, int on) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    ctx->use_graphs = on ? 1 : 0;
     return FITRE_OK;
 }
 

@@ -70,8 +70,19 @@ struct fitre_context {
     long hv_sent_from = 0;
     double *staging_buf = nullptr;        // staging of the opt-in tensor-core modes (operand copies, digit
     long staging_cap = 0;                 // planes, split slabs), owned by the context, grown on demand
-    cudaStream_t inv_streams[4] = {};     // side streams of the batched factor inversion
-    cudaEvent_t inv_fork = nullptr, inv_join[4] = {};
+    cudaStream_t inv_streams[8] = {};     // side streams of the batched factor inversion
+    cudaEvent_t inv_fork = nullptr, inv_join[8] = {};
+    // The launch sequences of the factor inverses and of the natural gradient are fixed by the
+    // model and the buffers; each is captured once into a CUDA graph and replayed while its key
+    // (pointers, sizes, damping, solver) stays the same.
+    struct CapturedGraph {
+        std::vector<long long> key;
+        cudaGraphExec_t exec = nullptr;
+        long long launches = 0;
+    };
+    CapturedGraph graph_invert, graph_natgrad;
+    cudaStream_t graph_stream = nullptr;  // origin stream of the captures
+    int use_graphs = 1;
     // optional per-kernel timing (CUDA events on the launch stream), see fitre_profile_*
     bool prof_on = false;
     struct ProfRec { cudaEvent_t beg, end; int kind; double flops; };
@@ -156,6 +167,7 @@ long conv_patch_syrk_scratch(int N, int Cin, int H, int W, int k, int pad, bool 
 void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int Cin, int H, int W,
                      int k, int pad, bool bias, double alpha, double patch_scale, double *partials);
 void gemm_init_attributes();
+void kfac_init_attributes();
 // conv_tma.cu
 void conv_tma_init_attributes();
 long conv_fprop_tma_scratch(int N, int Cin, int H, int W, int k, int pad, int Cout);

@@ -1023,6 +1023,7 @@ void gemm_init_attributes() {
     conv_tma_init_attributes();
     conv_tf32_init_attributes();
     conv_i8_init_attributes();
+    kfac_init_attributes();
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));

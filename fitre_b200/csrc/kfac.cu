@@ -8,7 +8,6 @@
 #include <climits>
 #include <cmath>
 #include <cstring>
-#include <mutex>
 #include <string>
 #include <vector>
 
@@ -580,10 +579,6 @@ __global__ void __launch_bounds__(256) trsm_small_kernel(double *B, long ldb, in
 // that the packed diagonal blocks line up.
 void trsm_right(fitre_context *ctx, double *B, long ldb, int r, const double *L, long ldl, int t, bool trans) {
     if (t <= TR_MAX) {
-        static std::once_flag once;
-        std::call_once(once, [] {
-            cudaFuncSetAttribute(trsm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM);
-        });
         trsm_small_kernel<<<(r + TR_ROWS - 1) / TR_ROWS, 256, TR_SMEM, ctx->stream>>>(B, ldb, r, L, ldl, t,
                                                                                       trans ? 1 : 0);
         check_launch(ctx, "trsm_small_kernel");
@@ -657,6 +652,12 @@ void check_fail_word(fitre_context *ctx, int *fail) {
 }
 }  // namespace
 
+namespace fitre {
+void kfac_init_attributes() {
+    FITRE_CUDA(cudaFuncSetAttribute(trsm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM));
+}
+}  // namespace fitre
+
 extern "C" long fitre_kfac_inverse_mem_required(int n) {
     if (n < 1) return -1;
     const long nn = (long)n * n;
@@ -688,7 +689,8 @@ extern "C" int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix,
 // the least loaded rank; every rank then receives the others' inverses by one sum all-reduce over
 // buffers that hold zeros where a rank did no work).
 namespace {
-constexpr int kInvStreams = 4;
+constexpr int kInvStreams = 4;   // explicit inverses: each stream owns a scratch region of 2.5 n^2
+constexpr int kSideStreams = 8;  // streams that exist; the scratch-free sequences use all of them
 struct InvJob {
     const double *src;
     double *dst;
@@ -718,11 +720,71 @@ std::vector<InvJob> inverse_jobs(const CNN_MODEL *m, const FITRE_KFAC_INFO *info
 }
 void ensure_side_streams(fitre_context *ctx) {
     if (ctx->inv_streams[0]) return;
-    for (int s = 0; s < kInvStreams; ++s)
+    for (int s = 0; s < kSideStreams; ++s)
         FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->inv_streams[s], cudaStreamNonBlocking));
     FITRE_CUDA(cudaEventCreateWithFlags(&ctx->inv_fork, cudaEventDisableTiming));
-    for (int s = 0; s < kInvStreams; ++s)
+    for (int s = 0; s < kSideStreams; ++s)
         FITRE_CUDA(cudaEventCreateWithFlags(&ctx->inv_join[s], cudaEventDisableTiming));
+}
+long long ptr_key(const void *p) { return (long long)(uintptr_t)p; }
+long long bits_key(double v) {
+    long long b;
+    std::memcpy(&b, &v, sizeof b);
+    return b;
+}
+// Runs enqueue() -- which issues work on ctx->stream and on the side streams forked from it --
+// through a CUDA graph: captured on first use (from a stream of the library's own, because the
+// caller's may be the legacy default stream, which cannot be captured), replayed on ctx->stream
+// while `key` is unchanged.  If capture or instantiation is refused the sequence is launched
+// directly and graphs are switched off for this context.
+template <class F>
+void run_graphed(fitre_context *ctx, fitre_context::CapturedGraph &g, const std::vector<long long> &key,
+                 F &&enqueue) {
+    if (!ctx->use_graphs) {
+        enqueue();
+        return;
+    }
+    if (g.exec && g.key == key) {
+        FITRE_CUDA(cudaGraphLaunch(g.exec, ctx->stream));
+        ctx->launches += g.launches;
+        return;
+    }
+    if (g.exec) {
+        cudaGraphExecDestroy(g.exec);
+        g.exec = nullptr;
+    }
+    if (!ctx->graph_stream) FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->graph_stream, cudaStreamNonBlocking));
+    const long long l0 = ctx->launches;
+    cudaStream_t user = ctx->stream;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(ctx->graph_stream, cudaStreamCaptureModeRelaxed);
+    if (e == cudaSuccess) {
+        ctx->stream = ctx->graph_stream;
+        try {
+            enqueue();
+        } catch (...) {
+            ctx->stream = user;
+            cudaStreamEndCapture(ctx->graph_stream, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            throw;
+        }
+        ctx->stream = user;
+        e = cudaStreamEndCapture(ctx->graph_stream, &graph);
+        if (e == cudaSuccess) e = cudaGraphInstantiate(&g.exec, graph, 0);
+        if (graph) cudaGraphDestroy(graph);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        g.exec = nullptr;
+        ctx->use_graphs = 0;
+        ctx->launches = l0;
+        enqueue();
+        return;
+    }
+    g.key = key;
+    g.launches = ctx->launches - l0;
+    FITRE_CUDA(cudaGraphLaunch(g.exec, ctx->stream));
 }
 int max_block(const CNN_MODEL *m) {
     int mx = 1;
@@ -759,21 +821,31 @@ extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m,
             if (r == ctx->rank) mine.push_back(j);
         }
         int *fail = (int *)(ctx->dscal + 4002);
+        ensure_side_streams(ctx);
+        std::vector<long long> key = {ptr_key(omegaZ), ptr_key(omegaZInv), ptr_key(lambdaG), ptr_key(lambdaGInv),
+                                      ptr_key(devPtr), bits_key(damp), ctx->kfac_solver, ctx->rank, W,
+                                      info->OmegaZSize, info->LambdaGSize};
+        for (const InvJob &j : jobs) {
+            key.push_back(j.n);
+            key.push_back(ptr_key(j.dst));
+        }
+        run_graphed(ctx, ctx->graph_invert, key, [&] {
         FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), ctx->stream));
         if (W > 1) {
             vec_fill(ctx, info->OmegaZSize, 0.0, omegaZInv);
             vec_fill(ctx, info->LambdaGSize, 0.0, lambdaGInv);
         }
         // fork: the side streams start after everything queued on the context's stream
-        ensure_side_streams(ctx);
         cudaStream_t main_stream = ctx->stream;
         FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
         const long per = align32(fitre_kfac_inverse_mem_required(max_block(m)));
-        std::vector<double> sload(kInvStreams, 0.0);
+        std::vector<double> sload(kSideStreams, 0.0);
         try {
-            for (int s = 0; s < kInvStreams; ++s) FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
+            for (int s = 0; s < kSideStreams; ++s) FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
             for (const InvJob &j : mine) {
-                const int s = (int)(std::min_element(sload.begin(), sload.end()) - sload.begin());
+                // an explicit inverse needs one of the kInvStreams scratch regions; a factorisation needs none
+                const int ns = j.factor_only ? kSideStreams : kInvStreams;
+                const int s = (int)(std::min_element(sload.begin(), sload.begin() + ns) - sload.begin());
                 sload[s] += j.cost;
                 ctx->stream = ctx->inv_streams[s];
                 if (j.factor_only) factor_spd(ctx, j.src, j.dst, j.n, damp, fail);
@@ -784,10 +856,11 @@ extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m,
             throw;
         }
         ctx->stream = main_stream;
-        for (int s = 0; s < kInvStreams; ++s) {
+        for (int s = 0; s < kSideStreams; ++s) {
             FITRE_CUDA(cudaEventRecord(ctx->inv_join[s], ctx->inv_streams[s]));
             FITRE_CUDA(cudaStreamWaitEvent(main_stream, ctx->inv_join[s], 0));
         }
+        });
         if (W > 1) {
             comm_allreduce_sum(ctx, omegaZInv, info->OmegaZSize);
             comm_allreduce_sum(ctx, lambdaGInv, info->LambdaGSize);
@@ -817,7 +890,7 @@ long natural_gradient_layer_scratch(const CNN_MODEL *m) {
 
 extern "C" long fitre_kfac_natural_gradient_mem_required(const CNN_MODEL *m) {
     if (!m) return -1;
-    return kInvStreams * natural_gradient_layer_scratch(m);
+    return kSideStreams * natural_gradient_layer_scratch(m);
 }
 
 // nGradient = G^-1 [W|b] A^-1 per layer, in the flat gradient layout.  The layers are independent
@@ -835,10 +908,21 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
         const bool chol = ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY;
         const long per = natural_gradient_layer_scratch(m);
         ensure_side_streams(ctx);
+        std::vector<long long> key = {ptr_key(omegaZInv), ptr_key(lambdaGInv), ptr_key(gradient), ptr_key(nGradient),
+                                      ptr_key(devPtr), ctx->kfac_solver, hasb, m->cLayers, m->lLayers};
+        for (int l = 0; l < m->cLayers + m->lLayers; ++l) {
+            key.push_back(info->OmegaZOffsets[l]);
+            key.push_back(info->LambdaGOffsets[l]);
+            key.push_back(m->wOffsets[l]);
+            key.push_back(l < m->cLayers ? m->convLayer[l].outChannels : m->fcLayer[l - m->cLayers].out);
+            key.push_back(l < m->cLayers ? m->convLayer[l].inChannels * m->convLayer[l].kSize * m->convLayer[l].kSize
+                                         : m->fcLayer[l - m->cLayers].in);
+        }
+        run_graphed(ctx, ctx->graph_natgrad, key, [&] {
         cudaStream_t main_stream = ctx->stream;
         FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
-        for (int s = 0; s < kInvStreams; ++s) FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
-        std::vector<double> sload(kInvStreams, 0.0);
+        for (int s = 0; s < kSideStreams; ++s) FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
+        std::vector<double> sload(kSideStreams, 0.0);
         auto pick_stream = [&](double cost) {
             const int s = (int)(std::min_element(sload.begin(), sload.end()) - sload.begin());
             sload[s] += cost;
@@ -903,10 +987,11 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
             throw;
         }
         ctx->stream = main_stream;
-        for (int s = 0; s < kInvStreams; ++s) {
+        for (int s = 0; s < kSideStreams; ++s) {
             FITRE_CUDA(cudaEventRecord(ctx->inv_join[s], ctx->inv_streams[s]));
             FITRE_CUDA(cudaStreamWaitEvent(main_stream, ctx->inv_join[s], 0));
         }
+        });
         return FITRE_OK;
     } catch (const Error &e) {
         ctx->err = e.what();

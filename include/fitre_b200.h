@@ -242,6 +242,13 @@ int fitre_set_precision(fitre_context *ctx, int precision);
 enum { FITRE_KFAC_SOLVER_INVERSE = 0, FITRE_KFAC_SOLVER_CHOLESKY = 1 };
 int fitre_set_kfac_solver(fitre_context *ctx, int solver);
 
+/* 1 (default) = fitre_kfac_invert_factors and fitre_compute_natural_gradient, whose launch
+ * sequences (a thousand small dependent kernels) are fixed by the model and the buffers, capture
+ * that sequence into a CUDA graph on first use and replay it while pointers, sizes, damping and
+ * solver stay the same; 0 = launch kernel by kernel.  Same kernels and results either way.  No
+ * counterpart in the reference. */
+int fitre_set_graphs(fitre_context *ctx, int on);
+
 /* 1 (default) = use the TMA-fed convolution kernels wherever shape and alignment allow;
  * 0 = always use the gather kernels (same results; kept for comparison and as the path
  * for odd shapes).  No counterpart in the reference. */

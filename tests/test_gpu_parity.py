@@ -383,7 +383,22 @@ def test_cuda_cholesky_solve_natural_gradient_large_blocks():
         api.invertFactors(run.c, model, info, A, Ac, Gm, Gi2, scratch)
         ng = G.dev(np.zeros(model.pSize))
         api.computeNaturalGradient(run.c, model, info, Ac, Gi2, run.ws.gradient, ng, scratch)
+        # the same sequence launched kernel by kernel instead of replayed from the captured graph
+        run.c.set_graphs(0)
+        Ac2, Gi3 = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+        api.invertFactors(run.c, model, info, A, Ac2, Gm, Gi3, scratch)
+        ng2 = G.dev(np.zeros(model.pSize))
+        api.computeNaturalGradient(run.c, model, info, Ac2, Gi3, run.ws.gradient, ng2, scratch)
+        run.c.set_graphs(1)
+        assert np.array_equal(Ac2.cpu().numpy(), Ac.cpu().numpy())
+        assert np.array_equal(ng2.cpu().numpy(), ng.cpu().numpy())
+        # replay (second call with the same buffers) gives the same bits as the capture run
+        api.invertFactors(run.c, model, info, A, Ac, Gm, Gi2, scratch)
+        api.computeNaturalGradient(run.c, model, info, Ac, Gi2, run.ws.gradient, ng, scratch)
+        assert np.array_equal(Ac2.cpu().numpy(), Ac.cpu().numpy())
+        assert np.array_equal(ng2.cpu().numpy(), ng.cpu().numpy())
     finally:
+        run.c.set_graphs(1)
         run.c.set_kfac_solver(0)
     g_h, ng_h = run.ws.gradient.cpu().numpy(), ng.cpu().numpy()
     for l in range(model.cLayers):
