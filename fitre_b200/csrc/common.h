@@ -163,6 +163,9 @@ void syrk_tn(fitre_context *ctx, long rows, int n, double alpha, const double *A
              double *C, double *partials);
 
 long conv_patch_syrk_scratch(int N, int Cin, int H, int W, int k, int pad, bool bias);
+long conv_patch_syrk_tma_scratch(int N, int Cin, int H, int W, int k, int pad);
+int conv_patch_syrk_tma(fitre_context *ctx, const double *x, double *slabs, int N, int Cin, int H, int W,
+                        int k, int pad);
 // A = alpha * S (P~' P~) S over implicit im2col patches P~ = [im2col(x), 1], S = diag(patch_scale.., 1)
 void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int Cin, int H, int W,
                      int k, int pad, bool bias, double alpha, double patch_scale, double *partials);

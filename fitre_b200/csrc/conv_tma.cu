@@ -339,6 +339,150 @@ wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
         }
 }
 
+// ---------------------------------------------------------------------------------------------
+// TMA-fed KFAC A factor of a convolution without bias column: slab = im2col(X)' im2col(X)
+// (solvers/kfac_inverses.cu:515-540 forms the patch matrix and multiplies it by itself), the same
+// data flow as the weight gradient above with the errors replaced by a second raw patch: CTA tile
+// 128 rows q x 64 columns q', both operands read straight from the raw input boxes in shared
+// memory (element (q, m) = patch[rowbase(m) + qofs(q)]).  Only tiles that touch the lower
+// triangle are computed; scaling and the mirror image are applied by the caller's reducer.
+// ---------------------------------------------------------------------------------------------
+struct alignas(64) TmaSyrkArgs {
+    CUtensorMap amap, bmap;  // same tensor, boxes of CBW / CBB channels
+    double *out;             // slabs [split][K*K]
+    int *err;
+    long M;
+    int N, K, Ho, Wo, pad, TW, TN, HB, WB, xoff, x0, CBW, CBB, stages, tilesW;
+    int tiles_total, tiles_per_split, patchBytesA, patchBytesB;
+};
+
+template <int KS, int BMT>
+__global__ void __launch_bounds__(T_THREADS, 2)
+patch_syrk_tma_kernel(const __grid_constant__ TmaSyrkArgs p) {
+    const int q0 = blockIdx.x * W_BQ, c0 = blockIdx.y * W_BN;
+    if (c0 > q0 + W_BQ - 1) return;  // strictly above the diagonal: mirrored by the reducer
+    extern __shared__ unsigned char smraw[];
+    unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 1023) & ~(uintptr_t)1023);
+    const int stageBytes = p.patchBytesA + p.patchBytesB;  // [patch of the rows | patch of the columns]
+    int *rowbase_s = (int *)(sm + (size_t)p.stages * stageBytes);
+    unsigned long long *bars = (unsigned long long *)(rowbase_s + BMT);
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_q = warp & 3, warp_n = warp >> 2;
+    const int lr = lane >> 2, lc = lane & 3;
+    const int ca_lo = q0 / (KS * KS), cb_lo = c0 / (KS * KS);
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(bars + s), 1);                  // full
+            mbar_init(smem_u32(bars + 4 + s), T_THREADS / 32);  // empty
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int ml = tid; ml < BMT; ml += T_THREADS) {
+        const int ho = ml % p.Ho, r = ml / p.Ho;
+        const int wl = r % p.TW, nl = r / p.TW;
+        rowbase_s[ml] = (nl * p.WB + wl) * p.HB + ho + p.xoff;
+    }
+    __syncthreads();
+
+    // q >= K falls on channels >= Cin, which TMA zero-fills; 128 rows span at most CBW channels and
+    // 64 columns at most CBB, so every offset stays inside its patch
+    int qa[4], qb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int q = q0 + warp_q * 32 + i * 8 + lr;
+        const int c = q / (KS * KS), rem = q - c * (KS * KS);
+        const int j = rem / KS, ii = rem - j * KS;
+        qa[i] = ((c - ca_lo) * p.TN * p.WB + j) * p.HB + ii;
+        const int q2 = c0 + warp_n * 32 + i * 8 + lr;
+        const int c2 = q2 / (KS * KS), rem2 = q2 - c2 * (KS * KS);
+        const int j2 = rem2 / KS, i2 = rem2 - j2 * KS;
+        qb[i] = ((c2 - cb_lo) * p.TN * p.WB + j2) * p.HB + i2;
+    }
+
+    const int t_beg = blockIdx.z * p.tiles_per_split;
+    const int t_end = min(p.tiles_total, t_beg + p.tiles_per_split);
+    const int iters = max(0, t_end - t_beg);
+    const uint32_t txBytes = (uint32_t)(p.HB * p.WB * p.TN * (p.CBW + p.CBB) * 8);
+    auto issue = [&](int it) {
+        const int t = t_beg + it;
+        const int wt = t % p.tilesW, nt = t / p.tilesW;
+        const int s = it % p.stages;
+        const uint32_t bar = smem_u32(bars + s);
+        unsigned char *dst = sm + (size_t)s * stageBytes;
+        mbar_expect_tx(bar, txBytes);
+        tma_load_4d(smem_u32(dst), &p.amap, bar, p.x0, wt * p.TW - p.pad, nt * p.TN, ca_lo);
+        tma_load_4d(smem_u32(dst + p.patchBytesA), &p.bmap, bar, p.x0, wt * p.TW - p.pad, nt * p.TN, cb_lo);
+    };
+    if (tid == 0)
+        for (int it = 0; it < p.stages - 1 && it < iters; ++it) issue(it);
+
+    double acc[4][4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+    volatile int *vabort = &abort_flag;
+    for (int it = 0; it < iters; ++it) {
+        const int s = it % p.stages;
+        if (tid == 0 && it + p.stages - 1 < iters) {
+            const int nit = it + p.stages - 1, use = nit / p.stages;
+            if (use > 0 && !mbar_wait(smem_u32(bars + 4 + nit % p.stages), (uint32_t)((use - 1) & 1)))
+                *vabort = 1;
+            else
+                issue(nit);
+        }
+        if (*vabort || !mbar_wait(smem_u32(bars + s), (uint32_t)((it / p.stages) & 1))) {
+            *vabort = 1;
+            break;
+        }
+        {
+            const double *pa = (const double *)(sm + (size_t)s * stageBytes);
+            const double *pb = (const double *)(sm + (size_t)s * stageBytes + p.patchBytesA);
+#pragma unroll
+            for (int k4 = 0; k4 < BMT / 4; ++k4) {
+                const int rb = rowbase_s[k4 * 4 + lc];
+                double fa[4], fb[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    fa[i] = pa[rb + qa[i]];
+                    fb[i] = pb[rb + qb[i]];
+                }
+#pragma unroll
+                for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                    for (int ni = 0; ni < 4; ++ni)
+                        dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bars + 4 + s));
+    }
+    __syncthreads();
+    if (abort_flag) {
+        if (tid == 0) atomicExch(p.err, 1);
+        return;
+    }
+
+    double *out = p.out + (long)blockIdx.z * p.K * p.K;
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int col = c0 + warp_n * 32 + ni * 8 + 2 * lc + e;
+            if (col >= p.K) continue;
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) {
+                const int row = q0 + warp_q * 32 + mi * 8 + lr;
+                if (row < p.K) out[(long)col * p.K + row] = acc[mi][ni][e];
+            }
+        }
+}
+
 __global__ void reduce_slabs_tma_kernel(const double *partial, double *out, long n, int slabs) {
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n;
          i += (long)gridDim.x * blockDim.x) {
@@ -427,9 +571,73 @@ WgradPlan wgrad_plan(int N, int Cin, int H, int W, int k, int pad, int Cout) {
     return pl;
 }
 
+// Tiling plan of the TMA A-factor kernel; ok == false when shape/alignment rule it out.
+struct SyrkPlan {
+    bool ok = false;
+    int BMT = 0, TW = 0, TN = 0, HB = 0, WB = 0, x0 = 0, xoff = 0, CBW = 0, CBB = 0;
+    int patchBytesA = 0, patchBytesB = 0, stages = 0, tiles_total = 0, splits = 1, tiles_per_split = 0;
+    int tq = 0, tn = 0, smem = 0;
+};
+
+SyrkPlan syrk_plan(int N, int Cin, int H, int W, int k, int pad) {
+    SyrkPlan pl;
+    if (!encode_fn() || (k != 3 && k != 5)) return pl;
+    const int K = Cin * k * k;
+    if (K <= 128) return pl;  // one mostly empty tile: gather kernel
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    const long M = (long)N * Ho * Wo;
+    if (Ho < 1 || Wo < 1 || (H & 1) || (M & 1)) return pl;
+    const int padE = pad + (pad & 1);
+    pl.x0 = -padE;
+    pl.xoff = padE - pad;
+    pl.HB = (H + pad + padE + 1) & ~1;
+    pl.CBW = (k == 3) ? 16 : 8;                  // input channels 128 rows of q can touch
+    pl.CBB = (W_BN + k * k - 1) / (k * k) + 1;   // ... and 64 columns
+    for (int bmt : {64, 32}) {
+        int TW, TN;
+        if (Ho * Wo >= bmt) {
+            if (bmt % Ho) continue;
+            TW = bmt / Ho;
+            TN = 1;
+            if (Wo % TW) continue;
+        } else {
+            if (bmt % (Ho * Wo)) continue;
+            TW = Wo;
+            TN = bmt / (Ho * Wo);
+        }
+        const int WB = TW + k - 1;
+        if (pl.HB > 256 || WB > 256 || TN > 256) continue;
+        const int pa = (pl.HB * WB * TN * pl.CBW * 8 + 1023) & ~1023;
+        const int pb = (pl.HB * WB * TN * pl.CBB * 8 + 1023) & ~1023;
+        const int fixed = 1024 + bmt * 4 + 8 * 8;
+        const int stages = (kSmemBudget - fixed) / (pa + pb);
+        if (stages < 2) continue;
+        pl.BMT = bmt; pl.TW = TW; pl.TN = TN; pl.WB = WB; pl.patchBytesA = pa; pl.patchBytesB = pb;
+        pl.stages = std::min(stages, 4);
+        pl.smem = pl.stages * (pa + pb) + fixed;
+        pl.ok = true;
+        break;
+    }
+    if (!pl.ok) return pl;
+    pl.tq = (K + W_BQ - 1) / W_BQ;
+    pl.tn = (K + W_BN - 1) / W_BN;
+    pl.tiles_total = (int)((M + pl.BMT - 1) / pl.BMT);
+    long tiles = 0;  // tiles that touch the lower triangle
+    for (int qt = 0; qt < pl.tq; ++qt) tiles += std::min(pl.tn, 2 * qt + 2);
+    const double step_us = 8.3 * pl.BMT / 64.0;
+    pl.splits = best_split(tiles, pl.tiles_total, 256, 8, step_us, (double)K * K * 8);
+    pl.tiles_per_split = (pl.tiles_total + pl.splits - 1) / pl.splits;
+    pl.splits = (pl.tiles_total + pl.tiles_per_split - 1) / pl.tiles_per_split;
+    return pl;
+}
+
 }  // namespace
 
 void conv_tma_init_attributes() {
+    FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_tma_kernel<3, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_tma_kernel<3, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_tma_kernel<5, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_tma_kernel<5, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     FITRE_CUDA(cudaFuncSetAttribute(wgrad_tma_kernel<3, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     FITRE_CUDA(cudaFuncSetAttribute(wgrad_tma_kernel<3, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     FITRE_CUDA(cudaFuncSetAttribute(wgrad_tma_kernel<5, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
@@ -591,6 +799,42 @@ bool conv_wgrad_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, double *d
         check_launch(ctx, "reduce_slabs_tma_kernel");
     }
     return true;
+}
+
+long conv_patch_syrk_tma_scratch(int N, int Cin, int H, int W, int k, int pad) {
+    const SyrkPlan pl = syrk_plan(N, Cin, H, W, k, pad);
+    if (!pl.ok) return 0;
+    return (long)pl.splits * Cin * k * k * Cin * k * k;
+}
+
+// slabs[s] (K x K each, lower triangle valid) = partial sums of im2col(x)' im2col(x); returns the
+// number of slabs, or 0 when the TMA kernel cannot take the shape (the caller then gathers).
+int conv_patch_syrk_tma(fitre_context *ctx, const double *x, double *slabs, int N, int Cin, int H, int W,
+                        int k, int pad) {
+    const SyrkPlan pl = syrk_plan(N, Cin, H, W, k, pad);
+    if (!pl.ok || ((uintptr_t)x & 15)) return 0;
+    const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
+    TmaSyrkArgs a{};
+    a.M = (long)N * Ho * Wo;
+    a.N = N; a.K = Cin * k * k; a.Ho = Ho; a.Wo = Wo; a.pad = pad;
+    a.TW = pl.TW; a.TN = pl.TN; a.HB = pl.HB; a.WB = pl.WB; a.xoff = pl.xoff; a.x0 = pl.x0;
+    a.CBW = pl.CBW; a.CBB = pl.CBB; a.stages = pl.stages; a.tilesW = Wo / pl.TW;
+    a.tiles_total = pl.tiles_total; a.tiles_per_split = pl.tiles_per_split;
+    a.patchBytesA = pl.patchBytesA; a.patchBytesB = pl.patchBytesB;
+    a.out = slabs;
+    a.err = (int *)(ctx->dscal + 4000);
+    cuuint64_t xd[4] = {(cuuint64_t)H, (cuuint64_t)W, (cuuint64_t)N, (cuuint64_t)Cin};
+    cuuint64_t xs[3] = {(cuuint64_t)H * 8, (cuuint64_t)H * W * 8, (cuuint64_t)H * W * N * 8};
+    cuuint32_t xa[4] = {(cuuint32_t)pl.HB, (cuuint32_t)pl.WB, (cuuint32_t)pl.TN, (cuuint32_t)pl.CBW};
+    cuuint32_t xb[4] = {(cuuint32_t)pl.HB, (cuuint32_t)pl.WB, (cuuint32_t)pl.TN, (cuuint32_t)pl.CBB};
+    if (!encode(&a.amap, x, 4, xd, xs, xa) || !encode(&a.bmap, x, 4, xd, xs, xb)) return 0;
+    dim3 grid(pl.tq, pl.tn, pl.splits);
+    if (k == 3 && pl.BMT == 64) patch_syrk_tma_kernel<3, 64><<<grid, T_THREADS, pl.smem, ctx->stream>>>(a);
+    else if (k == 3) patch_syrk_tma_kernel<3, 32><<<grid, T_THREADS, pl.smem, ctx->stream>>>(a);
+    else if (pl.BMT == 64) patch_syrk_tma_kernel<5, 64><<<grid, T_THREADS, pl.smem, ctx->stream>>>(a);
+    else patch_syrk_tma_kernel<5, 32><<<grid, T_THREADS, pl.smem, ctx->stream>>>(a);
+    check_launch(ctx, "patch_syrk_tma_kernel");
+    return pl.splits;
 }
 
 }  // namespace fitre

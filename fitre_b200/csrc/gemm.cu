@@ -789,7 +789,8 @@ __global__ void patch_syrk_reduce_kernel(const double *partial, double *out, int
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nn;
          i += (long)gridDim.x * blockDim.x) {
         const int col = (int)(i / Kb), row = (int)(i - (long)col * Kb);
-        const long src = (col / WG_BN <= row / WG_BQ) ? i : (long)row * Kb + col;
+        // every producer computes at least the tiles that hold the lower triangle
+        const long src = (row >= col) ? i : (long)row * Kb + col;
         double s = 0.0;
         for (int k = 0; k < slabs; ++k) s += partial[(long)k * nn + src];
         const double sc = (row < K ? patch_scale : 1.0) * (col < K ? patch_scale : 1.0);
@@ -986,7 +987,9 @@ static int patch_syrk_splits(long M, int Kb) {
 long conv_patch_syrk_scratch(int N, int Cin, int H, int W, int k, int pad, bool bias) {
     const long M = (long)N * (H + 2 * pad - k + 1) * (W + 2 * pad - k + 1);
     const int Kb = Cin * k * k + (bias ? 1 : 0);
-    return (long)patch_syrk_splits(M, Kb) * Kb * Kb;
+    long need = (long)patch_syrk_splits(M, Kb) * Kb * Kb;
+    if (!bias) need = std::max(need, conv_patch_syrk_tma_scratch(N, Cin, H, W, k, pad));
+    return need;
 }
 
 void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int Cin, int H, int W,
@@ -1001,6 +1004,17 @@ void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int 
     a.K = Cin * k * k;
     a.Kb = a.K + (bias ? 1 : 0);
     a.M = (long)N * a.Ho * a.Wo;
+    const long nn = (long)a.Kb * a.Kb;
+    const int blocks = (int)std::min<long>((nn + 255) / 256, 1184);
+    if (!bias && ctx->use_tma) {  // the TMA kernel has no ones column
+        const int St = conv_patch_syrk_tma(ctx, x, partials, N, Cin, H, W, k, pad);
+        if (St > 0) {
+            patch_syrk_reduce_kernel<<<blocks, 256, 0, ctx->stream>>>(partials, A, a.Kb, a.K, St, alpha,
+                                                                      patch_scale);
+            check_launch(ctx, "patch_syrk_reduce_kernel");
+            return;
+        }
+    }
     const int S = patch_syrk_splits(a.M, a.Kb);
     a.chunk = ((a.M + S - 1) / S + WG_BK - 1) / WG_BK * WG_BK;
     const int t = (a.Kb + WG_BQ - 1) / WG_BQ;
@@ -1012,8 +1026,6 @@ void conv_patch_syrk(fitre_context *ctx, const double *x, double *A, int N, int 
     else
         patch_syrk_kernel<0><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
     check_launch(ctx, "patch_syrk_kernel");
-    const long nn = (long)a.Kb * a.Kb;
-    int blocks = (int)std::min<long>((nn + 255) / 256, 1184);
     patch_syrk_reduce_kernel<<<blocks, 256, 0, ctx->stream>>>(partials, A, a.Kb, a.K, S, alpha,
                                                               patch_scale);
     check_launch(ctx, "patch_syrk_reduce_kernel");

@@ -141,8 +141,9 @@ def test_cuda_midsize_alexnet_and_vgg11_vs_oracle():
 def test_cuda_kfac_factors_vs_oracle():
     import gpu_util as G
     from fitre_b200 import api, _lib
+    # vgg11 at 4 images: factor sizes 576 ... 4608, the shapes the TMA-fed A-factor kernel takes
     for builder, kwargs, n in (("vgg_small", dict(), 6), ("lenet_small", dict(), 5),
-                               ("alexnet_small", dict(bias=True), 4)):
+                               ("alexnet_small", dict(bias=True), 4), ("vgg11", dict(), 4)):
         model = getattr(nets, builder)(n, **kwargs)
         O.finalize(model)
         x, y, w, v, ncls = G.synth(model, n, seed=31)
@@ -177,6 +178,14 @@ def test_cuda_kfac_factors_vs_oracle():
             assert G.relmax(A[a0:a0 + kb * kb], A_o[a0:a0 + kb * kb]) < TOL, l
             g0, g1 = info.LambdaGOffsets[l], info.LambdaGOffsets[l + 1]
             assert G.relmax(Gm[g0:g1], G_o[g0:g1]) < TOL, l
+        # the gather kernel (TMA off) forms the same factors
+        run.c.set_tma(0)
+        try:
+            A2 = G.dev(np.zeros(info.OmegaZSize))
+            api.computeOmegaZ(run.c, model, run.data, run.ws.z, n, A2, info2, scratch)
+        finally:
+            run.c.set_tma(1)
+        assert G.relmax(A2.cpu().numpy(), A) < 1e-13
 
 
 def test_cuda_host_entry_point():
