@@ -143,7 +143,8 @@ def test_cuda_kfac_factors_vs_oracle():
     from fitre_b200 import api, _lib
     # vgg11 at 4 images: factor sizes 576 ... 4608, the shapes the TMA-fed A-factor kernel takes
     for builder, kwargs, n in (("vgg_small", dict(), 6), ("lenet_small", dict(), 5),
-                               ("alexnet_small", dict(bias=True), 4), ("vgg11", dict(), 4)):
+                               ("alexnet_small", dict(bias=True), 4), ("vgg11", dict(), 4),
+                               ("alexnet", dict(), 2)):  # 5 x 5 taps, K = 1600, through the TMA kernel
         model = getattr(nets, builder)(n, **kwargs)
         O.finalize(model)
         x, y, w, v, ncls = G.synth(model, n, seed=31)
