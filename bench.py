@@ -399,7 +399,8 @@ def run_extra(args):
     extra = {}
     if wl == "kfac":
         ctx.set_kfac_solver(1 if args.kfac_solver == "cholesky" else 0)
-        extra["kfac_solver"] = args.kfac_solver
+        ctx.set_graphs(not args.no_graphs)
+        extra["kfac_solver"], extra["cuda_graphs"] = args.kfac_solver, not args.no_graphs
         info = api.computeKFACStorageIndices(model)
         need = _lib.load().fitre_kfac_mem_required(C.byref(model))
         kscr = torch.zeros(max(need, ws.dev.numel()), **f64)
@@ -413,7 +414,7 @@ def run_extra(args):
         Ai, Gi = torch.zeros(info.OmegaZSize, **f64), torch.zeros(info.LambdaGSize, **f64)
         ngrad = torch.zeros(model.pSize, **f64)
         L = _lib.load()
-        iscr = torch.zeros(max(L.fitre_kfac_invert_factors_mem_required(C.byref(model)),
+        iscr = torch.zeros(max(L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model)),
                                L.fitre_kfac_natural_gradient_mem_required(C.byref(model))), **f64)
         info.regLambda, info.dampGamma = 1e-3, 0.0
         blocks = []
@@ -442,9 +443,8 @@ def run_extra(args):
         else:
             api.computeDistributionErrors(ctx, ws.probs, U, tgt, e1b, n, 10)
             api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
-            api.computeOmegaZ(ctx, model, data, ws.z, n, A, info, kscr)
-            api.computeLambdaDelta(ctx, model, ddx, n, G, info, kscr)
-            api.invertFactors(ctx, model, info, A, Ai, G, Gi, iscr)  # 22 damped factors: inverses or Cholesky
+            # A/G factors and the 22 damped factorisations (inverses or Cholesky), overlapped
+            api.computeFactorsAndInverses(ctx, model, data, ws.z, ddx, n, A, Ai, G, Gi, info, iscr)
             api.computeNaturalGradient(ctx, model, info, Ai, Gi, ws.gradient, ngrad, iscr)
 
     def barrier():
@@ -504,6 +504,7 @@ def run_fitre(args):
     if world > 1:
         ctx.comm_init_from_torch()
     ctx.set_kfac_solver(1 if args.kfac_solver == "cholesky" else 0)
+    ctx.set_graphs(not args.no_graphs)
     n = 256
     model = nets.vgg11(n)
     api.finalize(model)
@@ -573,6 +574,9 @@ def main():
     ap.add_argument("--kfac-solver", default="cholesky", choices=["inverse", "cholesky"],
                     help="kfac / fitre workloads: explicit damped inverses of the A blocks (the "
                          "reference's form) or Cholesky factors applied by triangular solves")
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="kfac / fitre workloads: launch the factorisation and natural-gradient "
+                         "sequences kernel by kernel instead of replaying their CUDA graphs")
     ap.add_argument("--skip-cpu", action="store_true",
                     help="leave the CPU baseline leg out (profiling runs)")
     args = ap.parse_args()

@@ -341,6 +341,17 @@ def make_full_dataset(weights, trainX, trainY, testX, testY, numClasses, feature
     return d
 
 
+def computeFactorsAndInverses(ctx, model, data, z, dx, samples, omegaZ, omegaZInv, lambdaG, lambdaGInv, info,
+                              devPtr):
+    """computeOmegaZ + computeLambdaDelta of the reference in one call (factors and their damped
+    inverses, solvers/kfac_inverses.cu:450-630,759-857), factorisations overlapped with the factor
+    products; live state (the batch, z, dx of the sampled-label backward pass)."""
+    ctx.check(ctx.lib.fitre_kfac_factors_and_inverses(
+        ctx.h, C.byref(model), data.currentBatch, z.data_ptr(), dx.data_ptr(), 0, int(samples),
+        omegaZ.data_ptr(), omegaZInv.data_ptr(), lambdaG.data_ptr(), lambdaGInv.data_ptr(), C.byref(info),
+        devPtr.data_ptr()))
+
+
 def invertFactors(ctx, model, info, omegaZ, omegaZInv, lambdaG, lambdaGInv, devPtr):
     """All damped factor inverses of one KFAC step (several streams, divided among ranks)."""
     ctx.check(ctx.lib.fitre_kfac_invert_factors(ctx.h, C.byref(model), C.byref(info), omegaZ.data_ptr(),

@@ -123,6 +123,8 @@ int fitre_context_destroy(fitre_context *ctx) {
     if (ctx->inv_fork) cudaEventDestroy(ctx->inv_fork);
     if (ctx->graph_invert.exec) cudaGraphExecDestroy(ctx->graph_invert.exec);
     if (ctx->graph_natgrad.exec) cudaGraphExecDestroy(ctx->graph_natgrad.exec);
+    if (ctx->graph_factors.exec) cudaGraphExecDestroy(ctx->graph_factors.exec);
+    for (cudaEvent_t e : ctx->layer_ev) cudaEventDestroy(e);
     if (ctx->graph_stream) cudaStreamDestroy(ctx->graph_stream);
     if (ctx->ev_up) cudaEventDestroy(ctx->ev_up);
     if (ctx->ev_w2) cudaEventDestroy(ctx->ev_w2);

@@ -80,7 +80,8 @@ struct fitre_context {
         cudaGraphExec_t exec = nullptr;
         long long launches = 0;
     };
-    CapturedGraph graph_invert, graph_natgrad;
+    CapturedGraph graph_invert, graph_natgrad, graph_factors;
+    std::vector<cudaEvent_t> layer_ev;    // "factor of layer l is ready" (fused factors + inverses)
     cudaStream_t graph_stream = nullptr;  // origin stream of the captures
     int use_graphs = 1;
     // optional per-kernel timing (CUDA events on the launch stream), see fitre_profile_*

@@ -91,10 +91,12 @@ namespace {
 // Layer inputs come either from the live state (x0 = the batch, zbase = z with the model's z
 // offsets) or, packed == true, from the running averages of the "speed-up" variant (x0 =
 // dampedInput, zbase = dampedZ with the model's zzt offsets: solvers/kfac_inverses.cu:479-489,553-575).
-void omega_z_impl(fitre_context *ctx, const CNN_MODEL *m, const double *x0, const double *zbase, bool packed,
-                  int samples, double *omegaZ, const FITRE_KFAC_INFO *info, double *devPtr) {
+// A factor of layer li (convolutions first, then the FC layers), all-reduced when there are ranks
+void omega_z_layer(fitre_context *ctx, const CNN_MODEL *m, const double *x0, const double *zbase, bool packed,
+                   int samples, double *omegaZ, const FITRE_KFAC_INFO *info, double *devPtr, int li) {
     const double Ng = (double)samples * ctx->world;
-    for (int l = 0; l < m->cLayers; ++l) {
+    if (li < m->cLayers) {
+        const int l = li;
         const ConvGeom g = conv_geom(m, l);
         const double *x = (l == 0) ? x0
                           : packed ? zbase + m->zztOffsets[l]
@@ -109,30 +111,36 @@ void omega_z_impl(fitre_context *ctx, const CNN_MODEL *m, const double *x0, cons
             comm_allreduce_sum(ctx, A, (size_t)Kb * Kb);
             vec_scale(ctx, (long)Kb * Kb, 1.0 / Ng, A);
         }
+        return;
     }
+    const int l = li - m->cLayers;
     const ConvGeom lg = conv_geom(m, m->cLayers - 1);
-    for (int l = 0; l < m->lLayers; ++l) {
-        const FC_LAYER &f = m->fcLayer[l];
-        const double *zin = packed ? zbase + m->zztOffsets[m->cLayers + l]
-                            : (l == 0) ? zbase + lg.zoff + lg.outOff
-                                       : zbase + m->zOffsets[m->cLayers + l];
-        double *A = omegaZ + info->OmegaZOffsets[m->cLayers + l];
-        int R = f.in;
-        const double *zm = zin;
-        if (m->bias) {
-            R = f.in + 1;
-            const long total = (long)R * samples;
-            int blocks = (int)std::min<long>((total + 255) / 256, 1184);
-            fc_augment_kernel<<<blocks, 256, 0, ctx->stream>>>(zin, devPtr, f.in, samples);
-            check_launch(ctx, "fc_augment_kernel");
-            zm = devPtr;
-        }
-        dgemm(ctx, false, true, R, R, samples, ctx->world > 1 ? 1.0 : 1.0 / Ng, zm, R, zm, R, 0.0, A, R);
-        if (ctx->world > 1) {
-            comm_allreduce_sum(ctx, A, (size_t)R * R);
-            vec_scale(ctx, (long)R * R, 1.0 / Ng, A);
-        }
+    const FC_LAYER &f = m->fcLayer[l];
+    const double *zin = packed ? zbase + m->zztOffsets[m->cLayers + l]
+                        : (l == 0) ? zbase + lg.zoff + lg.outOff
+                                   : zbase + m->zOffsets[m->cLayers + l];
+    double *A = omegaZ + info->OmegaZOffsets[m->cLayers + l];
+    int R = f.in;
+    const double *zm = zin;
+    if (m->bias) {
+        R = f.in + 1;
+        const long total = (long)R * samples;
+        int blocks = (int)std::min<long>((total + 255) / 256, 1184);
+        fc_augment_kernel<<<blocks, 256, 0, ctx->stream>>>(zin, devPtr, f.in, samples);
+        check_launch(ctx, "fc_augment_kernel");
+        zm = devPtr;
     }
+    dgemm(ctx, false, true, R, R, samples, ctx->world > 1 ? 1.0 : 1.0 / Ng, zm, R, zm, R, 0.0, A, R);
+    if (ctx->world > 1) {
+        comm_allreduce_sum(ctx, A, (size_t)R * R);
+        vec_scale(ctx, (long)R * R, 1.0 / Ng, A);
+    }
+}
+
+void omega_z_impl(fitre_context *ctx, const CNN_MODEL *m, const double *x0, const double *zbase, bool packed,
+                  int samples, double *omegaZ, const FITRE_KFAC_INFO *info, double *devPtr) {
+    for (int li = 0; li < m->cLayers + m->lLayers; ++li)
+        omega_z_layer(ctx, m, x0, zbase, packed, samples, omegaZ, info, devPtr, li);
 }
 
 void lambda_delta_impl(fitre_context *ctx, const CNN_MODEL *m, const double *dbase, bool packed, int samples,
@@ -292,10 +300,11 @@ extern "C" int fitre_kfac_lambda_delta_damped(fitre_context *ctx, const CNN_MODE
 // Reference: computeMatrixInverseCusolver (solvers/kfac_inverses.cu:133-186: add (lambda+gamma)
 // to the diagonal, cusolverDnDpotrf, cusolverDnDpotrs against the identity) and
 // computeNaturalGradient (solvers/kfac_natural_gradient.cu:36-241: G^-1 [W|b] A^-1 per layer).
-// Here the Cholesky factorisation is a right-looking blocked one whose panel solves and
-// trailing updates are DMMA GEMMs, the triangular inverse is recursive (two GEMMs per level)
-// and the final L^-T L^-1 is the A'A kernel; only the 64x64 diagonal blocks are handled by a
-// small shared-memory kernel.  No cuSOLVER / cuBLAS.
+// Here: explicit inverses by one recursion that factors and inverts with GEMMs (factor_invert),
+// or, with FITRE_KFAC_SOLVER_CHOLESKY, a recursive blocked Cholesky factorisation in place
+// (chol_factor) whose factors the natural gradient applies by triangular solves (trsm_right).
+// Only the 64x64 diagonal blocks and triangles up to 256 run in small dedicated kernels; every
+// other product is a DMMA GEMM.  No cuSOLVER / cuBLAS.
 // ---------------------------------------------------------------------------------------------
 namespace {
 constexpr int NB = 64;
@@ -872,6 +881,131 @@ extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m,
         ctx->err = e.what();
         return e.code;
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Factors and their damped inverses in one call, as computeOmegaZ / computeLambdaDelta do layer
+// by layer (solvers/kfac_inverses.cu:450-630,759-857: each factor is inverted right after it is
+// formed).  On one GPU the two kinds of work are overlapped: the factor products (tensor-bound,
+// fill the GPU) run on the context's stream, largest A blocks first, and every factorisation
+// (a chain of small dependent kernels) starts on a side stream as soon as its factor is ready,
+// so the chains hide under the remaining products.  On one GPU the whole sequence is one CUDA
+// graph; with ranks each factor is all-reduced on the context's stream before its factorisation
+// starts on the rank that owns it, and the results are exchanged as fitre_kfac_invert_factors does.
+// ---------------------------------------------------------------------------------------------
+extern "C" long fitre_kfac_factors_and_inverses_mem_required(const CNN_MODEL *m) {
+    if (!m) return -1;
+    return align32(fitre_kfac_mem_required(m)) + fitre_kfac_invert_factors_mem_required(m);
+}
+
+extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MODEL *m, const real *x0,
+                                               const real *zbase, const real *dbase, int packed, int samples,
+                                               real *omegaZ, real *omegaZInv, real *lambdaG, real *lambdaGInv,
+                                               const FITRE_KFAC_INFO *info, real *devPtr) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(m && x0 && zbase && dbase && omegaZ && omegaZInv && lambdaG && lambdaGInv && info && devPtr,
+                  FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    model_check_batch(m, samples);
+    double *inv_scratch = devPtr + align32(fitre_kfac_mem_required(m));
+    const int W = ctx->world;
+    const bool chol = ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY;
+    const double damp = info->regLambda + info->dampGamma;
+    const int nl = m->cLayers + m->lLayers;
+    std::vector<InvJob> jobs = inverse_jobs(m, info, omegaZ, omegaZInv, lambdaG, lambdaGInv, chol);
+    // with ranks: the same division of the factorisations as fitre_kfac_invert_factors
+    std::vector<char> mine(jobs.size(), 1);
+    if (W > 1) {
+        std::vector<double> load(W, 0.0);
+        for (size_t i = 0; i < jobs.size(); ++i) {
+            const int r = (int)(std::min_element(load.begin(), load.end()) - load.begin());
+            load[r] += jobs[i].cost;
+            mine[i] = r == ctx->rank;
+        }
+    }
+    int *fail = (int *)(ctx->dscal + 4002);
+    ensure_side_streams(ctx);
+    while ((int)ctx->layer_ev.size() < nl) {
+        cudaEvent_t e;
+        FITRE_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        ctx->layer_ev.push_back(e);
+    }
+    std::vector<long long> key = {ptr_key(x0), ptr_key(zbase), ptr_key(dbase), packed, samples, ptr_key(omegaZ),
+                                  ptr_key(omegaZInv), ptr_key(lambdaG), ptr_key(lambdaGInv), ptr_key(devPtr),
+                                  bits_key(damp), ctx->kfac_solver, m->bias, info->OmegaZSize, info->LambdaGSize};
+    for (const InvJob &j : jobs) {
+        key.push_back(j.n);
+        key.push_back(ptr_key(j.dst));
+    }
+    for (int l = 0; l < m->cLayers; ++l) {
+        key.push_back(m->zOffsets[l]);
+        key.push_back(m->convLayer[l].height);
+        key.push_back(m->convLayer[l].width);
+    }
+    auto body = [&] {
+        cudaStream_t main_stream = ctx->stream;
+        FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), main_stream));
+        if (W > 1) {
+            vec_fill(ctx, info->OmegaZSize, 0.0, omegaZInv);
+            vec_fill(ctx, info->LambdaGSize, 0.0, lambdaGInv);
+        }
+        const long per = align32(fitre_kfac_inverse_mem_required(max_block(m)));
+        std::vector<double> sload(kSideStreams, 0.0);
+        // one job on the least loaded side stream, after `ready` (recorded on the main stream)
+        auto start_job = [&](const InvJob &j, cudaEvent_t ready) {
+            const int ns = j.factor_only ? kSideStreams : kInvStreams;
+            const int s = (int)(std::min_element(sload.begin(), sload.begin() + ns) - sload.begin());
+            sload[s] += j.cost;
+            FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ready, 0));
+            ctx->stream = ctx->inv_streams[s];
+            if (j.factor_only) factor_spd(ctx, j.src, j.dst, j.n, damp, fail);
+            else invert_spd(ctx, j.src, j.dst, j.n, damp, inv_scratch + (long)s * per, fail);
+            ctx->stream = main_stream;
+        };
+        try {
+            // every side stream joins the sequence, whether or not a job lands on it
+            FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
+            for (int s = 0; s < kSideStreams; ++s)
+                FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
+            // G factors: a fraction of a millisecond in all; their inverses start at once
+            lambda_delta_impl(ctx, m, dbase, packed != 0, samples, lambdaG, info, devPtr);
+            FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
+            for (size_t i = 0; i < jobs.size(); ++i)
+                if (mine[i] && jobs[i].src >= lambdaG && jobs[i].src < lambdaG + info->LambdaGSize)
+                    start_job(jobs[i], ctx->inv_fork);
+            // A factors, most expensive factorisation first
+            std::vector<int> order(nl);
+            for (int l = 0; l < nl; ++l) order[l] = l;
+            auto block = [&](int l) {
+                return l < m->cLayers ? m->convLayer[l].inChannels * m->convLayer[l].kSize * m->convLayer[l].kSize
+                                      : m->fcLayer[l - m->cLayers].in;
+            };
+            std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return block(x) > block(y); });
+            for (int l : order) {
+                omega_z_layer(ctx, m, x0, zbase, packed != 0, samples, omegaZ, info, devPtr, l);
+                FITRE_CUDA(cudaEventRecord(ctx->layer_ev[l], main_stream));
+                for (size_t i = 0; i < jobs.size(); ++i)
+                    if (mine[i] && jobs[i].src == omegaZ + info->OmegaZOffsets[l]) start_job(jobs[i], ctx->layer_ev[l]);
+            }
+        } catch (...) {
+            ctx->stream = main_stream;
+            throw;
+        }
+        for (int s = 0; s < kSideStreams; ++s) {
+            FITRE_CUDA(cudaEventRecord(ctx->inv_join[s], ctx->inv_streams[s]));
+            FITRE_CUDA(cudaStreamWaitEvent(main_stream, ctx->inv_join[s], 0));
+        }
+    };
+    if (W > 1) {
+        // the per-layer all-reduces of the factors sit between the kernels: launched directly
+        body();
+        comm_allreduce_sum(ctx, omegaZInv, info->OmegaZSize);
+        comm_allreduce_sum(ctx, lambdaGInv, info->LambdaGSize);
+        comm_allreduce_sum(ctx, ctx->dscal + 4002, 1);  // a failure on any rank is seen by all
+    } else {
+        run_graphed(ctx, ctx->graph_factors, key, body);
+    }
+    check_fail_word(ctx, fail);
+    KFAC_ENTRY_END
 }
 
 namespace {

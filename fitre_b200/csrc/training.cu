@@ -441,7 +441,7 @@ TrLayout tr_layout(const CNN_MODEL *m, const DEVICE_DATASET *data, const FITRE_K
     }
     long need = std::max(fitre_cnn_gradient_mem_required(m), fitre_quadratic_model_mem_required(m));
     need = std::max(need, fitre_kfac_mem_required(m));
-    need = std::max(need, fitre_kfac_invert_factors_mem_required(m));
+    need = std::max(need, fitre_kfac_factors_and_inverses_mem_required(m));
     need = std::max(need, fitre_kfac_natural_gradient_mem_required(m));
     need = std::max(need, fitre_generalization_mem_required(m));
     L.scratch = take(need);
@@ -544,14 +544,13 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
                 else if (total_mb % invFreq == 0) from_avg = true;
                 else refresh = false;
             }
-            if (refresh && from_avg) {
-                FITRE_RC(fitre_kfac_omega_z_damped(ctx, m, dInput, dZ, B, A, kfacInfo, work));
-                FITRE_RC(fitre_kfac_lambda_delta_damped(ctx, m, dLambda, B, G, kfacInfo, work));
-            } else if (refresh) {
-                FITRE_RC(fitre_kfac_omega_z(ctx, m, data, z, B, A, kfacInfo, work));
-                FITRE_RC(fitre_kfac_lambda_delta(ctx, m, distDX, B, G, kfacInfo, work));
-            }
-            if (refresh) FITRE_RC(fitre_kfac_invert_factors(ctx, m, kfacInfo, A, Ainv, G, Ginv, work));
+            // one call forms the factors and inverts them, the factorisations under the factor products
+            if (refresh && from_avg)
+                FITRE_RC(fitre_kfac_factors_and_inverses(ctx, m, dInput, dZ, dLambda, 1, B, A, Ainv, G, Ginv,
+                                                         kfacInfo, work));
+            else if (refresh)
+                FITRE_RC(fitre_kfac_factors_and_inverses(ctx, m, data->currentBatch, z, distDX, 0, B, A, Ainv, G,
+                                                         Ginv, kfacInfo, work));
             FITRE_RC(fitre_compute_natural_gradient(ctx, m, kfacInfo, Ainv, Ginv, gradient, nGradient, work));
 
             // quadratic models of the two candidate steps (:452-470); each call scales its direction

@@ -404,14 +404,37 @@ int fitre_kfac_lambda_delta_damped(fitre_context *ctx, const CNN_MODEL *m, const
  * The independent matrices run on several streams of the GPU and, with a communicator, are
  * divided among the ranks (largest first onto the least loaded rank) and exchanged by one sum
  * all-reduce, which replaces the reference's dormant second-GPU inverse thread
- * (solvers/kfac_thread.cu:77-204).  devPtr: fitre_kfac_invert_factors_mem_required doubles. */
+ * (solvers/kfac_thread.cu:77-204).  With FITRE_KFAC_SOLVER_CHOLESKY the A slots receive Cholesky
+ * factors instead (see fitre_set_kfac_solver).  The launch sequence is replayed from a CUDA graph
+ * while the arguments stay the same (fitre_set_graphs).  devPtr:
+ * fitre_kfac_invert_factors_mem_required doubles. */
 long fitre_kfac_invert_factors_mem_required(const CNN_MODEL *m);
 int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m, const FITRE_KFAC_INFO *info,
                               const real *omegaZ, real *omegaZInv, const real *lambdaG,
                               real *lambdaGInv, real *devPtr);
+/* Factors and damped inverses of one KFAC step in one call -- what computeOmegaZ and
+ * computeLambdaDelta do together in the reference, where each factor is inverted right after it
+ * is formed (solvers/kfac_inverses.cu:450-630,759-857).  x0 / zbase / dbase: the batch
+ * (data->currentBatch), z and the dx of the sampled-label backward pass (packed == 0), or the
+ * running averages dampedInput / dampedZ / dampedLambda of the inverseFreq > 1 variant
+ * (packed == 1, as fitre_kfac_omega_z_damped / fitre_kfac_lambda_delta_damped take them).  Same
+ * results as fitre_kfac_omega_z + fitre_kfac_lambda_delta + fitre_kfac_invert_factors, bit for
+ * bit; on one GPU the factor products run on the context's stream, largest first, and every
+ * factorisation starts on a side stream as soon as its factor is ready, so the chains of small
+ * kernels hide under the remaining products (one CUDA graph on a single GPU).  With a
+ * communicator each factor is all-reduced before its factorisation starts on the rank that owns
+ * it.  devPtr: fitre_kfac_factors_and_inverses_mem_required doubles. */
+long fitre_kfac_factors_and_inverses_mem_required(const CNN_MODEL *m);
+int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MODEL *m, const real *x0,
+                                    const real *zbase, const real *dbase, int packed, int samples,
+                                    real *omegaZ, real *omegaZInv, real *lambdaG, real *lambdaGInv,
+                                    const FITRE_KFAC_INFO *info, real *devPtr);
 /* solvers/kfac_natural_gradient.cu:36-241 (computeNaturalGradient): nGradient = G^-1 [W|b] A^-1
- * per layer, in the flat layout of `gradient`.  omegaZInv / lambdaGInv hold the inverted factors
- * at the offsets of `info` (A blocks K' x K' with K' = K + bias). */
+ * per layer, in the flat layout of `gradient`.  omegaZInv / lambdaGInv hold what
+ * fitre_kfac_invert_factors left there under the same solver setting: the inverted factors at
+ * the offsets of `info` (A blocks K' x K' with K' = K + bias), or, with
+ * FITRE_KFAC_SOLVER_CHOLESKY, Cholesky factors in the A slots, applied by triangular solves.  The
+ * layers run on side streams; devPtr: fitre_kfac_natural_gradient_mem_required doubles. */
 long fitre_kfac_natural_gradient_mem_required(const CNN_MODEL *m);
 int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODEL *m,
                                    const FITRE_KFAC_INFO *info, const real *omegaZInv,

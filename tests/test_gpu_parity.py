@@ -410,6 +410,22 @@ def test_cuda_cholesky_solve_natural_gradient_large_blocks():
     finally:
         run.c.set_graphs(1)
         run.c.set_kfac_solver(0)
+    # factors and factorisations in one overlapped call: the same bits as the separate calls
+    fscr = G.dev(np.zeros(L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model))))
+    for solver, want in ((0, Ai), (1, Ac)):
+        run.c.set_kfac_solver(solver)
+        try:
+            A3, G3 = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+            Ai3, Gi4 = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+            for _ in range(2):  # capture, then replay
+                api.computeFactorsAndInverses(run.c, model, run.data, run.ws.z, run.ws.dx, n, A3, Ai3, G3, Gi4,
+                                              info, fscr)
+        finally:
+            run.c.set_kfac_solver(0)
+        assert np.array_equal(A3.cpu().numpy(), A.cpu().numpy())
+        assert np.array_equal(G3.cpu().numpy(), Gm.cpu().numpy())
+        assert np.array_equal(Ai3.cpu().numpy(), want.cpu().numpy())
+        assert np.array_equal(Gi4.cpu().numpy(), Gi.cpu().numpy())
     g_h, ng_h = run.ws.gradient.cpu().numpy(), ng.cpu().numpy()
     for l in range(model.cLayers):
         c = model.convLayer[l]
