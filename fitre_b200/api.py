@@ -271,6 +271,11 @@ def computeMatrixInverse(ctx, matrix, inverse, n, devPtr, lam, dampGamma):
                                                 float(lam), float(dampGamma)))
 
 
+def computeMatrixFactor(ctx, matrix, factor, n, lam, gamma):
+    """Packed Cholesky factor of matrix + (lam + gamma) I (the Cholesky form of one A block)."""
+    ctx.check(ctx.lib.fitre_kfac_matrix_factor(ctx.h, _ptr(matrix), _ptr(factor), n, lam, gamma))
+
+
 def computeNaturalGradient(ctx, model, info, omegaZInv, lambdaGInv, gradient, nGradient, devPtr):
     """solvers/kfac_natural_gradient.cu:36-241."""
     ctx.check(ctx.lib.fitre_compute_natural_gradient(ctx.h, C.byref(model), C.byref(info),

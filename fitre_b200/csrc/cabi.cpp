@@ -166,6 +166,8 @@ int fitre_set_kfac_solver(fitre_context *ctx, int solver) {
     return FITRE_OK;
 }
 
+int fitre_get_kfac_solver(const fitre_context *ctx) { return ctx ? ctx->kfac_solver : -1; }
+
 int fitre_set_graphs(fitre_context *ctx, int on) {
     if (!ctx) return FITRE_ERR_BAD_ARG;
     ctx->use_graphs = on ? 1 : 0;

@@ -691,6 +691,24 @@ extern "C" int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix,
     }
 }
 
+// factor = packed Cholesky factor of matrix + (lambda + dampGamma) I, both n x n column-major.
+extern "C" int fitre_kfac_matrix_factor(fitre_context *ctx, const real *matrix, real *factor, int n,
+                                        real lambda, real dampGamma) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    try {
+        FITRE_CUDA(cudaSetDevice(ctx->device));
+        FITRE_REQUIRE(matrix && factor && n > 0, FITRE_ERR_BAD_ARG, "bad argument");
+        int *fail = (int *)(ctx->dscal + 4002);
+        FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), ctx->stream));
+        factor_spd(ctx, matrix, factor, n, lambda + dampGamma, fail);
+        check_fail_word(ctx, fail);
+        return FITRE_OK;
+    } catch (const Error &e) {
+        ctx->err = e.what();
+        return e.code;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // All 2L factor inverses of one KFAC step.  The matrices are independent: they are spread over a
 // few streams of this GPU (the leaves of the factorisation occupy one SM, so concurrent matrices

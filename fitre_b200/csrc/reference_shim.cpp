@@ -267,9 +267,15 @@ void computeOmegaZ(kfac_curvature *kfac_info, cnn *model, dev_dataset *data, int
     for (int l = 0; l < m->cLayers + m->lLayers; ++l) {
         int a, g;
         block_sizes(m, l, &a, &g);
-        die(fitre_kfac_matrix_inverse(ctx(), A + info.OmegaZOffsets[l], omegaZInv + info.OmegaZOffsets[l], a, work,
-                                      info.regLambda, info.dampGamma),
-            "computeOmegaZ (inverse)");
+        // the A slots hold what computeNaturalGradient expects under the context's solver setting
+        if (fitre_get_kfac_solver(ctx()) == FITRE_KFAC_SOLVER_CHOLESKY)
+            die(fitre_kfac_matrix_factor(ctx(), A + info.OmegaZOffsets[l], omegaZInv + info.OmegaZOffsets[l], a,
+                                         info.regLambda, info.dampGamma),
+                "computeOmegaZ (factor)");
+        else
+            die(fitre_kfac_matrix_inverse(ctx(), A + info.OmegaZOffsets[l], omegaZInv + info.OmegaZOffsets[l], a,
+                                          work, info.regLambda, info.dampGamma),
+                "computeOmegaZ (inverse)");
     }
     cudaDeviceSynchronize();
 }

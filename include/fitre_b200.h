@@ -241,6 +241,7 @@ int fitre_set_precision(fitre_context *ctx, int precision);
  *     setting.  No counterpart in the reference. */
 enum { FITRE_KFAC_SOLVER_INVERSE = 0, FITRE_KFAC_SOLVER_CHOLESKY = 1 };
 int fitre_set_kfac_solver(fitre_context *ctx, int solver);
+int fitre_get_kfac_solver(const fitre_context *ctx); /* the current setting; -1 without a context */
 
 /* 1 (default) = fitre_kfac_invert_factors and fitre_compute_natural_gradient, whose launch
  * sequences (a thousand small dependent kernels) are fixed by the model and the buffers, capture
@@ -377,6 +378,13 @@ int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, const real *
 long fitre_kfac_inverse_mem_required(int n);
 int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix, real *inverse, int n,
                               real *devPtr, real lambda, real dampGamma);
+/* The Cholesky form of one block: factor <- the packed Cholesky factor of matrix + (lambda +
+ * dampGamma) I (lower triangle L; the upper triangles of the 64 x 64 diagonal blocks hold those
+ * blocks' inverses), what fitre_kfac_invert_factors writes into an A slot under
+ * FITRE_KFAC_SOLVER_CHOLESKY.  No scratch.  For callers that invert block by block as
+ * computeOmegaZ does (solvers/kfac_inverses.cu:542-544). */
+int fitre_kfac_matrix_factor(fitre_context *ctx, const real *matrix, real *factor, int n, real lambda,
+                             real dampGamma);
 /* The running-average ("speed-up") variant, solvers/kfac_inverses.cu:106-126 (updateRunningStats:
  * theta <- m*theta + (1-m)*update in the reference's operation order, m == 0 copies), :386-447
  * (computeSpeedUpOmegaZ: averages of the batch into dampedInput and of every layer's output into

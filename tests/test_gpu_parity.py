@@ -458,6 +458,19 @@ def test_cuda_matrix_inverse_blocked_sizes_and_failure():
         api.computeMatrixInverse(c, G.dev(F.reshape(-1)), out, n, scratch, 1e-3, 0.1)
         ref = np.linalg.inv(F + 0.101 * np.eye(n))
         assert G.relmax(out.cpu().numpy().reshape(n, n), ref) < 1e-9, n
+    # the Cholesky form of a block: L L' reproduces the damped matrix, every size class
+    for n in (1, 63, 64, 65, 200, 257, 333, 1000):
+        B = rng.standard_normal((n, n + 8))
+        F = B @ B.T / n
+        out = G.dev(np.zeros(n * n))
+        api.computeMatrixFactor(c, G.dev(F.reshape(-1)), out, n, 1e-3, 0.1)
+        Lf = np.tril(out.cpu().numpy().reshape(n, n).T)
+        ref = F + 0.101 * np.eye(n)
+        assert np.abs(Lf @ Lf.T - ref).max() < 1e-12 * np.abs(ref).max() * max(n, 8), n
+        assert np.abs(Lf - np.linalg.cholesky(ref)).max() < 1e-10 * np.abs(ref).max(), n
+    with pytest.raises(api.FitreError) as e:
+        api.computeMatrixFactor(c, G.dev(-np.eye(70).reshape(-1)), G.dev(np.zeros(4900)), 70, 0.0, 0.0)
+    assert e.value.status == S.ERR_NOT_CONVERGED
     with pytest.raises(api.FitreError) as e:
         api.computeMatrixInverse(c, G.dev(-np.eye(70).reshape(-1)), G.dev(np.zeros(4900)), 70,
                                  G.dev(np.zeros(L.fitre_kfac_inverse_mem_required(70))), 0.0, 0.0)
