@@ -400,7 +400,10 @@ def run_extra(args):
     if wl == "kfac":
         ctx.set_kfac_solver(1 if args.kfac_solver == "cholesky" else 0)
         ctx.set_graphs(not args.no_graphs)
+        ctx.set_kfac_distribution(1)  # with ranks: factors stay on a layer's owner rank
         extra["kfac_solver"], extra["cuda_graphs"] = args.kfac_solver, not args.no_graphs
+        if world > 1:
+            extra["kfac_distribution"] = "layer_owned"
         info = api.computeKFACStorageIndices(model)
         need = _lib.load().fitre_kfac_mem_required(C.byref(model))
         kscr = torch.zeros(max(need, ws.dev.numel()), **f64)

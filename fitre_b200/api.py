@@ -82,6 +82,11 @@ class Context:
         the same slots, applied by two triangular solves in the natural gradient."""
         self.check(self.lib.fitre_set_kfac_solver(self.h, int(solver)))
 
+    def set_kfac_distribution(self, mode):
+        """With ranks: 0 = every rank holds all factors and inverses; 1 = each layer's factors live
+        on an owner rank, which also forms that layer's slice of the natural gradient."""
+        self.check(self.lib.fitre_set_kfac_distribution(self.h, int(mode)))
+
     def set_graphs(self, on):
         """CUDA-graph replay of the factor-inverse and natural-gradient launch sequences (default on)."""
         self.check(self.lib.fitre_set_graphs(self.h, int(bool(on))))

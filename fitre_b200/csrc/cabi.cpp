@@ -166,6 +166,12 @@ int fitre_set_kfac_solver(fitre_context *ctx, int solver) {
     return FITRE_OK;
 }
 
+int fitre_set_kfac_distribution(fitre_context *ctx, int mode) {
+    if (!ctx || (mode != FITRE_KFAC_REPLICATED && mode != FITRE_KFAC_LAYER_OWNED)) return FITRE_ERR_BAD_ARG;
+    ctx->kfac_owned = mode;
+    return FITRE_OK;
+}
+
 int fitre_get_kfac_solver(const fitre_context *ctx) { return ctx ? ctx->kfac_solver : -1; }
 
 int fitre_set_graphs(fitre_context *ctx, int on) {

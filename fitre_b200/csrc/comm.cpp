@@ -26,6 +26,7 @@ struct Api {
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Reduce)(const void *, void *, size_t, int, int, int, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -42,8 +43,9 @@ Api &api() {
     a.CommInitRank = (decltype(a.CommInitRank))dlsym(a.handle, "ncclCommInitRank");
     a.CommDestroy = (decltype(a.CommDestroy))dlsym(a.handle, "ncclCommDestroy");
     a.AllReduce = (decltype(a.AllReduce))dlsym(a.handle, "ncclAllReduce");
+    a.Reduce = (decltype(a.Reduce))dlsym(a.handle, "ncclReduce");
     a.GetErrorString = (decltype(a.GetErrorString))dlsym(a.handle, "ncclGetErrorString");
-    FITRE_REQUIRE(a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce,
+    FITRE_REQUIRE(a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.Reduce,
                   FITRE_ERR_COMM, "libnccl lacks a required symbol");
     return a;
 }
@@ -65,6 +67,13 @@ void comm_allreduce_sum(fitre_context *ctx, double *dev_buf, size_t n) {
     check(api().AllReduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, ctx->comm->comm, ctx->stream),
           "ncclAllReduce");
     ctx->launches += 1;  // NCCL's kernel; counted so the launch figure covers the whole step
+}
+
+// sum over the ranks, result on `root` only (the buffers of the other ranks are left as they were)
+void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root) {
+    if (ctx->world <= 1 || !ctx->comm || n == 0) return;
+    check(api().Reduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, root, ctx->comm->comm, ctx->stream), "ncclReduce");
+    ctx->launches += 1;
 }
 
 void comm_destroy(fitre_context *ctx) {

@@ -49,6 +49,7 @@ struct fitre_context {
     int ref_softmax = 1;
     int precision = 0;          // FITRE_PRECISION_* (convolution products)
     int kfac_solver = 0;        // FITRE_KFAC_SOLVER_* (what the A-factor slots hold)
+    int kfac_owned = 0;         // FITRE_KFAC_LAYER_OWNED: with ranks, each layer's factors live on one rank
     bool use_tma = true;        // TMA-fed convolution kernels where shape and alignment allow
     double *pinned = nullptr;   // 256 pinned host doubles (scalar read-back)
     double *dscal = nullptr;    // 4096 device doubles (scalar reductions)
@@ -115,6 +116,7 @@ struct ProfScope {
 
 // ---- comm.cpp: all-reduce hooks (no-ops when world == 1) ----
 void comm_allreduce_sum(fitre_context *ctx, double *dev_buf, size_t n);
+void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root);
 void comm_destroy(fitre_context *ctx);
 
 // ---- model.cpp ----

@@ -92,8 +92,17 @@ namespace {
 // offsets) or, packed == true, from the running averages of the "speed-up" variant (x0 =
 // dampedInput, zbase = dampedZ with the model's zzt offsets: solvers/kfac_inverses.cu:479-489,553-575).
 // A factor of layer li (convolutions first, then the FC layers), all-reduced when there are ranks
+// sum of a factor block over the ranks: on every rank (root < 0) or on `root` only, then the scale
+void reduce_block(fitre_context *ctx, double *F, long n, double scale, int root) {
+    if (ctx->world <= 1) return;
+    if (root < 0) comm_allreduce_sum(ctx, F, (size_t)n);
+    else comm_reduce_sum(ctx, F, (size_t)n, root);
+    if (root < 0 || root == ctx->rank) vec_scale(ctx, n, scale, F);
+}
+
 void omega_z_layer(fitre_context *ctx, const CNN_MODEL *m, const double *x0, const double *zbase, bool packed,
-                   int samples, double *omegaZ, const FITRE_KFAC_INFO *info, double *devPtr, int li) {
+                   int samples, double *omegaZ, const FITRE_KFAC_INFO *info, double *devPtr, int li,
+                   int root = -1) {
     const double Ng = (double)samples * ctx->world;
     if (li < m->cLayers) {
         const int l = li;
@@ -107,10 +116,7 @@ void omega_z_layer(fitre_context *ctx, const CNN_MODEL *m, const double *x0, con
         const double alpha = ctx->world > 1 ? 1.0 : 1.0 / Ng;
         conv_patch_syrk(ctx, x, A, samples, g.Cin, g.H, g.W, g.k, g.pad, m->bias != 0, alpha,
                         1.0 / (double)(g.Ho * g.Wo), devPtr);
-        if (ctx->world > 1) {
-            comm_allreduce_sum(ctx, A, (size_t)Kb * Kb);
-            vec_scale(ctx, (long)Kb * Kb, 1.0 / Ng, A);
-        }
+        reduce_block(ctx, A, (long)Kb * Kb, 1.0 / Ng, root);
         return;
     }
     const int l = li - m->cLayers;
@@ -131,10 +137,7 @@ void omega_z_layer(fitre_context *ctx, const CNN_MODEL *m, const double *x0, con
         zm = devPtr;
     }
     dgemm(ctx, false, true, R, R, samples, ctx->world > 1 ? 1.0 : 1.0 / Ng, zm, R, zm, R, 0.0, A, R);
-    if (ctx->world > 1) {
-        comm_allreduce_sum(ctx, A, (size_t)R * R);
-        vec_scale(ctx, (long)R * R, 1.0 / Ng, A);
-    }
+    reduce_block(ctx, A, (long)R * R, 1.0 / Ng, root);
 }
 
 void omega_z_impl(fitre_context *ctx, const CNN_MODEL *m, const double *x0, const double *zbase, bool packed,
@@ -143,32 +146,33 @@ void omega_z_impl(fitre_context *ctx, const CNN_MODEL *m, const double *x0, cons
         omega_z_layer(ctx, m, x0, zbase, packed, samples, omegaZ, info, devPtr, li);
 }
 
-void lambda_delta_impl(fitre_context *ctx, const CNN_MODEL *m, const double *dbase, bool packed, int samples,
-                       double *lambdaG, const FITRE_KFAC_INFO *info, double *devPtr) {
+// G factor of layer li (convolutions first, then the FC layers)
+void lambda_delta_layer(fitre_context *ctx, const CNN_MODEL *m, const double *dbase, bool packed, int samples,
+                        double *lambdaG, const FITRE_KFAC_INFO *info, double *devPtr, int li, int root = -1) {
     const double Ng = (double)samples * ctx->world;
-    for (int l = 0; l < m->cLayers; ++l) {
+    if (li < m->cLayers) {
+        const int l = li;
         const ConvGeom g = conv_geom(m, l);
         const double *d = packed ? dbase + m->zztOffsets[l + 1] : dbase + g.zoff + (g.bn ? g.bnOff : g.actOff);
         const long M = (long)samples * g.Ho * g.Wo;
         double *G = lambdaG + info->LambdaGOffsets[l];
         const double sc = (double)g.Ho * g.Wo * Ng;  // solvers/kfac_inverses.cu:815-816
         syrk_tn(ctx, M, g.Cout, ctx->world > 1 ? 1.0 : sc, d, M, G, devPtr);
-        if (ctx->world > 1) {
-            comm_allreduce_sum(ctx, G, (size_t)g.Cout * g.Cout);
-            vec_scale(ctx, (long)g.Cout * g.Cout, sc, G);
-        }
+        reduce_block(ctx, G, (long)g.Cout * g.Cout, sc, root);
+        return;
     }
-    for (int l = 0; l < m->lLayers; ++l) {
-        const FC_LAYER &f = m->fcLayer[l];
-        const double *d = packed ? dbase + m->zztOffsets[m->cLayers + l + 1] : dbase + m->zOffsets[m->cLayers + l + 1];
-        double *G = lambdaG + info->LambdaGOffsets[m->cLayers + l];
-        dgemm(ctx, false, true, f.out, f.out, samples, ctx->world > 1 ? 1.0 : Ng, d, f.out, d,
-              f.out, 0.0, G, f.out);
-        if (ctx->world > 1) {
-            comm_allreduce_sum(ctx, G, (size_t)f.out * f.out);
-            vec_scale(ctx, (long)f.out * f.out, Ng, G);
-        }
-    }
+    const int l = li - m->cLayers;
+    const FC_LAYER &f = m->fcLayer[l];
+    const double *d = packed ? dbase + m->zztOffsets[m->cLayers + l + 1] : dbase + m->zOffsets[m->cLayers + l + 1];
+    double *G = lambdaG + info->LambdaGOffsets[m->cLayers + l];
+    dgemm(ctx, false, true, f.out, f.out, samples, ctx->world > 1 ? 1.0 : Ng, d, f.out, d, f.out, 0.0, G, f.out);
+    reduce_block(ctx, G, (long)f.out * f.out, Ng, root);
+}
+
+void lambda_delta_impl(fitre_context *ctx, const CNN_MODEL *m, const double *dbase, bool packed, int samples,
+                       double *lambdaG, const FITRE_KFAC_INFO *info, double *devPtr) {
+    for (int li = 0; li < m->cLayers + m->lLayers; ++li)
+        lambda_delta_layer(ctx, m, dbase, packed, samples, lambdaG, info, devPtr, li);
 }
 
 // theta <- m * theta + (1 - m) * update, in the reference's operation order
@@ -724,6 +728,7 @@ struct InvJob {
     int n;
     double cost;
     bool factor_only;  // Cholesky factor instead of the inverse
+    int layer;
 };
 std::vector<InvJob> inverse_jobs(const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const double *A,
                                  double *Ainv, const double *G, double *Ginv, bool chol) {
@@ -739,11 +744,34 @@ std::vector<InvJob> inverse_jobs(const CNN_MODEL *m, const FITRE_KFAC_INFO *info
             g = m->fcLayer[l - m->cLayers].out;
         }
         jobs.push_back({A + info->OmegaZOffsets[l], Ainv + info->OmegaZOffsets[l], a,
-                        (double)a * a * a / (chol ? 3.0 : 1.0), chol});
-        jobs.push_back({G + info->LambdaGOffsets[l], Ginv + info->LambdaGOffsets[l], g, (double)g * g * g, false});
+                        (double)a * a * a / (chol ? 3.0 : 1.0), chol, l});
+        jobs.push_back({G + info->LambdaGOffsets[l], Ginv + info->LambdaGOffsets[l], g, (double)g * g * g, false, l});
     }
     std::stable_sort(jobs.begin(), jobs.end(), [](const InvJob &x, const InvJob &y) { return x.cost > y.cost; });
     return jobs;
+}
+// FITRE_KFAC_LAYER_OWNED: which rank holds the factors of each layer and forms its slice of the
+// natural gradient (most expensive layer first onto the least loaded rank)
+std::vector<int> layer_owners(const CNN_MODEL *m, int world, bool chol) {
+    const int nl = m->cLayers + m->lLayers;
+    std::vector<double> cost(nl);
+    std::vector<int> order(nl), owner(nl, 0);
+    for (int l = 0; l < nl; ++l) {
+        const double a = l < m->cLayers ? (double)m->convLayer[l].inChannels * m->convLayer[l].kSize *
+                                              m->convLayer[l].kSize
+                                        : (double)m->fcLayer[l - m->cLayers].in;
+        const double g = l < m->cLayers ? m->convLayer[l].outChannels : m->fcLayer[l - m->cLayers].out;
+        cost[l] = a * a * a / (chol ? 3.0 : 1.0) + g * g * g + 2.0 * g * a * (a + g);
+        order[l] = l;
+    }
+    std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return cost[x] > cost[y]; });
+    std::vector<double> load(world, 0.0);
+    for (int l : order) {
+        const int r = (int)(std::min_element(load.begin(), load.end()) - load.begin());
+        load[r] += cost[l];
+        owner[l] = r;
+    }
+    return owner;
 }
 void ensure_side_streams(fitre_context *ctx) {
     if (ctx->inv_streams[0]) return;
@@ -932,7 +960,12 @@ extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MOD
     std::vector<InvJob> jobs = inverse_jobs(m, info, omegaZ, omegaZInv, lambdaG, lambdaGInv, chol);
     // with ranks: the same division of the factorisations as fitre_kfac_invert_factors
     std::vector<char> mine(jobs.size(), 1);
-    if (W > 1) {
+    const bool owned = W > 1 && ctx->kfac_owned;
+    std::vector<int> owner(nl, -1);  // -1: factors summed onto every rank
+    if (owned) {
+        owner = layer_owners(m, W, chol);
+        for (size_t i = 0; i < jobs.size(); ++i) mine[i] = owner[jobs[i].layer] == ctx->rank;
+    } else if (W > 1) {
         std::vector<double> load(W, 0.0);
         for (size_t i = 0; i < jobs.size(); ++i) {
             const int r = (int)(std::min_element(load.begin(), load.end()) - load.begin());
@@ -962,7 +995,7 @@ extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MOD
     auto body = [&] {
         cudaStream_t main_stream = ctx->stream;
         FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), main_stream));
-        if (W > 1) {
+        if (W > 1 && !owned) {
             vec_fill(ctx, info->OmegaZSize, 0.0, omegaZInv);
             vec_fill(ctx, info->LambdaGSize, 0.0, lambdaGInv);
         }
@@ -985,7 +1018,8 @@ extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MOD
             for (int s = 0; s < kSideStreams; ++s)
                 FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
             // G factors: a fraction of a millisecond in all; their inverses start at once
-            lambda_delta_impl(ctx, m, dbase, packed != 0, samples, lambdaG, info, devPtr);
+            for (int l = 0; l < nl; ++l)
+                lambda_delta_layer(ctx, m, dbase, packed != 0, samples, lambdaG, info, devPtr, l, owner[l]);
             FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
             for (size_t i = 0; i < jobs.size(); ++i)
                 if (mine[i] && jobs[i].src >= lambdaG && jobs[i].src < lambdaG + info->LambdaGSize)
@@ -999,7 +1033,7 @@ extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MOD
             };
             std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return block(x) > block(y); });
             for (int l : order) {
-                omega_z_layer(ctx, m, x0, zbase, packed != 0, samples, omegaZ, info, devPtr, l);
+                omega_z_layer(ctx, m, x0, zbase, packed != 0, samples, omegaZ, info, devPtr, l, owner[l]);
                 FITRE_CUDA(cudaEventRecord(ctx->layer_ev[l], main_stream));
                 for (size_t i = 0; i < jobs.size(); ++i)
                     if (mine[i] && jobs[i].src == omegaZ + info->OmegaZOffsets[l]) start_job(jobs[i], ctx->layer_ev[l]);
@@ -1016,8 +1050,10 @@ extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MOD
     if (W > 1) {
         // the per-layer all-reduces of the factors sit between the kernels: launched directly
         body();
-        comm_allreduce_sum(ctx, omegaZInv, info->OmegaZSize);
-        comm_allreduce_sum(ctx, lambdaGInv, info->LambdaGSize);
+        if (!owned) {
+            comm_allreduce_sum(ctx, omegaZInv, info->OmegaZSize);
+            comm_allreduce_sum(ctx, lambdaGInv, info->LambdaGSize);
+        }
         comm_allreduce_sum(ctx, ctx->dscal + 4002, 1);  // a failure on any rank is seen by all
     } else {
         run_graphed(ctx, ctx->graph_factors, key, body);
@@ -1060,8 +1096,12 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
         const bool chol = ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY;
         const long per = natural_gradient_layer_scratch(m);
         ensure_side_streams(ctx);
+        const bool owned = ctx->world > 1 && ctx->kfac_owned;
+        std::vector<int> owner;
+        if (owned) owner = layer_owners(m, ctx->world, chol);
         std::vector<long long> key = {ptr_key(omegaZInv), ptr_key(lambdaGInv), ptr_key(gradient), ptr_key(nGradient),
-                                      ptr_key(devPtr), ctx->kfac_solver, hasb, m->cLayers, m->lLayers};
+                                      ptr_key(devPtr), ctx->kfac_solver, hasb, m->cLayers, m->lLayers,
+                                      owned ? ctx->rank : -1, owned ? ctx->world : 1, m->pSize};
         for (int l = 0; l < m->cLayers + m->lLayers; ++l) {
             key.push_back(info->OmegaZOffsets[l]);
             key.push_back(info->LambdaGOffsets[l]);
@@ -1072,6 +1112,7 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
         }
         run_graphed(ctx, ctx->graph_natgrad, key, [&] {
         cudaStream_t main_stream = ctx->stream;
+        if (owned) vec_fill(ctx, m->pSize, 0.0, nGradient);  // the other ranks' slices arrive by the all-reduce
         FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
         for (int s = 0; s < kSideStreams; ++s) FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
         std::vector<double> sload(kSideStreams, 0.0);
@@ -1095,6 +1136,7 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
             }
             std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return cost[x] > cost[y]; });
             for (int li : order) {
+                if (owned && owner[li] != ctx->rank) continue;
                 double *work = pick_stream(cost[li]);
                 const double *Ai = omegaZInv + info->OmegaZOffsets[li];
                 const double *Gi = lambdaGInv + info->LambdaGOffsets[li];
@@ -1144,6 +1186,7 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
             FITRE_CUDA(cudaStreamWaitEvent(main_stream, ctx->inv_join[s], 0));
         }
         });
+        if (owned) comm_allreduce_sum(ctx, nGradient, (size_t)m->pSize);
         return FITRE_OK;
     } catch (const Error &e) {
         ctx->err = e.what();

@@ -474,6 +474,14 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
                   FITRE_ERR_BAD_ARG, "data set pointers missing");
     FITRE_RC(fitre_model_validate(m));
     FITRE_RC(fitre_kfac_storage_indices(m, kfacInfo));
+    // the factor and inverse buffers are the loop's own: with ranks each layer's factors stay on an
+    // owner rank and only the natural gradient is exchanged
+    struct OwnedFactors {
+        fitre_context *c;
+        int prev;
+        explicit OwnedFactors(fitre_context *ctx_) : c(ctx_), prev(ctx_->kfac_owned) { c->kfac_owned = 1; }
+        ~OwnedFactors() { c->kfac_owned = prev; }
+    } owned_factors(ctx);
     const TrLayout L = tr_layout(m, data, *kfacInfo);
     double *base = scratch->nextDevPtr;
     int *shuffle = (int *)(base + L.indices);

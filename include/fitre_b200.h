@@ -243,6 +243,21 @@ enum { FITRE_KFAC_SOLVER_INVERSE = 0, FITRE_KFAC_SOLVER_CHOLESKY = 1 };
 int fitre_set_kfac_solver(fitre_context *ctx, int solver);
 int fitre_get_kfac_solver(const fitre_context *ctx); /* the current setting; -1 without a context */
 
+/* Where the KFAC factors live when the context has a communicator (no effect on one GPU):
+ *   FITRE_KFAC_REPLICATED (default): every rank ends up with all global factors and all inverses
+ *     (factor blocks all-reduced, the factorisations divided among the ranks and exchanged).
+ *   FITRE_KFAC_LAYER_OWNED: every layer has an owner rank (most expensive layer first onto the
+ *     least loaded rank).  fitre_kfac_factors_and_inverses reduces each factor block onto its
+ *     owner only, which factorises it; nothing is sent back, so omegaZ / lambdaG and the inverse
+ *     slots of a layer are valid on its owner alone.  fitre_compute_natural_gradient forms each
+ *     layer's slice on the owner and one all-reduce of nGradient (pSize doubles) completes the
+ *     vector on every rank: the 2 x OmegaZSize doubles of factor traffic per step become about
+ *     half of one, and the natural-gradient work is divided as well.  Set it before both calls;
+ *     fitre_subsampled_trust_region_kfac uses it by itself.  The reference is single-GPU; its
+ *     dormant second-GPU thread (solvers/kfac_thread.cu:77-204) is the nearest counterpart. */
+enum { FITRE_KFAC_REPLICATED = 0, FITRE_KFAC_LAYER_OWNED = 1 };
+int fitre_set_kfac_distribution(fitre_context *ctx, int mode);
+
 /* 1 (default) = fitre_kfac_invert_factors and fitre_compute_natural_gradient, whose launch
  * sequences (a thousand small dependent kernels) are fixed by the model and the buffers, capture
  * that sequence into a CUDA graph on first use and replay it while pointers, sizes, damping and

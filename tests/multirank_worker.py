@@ -147,6 +147,28 @@ def main():
         Ai, Gi = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
         iscr = G.dev(np.zeros(_lib.load().fitre_kfac_invert_factors_mem_required(C.byref(model))))
         api.invertFactors(ctx, model, info, A, Ai, Gm, Gi, iscr)
+        # natural gradient three ways: replicated inverses; factors owned by one rank per layer
+        # (fused call, reduce onto the owner, only the natural gradient exchanged), explicit
+        # inverses and Cholesky form
+        L = _lib.load()
+        nscr = G.dev(np.zeros(max(L.fitre_kfac_natural_gradient_mem_required(C.byref(model)),
+                                  L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model)))))
+        ng_rep = G.dev(np.zeros(model.pSize))
+        api.computeNaturalGradient(ctx, model, info, Ai, Gi, run.ws.gradient, ng_rep, nscr)
+        ng_owned = {}
+        ctx.set_kfac_distribution(1)
+        for solver in (0, 1):
+            ctx.set_kfac_solver(solver)
+            A2, G2 = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+            Ai2, Gi2 = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+            api.computeFactorsAndInverses(ctx, model, run.data, run.ws.z, run.ws.dx, per, A2, Ai2, G2, Gi2,
+                                          info, nscr)
+            ng = G.dev(np.zeros(model.pSize))
+            api.computeNaturalGradient(ctx, model, info, Ai2, Gi2, run.ws.gradient, ng, nscr)
+            ng_owned[solver] = ng.cpu().numpy()
+        ctx.set_kfac_solver(0)
+        ctx.set_kfac_distribution(0)
+        ng_rep = ng_rep.cpu().numpy()
         # the same gradient and Hv in the compensated tensor-core mode (sharded batch-norm statistics
         # and all-reduces around the tcgen05 kernels)
         g64, loss64 = run.gradient.copy(), run.loss
@@ -157,7 +179,8 @@ def main():
         ctx.set_precision(0)
         np.savez(out, loss=loss64, gradient=g64, hv=hv, A=A.cpu().numpy(),
                  G=Gm.cpu().numpy(), Ainv=Ai.cpu().numpy(), Ginv=Gi.cpu().numpy(),
-                 gradient_x3=run3.gradient, hv_x3=hv3)
+                 gradient_x3=run3.gradient, hv_x3=hv3, ng_rep=ng_rep, ng_owned=ng_owned[0],
+                 ng_owned_chol=ng_owned[1])
         torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

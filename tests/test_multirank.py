@@ -105,6 +105,10 @@ def test_two_gpu_cuda_matches_full_batch(tmp_path, builder):
         assert rel(res["A"], A) < 1e-10 and rel(res["G"], G) < 1e-10
         # every rank holds every inverse although each computed only its share
         assert rel(res["Ainv"], Ainv) < 1e-8 and rel(res["Ginv"], Ginv) < 1e-8
+        # layer-owned factors (reduced onto one rank per layer, natural gradient all-reduced) give
+        # every rank the natural gradient of the replicated form, with inverses and with Cholesky solves
+        assert rel(res["ng_owned"], res["ng_rep"]) < 1e-9
+        assert rel(res["ng_owned_chol"], res["ng_rep"]) < 1e-8
         # 3xTF32 mode across ranks: stated tolerance 1e-3 against the fp64 full-batch result
         assert rel(res["gradient_x3"], g) < 1e-3 and rel(res["hv_x3"], hv) < 1e-3
 
