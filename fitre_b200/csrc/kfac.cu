@@ -988,9 +988,15 @@ extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MOD
         key.push_back(ptr_key(j.dst));
     }
     for (int l = 0; l < m->cLayers; ++l) {
-        key.push_back(m->zOffsets[l]);
         key.push_back(m->convLayer[l].height);
         key.push_back(m->convLayer[l].width);
+        key.push_back(m->convLayer[l].outputOffset);
+        key.push_back(m->convLayer[l].batchNormOffset);
+        key.push_back(m->convLayer[l].activationOffset);
+    }
+    for (int l = 0; l <= nl; ++l) {
+        key.push_back(m->zOffsets[l]);
+        key.push_back(m->zztOffsets[l]);
     }
     auto body = [&] {
         cudaStream_t main_stream = ctx->stream;
@@ -1106,6 +1112,7 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
             key.push_back(info->OmegaZOffsets[l]);
             key.push_back(info->LambdaGOffsets[l]);
             key.push_back(m->wOffsets[l]);
+            key.push_back(m->bOffsets[l]);
             key.push_back(l < m->cLayers ? m->convLayer[l].outChannels : m->fcLayer[l - m->cLayers].out);
             key.push_back(l < m->cLayers ? m->convLayer[l].inChannels * m->convLayer[l].kSize * m->convLayer[l].kSize
                                          : m->fcLayer[l - m->cLayers].in);
