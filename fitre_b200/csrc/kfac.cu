@@ -313,38 +313,23 @@ extern "C" int fitre_kfac_lambda_delta_damped(fitre_context *ctx, const CNN_MODE
 namespace {
 constexpr int NB = 64;
 
-// In place: A (nb x nb, lower, leading dim lda) <- its Cholesky factor L;
-// Linv (nb x nb, leading dim ldi, upper part zero) <- L^-1.  *fail is set to 1 + column on a pivot <= 0.
-// With Linv == nullptr the inverse is packed into the block itself: the strictly upper triangle
-// of A receives (L^-1)' (element (a, b), a < b, holds L^-1[b][a]; the diagonal of L^-1 is the
-// reciprocal of the diagonal of L), which is what trsm_small_kernel reads.
-__global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, int nb, double *Linv,
-                                                         long ldi, int *fail, int col0) {
-    // staging for the coalesced write-out: lower triangle L; strictly upper triangle (L^-1)'
-    // off-diagonal; xd: diagonal of L^-1
-    __shared__ double L[NB][NB + 1];
-    __shared__ double xd[NB];
-    __shared__ double lcol[2][NB], wrow[2][NB], piv[2];
-    const int tid = threadIdx.x, ty = tid & 15, tx = tid >> 4;
-    // Right-looking elimination with the block in registers: thread (ty, tx) owns the cyclic 4 x 4
-    // sub-tile rows ty + 16 i, columns tx + 16 jj of the block (a) and of W, which starts as the
-    // identity and receives the same row operations, so that W ends as L^-1.  One barrier per
-    // column: the owners publish column j of a, row j of W and the pivot unscaled, everybody
-    // forms 1/sqrt(pivot) for itself.
-    double a[4][4], w[4][4];
+// Right-looking elimination of a 64 x 64 block held in registers by 256 threads: thread (ty, tx)
+// owns the cyclic 4 x 4 sub-tile rows ty + 16 i, columns tx + 16 jj of the block (a) and of W, which
+// starts as the identity and receives the same row operations, so that a ends as L (lower part) and
+// W as L^-1.  One block barrier per column: the owners publish column j of a, row j of W and the
+// pivot unscaled, every thread forms 1/sqrt(pivot) for itself.  bad <- 1 + first column whose
+// pivot is not positive.
+__device__ __forceinline__ void chol64_eliminate(double (&a)[4][4], double (&w)[4][4], double (*lcol)[64],
+                                                 double (*wrow)[64], double *piv, int &bad, int ty, int tx) {
+    constexpr int NB = 64;
+    // jq (which of a thread's four rows / columns holds index j) is unrolled so that the register
+    // tiles are indexed statically; the sixteen columns of each group run as a loop, which keeps the
+    // code small enough to stay in the instruction cache
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-            const int r = ty + 16 * i, c = tx + 16 * jj;
-            a[i][jj] = (r < nb && c < nb) ? (r >= c ? A[(long)c * lda + r] : 0.0) : (r == c ? 1.0 : 0.0);
-            w[i][jj] = r == c ? 1.0 : 0.0;
-        }
-    }
-    int bad = 0;
-#pragma unroll
-    for (int j = 0; j < NB; ++j) {
-        const int jq = j >> 4, jr = j & 15, b = j & 1;
+    for (int jq = 0; jq < 4; ++jq)
+#pragma unroll 1
+    for (int jr = 0; jr < 16; ++jr) {
+        const int j = jq * 16 + jr, b = j & 1;
         if (tx == jr) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) lcol[b][ty + 16 * i] = a[i][jq];
@@ -384,6 +369,33 @@ __global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, in
             }
         }
     }
+}
+
+// In place: A (nb x nb, lower, leading dim lda) <- its Cholesky factor L;
+// Linv (nb x nb, leading dim ldi, upper part zero) <- L^-1.  *fail is set to 1 + column on a pivot <= 0.
+// With Linv == nullptr the inverse is packed into the block itself: the strictly upper triangle
+// of A receives (L^-1)' (element (a, b), a < b, holds L^-1[b][a]; the diagonal of L^-1 is the
+// reciprocal of the diagonal of L), which is what trsm_small_kernel reads.
+__global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, int nb, double *Linv,
+                                                         long ldi, int *fail, int col0) {
+    // staging for the coalesced write-out: lower triangle L; strictly upper triangle (L^-1)'
+    // off-diagonal; xd: diagonal of L^-1
+    __shared__ double L[NB][NB + 1];
+    __shared__ double xd[NB];
+    __shared__ double lcol[2][NB], wrow[2][NB], piv[2];
+    const int tid = threadIdx.x, ty = tid & 15, tx = tid >> 4;
+    double a[4][4], w[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int r = ty + 16 * i, c = tx + 16 * jj;
+            a[i][jj] = (r < nb && c < nb) ? (r >= c ? A[(long)c * lda + r] : 0.0) : (r == c ? 1.0 : 0.0);
+            w[i][jj] = r == c ? 1.0 : 0.0;
+        }
+    }
+    int bad = 0;
+    chol64_eliminate(a, w, lcol, wrow, piv, bad, ty, tx);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
 #pragma unroll
@@ -405,6 +417,118 @@ __global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, in
         if (Linv && r < nb && c < nb) Linv[(long)c * ldi + r] = (r == c) ? xd[c] : (r > c ? L[c][r] : 0.0);
     }
     if (tid == 0 && bad) atomicCAS(fail, 0, col0 + bad);
+}
+
+// Two 64 x 64 leaves, the solve and the update between them in one launch (packed form only):
+// A (n x n, 64 < n <= 128, lower, leading dim lda) <- L, the upper triangles of its two diagonal
+// blocks <- their packed inverses.  The block lives in shared memory (S, row stride 129); the two
+// eliminations run in registers as in chol_block_kernel, L21 = A21 L11^-T and A22 -= L21 L21' as
+// 64 x 64 x 64 products with 16 results per thread.  Replaces four dependent launches.
+constexpr int CH2 = 2 * NB, CH2_LD = CH2 + 1;
+constexpr int CH2_SMEM = (CH2 * CH2_LD + NB + 4 * NB + 2) * (int)sizeof(double);
+
+__global__ void __launch_bounds__(256) chol128_kernel(double *A, long lda, int n, int *fail, int col0) {
+    extern __shared__ __align__(16) double ch_sm[];
+    double (*S)[CH2_LD] = reinterpret_cast<double (*)[CH2_LD]>(ch_sm);
+    double *xd = ch_sm + CH2 * CH2_LD;                                   // diagonal of L11^-1
+    double (*lcol)[NB] = reinterpret_cast<double (*)[NB]>(xd + NB);      // [2][64]
+    double (*wrow)[NB] = reinterpret_cast<double (*)[NB]>(xd + 3 * NB);  // [2][64]
+    double *piv = xd + 5 * NB;                                           // [2]
+    const int tid = threadIdx.x, ty = tid & 15, tx = tid >> 4;
+    // lower triangle in, identity outside a ragged block
+    for (int e = tid; e < CH2 * CH2; e += 256) {
+        const int r = e % CH2, c = e / CH2;
+        S[r][c] = (r < n && c < n) ? (r >= c ? A[(long)c * lda + r] : 0.0) : (r == c ? 1.0 : 0.0);
+    }
+    __syncthreads();
+    int bad_all = 0;
+    double a[4][4], w[4][4];
+    for (int blk = 0; blk < 2; ++blk) {
+        const int o = blk * NB;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int r = ty + 16 * i, c = tx + 16 * jj;
+                a[i][jj] = r >= c ? S[o + r][o + c] : 0.0;
+                w[i][jj] = r == c ? 1.0 : 0.0;
+            }
+        int bad = 0;
+        chol64_eliminate(a, w, lcol, wrow, piv, bad, ty, tx);
+        if (bad && !bad_all) bad_all = o + bad;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int r = ty + 16 * i, c = tx + 16 * jj;
+                if (r > c) {
+                    S[o + r][o + c] = a[i][jj];
+                    S[o + c][o + r] = w[i][jj];  // packed inverse: (row c, col r) holds L^-1[r][c]
+                } else if (r == c) {
+                    S[o + r][o + r] = a[i][jj];
+                    if (blk == 0) xd[r] = w[i][jj];
+                }
+            }
+        __syncthreads();
+        if (blk == 1) break;
+        // L21 = A21 W11', W11 = L11^-1 lower: L21[r][c] = sum_{k <= c} A21[r][k] W11[c][k]
+        double acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0;
+        for (int k = 0; k < NB; ++k) {
+            double av[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = S[NB + ty + 16 * i][k];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int c = tx + 16 * jj;
+                wv[jj] = k < c ? S[k][c] : (k == c ? xd[c] : 0.0);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) acc[i][jj] += av[i] * wv[jj];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) S[NB + ty + 16 * i][tx + 16 * jj] = acc[i][jj];
+        __syncthreads();
+        // A22 -= L21 L21' (the lower triangle is what the second elimination reads)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0;
+        for (int k = 0; k < NB; ++k) {
+            double av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = S[NB + ty + 16 * i][k];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) bv[jj] = S[NB + tx + 16 * jj][k];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) acc[i][jj] += av[i] * bv[jj];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int r = ty + 16 * i, c = tx + 16 * jj;
+                if (r >= c) S[NB + r][NB + c] -= acc[i][jj];
+            }
+        __syncthreads();
+    }
+    // out: everything at or below the diagonal, and the upper triangles of the two diagonal blocks
+    for (int e = tid; e < CH2 * CH2; e += 256) {
+        const int r = e % CH2, c = e / CH2;
+        if (r < n && c < n && (r >= c || r / NB == c / NB)) A[(long)c * lda + r] = S[r][c];
+    }
+    if (tid == 0 && bad_all) atomicCAS(fail, 0, col0 + bad_all);
 }
 
 __global__ void add_diagonal_kernel(double *A, int n, double v) {
@@ -621,6 +745,11 @@ void chol_factor(fitre_context *ctx, double *A, long ld, int n, int col0, int *f
         check_launch(ctx, "chol_block_kernel");
         return;
     }
+    if (n <= CH2) {
+        chol128_kernel<<<1, 256, CH2_SMEM, ctx->stream>>>(A, ld, n, fail, col0);
+        check_launch(ctx, "chol128_kernel");
+        return;
+    }
     const int n1 = ((n / 2 + NB - 1) / NB) * NB, n2 = n - n1;
     double *A21 = A + n1, *A22 = A + (long)n1 * ld + n1;
     chol_factor(ctx, A, ld, n1, col0, fail);
@@ -667,6 +796,7 @@ void check_fail_word(fitre_context *ctx, int *fail) {
 
 namespace fitre {
 void kfac_init_attributes() {
+    FITRE_CUDA(cudaFuncSetAttribute(chol128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CH2_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(trsm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM));
 }
 }  // namespace fitre
