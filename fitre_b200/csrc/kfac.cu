@@ -424,17 +424,26 @@ __global__ void __launch_bounds__(256) chol_block_kernel(double *A, long lda, in
 // blocks <- their packed inverses.  The block lives in shared memory (S, row stride 129); the two
 // eliminations run in registers as in chol_block_kernel, L21 = A21 L11^-T and A22 -= L21 L21' as
 // 64 x 64 x 64 products with 16 results per thread.  Replaces four dependent launches.
-constexpr int CH2 = 2 * NB, CH2_LD = CH2 + 1;
-constexpr int CH2_SMEM = (CH2 * CH2_LD + NB + 4 * NB + 2) * (int)sizeof(double);
+// D (8 x 8, two entries per lane) += A (8 x 4) B (4 x 8) on the fp64 tensor cores
+__device__ __forceinline__ void dmma_f64(double &c0, double &c1, double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
+                 : "+d"(c0), "+d"(c1)
+                 : "d"(a), "d"(b));
+}
+constexpr int CH2 = 2 * NB, CH2_LD = CH2 + 4, CHW_LD = NB + 4;  // strides = 4 mod 16: DMMA fragments conflict-free
+constexpr int CH2_SMEM = (CH2 * CH2_LD + NB * CHW_LD + 4 * NB + 2) * (int)sizeof(double);
 
 __global__ void __launch_bounds__(256) chol128_kernel(double *A, long lda, int n, int *fail, int col0) {
     extern __shared__ __align__(16) double ch_sm[];
     double (*S)[CH2_LD] = reinterpret_cast<double (*)[CH2_LD]>(ch_sm);
-    double *xd = ch_sm + CH2 * CH2_LD;                                   // diagonal of L11^-1
-    double (*lcol)[NB] = reinterpret_cast<double (*)[NB]>(xd + NB);      // [2][64]
-    double (*wrow)[NB] = reinterpret_cast<double (*)[NB]>(xd + 3 * NB);  // [2][64]
-    double *piv = xd + 5 * NB;                                           // [2]
+    double (*Wb)[CHW_LD] = reinterpret_cast<double (*)[CHW_LD]>(ch_sm + CH2 * CH2_LD);  // Wb[k][c] = L11^-1[c][k]
+    double *aux = ch_sm + CH2 * CH2_LD + NB * CHW_LD;
+    double (*lcol)[NB] = reinterpret_cast<double (*)[NB]>(aux);           // [2][64]
+    double (*wrow)[NB] = reinterpret_cast<double (*)[NB]>(aux + 2 * NB);  // [2][64]
+    double *piv = aux + 4 * NB;                                           // [2]
     const int tid = threadIdx.x, ty = tid & 15, tx = tid >> 4;
+    const int lane = tid & 31, warp = tid >> 5, lr = lane >> 2, lc = lane & 3;
+    const int warp_m = warp & 1, warp_n = warp >> 1;  // 64 x 64 products: warp tile 32 x 16
     // lower triangle in, identity outside a ragged block
     for (int e = tid; e < CH2 * CH2; e += 256) {
         const int r = e % CH2, c = e / CH2;
@@ -467,61 +476,47 @@ __global__ void __launch_bounds__(256) chol128_kernel(double *A, long lda, int n
                     S[o + c][o + r] = w[i][jj];  // packed inverse: (row c, col r) holds L^-1[r][c]
                 } else if (r == c) {
                     S[o + r][o + r] = a[i][jj];
-                    if (blk == 0) xd[r] = w[i][jj];
                 }
+                if (blk == 0) Wb[c][r] = w[i][jj];  // all of L11^-1 (zero above its diagonal), transposed
             }
         __syncthreads();
         if (blk == 1) break;
-        // L21 = A21 W11', W11 = L11^-1 lower: L21[r][c] = sum_{k <= c} A21[r][k] W11[c][k]
-        double acc[4][4];
+        // L21 = A21 L11^-T and then A22 -= L21 L21', each a 64 x 64 x 64 product on the fp64 tensor cores
+        for (int pass = 0; pass < 2; ++pass) {
+            double acc[4][2][2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+            for (int mi = 0; mi < 4; ++mi)
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0;
-        for (int k = 0; k < NB; ++k) {
-            double av[4], wv[4];
+                for (int ni = 0; ni < 2; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = 0.0;
+#pragma unroll 4
+            for (int k4 = 0; k4 < NB / 4; ++k4) {
+                const int k = k4 * 4 + lc;
+                double fa[4], fb[2];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) av[i] = S[NB + ty + 16 * i][k];
+                for (int mi = 0; mi < 4; ++mi) fa[mi] = S[NB + warp_m * 32 + mi * 8 + lr][k];
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const int c = tx + 16 * jj;
-                wv[jj] = k < c ? S[k][c] : (k == c ? xd[c] : 0.0);
+                for (int ni = 0; ni < 2; ++ni) {
+                    const int c = warp_n * 16 + ni * 8 + lr;
+                    fb[ni] = pass == 0 ? Wb[k][c] : S[NB + c][k];
+                }
+#pragma unroll
+                for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                    for (int ni = 0; ni < 2; ++ni) dmma_f64(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
             }
+            __syncthreads();  // every read of A21 / L21 is done
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int mi = 0; mi < 4; ++mi)
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) acc[i][jj] += av[i] * wv[jj];
+                for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int r = warp_m * 32 + mi * 8 + lr, c = warp_n * 16 + ni * 8 + 2 * lc + e;
+                        if (pass == 0) S[NB + r][c] = acc[mi][ni][e];
+                        else if (r >= c) S[NB + r][NB + c] -= acc[mi][ni][e];
+                    }
+            __syncthreads();
         }
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) S[NB + ty + 16 * i][tx + 16 * jj] = acc[i][jj];
-        __syncthreads();
-        // A22 -= L21 L21' (the lower triangle is what the second elimination reads)
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0;
-        for (int k = 0; k < NB; ++k) {
-            double av[4], bv[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) av[i] = S[NB + ty + 16 * i][k];
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) bv[jj] = S[NB + tx + 16 * jj][k];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) acc[i][jj] += av[i] * bv[jj];
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const int r = ty + 16 * i, c = tx + 16 * jj;
-                if (r >= c) S[NB + r][NB + c] -= acc[i][jj];
-            }
-        __syncthreads();
     }
     // out: everything at or below the diagonal, and the upper triangles of the two diagonal blocks
     for (int e = tid; e < CH2 * CH2; e += 256) {
