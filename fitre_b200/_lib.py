@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libfitre_b200.so")
 # every symbol include/fitre_b200.h declares
 SYMBOLS = [
     "fitre_context_create", "fitre_context_destroy", "fitre_last_error", "fitre_launch_count",
-    "fitre_set_reference_softmax", "fitre_set_precision", "fitre_set_kfac_solver", "fitre_set_kfac_distribution", "fitre_get_kfac_solver", "fitre_kfac_matrix_factor", "fitre_set_graphs", "fitre_set_tma", "fitre_profile_enable", "fitre_profile_read",
+    "fitre_set_reference_softmax", "fitre_set_reference_quadratic_damping", "fitre_kernel_launches", "fitre_set_precision", "fitre_set_kfac_solver", "fitre_set_kfac_distribution", "fitre_get_kfac_solver", "fitre_kfac_matrix_factor", "fitre_set_graphs", "fitre_set_tma", "fitre_profile_enable", "fitre_profile_read",
     "fitre_comm_unique_id", "fitre_comm_init", "fitre_comm_world",
     "fitre_read_lenet_cnn", "fitre_read_alexnet_cnn", "fitre_read_vgg11", "fitre_read_test_vgg",
     "fitre_model_finalize", "fitre_model_validate",
@@ -65,6 +65,8 @@ def load():
     sig("fitre_last_error", C.c_char_p, vp)
     sig("fitre_launch_count", C.c_longlong, vp)
     sig("fitre_set_reference_softmax", i, vp, i)
+    sig("fitre_set_reference_quadratic_damping", i, vp, i)
+    sig("fitre_kernel_launches", C.c_longlong, vp, C.c_char_p)
     sig("fitre_set_precision", i, vp, i)
     sig("fitre_set_kfac_solver", i, vp, i)
     sig("fitre_set_graphs", i, vp, i)

@@ -71,6 +71,15 @@ class Context:
     def set_reference_softmax(self, on):
         self.check(self.lib.fitre_set_reference_softmax(self.h, int(bool(on))))
 
+    def set_reference_quadratic_damping(self, on):
+        """1 (default): computeQuadraticModel adds weightDecay * weights to Hv as the C reference
+        does (functions/model_reduction.cu:50-52); 0: weightDecay * vector (pytorch/peng/utils.py:77)."""
+        self.check(self.lib.fitre_set_reference_quadratic_damping(self.h, int(bool(on))))
+
+    def kernel_launches(self, name):
+        """Launches issued so far of the kernel called `name` (e.g. "conv_tma_kernel")."""
+        return int(self.lib.fitre_kernel_launches(self.h, name.encode()))
+
     def set_precision(self, precision):
         """0 = fp64 (reference arithmetic); opt-in tcgen05 modes for the convolution products:
         1 = one TF32 product (loss within 1e-3, deep-net gradients only within 1e-1),

@@ -151,6 +151,20 @@ int fitre_set_reference_softmax(fitre_context *ctx, int on) {
     return FITRE_OK;
 }
 
+int fitre_set_reference_quadratic_damping(fitre_context *ctx, int on) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    ctx->ref_quadratic = on ? 1 : 0;
+    return FITRE_OK;
+}
+
+long long fitre_kernel_launches(const fitre_context *ctx, const char *name) {
+    if (!ctx || !name) return -1;
+    long long n = 0;
+    for (const auto &r : ctx->launch_names)
+        if (std::strcmp(r.first, name) == 0) n += r.second;
+    return n;
+}
+
 int fitre_set_precision(fitre_context *ctx, int precision) {
     if (!ctx || (precision != FITRE_PRECISION_FP64 && precision != FITRE_PRECISION_TF32 &&
                  precision != FITRE_PRECISION_TF32X3 && precision != FITRE_PRECISION_FP64_I8))
@@ -338,12 +352,14 @@ int fitre_cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *d
         require_ptrs({m, data, z, probs, lossFuncErrors, dx, vector, hv, devPtr});
         model_check_batch(m, curBatchSize);
         cnn_hv(ctx, m, data, z, probs, lossFuncErrors, dx, vector, hv, curBatchSize, devPtr);
+        check_device_error(ctx);
     });
 }
 
-// functions/model_reduction.cu:20-93.  The damping term is weightDecay * vector (what the
-// reference's PyTorch twin adds, pytorch/peng/utils.py:77); the C reference adds
-// weightDecay * weights (model_reduction.cu:50-52); both vanish at weightDecay == 0.
+// functions/model_reduction.cu:20-93.  The damping term added to Hv is weightDecay * weights as
+// in the C reference (model_reduction.cu:50-52) or, with fitre_set_reference_quadratic_damping(0),
+// weightDecay * vector (what the reference's PyTorch twin adds, pytorch/peng/utils.py:77); both
+// vanish at weightDecay == 0.
 long fitre_quadratic_model_mem_required(const CNN_MODEL *m) {
     if (!m) return -1;
     return align32(m->pSize) + fitre_cnn_hv_mem_required(m);
@@ -362,9 +378,10 @@ int fitre_compute_quadratic_model(fitre_context *ctx, const CNN_MODEL *m,
         double *hv = devPtr;
         double *next = hv + align32(P);
         cnn_hv(ctx, m, data, z, probs, lossFuncErrors, dx, vector, hv, curBatchSize, next);
-        vec_axpy(ctx, P, weightDecay, vector, hv);
+        vec_axpy(ctx, P, weightDecay, ctx->ref_quadratic ? data->weights : vector, hv);
         double d[3];
         vec_dots(ctx, P, hv, vector, vector, vector, gradient, vector, d);
+        check_device_error(ctx);
         const double vHv = d[0], nrm = std::sqrt(d[1]), gv = d[2];
         double alpha, val;
         if (vHv < 0) {
@@ -449,6 +466,7 @@ int fitre_cg_steihaug(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
         cnn_hv(ctx, m, data, z, probs, lossFuncErrors, dx, p, Hd, curBatchSize, ws);
         ++hvc;
         vec_dots(ctx, P, Hd, p, p, gradient, p, p, d);
+        check_device_error(ctx);
         prm->modelValue = 0.5 * d[0] + d[1] + 0.5 * wd * d[2];
         prm->iterations = it + 1;
         prm->flag = flag;

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <stdexcept>
+#include <cstring>
 #include <string>
 #include <utility>
 #include <vector>
@@ -47,6 +48,7 @@ struct fitre_context {
     long long launches = 0;
     std::string err;
     int ref_softmax = 1;
+    int ref_quadratic = 1;      // quadratic model damps with lambda * weights (reference) or lambda * vector
     int precision = 0;          // FITRE_PRECISION_* (convolution products)
     int kfac_solver = 0;        // FITRE_KFAC_SOLVER_* (what the A-factor slots hold)
     int kfac_owned = 0;         // FITRE_KFAC_LAYER_OWNED: with ranks, each layer's factors live on one rank
@@ -90,6 +92,9 @@ struct fitre_context {
     struct ProfRec { cudaEvent_t beg, end; int kind; double flops; };
     std::vector<ProfRec> prof;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_pool;
+    // launches per kernel name (the literal handed to check_launch; a name may appear under
+    // several pointers, one per translation unit), read by fitre_kernel_launches
+    std::vector<std::pair<const char *, long long>> launch_names;
 };
 
 namespace fitre {
@@ -102,6 +107,12 @@ inline void check_launch(fitre_context *ctx, const char *name) {
     if (e != cudaSuccess)
         throw Error(FITRE_ERR_CUDA, std::string("launch of ") + name + ": " + cudaGetErrorString(e));
     ctx->launches += 1;
+    for (auto &r : ctx->launch_names)
+        if (r.first == name) {
+            r.second += 1;
+            return;
+        }
+    ctx->launch_names.emplace_back(name, 1);
 }
 
 // Kernel classes the optional event timing distinguishes.

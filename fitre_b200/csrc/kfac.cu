@@ -211,6 +211,7 @@ extern "C" int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m, const 
     FITRE_REQUIRE(m && data && z && omegaZ && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
     model_check_batch(m, samples);
     omega_z_impl(ctx, m, data->currentBatch, z, false, samples, omegaZ, info, devPtr);
+    check_device_error(ctx);  // the TMA-fed A-factor kernel has bounded waits
     KFAC_ENTRY_END
 }
 
@@ -781,7 +782,7 @@ void invert_spd(fitre_context *ctx, const double *matrix, double *inverse, int n
 
 void check_fail_word(fitre_context *ctx, int *fail) {
     FITRE_CUDA(cudaMemcpyAsync(ctx->pinned + 202, fail, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
-    FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+    check_device_error(ctx);  // synchronises the stream; also reports a TMA wait that ran out
     int f;
     std::memcpy(&f, ctx->pinned + 202, sizeof(int));
     FITRE_REQUIRE(f == 0, FITRE_ERR_NOT_CONVERGED,

@@ -201,6 +201,18 @@ long long fitre_launch_count(const fitre_context *ctx);
 /* 1 = replicate the reference's softmax quirks (max-shift starts at 0 and
  * probs += 1e-10: functions/softmax_loss.cu:24-27,55); 0 = textbook softmax. Default 1. */
 int fitre_set_reference_softmax(fitre_context *ctx, int on);
+/* Term that fitre_compute_quadratic_model adds to the Hessian-vector product when weightDecay
+ * is non-zero: 1 (default) = weightDecay * data->weights, as the C reference does
+ * (functions/model_reduction.cu:50-52); 0 = weightDecay * vector, the curvature of the L2 term,
+ * as the reference's PyTorch twin does (pytorch/peng/utils.py:77).  The trust-region loop
+ * (fitre_subsampled_trust_region_kfac) follows the setting. */
+int fitre_set_reference_quadratic_damping(fitre_context *ctx, int on);
+/* Number of launches the host has issued through `ctx` of the kernel called `name` (the
+ * __global__ function's name without template arguments, e.g. "conv_tma_kernel"); launches
+ * replayed from a captured CUDA graph are counted once, at capture.  -1 on a NULL argument.
+ * Lets a caller or a test see which kernel variant a shape was routed to.  No counterpart in
+ * the reference. */
+long long fitre_kernel_launches(const fitre_context *ctx, const char *name);
 
 /* Arithmetic of the convolution products: forward, data gradient, weight gradient and their
  * R-operator forms.  FITRE_PRECISION_FP64 (default) is the reference's arithmetic.  The two other

@@ -50,6 +50,7 @@ void ora_env_default(ORA_ENV *env) {
     env->user = NULL;
     env->eval_type = FITRE_MODEL_TRAIN;
     env->rank = 0;
+    env->ref_quadratic = 1;
 }
 
 static void env_allreduce(const ORA_ENV *env, double *buf, long n) {
@@ -1217,8 +1218,9 @@ void ora_cnn_hv(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
     free(rError);
 }
 
-/* functions/model_reduction.cu:20-93; the weight-decay term is weightDecay * vector
- * (the PyTorch twin pytorch/peng/utils.py:77), identical to the reference at weightDecay 0. */
+/* functions/model_reduction.cu:20-93.  The term added to Hv is weightDecay * weights as the C
+ * reference has it (:50-52) when env->ref_quadratic is set (NULL env: set), else
+ * weightDecay * vector (the PyTorch twin, pytorch/peng/utils.py:77). */
 double ora_quadratic_model(const ORA_ENV *env, const CNN_MODEL *m, const double *batch,
                            const double *weights, int numClasses, const double *z,
                            const double *probs, const double *errors, const double *dx,
@@ -1227,7 +1229,7 @@ double ora_quadratic_model(const ORA_ENV *env, const CNN_MODEL *m, const double 
     long P = m->pSize;
     double *hv = xmalloc(P), *rz = xmalloc(m->zSize);
     ora_cnn_hv(env, m, batch, weights, numClasses, z, probs, errors, dx, vector, hv, rz, n);
-    axpy(P, weightDecay, vector, hv);
+    axpy(P, weightDecay, (!env || env->ref_quadratic) ? weights : vector, hv);
     double vHv = dot(P, hv, vector);
     double nrm = sqrt(dot(P, vector, vector));
     double gv = dot(P, gradient, vector);

@@ -30,6 +30,9 @@ typedef struct ora_env {
                              * statistics (functions/dev_batch_norm.cu:331-393) */
     int rank;               /* this rank's index among `world` (outer loop: which slice of each
                              * global minibatch it assembles) */
+    int ref_quadratic;      /* 1: the quadratic model adds weightDecay * weights to Hv
+                             * (functions/model_reduction.cu:50-52); 0: weightDecay * vector
+                             * (pytorch/peng/utils.py:77) */
 } ORA_ENV;
 
 void ora_env_default(ORA_ENV *env);

@@ -21,7 +21,7 @@ ALLREDUCE_FN = C.CFUNCTYPE(None, C.POINTER(C.c_double), C.c_long, C.c_void_p)
 class ORA_ENV(C.Structure):
     _fields_ = [("ref_softmax", C.c_int), ("world", C.c_int),
                 ("allreduce", ALLREDUCE_FN), ("user", C.c_void_p), ("eval_type", C.c_int),
-                ("rank", C.c_int)]
+                ("rank", C.c_int), ("ref_quadratic", C.c_int)]
 
 
 def lib():
@@ -56,6 +56,8 @@ def lib():
         L.ora_natural_gradient.argtypes = [MP, C.POINTER(S.KFAC_INFO), dp, dp, dp, dp]
         L.ora_cnn_backward.argtypes = [EP, MP, dp, dp, dp, dp, dp, dp, i]
         L.ora_distribution_errors.argtypes = [EP, dp, dp, i, i, dp, dp]
+        L.ora_softmax_loss.argtypes = [EP, dp, dp, i, i, dp]
+        L.ora_softmax_loss.restype = d
         L.ora_im2col.argtypes = [dp, i, i, i, i, i, i, i, dp]
         L.ora_im2col_index.argtypes = [i, i, i, i, i, i, i,
                                        np.ctypeslib.ndpointer(dtype=np.int64, flags="C_CONTIGUOUS")]
@@ -92,9 +94,10 @@ def lib():
     return _LIB
 
 
-def make_env(ref_softmax=1, world=1, allreduce=None, eval_type=10, rank=0):
+def make_env(ref_softmax=1, world=1, allreduce=None, eval_type=10, rank=0, ref_quadratic=1):
     env = ORA_ENV()
     env.rank = int(rank)
+    env.ref_quadratic = int(ref_quadratic)
     env.ref_softmax, env.world = int(ref_softmax), int(world)
     env.eval_type = int(eval_type)
     if allreduce is not None:

@@ -1,0 +1,236 @@
+"""GPU parity at the sizes the benchmark configurations state: the CUDA library (through the C
+ABI) against the CPU oracle on the same seeded inputs, so that the tilings, split counts and
+kernel variants the library picks at those batch sizes are the ones compared.
+
+  LeNet, 256 images: gradient, Hessian-vector product, 10 Steihaug-CG iterations;
+  AlexNet with batch norm, 1024 images: gradient + Hessian-vector product;
+  VGG-11 with batch norm, 512 images (the per-GPU shape of the 4096-image configuration):
+    gradient + Hessian-vector product, the whole stored forward and backward state;
+  KFAC step on VGG-11 with batch norm, 256 images (the per-GPU shape of the 2048-image
+    configuration), lambda = 1e-3: sampled labels, A and G factors, damped factorisations,
+    natural gradient.
+
+Tolerance 1e-10 relative, norm-wise and max-wise (fp64); integer artefacts (sampled labels,
+CG exit flags and iteration counts) identical."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import nets
+import oracle_lib as O
+from fitre_b200 import _structs as S
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-10
+
+
+def _state_mismatch(model, n, got, want, what):
+    """Compares a z-shaped state vector layer by layer; returns a list of
+    (layer, slot, max-wise relative error, number of differing entries) for slots beyond TOL."""
+    import gpu_util as G
+    bad = []
+    for l in range(model.cLayers):
+        c = model.convLayer[l]
+        V = c.convVolumn * n
+        b = model.zOffsets[l + 1]
+        slots = {"conv": 0, "act": c.activationOffset}
+        if c.batchNorm != S.NO_BATCH_NORM:
+            slots["bn"] = c.batchNormOffset
+        if what == "z" and c.poolOffset > 0 and c.outputOffset == c.poolOffset:
+            slots["pool"] = c.poolOffset
+        for name, off in slots.items():
+            size = V if name != "pool" else c.poolVolumn * n
+            a, r = got[b + off:b + off + size], want[b + off:b + off + size]
+            e = G.relmax(a, r)
+            if not e < TOL:
+                scale = np.max(np.abs(r))
+                bad.append((l, name, e, int(np.count_nonzero(np.abs(a - r) > TOL * scale))))
+    return bad
+
+
+def _cond_bound(F, lam):
+    """Upper bound of the condition number of F = S + lam I with S positive semi-definite:
+    (largest eigenvalue by power iteration, with a margin) / lam."""
+    v = np.ones(F.shape[0]) / np.sqrt(F.shape[0])
+    top = 0.0
+    for _ in range(40):
+        u = F @ v
+        top = np.linalg.norm(u)
+        v = u / top
+    return 1.05 * top / lam
+
+
+def _check_grad_hv(model, n, seed, with_state=False, weight_decay=0.0):
+    import gpu_util as G
+    O.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=seed)
+    st = O.gradient(model, x, y, w, ncls, n, weight_decay=weight_decay)
+    hv_o = O.hv(model, x, w, ncls, n, st, v)
+    run = G.GpuRun(model, x, y, w, ncls, ref_softmax=1, weight_decay=weight_decay)
+    assert abs(run.loss - st.loss) <= TOL * abs(st.loss)
+    assert G.rel(run.gradient, st.gradient) < TOL
+    assert G.relmax(run.gradient, st.gradient) < TOL
+    hv = run.hv(v)
+    assert G.rel(hv, hv_o) < TOL
+    assert G.relmax(hv, hv_o) < TOL
+    if with_state:
+        z = run.ws.z.cpu().numpy()
+        assert _state_mismatch(model, n, z, st.z, "z") == []
+        del z
+        dx = run.ws.dx.cpu().numpy()
+        assert _state_mismatch(model, n, dx, st.dx, "dx") == []
+        del dx
+    return run, st, (x, y, w, v, ncls)
+
+
+@pytest.mark.parametrize("kwargs", [dict(act=S.CNN_ACT_RELU, pool=S.MAX_POOL), dict()],
+                         ids=["relu-maxpool", "swish-avgpool"])
+def test_lenet_256_gradient_hv_and_cg10(kwargs):
+    """LeNet on 256 images of 3x32x32 with bias: gradient, Hessian-vector product and 10
+    Steihaug-CG iterations in a trust region wide enough that no boundary exit occurs.  ReLU + max
+    pooling is the benchmark's statement of the net, Swish + average pooling the reference
+    builder's (nn/read_nn.c:500-725)."""
+    import gpu_util as G
+    from fitre_b200 import api
+    n = 256
+    model = nets.lenet(n, **kwargs)
+    run, st, (x, y, w, v, ncls) = _check_grad_hv(model, n, seed=1234, with_state=True, weight_decay=1e-3)
+    assert model.pSize == 62006
+    prm_o, prm_g = S.CG_PARAMS(), S.CG_PARAMS()
+    for prm in (prm_o, prm_g):
+        prm.delta, prm.tolerance, prm.maxIterations, prm.weightDecay = 1e3, 1e-30, 10, 1e-3
+    p_o = np.zeros(model.pSize)
+    env = O.make_env()
+    O.lib().ora_cg_steihaug(C.byref(env), C.byref(model), x, w, ncls, st.z, st.probs, st.errors, st.dx,
+                            st.gradient, p_o, n, C.byref(prm_o))
+    ws = run.ws
+    p = G.dev(np.zeros(model.pSize))
+    api.cgSteihaug(run.c, model, run.data, ws.z, ws.probs, ws.errors, ws.dx, ws.gradient, p, n, ws.dev, prm_g)
+    assert (prm_g.flag, prm_g.iterations, prm_g.hvCalls) == (prm_o.flag, prm_o.iterations, prm_o.hvCalls)
+    assert prm_g.iterations == 10
+    # ten conjugate-gradient steps amplify the 1e-15 differences of the products
+    assert G.rel(p.cpu().numpy(), p_o) < 1e-8
+    assert abs(prm_g.modelValue - prm_o.modelValue) <= 1e-9 * abs(prm_o.modelValue)
+
+
+def test_alexnet_bn_1024_gradient_hv():
+    """AlexNet-style net with batch norm, 1024 images: 5x5 convolutions with K = 75 and 1600,
+    3/2/1 max pooling (overlapping windows), FC 4096-384-192-10."""
+    model = nets.alexnet(1024)
+    run, _, _ = _check_grad_hv(model, 1024, seed=2234)
+    assert run.c.kernel_launches("conv_tma_kernel") > 0
+
+
+def test_vgg11_bn_512_gradient_hv_and_state():
+    """The benchmark shape: VGG-11 with batch norm, 512 images.  Every stored tensor of the forward
+    pass (z) and of the backward pass (dx) is compared as well, which includes the arg-max routing
+    of 16.9 M pooling windows; the TMA-fed kernels must be the ones that ran."""
+    import gpu_util as G
+    c = G.ctx()
+    before = {k: c.kernel_launches(k) for k in ("conv_tma_kernel", "wgrad_tma_kernel", "conv_fprop_kernel")}
+    model = nets.vgg11(512)
+    run, _, _ = _check_grad_hv(model, 512, seed=3234, with_state=True)
+    ran = {k: run.c.kernel_launches(k) - before[k] for k in before}
+    # 7 layers x (forward + data gradient + R-forward + R-data-gradient) minus the first layer's
+    # data gradients; 7 layers x (weight gradient + R-weight-gradient)
+    assert ran["conv_tma_kernel"] >= 24 and ran["wgrad_tma_kernel"] >= 14, ran
+
+
+def test_vgg11_bn_256_kfac_step():
+    """KFAC step at the per-GPU shape of the 2048-image configuration, lambda = 1e-3, gamma = 0:
+    labels sampled from the model's distribution (injected uniforms), the second backward pass,
+    A and G factors against the oracle; then the damped Cholesky factorisations and the natural
+    gradient against LAPACK on the host (potrf / potrs are what the reference calls through
+    cuSOLVER, solvers/kfac_inverses.cu:142-179), computed from the ORACLE's factors."""
+    import scipy.linalg as sla
+    import torch
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    L = _lib.load()
+    n, lam = 256, 1e-3
+    model = nets.vgg11(n)
+    O.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=4234)
+    u = np.random.default_rng(4238).random(n)
+    env = O.make_env()
+    st = O.gradient(model, x, y, w, ncls, n)
+    t_o, e_o = np.zeros(n), np.zeros(n * ncls)
+    O.lib().ora_distribution_errors(C.byref(env), st.probs, u, n, ncls, t_o, e_o)
+    g2_o, dx2_o = np.zeros(model.pSize), np.zeros(model.zSize)
+    O.lib().ora_cnn_backward(C.byref(env), C.byref(model), x, w, st.z, g2_o, dx2_o, e_o, n)
+    info_o = S.KFAC_INFO()
+    assert O.lib().ora_kfac_storage_indices(C.byref(model), C.byref(info_o)) == 0
+    A_o, G_o = np.zeros(info_o.OmegaZSize), np.zeros(info_o.LambdaGSize)
+    O.lib().ora_kfac_omega_z(C.byref(env), C.byref(model), x, st.z, n, A_o, C.byref(info_o))
+    O.lib().ora_kfac_lambda_delta(C.byref(env), C.byref(model), dx2_o, n, G_o, C.byref(info_o))
+
+    run = G.GpuRun(model, x, y, w, ncls)
+    assert G.rel(run.gradient, st.gradient) < TOL
+    ws = run.ws
+    info = api.computeKFACStorageIndices(model)
+    info.regLambda, info.dampGamma = lam, 0.0
+    md = model.maxDeltaSize + n * ncls
+    t_d, e1, e2 = G.dev(np.zeros(n)), G.dev(np.zeros(md)), G.dev(np.zeros(md))
+    api.computeDistributionErrors(run.c, ws.probs, G.dev(u), t_d, e1, n, ncls)
+    assert np.array_equal(t_d.cpu().numpy(), t_o)
+    kscr = G.dev(np.zeros(max(L.fitre_kfac_mem_required(C.byref(model)), ws.dev.numel())))
+    g2, dx2 = G.dev(np.zeros(model.pSize)), G.dev(np.zeros(model.zSize))
+    api.cnnBackward(run.c, model, run.data, kscr, ws.z, g2, dx2, e1, e2, 0, n)
+    assert G.rel(g2.cpu().numpy(), g2_o) < TOL
+    del kscr, e1, e2
+    iscr = G.dev(np.zeros(max(L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model)),
+                              L.fitre_kfac_natural_gradient_mem_required(C.byref(model)))))
+    A, Gm = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+    Ai, Gi = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+    before = run.c.kernel_launches("patch_syrk_tma_kernel")
+    run.c.set_kfac_solver(1)
+    try:
+        api.computeFactorsAndInverses(run.c, model, run.data, ws.z, dx2, n, A, Ai, Gm, Gi, info, iscr)
+        ng = G.dev(np.zeros(model.pSize))
+        api.computeNaturalGradient(run.c, model, info, Ai, Gi, ws.gradient, ng, iscr)
+        ng_chol = ng.cpu().numpy()
+    finally:
+        run.c.set_kfac_solver(0)
+    assert run.c.kernel_launches("patch_syrk_tma_kernel") - before >= 7
+    api.computeFactorsAndInverses(run.c, model, run.data, ws.z, dx2, n, A, Ai, Gm, Gi, info, iscr)
+    api.computeNaturalGradient(run.c, model, info, Ai, Gi, ws.gradient, ng, iscr)
+    ng_inv = ng.cpu().numpy()
+    A_h, G_h = A.cpu().numpy(), Gm.cpu().numpy()
+    del A, Ai, Gm, Gi, iscr
+    torch.cuda.empty_cache()
+
+    nl = model.cLayers + model.lLayers
+    worst = 0.0
+    for l in range(nl):
+        if l < model.cLayers:
+            c = model.convLayer[l]
+            K, co = c.inChannels * c.kSize ** 2, c.outChannels
+        else:
+            f = model.fcLayer[l - model.cLayers]
+            K, co = f.in_, f.out
+        a0, g0 = info.OmegaZOffsets[l], info.LambdaGOffsets[l]
+        assert (a0, g0) == (info_o.OmegaZOffsets[l], info_o.LambdaGOffsets[l])
+        # factors: CUDA against the oracle
+        assert G.relmax(A_h[a0:a0 + K * K], A_o[a0:a0 + K * K]) < TOL, l
+        assert G.relmax(G_h[g0:g0 + co * co], G_o[g0:g0 + co * co]) < TOL, l
+        # natural gradient of the layer from the oracle's factors by LAPACK: G^-1 [dW] A^-1
+        Al = A_o[a0:a0 + K * K].reshape(K, K) + lam * np.eye(K)
+        Gl = G_o[g0:g0 + co * co].reshape(co, co) + lam * np.eye(co)
+        w0 = model.wOffsets[l]
+        # conv weights are K x Cout column-major, FC weights out x in column-major: rows = outputs
+        conv = l < model.cLayers
+        blk = (lambda a: a[w0:w0 + K * co].reshape(co, K)) if conv else (lambda a: a[w0:w0 + K * co].reshape(K, co).T)
+        Wg = blk(st.gradient)
+        ca, cg = sla.cho_factor(Al, lower=True), sla.cho_factor(Gl, lower=True)
+        ref = sla.cho_solve(cg, sla.cho_solve(ca, Wg.T).T)
+        # rounding of a solve with condition number kappa is about kappa * 2^-53; the damped
+        # factors have kappa = (largest eigenvalue + lambda) / (smallest + lambda)
+        kap = _cond_bound(Gl, lam) * _cond_bound(Al, lam)
+        tol = max(TOL, 8 * kap * 2.0 ** -53)
+        for got in (ng_chol, ng_inv):
+            e = G.rel(blk(got), ref)
+            worst = max(worst, e / tol)
+            assert e < tol, (l, e, kap)
+    assert worst < 1.0

@@ -17,7 +17,9 @@ from fitre_b200 import _structs as S
 pytestmark = pytest.mark.gpu
 
 TOL = 1e-10
-GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+_ALL = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+GOLDEN = [p for p in _ALL if not os.path.basename(p).startswith("kfac_")]
+KFAC_GOLDEN = [p for p in _ALL if os.path.basename(p).startswith("kfac_")]
 FLAGS = {"Small Residue": S.CG_CONVERGED, "Negative Curvature": S.CG_NEG_CURVATURE,
          "Hit Boundary": S.CG_HIT_BOUNDARY, "Maximum Iterations": S.CG_MAX_ITERS}
 
@@ -68,6 +70,125 @@ def test_cuda_quadratic_model_and_cg_match_golden(path):
         assert prm.iterations == int(d[tag + "_iters"]), tag
         assert G.rel(p.cpu().numpy(), d[tag + "_p"]) < 1e-7, tag
         assert abs(prm.modelValue - float(d[tag + "_model"])) <= 1e-7 * abs(float(d[tag + "_model"])), tag
+
+
+@pytest.mark.parametrize("path", KFAC_GOLDEN, ids=[os.path.basename(p)[:-4] for p in KFAC_GOLDEN])
+def test_cuda_kfac_matches_reference_pytorch_fixtures(path):
+    """A and G factors, damped inverses and natural gradient against the fixtures produced by the
+    reference's own PyTorch KFAC code (pytorch/kfac/kfac_utils.py, tests/golden/make_kfac_golden.py),
+    explicit-inverse and Cholesky form."""
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    L = _lib.load()
+    d, spec, model = load_case(path)
+    n, ncls = spec["batch"], spec["classes"]
+    run = G.GpuRun(model, d["batch"], d["labels"], d["weights"], ncls, ref_softmax=0)
+    assert G.rel(run.gradient, d["gradient"]) < TOL
+    ws = run.ws
+    # second backward pass on the sampled labels (the fixture fixes them): errors (p - onehot) / N
+    probs = ws.probs.cpu().numpy().reshape(n, ncls)
+    onehot = np.zeros((n, ncls))
+    onehot[np.arange(n), d["sampled_labels"].astype(int) - 1] = 1.0
+    md = model.maxDeltaSize + n * ncls
+    e1, e2 = G.dev(np.zeros(md)), G.dev(np.zeros(md))
+    e1[:n * ncls] = G.dev(((probs - onehot) / n).reshape(-1))
+    g2, dx2 = G.dev(np.zeros(model.pSize)), G.dev(np.zeros(model.zSize))
+    api.cnnBackward(run.c, model, run.data, ws.dev, ws.z, g2, dx2, e1, e2, 0, n)
+    info = api.computeKFACStorageIndices(model)
+    info.regLambda, info.dampGamma = float(d["regLambda"]), float(d["dampGamma"])
+    scratch = G.dev(np.zeros(max(L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model)),
+                                 L.fitre_kfac_natural_gradient_mem_required(C.byref(model)))))
+    nl = model.cLayers + model.lLayers
+    for solver in (0, 1):
+        run.c.set_kfac_solver(solver)
+        try:
+            A, Gm = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+            Ai, Gi = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+            api.computeFactorsAndInverses(run.c, model, run.data, ws.z, dx2, n, A, Ai, Gm, Gi, info, scratch)
+            ng = G.dev(np.zeros(model.pSize))
+            api.computeNaturalGradient(run.c, model, info, Ai, Gi, ws.gradient, ng, scratch)
+        finally:
+            run.c.set_kfac_solver(0)
+        A_h, G_h, Ai_h, Gi_h = (t.cpu().numpy() for t in (A, Gm, Ai, Gi))
+        for l in range(nl):
+            if l < model.cLayers:
+                c = model.convLayer[l]
+                kb, co = c.inChannels * c.kSize ** 2 + model.bias, c.outChannels
+            else:
+                f = model.fcLayer[l - model.cLayers]
+                kb, co = f.in_ + model.bias, f.out
+            a0, g0 = info.OmegaZOffsets[l], info.LambdaGOffsets[l]
+            assert G.relmax(A_h[a0:a0 + kb * kb].reshape(kb, kb), d["A%d" % l]) < TOL, l
+            assert G.relmax(G_h[g0:g0 + co * co].reshape(co, co), d["G%d" % l]) < TOL, l
+            assert G.rel(Gi_h[g0:g0 + co * co].reshape(co, co), d["Ginv%d" % l]) < 1e-9, l
+            if solver == 0:
+                assert G.rel(Ai_h[a0:a0 + kb * kb].reshape(kb, kb), d["Ainv%d" % l]) < 1e-9, l
+        assert G.rel(ng.cpu().numpy(), d["natural_gradient"]) < 1e-9, solver
+
+
+def test_cuda_softmax_reference_quirks_known_answer():
+    """The hand-worked two-sample, three-class case of functions/softmax_loss.cu:24-27,55 (running
+    maximum starting at 0, + 1e-10 after normalising) through the CUDA forward pass: an identity
+    convolution and a selecting FC layer put the chosen logits in front of the softmax."""
+    import gpu_util as G
+    from fitre_b200 import api
+    model = S.describe_model(
+        [dict(cin=1, cout=1, h=2, w=2, k=3, pad=1, bn=False, act=S.CNN_ACT_NONE, pool=None)],
+        [(4, 3, S.CNN_ACT_NONE)], 2, False)
+    api.finalize(model)
+    w = np.zeros(model.pSize)
+    w[4] = 1.0                              # centre tap: the convolution copies its input
+    for o in range(3):                      # FC weights out x in column-major: logit o = pixel o
+        w[model.wOffsets[1] + o * 3 + o] = 1.0
+    x = np.array([-1.0, -2.5, -0.5, 9.0, 2.0, 0.5, -1.0, 9.0])   # [C=1][N=2][W][H]
+    y = np.array([2.0, 1.0])
+    want_p = np.array([0.3482074279837349, 0.0776955792485706, 0.5740969930676946,
+                       0.7855970346892759, 0.1752903922400367, 0.03911257337068746])
+    want_loss = 1.3981341074423905
+    c = G.ctx(1)
+    ws = api.Workspace(model, 3)
+    data = api.make_dataset(G.dev(w), G.dev(x), G.dev(y), 3)
+    loss = api.cnnForward(c, model, data, ws.scratch, ws.z, ws.probs, ws.errors, 0, 2)
+    probs, errs = ws.probs.cpu().numpy(), ws.errors.cpu().numpy()
+    assert np.abs(probs - want_p).max() < 4e-16
+    assert abs(loss - want_loss) < 4e-15
+    onehot = np.array([0, 1, 0, 1, 0, 0], dtype=np.float64)
+    assert np.abs(errs - (want_p - onehot) / 2).max() < 4e-16
+    G.ctx(0)                                # textbook softmax: the + 1e-10 is gone
+    api.cnnForward(G.ctx(0), model, data, ws.scratch, ws.z, ws.probs, ws.errors, 0, 2)
+    assert np.abs((probs - ws.probs.cpu().numpy()) - 1e-10).max() < 1e-15
+    G.ctx(1)
+
+
+def test_cuda_quadratic_model_damping_term_both_forms():
+    """weightDecay != 0: the reference form (Hv + lambda * weights, functions/model_reduction.cu:50-52,
+    the default) and the PyTorch twin's (Hv + lambda * v) against the oracle in the same setting."""
+    import gpu_util as G
+    from fitre_b200 import api
+    n, lam, delta = 6, 0.3, 0.7
+    model = nets.vgg_small(n)
+    O.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=19)
+    vals = {}
+    for refq in (1, 0):
+        env = O.make_env(ref_quadratic=refq)
+        st = O.gradient(model, x, y, w, ncls, n, weight_decay=lam, env=env)
+        v_o = v.copy()
+        m_o = O.lib().ora_quadratic_model(C.byref(env), C.byref(model), x, w, ncls, st.z, st.probs,
+                                          st.errors, st.dx, st.gradient, v_o, delta, n, lam)
+        run = G.GpuRun(model, x, y, w, ncls, weight_decay=lam)
+        run.c.set_reference_quadratic_damping(refq)
+        try:
+            vd = G.dev(v)
+            ws = run.ws
+            m_g = api.computeQuadraticModel(run.c, model, run.data, ws.z, ws.probs, ws.errors, ws.dx,
+                                            ws.gradient, vd, delta, 0, n, lam, ws.dev)
+        finally:
+            run.c.set_reference_quadratic_damping(1)
+        assert abs(m_g - m_o) <= 1e-10 * abs(m_o), refq
+        assert G.rel(vd.cpu().numpy(), v_o) < TOL, refq
+        vals[refq] = m_g
+    assert vals[0] != vals[1]
 
 
 CASES = [

@@ -31,8 +31,24 @@ def run_ranks(backend, world, tmp_path, builder):
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "multirank_worker.py"), backend,
                                str(r), str(world), port, outs[r], builder], env=env)
              for r in range(world)]
-    for p in procs:
-        assert p.wait(timeout=600) == 0
+    # a rank that fails or runs out of time must not leave its peers blocked in a collective:
+    # on any failure every rank still running is killed and reaped before the test reports
+    codes = []
+    try:
+        for p in procs:
+            codes.append(p.wait(timeout=600))
+            if codes[-1] != 0:
+                break
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        for p in procs:
+            try:
+                p.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                pass
+    assert codes == [0] * world, "rank exit codes %s" % codes
     return [np.load(o) for o in outs]
 
 

@@ -13,7 +13,9 @@ import oracle_lib as O
 from fitre_b200 import _structs as S
 from fitre_b200 import layout
 
-GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+_ALL = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+GOLDEN = [p for p in _ALL if not os.path.basename(p).startswith("kfac_")]
+KFAC_GOLDEN = [p for p in _ALL if os.path.basename(p).startswith("kfac_")]
 FLAGS = {"Small Residue": S.CG_CONVERGED, "Negative Curvature": S.CG_NEG_CURVATURE,
          "Hit Boundary": S.CG_HIT_BOUNDARY, "Maximum Iterations": S.CG_MAX_ITERS}
 
@@ -31,7 +33,7 @@ def load_case(path):
 
 
 def test_fixtures_present():
-    assert len(GOLDEN) >= 7
+    assert len(GOLDEN) >= 7 and len(KFAC_GOLDEN) >= 3
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
@@ -278,3 +280,107 @@ def test_kfac_inverse_and_natural_gradient_host():
     exp = Gm @ Wb @ A
     assert np.allclose(ng[model.wOffsets[1]:model.wOffsets[1] + K * Co].reshape(Co, K), exp[:, :K])
     assert np.allclose(ng[model.bOffsets[1]:model.bOffsets[1] + Co], exp[:, K])
+
+
+def kfac_layer_sizes(model, l):
+    """(rows of the A block incl. the bias column, rows of the G block) of layer l."""
+    if l < model.cLayers:
+        c = model.convLayer[l]
+        return c.inChannels * c.kSize ** 2 + model.bias, c.outChannels
+    f = model.fcLayer[l - model.cLayers]
+    return f.in_ + model.bias, f.out
+
+
+@pytest.mark.parametrize("path", KFAC_GOLDEN, ids=[os.path.basename(p)[:-4] for p in KFAC_GOLDEN])
+def test_kfac_factors_inverses_natural_gradient_match_reference_pytorch(path):
+    """The fixtures were produced by the reference's own PyTorch KFAC code
+    (pytorch/kfac/kfac_utils.py: matmulOmega, matmul3d, matmulLambda, computeMatVec) run on CPU:
+    they pin the factor scalings 1/N, 1/(Ho Wo), N Ho Wo and N, the bias column, the damping
+    (lambda + gamma) I and the order G^-1 [W|b] A^-1 of the oracle's restatement of
+    solvers/kfac_inverses.cu:450-630,759-857 and solvers/kfac_natural_gradient.cu:36-241."""
+    d, spec, model = load_case(path)
+    n, ncls = spec["batch"], spec["classes"]
+    L = O.lib()
+    env = O.make_env(ref_softmax=0)
+    st = O.gradient(model, d["batch"], d["labels"], d["weights"], ncls, n, env=env)
+    assert rel(st.gradient, d["gradient"]) < 1e-12
+    # the second backward pass of KFAC is a backward pass on other labels
+    st_s = O.gradient(model, d["batch"], d["sampled_labels"], d["weights"], ncls, n, env=env)
+    info = S.KFAC_INFO()
+    assert L.ora_kfac_storage_indices(C.byref(model), C.byref(info)) == 0
+    A, G = np.zeros(info.OmegaZSize), np.zeros(info.LambdaGSize)
+    L.ora_kfac_omega_z(C.byref(env), C.byref(model), d["batch"], st.z, n, A, C.byref(info))
+    L.ora_kfac_lambda_delta(C.byref(env), C.byref(model), st_s.dx, n, G, C.byref(info))
+    lam, gam = float(d["regLambda"]), float(d["dampGamma"])
+    Ai, Gi = np.zeros(info.OmegaZSize), np.zeros(info.LambdaGSize)
+    for l in range(model.cLayers + model.lLayers):
+        kb, co = kfac_layer_sizes(model, l)
+        a0, g0 = info.OmegaZOffsets[l], info.LambdaGOffsets[l]
+        a, g = A[a0:a0 + kb * kb].reshape(kb, kb), G[g0:g0 + co * co].reshape(co, co)
+        assert d["A%d" % l].shape == (kb, kb) and d["G%d" % l].shape == (co, co)
+        assert rel(a, d["A%d" % l]) < 1e-12, l       # symmetric: row / column major agree
+        assert rel(g, d["G%d" % l]) < 1e-12, l
+        ai, gi = np.zeros(kb * kb), np.zeros(co * co)
+        assert L.ora_kfac_matrix_inverse(np.ascontiguousarray(a.reshape(-1)), ai, kb, lam, gam) == 0
+        assert L.ora_kfac_matrix_inverse(np.ascontiguousarray(g.reshape(-1)), gi, co, lam, gam) == 0
+        assert rel(ai.reshape(kb, kb), d["Ainv%d" % l]) < 1e-9, l
+        assert rel(gi.reshape(co, co), d["Ginv%d" % l]) < 1e-9, l
+        Ai[a0:a0 + kb * kb], Gi[g0:g0 + co * co] = ai, gi
+    ng = np.zeros(model.pSize)
+    L.ora_natural_gradient(C.byref(model), C.byref(info), Ai, Gi, st.gradient, ng)
+    assert rel(ng, d["natural_gradient"]) < 1e-9
+
+
+def test_softmax_reference_quirks_known_answer():
+    """functions/softmax_loss.cu:24-27,55 and :231-245, worked by hand for two samples of three
+    classes.  Sample 1 has only negative logits: the running maximum starts at 0, so nothing is
+    subtracted and e = exp(z) itself; sample 2 is shifted by its largest logit 2.  Every
+    probability then gets + 1e-10; loss = mean of -log p_label; errors = (p - onehot) / N."""
+    logits = np.array([-1.0, -2.5, -0.5, 2.0, 0.5, -1.0])      # [classes x N] column-major
+    target = np.array([2.0, 1.0])
+    want_p = np.array([0.3482074279837349, 0.0776955792485706, 0.5740969930676946,
+                       0.7855970346892759, 0.1752903922400367, 0.03911257337068746])
+    want_loss = 1.3981341074423905
+    # the same by the formula, written out
+    e1 = np.exp(np.array([-1.0, -2.5, -0.5]) - 0.0)
+    e2 = np.exp(np.array([2.0, 0.5, -1.0]) - 2.0)
+    by_formula = np.concatenate([e1 / e1.sum() + 1e-10, e2 / e2.sum() + 1e-10])
+    assert np.abs(by_formula - want_p).max() < 1e-15
+    assert abs(by_formula.sum() - (2.0 + 6e-10)) < 1e-14        # rows sum to 1 + 3e-10, not 1
+    env = O.make_env(ref_softmax=1)
+    probs = np.zeros(6)
+    loss = O.lib().ora_softmax_loss(C.byref(env), logits, target, 2, 3, probs)
+    assert np.abs(probs - want_p).max() < 2e-16
+    assert abs(loss - want_loss) < 1e-15
+    # textbook softmax (quirks off) differs by exactly the 1e-10 shift
+    env0 = O.make_env(ref_softmax=0)
+    probs0 = np.zeros(6)
+    O.lib().ora_softmax_loss(C.byref(env0), logits, target, 2, 3, probs0)
+    assert np.abs((probs - probs0) - 1e-10).max() < 1e-15
+
+
+def test_quadratic_model_damping_term_reference_and_pytorch_forms():
+    """functions/model_reduction.cu:50-52 adds weightDecay * weights to Hv before v'Hv;
+    pytorch/peng/utils.py:77 adds weightDecay * v.  Both forms against the formulas written out."""
+    n = 5
+    model = nets.vgg_small(n)
+    O.finalize(model)
+    rng = np.random.default_rng(8)
+    c0 = model.convLayer[0]
+    x = layout.batch_to_ref(rng.standard_normal((n, c0.inChannels, c0.height, c0.width)))
+    y = rng.integers(1, 11, n).astype(np.float64)
+    w = layout.he_normal_params(model, rng)
+    v = rng.standard_normal(model.pSize)
+    lam, delta = 0.3, 0.7
+    for refq in (1, 0):
+        env = O.make_env(ref_quadratic=refq)
+        st = O.gradient(model, x, y, w, 10, n, weight_decay=lam, env=env)
+        hv = O.hv(model, x, w, 10, n, st, v, env=env) + lam * (w if refq else v)
+        vHv, nrm, gv = hv.dot(v), np.linalg.norm(v), st.gradient.dot(v)
+        alpha = delta / nrm if vHv < 0 else min(gv / (vHv + 1e-6), delta / (nrm + 1e-16))
+        want = 0.5 * vHv * alpha * alpha - gv * alpha
+        vv = v.copy()
+        got = O.lib().ora_quadratic_model(C.byref(env), C.byref(model), x, w, 10, st.z, st.probs,
+                                          st.errors, st.dx, st.gradient, vv, delta, n, lam)
+        assert abs(got - want) <= 1e-12 * abs(want)
+        assert rel(vv, alpha * v) < 1e-13

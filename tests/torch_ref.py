@@ -50,6 +50,39 @@ def forward(model, params, x):
     return out
 
 
+def forward_capture(model, params, x):
+    """forward() that also returns, per layer, the tensor the layer reads (conv: [N][C][H][W];
+    FC: the previous layer's output, 4-D in front of the first FC layer) and the tensor its
+    convolution / matrix product writes (before batch norm and activation) -- what the
+    reference's KFAC hooks store as Zis and dxA (pytorch/kfac/kfac_utils.py:30-32)."""
+    it = iter(params)
+    out = x
+    ins, outs = [], []
+    for l in range(model.cLayers):
+        c, p = model.convLayer[l], model.poolLayer[l]
+        w = next(it)
+        b = next(it) if model.bias else None
+        ins.append(out)
+        out = F.conv2d(out, w, b, stride=c.stride, padding=c.padding)
+        outs.append(out)
+        if c.batchNorm != S.NO_BATCH_NORM:
+            out = F.batch_norm(out, None, None, training=True, eps=1e-5)
+        out = _act(model.actFuns[l], out)
+        if p.type == S.MAX_POOL:
+            out = F.max_pool2d(out, p.pSize, p.stride, p.padding)
+        elif p.type == S.AVG_POOL:
+            out = F.avg_pool2d(out, p.pSize, p.stride, p.padding)
+    for l in range(model.lLayers):
+        f = model.fcLayer[l]
+        w = next(it)
+        b = next(it) if model.bias else None
+        ins.append(out)
+        out = F.linear(out.reshape(out.shape[0], -1), w, b)
+        outs.append(out)
+        out = _act(f.actFun, out)
+    return out, ins, outs
+
+
 def torch_params(model, flat):
     return [torch.tensor(np.ascontiguousarray(a), dtype=torch.float64, requires_grad=True)
             for a in layout.params_from_ref(model, flat)]
