@@ -38,12 +38,13 @@ GATHER_CASES = [
     (4, 8, 3, 1, 4, True),
     (2, 10, 3, 0, 4, True),
     (2, 8, 3, 2, 3, False),    # Ho = 10 does not divide the 128-row tile: gather kernel
-    (2, 8, 5, 2, 4, True),
-    (2, 12, 5, 0, 2, True),
+    (2, 8, 5, 2, 4, False),    # 5 x 5 taps: two ring stages of 100 weight rows exceed the shared
+    (2, 12, 5, 0, 2, False),   # memory of two resident blocks, so these run on the gather kernel
     (4, 16, 5, 1, 2, False),   # Ho = 14
     (3, 7, 3, 1, 5, False),    # odd height and odd K
     (6, 16, 3, 1, 16, True),   # one image per tile row block, several tiles
-    (2, 32, 5, 2, 6, True),    # Ho * Wo > 128: tiles of 4 output columns
+    (2, 32, 5, 2, 6, False),
+    (2, 32, 3, 1, 6, True),    # Ho * Wo > 128: tiles of 4 output columns
 ]
 
 

@@ -140,7 +140,9 @@ def test_cuda_softmax_reference_quirks_known_answer():
     w[4] = 1.0                              # centre tap: the convolution copies its input
     for o in range(3):                      # FC weights out x in column-major: logit o = pixel o
         w[model.wOffsets[1] + o * 3 + o] = 1.0
-    x = np.array([-1.0, -2.5, -0.5, 9.0, 2.0, 0.5, -1.0, 9.0])   # [C=1][N=2][W][H]
+    # [C=1][N=2][W][H] with h fastest; the FC layer reads a sample as (h, w) row-major, so pixel
+    # (h, w) = (0, 1) is the second logit and (1, 0) the third
+    x = np.array([-1.0, -0.5, -2.5, 9.0, 2.0, -1.0, 0.5, 9.0])
     y = np.array([2.0, 1.0])
     want_p = np.array([0.3482074279837349, 0.0776955792485706, 0.5740969930676946,
                        0.7855970346892759, 0.1752903922400367, 0.03911257337068746])
