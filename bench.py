@@ -6,18 +6,26 @@
 One step = one computeCNNGradient + one cnnHv on one synthetic batch per GPU:
 VGG-11-BN, fp64, 512 images of 3x32x32 per GPU (weak scaling: at 8 GPUs this is the
 4096-image configuration the metric is quoted on).  Inputs are seeded synthetic data
-(N(0,1) images, uniform labels, He-normal weights, N(0,1) direction).
+(N(0,1) images, uniform labels, He-normal weights, N(0,1) direction); the models come from the
+library's own builders (fitre_read_vgg11 and friends).
 
 Prints ONE JSON line: images/s over all GPUs (device-resident inputs, CUDA events, max over
 ranks), the same metric end to end through the host-buffer C-ABI entry point (`e2e`), the
 roofline of the dominant kernel (implicit-GEMM convolution, fp64 tensor path) with its
-duration measured by CUDA events inside the timed region, and on 1 GPU the CPU baseline
-(the oracle port on the host cores, bounded sample).
+duration measured by CUDA events inside the timed region, on 1 GPU the CPU baseline, and in
+`secondary` the device-timed figures of the path's other configurations at the same GPU count
+(LeNet gradient + Hv + 10 Steihaug-CG iterations, AlexNet-BN gradient + Hv at a global batch of
+1024, the KFAC step at 256 images per GPU).  With more than one GPU, `multi_gpu_parity` holds
+the relative errors of a small sharded problem against the full-batch oracle.
 
-`--impl reference` times the reference path's CPU restatement (oracle/) with all host
-threads on a bounded sample of the same workload and prints the same line shape.
+`--impl reference` times the same step on the host cores: the gradient and the Hessian-vector
+product by double backward as PyTorch computes them on the CPU (the operator of the
+reference's pytorch/ path), all threads, one full per-GPU batch per step; the C + OpenMP port
+of the reference's CUDA host code (oracle/) is timed beside it on a bounded sample and the
+faster of the two is the reported value.
 """
 import argparse
+import ctypes as C
 import json
 import os
 import statistics
@@ -35,18 +43,29 @@ import numpy as np  # noqa: E402
 
 PER_GPU_BATCH = 512
 WORKLOAD = "vgg11bn_32x32_fp64_gradient+hv"
-# algorithmic flops per image (2*M*K*Cout products only): gradient 913.1 MF + Hv 1819.1 MF
-TORCH_SAMPLE_IMAGES = 256    # PyTorch-on-CPU leg beside it
-CPU_SAMPLE_IMAGES = 256      # cpu_baseline leg of the default run: one pass, ~15 s on 16 cores
-REF_SAMPLE_IMAGES = 64       # --impl reference: per timed step
+PORT_SAMPLE_IMAGES = 256     # oracle port (C + OpenMP): one pass, ~7-15 s on 16 cores
+TORCH_SAMPLE_IMAGES = 256    # PyTorch-on-CPU leg of the default run
+DMMA_FMA_PER_CLK_SM = 64     # fp64 tensor-pipe issue limit of one SM (FMA per clock)
+N_SM = 148
 
 
-def build_model(n):
-    import nets
+# ---- models (the library's own builders) ----------------------------------------------------
+def product_model(kind, n):
     from fitre_b200 import api
-    m = nets.vgg11(n)
-    api.finalize(m)
-    return m
+    from fitre_b200 import _structs as S
+    if kind == "vgg11":      # nn/read_vgg.c:216-299: no bias, batch norm, Swish, max pooling
+        return api.readVGG11(n, 32, 32, 10, 3, 0, 1, S.CNN_ACT_SWISH)
+    if kind == "alexnet":    # nn/read_alexnet.c:14-243 topology with batch norm
+        return api.readAlexNetCNN(n, 32, 32, 10, 0, 1, S.CNN_ACT_SWISH)
+    if kind == "lenet":      # nn/read_nn.c:500-725 topology; ReLU + max pooling as the configuration states
+        return api.readLenetCNN(3, 32, 32, n, 1, 0, S.CNN_ACT_RELU, S.MAX_POOL)
+    raise ValueError(kind)
+
+
+def bench_config(n, world):
+    return {"workload": WORKLOAD, "per_gpu_batch": n, "global_batch": n * world,
+            "parallelism": "dp%d" % world, "activation": "swish", "batch_norm": True,
+            "l2": "inputs larger than L2 (z/dx/rz are 1.85 GiB each per GPU)"}
 
 
 def synth(model, n, seed):
@@ -129,14 +148,37 @@ class ClockSampler:
         return out
 
 
-def cpu_oracle_rate(sample_images, threads=None):
-    """images/s of one gradient + one Hv of the oracle port on the host cores."""
-    import oracle_lib as O
+# ---- CPU legs ---------------------------------------------------------------------------------
+def host_threads():
+    return os.cpu_count() or 1
+
+
+def use_all_host_threads():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU legs use every
+    core, so the variable is set before an OpenMP runtime reads it and the oracle library is
+    told explicitly as well."""
+    os.environ["OMP_NUM_THREADS"] = str(host_threads())
+
+
+def checker_model(n):
+    """VGG-11-BN description for the CPU legs, built without the CUDA library (test-side net
+    description + the oracle's own offset computation; byte-identical to fitre_read_vgg11's)."""
     import nets
-    if threads:
-        os.environ["OMP_NUM_THREADS"] = str(threads)
-    m = nets.vgg11(sample_images)
+    import oracle_lib as O
+    m = nets.vgg11(n)
     O.finalize(m)
+    return m
+
+
+def cpu_oracle_rate(sample_images):
+    """images/s of one gradient + one Hv of the oracle port on the host cores."""
+    use_all_host_threads()
+    import oracle_lib as O
+    try:
+        O.lib().ora_set_num_threads(host_threads())
+    except AttributeError:
+        pass
+    m = checker_model(sample_images)
     x, y, w, v = synth(m, sample_images, 4321)
     t0 = time.perf_counter()
     st = O.gradient(m, x, y, w, 10, sample_images)
@@ -145,58 +187,232 @@ def cpu_oracle_rate(sample_images, threads=None):
     return sample_images / dt, dt
 
 
-def cpu_pytorch_rate(sample_images):
-    """images/s of the same step as PyTorch runs it on the host cores: fp64 autograd gradient and
-    Hessian-vector product by double backward, the operator of the reference's pytorch/ path
-    (pytorch/kfac/alexnet_cifar.py:297-324), all threads."""
-    import torch
-    import nets
-    import oracle_lib as O
+def cpu_pytorch_step(case):
+    """One gradient + Hessian-vector product as PyTorch runs it on the host cores: fp64 autograd
+    gradient and double backward, the operator of the reference's pytorch/ path
+    (pytorch/kfac/alexnet_cifar.py:297-324).  Returns the seconds of the step."""
     import torch_ref
-    torch.set_num_threads(os.cpu_count() or 1)
-    m = nets.vgg11(sample_images)
-    O.finalize(m)
-    x, y, w, v = synth(m, sample_images, 4321)
+    m, x, y, w, v, n = case
     t0 = time.perf_counter()
-    torch_ref.loss_grad_hv(m, w, x, y, sample_images, vectors=(v,))
-    dt = time.perf_counter() - t0
-    return sample_images / dt, dt
+    torch_ref.loss_grad_hv(m, w, x, y, n, vectors=(v,))
+    return time.perf_counter() - t0
+
+
+def cpu_pytorch_case(n):
+    import torch
+    torch.set_num_threads(host_threads())
+    m = checker_model(n)
+    x, y, w, v = synth(m, n, 4321)
+    return m, x, y, w, v, n
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
-    rates = []
-    for i in range(args.warmup + args.steps):
-        r, dt = cpu_oracle_rate(REF_SAMPLE_IMAGES)
-        if i >= args.warmup:
-            rates.append((r, dt))
-    value = REF_SAMPLE_IMAGES * len(rates) / sum(dt for _, dt in rates)
+    use_all_host_threads()
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    n = args.per_gpu_batch
+    cores = host_threads()
     line = {
-        "impl": "reference", "metric": "gradient+Hv images/sec", "value": value, "unit": "images/s",
+        "impl": "reference", "metric": "gradient+Hv images/sec", "unit": "images/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * sum(dt for _, dt in rates) / len(rates),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD, "per_gpu_batch": PER_GPU_BATCH,
-                   "note": "CPU restatement of the reference path (oracle/, C + OpenMP); each step "
-                           "is a %d-image sample of the workload" % REF_SAMPLE_IMAGES},
-        "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port",
-                         "sample": "%d images of the VGG-11-BN fp64 gradient+Hv step" % REF_SAMPLE_IMAGES},
-        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "data": "synthetic", "config": bench_config(n, world), "gpu_launches": 0,
     }
-    try:  # the same step as PyTorch runs it on the host cores, for comparison with the port
-        rt, dtt = cpu_pytorch_rate(TORCH_SAMPLE_IMAGES)
-        line["cpu_baseline_pytorch"] = {"value": rt, "unit": "images/s", "cores": cores,
-                                        "sample": "%d images (%.1f s)" % (TORCH_SAMPLE_IMAGES, dtt)}
-    except Exception as e:  # noqa: BLE001
+    # the C + OpenMP port of the reference's CUDA host code, one bounded pass
+    port_rate, port_dt = cpu_oracle_rate(PORT_SAMPLE_IMAGES)
+    line["cpu_baseline_port"] = {"value": port_rate, "unit": "images/s", "cores": cores, "kind": "port",
+                                 "sample": "%d images, C + OpenMP restatement of the reference's CUDA host "
+                                           "code (%.1f s)" % (PORT_SAMPLE_IMAGES, port_dt)}
+    value, ms, kind, sample = port_rate, 1e3 * port_dt * n / PORT_SAMPLE_IMAGES, "port", line["cpu_baseline_port"]["sample"]
+    try:
+        case = cpu_pytorch_case(n)
+        first = cpu_pytorch_step(case)
+        warm, steps = args.warmup, args.steps
+        if first * (warm + steps) > 600.0:
+            # this host would need more than ten minutes: one warm-up step and what fits four minutes
+            warm, steps = min(warm, 1), max(1, min(steps, int(240.0 / first)))
+            line["steps"], line["warmup"] = steps, warm
+        times = [first] if warm == 0 else []
+        for _ in range(max(warm - 1, 0)):
+            cpu_pytorch_step(case)
+        while len(times) < steps:
+            times.append(cpu_pytorch_step(case))
+        t_rate = n * len(times) / sum(times)
+        line["cpu_baseline_pytorch"] = {"value": t_rate, "unit": "images/s", "cores": cores,
+                                        "sample": "%d steps of one %d-image batch each" % (len(times), n)}
+        if t_rate >= port_rate:
+            value, ms, kind = t_rate, 1e3 * sum(times) / len(times), "port"
+            sample = ("%d-image batches, fp64 autograd gradient + double-backward Hessian-vector product in "
+                      "PyTorch on the host cores (the operator of the reference's pytorch/ path, restated "
+                      "for current PyTorch); faster than the C + OpenMP port (%.1f images/s)" % (n, port_rate))
+    except Exception as e:  # noqa: BLE001 -- a missing or failing torch CPU path leaves the port figure
         line["cpu_baseline_pytorch"] = {"unavailable": str(e)[:200]}
+    line.update({"value": value, "ms_per_step": ms,
+                 "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": kind, "sample": sample},
+                 "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
     print(json.dumps(line), flush=True)
 
 
+# ---- secondary workloads (the path's other configurations) -----------------------------------
+SECONDARY_NAMES = {"alexnet": "alexnetbn_32x32_fp64_gradient+hv",
+                   "lenet": "lenet_32x32_fp64_gradient+hv+cg10",
+                   "kfac": "vgg11bn_32x32_fp64_kfac_step(grad,sampled bwd,A/G factors,factorisations,natural gradient)"}
+
+
+def time_secondary(ctx, wl, world, rank, steps, warmup, kfac_solver="cholesky", graphs=True):
+    """Device-timed steps of one secondary workload at the current rank count.
+    alexnet: gradient + Hv, AlexNet-BN, 1024 images over the ranks (strong scaling);
+    lenet: gradient, Hv and 10 Steihaug-CG iterations at 256 images per GPU;
+    kfac: VGG-11-BN KFAC step, 256 images per GPU (gradient, sampled-label backward, A and G
+    factors, 22 damped factorisations, natural gradient; layer-owned factors with ranks)."""
+    import torch
+    import torch.distributed as dist
+    from fitre_b200 import _lib, api
+    from fitre_b200 import _structs as S
+    L = _lib.load()
+    n = {"alexnet": max(1, 1024 // world), "lenet": 256, "kfac": 256}[wl]
+    model = product_model({"kfac": "vgg11"}.get(wl, wl), n)
+    x, y, w, v = synth(model, n, 2234 + rank)
+    _, _, w, v = synth(model, n, 2234)
+    f64 = dict(dtype=torch.float64, device="cuda")
+    X, Y, W, V = (torch.tensor(a, **f64) for a in (x, y, w, v))
+    data = api.make_dataset(W, X, Y, 10)
+    ws = api.Workspace(model, 10)
+    extra = {}
+    if wl == "kfac":
+        ctx.set_kfac_solver(1 if kfac_solver == "cholesky" else 0)
+        ctx.set_graphs(graphs)
+        ctx.set_kfac_distribution(1)  # with ranks: factors stay on a layer's owner rank
+        extra["kfac_solver"], extra["cuda_graphs"] = kfac_solver, bool(graphs)
+        if world > 1:
+            extra["kfac_distribution"] = "layer_owned"
+        info = api.computeKFACStorageIndices(model)
+        kscr = torch.zeros(max(L.fitre_kfac_mem_required(C.byref(model)), ws.dev.numel()), **f64)
+        A, G = torch.zeros(info.OmegaZSize, **f64), torch.zeros(info.LambdaGSize, **f64)
+        Ai, Gi = torch.zeros(info.OmegaZSize, **f64), torch.zeros(info.LambdaGSize, **f64)
+        U, tgt = torch.rand(n, **f64), torch.zeros(n, **f64)
+        md = model.maxDeltaSize + 32
+        e1b, e2b = torch.zeros(md, **f64), torch.zeros(md, **f64)
+        dgrad, ddx = torch.zeros(model.pSize, **f64), torch.zeros(model.zSize, **f64)
+        ngrad = torch.zeros(model.pSize, **f64)
+        iscr = torch.zeros(max(L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model)),
+                               L.fitre_kfac_natural_gradient_mem_required(C.byref(model))), **f64)
+        info.regLambda, info.dampGamma = 1e-3, 0.0
+    elif wl == "lenet":
+        p = torch.zeros(model.pSize, **f64)
+
+    def step():
+        api.computeCNNGradient(ctx, model, data, ws.scratch, ws.z, ws.dx, ws.probs, ws.errors,
+                               ws.gradient, 0, n, 0.0)
+        if wl == "alexnet":
+            api.cnnHv(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, V, ws.hv, 0, n, ws.dev)
+        elif wl == "lenet":
+            api.cnnHv(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, V, ws.hv, 0, n, ws.dev)
+            prm = S.CG_PARAMS()
+            # H + 500 I is positive definite for this net, so all ten iterations run
+            prm.delta, prm.tolerance, prm.maxIterations, prm.weightDecay = 1e3, 1e-30, 10, 500.0
+            api.cgSteihaug(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, ws.gradient, p,
+                           n, ws.dev, prm)
+            extra["cg_iterations"], extra["cg_hv_calls"] = prm.iterations, prm.hvCalls
+        else:
+            api.computeDistributionErrors(ctx, ws.probs, U, tgt, e1b, n, 10)
+            api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
+            # A/G factors and the 22 damped factorisations (inverses or Cholesky), overlapped
+            api.computeFactorsAndInverses(ctx, model, data, ws.z, ddx, n, A, Ai, G, Gi, info, iscr)
+            api.computeNaturalGradient(ctx, model, info, Ai, Gi, ws.gradient, ngrad, iscr)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    try:
+        for _ in range(warmup):
+            step()
+        barrier()
+        l0 = ctx.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = ctx.launches - l0
+    finally:
+        if wl == "kfac":
+            ctx.set_kfac_solver(0)
+            ctx.set_kfac_distribution(0)
+            ctx.set_graphs(True)
+    if world > 1:
+        t = torch.tensor([ms], **f64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    images = n * world
+    return {"workload": SECONDARY_NAMES[wl], "value": images * steps / (ms * 1e-3), "unit": "images/s",
+            "ms_per_step": ms / steps, "steps": steps, "warmup": warmup, "per_gpu_batch": n,
+            "global_batch": images, "scaling": {"alexnet": "strong", "lenet": "weak", "kfac": "weak"}[wl],
+            "gpu_launches": launches, **extra}
+
+
+def multi_gpu_parity(ctx, world, rank):
+    """A small sharded problem against the full-batch oracle: vgg_small with batch norm, 8 images per
+    rank.  Every rank evaluates its shard through the library (sync batch norm, all-reduced
+    gradient / Hv / A factors); rank 0 evaluates the whole batch with the CPU oracle and reports the
+    relative differences.  Outside every timed region."""
+    import torch
+    from fitre_b200 import _lib, api, layout
+    from fitre_b200 import _structs as S
+
+    def small_vgg(batch):  # conv3 + BN + Swish three times, max pooling after the first and third
+        sw, mp = S.CNN_ACT_SWISH, (S.MAX_POOL, 2, 2, 0)
+        convs = [dict(cin=3, cout=8, h=8, w=8, k=3, pad=1, bn=True, act=sw, pool=mp),
+                 dict(cin=8, cout=8, h=4, w=4, k=3, pad=1, bn=True, act=sw, pool=None),
+                 dict(cin=8, cout=16, h=4, w=4, k=3, pad=1, bn=True, act=sw, pool=mp)]
+        return api.finalize(S.describe_model(convs, [(16 * 2 * 2, 10, S.CNN_ACT_NONE)], batch, False))
+
+    per = 8
+    n_glob = per * world
+    full = small_vgg(n_glob)
+    x, y, w, v = synth(full, n_glob, 2024)
+    c0 = full.convLayer[0]
+    xs = layout.shard_batch(x, n_glob, c0.inChannels, c0.height, c0.width, rank, world)
+    ys = np.ascontiguousarray(y[rank * per:(rank + 1) * per])
+    model = small_vgg(per)
+    f64 = dict(dtype=torch.float64, device="cuda")
+    X, Y, W, V = (torch.tensor(a, **f64) for a in (xs, ys, w, v))
+    data = api.make_dataset(W, X, Y, 10)
+    ws = api.Workspace(model, 10)
+    loss = api.computeCNNGradient(ctx, model, data, ws.scratch, ws.z, ws.dx, ws.probs, ws.errors,
+                                  ws.gradient, 0, per, 0.0)
+    api.cnnHv(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, V, ws.hv, 0, per, ws.dev)
+    info = api.computeKFACStorageIndices(model)
+    A = torch.zeros(info.OmegaZSize, **f64)
+    kscr = torch.zeros(_lib.load().fitre_kfac_mem_required(C.byref(model)), **f64)
+    api.computeOmegaZ(ctx, model, data, ws.z, per, A, info, kscr)
+    g, hv, A = ws.gradient.cpu().numpy(), ws.hv.cpu().numpy(), A.cpu().numpy()
+    if rank != 0:
+        return None
+    import oracle_lib as O
+    st = O.gradient(full, x, y, w, 10, n_glob)
+    hv_o = O.hv(full, x, w, 10, n_glob, st, v)
+    info_o = S.KFAC_INFO()
+    O.lib().ora_kfac_storage_indices(C.byref(full), C.byref(info_o))
+    A_o = np.zeros(info_o.OmegaZSize)
+    env = O.make_env()
+    O.lib().ora_kfac_omega_z(C.byref(env), C.byref(full), x, st.z, n_glob, A_o, C.byref(info_o))
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    k1 = full.convLayer[1].inChannels * 9
+    a0 = info_o.OmegaZOffsets[1]
+    return {"case": "vgg_small with batch norm, %d images per rank, %d ranks, against the full-batch CPU oracle" % (per, world),
+            "loss_rel": abs(loss - st.loss) / abs(st.loss), "gradient_rel": rel(g, st.gradient),
+            "hv_rel": rel(hv, hv_o), "kfac_A_layer1_rel": rel(A[a0:a0 + k1 * k1], A_o[a0:a0 + k1 * k1]),
+            "tolerance": 1e-10}
+
+
+# ---- the benchmark ----------------------------------------------------------------------------
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -214,7 +430,7 @@ def run_ours(args):
         sys.stderr.write("bench.py: --gpus %d but WORLD_SIZE %d; using WORLD_SIZE\n" % (args.gpus, world))
 
     n = args.per_gpu_batch
-    model = build_model(n)
+    model = product_model("vgg11", n)
     ctx = api.Context(local)
     if world > 1:
         ctx.comm_init_from_torch()
@@ -278,7 +494,6 @@ def run_ours(args):
     for _ in range(max(1, min(args.warmup, 3))):
         host_step()
     barrier()
-    t0 = time.perf_counter()
     e0.record()
     for _ in range(args.steps):
         host_step()
@@ -292,6 +507,23 @@ def run_ours(args):
     e2e_value = world * n * args.steps / (e2e_ms * 1e-3)
     h2d = 8 * (x.size + y.size + w.size + v.size)
     d2h = 8 * 2 * model.pSize
+
+    # ---- the path's other configurations at this GPU count, and the sharded-parity check
+    secondary, parity = {}, None
+    if not args.no_secondary and args.precision == "fp64":
+        del X, Y, data
+        torch.cuda.empty_cache()
+        for wl, st_, wu_ in (("lenet", 5, 2), ("alexnet", 3, 2), ("kfac", 3, 2)):
+            try:
+                secondary[wl] = time_secondary(ctx, wl, world, rank, st_, wu_)
+            except Exception as e:  # noqa: BLE001 -- a secondary figure must not take the headline down
+                secondary[wl] = {"workload": SECONDARY_NAMES[wl], "error": str(e)[:300]}
+            torch.cuda.empty_cache()
+        if world > 1:
+            try:
+                parity = multi_gpu_parity(ctx, world, rank)
+            except Exception as e:  # noqa: BLE001
+                parity = {"error": str(e)[:300]}
 
     if rank != 0:
         if world > 1:
@@ -314,15 +546,16 @@ def run_ours(args):
 
     achieved = (k_flops / (k_ms * 1e-3)) / 1e12 if k_ms > 0 else None
     gpi, hpi = conv_flops_per_image(model)
+    sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
+    issue_limit = 2.0 * DMMA_FMA_PER_CLK_SM * N_SM * sm_mhz * 1e6 / 1e12
+    cfg = bench_config(n, world)
+    cfg["algorithmic_mflop_per_image"] = {"gradient": gpi / 1e6, "hv": hpi / 1e6}
     line = {
         "metric": "gradient+Hv images/sec", "value": value, "unit": "images/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64" if args.precision == "fp64" else args.precision, "data": "synthetic",
-        "config": {"workload": WORKLOAD, "per_gpu_batch": n, "global_batch": n * world,
-                   "parallelism": "dp%d" % world, "activation": "swish", "batch_norm": True,
-                   "l2": "inputs larger than L2 (z/dx/rz are 1.85 GiB each per GPU)",
-                   "algorithmic_mflop_per_image": {"gradient": gpi / 1e6, "hv": hpi / 1e6}},
+        "config": cfg,
         "roofline": {"bound": "tensor",
                      "kernel": "conv_tma_kernel (TMA-fed implicit-GEMM fprop/dgrad, fp64 DMMA; gather kernel for layer 0)"
                      if args.precision == "fp64" else
@@ -332,6 +565,10 @@ def run_ours(args):
                      "achieved": achieved, "peak": dgemm_tflops, "unit": "TFLOP/s",
                      "frac": (achieved / dgemm_tflops) if achieved else None,
                      "peak_source": "cuBLAS DGEMM 8192^3 measured in this run (MEASURED_PEAKS.json has no fp64 figure)",
+                     # the same against the instruction-issue limit of the fp64 tensor pipe, which no
+                     # measured probe can flatter: 64 FMA per clock per SM x 148 SMs x the sampled SM clock
+                     "issue_limit": issue_limit,
+                     "frac_of_issue_limit": (achieved / issue_limit) if achieved else None,
                      "launches": k_n, "avg_launch_ms": k_ms / max(k_n, 1),
                      "share_of_step": k_ms / ms,
                      # dram__bytes_read+write of the layer-3 forward launch, ncu capture at 256
@@ -347,18 +584,27 @@ def run_ours(args):
         "clocks": clocks,
         "per_gpu_algorithmic_tflops": (gpi + hpi) * n * args.steps / (ms * 1e-3) / 1e12,
     }
+    if secondary:
+        line["secondary"] = secondary
+    if parity is not None:
+        line["multi_gpu_parity"] = parity
     if world == 1 and not args.skip_cpu:
-        r, dt = cpu_oracle_rate(CPU_SAMPLE_IMAGES)
-        line["cpu_baseline"] = {"value": r, "unit": "images/s", "cores": os.cpu_count() or 1,
-                                "kind": "port",
-                                "sample": "%d images of the same VGG-11-BN fp64 gradient+Hv step "
-                                          "(%.1f s of CPU work)" % (CPU_SAMPLE_IMAGES, dt)}
-        try:  # the same step in PyTorch on the host cores, reported beside the port
-            rt, dtt = cpu_pytorch_rate(TORCH_SAMPLE_IMAGES)
-            line["cpu_baseline_pytorch"] = {
-                "value": rt, "unit": "images/s", "cores": os.cpu_count() or 1,
-                "sample": "%d images, fp64 autograd gradient + double-backward Hv (%.1f s)"
-                          % (TORCH_SAMPLE_IMAGES, dtt)}
+        r, dt = cpu_oracle_rate(PORT_SAMPLE_IMAGES)
+        port = {"value": r, "unit": "images/s", "cores": host_threads(), "kind": "port",
+                "sample": "%d images of the same VGG-11-BN fp64 gradient+Hv step, C + OpenMP port of the "
+                          "reference's CUDA host code (%.1f s of CPU work)" % (PORT_SAMPLE_IMAGES, dt)}
+        line["cpu_baseline"] = port
+        try:  # the same step in PyTorch on the host cores; the faster leg is the reported baseline
+            case = cpu_pytorch_case(TORCH_SAMPLE_IMAGES)
+            dtt = cpu_pytorch_step(case)
+            rt = TORCH_SAMPLE_IMAGES / dtt
+            torch_leg = {"value": rt, "unit": "images/s", "cores": host_threads(), "kind": "port",
+                         "sample": "%d images, fp64 autograd gradient + double-backward Hv in PyTorch on the "
+                                   "host cores, the operator of the reference's pytorch/ path (%.1f s)"
+                                   % (TORCH_SAMPLE_IMAGES, dtt)}
+            line["cpu_baseline_pytorch"] = torch_leg
+            if rt > r:
+                line["cpu_baseline"], line["cpu_baseline_port"] = torch_leg, port
         except Exception as e:  # noqa: BLE001 -- a missing or failing torch CPU path must not fail the bench
             line["cpu_baseline_pytorch"] = {"unavailable": str(e)[:200]}
     print(json.dumps(line), flush=True)
@@ -367,16 +613,11 @@ def run_ours(args):
 
 
 def run_extra(args):
-    """Secondary workloads (the other configurations of the path): one JSON line each, device
-    timing only.  alexnet: gradient+Hv, AlexNet-BN, 1024 images over the ranks; lenet: gradient,
-    Hv and 10 Steihaug-CG iterations at 256 images; kfac: VGG-11-BN KFAC factor step (gradient,
-    sampled-label backward, A and G factors), 256 images per GPU."""
-    import ctypes as C
+    """One secondary workload by itself (`--workload alexnet|lenet|kfac`): one JSON line, device
+    timing only."""
     import torch
     import torch.distributed as dist
-    import nets
-    from fitre_b200 import _lib, api
-    from fitre_b200 import _structs as S
+    from fitre_b200 import api
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -386,102 +627,18 @@ def run_extra(args):
     ctx = api.Context(local)
     if world > 1:
         ctx.comm_init_from_torch()
-    wl = args.workload
-    n = {"alexnet": 1024 // world, "lenet": 256, "kfac": 256}[wl]
-    model = {"alexnet": nets.alexnet, "lenet": nets.lenet, "kfac": nets.vgg11}[wl](n)
-    api.finalize(model)
-    x, y, w, v = synth(model, n, 2234 + rank)
-    _, _, w, v = synth(model, n, 2234)
-    f64 = dict(dtype=torch.float64, device="cuda")
-    X, Y, W, V = (torch.tensor(a, **f64) for a in (x, y, w, v))
-    data = api.make_dataset(W, X, Y, 10)
-    ws = api.Workspace(model, 10)
-    extra = {}
-    if wl == "kfac":
-        ctx.set_kfac_solver(1 if args.kfac_solver == "cholesky" else 0)
-        ctx.set_graphs(not args.no_graphs)
-        ctx.set_kfac_distribution(1)  # with ranks: factors stay on a layer's owner rank
-        extra["kfac_solver"], extra["cuda_graphs"] = args.kfac_solver, not args.no_graphs
-        if world > 1:
-            extra["kfac_distribution"] = "layer_owned"
-        info = api.computeKFACStorageIndices(model)
-        need = _lib.load().fitre_kfac_mem_required(C.byref(model))
-        kscr = torch.zeros(max(need, ws.dev.numel()), **f64)
-        A = torch.zeros(info.OmegaZSize, **f64)
-        G = torch.zeros(info.LambdaGSize, **f64)
-        U = torch.rand(n, **f64)
-        tgt = torch.zeros(n, **f64)
-        md = model.maxDeltaSize + 32
-        e1b, e2b = torch.zeros(md, **f64), torch.zeros(md, **f64)
-        dgrad, ddx = torch.zeros(model.pSize, **f64), torch.zeros(model.zSize, **f64)
-        Ai, Gi = torch.zeros(info.OmegaZSize, **f64), torch.zeros(info.LambdaGSize, **f64)
-        ngrad = torch.zeros(model.pSize, **f64)
-        L = _lib.load()
-        iscr = torch.zeros(max(L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model)),
-                               L.fitre_kfac_natural_gradient_mem_required(C.byref(model))), **f64)
-        info.regLambda, info.dampGamma = 1e-3, 0.0
-        blocks = []
-        for l in range(model.cLayers + model.lLayers):
-            if l < model.cLayers:
-                c = model.convLayer[l]
-                kb, co = c.inChannels * c.kSize ** 2 + model.bias, c.outChannels
-            else:
-                f = model.fcLayer[l - model.cLayers]
-                kb, co = f.in_ + model.bias, f.out
-            blocks.append((kb, info.OmegaZOffsets[l], A, Ai))
-            blocks.append((co, info.LambdaGOffsets[l], G, Gi))
-
-    def step():
-        api.computeCNNGradient(ctx, model, data, ws.scratch, ws.z, ws.dx, ws.probs, ws.errors,
-                               ws.gradient, 0, n, 0.0)
-        if wl == "alexnet":
-            api.cnnHv(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, V, ws.hv, 0, n, ws.dev)
-        elif wl == "lenet":
-            api.cnnHv(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, V, ws.hv, 0, n, ws.dev)
-            prm = S.CG_PARAMS()
-            prm.delta, prm.tolerance, prm.maxIterations, prm.weightDecay = 1e3, 1e-30, 10, 1.0
-            api.cgSteihaug(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, ws.gradient, ws.hv,
-                           n, ws.dev, prm)
-            extra["cg_iterations"], extra["cg_hv_calls"] = prm.iterations, prm.hvCalls
-        else:
-            api.computeDistributionErrors(ctx, ws.probs, U, tgt, e1b, n, 10)
-            api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
-            # A/G factors and the 22 damped factorisations (inverses or Cholesky), overlapped
-            api.computeFactorsAndInverses(ctx, model, data, ws.z, ddx, n, A, Ai, G, Gi, info, iscr)
-            api.computeNaturalGradient(ctx, model, info, Ai, Gi, ws.gradient, ngrad, iscr)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    l0 = ctx.launches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    r = time_secondary(ctx, args.workload, world, rank, args.steps, args.warmup, args.kfac_solver,
+                       not args.no_graphs)
     if world > 1:
-        t = torch.tensor([ms], **f64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
         dist.destroy_process_group()
     if rank == 0:
-        names = {"alexnet": "alexnetbn_32x32_fp64_gradient+hv",
-                 "lenet": "lenet_32x32_fp64_gradient+hv+cg10",
-                 "kfac": "vgg11bn_32x32_fp64_kfac_step(grad,sampled bwd,A/G factors,inverses,natural gradient)"}
+        cfg = {k: r[k] for k in r if k not in ("value", "unit", "ms_per_step", "steps", "warmup", "gpu_launches",
+                                                "scaling")}
         print(json.dumps({
-            "metric": "images/sec", "value": world * n * args.steps / (ms * 1e-3), "unit": "images/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong" if wl == "alexnet" else "weak", "dtype": "f64", "data": "synthetic",
-            "config": dict({"workload": names[wl], "per_gpu_batch": n}, **extra),
-            "gpu_launches": ctx.launches - l0}), flush=True)
+            "metric": "images/sec", "value": r["value"], "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": r["scaling"], "dtype": "f64", "data": "synthetic",
+            "config": cfg, "gpu_launches": r["gpu_launches"]}), flush=True)
 
 
 def run_fitre(args):
@@ -489,11 +646,8 @@ def run_fitre(args):
     minibatch of the whole loop body -- device minibatch assembly with augmentation, gradient,
     sampled-label backward, A/G factors, damped inverses, natural gradient, two quadratic models
     (two Hessian-vector products), weight update, re-evaluation -- as the library's own loop runs it."""
-    import ctypes as C
-    import numpy as np
     import torch
     import torch.distributed as dist
-    import nets
     from fitre_b200 import _lib, api
     from fitre_b200 import _structs as S
     from fitre_b200 import layout
@@ -509,8 +663,7 @@ def run_fitre(args):
     ctx.set_kfac_solver(1 if args.kfac_solver == "cholesky" else 0)
     ctx.set_graphs(not args.no_graphs)
     n = 256
-    model = nets.vgg11(n)
-    api.finalize(model)
+    model = product_model("vgg11", n)
     mbs = args.warmup + args.steps
     n_train = (mbs + 1) * n * world        # the loop stops before the batch that reaches the end
     rng = np.random.default_rng(99)        # same synthetic CIFAR-shaped set on every rank
@@ -566,7 +719,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="vgg11", choices=["vgg11", "alexnet", "lenet", "kfac", "fitre"],
                     help="vgg11 = the benchmark (default); the others print a device-timed line "
-                         "for the path's other configurations")
+                         "for one of the path's other configurations by itself")
     ap.add_argument("--per-gpu-batch", type=int, default=PER_GPU_BATCH,
                     help="images per GPU (default 512, the benchmark shape; smaller values are "
                          "for profiler captures only)")
@@ -582,6 +735,8 @@ def main():
                          "sequences kernel by kernel instead of replaying their CUDA graphs")
     ap.add_argument("--skip-cpu", action="store_true",
                     help="leave the CPU baseline leg out (profiling runs)")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="leave the secondary workloads and the sharded-parity check out (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -16,7 +16,7 @@ CNN_ACT_NONE, CNN_ACT_SOFTPLUS, CNN_ACT_ELU, CNN_ACT_RELU, CNN_ACT_SWISH = 10, 1
 MAX_POOL, AVG_POOL, NO_POOL = 0, 1, 2
 
 # status codes
-OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_COMM, ERR_NOT_CONVERGED, ERR_TOO_LARGE = range(8)
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_COMM, ERR_NOT_CONVERGED, ERR_TOO_LARGE, ERR_NOT_FINITE = range(9)
 
 CG_CONVERGED, CG_NEG_CURVATURE, CG_HIT_BOUNDARY, CG_MAX_ITERS = range(4)
 

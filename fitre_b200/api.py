@@ -76,6 +76,10 @@ class Context:
         does (functions/model_reduction.cu:50-52); 0: weightDecay * vector (pytorch/peng/utils.py:77)."""
         self.check(self.lib.fitre_set_reference_quadratic_damping(self.h, int(bool(on))))
 
+    def set_scratch_limit(self, doubles):
+        """Doubles available behind the scratch pointers of the following calls (0 = unchecked)."""
+        self.check(self.lib.fitre_set_scratch_limit(self.h, int(doubles)))
+
     def kernel_launches(self, name):
         """Launches issued so far of the kernel called `name` (e.g. "conv_tma_kernel")."""
         return int(self.lib.fitre_kernel_launches(self.h, name.encode()))
@@ -129,6 +133,23 @@ class Context:
         raw = bytes(t.cpu().tolist())
         idbuf = (C.c_ubyte * 128).from_buffer_copy(raw)
         self.check(self.lib.fitre_comm_init(self.h, C.cast(idbuf, C.c_void_p), rank, world))
+
+    def set_comm_timeout(self, seconds):
+        """Bound (seconds) of communicator set-up and of every host wait on a collective."""
+        self.check(self.lib.fitre_set_comm_timeout(self.h, float(seconds)))
+
+    def comm_init(self, unique_id_bytes, rank, world):
+        """fitre_comm_init with an id obtained from comm_unique_id() on rank 0."""
+        idbuf = (C.c_ubyte * 128).from_buffer_copy(bytes(unique_id_bytes))
+        self.check(self.lib.fitre_comm_init(self.h, C.cast(idbuf, C.c_void_p), int(rank), int(world)))
+
+    @staticmethod
+    def comm_unique_id():
+        buf = (C.c_ubyte * 128)()
+        rc = _lib.load().fitre_comm_unique_id(C.cast(buf, C.c_void_p))
+        if rc != S.OK:
+            raise FitreError(rc, "fitre_comm_unique_id failed")
+        return bytes(buf)
 
     @property
     def world(self):

@@ -39,7 +39,7 @@ namespace fitre {
 void check_device_error(fitre_context *ctx) {
     FITRE_CUDA(cudaMemcpyAsync(ctx->pinned + 200, ctx->dscal + 4000, sizeof(double),
                                cudaMemcpyDeviceToHost, ctx->stream));
-    FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+    stream_wait(ctx, ctx->stream);
     int word;
     std::memcpy(&word, ctx->pinned + 200, sizeof(int));
     if (word != 0) {
@@ -105,7 +105,10 @@ int fitre_context_create(fitre_context **out, int device, void *stream) {
 int fitre_context_destroy(fitre_context *ctx) {
     if (!ctx) return FITRE_OK;
     cudaSetDevice(ctx->device);
-    cudaStreamSynchronize(ctx->stream);
+    try {
+        stream_wait(ctx, ctx->stream);  // bounded when a communicator exists
+    } catch (...) {
+    }
     try {
         comm_destroy(ctx);
     } catch (...) {
@@ -148,6 +151,12 @@ long long fitre_launch_count(const fitre_context *ctx) { return ctx ? ctx->launc
 int fitre_set_reference_softmax(fitre_context *ctx, int on) {
     if (!ctx) return FITRE_ERR_BAD_ARG;
     ctx->ref_softmax = on ? 1 : 0;
+    return FITRE_OK;
+}
+
+int fitre_set_scratch_limit(fitre_context *ctx, long doubles) {
+    if (!ctx || doubles < 0) return FITRE_ERR_BAD_ARG;
+    ctx->scratch_limit = doubles;
     return FITRE_OK;
 }
 
@@ -209,7 +218,7 @@ int fitre_profile_enable(fitre_context *ctx, int on) {
 int fitre_profile_read(fitre_context *ctx, int kind, double *ms, double *flops, long *launches) {
     return guarded(ctx, [&] {
         FITRE_REQUIRE(kind >= 0 && kind < PROF_KINDS, FITRE_ERR_BAD_ARG, "bad kernel class");
-        FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+        stream_wait(ctx, ctx->stream);
         double t = 0.0, f = 0.0;
         long n = 0;
         std::vector<fitre_context::ProfRec> keep;
@@ -248,6 +257,11 @@ int fitre_comm_init(fitre_context *ctx, const void *id, int rank, int world) {
     });
 }
 int fitre_comm_world(const fitre_context *ctx) { return ctx ? ctx->world : 0; }
+int fitre_set_comm_timeout(fitre_context *ctx, double seconds) {
+    if (!ctx || !(seconds > 0.0)) return FITRE_ERR_BAD_ARG;
+    ctx->comm_timeout_s = seconds;
+    return FITRE_OK;
+}
 
 long fitre_cnn_forward_mem_required(const CNN_MODEL *m) { return m ? forward_scratch(m) : -1; }
 long fitre_cnn_backward_mem_required(const CNN_MODEL *m) { return m ? backward_scratch(m) : -1; }
@@ -274,10 +288,12 @@ int fitre_cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
                           evalType == FITRE_MODEL_TEST_ACCURACY,
                       FITRE_ERR_BAD_ARG, "unknown EVAL_TYPE");
         model_check_batch(m, curBatchSize);
+        require_scratch(ctx, forward_scratch(m), "fitre_cnn_forward");
         // the two accuracy modes normalise with the running statistics (functions/dev_batch_norm.cu:386-392)
         double loss = cnn_forward(ctx, m, data, scratch->nextDevPtr, z, probs, errors, curBatchSize, true,
                                   evalType != FITRE_MODEL_TRAIN);
         if (loss_host) *loss_host = loss;
+        FITRE_REQUIRE(std::isfinite(loss), FITRE_ERR_NOT_FINITE, "the loss is not finite (NaN or Inf in the batch or the weights)");
     });
 }
 
@@ -289,6 +305,7 @@ int fitre_cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATA
     return guarded(ctx, [&] {
         require_ptrs({m, data, devPtr, z, gradient, dx, delta, delta_new});
         model_check_batch(m, batchSize);
+        require_scratch(ctx, backward_scratch(m), "fitre_cnn_backward");
         cnn_backward(ctx, m, data, devPtr, z, gradient, dx, delta, delta_new, batchSize);
     });
 }
@@ -302,6 +319,7 @@ int fitre_compute_cnn_gradient(fitre_context *ctx, const CNN_MODEL *m, const DEV
         require_ptrs({m, data, scratch, z, dx, probs, lossFuncErrors, gradient});
         require_ptrs({data->weights, data->currentBatch, data->sampledTrainY, scratch->nextDevPtr});
         model_check_batch(m, curBatchSize);
+        require_scratch(ctx, fitre_cnn_gradient_mem_required(m), "fitre_compute_cnn_gradient");
         // functions/cnn_gradient.cu:24-31: two error buffers in front of the pass scratch
         const long md = align32(max_delta_elems(m));
         double *errors = scratch->nextDevPtr;
@@ -317,7 +335,9 @@ int fitre_compute_cnn_gradient(fitre_context *ctx, const CNN_MODEL *m, const DEV
         FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost,
                                    ctx->stream));
         check_device_error(ctx);
-        if (loss_host) *loss_host = ctx->pinned[0] / ((double)curBatchSize * ctx->world);
+        const double loss = ctx->pinned[0] / ((double)curBatchSize * ctx->world);
+        if (loss_host) *loss_host = loss;
+        FITRE_REQUIRE(std::isfinite(loss), FITRE_ERR_NOT_FINITE, "the loss is not finite (NaN or Inf in the batch or the weights)");
     });
 }
 
@@ -328,6 +348,7 @@ int fitre_cnn_rop_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_D
     return guarded(ctx, [&] {
         require_ptrs({m, data, z, vector, rz, devPtr});
         model_check_batch(m, curBatchSize);
+        require_scratch(ctx, rop_forward_scratch(m), "fitre_cnn_rop_forward");
         cnn_rop_forward(ctx, m, data, z, vector, rz, curBatchSize, devPtr);
     });
 }
@@ -340,6 +361,7 @@ int fitre_cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_
     return guarded(ctx, [&] {
         require_ptrs({m, data, z, dx, lossFuncErrors, rError, rz, vector, hv, devPtr});
         model_check_batch(m, curBatchSize);
+        require_scratch(ctx, rop_backward_scratch(m), "fitre_cnn_rop_backward");
         cnn_rop_backward(ctx, m, data, z, dx, lossFuncErrors, rError, rz, vector, hv, curBatchSize, devPtr);
     });
 }
@@ -351,6 +373,7 @@ int fitre_cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *d
     return guarded(ctx, [&] {
         require_ptrs({m, data, z, probs, lossFuncErrors, dx, vector, hv, devPtr});
         model_check_batch(m, curBatchSize);
+        require_scratch(ctx, fitre_cnn_hv_mem_required(m), "fitre_cnn_hv");
         cnn_hv(ctx, m, data, z, probs, lossFuncErrors, dx, vector, hv, curBatchSize, devPtr);
         check_device_error(ctx);
     });
@@ -374,6 +397,7 @@ int fitre_compute_quadratic_model(fitre_context *ctx, const CNN_MODEL *m,
     return guarded(ctx, [&] {
         require_ptrs({m, data, z, probs, lossFuncErrors, dx, gradient, vector, devPtr});
         model_check_batch(m, curBatchSize);
+        require_scratch(ctx, fitre_quadratic_model_mem_required(m), "fitre_compute_quadratic_model");
         const long P = m->pSize;
         double *hv = devPtr;
         double *next = hv + align32(P);
@@ -406,6 +430,7 @@ int fitre_cg_steihaug(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
         model_check_batch(m, curBatchSize);
         FITRE_REQUIRE(prm->maxIterations >= 1 && prm->delta > 0, FITRE_ERR_BAD_ARG, "bad CG parameters");
         const long P = m->pSize, Pa = align32(P);
+        require_scratch(ctx, 4 * Pa + fitre_cnn_hv_mem_required(m), "fitre_cg_steihaug");
         double *zs = devPtr, *rs = zs + Pa, *ds = rs + Pa, *Hd = ds + Pa, *ws = Hd + Pa;
         const double delta = prm->delta, wd = prm->weightDecay;
         vec_fill(ctx, P, 0.0, zs);
@@ -561,7 +586,7 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         if (sent_from > 0)
             FITRE_CUDA(cudaMemcpyAsync(hv_host, hv, sizeof(double) * sent_from, cudaMemcpyDeviceToHost, st));
         FITRE_CUDA(cudaEventRecord(ctx->ev_down, cs));
-        FITRE_CUDA(cudaStreamSynchronize(st));
+        stream_wait(ctx, st);
         FITRE_CUDA(cudaEventSynchronize(ctx->ev_down));
         if (loss_host) *loss_host = loss;
     });

@@ -3,20 +3,32 @@
 // disabled cudaMemcpyPeer offload of solvers/kfac_thread.cu:94-134), so this layer has no
 // counterpart there.  NCCL is loaded at run time (dlopen) the first time a communicator is
 // requested, so single-GPU users need no NCCL installation.
+//
+// Failure handling is on the host.  The communicator is created by a helper thread so that a
+// peer that never joins costs a bounded wait and a status, not a hang.  With a communicator,
+// every host wait on the context's stream polls the stream and ncclCommGetAsyncError; a
+// reported error or an expired deadline aborts the communicator (ncclCommAbort stops NCCL's
+// kernels, the CUDA context stays usable) and the call returns FITRE_ERR_COMM.
 #include <dlfcn.h>
 
+#include <chrono>
+#include <condition_variable>
+#include <cstdlib>
 #include <cstring>
+#include <memory>
+#include <mutex>
+#include <thread>
 
 #include "common.h"
 
 namespace fitre {
 
 namespace {
-// the slice of the NCCL C API used here (nccl.h, stable since NCCL 2.0)
+// the slice of the NCCL C API used here (nccl.h, stable since NCCL 2.4)
 typedef struct ncclComm *ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
 typedef int ncclResult_t;
-enum { ncclSuccess = 0 };
+enum { ncclSuccess = 0, ncclInProgress = 7 };
 enum { ncclFloat64 = 8 };
 enum { ncclSum = 0 };
 
@@ -25,6 +37,8 @@ struct Api {
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Reduce)(const void *, void *, size_t, int, int, int, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
@@ -33,52 +47,128 @@ struct Api {
 Api &api() {
     static Api a;
     if (a.handle) return a;
-    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    // FITRE_NCCL_LIBRARY names the library to load instead of the system's libnccl.so.2
+    const char *over = std::getenv("FITRE_NCCL_LIBRARY");
+    const char *names[] = {over && *over ? over : "libnccl.so.2", "libnccl.so"};
     for (const char *n : names) {
         a.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
-        if (a.handle) break;
+        if (a.handle || (over && *over)) break;
     }
-    FITRE_REQUIRE(a.handle != nullptr, FITRE_ERR_COMM, "cannot load libnccl.so.2");
+    FITRE_REQUIRE(a.handle != nullptr, FITRE_ERR_COMM, "cannot load the NCCL library (libnccl.so.2)");
     a.GetUniqueId = (decltype(a.GetUniqueId))dlsym(a.handle, "ncclGetUniqueId");
     a.CommInitRank = (decltype(a.CommInitRank))dlsym(a.handle, "ncclCommInitRank");
     a.CommDestroy = (decltype(a.CommDestroy))dlsym(a.handle, "ncclCommDestroy");
+    a.CommAbort = (decltype(a.CommAbort))dlsym(a.handle, "ncclCommAbort");
+    a.CommGetAsyncError = (decltype(a.CommGetAsyncError))dlsym(a.handle, "ncclCommGetAsyncError");
     a.AllReduce = (decltype(a.AllReduce))dlsym(a.handle, "ncclAllReduce");
     a.Reduce = (decltype(a.Reduce))dlsym(a.handle, "ncclReduce");
     a.GetErrorString = (decltype(a.GetErrorString))dlsym(a.handle, "ncclGetErrorString");
-    FITRE_REQUIRE(a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.Reduce,
-                  FITRE_ERR_COMM, "libnccl lacks a required symbol");
+    const bool ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.CommAbort && a.CommGetAsyncError &&
+                    a.AllReduce && a.Reduce;
+    if (!ok) {
+        a.handle = nullptr;
+        throw Error(FITRE_ERR_COMM, "the NCCL library lacks a required symbol");
+    }
     return a;
 }
 
-void check(ncclResult_t r, const char *what) {
-    if (r != ncclSuccess) {
-        const char *s = api().GetErrorString ? api().GetErrorString(r) : "?";
-        throw Error(FITRE_ERR_COMM, std::string(what) + ": " + s);
-    }
+std::string nccl_text(ncclResult_t r) {
+    const char *s = api().GetErrorString ? api().GetErrorString(r) : nullptr;
+    return s ? s : ("NCCL result " + std::to_string(r));
 }
+
+void check(ncclResult_t r, const char *what) {
+    if (r != ncclSuccess) throw Error(FITRE_ERR_COMM, std::string(what) + ": " + nccl_text(r));
+}
+
+// State shared with the set-up thread; it outlives the context when the set-up never returns.
+struct InitJob {
+    std::mutex mu;
+    std::condition_variable cv;
+    bool done = false, abandoned = false;
+    ncclResult_t result = ncclSuccess;
+    ncclComm_t comm = nullptr;
+};
 }  // namespace
 
 struct Comm {
     ncclComm_t comm = nullptr;
+    bool aborted = false;
 };
+
+namespace {
+// Stops NCCL's work on this communicator and marks it unusable; later collectives fail fast.
+void abort_comm(fitre_context *ctx) {
+    if (!ctx->comm || ctx->comm->aborted) return;
+    ctx->comm->aborted = true;
+    if (ctx->comm->comm) api().CommAbort(ctx->comm->comm);
+    ctx->comm->comm = nullptr;
+}
+
+ncclComm_t live_comm(fitre_context *ctx) {
+    FITRE_REQUIRE(ctx->comm && !ctx->comm->aborted && ctx->comm->comm, FITRE_ERR_COMM,
+                  "the communicator was aborted after an error; create a new one with fitre_comm_init");
+    return ctx->comm->comm;
+}
+}  // namespace
 
 void comm_allreduce_sum(fitre_context *ctx, double *dev_buf, size_t n) {
     if (ctx->world <= 1 || !ctx->comm || n == 0) return;
-    check(api().AllReduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, ctx->comm->comm, ctx->stream),
-          "ncclAllReduce");
+    check(api().AllReduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, live_comm(ctx), ctx->stream), "ncclAllReduce");
     ctx->launches += 1;  // NCCL's kernel; counted so the launch figure covers the whole step
 }
 
 // sum over the ranks, result on `root` only (the buffers of the other ranks are left as they were)
 void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root) {
     if (ctx->world <= 1 || !ctx->comm || n == 0) return;
-    check(api().Reduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, root, ctx->comm->comm, ctx->stream), "ncclReduce");
+    check(api().Reduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, root, live_comm(ctx), ctx->stream), "ncclReduce");
     ctx->launches += 1;
+}
+
+// Host wait for everything queued on `stream` (the context's stream, or another stream whose
+// work depends on it).  Without a communicator this is cudaStreamSynchronize.  With one, the
+// stream is polled together with the communicator's asynchronous error state, for at most
+// ctx->comm_timeout_s seconds: a lost peer leaves NCCL's kernel spinning on the device, which a
+// plain synchronize would wait for without end.
+void stream_wait(fitre_context *ctx, cudaStream_t stream) {
+    if (ctx->world <= 1 || !ctx->comm || ctx->comm->aborted) {
+        FITRE_CUDA(cudaStreamSynchronize(stream));
+        return;
+    }
+    using clock = std::chrono::steady_clock;
+    const auto deadline = clock::now() + std::chrono::duration<double>(ctx->comm_timeout_s);
+    long spins = 0;
+    for (;;) {
+        const cudaError_t e = cudaStreamQuery(stream);
+        if (e == cudaSuccess) return;
+        if (e != cudaErrorNotReady)
+            throw Error(FITRE_ERR_CUDA, std::string("cudaStreamQuery: ") + cudaGetErrorString(e));
+        ++spins;
+        if ((spins & 63) == 0) {
+            ncclResult_t state = ncclSuccess;
+            const ncclResult_t q = api().CommGetAsyncError(ctx->comm->comm, &state);
+            if (q != ncclSuccess || (state != ncclSuccess && state != ncclInProgress)) {
+                const std::string why = nccl_text(q != ncclSuccess ? q : state);
+                abort_comm(ctx);
+                throw Error(FITRE_ERR_COMM, "NCCL reported an asynchronous error: " + why);
+            }
+            if (clock::now() > deadline) {
+                abort_comm(ctx);
+                throw Error(FITRE_ERR_COMM, "a collective did not finish within " +
+                                                std::to_string(ctx->comm_timeout_s) +
+                                                " s (lost peer?); the communicator was aborted");
+            }
+        }
+        if (spins > 4096)
+            std::this_thread::sleep_for(std::chrono::microseconds(20));
+        else
+            std::this_thread::yield();
+    }
 }
 
 void comm_destroy(fitre_context *ctx) {
     if (ctx->comm) {
-        if (ctx->comm->comm) api().CommDestroy(ctx->comm->comm);
+        if (ctx->comm->comm && !ctx->comm->aborted) api().CommDestroy(ctx->comm->comm);
         delete ctx->comm;
         ctx->comm = nullptr;
     }
@@ -96,11 +186,40 @@ void comm_init(fitre_context *ctx, const void *id128, int rank, int world) {
     FITRE_REQUIRE(world >= 1 && rank >= 0 && rank < world, FITRE_ERR_BAD_ARG, "bad rank/world");
     comm_destroy(ctx);
     if (world == 1) return;
+    Api &a = api();
     ncclUniqueId id;
     std::memcpy(&id, id128, sizeof(id));
-    FITRE_CUDA(cudaSetDevice(ctx->device));
+    // ncclCommInitRank blocks until every rank has joined.  It runs on a helper thread; this
+    // thread waits for it at most comm_timeout_s seconds.  If the time runs out the job is
+    // abandoned: should the set-up ever return, the helper aborts the communicator it got.
+    auto job = std::make_shared<InitJob>();
+    const int device = ctx->device;
+    std::thread([job, id, rank, world, device, &a]() {
+        cudaSetDevice(device);
+        ncclComm_t c = nullptr;
+        const ncclResult_t r = a.CommInitRank(&c, world, id, rank);
+        std::unique_lock<std::mutex> lk(job->mu);
+        job->result = r;
+        job->comm = c;
+        job->done = true;
+        if (job->abandoned && r == ncclSuccess && c) a.CommAbort(c);
+        lk.unlock();
+        job->cv.notify_all();
+    }).detach();
+    {
+        std::unique_lock<std::mutex> lk(job->mu);
+        const bool in_time = job->cv.wait_for(lk, std::chrono::duration<double>(ctx->comm_timeout_s),
+                                              [&] { return job->done; });
+        if (!in_time) {
+            job->abandoned = true;
+            throw Error(FITRE_ERR_COMM, "communicator set-up did not finish within " +
+                                            std::to_string(ctx->comm_timeout_s) +
+                                            " s: a rank did not join");
+        }
+    }
+    check(job->result, "ncclCommInitRank");
     ctx->comm = new Comm();
-    check(api().CommInitRank(&ctx->comm->comm, world, id, rank), "ncclCommInitRank");
+    ctx->comm->comm = job->comm;
     ctx->rank = rank;
     ctx->world = world;
 }

@@ -48,6 +48,7 @@ struct fitre_context {
     long long launches = 0;
     std::string err;
     int ref_softmax = 1;
+    long scratch_limit = 0;     // doubles behind the caller's scratch pointer (0 = unknown, unchecked)
     int ref_quadratic = 1;      // quadratic model damps with lambda * weights (reference) or lambda * vector
     int precision = 0;          // FITRE_PRECISION_* (convolution products)
     int kfac_solver = 0;        // FITRE_KFAC_SOLVER_* (what the A-factor slots hold)
@@ -57,6 +58,7 @@ struct fitre_context {
     double *dscal = nullptr;    // 4096 device doubles (scalar reductions)
     fitre::Comm *comm = nullptr;
     int rank = 0, world = 1;
+    double comm_timeout_s = 300.0;  // bound of communicator set-up and of every host wait on a collective
     // workspace of the host-buffer entry point (allocated on first use, reused)
     double *host_ws = nullptr;
     size_t host_ws_doubles = 0;
@@ -115,6 +117,14 @@ inline void check_launch(fitre_context *ctx, const char *name) {
     ctx->launch_names.emplace_back(name, 1);
 }
 
+// A call that needs `need` doubles of caller scratch: refused when the caller declared fewer.
+inline void require_scratch(const fitre_context *ctx, long need, const char *what) {
+    if (ctx->scratch_limit > 0 && need > ctx->scratch_limit)
+        throw Error(FITRE_ERR_WORKSPACE, std::string(what) + " needs " + std::to_string(need) +
+                                             " doubles of scratch, the caller declared " +
+                                             std::to_string(ctx->scratch_limit));
+}
+
 // Kernel classes the optional event timing distinguishes.
 enum { PROF_CONV_IGEMM = 0, PROF_CONV_WGRAD = 1, PROF_KINDS = 2 };
 // Brackets one launch with events when profiling is on (no-op otherwise).
@@ -129,6 +139,8 @@ struct ProfScope {
 void comm_allreduce_sum(fitre_context *ctx, double *dev_buf, size_t n);
 void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root);
 void comm_destroy(fitre_context *ctx);
+// host wait on a stream; with a communicator it also watches NCCL's error state and a deadline
+void stream_wait(fitre_context *ctx, cudaStream_t stream);
 
 // ---- model.cpp ----
 struct ConvGeom {

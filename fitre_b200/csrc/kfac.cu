@@ -209,6 +209,7 @@ extern "C" int fitre_kfac_omega_z(fitre_context *ctx, const CNN_MODEL *m, const 
                                   real *devPtr) {
     KFAC_ENTRY_BEGIN
     FITRE_REQUIRE(m && data && z && omegaZ && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    require_scratch(ctx, fitre_kfac_mem_required(m), "fitre_kfac_omega_z");
     model_check_batch(m, samples);
     omega_z_impl(ctx, m, data->currentBatch, z, false, samples, omegaZ, info, devPtr);
     check_device_error(ctx);  // the TMA-fed A-factor kernel has bounded waits
@@ -219,6 +220,7 @@ extern "C" int fitre_kfac_lambda_delta(fitre_context *ctx, const CNN_MODEL *m, c
                                        real *lambdaG, const FITRE_KFAC_INFO *info, real *devPtr) {
     KFAC_ENTRY_BEGIN
     FITRE_REQUIRE(m && dx && lambdaG && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    require_scratch(ctx, fitre_kfac_mem_required(m), "fitre_kfac_lambda_delta");
     model_check_batch(m, samples);
     lambda_delta_impl(ctx, m, dx, false, samples, lambdaG, info, devPtr);
     KFAC_ENTRY_END
@@ -285,6 +287,7 @@ extern "C" int fitre_kfac_omega_z_damped(fitre_context *ctx, const CNN_MODEL *m,
                                          const FITRE_KFAC_INFO *info, real *devPtr) {
     KFAC_ENTRY_BEGIN
     FITRE_REQUIRE(m && dampedInput && dampedZ && omegaZ && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    require_scratch(ctx, fitre_kfac_mem_required(m), "fitre_kfac_omega_z_damped");
     model_check_batch(m, samples);
     omega_z_impl(ctx, m, dampedInput, dampedZ, true, samples, omegaZ, info, devPtr);
     KFAC_ENTRY_END
@@ -295,6 +298,7 @@ extern "C" int fitre_kfac_lambda_delta_damped(fitre_context *ctx, const CNN_MODE
                                               real *devPtr) {
     KFAC_ENTRY_BEGIN
     FITRE_REQUIRE(m && dampedLambda && lambdaG && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    require_scratch(ctx, fitre_kfac_mem_required(m), "fitre_kfac_lambda_delta_damped");
     model_check_batch(m, samples);
     lambda_delta_impl(ctx, m, dampedLambda, true, samples, lambdaG, info, devPtr);
     KFAC_ENTRY_END
@@ -810,6 +814,7 @@ extern "C" int fitre_kfac_matrix_inverse(fitre_context *ctx, const real *matrix,
     try {
         FITRE_CUDA(cudaSetDevice(ctx->device));
         FITRE_REQUIRE(matrix && inverse && devPtr && n > 0, FITRE_ERR_BAD_ARG, "bad argument");
+        require_scratch(ctx, fitre_kfac_inverse_mem_required(n), "fitre_kfac_matrix_inverse");
         int *fail = (int *)(ctx->dscal + 4002);
         FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), ctx->stream));
         invert_spd(ctx, matrix, inverse, n, lambda + dampGamma, devPtr, fail);
@@ -990,6 +995,7 @@ extern "C" int fitre_kfac_invert_factors(fitre_context *ctx, const CNN_MODEL *m,
         FITRE_CUDA(cudaSetDevice(ctx->device));
         FITRE_REQUIRE(m && info && omegaZ && omegaZInv && lambdaG && lambdaGInv && devPtr, FITRE_ERR_BAD_ARG,
                       "NULL pointer argument");
+        require_scratch(ctx, fitre_kfac_invert_factors_mem_required(m), "fitre_kfac_invert_factors");
         const double damp = info->regLambda + info->dampGamma;
         std::vector<InvJob> jobs = inverse_jobs(m, info, omegaZ, omegaZInv, lambdaG, lambdaGInv,
                                                 ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY);
@@ -1078,6 +1084,7 @@ extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MOD
     FITRE_REQUIRE(m && x0 && zbase && dbase && omegaZ && omegaZInv && lambdaG && lambdaGInv && info && devPtr,
                   FITRE_ERR_BAD_ARG, "NULL pointer argument");
     model_check_batch(m, samples);
+    require_scratch(ctx, fitre_kfac_factors_and_inverses_mem_required(m), "fitre_kfac_factors_and_inverses");
     double *inv_scratch = devPtr + align32(fitre_kfac_mem_required(m));
     const int W = ctx->world;
     const bool chol = ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY;
@@ -1224,6 +1231,7 @@ extern "C" int fitre_compute_natural_gradient(fitre_context *ctx, const CNN_MODE
         FITRE_CUDA(cudaSetDevice(ctx->device));
         FITRE_REQUIRE(m && info && omegaZInv && lambdaGInv && gradient && nGradient && devPtr,
                       FITRE_ERR_BAD_ARG, "NULL pointer argument");
+        require_scratch(ctx, fitre_kfac_natural_gradient_mem_required(m), "fitre_compute_natural_gradient");
         const int hasb = m->bias ? 1 : 0;
         const bool chol = ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY;
         const long per = natural_gradient_layer_scratch(m);

@@ -1002,7 +1002,7 @@ void vec_dots(fitre_context *ctx, long n, const double *a0, const double *b0, co
     check_launch(ctx, "dots_final_kernel");
     FITRE_CUDA(cudaMemcpyAsync(ctx->pinned + 8, ctx->dscal + 8, 3 * sizeof(double),
                                cudaMemcpyDeviceToHost, ctx->stream));
-    FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+    stream_wait(ctx, ctx->stream);
     for (int i = 0; i < 3; ++i) host_out[i] = ctx->pinned[8 + i];
 }
 

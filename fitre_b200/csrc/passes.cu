@@ -121,7 +121,7 @@ double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET 
     comm_allreduce_sum(ctx, ctx->dscal, 1);
     FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost,
                                ctx->stream));
-    FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+    stream_wait(ctx, ctx->stream);
     return ctx->pinned[0] * inv_ng;
 }
 

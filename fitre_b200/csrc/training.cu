@@ -134,7 +134,7 @@ double compute_hits(fitre_context *ctx, const double *probs, const double *targe
     check_launch(ctx, "accuracy_kernel");
     comm_allreduce_sum(ctx, ctx->dscal, 1);
     FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
-    FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+    stream_wait(ctx, ctx->stream);
     return ctx->pinned[0];
 }
 
@@ -515,7 +515,7 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
         for (long i = 0; i < trainN; ++i) host_idx[i] = (int)i;
         for (long i = trainN - 1; i > 0; --i) std::swap(host_idx[i], host_idx[rng.next() % (unsigned long long)(i + 1)]);
         FITRE_CUDA(cudaMemcpyAsync(shuffle, host_idx.data(), sizeof(int) * trainN, cudaMemcpyHostToDevice, ctx->stream));
-        FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+        stream_wait(ctx, ctx->stream);
         long offset = 0;
         int mb = 0;
         // the reference stops before the last batch that would reach the end of the set (:303-308)
@@ -525,7 +525,7 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
             for (int part = 0; part < 4; ++part)
                 FITRE_CUDA(cudaMemcpyAsync(uniforms + (long)part * B, host_u.data() + part * GB + (long)ctx->rank * B,
                                            sizeof(double) * B, cudaMemcpyHostToDevice, ctx->stream));
-            FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+            stream_wait(ctx, ctx->stream);
             prepare_minibatch(ctx, m, data, data->trainSetX, data->trainSetY, shuffle,
                               offset + (long)ctx->rank * B, B, enableDA ? uniforms : nullptr);
 
@@ -595,7 +595,7 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
             ++mb;
             ++total_mb;
         }
-        FITRE_CUDA(cudaStreamSynchronize(ctx->stream));
+        stream_wait(ctx, ctx->stream);
         const double secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
         // end of epoch: generalisation errors with the running statistics (:621-640)
         FITRE_TR_EPOCH ep{};

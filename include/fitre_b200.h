@@ -55,7 +55,9 @@ enum {
     FITRE_ERR_CUDA = 4,          /* a CUDA runtime call or launch failed */
     FITRE_ERR_COMM = 5,          /* NCCL error or time-out */
     FITRE_ERR_NOT_CONVERGED = 6, /* solver hit its iteration limit (informational) */
-    FITRE_ERR_TOO_LARGE = 7      /* size beyond a fixed built-in limit */
+    FITRE_ERR_TOO_LARGE = 7,     /* size beyond a fixed built-in limit */
+    FITRE_ERR_NOT_FINITE = 8     /* the loss came out NaN or Inf (non-finite inputs or weights); the
+                                  * outputs are written as computed, the reference would carry on */
 };
 
 /* ---- boundary structs (reference layouts) ------------------------------ */
@@ -207,6 +209,12 @@ int fitre_set_reference_softmax(fitre_context *ctx, int on);
  * as the reference's PyTorch twin does (pytorch/peng/utils.py:77).  The trust-region loop
  * (fitre_subsampled_trust_region_kfac) follows the setting. */
 int fitre_set_reference_quadratic_damping(fitre_context *ctx, int on);
+/* Declares how many doubles are available behind the scratch pointer handed to the calls that
+ * follow (SCRATCH_AREA.nextDevPtr, devPtr): a call that needs more, by the matching
+ * *_mem_required figure, returns FITRE_ERR_WORKSPACE before launching anything.  0 (default) =
+ * unknown, no check, as in the reference, whose callers carve the workspace by pointer arithmetic
+ * without passing sizes (drivers/cnn_driver.cu:193-209). */
+int fitre_set_scratch_limit(fitre_context *ctx, long doubles);
 /* Number of launches the host has issued through `ctx` of the kernel called `name` (the
  * __global__ function's name without template arguments, e.g. "conv_tma_kernel"); launches
  * replayed from a captured CUDA graph are counted once, at capture.  -1 on a NULL argument.
@@ -299,6 +307,18 @@ int fitre_profile_read(fitre_context *ctx, int kind, double *ms, double *flops, 
 int fitre_comm_unique_id(void *unique_id_128_host);
 int fitre_comm_init(fitre_context *ctx, const void *unique_id_128_host, int rank, int world);
 int fitre_comm_world(const fitre_context *ctx);
+/* Failure handling of the data-parallel mode, all on the host.  `seconds` (default 300) bounds
+ * (1) fitre_comm_init: the communicator is created on a helper thread and a peer that never
+ * joins yields FITRE_ERR_COMM after that time instead of a hang; (2) every host wait on the
+ * context's stream while a communicator exists: the wait polls the stream together with
+ * ncclCommGetAsyncError, and on a reported error or when the time runs out the communicator is
+ * aborted (ncclCommAbort stops NCCL's device work; the CUDA context and the fitre context stay
+ * usable) and the call returns FITRE_ERR_COMM.  After that every collective fails fast with
+ * FITRE_ERR_COMM until fitre_comm_init is called again (world 1 returns to single-GPU mode).
+ * The environment variable FITRE_NCCL_LIBRARY names the NCCL library to load instead of
+ * libnccl.so.2.  The reference has no counterpart: every failure there is print + exit
+ * (device/cuda_utils.h:28-92). */
+int fitre_set_comm_timeout(fitre_context *ctx, double seconds);
 
 /* ---- model builders (nn/read_nn.c:500-725, nn/read_alexnet.c:14-243,
  *      nn/read_vgg.c:25-120,122-212,216-299, nn/utils.c:19-172) ---------- */

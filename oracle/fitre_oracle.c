@@ -25,6 +25,9 @@
 #include "fitre_oracle.h"
 
 #include <float.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <limits.h>
 #include <math.h>
 #include <stdio.h>
@@ -51,6 +54,15 @@ void ora_env_default(ORA_ENV *env) {
     env->eval_type = FITRE_MODEL_TRAIN;
     env->rank = 0;
     env->ref_quadratic = 1;
+}
+
+/* number of OpenMP threads of the following calls (a launcher may have exported OMP_NUM_THREADS=1) */
+void ora_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
 }
 
 static void env_allreduce(const ORA_ENV *env, double *buf, long n) {

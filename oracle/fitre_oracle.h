@@ -36,6 +36,7 @@ typedef struct ora_env {
 } ORA_ENV;
 
 void ora_env_default(ORA_ENV *env);
+void ora_set_num_threads(int n);
 
 /* model set-up: nn/utils.c:12-172, nn/read_vgg.c:25-120 */
 int ora_model_finalize(CNN_MODEL *m);

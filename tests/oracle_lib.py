@@ -34,6 +34,8 @@ def lib():
         L = C.CDLL(so)
         MP, EP = C.POINTER(S.CNN_MODEL), C.POINTER(ORA_ENV)
         i, d = C.c_int, C.c_double
+        L.ora_set_num_threads.argtypes = [i]
+        L.ora_set_num_threads.restype = None
         L.ora_model_finalize.argtypes = [MP]
         L.ora_model_finalize.restype = i
         L.ora_cnn_gradient.argtypes = [EP, MP, dp, dp, dp, i, dp, dp, dp, dp, dp, i, d]
