@@ -25,8 +25,14 @@
 namespace fitre {
 namespace {
 
-constexpr int T_BM = 128, T_BN = 64, T_CB = 4, T_THREADS = 256;
+constexpr int T_BM = 128, T_BN = 64, T_THREADS = 256;
 constexpr int kSmemBudget = 110 * 1024;  // two CTAs per SM
+// Input channels per K-chunk of the forward / data-gradient kernel.  3x3 taps: 4 channels = 36
+// rows of the weight matrix.  5x5 taps: 2 channels = 50 rows, carried as 52 (the DMMA step is 4
+// rows; the two extra rows belong to the next chunk and meet zeros on the A side), so that a
+// ring of three stages fits the shared memory of two resident blocks.  36 and 52 are both
+// 4 mod 16: the B fragments of 8 channels x 4 rows then fall into distinct banks.
+__host__ __device__ constexpr int chunk_channels(int ks) { return ks == 5 ? 2 : 4; }
 
 struct alignas(64) TmaConvArgs {
     CUtensorMap xmap[2];
@@ -43,7 +49,9 @@ struct alignas(64) TmaConvArgs {
 template <int KS>
 __global__ void __launch_bounds__(T_THREADS, 2)
 conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
-    constexpr int KCH = T_CB * KS * KS;  // K rows per chunk: 36 (3x3) or 100 (5x5); both = 4 mod 16
+    constexpr int T_CB = chunk_channels(KS);
+    constexpr int KROWS = T_CB * KS * KS;   // rows of the weight matrix one chunk consumes: 36 / 50
+    constexpr int KCH = (KROWS + 3) & ~3;   // rows one stage holds: 36 / 52
     extern __shared__ unsigned char smraw[];
     unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 127) & ~(uintptr_t)127);
     const int stageBytes = p.patchBytes + KCH * T_BN * 8;
@@ -70,7 +78,7 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
     for (int q = tid; q < KCH; q += T_THREADS) {
         const int cl = q / (KS * KS), rem = q - cl * (KS * KS);
         const int j = rem / KS, i = rem - j * KS;
-        colofs[q] = (cl * p.TN * p.WB + j) * p.HB + i;
+        colofs[q] = q < KROWS ? (cl * p.TN * p.WB + j) * p.HB + i : 0;
     }
     __syncthreads();
 
@@ -99,7 +107,7 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
         unsigned char *dst = sm + (size_t)s * stageBytes;
         mbar_expect_tx(bar, txBytes);
         tma_load_4d(smem_u32(dst), &p.xmap[seg], bar, p.x0, w0 - p.pad, n0, ch * T_CB);
-        tma_load_2d(smem_u32(dst + p.patchBytes), &p.wmap[seg], bar, ch * KCH, c0);
+        tma_load_2d(smem_u32(dst + p.patchBytes), &p.wmap[seg], bar, ch * KROWS, c0);
     };
     if (tid == 0)
         for (int it = 0; it < p.stages - 1 && it < iters; ++it) issue(it);
@@ -136,6 +144,11 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
                 double fa[4], fb[4];
 #pragma unroll
                 for (int mi = 0; mi < 4; ++mi) fa[mi] = patch[co + rowbase[mi]];
+                if (KROWS != KCH && k4 == KCH / 4 - 1 && k4 * 4 + lc >= KROWS) {
+                    // rows past the chunk hold the next chunk's weights: they meet zeros
+#pragma unroll
+                    for (int mi = 0; mi < 4; ++mi) fa[mi] = 0.0;
+                }
 #pragma unroll
                 for (int ni = 0; ni < 4; ++ni) fb[ni] = Bs[ni * 8 * KCH + k4 * 4];
 #pragma unroll
@@ -655,8 +668,9 @@ int fprop_split(int N, int Cin, int H, int W, int k, int pad, int Cout, int nseg
     const int Ho = H + 2 * pad - k + 1, Wo = W + 2 * pad - k + 1;
     const long M = (long)N * Ho * Wo;
     const long tiles = ((M + T_BM - 1) / T_BM) * ((Cout + T_BN - 1) / T_BN);
-    const int iters = nseg * ((Cin + T_CB - 1) / T_CB);
-    const double step_us = 4.7 * (k * k) / 9.0;  // one 128x64x(4 k^2) chunk with two CTAs per SM
+    const int cb = chunk_channels(k);
+    const int iters = nseg * ((Cin + cb - 1) / cb);
+    const double step_us = 4.7 * (cb * k * k) / 36.0;  // one 128 x 64 x (cb k^2) chunk with two CTAs per SM
     return best_split(tiles, iters, 16, 8, step_us, (double)M * Cout * 8);
 }
 }  // namespace
@@ -698,7 +712,8 @@ bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const dou
     a.HB = (H + pad + padE + 1) & ~1;
     a.WB = TW + k - 1;
     if (a.HB > 256 || a.WB > 256 || TN > 256) return false;
-    const int KCH = T_CB * k * k;
+    const int T_CB = chunk_channels(k);
+    const int KCH = (T_CB * k * k + 3) & ~3;
     a.patchBytes = (a.HB * a.WB * TN * T_CB * 8 + 127) & ~127;
     const int stageBytes = a.patchBytes + KCH * T_BN * 8;
     const int fixed = 128 + (((KCH + 3) & ~3) + 4) * 4 + 8 * 8;

@@ -126,10 +126,12 @@ def test_alexnet_bn_1024_gradient_hv():
     import gpu_util as G
     model = nets.alexnet(1024)
     c = G.ctx()
-    before = c.kernel_launches("wgrad_tma_kernel")
+    before = {k: c.kernel_launches(k) for k in ("wgrad_tma_kernel", "conv_tma_kernel")}
     run, _, _ = _check_grad_hv(model, 1024, seed=2234)
-    # second layer (K = 1600): weight gradient and its R-operator form through the TMA-fed kernel
-    assert run.c.kernel_launches("wgrad_tma_kernel") - before >= 2
+    # second layer (K = 1600): forward, data gradient, weight gradient and their R-operator forms
+    # through the TMA-fed kernels (the first layer's K = 75 is odd and takes the gather kernels)
+    assert run.c.kernel_launches("wgrad_tma_kernel") - before["wgrad_tma_kernel"] >= 2
+    assert run.c.kernel_launches("conv_tma_kernel") - before["conv_tma_kernel"] >= 4
 
 
 def test_vgg11_bn_512_gradient_hv_and_state():

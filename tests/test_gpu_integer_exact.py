@@ -38,13 +38,15 @@ GATHER_CASES = [
     (4, 8, 3, 1, 4, True),
     (2, 10, 3, 0, 4, True),
     (2, 8, 3, 2, 3, False),    # Ho = 10 does not divide the 128-row tile: gather kernel
-    (2, 8, 5, 2, 4, False),    # 5 x 5 taps: two ring stages of 100 weight rows exceed the shared
-    (2, 12, 5, 0, 2, False),   # memory of two resident blocks, so these run on the gather kernel
+    (2, 8, 5, 2, 4, True),     # 5 x 5 taps: chunks of 2 channels (50 weight rows carried as 52)
+    (2, 12, 5, 0, 2, True),
     (4, 16, 5, 1, 2, False),   # Ho = 14
     (3, 7, 3, 1, 5, False),    # odd height and odd K
     (6, 16, 3, 1, 16, True),   # one image per tile row block, several tiles
-    (2, 32, 5, 2, 6, False),
-    (2, 32, 3, 1, 6, True),    # Ho * Wo > 128: tiles of 4 output columns
+    (2, 32, 5, 2, 6, True),    # Ho * Wo > 128: tiles of 4 output columns
+    (2, 32, 3, 1, 6, True),
+    (5, 16, 5, 2, 3, False),   # odd K = 125: 16-byte stride rule of the weight map fails
+    (6, 16, 5, 2, 3, True),    # three chunks of two channels
 ]
 
 
