@@ -328,8 +328,18 @@ int fitre_compute_cnn_gradient(fitre_context *ctx, const CNN_MODEL *m, const DEV
         cnn_forward(ctx, m, data, ws, z, probs, lossFuncErrors, curBatchSize, false);
         const int classes = m->fcLayer[m->lLayers - 1].out;
         vec_copy(ctx, (long)classes * curBatchSize, lossFuncErrors, errors);
-        cnn_backward(ctx, m, data, ws, z, gradient, dx, errors, errors1, curBatchSize);
-        comm_allreduce_sum(ctx, gradient, m->pSize);
+        // the gradient is a batch sum: each layer's slice is all-reduced as soon as the backward
+        // sweep has finished it, on the side communicator, under the rest of the sweep
+        ctx->reduce_slices = true;
+        ctx->reduced_from = m->pSize;
+        try {
+            cnn_backward(ctx, m, data, ws, z, gradient, dx, errors, errors1, curBatchSize);
+        } catch (...) {
+            ctx->reduce_slices = false;
+            throw;
+        }
+        ctx->reduce_slices = false;
+        comm_async_join(ctx);
         vec_axpy(ctx, m->pSize, weightDecay, data->weights, gradient);
         comm_allreduce_sum(ctx, ctx->dscal, 1);
         FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost,
@@ -575,9 +585,9 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         // travels back on the copy stream while the Hessian-vector product runs
         FITRE_CUDA(cudaMemcpyAsync(gradient_host, g, sizeof(double) * m->pSize, cudaMemcpyDeviceToHost, cs));
         FITRE_CUDA(cudaStreamWaitEvent(st, ctx->ev_up, 0));
-        // single rank: finished slices of hv follow the gradient on the copy stream as the backward
-        // sweep completes its layers; with several ranks hv is only final after the all-reduce
-        ctx->hv_host_dst = ctx->world == 1 ? hv_host : nullptr;
+        // finished slices of hv follow the gradient on the copy stream as the backward sweep completes
+        // its layers (with ranks: as each layer's slice has been all-reduced on the side stream)
+        ctx->hv_host_dst = (ctx->world == 1 || comm_async_stream(ctx)) ? hv_host : nullptr;
         ctx->hv_sent_from = m->pSize;
         rc = fitre_cnn_hv(ctx, m, &data, z, probs, errs, dx, v, hv, 0, n, ws, nullptr, weightDecay);
         const long sent_from = ctx->hv_host_dst ? ctx->hv_sent_from : m->pSize;

@@ -29,7 +29,7 @@ typedef struct ncclComm *ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
 typedef int ncclResult_t;
 enum { ncclSuccess = 0, ncclInProgress = 7 };
-enum { ncclFloat64 = 8 };
+enum { ncclChar = 0, ncclFloat64 = 8 };
 enum { ncclSum = 0 };
 
 struct Api {
@@ -41,6 +41,7 @@ struct Api {
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Reduce)(const void *, void *, size_t, int, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Broadcast)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -62,9 +63,10 @@ Api &api() {
     a.CommGetAsyncError = (decltype(a.CommGetAsyncError))dlsym(a.handle, "ncclCommGetAsyncError");
     a.AllReduce = (decltype(a.AllReduce))dlsym(a.handle, "ncclAllReduce");
     a.Reduce = (decltype(a.Reduce))dlsym(a.handle, "ncclReduce");
+    a.Broadcast = (decltype(a.Broadcast))dlsym(a.handle, "ncclBroadcast");
     a.GetErrorString = (decltype(a.GetErrorString))dlsym(a.handle, "ncclGetErrorString");
     const bool ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.CommAbort && a.CommGetAsyncError &&
-                    a.AllReduce && a.Reduce;
+                    a.AllReduce && a.Reduce && a.Broadcast;
     if (!ok) {
         a.handle = nullptr;
         throw Error(FITRE_ERR_COMM, "the NCCL library lacks a required symbol");
@@ -92,7 +94,16 @@ struct InitJob {
 }  // namespace
 
 struct Comm {
-    ncclComm_t comm = nullptr;
+    ncclComm_t comm = nullptr;    // collectives on the context's stream (batch statistics, scalars, factors)
+    // A second communicator on a stream of its own carries the all-reduces of finished slices of
+    // the gradient / Hessian-vector product while the backward sweep goes on; two communicators,
+    // because collectives of one communicator run in issue order whatever their streams.
+    ncclComm_t side = nullptr;
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t ev_ready[32] = {};  // "slice is written" (context stream -> side stream)
+    cudaEvent_t ev_done = nullptr;  // "all slices are reduced" (side stream -> context stream)
+    int next_ev = 0;
+    bool pending = false;
     bool aborted = false;
 };
 
@@ -102,7 +113,8 @@ void abort_comm(fitre_context *ctx) {
     if (!ctx->comm || ctx->comm->aborted) return;
     ctx->comm->aborted = true;
     if (ctx->comm->comm) api().CommAbort(ctx->comm->comm);
-    ctx->comm->comm = nullptr;
+    if (ctx->comm->side) api().CommAbort(ctx->comm->side);
+    ctx->comm->comm = ctx->comm->side = nullptr;
 }
 
 ncclComm_t live_comm(fitre_context *ctx) {
@@ -123,6 +135,40 @@ void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root) {
     if (ctx->world <= 1 || !ctx->comm || n == 0) return;
     check(api().Reduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, root, live_comm(ctx), ctx->stream), "ncclReduce");
     ctx->launches += 1;
+}
+
+// All-reduce of dev_buf[0, n) on the side communicator and stream, ordered after everything queued
+// on the context's stream so far; the context's stream does not wait for it until comm_async_join.
+void comm_allreduce_async(fitre_context *ctx, double *dev_buf, size_t n) {
+    if (ctx->world <= 1 || !ctx->comm || n == 0) return;
+    live_comm(ctx);
+    Comm *c = ctx->comm;
+    if (!c->side) {  // no side communicator: the plain ordered all-reduce
+        comm_allreduce_sum(ctx, dev_buf, n);
+        return;
+    }
+    cudaEvent_t &ev = c->ev_ready[c->next_ev++ & 31];
+    if (!ev) FITRE_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    FITRE_CUDA(cudaEventRecord(ev, ctx->stream));
+    FITRE_CUDA(cudaStreamWaitEvent(c->side_stream, ev, 0));
+    check(api().AllReduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, c->side, c->side_stream), "ncclAllReduce");
+    c->pending = true;
+    ctx->launches += 1;
+}
+
+// The stream that carries the asynchronous slice all-reduces (NULL without one).
+cudaStream_t comm_async_stream(fitre_context *ctx) {
+    return (ctx->world > 1 && ctx->comm && ctx->comm->side) ? ctx->comm->side_stream : nullptr;
+}
+
+// Makes the context's stream wait for every all-reduce started by comm_allreduce_async.
+void comm_async_join(fitre_context *ctx) {
+    if (ctx->world <= 1 || !ctx->comm || !ctx->comm->pending) return;
+    Comm *c = ctx->comm;
+    c->pending = false;
+    if (c->aborted || !c->side) return;
+    FITRE_CUDA(cudaEventRecord(c->ev_done, c->side_stream));
+    FITRE_CUDA(cudaStreamWaitEvent(ctx->stream, c->ev_done, 0));
 }
 
 // Host wait for everything queued on `stream` (the context's stream, or another stream whose
@@ -146,7 +192,9 @@ void stream_wait(fitre_context *ctx, cudaStream_t stream) {
         ++spins;
         if ((spins & 63) == 0) {
             ncclResult_t state = ncclSuccess;
-            const ncclResult_t q = api().CommGetAsyncError(ctx->comm->comm, &state);
+            ncclResult_t q = api().CommGetAsyncError(ctx->comm->comm, &state);
+            if (q == ncclSuccess && (state == ncclSuccess || state == ncclInProgress) && ctx->comm->side)
+                q = api().CommGetAsyncError(ctx->comm->side, &state);
             if (q != ncclSuccess || (state != ncclSuccess && state != ncclInProgress)) {
                 const std::string why = nccl_text(q != ncclSuccess ? q : state);
                 abort_comm(ctx);
@@ -168,7 +216,12 @@ void stream_wait(fitre_context *ctx, cudaStream_t stream) {
 
 void comm_destroy(fitre_context *ctx) {
     if (ctx->comm) {
+        if (ctx->comm->side && !ctx->comm->aborted) api().CommDestroy(ctx->comm->side);
         if (ctx->comm->comm && !ctx->comm->aborted) api().CommDestroy(ctx->comm->comm);
+        if (ctx->comm->side_stream) cudaStreamDestroy(ctx->comm->side_stream);
+        for (cudaEvent_t e : ctx->comm->ev_ready)
+            if (e) cudaEventDestroy(e);
+        if (ctx->comm->ev_done) cudaEventDestroy(ctx->comm->ev_done);
         delete ctx->comm;
         ctx->comm = nullptr;
     }
@@ -182,16 +235,12 @@ void comm_unique_id(void *out128) {
     std::memcpy(out128, &id, sizeof(id));
 }
 
-void comm_init(fitre_context *ctx, const void *id128, int rank, int world) {
-    FITRE_REQUIRE(world >= 1 && rank >= 0 && rank < world, FITRE_ERR_BAD_ARG, "bad rank/world");
-    comm_destroy(ctx);
-    if (world == 1) return;
+namespace {
+// ncclCommInitRank blocks until every rank has joined.  It runs on a helper thread; the caller
+// waits for it at most comm_timeout_s seconds.  If the time runs out the job is abandoned: should
+// the set-up ever return, the helper aborts the communicator it got.
+ncclComm_t bounded_init(fitre_context *ctx, const ncclUniqueId &id, int rank, int world) {
     Api &a = api();
-    ncclUniqueId id;
-    std::memcpy(&id, id128, sizeof(id));
-    // ncclCommInitRank blocks until every rank has joined.  It runs on a helper thread; this
-    // thread waits for it at most comm_timeout_s seconds.  If the time runs out the job is
-    // abandoned: should the set-up ever return, the helper aborts the communicator it got.
     auto job = std::make_shared<InitJob>();
     const int device = ctx->device;
     std::thread([job, id, rank, world, device, &a]() {
@@ -218,10 +267,43 @@ void comm_init(fitre_context *ctx, const void *id128, int rank, int world) {
         }
     }
     check(job->result, "ncclCommInitRank");
+    return job->comm;
+}
+}  // namespace
+
+void comm_init(fitre_context *ctx, const void *id128, int rank, int world) {
+    FITRE_REQUIRE(world >= 1 && rank >= 0 && rank < world, FITRE_ERR_BAD_ARG, "bad rank/world");
+    comm_destroy(ctx);
+    if (world == 1) return;
+    Api &a = api();
+    ncclUniqueId id;
+    std::memcpy(&id, id128, sizeof(id));
+    FITRE_CUDA(cudaSetDevice(ctx->device));
     ctx->comm = new Comm();
-    ctx->comm->comm = job->comm;
+    ctx->comm->comm = bounded_init(ctx, id, rank, world);
     ctx->rank = rank;
     ctx->world = world;
+    // The side communicator: rank 0 draws a second id and hands it round through the first one.
+    // FITRE_SIDE_COMM=0 keeps a single communicator (slices are then reduced in stream order).
+    const char *sw = std::getenv("FITRE_SIDE_COMM");
+    if (sw && sw[0] == '0') return;
+    try {
+        ncclUniqueId id2;
+        std::memset(&id2, 0, sizeof(id2));
+        if (rank == 0) check(a.GetUniqueId(&id2), "ncclGetUniqueId");
+        char *dev = reinterpret_cast<char *>(ctx->dscal + 3900);  // 128 bytes of the scalar slab
+        FITRE_CUDA(cudaMemcpyAsync(dev, &id2, sizeof(id2), cudaMemcpyHostToDevice, ctx->stream));
+        check(a.Broadcast(dev, dev, sizeof(id2), ncclChar, 0, ctx->comm->comm, ctx->stream), "ncclBroadcast");
+        FITRE_CUDA(cudaMemcpyAsync(&id2, dev, sizeof(id2), cudaMemcpyDeviceToHost, ctx->stream));
+        stream_wait(ctx, ctx->stream);
+        FITRE_CUDA(cudaMemsetAsync(dev, 0, sizeof(id2), ctx->stream));
+        ctx->comm->side = bounded_init(ctx, id2, rank, world);
+        FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->comm->side_stream, cudaStreamNonBlocking));
+        FITRE_CUDA(cudaEventCreateWithFlags(&ctx->comm->ev_done, cudaEventDisableTiming));
+    } catch (...) {
+        comm_destroy(ctx);
+        throw;
+    }
 }
 
 }  // namespace fitre

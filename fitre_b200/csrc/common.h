@@ -73,6 +73,10 @@ struct fitre_context {
     int fwd_wait_layer = -1;
     double *hv_host_dst = nullptr;
     long hv_sent_from = 0;
+    // set around a backward sweep whose result vector is a batch sum wanted on every rank: the
+    // sweep then all-reduces each layer's finished slice while it computes the next layer
+    bool reduce_slices = false;
+    long reduced_from = 0;
     double *staging_buf = nullptr;        // staging of the opt-in tensor-core modes (operand copies, digit
     long staging_cap = 0;                 // planes, split slabs), owned by the context, grown on demand
     cudaStream_t inv_streams[8] = {};     // side streams of the batched factor inversion
@@ -139,6 +143,11 @@ struct ProfScope {
 void comm_allreduce_sum(fitre_context *ctx, double *dev_buf, size_t n);
 void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root);
 void comm_destroy(fitre_context *ctx);
+// all-reduce of a finished slice on the side communicator / stream; join = the context's stream
+// waits for all of them (no-ops on one rank)
+void comm_allreduce_async(fitre_context *ctx, double *dev_buf, size_t n);
+void comm_async_join(fitre_context *ctx);
+cudaStream_t comm_async_stream(fitre_context *ctx);
 // host wait on a stream; with a communicator it also watches NCCL's error state and a deadline
 void stream_wait(fitre_context *ctx, cudaStream_t stream);
 

@@ -61,6 +61,16 @@ long max_fc_elems(const CNN_MODEL *m) {
     return v;
 }
 
+// Data-parallel sweeps whose result is wanted on every rank (ctx->reduce_slices): the backward
+// sweeps finish the parameter vector from its end towards its start, one layer at a time, so
+// everything at or beyond `from` is final once the current layer's weight gradient is queued.
+// That slice is all-reduced on the side communicator while the sweep computes the next layer.
+void reduce_finished_slice(fitre_context *ctx, double *vec, long from) {
+    if (!ctx->reduce_slices || ctx->world <= 1 || from >= ctx->reduced_from) return;
+    comm_allreduce_async(ctx, vec + from, (size_t)(ctx->reduced_from - from));
+    ctx->reduced_from = from;
+}
+
 const double *layer_input(const CNN_MODEL *m, const DEVICE_DATASET *data, const double *z, int l) {
     if (l == 0) return data->currentBatch;
     return z + m->zOffsets[l] + m->convLayer[l - 1].outputOffset;
@@ -152,6 +162,7 @@ void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *
         std::swap(delta, delta_new);
     }
     fc_to_conv(ctx, delta, lg.Cout, n, lg.Hp, lg.Wp, tmp);  // :310-326
+    reduce_finished_slice(ctx, gradient, m->wOffsets[cL]);
 
     for (int c = cL - 1; c >= 0; --c) {  // :355-852
         const ConvGeom g = conv_geom(m, c);
@@ -161,6 +172,7 @@ void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *
                                                  m->bias ? gradient + m->bOffsets[c] : nullptr, bnws);
         ConvSeg wseg{layer_input(m, data, z, c), dconv};
         conv_wgrad(ctx, 1, &wseg, gradient + m->wOffsets[c], n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wg);
+        reduce_finished_slice(ctx, gradient, m->wOffsets[c]);
         if (c != 0) {
             ConvSeg dseg{dconv, weights + m->wOffsets[c]};
             conv_dgrad(ctx, 1, &dseg, delta_new, n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wperm, split);
@@ -213,14 +225,21 @@ void cnn_rop_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASE
 }
 
 // ---------------------------------------------------------------------------------------------
-// Host-buffer entry point only (single rank): everything of hv at or beyond `from` is final once
-// the layers processed so far are done (the backward sweep runs from the last layer to the first),
-// so that slice goes to the host on the copy stream while the earlier layers are still computed.
+// Host-buffer entry point only: everything of hv at or beyond `from` is final once the layers
+// processed so far are done (the backward sweep runs from the last layer to the first) and, with
+// ranks, their slice is all-reduced, so that slice goes to the host on the copy stream while the
+// earlier layers are still computed.
 static void send_finished_hv(fitre_context *ctx, const double *hv, long from, int slot) {
-    if (!ctx->hv_host_dst || ctx->world > 1 || !ctx->copy_stream || from >= ctx->hv_sent_from) return;
+    if (!ctx->hv_host_dst || !ctx->copy_stream || from >= ctx->hv_sent_from) return;
+    // with ranks the slice is final once its all-reduce on the side stream is done
+    cudaStream_t after = ctx->stream;
+    if (ctx->world > 1) {
+        after = comm_async_stream(ctx);
+        if (!after || !ctx->reduce_slices || ctx->reduced_from > from) return;
+    }
     cudaEvent_t &ev = ctx->chunk_ev[slot % 24];
     if (!ev) FITRE_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-    FITRE_CUDA(cudaEventRecord(ev, ctx->stream));
+    FITRE_CUDA(cudaEventRecord(ev, after));
     FITRE_CUDA(cudaStreamWaitEvent(ctx->copy_stream, ev, 0));
     FITRE_CUDA(cudaMemcpyAsync(ctx->hv_host_dst + from, hv + from, sizeof(double) * (size_t)(ctx->hv_sent_from - from),
                                cudaMemcpyDeviceToHost, ctx->copy_stream));
@@ -272,6 +291,7 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
         vec_copy(ctx, (long)l.in * n, t2, rError);
     }
     fc_to_conv(ctx, rError, lg.Cout, n, lg.Hp, lg.Wp, tmp);  // :414-427
+    reduce_finished_slice(ctx, hv, m->wOffsets[cL]);
     send_finished_hv(ctx, hv, m->wOffsets[cL], cL);
 
     for (int c = cL - 1; c >= 0; --c) {  // :436-907
@@ -289,6 +309,7 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
             nseg = 2;
         }
         conv_wgrad(ctx, nseg, ws, hv + m->wOffsets[c], n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wg);
+        reduce_finished_slice(ctx, hv, m->wOffsets[c]);
         if (c != 0) {  // Rdelta <- dgrad(Rdelta, W) + dgrad(delta, V)  (:854-898)
             ConvSeg ds[2] = {ConvSeg{rout, weights + m->wOffsets[c]},
                              ConvSeg{dprev, vector + m->wOffsets[c]}};
@@ -310,8 +331,17 @@ void cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, 
     const double inv_ng = 1.0 / ((double)n * ctx->world);
     softmax_rop_error(ctx, rz + m->zOffsets[m->cLayers + m->lLayers], probs, n, classes, rError,
                       inv_ng);
-    cnn_rop_backward(ctx, m, data, z, dx, lossErrors, rError, rz, vector, hv, n, scratch);
-    comm_allreduce_sum(ctx, hv, m->pSize);
+    // hv is a batch sum: every layer's slice is all-reduced as soon as the sweep has finished it
+    ctx->reduce_slices = true;
+    ctx->reduced_from = m->pSize;
+    try {
+        cnn_rop_backward(ctx, m, data, z, dx, lossErrors, rError, rz, vector, hv, n, scratch);
+    } catch (...) {
+        ctx->reduce_slices = false;
+        throw;
+    }
+    ctx->reduce_slices = false;
+    comm_async_join(ctx);
 }
 
 }  // namespace fitre

@@ -54,5 +54,9 @@ int ncclReduce(const void *s, void *r, size_t n, int dt, int op, int root, void 
     (void)s; (void)r; (void)n; (void)dt; (void)op; (void)root; (void)comm;
     return collective(stream);
 }
+int ncclBroadcast(const void *s, void *r, size_t n, int dt, int root, void *comm, cudaStream_t stream) {
+    (void)s; (void)r; (void)n; (void)dt; (void)root; (void)comm; (void)stream;
+    return 0;   /* set-up traffic: never stalled */
+}
 const char *ncclGetErrorString(int r) { return r == 6 ? "remote error (fake)" : "fake result"; }
 int fake_nccl_count(int which) { return counts[which & 3]; }

@@ -177,7 +177,12 @@ def main():
         run3 = G.GpuRun(model, xs, ys, w, ncls, ref_softmax=1)
         hv3 = run3.hv(v)
         ctx.set_precision(0)
+        # the host-buffer entry point on the shard: same bits as the device-resident calls (its
+        # Hessian-vector slices travel to the host as each layer's all-reduce completes)
+        g_host, hv_host = np.zeros(model.pSize), np.zeros(model.pSize)
+        loss_host = api.gradientHvHost(ctx, model, xs, ys, w, v, per, ncls, 0.0, g_host, hv_host)
         np.savez(out, loss=loss64, gradient=g64, hv=hv, A=A.cpu().numpy(),
+                 loss_host=loss_host, gradient_host=g_host, hv_host=hv_host,
                  G=Gm.cpu().numpy(), Ainv=Ai.cpu().numpy(), Ginv=Gi.cpu().numpy(),
                  gradient_x3=run3.gradient, hv_x3=hv3, ng_rep=ng_rep, ng_owned=ng_owned[0],
                  ng_owned_chol=ng_owned[1])

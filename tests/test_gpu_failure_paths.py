@@ -112,7 +112,7 @@ def test_comm_async_error_aborts_and_returns_status(fake_nccl):
     assert r["world"] == 2
     assert r["status"] == S.ERR_COMM and "asynchronous error" in r["text"]
     assert r["status_again"] == S.ERR_COMM
-    assert r["aborts"] == 1 and r["destroys"] == 0
+    assert r["aborts"] == 2 and r["destroys"] == 0      # both communicators of the context
     assert r["single_gpu_status_after"] == 0
 
 
@@ -120,7 +120,7 @@ def test_comm_stalled_collective_hits_the_deadline(fake_nccl):
     r = run_worker("fake_stalled_collective", {"FITRE_NCCL_LIBRARY": fake_nccl, "FAKE_NCCL_STALL_MS": "2500"})
     assert r["status"] == S.ERR_COMM and "did not finish" in r["text"]
     assert 0.9 < r["seconds"] < 2.4
-    assert r["aborts"] == 1 and r["single_gpu_status_after"] == 0
+    assert r["aborts"] == 2 and r["single_gpu_status_after"] == 0
 
 
 def test_real_nccl_peer_never_joins():

@@ -125,6 +125,10 @@ def test_two_gpu_cuda_matches_full_batch(tmp_path, builder):
         # every rank the natural gradient of the replicated form, with inverses and with Cholesky solves
         assert rel(res["ng_owned"], res["ng_rep"]) < 1e-9
         assert rel(res["ng_owned_chol"], res["ng_rep"]) < 1e-8
+        # host-buffer entry point with ranks: bit-identical to the device-resident calls
+        assert float(res["loss_host"]) == float(res["loss"])
+        assert np.array_equal(res["gradient_host"], res["gradient"])
+        assert np.array_equal(res["hv_host"], res["hv"])
         # 3xTF32 mode across ranks: stated tolerance 1e-3 against the fp64 full-batch result
         assert rel(res["gradient_x3"], g) < 1e-3 and rel(res["hv_x3"], hv) < 1e-3
 
