@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libfitre_b200.so")
 SYMBOLS = [
     "fitre_context_create", "fitre_context_destroy", "fitre_last_error", "fitre_launch_count",
     "fitre_set_reference_softmax", "fitre_set_reference_quadratic_damping", "fitre_set_scratch_limit", "fitre_kernel_launches", "fitre_set_precision", "fitre_set_kfac_solver", "fitre_set_kfac_distribution", "fitre_get_kfac_solver", "fitre_kfac_matrix_factor", "fitre_set_graphs", "fitre_set_tma", "fitre_profile_enable", "fitre_profile_read",
-    "fitre_comm_unique_id", "fitre_comm_init", "fitre_comm_world", "fitre_set_comm_timeout",
+    "fitre_comm_unique_id", "fitre_comm_init", "fitre_comm_world", "fitre_set_comm_timeout", "fitre_peer_reduce_enabled", "fitre_peer_wait_selftest",
     "fitre_read_lenet_cnn", "fitre_read_alexnet_cnn", "fitre_read_vgg11", "fitre_read_test_vgg",
     "fitre_model_finalize", "fitre_model_validate",
     "fitre_cnn_forward_mem_required", "fitre_cnn_backward_mem_required",
@@ -80,6 +80,8 @@ def load():
     sig("fitre_comm_init", i, vp, vp, i, i)
     sig("fitre_comm_world", i, vp)
     sig("fitre_set_comm_timeout", i, vp, d)
+    sig("fitre_peer_reduce_enabled", i, vp)
+    sig("fitre_peer_wait_selftest", i, vp, d)
     sig("fitre_read_lenet_cnn", i, MP, i, i, i, i, i, i, i, i)
     sig("fitre_read_alexnet_cnn", i, MP, i, i, i, i, i, i, i)
     sig("fitre_read_vgg11", i, MP, i, i, i, i, i, i, i, i)

@@ -138,6 +138,15 @@ class Context:
         """Bound (seconds) of communicator set-up and of every host wait on a collective."""
         self.check(self.lib.fitre_set_comm_timeout(self.h, float(seconds)))
 
+    @property
+    def peer_reduce_enabled(self):
+        """True when short vectors are all-reduced by the library's own kernel over peer memory."""
+        return bool(self.lib.fitre_peer_reduce_enabled(self.h))
+
+    def peer_wait_selftest(self, wait_ms):
+        """Runs the peer all-reduce kernel against a flag nothing raises; raises FitreError(ERR_COMM)."""
+        self.check(self.lib.fitre_peer_wait_selftest(self.h, float(wait_ms)))
+
     def comm_init(self, unique_id_bytes, rank, world):
         """fitre_comm_init with an id obtained from comm_unique_id() on rank 0."""
         idbuf = (C.c_ubyte * 128).from_buffer_copy(bytes(unique_id_bytes))

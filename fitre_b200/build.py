@@ -11,7 +11,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["gemm.cu", "conv_tma.cu", "conv_tf32.cu", "conv_i8.cu", "layers.cu", "passes.cu", "kfac.cu", "training.cu", "model.cpp", "comm.cpp", "cabi.cpp"]
+SOURCES = ["gemm.cu", "conv_tma.cu", "conv_tf32.cu", "conv_i8.cu", "layers.cu", "peer.cu", "passes.cu", "kfac.cu", "training.cu", "model.cpp", "comm.cpp", "cabi.cpp"]
 LIB = os.path.join(HERE, "libfitre_b200.so")
 # C++ functions with the reference's own (mangled) names on top of the C ABI
 SHIM_SRC = os.path.join(HERE, "csrc", "reference_shim.cpp")

@@ -44,6 +44,8 @@ void check_device_error(fitre_context *ctx) {
     std::memcpy(&word, ctx->pinned + 200, sizeof(int));
     if (word != 0) {
         FITRE_CUDA(cudaMemsetAsync(ctx->dscal + 4000, 0, sizeof(double), ctx->stream));
+        if (word == 2)
+            throw Error(FITRE_ERR_COMM, "the peer all-reduce kernel's bounded wait for another rank's flag ran out");
         throw Error(FITRE_ERR_CUDA, "a kernel's bounded wait on a TMA transfer ran out");
     }
 }
@@ -257,6 +259,15 @@ int fitre_comm_init(fitre_context *ctx, const void *id, int rank, int world) {
     });
 }
 int fitre_comm_world(const fitre_context *ctx) { return ctx ? ctx->world : 0; }
+int fitre_peer_wait_selftest(fitre_context *ctx, double wait_ms) {
+    return guarded(ctx, [&] {
+        FITRE_REQUIRE(wait_ms > 0.0 && wait_ms <= 5000.0, FITRE_ERR_BAD_ARG, "wait_ms must be in (0, 5000]");
+        const int word = peer_wait_selftest(ctx, wait_ms);
+        FITRE_REQUIRE(word == 0, FITRE_ERR_COMM, "the bounded wait for a peer's flag ran out (error word " +
+                                                     std::to_string(word) + ")");
+    });
+}
+int fitre_peer_reduce_enabled(const fitre_context *ctx) { return ctx ? (ctx->peer.enabled ? 1 : 0) : 0; }
 int fitre_set_comm_timeout(fitre_context *ctx, double seconds) {
     if (!ctx || !(seconds > 0.0)) return FITRE_ERR_BAD_ARG;
     ctx->comm_timeout_s = seconds;
@@ -341,7 +352,7 @@ int fitre_compute_cnn_gradient(fitre_context *ctx, const CNN_MODEL *m, const DEV
         ctx->reduce_slices = false;
         comm_async_join(ctx);
         vec_axpy(ctx, m->pSize, weightDecay, data->weights, gradient);
-        comm_allreduce_sum(ctx, ctx->dscal, 1);
+        comm_allreduce_small(ctx, ctx->dscal, 1);
         FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost,
                                    ctx->stream));
         check_device_error(ctx);

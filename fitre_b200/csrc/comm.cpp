@@ -18,6 +18,7 @@
 #include <memory>
 #include <mutex>
 #include <thread>
+#include <vector>
 
 #include "common.h"
 
@@ -42,6 +43,7 @@ struct Api {
     ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Reduce)(const void *, void *, size_t, int, int, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Broadcast)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;  // optional
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -64,6 +66,7 @@ Api &api() {
     a.AllReduce = (decltype(a.AllReduce))dlsym(a.handle, "ncclAllReduce");
     a.Reduce = (decltype(a.Reduce))dlsym(a.handle, "ncclReduce");
     a.Broadcast = (decltype(a.Broadcast))dlsym(a.handle, "ncclBroadcast");
+    a.AllGather = (decltype(a.AllGather))dlsym(a.handle, "ncclAllGather");
     a.GetErrorString = (decltype(a.GetErrorString))dlsym(a.handle, "ncclGetErrorString");
     const bool ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.CommAbort && a.CommGetAsyncError &&
                     a.AllReduce && a.Reduce && a.Broadcast;
@@ -115,6 +118,7 @@ void abort_comm(fitre_context *ctx) {
     if (ctx->comm->comm) api().CommAbort(ctx->comm->comm);
     if (ctx->comm->side) api().CommAbort(ctx->comm->side);
     ctx->comm->comm = ctx->comm->side = nullptr;
+    ctx->peer.enabled = false;
 }
 
 ncclComm_t live_comm(fitre_context *ctx) {
@@ -135,6 +139,16 @@ void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root) {
     if (ctx->world <= 1 || !ctx->comm || n == 0) return;
     check(api().Reduce(dev_buf, dev_buf, n, ncclFloat64, ncclSum, root, live_comm(ctx), ctx->stream), "ncclReduce");
     ctx->launches += 1;
+}
+
+void comm_allreduce_small(fitre_context *ctx, double *dev_buf, size_t n) {
+    if (ctx->world <= 1 || !ctx->comm || n == 0) return;
+    if (peer_allreduce_ready(ctx, (long)n)) {
+        live_comm(ctx);
+        peer_allreduce(ctx, nullptr, 0, 1, dev_buf, (int)n);
+    } else {
+        comm_allreduce_sum(ctx, dev_buf, n);
+    }
 }
 
 // All-reduce of dev_buf[0, n) on the side communicator and stream, ordered after everything queued
@@ -214,7 +228,76 @@ void stream_wait(fitre_context *ctx, cudaStream_t stream) {
     }
 }
 
+namespace {
+void peer_teardown(fitre_context *ctx) {
+    ctx->peer.enabled = false;
+    for (int r = 0; r < FITRE_PEER_MAX_RANKS; ++r) {
+        if (!ctx->peer.inbox[r]) continue;
+        if (r == ctx->rank) cudaFree(ctx->peer.inbox[r]);
+        else cudaIpcCloseMemHandle(ctx->peer.inbox[r]);
+        ctx->peer.inbox[r] = nullptr;
+    }
+    cudaGetLastError();
+}
+
+// Mailboxes of the peer-memory all-reduce (peer.cu): every rank allocates one, the IPC handles go
+// round through NCCL, every rank maps every other mailbox.  Best effort and all-or-nothing: the
+// ranks agree (one all-reduce of a success flag) and use NCCL for the short vectors otherwise.
+// FITRE_PEER_REDUCE=0 switches it off.
+void peer_setup(fitre_context *ctx) {
+    Api &a = api();
+    const char *sw = std::getenv("FITRE_PEER_REDUCE");
+    if ((sw && sw[0] == '0') || !a.AllGather || ctx->world > FITRE_PEER_MAX_RANKS) return;
+    const int W = ctx->world, me = ctx->rank;
+    const size_t doubles = 2 * (size_t)W * FITRE_PEER_MAX_DOUBLES + 2 * (size_t)W;
+    bool ok = true;
+    double *own = nullptr;
+    char *stage = nullptr;  // [W + 1] handles of 64 bytes: gathered ones, then this rank's
+    cudaIpcMemHandle_t mine;
+    std::vector<cudaIpcMemHandle_t> all(W);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    FITRE_CUDA(cudaMalloc((void **)&own, doubles * sizeof(double)));
+    ctx->peer.inbox[me] = own;
+    FITRE_CUDA(cudaMemsetAsync(own, 0, doubles * sizeof(double), ctx->stream));
+    FITRE_CUDA(cudaMalloc((void **)&stage, (size_t)(W + 1) * 64));
+    std::memset(&mine, 0, sizeof(mine));
+    if (cudaIpcGetMemHandle(&mine, own) != cudaSuccess) {
+        cudaGetLastError();
+        ok = false;
+    }
+    FITRE_CUDA(cudaMemcpyAsync(stage + (size_t)W * 64, &mine, 64, cudaMemcpyHostToDevice, ctx->stream));
+    check(a.AllGather(stage + (size_t)W * 64, stage, 64, ncclChar, ctx->comm->comm, ctx->stream), "ncclAllGather");
+    FITRE_CUDA(cudaMemcpyAsync(all.data(), stage, (size_t)W * 64, cudaMemcpyDeviceToHost, ctx->stream));
+    stream_wait(ctx, ctx->stream);
+    for (int r = 0; r < W && ok; ++r) {
+        if (r == me) continue;
+        void *p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            ok = false;
+        } else {
+            ctx->peer.inbox[r] = (double *)p;
+        }
+    }
+    double flag = ok ? 1.0 : 0.0;
+    FITRE_CUDA(cudaMemcpyAsync(ctx->dscal + 3990, &flag, sizeof(double), cudaMemcpyHostToDevice, ctx->stream));
+    comm_allreduce_sum(ctx, ctx->dscal + 3990, 1);
+    FITRE_CUDA(cudaMemcpyAsync(&flag, ctx->dscal + 3990, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
+    stream_wait(ctx, ctx->stream);
+    cudaFree(stage);
+    if (flag == (double)W) {
+        ctx->peer.enabled = true;
+        ctx->peer.epoch = 0;
+        const double lim = ctx->comm_timeout_s < 30.0 ? ctx->comm_timeout_s : 30.0;
+        ctx->peer.wait_ns = (long long)(lim * 1e9);
+    } else {
+        peer_teardown(ctx);
+    }
+}
+}  // namespace
+
 void comm_destroy(fitre_context *ctx) {
+    peer_teardown(ctx);
     if (ctx->comm) {
         if (ctx->comm->side && !ctx->comm->aborted) api().CommDestroy(ctx->comm->side);
         if (ctx->comm->comm && !ctx->comm->aborted) api().CommDestroy(ctx->comm->comm);
@@ -286,8 +369,11 @@ void comm_init(fitre_context *ctx, const void *id128, int rank, int world) {
     // The side communicator: rank 0 draws a second id and hands it round through the first one.
     // FITRE_SIDE_COMM=0 keeps a single communicator (slices are then reduced in stream order).
     const char *sw = std::getenv("FITRE_SIDE_COMM");
-    if (sw && sw[0] == '0') return;
     try {
+        if (sw && sw[0] == '0') {
+            peer_setup(ctx);
+            return;
+        }
         ncclUniqueId id2;
         std::memset(&id2, 0, sizeof(id2));
         if (rank == 0) check(a.GetUniqueId(&id2), "ncclGetUniqueId");
@@ -300,6 +386,7 @@ void comm_init(fitre_context *ctx, const void *id128, int rank, int world) {
         ctx->comm->side = bounded_init(ctx, id2, rank, world);
         FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->comm->side_stream, cudaStreamNonBlocking));
         FITRE_CUDA(cudaEventCreateWithFlags(&ctx->comm->ev_done, cudaEventDisableTiming));
+        peer_setup(ctx);
     } catch (...) {
         comm_destroy(ctx);
         throw;

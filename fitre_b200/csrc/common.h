@@ -38,6 +38,16 @@ struct Error : std::runtime_error {
 
 struct Comm;  // NCCL state (comm.cpp)
 
+// Mailbox all-reduce over peer memory (set up in comm.cpp, used by peer.cu)
+#define FITRE_PEER_MAX_RANKS 8
+#define FITRE_PEER_MAX_DOUBLES 3584   // 7 sums x 512 channels
+struct PeerBox {
+    bool enabled = false;
+    double *inbox[FITRE_PEER_MAX_RANKS] = {};  // inbox[r]: rank r's mailbox mapped here (own rank: local)
+    unsigned long long epoch = 0;
+    long long wait_ns = 30000000000ll;          // bound of the device-side wait for the peers' flags
+};
+
 }  // namespace fitre
 
 // One context per GPU and host thread.  Owns only small fixed buffers (pinned scalars and a
@@ -57,6 +67,7 @@ struct fitre_context {
     double *pinned = nullptr;   // 256 pinned host doubles (scalar read-back)
     double *dscal = nullptr;    // 4096 device doubles (scalar reductions)
     fitre::Comm *comm = nullptr;
+    fitre::PeerBox peer;
     int rank = 0, world = 1;
     double comm_timeout_s = 300.0;  // bound of communicator set-up and of every host wait on a collective
     // workspace of the host-buffer entry point (allocated on first use, reused)
@@ -148,6 +159,13 @@ void comm_destroy(fitre_context *ctx);
 void comm_allreduce_async(fitre_context *ctx, double *dev_buf, size_t n);
 void comm_async_join(fitre_context *ctx);
 cudaStream_t comm_async_stream(fitre_context *ctx);
+// short vectors (batch statistics, scalars): one kernel over peer memory when the mailboxes are
+// up, NCCL otherwise
+void comm_allreduce_small(fitre_context *ctx, double *dev_buf, size_t n);
+// peer.cu
+bool peer_allreduce_ready(const fitre_context *ctx, long n);
+void peer_allreduce(fitre_context *ctx, const double *partials, int S, int NS, double *io, int n);
+int peer_wait_selftest(fitre_context *ctx, double wait_ms);
 // host wait on a stream; with a communicator it also watches NCCL's error state and a deadline
 void stream_wait(fitre_context *ctx, cudaStream_t stream);
 

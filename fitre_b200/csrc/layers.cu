@@ -167,9 +167,14 @@ double *channel_pass(fitre_context *ctx, const Op &op, int C, long rows, double 
     check_launch(ctx, name);
     if (NS > 0) {
         const int n = C * NS;
-        finalize_partials_kernel<<<(n + 127) / 128, 128, 0, ctx->stream>>>(partials, C, S, NS, sums);
-        check_launch(ctx, "finalize_partials_kernel");
-        if (sync) comm_allreduce_sum(ctx, sums, n);
+        if (sync && peer_allreduce_ready(ctx, n)) {
+            // slice sums and the exchange with the other ranks in one launch over peer memory
+            peer_allreduce(ctx, partials, S, NS, sums, n);
+        } else {
+            finalize_partials_kernel<<<(n + 127) / 128, 128, 0, ctx->stream>>>(partials, C, S, NS, sums);
+            check_launch(ctx, "finalize_partials_kernel");
+            if (sync) comm_allreduce_sum(ctx, sums, n);
+        }
     }
     return sums;
 }

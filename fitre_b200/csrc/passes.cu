@@ -128,7 +128,7 @@ double cnn_forward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET 
     const double inv_ng = 1.0 / ((double)n * ctx->world);
     softmax_loss(ctx, logits, data->sampledTrainY, n, classes, probs, errors, inv_ng);
     if (!want_loss) return 0.0;
-    comm_allreduce_sum(ctx, ctx->dscal, 1);
+    comm_allreduce_small(ctx, ctx->dscal, 1);
     FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost,
                                ctx->stream));
     stream_wait(ctx, ctx->stream);

@@ -132,7 +132,7 @@ void init_batch_norm_data(fitre_context *ctx, const CNN_MODEL *m, double *z) {
 double compute_hits(fitre_context *ctx, const double *probs, const double *target, int rows, int classes) {
     accuracy_kernel<<<1, kThreads, 0, ctx->stream>>>(probs, target, rows, classes, ctx->dscal);
     check_launch(ctx, "accuracy_kernel");
-    comm_allreduce_sum(ctx, ctx->dscal, 1);
+    comm_allreduce_small(ctx, ctx->dscal, 1);
     FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
     stream_wait(ctx, ctx->stream);
     return ctx->pinned[0];

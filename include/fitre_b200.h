@@ -319,6 +319,20 @@ int fitre_comm_world(const fitre_context *ctx);
  * libnccl.so.2.  The reference has no counterpart: every failure there is print + exit
  * (device/cuda_utils.h:28-92). */
 int fitre_set_comm_timeout(fitre_context *ctx, double seconds);
+/* Short vectors that the data-parallel passes exchange on their critical path (batch-norm
+ * statistics, about forty per step, and the loss) do not go through NCCL when the ranks share a
+ * node: every rank maps every other rank's mailbox (CUDA IPC, set up by fitre_comm_init) and one
+ * kernel -- the same launch that finishes the per-channel sums -- stores this rank's vector into all
+ * mailboxes, waits for the peers' flags in its own and adds the rows in rank order, so all ranks
+ * hold the same bits.  fitre_peer_reduce_enabled tells whether that path is up (it is all-or-nothing
+ * over the ranks; FITRE_PEER_REDUCE=0 in the environment, more than 8 ranks or a failed IPC mapping
+ * leave these vectors to NCCL).  The kernel's wait is bounded (the smaller of the communicator
+ * time-out and 30 s); when it runs out the call returns FITRE_ERR_COMM through the device error
+ * word.  fitre_peer_wait_selftest runs that kernel on ONE GPU against a two-rank mailbox whose
+ * second flag nothing raises and returns FITRE_ERR_COMM after about wait_ms: the host-visible
+ * proof that a lost peer ends in a status.  No counterpart in the reference. */
+int fitre_peer_reduce_enabled(const fitre_context *ctx);
+int fitre_peer_wait_selftest(fitre_context *ctx, double wait_ms);
 
 /* ---- model builders (nn/read_nn.c:500-725, nn/read_alexnet.c:14-243,
  *      nn/read_vgg.c:25-120,122-212,216-299, nn/utils.c:19-172) ---------- */

@@ -58,5 +58,9 @@ int ncclBroadcast(const void *s, void *r, size_t n, int dt, int root, void *comm
     (void)s; (void)r; (void)n; (void)dt; (void)root; (void)comm; (void)stream;
     return 0;   /* set-up traffic: never stalled */
 }
+int ncclAllGather(const void *s, void *r, size_t n, int dt, void *comm, cudaStream_t stream) {
+    (void)s; (void)r; (void)n; (void)dt; (void)comm; (void)stream;
+    return 0;   /* set-up traffic: the gathered IPC handles stay zero, so the peer path stays off */
+}
 const char *ncclGetErrorString(int r) { return r == 6 ? "remote error (fake)" : "fake result"; }
 int fake_nccl_count(int which) { return counts[which & 3]; }

@@ -181,7 +181,8 @@ def main():
         # Hessian-vector slices travel to the host as each layer's all-reduce completes)
         g_host, hv_host = np.zeros(model.pSize), np.zeros(model.pSize)
         loss_host = api.gradientHvHost(ctx, model, xs, ys, w, v, per, ncls, 0.0, g_host, hv_host)
-        np.savez(out, loss=loss64, gradient=g64, hv=hv, A=A.cpu().numpy(),
+        np.savez(out, loss=loss64, gradient=g64, hv=hv, A=A.cpu().numpy(), peer_reduce=int(ctx.peer_reduce_enabled),
+                 peer_launches=ctx.kernel_launches("peer_allreduce_kernel"),
                  loss_host=loss_host, gradient_host=g_host, hv_host=hv_host,
                  G=Gm.cpu().numpy(), Ainv=Ai.cpu().numpy(), Ginv=Gi.cpu().numpy(),
                  gradient_x3=run3.gradient, hv_x3=hv3, ng_rep=ng_rep, ng_owned=ng_owned[0],

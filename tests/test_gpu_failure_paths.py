@@ -130,3 +130,24 @@ def test_real_nccl_peer_never_joins():
     r = run_worker("real_peer_never_joins", {})
     assert r["status"] == S.ERR_COMM and r["seconds"] < 15
     assert r["world_after"] == 1 and r["single_gpu_status_after"] == 0
+
+
+def test_peer_allreduce_kernel_wait_is_bounded():
+    """The library's own small all-reduce waits on flags that other ranks raise in this rank's
+    mailbox.  On one GPU: a two-rank mailbox whose second flag nothing raises; the kernel gives up
+    after the limit, the call reports FITRE_ERR_COMM, and the context goes on working."""
+    import time
+    import gpu_util as G
+    from fitre_b200 import api
+    c = G.ctx()
+    t0 = time.time()
+    with pytest.raises(api.FitreError) as e:
+        c.peer_wait_selftest(300.0)
+    assert e.value.status == S.ERR_COMM
+    assert 0.25 < time.time() - t0 < 5.0
+    n = 4
+    model = nets.vgg_small(n)
+    api.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=2)
+    run = G.GpuRun(model, x, y, w, ncls)
+    assert np.isfinite(run.loss)

@@ -125,6 +125,8 @@ def test_two_gpu_cuda_matches_full_batch(tmp_path, builder):
         # every rank the natural gradient of the replicated form, with inverses and with Cholesky solves
         assert rel(res["ng_owned"], res["ng_rep"]) < 1e-9
         assert rel(res["ng_owned_chol"], res["ng_rep"]) < 1e-8
+        # the batch-norm statistics went through the library's own kernel over peer memory
+        assert int(res["peer_reduce"]) == 1 and int(res["peer_launches"]) > 0
         # host-buffer entry point with ranks: bit-identical to the device-resident calls
         assert float(res["loss_host"]) == float(res["loss"])
         assert np.array_equal(res["gradient_host"], res["gradient"])
