@@ -261,7 +261,7 @@ SECONDARY_NAMES = {"alexnet": "alexnetbn_32x32_fp64_gradient+hv",
                    "kfac": "vgg11bn_32x32_fp64_kfac_step(grad,sampled bwd,A/G factors,factorisations,natural gradient)"}
 
 
-def time_secondary(ctx, wl, world, rank, steps, warmup, kfac_solver="cholesky", graphs=True):
+def time_secondary(ctx, wl, world, rank, steps, warmup, kfac_solver="cholesky", graphs=True, one_call=False):
     """Device-timed steps of one secondary workload at the current rank count.
     alexnet: gradient + Hv, AlexNet-BN, 1024 images over the ranks (strong scaling);
     lenet: gradient, Hv and 10 Steihaug-CG iterations at 256 images per GPU;
@@ -286,6 +286,8 @@ def time_secondary(ctx, wl, world, rank, steps, warmup, kfac_solver="cholesky", 
         ctx.set_graphs(graphs)
         ctx.set_kfac_distribution(1)  # with ranks: factors stay on a layer's owner rank
         extra["kfac_solver"], extra["cuda_graphs"] = kfac_solver, bool(graphs)
+        extra["factor_calls"] = "one call after the sampled-label pass" if one_call else \
+            "A side started before the sampled-label pass, G side after it"
         if world > 1:
             extra["kfac_distribution"] = "layer_owned"
         info = api.computeKFACStorageIndices(model)
@@ -316,11 +318,19 @@ def time_secondary(ctx, wl, world, rank, steps, warmup, kfac_solver="cholesky", 
             api.cgSteihaug(ctx, model, data, ws.z, ws.probs, ws.errors, ws.dx, ws.gradient, p,
                            n, ws.dev, prm)
             extra["cg_iterations"], extra["cg_hv_calls"] = prm.iterations, prm.hvCalls
-        else:
+        elif one_call:
             api.computeDistributionErrors(ctx, ws.probs, U, tgt, e1b, n, 10)
             api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
             # A/G factors and the 22 damped factorisations (inverses or Cholesky), overlapped
             api.computeFactorsAndInverses(ctx, model, data, ws.z, ddx, n, A, Ai, G, Gi, info, iscr)
+            api.computeNaturalGradient(ctx, model, info, Ai, Gi, ws.gradient, ngrad, iscr)
+        else:
+            # A factors and their factorisation chains start on the library's own streams and run
+            # underneath the sampled-label backward pass; the G side joins them afterwards
+            api.computeOmegaZBegin(ctx, model, data, ws.z, n, A, Ai, info, iscr)
+            api.computeDistributionErrors(ctx, ws.probs, U, tgt, e1b, n, 10)
+            api.cnnBackward(ctx, model, data, kscr, ws.z, dgrad, ddx, e1b, e2b, 0, n)
+            api.computeLambdaDeltaFinish(ctx, model, ddx, n, G, Gi, info, iscr)
             api.computeNaturalGradient(ctx, model, info, Ai, Gi, ws.gradient, ngrad, iscr)
 
     def barrier():
@@ -656,7 +666,7 @@ def run_extra(args):
     if world > 1:
         ctx.comm_init_from_torch()
     r = time_secondary(ctx, args.workload, world, rank, args.steps, args.warmup, args.kfac_solver,
-                       not args.no_graphs)
+                       not args.no_graphs, args.kfac_one_call)
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
@@ -761,6 +771,9 @@ def main():
     ap.add_argument("--no-graphs", action="store_true",
                     help="kfac / fitre workloads: launch the factorisation and natural-gradient "
                          "sequences kernel by kernel instead of replaying their CUDA graphs")
+    ap.add_argument("--kfac-one-call", action="store_true",
+                    help="kfac workload: factors and factorisations in one call after the sampled-label "
+                         "backward pass instead of starting the A side before it")
     ap.add_argument("--skip-cpu", action="store_true",
                     help="leave the CPU baseline leg out (profiling runs)")
     ap.add_argument("--no-secondary", action="store_true",

@@ -29,6 +29,7 @@ SYMBOLS = [
     "fitre_kfac_omega_z_damped", "fitre_kfac_lambda_delta_damped",
     "fitre_kfac_invert_factors_mem_required", "fitre_kfac_invert_factors",
     "fitre_kfac_factors_and_inverses_mem_required", "fitre_kfac_factors_and_inverses",
+    "fitre_kfac_omega_z_begin", "fitre_kfac_lambda_delta_finish",
     "fitre_kfac_natural_gradient_mem_required", "fitre_compute_natural_gradient",
     "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host",
     "fitre_init_batch_norm_data", "fitre_evaluate_cnn_model", "fitre_compute_accuracy",
@@ -117,6 +118,8 @@ def load():
     sig("fitre_kfac_invert_factors", i, vp, MP, C.POINTER(S.KFAC_INFO), vp, vp, vp, vp, vp)
     sig("fitre_kfac_factors_and_inverses_mem_required", l, MP)
     sig("fitre_kfac_factors_and_inverses", i, vp, MP, vp, vp, vp, i, i, vp, vp, vp, vp, C.POINTER(S.KFAC_INFO), vp)
+    sig("fitre_kfac_omega_z_begin", i, vp, MP, vp, vp, i, i, vp, vp, C.POINTER(S.KFAC_INFO), vp)
+    sig("fitre_kfac_lambda_delta_finish", i, vp, MP, vp, i, i, vp, vp, C.POINTER(S.KFAC_INFO), vp)
     sig("fitre_kfac_natural_gradient_mem_required", l, MP)
     sig("fitre_compute_natural_gradient", i, vp, MP, C.POINTER(S.KFAC_INFO), vp, vp, vp, vp, vp)
     sig("fitre_syrk_tn_static_scratch", i, vp, l, i, l, d, vp, vp)

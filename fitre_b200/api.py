@@ -401,6 +401,21 @@ def computeFactorsAndInverses(ctx, model, data, z, dx, samples, omegaZ, omegaZIn
         devPtr.data_ptr()))
 
 
+def computeOmegaZBegin(ctx, model, data, z, samples, omegaZ, omegaZInv, info, devPtr):
+    """A factors and their damped factorisations, started on the library's own streams; returns at
+    once.  Pair with computeLambdaDeltaFinish; queue the sampled-label backward pass in between."""
+    ctx.check(ctx.lib.fitre_kfac_omega_z_begin(
+        ctx.h, C.byref(model), data.currentBatch, z.data_ptr(), 0, int(samples), omegaZ.data_ptr(),
+        omegaZInv.data_ptr(), C.byref(info), devPtr.data_ptr()))
+
+
+def computeLambdaDeltaFinish(ctx, model, dx, samples, lambdaG, lambdaGInv, info, devPtr):
+    """G factors and inverses, then waits for everything computeOmegaZBegin started."""
+    ctx.check(ctx.lib.fitre_kfac_lambda_delta_finish(
+        ctx.h, C.byref(model), dx.data_ptr(), 0, int(samples), lambdaG.data_ptr(), lambdaGInv.data_ptr(),
+        C.byref(info), devPtr.data_ptr()))
+
+
 def invertFactors(ctx, model, info, omegaZ, omegaZInv, lambdaG, lambdaGInv, devPtr):
     """All damped factor inverses of one KFAC step (several streams, divided among ranks)."""
     ctx.check(ctx.lib.fitre_kfac_invert_factors(ctx.h, C.byref(model), C.byref(info), omegaZ.data_ptr(),

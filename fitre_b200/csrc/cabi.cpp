@@ -129,6 +129,11 @@ int fitre_context_destroy(fitre_context *ctx) {
     if (ctx->graph_invert.exec) cudaGraphExecDestroy(ctx->graph_invert.exec);
     if (ctx->graph_natgrad.exec) cudaGraphExecDestroy(ctx->graph_natgrad.exec);
     if (ctx->graph_factors.exec) cudaGraphExecDestroy(ctx->graph_factors.exec);
+    if (ctx->graph_factors_a.exec) cudaGraphExecDestroy(ctx->graph_factors_a.exec);
+    if (ctx->graph_factors_g.exec) cudaGraphExecDestroy(ctx->graph_factors_g.exec);
+    if (ctx->phase_stream) cudaStreamDestroy(ctx->phase_stream);
+    if (ctx->phase_fork) cudaEventDestroy(ctx->phase_fork);
+    if (ctx->phase_done) cudaEventDestroy(ctx->phase_done);
     for (cudaEvent_t e : ctx->layer_ev) cudaEventDestroy(e);
     if (ctx->graph_stream) cudaStreamDestroy(ctx->graph_stream);
     if (ctx->ev_up) cudaEventDestroy(ctx->ev_up);

@@ -100,7 +100,11 @@ struct fitre_context {
         cudaGraphExec_t exec = nullptr;
         long long launches = 0;
     };
-    CapturedGraph graph_invert, graph_natgrad, graph_factors;
+    CapturedGraph graph_invert, graph_natgrad, graph_factors, graph_factors_a, graph_factors_g;
+    // two-call form of the factor step: the A side runs on a stream of its own between the calls
+    cudaStream_t phase_stream = nullptr;
+    cudaEvent_t phase_fork = nullptr, phase_done = nullptr;
+    bool phase_open = false;
     std::vector<cudaEvent_t> layer_ev;    // "factor of layer l is ready" (fused factors + inverses)
     cudaStream_t graph_stream = nullptr;  // origin stream of the captures
     int use_graphs = 1;

@@ -1201,6 +1201,217 @@ extern "C" int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MOD
     KFAC_ENTRY_END
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same work in two calls, so that the A side -- whose factorisations are chains of a thousand
+// small dependent kernels that leave most of the GPU idle -- runs underneath whatever the caller
+// queues between them (in the KFAC step: the second backward pass on the sampled labels, which
+// only the G factors depend on).
+//   fitre_kfac_omega_z_begin: A factors (they need the forward state only) and the factorisation
+//     of each as soon as it is ready, all on streams of the library's own, ordered after the work
+//     queued on the context's stream so far.  Returns without waiting; the context's stream does
+//     not wait either.
+//   fitre_kfac_lambda_delta_finish: G factors and their inverses, then the context's stream (and
+//     the host, for the "not positive definite" status) waits for everything both calls started.
+// Same bits as fitre_kfac_factors_and_inverses.
+// ---------------------------------------------------------------------------------------------
+namespace {
+struct PhasePlan {
+    std::vector<InvJob> jobs;
+    std::vector<char> mine;
+    std::vector<int> owner;
+    bool owned = false, chol = false;
+    double damp = 0.0;
+    int nl = 0;
+};
+PhasePlan make_phase_plan(fitre_context *ctx, const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const double *omegaZ,
+                          double *omegaZInv, const double *lambdaG, double *lambdaGInv) {
+    PhasePlan p;
+    const int W = ctx->world;
+    p.chol = ctx->kfac_solver == FITRE_KFAC_SOLVER_CHOLESKY;
+    p.damp = info->regLambda + info->dampGamma;
+    p.nl = m->cLayers + m->lLayers;
+    p.jobs = inverse_jobs(m, info, omegaZ, omegaZInv, lambdaG, lambdaGInv, p.chol);
+    p.mine.assign(p.jobs.size(), 1);
+    p.owned = W > 1 && ctx->kfac_owned;
+    p.owner.assign(p.nl, -1);
+    if (p.owned) {
+        p.owner = layer_owners(m, W, p.chol);
+        for (size_t i = 0; i < p.jobs.size(); ++i) p.mine[i] = p.owner[p.jobs[i].layer] == ctx->rank;
+    } else if (W > 1) {
+        std::vector<double> load(W, 0.0);
+        for (size_t i = 0; i < p.jobs.size(); ++i) {
+            const int r = (int)(std::min_element(load.begin(), load.end()) - load.begin());
+            load[r] += p.jobs[i].cost;
+            p.mine[i] = r == ctx->rank;
+        }
+    }
+    return p;
+}
+std::vector<long long> phase_key(fitre_context *ctx, const CNN_MODEL *m, const FITRE_KFAC_INFO *info,
+                                 const PhasePlan &p, const void *a, const void *b, const void *c, const void *d,
+                                 const void *e, int packed, int samples) {
+    std::vector<long long> key = {ptr_key(a), ptr_key(b), ptr_key(c), ptr_key(d), ptr_key(e), packed, samples,
+                                  bits_key(p.damp), ctx->kfac_solver, m->bias, info->OmegaZSize, info->LambdaGSize};
+    for (const InvJob &j : p.jobs) {
+        key.push_back(j.n);
+        key.push_back(ptr_key(j.dst));
+    }
+    for (int l = 0; l < m->cLayers; ++l) {
+        key.push_back(m->convLayer[l].height);
+        key.push_back(m->convLayer[l].width);
+        key.push_back(m->convLayer[l].outputOffset);
+        key.push_back(m->convLayer[l].batchNormOffset);
+        key.push_back(m->convLayer[l].activationOffset);
+    }
+    for (int l = 0; l <= p.nl; ++l) {
+        key.push_back(m->zOffsets[l]);
+        key.push_back(m->zztOffsets[l]);
+    }
+    return key;
+}
+// One side of the factors (A: doA, G: !doA) on ctx->stream with its factorisations forked onto the
+// side streams and joined back at the end.
+void run_factor_phase(fitre_context *ctx, const CNN_MODEL *m, const FITRE_KFAC_INFO *info, const PhasePlan &p,
+                      bool doA, const double *x0, const double *base, bool packed, int samples, double *factors,
+                      double *devPtr, int *fail) {
+    cudaStream_t main_stream = ctx->stream;
+    double *inv_scratch = devPtr + align32(fitre_kfac_mem_required(m));
+    const long per = align32(fitre_kfac_inverse_mem_required(max_block(m)));
+    std::vector<double> sload(kSideStreams, 0.0);
+    auto start_job = [&](const InvJob &j, cudaEvent_t ready) {
+        const int ns = j.factor_only ? kSideStreams : kInvStreams;
+        const int s = (int)(std::min_element(sload.begin(), sload.begin() + ns) - sload.begin());
+        sload[s] += j.cost;
+        FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ready, 0));
+        ctx->stream = ctx->inv_streams[s];
+        if (j.factor_only) factor_spd(ctx, j.src, j.dst, j.n, p.damp, fail);
+        else invert_spd(ctx, j.src, j.dst, j.n, p.damp, inv_scratch + (long)s * per, fail);
+        ctx->stream = main_stream;
+    };
+    try {
+        FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
+        for (int s = 0; s < kSideStreams; ++s) FITRE_CUDA(cudaStreamWaitEvent(ctx->inv_streams[s], ctx->inv_fork, 0));
+        if (!doA) {
+            for (int l = 0; l < p.nl; ++l)
+                lambda_delta_layer(ctx, m, base, packed, samples, factors, info, devPtr, l, p.owner[l]);
+            FITRE_CUDA(cudaEventRecord(ctx->inv_fork, main_stream));
+            for (size_t i = 0; i < p.jobs.size(); ++i)
+                if (p.mine[i] && p.jobs[i].src >= factors && p.jobs[i].src < factors + info->LambdaGSize)
+                    start_job(p.jobs[i], ctx->inv_fork);
+        } else {
+            std::vector<int> order(p.nl);
+            for (int l = 0; l < p.nl; ++l) order[l] = l;
+            auto block = [&](int l) {
+                return l < m->cLayers ? m->convLayer[l].inChannels * m->convLayer[l].kSize * m->convLayer[l].kSize
+                                      : m->fcLayer[l - m->cLayers].in;
+            };
+            std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return block(x) > block(y); });
+            for (int l : order) {
+                omega_z_layer(ctx, m, x0, base, packed, samples, factors, info, devPtr, l, p.owner[l]);
+                FITRE_CUDA(cudaEventRecord(ctx->layer_ev[l], main_stream));
+                for (size_t i = 0; i < p.jobs.size(); ++i)
+                    if (p.mine[i] && p.jobs[i].src == factors + info->OmegaZOffsets[l])
+                        start_job(p.jobs[i], ctx->layer_ev[l]);
+            }
+        }
+    } catch (...) {
+        ctx->stream = main_stream;
+        throw;
+    }
+    for (int s = 0; s < kSideStreams; ++s) {
+        FITRE_CUDA(cudaEventRecord(ctx->inv_join[s], ctx->inv_streams[s]));
+        FITRE_CUDA(cudaStreamWaitEvent(main_stream, ctx->inv_join[s], 0));
+    }
+}
+void ensure_phase_objects(fitre_context *ctx, int nl) {
+    ensure_side_streams(ctx);
+    while ((int)ctx->layer_ev.size() < nl) {
+        cudaEvent_t e;
+        FITRE_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        ctx->layer_ev.push_back(e);
+    }
+    if (!ctx->phase_stream) {
+        FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->phase_stream, cudaStreamNonBlocking));
+        FITRE_CUDA(cudaEventCreateWithFlags(&ctx->phase_fork, cudaEventDisableTiming));
+        FITRE_CUDA(cudaEventCreateWithFlags(&ctx->phase_done, cudaEventDisableTiming));
+    }
+}
+}  // namespace
+
+extern "C" int fitre_kfac_omega_z_begin(fitre_context *ctx, const CNN_MODEL *m, const real *x0, const real *zbase,
+                                        int packed, int samples, real *omegaZ, real *omegaZInv,
+                                        const FITRE_KFAC_INFO *info, real *devPtr) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(m && x0 && zbase && omegaZ && omegaZInv && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    FITRE_REQUIRE(!ctx->phase_open, FITRE_ERR_BAD_ARG, "fitre_kfac_omega_z_begin called twice without the finish call");
+    model_check_batch(m, samples);
+    require_scratch(ctx, fitre_kfac_factors_and_inverses_mem_required(m), "fitre_kfac_omega_z_begin");
+    // the G side's blocks are not touched here: placeholders that match no A block
+    double *none = reinterpret_cast<double *>((uintptr_t)64);
+    const PhasePlan p = make_phase_plan(ctx, m, info, omegaZ, omegaZInv, none, none);
+    int *fail = (int *)(ctx->dscal + 4002);
+    ensure_phase_objects(ctx, p.nl);
+    // everything of this call runs on the phase stream (and the side streams forked from it)
+    cudaStream_t user = ctx->stream;
+    FITRE_CUDA(cudaEventRecord(ctx->phase_fork, user));
+    FITRE_CUDA(cudaStreamWaitEvent(ctx->phase_stream, ctx->phase_fork, 0));
+    ctx->stream = ctx->phase_stream;
+    try {
+        std::vector<long long> key = phase_key(ctx, m, info, p, x0, zbase, omegaZ, omegaZInv, devPtr, packed, samples);
+        key.push_back(1);
+        auto body = [&] {
+            FITRE_CUDA(cudaMemsetAsync(fail, 0, sizeof(double), ctx->stream));
+            if (ctx->world > 1 && !p.owned) vec_fill(ctx, info->OmegaZSize, 0.0, omegaZInv);
+            run_factor_phase(ctx, m, info, p, true, x0, zbase, packed != 0, samples, omegaZ, devPtr, fail);
+        };
+        if (ctx->world > 1) {
+            body();
+            if (!p.owned) comm_allreduce_sum(ctx, omegaZInv, info->OmegaZSize);
+        } else {
+            run_graphed(ctx, ctx->graph_factors_a, key, body);
+        }
+        FITRE_CUDA(cudaEventRecord(ctx->phase_done, ctx->phase_stream));
+    } catch (...) {
+        ctx->stream = user;
+        throw;
+    }
+    ctx->stream = user;
+    ctx->phase_open = true;
+    KFAC_ENTRY_END
+}
+
+extern "C" int fitre_kfac_lambda_delta_finish(fitre_context *ctx, const CNN_MODEL *m, const real *dbase, int packed,
+                                              int samples, real *lambdaG, real *lambdaGInv,
+                                              const FITRE_KFAC_INFO *info, real *devPtr) {
+    KFAC_ENTRY_BEGIN
+    FITRE_REQUIRE(m && dbase && lambdaG && lambdaGInv && info && devPtr, FITRE_ERR_BAD_ARG, "NULL pointer argument");
+    FITRE_REQUIRE(ctx->phase_open, FITRE_ERR_BAD_ARG, "fitre_kfac_lambda_delta_finish without fitre_kfac_omega_z_begin");
+    model_check_batch(m, samples);
+    require_scratch(ctx, fitre_kfac_factors_and_inverses_mem_required(m), "fitre_kfac_lambda_delta_finish");
+    ctx->phase_open = false;
+    double *none = reinterpret_cast<double *>((uintptr_t)64);
+    const PhasePlan p = make_phase_plan(ctx, m, info, none, none, lambdaG, lambdaGInv);
+    int *fail = (int *)(ctx->dscal + 4002);
+    ensure_phase_objects(ctx, p.nl);
+    // the A side owns the scratch and the side streams until it is done: G comes after it
+    FITRE_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->phase_done, 0));
+    std::vector<long long> key = phase_key(ctx, m, info, p, dbase, lambdaG, lambdaGInv, devPtr, nullptr, packed, samples);
+    key.push_back(2);
+    auto body = [&] {
+        if (ctx->world > 1 && !p.owned) vec_fill(ctx, info->LambdaGSize, 0.0, lambdaGInv);
+        run_factor_phase(ctx, m, info, p, false, nullptr, dbase, packed != 0, samples, lambdaG, devPtr, fail);
+    };
+    if (ctx->world > 1) {
+        body();
+        if (!p.owned) comm_allreduce_sum(ctx, lambdaGInv, info->LambdaGSize);
+        comm_allreduce_sum(ctx, ctx->dscal + 4002, 1);  // a failure on any rank is seen by all
+    } else {
+        run_graphed(ctx, ctx->graph_factors_g, key, body);
+    }
+    check_fail_word(ctx, fail);
+    KFAC_ENTRY_END
+}
+
 namespace {
 long natural_gradient_layer_scratch(const CNN_MODEL *m) {
     long need = 0;

@@ -405,7 +405,7 @@ struct Rng {
 
 struct TrLayout {
     long indices, uniforms, A, Ainv, G, Ginv, gradient, distGradient, prevWeights, nGradient, z, dx,
-        distDX, probs, errors, dist1, dist2, distTarget, dInput, dZ, dLambda, scratch, total;
+        distDX, probs, errors, dist1, dist2, distTarget, dInput, dZ, dLambda, scratch, factorScratch, total;
 };
 TrLayout tr_layout(const CNN_MODEL *m, const DEVICE_DATASET *data, const FITRE_KFAC_INFO &info) {
     TrLayout L{};
@@ -445,6 +445,8 @@ TrLayout tr_layout(const CNN_MODEL *m, const DEVICE_DATASET *data, const FITRE_K
     need = std::max(need, fitre_kfac_natural_gradient_mem_required(m));
     need = std::max(need, fitre_generalization_mem_required(m));
     L.scratch = take(need);
+    // the A side of the factor step runs underneath the backward passes: scratch of its own
+    L.factorScratch = take(fitre_kfac_factors_and_inverses_mem_required(m));
     L.total = o;
     return L;
 }
@@ -490,7 +492,7 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
            *prevWeights = base + L.prevWeights, *nGradient = base + L.nGradient, *z = base + L.z,
            *dx = base + L.dx, *distDX = base + L.distDX, *probs = base + L.probs,
            *errors = base + L.errors, *dist1 = base + L.dist1, *dist2 = base + L.dist2,
-           *distTarget = base + L.distTarget, *work = base + L.scratch;
+           *distTarget = base + L.distTarget, *work = base + L.scratch, *fwork = base + L.factorScratch;
     const int invFreq = kfacInfo->inverseFreq > 1 ? kfacInfo->inverseFreq : 1;
     double *dInput = invFreq > 1 ? base + L.dInput : nullptr, *dZ = invFreq > 1 ? base + L.dZ : nullptr,
            *dLambda = invFreq > 1 ? base + L.dLambda : nullptr;
@@ -531,6 +533,12 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
 
             // gradient of the regularised loss (:343-362)
             const double trainLik = cnn_forward(ctx, m, data, work, z, probs, errors, B, true, false);
+            // Live-state factors: the A side needs the forward state only, so its factor products and
+            // the factorisation chains start here, on the library's own streams, and run underneath the
+            // two backward passes; the G side joins them after the sampled-label pass.
+            const bool two_call = invFreq <= 1;
+            if (two_call)
+                FITRE_RC(fitre_kfac_omega_z_begin(ctx, m, data->currentBatch, z, 0, B, A, Ainv, kfacInfo, fwork));
             vec_copy(ctx, (long)B * classes, errors, dist1);
             cnn_backward(ctx, m, data, work, z, gradient, dx, dist1, dist2, B);
             comm_allreduce_sum(ctx, gradient, P);
@@ -553,7 +561,9 @@ extern "C" int fitre_subsampled_trust_region_kfac(fitre_context *ctx, CNN_MODEL 
                 else refresh = false;
             }
             // one call forms the factors and inverts them, the factorisations under the factor products
-            if (refresh && from_avg)
+            if (two_call)
+                FITRE_RC(fitre_kfac_lambda_delta_finish(ctx, m, distDX, 0, B, G, Ginv, kfacInfo, fwork));
+            else if (refresh && from_avg)
                 FITRE_RC(fitre_kfac_factors_and_inverses(ctx, m, dInput, dZ, dLambda, 1, B, A, Ainv, G, Ginv,
                                                          kfacInfo, work));
             else if (refresh)

@@ -498,6 +498,30 @@ int fitre_kfac_factors_and_inverses(fitre_context *ctx, const CNN_MODEL *m, cons
                                     const real *zbase, const real *dbase, int packed, int samples,
                                     real *omegaZ, real *omegaZInv, real *lambdaG, real *lambdaGInv,
                                     const FITRE_KFAC_INFO *info, real *devPtr);
+/* fitre_kfac_factors_and_inverses as two calls, so that the A side -- whose factorisations are
+ * chains of about a thousand small dependent kernels that leave most of the GPU idle -- runs
+ * underneath whatever the caller queues between the two (in a KFAC step: the second backward pass on
+ * the sampled labels, which only the G factors depend on).
+ *   fitre_kfac_omega_z_begin: the A factors (they need the forward state z only) and the damped
+ *     factorisation of each as soon as it is ready, on streams of the library's own, ordered after
+ *     everything queued on the context's stream so far.  Returns without waiting, and the context's
+ *     stream does not wait either: omegaZ / omegaZInv and devPtr belong to the library until the
+ *     finish call returns.
+ *   fitre_kfac_lambda_delta_finish: the G factors and their inverses (after the A side, with which
+ *     they share devPtr), then the context's stream and the host wait for everything both calls
+ *     started; FITRE_ERR_NOT_CONVERGED as in the one-call form.
+ * devPtr: fitre_kfac_factors_and_inverses_mem_required(m) doubles, the same buffer in both calls
+ * and not the scratch of the work queued in between.  Same bits as the one-call form; follows
+ * fitre_set_kfac_solver / fitre_set_kfac_distribution.  Reference: the two halves are
+ * computeOmegaZ and computeLambdaDelta (solvers/kfac_inverses.cu:450-630,759-857), which it
+ * runs one after the other. */
+int fitre_kfac_omega_z_begin(fitre_context *ctx, const CNN_MODEL *m, const real *x0, const real *zbase,
+                             int packed, int samples, real *omegaZ, real *omegaZInv,
+                             const FITRE_KFAC_INFO *info, real *devPtr);
+int fitre_kfac_lambda_delta_finish(fitre_context *ctx, const CNN_MODEL *m, const real *dbase, int packed,
+                                   int samples, real *lambdaG, real *lambdaGInv,
+                                   const FITRE_KFAC_INFO *info, real *devPtr);
+
 /* solvers/kfac_natural_gradient.cu:36-241 (computeNaturalGradient): nGradient = G^-1 [W|b] A^-1
  * per layer, in the flat layout of `gradient`.  omegaZInv / lambdaGInv hold what
  * fitre_kfac_invert_factors left there under the same solver setting: the inverted factors at

@@ -565,6 +565,58 @@ def test_cuda_cholesky_solve_natural_gradient_large_blocks():
     assert G.rel(ng_h, ng_inv.cpu().numpy()) < 1e-9
 
 
+def test_cuda_two_call_factor_step_same_bits_as_one_call():
+    """fitre_kfac_omega_z_begin / fitre_kfac_lambda_delta_finish around the sampled-label backward
+    pass (the A side runs underneath it on the library's own streams) against
+    fitre_kfac_factors_and_inverses after it: identical factors, inverses and Cholesky factors, on
+    the first call (graph capture) and on the replay, and the scratch of the pass in between is
+    left alone."""
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    L = _lib.load()
+    for model, n in ((nets.vgg11(2), 2), (nets.vgg_small(6), 6), (nets.alexnet_small(4, bias=True), 4)):
+        O.finalize(model)
+        x, y, w, v, ncls = G.synth(model, n, seed=91)
+        run = G.GpuRun(model, x, y, w, ncls)
+        ws = run.ws
+        info = api.computeKFACStorageIndices(model)
+        info.regLambda, info.dampGamma = 1e-3, 1e-2
+        u = G.dev(np.random.default_rng(5).random(n))
+        md = model.maxDeltaSize + n * ncls
+        fscr = G.dev(np.zeros(L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model))))
+        kscr = G.dev(np.zeros(max(L.fitre_kfac_mem_required(C.byref(model)), ws.dev.numel())))
+
+        def sampled_backward():
+            t, e1, e2 = G.dev(np.zeros(n)), G.dev(np.zeros(md)), G.dev(np.zeros(md))
+            api.computeDistributionErrors(run.c, ws.probs, u, t, e1, n, ncls)
+            g2, dx2 = G.dev(np.zeros(model.pSize)), G.dev(np.zeros(model.zSize))
+            api.cnnBackward(run.c, model, run.data, kscr, ws.z, g2, dx2, e1, e2, 0, n)
+            return g2, dx2
+
+        for solver in (0, 1):
+            run.c.set_kfac_solver(solver)
+            try:
+                g_ref, dx_ref = sampled_backward()
+                A1, G1, Ai1, Gi1 = (G.dev(np.zeros(k)) for k in (info.OmegaZSize, info.LambdaGSize) * 2)
+                api.computeFactorsAndInverses(run.c, model, run.data, ws.z, dx_ref, n, A1, Ai1, G1, Gi1, info, fscr)
+                for _ in range(2):  # capture, then replay
+                    A2, G2, Ai2, Gi2 = (G.dev(np.zeros(k)) for k in (info.OmegaZSize, info.LambdaGSize) * 2)
+                    api.computeOmegaZBegin(run.c, model, run.data, ws.z, n, A2, Ai2, info, fscr)
+                    g2, dx2 = sampled_backward()
+                    api.computeLambdaDeltaFinish(run.c, model, dx2, n, G2, Gi2, info, fscr)
+                    assert np.array_equal(g2.cpu().numpy(), g_ref.cpu().numpy())
+                    assert np.array_equal(dx2.cpu().numpy(), dx_ref.cpu().numpy())
+                    for a, b in ((A1, A2), (G1, G2), (Ai1, Ai2), (Gi1, Gi2)):
+                        assert np.array_equal(a.cpu().numpy(), b.cpu().numpy()), solver
+            finally:
+                run.c.set_kfac_solver(0)
+        # the finish call without its begin call is refused
+        with pytest.raises(api.FitreError) as e:
+            api.computeLambdaDeltaFinish(run.c, model, dx_ref, n, G1, Gi1, info, fscr)
+        assert e.value.status == S.ERR_BAD_ARG
+        del run
+
+
 def test_cuda_matrix_inverse_blocked_sizes_and_failure():
     """Sizes that exercise the blocked path (several 64-blocks, ragged last block) and the
     not-positive-definite status."""
