@@ -52,8 +52,11 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
     constexpr int T_CB = chunk_channels(KS);
     constexpr int KROWS = T_CB * KS * KS;   // rows of the weight matrix one chunk consumes: 36 / 50
     constexpr int KCH = (KROWS + 3) & ~3;   // rows one stage holds: 36 / 52
-    extern __shared__ unsigned char smraw[];
-    unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 127) & ~(uintptr_t)127);
+    // Aligned by declaration, not by rounding the address: a pointer that went through an integer is a
+    // generic pointer to the compiler, and generic loads of shared memory cost the DMMA loop 5 %
+    // (35.2 against 37.0 TFLOP/s in a fragment-load + DMMA loop over a resident tile).
+    extern __shared__ __align__(1024) unsigned char smraw[];
+    unsigned char *sm = smraw;
     const int stageBytes = p.patchBytes + KCH * T_BN * 8;
     int *colofs = (int *)(sm + (size_t)p.stages * stageBytes);
     unsigned long long *bars = (unsigned long long *)(colofs + ((KCH + 3) & ~3) + 4);
@@ -220,8 +223,8 @@ struct alignas(64) TmaWgradArgs {
 template <int KS, int BMT>
 __global__ void __launch_bounds__(T_THREADS, 2)
 wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
-    extern __shared__ unsigned char smraw[];
-    unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char smraw[];
+    unsigned char *sm = smraw;
     constexpr int dBytes = BMT * W_BN * 8;           // BMT/16 swizzled boxes of 16 x 64 doubles
     const int stageBytes = dBytes + p.patchBytes;    // [errors | patch], both 1024-aligned
     int *rowbase_s = (int *)(sm + (size_t)p.stages * stageBytes);
@@ -374,8 +377,8 @@ __global__ void __launch_bounds__(T_THREADS, 2)
 patch_syrk_tma_kernel(const __grid_constant__ TmaSyrkArgs p) {
     const int q0 = blockIdx.x * W_BQ, c0 = blockIdx.y * W_BN;
     if (c0 > q0 + W_BQ - 1) return;  // strictly above the diagonal: mirrored by the reducer
-    extern __shared__ unsigned char smraw[];
-    unsigned char *sm = (unsigned char *)(((uintptr_t)smraw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char smraw[];
+    unsigned char *sm = smraw;
     const int stageBytes = p.patchBytesA + p.patchBytesB;  // [patch of the rows | patch of the columns]
     int *rowbase_s = (int *)(sm + (size_t)p.stages * stageBytes);
     unsigned long long *bars = (unsigned long long *)(rowbase_s + BMT);

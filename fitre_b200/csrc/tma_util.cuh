@@ -32,6 +32,20 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 // Bounded wait: gives up after ~2^31 clock ticks and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+#ifdef FITRE_FAST_WAIT
+    for (unsigned spins = 0; spins < (1u << 28); ++spins) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+#endif
     const long long t0 = clock64();
     for (;;) {
         uint32_t ok;
