@@ -267,13 +267,16 @@ void conv_post_rop_forward(fitre_context *ctx, const ConvGeom &g, int N, const d
                            double *rzl, double *scratch);
 // pooled errors -> dx_P, dx_A, dx_BN (written into dxl); returns pointer to the errors the
 // convolution consumes (dx_BN or dx_A).  db (may be NULL) receives the bias gradient.
+// `pool_map` (pool_map_doubles(g, N) doubles of scratch, may be NULL): room for the arg-max map of
+// the layer's pooling windows, which the backward gather of a general max pool then reads
+long pool_map_doubles(const ConvGeom &g, int N);
 const double *conv_post_backward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
                                  double *dxl, const double *delta_pool, double *db,
-                                 double *scratch);
+                                 double *scratch, unsigned char *pool_map = nullptr);
 // R-op of the backward chain: Rdelta_pool -> Rdelta for the convolution (written to `rout`).
 void conv_post_rop_backward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
                             const double *rzl, const double *dxl, const double *rdelta_pool,
-                            double *rout, double *rdb, double *scratch);
+                            double *rout, double *rdb, double *scratch, unsigned char *pool_map = nullptr);
 void conv_to_fc(fitre_context *ctx, double *buf, int C, int N, int Hp, int Wp, double *tmp);
 void fc_to_conv(fitre_context *ctx, double *buf, int C, int N, int Hp, int Wp, double *tmp);
 void act_backward(fitre_context *ctx, int act, double *delta, const double *zin,

@@ -752,12 +752,14 @@ bool conv_fprop_tma(fitre_context *ctx, int nseg, const ConvSeg *segs, const dou
     }
     dim3 grid((unsigned)(a.tilesW * tilesN), (unsigned)((Cout + T_BN - 1) / T_BN), (unsigned)SK);
     const int smem = a.stages * stageBytes + fixed;
-    ProfScope prof(ctx, PROF_CONV_IGEMM, 2.0 * (double)a.M * K * Cout * nseg);
-    if (k == 3)
-        conv_tma_kernel<3><<<grid, T_THREADS, smem, ctx->stream>>>(a);
-    else
-        conv_tma_kernel<5><<<grid, T_THREADS, smem, ctx->stream>>>(a);
-    check_launch(ctx, "conv_tma_kernel");
+    {   // the event pair brackets the product kernel alone, not the slab reducer behind it
+        ProfScope prof(ctx, PROF_CONV_IGEMM, 2.0 * (double)a.M * K * Cout * nseg);
+        if (k == 3)
+            conv_tma_kernel<3><<<grid, T_THREADS, smem, ctx->stream>>>(a);
+        else
+            conv_tma_kernel<5><<<grid, T_THREADS, smem, ctx->stream>>>(a);
+        check_launch(ctx, "conv_tma_kernel");
+    }
     if (SK > 1) {
         const long n = a.M * Cout;
         const int blocks = (int)std::min<long>((n + 255) / 256, 148 * 8);

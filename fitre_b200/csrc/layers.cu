@@ -246,6 +246,11 @@ struct NormActOp {  // bn out (optional) and activation out
 
 struct PoolGeom {
     int type, pk, ps, pp, H, W, Hp, Wp;  // H,W: pool input (= conv output) plane
+    // optional: for every pooling window the position of its arg-max inside the window
+    // (column * pk + row, 255 = empty window), laid out like the pooled tensor; filled by
+    // pool_argmax_map_kernel so that the gather below compares one byte per covering window
+    // instead of re-scanning the window's pk * pk activations
+    const unsigned char *map;
 };
 
 // arg-max of one pooling window, scan order of the backward kernel: column outer, row inner,
@@ -273,7 +278,8 @@ __device__ __forceinline__ int window_argmax(const double *plane, const PoolGeom
 // errors arriving at element (h, w) of one plane through the pooling layer (gather form of
 // functions/dev_pool.cu:269-298,346-398 and the 1/k^2 scale of functions/cnn_backward.cu:471-473)
 __device__ __forceinline__ double pool_gather(const double *dpool_plane, const double *act_plane,
-                                              const PoolGeom &g, int h, int w) {
+                                              const PoolGeom &g, int h, int w,
+                                              const unsigned char *map_plane = nullptr) {
     if (g.type == FITRE_NO_POOL) return dpool_plane[w * g.H + h];
     if (g.type == FITRE_AVG_POOL) {
         const int k = h / g.pk, l = w / g.pk;
@@ -288,6 +294,14 @@ __device__ __forceinline__ double pool_gather(const double *dpool_plane, const d
     const int lmax = min((w + g.pp) / g.ps, g.Wp - 1);
     const int me = w * g.H + h;
     double s = 0.0;
+    if (map_plane) {
+        for (int l = lmin; l <= lmax; ++l)
+            for (int k = kmin; k <= kmax; ++k) {
+                const int code = (w - (l * g.ps - g.pp)) * g.pk + (h - (k * g.ps - g.pp));
+                if (map_plane[l * g.Hp + k] == code) s += dpool_plane[l * g.Hp + k];
+            }
+        return s;
+    }
     for (int l = lmin; l <= lmax; ++l)
         for (int k = kmin; k <= kmax; ++k)
             if (window_argmax(act_plane, g, k, l) == me) s += dpool_plane[l * g.Hp + k];
@@ -299,7 +313,8 @@ __device__ __forceinline__ double pool_gather(const double *dpool_plane, const d
 // is resolved from the two window columns directly; everything else takes the general gather.
 template <int V>
 __device__ __forceinline__ Pk<V> pool_gather_v(const double *dpool_plane, const double *act_plane,
-                                               const PoolGeom &g, int h, int w, const Pk<V> &a) {
+                                               const PoolGeom &g, int h, int w, const Pk<V> &a,
+                                               const unsigned char *map_plane = nullptr) {
     Pk<V> out;
     if (V == 2 && g.type == FITRE_MAX_POOL && g.pk == 2 && g.ps == 2 && g.pp == 0 &&
         !(g.H & 1) && !(g.W & 1)) {
@@ -320,7 +335,7 @@ __device__ __forceinline__ Pk<V> pool_gather_v(const double *dpool_plane, const 
     }
     if (g.type == FITRE_NO_POOL) return ldp<V>(dpool_plane + w * g.H + h);
 #pragma unroll
-    for (int e = 0; e < V; ++e) out.v[e] = pool_gather(dpool_plane, act_plane, g, h + e, w);
+    for (int e = 0; e < V; ++e) out.v[e] = pool_gather(dpool_plane, act_plane, g, h + e, w, map_plane);
     return out;
 }
 
@@ -356,7 +371,8 @@ struct PoolActBwdOp {  // dxP, dxA (+ sums: dA [, dA*zhat])
         const double *aplane = actv + ch.cbase + (long)n * ch.hw;
         const double *pplane = dpool + ch.pbase + (long)n * (g.type == FITRE_NO_POOL ? ch.hw : ch.pw);
         const Pk<V> av = ldp<V>(actv + i), zi = ldp<V>(zin + i);
-        const Pk<V> dP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av);
+        const unsigned char *mplane = g.map ? g.map + ch.pbase + (long)n * ch.pw : nullptr;
+        const Pk<V> dP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av, mplane);
         Pk<V> dA;
 #pragma unroll
         for (int e = 0; e < V; ++e) {
@@ -469,7 +485,8 @@ struct RPoolActBwdOp {  // RdA = h' RdP + h'' Rzin dxP   (+ sums, see conv_post_
         const double *pplane = rdpool + pc.pbase + (long)n * (g.type == FITRE_NO_POOL ? pc.hw : pc.pw);
         const Pk<V> av = ldp<V>(actv + i), zi = ldp<V>(zin + i), rzh = ldp<V>(rzin + i);
         const Pk<V> dp = ldp<V>(dxP + i);
-        const Pk<V> RdP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av);
+        const unsigned char *mplane = g.map ? g.map + pc.pbase + (long)n * pc.pw : nullptr;
+        const Pk<V> RdP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av, mplane);
         Pk<V> RdA;
 #pragma unroll
         for (int e = 0; e < V; ++e)
@@ -529,6 +546,23 @@ struct RBnBwdApplyOp {
 };
 
 // ---- stand-alone kernels ---------------------------------------------------------------------
+// One thread per pooling window: where inside the window its arg-max lies (see PoolGeom::map).
+__global__ void pool_argmax_map_kernel(const double *act, unsigned char *map, long planes, PoolGeom g) {
+    const long total = planes * g.Hp * g.Wp;
+    for (long t = blockIdx.x * (long)blockDim.x + threadIdx.x; t < total; t += (long)gridDim.x * blockDim.x) {
+        const long plane = t / (g.Hp * g.Wp);
+        const int rem = (int)(t - plane * (g.Hp * g.Wp));
+        const int l = rem / g.Hp, k = rem - l * g.Hp;
+        const int arg = window_argmax(act + plane * (long)(g.H * g.W), g, k, l);
+        int code = 255;
+        if (arg >= 0) {
+            const int w = arg / g.H, h = arg - w * g.H;
+            code = (w - (l * g.ps - g.pp)) * g.pk + (h - (k * g.ps - g.pp));
+        }
+        map[t] = (unsigned char)code;
+    }
+}
+
 __global__ void pool_forward_kernel(const double *in, double *out, long planes, PoolGeom g) {
     const long total = planes * g.Hp * g.Wp;
     for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total;
@@ -757,6 +791,7 @@ bool vec2_ok(const ConvGeom &g, int N, std::initializer_list<const void *> ptrs)
 
 PoolGeom pool_geom(const ConvGeom &g) {
     PoolGeom p;
+    p.map = nullptr;
     p.type = g.poolType;
     p.pk = g.pk; p.ps = g.ps; p.pp = g.pp;
     p.H = g.Ho; p.W = g.Wo;
@@ -767,6 +802,28 @@ PoolGeom pool_geom(const ConvGeom &g) {
 }  // namespace
 
 long bn_scratch(int) { return kScratchDoubles; }
+
+namespace {
+bool pool_wants_map(const ConvGeom &g) {
+    if (g.poolType != FITRE_MAX_POOL || g.pk > 15) return false;
+    const bool fast = g.pk == 2 && g.ps == 2 && g.pp == 0 && !(g.Ho & 1) && !(g.Wo & 1);
+    return !fast;  // the 2/2/0 pool resolves its window from two loads
+}
+// fills the arg-max map of this layer's pooling windows and hands it to the gather
+void prepare_pool_map(fitre_context *ctx, const ConvGeom &g, int N, const double *act, unsigned char *map,
+                      PoolGeom &pg) {
+    if (!map || !pool_wants_map(g)) return;
+    const long planes = (long)g.Cout * N;
+    pool_argmax_map_kernel<<<grid_for(planes * g.Hp * g.Wp), kThreads, 0, ctx->stream>>>(act, map, planes, pg);
+    check_launch(ctx, "pool_argmax_map_kernel");
+    pg.map = map;
+}
+}  // namespace
+
+// doubles of scratch the backward passes need for the arg-max map of layer g's pooling windows
+long pool_map_doubles(const ConvGeom &g, int N) {
+    return pool_wants_map(g) ? ((long)g.Cout * N * g.Hp * g.Wp + 7) / 8 : 0;
+}
 
 void add_channel_bias(fitre_context *ctx, double *x, const double *bias, long rows, int C) {
     const long total = rows * C;
@@ -866,11 +923,12 @@ void conv_post_rop_forward(fitre_context *ctx, const ConvGeom &g, int N, const d
 
 const double *conv_post_backward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
                                  double *dxl, const double *delta_pool, double *db,
-                                 double *scratch) {
+                                 double *scratch, unsigned char *pool_map) {
     const long rows = (long)N * g.Ho * g.Wo;
     const double m = (double)rows * ctx->world;
     const double *zin = g.bn ? zl + g.bnOff : zl;
-    const PoolGeom pg = pool_geom(g);
+    PoolGeom pg = pool_geom(g);
+    prepare_pool_map(ctx, g, N, zl + g.actOff, pool_map, pg);
     const bool v2 = vec2_ok(g, N, {zl, dxl, g.poolType == FITRE_NO_POOL ? delta_pool : nullptr});
     if (g.bn) {
         PoolActBwdOp<2> op{delta_pool, zl + g.actOff, zin, dxl, dxl + g.actOff, rows, pg, g.act};
@@ -904,10 +962,11 @@ const double *conv_post_backward(fitre_context *ctx, const ConvGeom &g, int N, c
 
 void conv_post_rop_backward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
                             const double *rzl, const double *dxl, const double *rdelta_pool,
-                            double *rout, double *rdb, double *scratch) {
+                            double *rout, double *rdb, double *scratch, unsigned char *pool_map) {
     const long rows = (long)N * g.Ho * g.Wo;
     const double m = (double)rows * ctx->world;
-    const PoolGeom pg = pool_geom(g);
+    PoolGeom pg = pool_geom(g);
+    prepare_pool_map(ctx, g, N, zl + g.actOff, pool_map, pg);
     const double *zin = g.bn ? zl + g.bnOff : zl;
     const double *rzin = g.bn ? rzl + g.bnOff : rzl;
     const double *mean = g.bn ? zl + g.bnOff + g.meanOff : nullptr;

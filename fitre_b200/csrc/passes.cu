@@ -54,6 +54,11 @@ long max_split_scratch(const CNN_MODEL *m) {
     }
     return v;
 }
+long max_pool_map(const CNN_MODEL *m) {
+    long v = 0;
+    for (int l = 0; l < m->cLayers; ++l) v = std::max(v, pool_map_doubles(conv_geom(m, l), m->batchSize));
+    return v;
+}
 long max_fc_elems(const CNN_MODEL *m) {
     long v = 0;
     for (int l = 0; l < m->lLayers; ++l)
@@ -84,12 +89,12 @@ long forward_scratch(const CNN_MODEL *m) {
 long rop_forward_scratch(const CNN_MODEL *m) { return forward_scratch(m); }
 long backward_scratch(const CNN_MODEL *m) {
     return bn_scratch(0) + align32(last_pool_elems(m)) + align32(max_wgrad_scratch(m)) +
-           align32(max_weight_elems(m)) + align32(max_split_scratch(m));
+           align32(max_weight_elems(m)) + align32(max_split_scratch(m)) + align32(max_pool_map(m));
 }
 long rop_backward_scratch(const CNN_MODEL *m) {
     return bn_scratch(0) + align32(last_pool_elems(m)) + align32(max_wgrad_scratch(m)) +
            2 * align32(max_weight_elems(m)) + align32(max_conv_volume(m)) +
-           2 * align32(max_fc_elems(m)) + align32(max_split_scratch(m));
+           2 * align32(max_fc_elems(m)) + align32(max_split_scratch(m)) + align32(max_pool_map(m));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -146,6 +151,7 @@ void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *
     double *wg = tmp + align32(last_pool_elems(m));
     double *wperm = wg + align32(max_wgrad_scratch(m));
     double *split = wperm + align32(max_weight_elems(m));
+    unsigned char *pmap = max_pool_map(m) ? (unsigned char *)(split + align32(max_split_scratch(m))) : nullptr;
     const ConvGeom lg = conv_geom(m, cL - 1);
 
     for (int f = lL - 1; f >= 0; --f) {  // functions/cnn_backward.cu:111-280
@@ -169,7 +175,7 @@ void cnn_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *
         const double *zl = z + g.zoff;
         double *dxl = dx + g.zoff;
         const double *dconv = conv_post_backward(ctx, g, n, zl, dxl, delta,
-                                                 m->bias ? gradient + m->bOffsets[c] : nullptr, bnws);
+                                                 m->bias ? gradient + m->bOffsets[c] : nullptr, bnws, pmap);
         ConvSeg wseg{layer_input(m, data, z, c), dconv};
         conv_wgrad(ctx, 1, &wseg, gradient + m->wOffsets[c], n, g.Cin, g.H, g.W, g.k, g.pad, g.Cout, wg);
         reduce_finished_slice(ctx, gradient, m->wOffsets[c]);
@@ -259,6 +265,7 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
     double *t1 = rout + align32(max_conv_volume(m));
     double *t2 = t1 + align32(max_fc_elems(m));
     double *split = t2 + align32(max_fc_elems(m));
+    unsigned char *pmap = max_pool_map(m) ? (unsigned char *)(split + align32(max_split_scratch(m))) : nullptr;
     const ConvGeom lg = conv_geom(m, cL - 1);
 
     for (int f = lL - 1; f >= 0; --f) {  // functions/cnn_hv_backward.cu:153-395
@@ -298,7 +305,7 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
         const ConvGeom g = conv_geom(m, c);
         const double *zl = z + g.zoff, *rzl = rz + g.zoff, *dxl = dx + g.zoff;
         conv_post_rop_backward(ctx, g, n, zl, rzl, dxl, rError, rout,
-                               m->bias ? hv + m->bOffsets[c] : nullptr, bnws);
+                               m->bias ? hv + m->bOffsets[c] : nullptr, bnws, pmap);
         const double *dprev = g.bn ? dxl + g.bnOff : dxl + g.actOff;
         // R dW = im2col(X)' Rdelta + im2col(RX)' delta  (:727-803)
         ConvSeg ws[2];
