@@ -927,43 +927,6 @@ long long bits_key(double v) {
     std::memcpy(&b, &v, sizeof b);
     return b;
 }
-// A captured graph does not keep the priorities of the streams its nodes were captured on.  The
-// kernels of the factorisation and solve chains have small grids and sit on the critical path; the
-// factor products beside them fill the GPU.  Kernel nodes with few blocks therefore get the highest
-// priority, so that their blocks go first whenever a slot frees up.  (FITRE_SIDE_PRIORITY=0: off.)
-void prioritise_small_kernels(cudaGraph_t graph) {
-    const char *sw = std::getenv("FITRE_SIDE_PRIORITY");
-    if (sw && sw[0] == '0') return;
-    int lo = 0, hi = 0;
-    if (cudaDeviceGetStreamPriorityRange(&lo, &hi) != cudaSuccess || lo == hi) {
-        cudaGetLastError();
-        return;
-    }
-    size_t n = 0;
-    if (cudaGraphGetNodes(graph, nullptr, &n) != cudaSuccess || n == 0) {
-        cudaGetLastError();
-        return;
-    }
-    std::vector<cudaGraphNode_t> nodes(n);
-    if (cudaGraphGetNodes(graph, nodes.data(), &n) != cudaSuccess) {
-        cudaGetLastError();
-        return;
-    }
-    for (size_t i = 0; i < n; ++i) {
-        cudaGraphNodeType t;
-        if (cudaGraphNodeGetType(nodes[i], &t) != cudaSuccess || t != cudaGraphNodeTypeKernel) continue;
-        cudaKernelNodeParams kp;
-        if (cudaGraphKernelNodeGetParams(nodes[i], &kp) != cudaSuccess) continue;
-        const unsigned long long blocks = (unsigned long long)kp.gridDim.x * kp.gridDim.y * kp.gridDim.z;
-        if (blocks > 192) continue;
-        cudaLaunchAttributeValue v;
-        std::memset(&v, 0, sizeof(v));
-        v.priority = hi;
-        cudaGraphKernelNodeSetAttribute(nodes[i], cudaLaunchAttributePriority, &v);
-    }
-    cudaGetLastError();
-}
-
 // Runs enqueue() -- which issues work on ctx->stream and on the side streams forked from it --
 // through a CUDA graph: captured on first use (from a stream of the library's own, because the
 // caller's may be the legacy default stream, which cannot be captured), replayed on ctx->stream
@@ -1003,7 +966,6 @@ void run_graphed(fitre_context *ctx, fitre_context::CapturedGraph &g, const std:
         }
         ctx->stream = user;
         e = cudaStreamEndCapture(ctx->graph_stream, &graph);
-        if (e == cudaSuccess) prioritise_small_kernels(graph);
         if (e == cudaSuccess) e = cudaGraphInstantiate(&g.exec, graph, 0);
         if (graph) cudaGraphDestroy(graph);
     }
