@@ -245,3 +245,87 @@ def test_vgg11_bn_256_kfac_step():
             worst = max(worst, e / tol)
             assert e < tol, (l, e, kap)
     assert worst < 1.0
+
+
+def test_vgg11_bn_512_tf32x3_tolerance_and_argmax_flips():
+    """The error-compensated tensor-core mode (3 x TF32 on tcgen05) at the benchmark size, against
+    the fp64 result of the same library (which the tests above pin to the oracle).
+
+    Stated tolerance, relative and norm-wise: 1e-3 for loss, gradient and Hessian-vector product
+    wherever the routing of max pooling is that of the fp64 run; 1e-2 when the mode's own forward
+    pass decides the routing of a max-pooling net at this batch size.  The second figure is not
+    arithmetic: among 8.5 M pooling windows a few dozen near-ties flip under a 1e-6 perturbation
+    of the activations, and every flip re-routes an error path.  Shown three ways:
+      (1) average pooling, same net and size: within 1e-3;
+      (2) max pooling with the fp64 forward state kept and only the backward / R passes in the
+          tensor-core mode (the routing is read from the stored activations): within 1e-3;
+      (3) max pooling end to end in the mode: the flipped windows are counted and are few."""
+    import torch
+    import gpu_util as G
+    from fitre_b200 import api
+    n = 512
+    c = G.ctx()
+    results = {}
+    for pool in (S.AVG_POOL, S.MAX_POOL):
+        model = nets.vgg11(n, pool=pool)
+        O.finalize(model)
+        x, y, w, v, ncls = G.synth(model, n, seed=3234)
+        run = G.GpuRun(model, x, y, w, ncls)
+        g64, loss64 = run.gradient.copy(), run.loss
+        hv64 = run.hv(v)
+        if pool == S.MAX_POOL:
+            # (2) fp64 forward state, tensor-core backward and R passes
+            ws = run.ws
+            c.set_precision(2)
+            try:
+                hv_fixed = run.hv(v)
+                md = model.maxDeltaSize + n * ncls
+                e1, e2 = G.dev(np.zeros(md)), G.dev(np.zeros(md))
+                e1[:n * ncls] = ws.errors
+                g_fixed, dx2 = G.dev(np.zeros(model.pSize)), G.dev(np.zeros(model.zSize))
+                api.cnnBackward(c, model, run.data, ws.dev, ws.z, g_fixed, dx2, e1, e2, 0, n)
+                g_fixed = g_fixed.cpu().numpy()
+            finally:
+                c.set_precision(0)
+            del dx2, e1, e2
+            assert 1e-12 < G.rel(g_fixed, g64) < 1e-3 and G.rel(hv_fixed, hv64) < 1e-3
+            acts64 = {}
+            for l in range(model.cLayers):
+                cl = model.convLayer[l]
+                if cl.outputOffset == cl.poolOffset and cl.poolOffset > 0:
+                    b = model.zOffsets[l + 1] + cl.activationOffset
+                    acts64[l] = ws.z[b:b + cl.convVolumn * n].cpu().numpy()
+        del run
+        torch.cuda.empty_cache()
+        c.set_precision(2)
+        try:
+            run3 = G.GpuRun(model, x, y, w, ncls)
+            hv3 = run3.hv(v)
+        finally:
+            c.set_precision(0)
+        results[pool] = (abs(run3.loss - loss64) / abs(loss64), G.rel(run3.gradient, g64), G.rel(hv3, hv64))
+        if pool == S.MAX_POOL:
+            flips = windows = 0
+            for l, a64 in acts64.items():
+                cl, pl = model.convLayer[l], model.poolLayer[l]
+                b = model.zOffsets[l + 1] + cl.activationOffset
+                a3 = run3.ws.z[b:b + cl.convVolumn * n].cpu().numpy()
+                cnt = cl.outChannels * n * pl.outHeight * pl.outWidth
+                m64, m3 = np.zeros(cnt, dtype=np.int32), np.zeros(cnt, dtype=np.int32)
+                O.lib().ora_max_pool_argmax(a64, n, cl.outChannels, cl.outHeight, cl.outWidth, pl.pSize, pl.stride,
+                                            pl.padding, m64)
+                O.lib().ora_max_pool_argmax(a3, n, cl.outChannels, cl.outHeight, cl.outWidth, pl.pSize, pl.stride,
+                                            pl.padding, m3)
+                flips += int(np.count_nonzero(m64 != m3))
+                windows += cnt
+            results["flips"] = (flips, windows)
+        del run3
+        torch.cuda.empty_cache()
+    la, ga, ha = results[S.AVG_POOL]
+    lm, gm, hm = results[S.MAX_POOL]
+    flips, windows = results["flips"]
+    print("3xTF32 at 512 images: avg pool %.1e %.1e %.1e; max pool %.1e %.1e %.1e; %d of %d windows flipped"
+          % (la, ga, ha, lm, gm, hm, flips, windows))
+    assert la < 1e-3 and ga < 1e-3 and ha < 1e-3          # (1)
+    assert lm < 1e-3 and gm < 1e-2 and hm < 1e-2          # (3) stated tolerance with own routing
+    assert 0 <= flips <= windows * 1e-4
