@@ -25,7 +25,7 @@ def _stale(obj, src):
     if not os.path.exists(obj):
         return True
     t = os.path.getmtime(obj)
-    deps = [src, os.path.join(CSRC, "common.h"), os.path.join(CSRC, "tma_util.cuh"),
+    deps = [src, os.path.join(CSRC, "common.h"), os.path.join(CSRC, "tma_util.cuh"), os.path.join(CSRC, "graphs.h"),
             os.path.join(os.path.dirname(HERE), "include", "fitre_b200.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 

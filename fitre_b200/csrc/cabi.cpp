@@ -131,6 +131,10 @@ int fitre_context_destroy(fitre_context *ctx) {
     if (ctx->graph_factors.exec) cudaGraphExecDestroy(ctx->graph_factors.exec);
     if (ctx->graph_factors_a.exec) cudaGraphExecDestroy(ctx->graph_factors_a.exec);
     if (ctx->graph_factors_g.exec) cudaGraphExecDestroy(ctx->graph_factors_g.exec);
+    for (auto &g : ctx->graph_hv)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+    for (auto &g : ctx->graph_grad)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
     if (ctx->phase_stream) cudaStreamDestroy(ctx->phase_stream);
     if (ctx->phase_fork) cudaEventDestroy(ctx->phase_fork);
     if (ctx->phase_done) cudaEventDestroy(ctx->phase_done);
@@ -341,22 +345,8 @@ int fitre_compute_cnn_gradient(fitre_context *ctx, const CNN_MODEL *m, const DEV
         double *errors = scratch->nextDevPtr;
         double *errors1 = errors + md;
         double *ws = errors1 + md;
-        cnn_forward(ctx, m, data, ws, z, probs, lossFuncErrors, curBatchSize, false);
-        const int classes = m->fcLayer[m->lLayers - 1].out;
-        vec_copy(ctx, (long)classes * curBatchSize, lossFuncErrors, errors);
-        // the gradient is a batch sum: each layer's slice is all-reduced as soon as the backward
-        // sweep has finished it, on the side communicator, under the rest of the sweep
-        ctx->reduce_slices = true;
-        ctx->reduced_from = m->pSize;
-        try {
-            cnn_backward(ctx, m, data, ws, z, gradient, dx, errors, errors1, curBatchSize);
-        } catch (...) {
-            ctx->reduce_slices = false;
-            throw;
-        }
-        ctx->reduce_slices = false;
-        comm_async_join(ctx);
-        vec_axpy(ctx, m->pSize, weightDecay, data->weights, gradient);
+        cnn_gradient(ctx, m, data, ws, z, dx, probs, lossFuncErrors, gradient, errors, errors1, curBatchSize,
+                     weightDecay);
         comm_allreduce_small(ctx, ctx->dscal, 1);
         FITRE_CUDA(cudaMemcpyAsync(ctx->pinned, ctx->dscal, sizeof(double), cudaMemcpyDeviceToHost,
                                    ctx->stream));

@@ -101,6 +101,13 @@ struct fitre_context {
         long long launches = 0;
     };
     CapturedGraph graph_invert, graph_natgrad, graph_factors, graph_factors_a, graph_factors_g;
+    // Launch sequences of the network passes (one Hessian-vector product, one gradient): a few
+    // recently used (model, buffer set) pairs each, so that a solver that alternates between two
+    // direction vectors replays both.  Only where launch latency is what the call costs: one
+    // rank, fp64 kernels, no host-buffer streaming, no event timing.
+    CapturedGraph graph_hv[4], graph_grad[2];
+    int graph_hv_next = 0, graph_grad_next = 0;
+    int use_pass_graphs = 1;
     // two-call form of the factor step: the A side runs on a stream of its own between the calls
     cudaStream_t phase_stream = nullptr;
     cudaEvent_t phase_fork = nullptr, phase_done = nullptr;
@@ -316,6 +323,11 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
 void cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, const double *z,
             const double *probs, const double *lossErrors, const double *dx, const double *vector,
             double *hv, int n, double *devPtr);
+// forward + backward + slice all-reduces + weight decay of computeCNNGradient (the loss sum stays in
+// ctx->dscal[0]); errors / errors1: the two error buffers, ws: scratch of the passes
+void cnn_gradient(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, double *ws, double *z,
+                  double *dx, double *probs, double *lossErrors, double *gradient, double *errors,
+                  double *errors1, int n, double weightDecay);
 long forward_scratch(const CNN_MODEL *m);
 long backward_scratch(const CNN_MODEL *m);
 long rop_forward_scratch(const CNN_MODEL *m);

@@ -8,6 +8,7 @@
 #include <algorithm>
 
 #include "common.h"
+#include "graphs.h"
 
 namespace fitre {
 namespace {
@@ -326,10 +327,94 @@ void cnn_rop_backward(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATAS
     }
 }
 
-// functions/cnn_hessian_vec.cu:18-122: devPtr = [rz (zSize) | rError (maxDelta) | scratch]
+namespace {
+// A pass may be replayed from a captured graph where launch latency is what it costs (small nets:
+// a LeNet Hessian-vector product is ~120 dependent kernels of a few microseconds each) and nothing
+// in it depends on the host: one rank (no collectives), fp64 kernels (the tensor-core modes grow
+// their staging buffer on demand), no host-buffer streaming hooks, no event timing.
+bool pass_graphable(const fitre_context *ctx) {
+    return ctx->use_graphs && ctx->use_pass_graphs && ctx->world == 1 && !ctx->prof_on &&
+           ctx->precision == FITRE_PRECISION_FP64 && !ctx->hv_host_dst && !ctx->fwd_wait_event;
+}
+long long model_key(const CNN_MODEL *m) {  // FNV-1a over the model description
+    const unsigned char *b = reinterpret_cast<const unsigned char *>(m);
+    unsigned long long h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(CNN_MODEL); ++i) h = (h ^ b[i]) * 1099511628211ull;
+    return (long long)h;
+}
+// the graph of `key` among the few kept, or the slot that is overwritten next
+fitre_context::CapturedGraph &pick_graph(fitre_context::CapturedGraph *slots, int count, int &next,
+                                         const std::vector<long long> &key) {
+    for (int i = 0; i < count; ++i)
+        if (slots[i].exec && slots[i].key == key) return slots[i];
+    fitre_context::CapturedGraph &g = slots[next];
+    next = (next + 1) % count;
+    return g;
+}
+void cnn_hv_direct(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, const double *z,
+                   const double *probs, const double *lossErrors, const double *dx, const double *vector,
+                   double *hv, int n, double *devPtr);
+}  // namespace
+
 void cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, const double *z,
             const double *probs, const double *lossErrors, const double *dx, const double *vector,
             double *hv, int n, double *devPtr) {
+    if (!pass_graphable(ctx)) {
+        cnn_hv_direct(ctx, m, data, z, probs, lossErrors, dx, vector, hv, n, devPtr);
+        return;
+    }
+    const std::vector<long long> key = {model_key(m), ptr_key(data->weights), ptr_key(data->currentBatch), ptr_key(z),
+                                        ptr_key(probs), ptr_key(lossErrors), ptr_key(dx), ptr_key(vector),
+                                        ptr_key(hv), ptr_key(devPtr), n, ctx->ref_softmax, ctx->use_tma};
+    run_graphed(ctx, pick_graph(ctx->graph_hv, 4, ctx->graph_hv_next, key), key,
+                [&] { cnn_hv_direct(ctx, m, data, z, probs, lossErrors, dx, vector, hv, n, devPtr); },
+                &ctx->use_pass_graphs);
+}
+
+namespace {
+void cnn_gradient_direct(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, double *ws,
+                         double *z, double *dx, double *probs, double *lossErrors, double *gradient,
+                         double *errors, double *errors1, int n, double weightDecay) {
+    cnn_forward(ctx, m, data, ws, z, probs, lossErrors, n, false);
+    const int classes = m->fcLayer[m->lLayers - 1].out;
+    vec_copy(ctx, (long)classes * n, lossErrors, errors);
+    // the gradient is a batch sum: each layer's slice is all-reduced as soon as the backward
+    // sweep has finished it, on the side communicator, under the rest of the sweep
+    ctx->reduce_slices = true;
+    ctx->reduced_from = m->pSize;
+    try {
+        cnn_backward(ctx, m, data, ws, z, gradient, dx, errors, errors1, n);
+    } catch (...) {
+        ctx->reduce_slices = false;
+        throw;
+    }
+    ctx->reduce_slices = false;
+    comm_async_join(ctx);
+    vec_axpy(ctx, m->pSize, weightDecay, data->weights, gradient);
+}
+}  // namespace
+
+void cnn_gradient(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, double *ws, double *z,
+                  double *dx, double *probs, double *lossErrors, double *gradient, double *errors,
+                  double *errors1, int n, double weightDecay) {
+    if (!pass_graphable(ctx)) {
+        cnn_gradient_direct(ctx, m, data, ws, z, dx, probs, lossErrors, gradient, errors, errors1, n, weightDecay);
+        return;
+    }
+    const std::vector<long long> key = {model_key(m), ptr_key(data->weights), ptr_key(data->currentBatch),
+                                        ptr_key(data->sampledTrainY), ptr_key(ws), ptr_key(z), ptr_key(dx),
+                                        ptr_key(probs), ptr_key(lossErrors), ptr_key(gradient), ptr_key(errors),
+                                        ptr_key(errors1), n, bits_key(weightDecay), ctx->ref_softmax, ctx->use_tma};
+    run_graphed(ctx, pick_graph(ctx->graph_grad, 2, ctx->graph_grad_next, key), key, [&] {
+        cnn_gradient_direct(ctx, m, data, ws, z, dx, probs, lossErrors, gradient, errors, errors1, n, weightDecay);
+    }, &ctx->use_pass_graphs);
+}
+
+namespace {
+// functions/cnn_hessian_vec.cu:18-122: devPtr = [rz (zSize) | rError (maxDelta) | scratch]
+void cnn_hv_direct(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, const double *z,
+                   const double *probs, const double *lossErrors, const double *dx, const double *vector,
+                   double *hv, int n, double *devPtr) {
     double *rz = devPtr;
     double *rError = rz + align32(m->zSize);
     double *scratch = rError + align32(max_delta_elems(m));
@@ -350,5 +435,6 @@ void cnn_hv(fitre_context *ctx, const CNN_MODEL *m, const DEVICE_DATASET *data, 
     ctx->reduce_slices = false;
     comm_async_join(ctx);
 }
+}  // namespace
 
 }  // namespace fitre
