@@ -149,6 +149,26 @@ def test_vgg11_bn_512_gradient_hv_and_state():
     assert ran["conv_tma_kernel"] >= 24 and ran["wgrad_tma_kernel"] >= 14, ran
 
 
+def _where(a, b, info, model):
+    """Where two sets of A factors differ: per layer the count of entries off by more than 1e-9
+    of the block's largest value, and the row / column ranges they span."""
+    out = []
+    for l in range(model.cLayers + model.lLayers):
+        if l < model.cLayers:
+            c = model.convLayer[l]
+            K = c.inChannels * c.kSize ** 2
+        else:
+            K = model.fcLayer[l - model.cLayers].in_
+        a0 = info.OmegaZOffsets[l]
+        x, y = a[a0:a0 + K * K].reshape(K, K), b[a0:a0 + K * K].reshape(K, K)
+        bad = np.argwhere(np.abs(x - y) > 1e-9 * np.max(np.abs(y)))
+        if len(bad):
+            out.append("layer %d (K=%d): %d entries, columns %d..%d rows %d..%d, max |diff| %.3e of %.3e" % (
+                l, K, len(bad), bad[:, 0].min(), bad[:, 0].max(), bad[:, 1].min(), bad[:, 1].max(),
+                np.max(np.abs(x - y)), np.max(np.abs(y))))
+    return "; ".join(out) or "no entry differs by more than 1e-9"
+
+
 def test_vgg11_bn_256_kfac_step():
     """KFAC step at the per-GPU shape of the 2048-image configuration, lambda = 1e-3, gamma = 0:
     labels sampled from the model's distribution (injected uniforms), the second backward pass,
@@ -202,6 +222,7 @@ def test_vgg11_bn_256_kfac_step():
         ng = G.dev(np.zeros(model.pSize))
         api.computeNaturalGradient(run.c, model, info, Ai, Gi, ws.gradient, ng, iscr)
         ng_chol = ng.cpu().numpy()
+        A_first = A.cpu().numpy()
     finally:
         run.c.set_kfac_solver(0)
     assert run.c.kernel_launches("patch_syrk_tma_kernel") - before >= 7
@@ -209,9 +230,14 @@ def test_vgg11_bn_256_kfac_step():
     api.computeNaturalGradient(run.c, model, info, Ai, Gi, ws.gradient, ng, iscr)
     ng_inv = ng.cpu().numpy()
     A_h, G_h = A.cpu().numpy(), Gm.cpu().numpy()
+    z_h = ws.z.cpu().numpy()
     del A, Ai, Gm, Gi, iscr
     torch.cuda.empty_cache()
 
+    # the factor products are the same kernels under either solver: same bits from both calls,
+    # and the activations they read are still the forward pass's
+    assert G.rel(z_h, st.z) < TOL
+    assert np.array_equal(A_first, A_h), _where(A_first, A_h, info, model)
     nl = model.cLayers + model.lLayers
     worst = 0.0
     for l in range(nl):
@@ -224,7 +250,7 @@ def test_vgg11_bn_256_kfac_step():
         a0, g0 = info.OmegaZOffsets[l], info.LambdaGOffsets[l]
         assert (a0, g0) == (info_o.OmegaZOffsets[l], info_o.LambdaGOffsets[l])
         # factors: CUDA against the oracle
-        assert G.relmax(A_h[a0:a0 + K * K], A_o[a0:a0 + K * K]) < TOL, l
+        assert G.relmax(A_h[a0:a0 + K * K], A_o[a0:a0 + K * K]) < TOL, (l, _where(A_h, A_o, info, model))
         assert G.relmax(G_h[g0:g0 + co * co], G_o[g0:g0 + co * co]) < TOL, l
         # natural gradient of the layer from the oracle's factors by LAPACK: G^-1 [dW] A^-1
         Al = A_o[a0:a0 + K * K].reshape(K, K) + lam * np.eye(K)
