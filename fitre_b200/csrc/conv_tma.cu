@@ -161,6 +161,7 @@ conv_tma_kernel(const __grid_constant__ TmaConvArgs p) {
                         dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
             }
         }
+        release_stage_reads();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(bars + 4 + s));
     }
@@ -330,6 +331,7 @@ wgrad_tma_kernel(const __grid_constant__ TmaWgradArgs p) {
                         dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
             }
         }
+        release_stage_reads();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(bars + 4 + s));
     }
@@ -475,6 +477,7 @@ patch_syrk_tma_kernel(const __grid_constant__ TmaSyrkArgs p) {
                         dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
             }
         }
+        release_stage_reads();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(bars + 4 + s));
     }

@@ -60,6 +60,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (clock64() - t0 > (1LL << 31)) return false;
     }
 }
+// Every lane calls this after its last plain load from a stage and before the warp's arrival on
+// the stage's "empty" barrier.  The refill is a TMA write, which goes through the asynchronous
+// proxy; an mbarrier arrival alone orders only generic-proxy accesses, and without this fence a
+// warp's last loads were (rarely, when other kernels share the SM) served after the refill had
+// begun.  The fence makes the loads complete before anything the asynchronous proxy does later.
+__device__ __forceinline__ void release_stage_reads() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
                                             int x, int y, int z, int w) {
     asm volatile(

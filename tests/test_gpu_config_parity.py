@@ -274,6 +274,43 @@ def test_vgg11_bn_256_kfac_step():
     assert worst < 1.0
 
 
+def test_vgg11_bn_256_factor_bits_repeatable():
+    """The factor products run while the factorisations of earlier layers occupy the same SMs from
+    side streams.  200 repetitions of the fused call (explicit inverses, the heaviest overlap)
+    must give the same bits every time: a stage of the TMA ring that is refilled while a warp's
+    last loads from it are still outstanding shows up here as a rank-few change inside one
+    128 x 64 tile of an A factor (seen about once in 70 calls before the ring's consumers fenced
+    their reads against the asynchronous proxy)."""
+    import torch
+    import gpu_util as G
+    from fitre_b200 import api, _lib
+    L = _lib.load()
+    n = 256
+    model = nets.vgg11(n)
+    O.finalize(model)
+    x, y, w, v, ncls = G.synth(model, n, seed=4234)
+    run = G.GpuRun(model, x, y, w, ncls)
+    ws = run.ws
+    info = api.computeKFACStorageIndices(model)
+    info.regLambda, info.dampGamma = 1e-3, 0.0
+    dx2 = ws.dx  # any fixed errors tensor serves: the test is about repeatability
+    iscr = G.dev(np.zeros(L.fitre_kfac_factors_and_inverses_mem_required(C.byref(model))))
+    A, Gm = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+    Ai, Gi = G.dev(np.zeros(info.OmegaZSize)), G.dev(np.zeros(info.LambdaGSize))
+    run.c.set_kfac_solver(0)
+    first = None
+    for rep in range(200):
+        api.computeFactorsAndInverses(run.c, model, run.data, ws.z, dx2, n, A, Ai, Gm, Gi, info, iscr)
+        torch.cuda.synchronize()
+        if first is None:
+            first = (A.clone(), Gm.clone(), Ai.clone(), Gi.clone())
+            continue
+        same = [torch.equal(a, b) for a, b in zip(first, (A, Gm, Ai, Gi))]
+        assert all(same), (rep, same, _where(A.cpu().numpy(), first[0].cpu().numpy(), info, model))
+    del A, Ai, Gm, Gi, iscr, first
+    torch.cuda.empty_cache()
+
+
 def test_vgg11_bn_512_tf32x3_tolerance_and_argmax_flips():
     """The error-compensated tensor-core mode (3 x TF32 on tcgen05) at the benchmark size, against
     the fp64 result of the same library (which the tests above pin to the oracle).
