@@ -281,10 +281,14 @@ int fitre_get_kfac_solver(const fitre_context *ctx); /* the current setting; -1 
 enum { FITRE_KFAC_REPLICATED = 0, FITRE_KFAC_LAYER_OWNED = 1 };
 int fitre_set_kfac_distribution(fitre_context *ctx, int mode);
 
-/* 1 (default) = fitre_kfac_invert_factors and fitre_compute_natural_gradient, whose launch
- * sequences (a thousand small dependent kernels) are fixed by the model and the buffers, capture
- * that sequence into a CUDA graph on first use and replay it while pointers, sizes, damping and
- * solver stay the same; 0 = launch kernel by kernel.  Same kernels and results either way.  No
+/* 1 (default) = calls whose launch sequence is fixed by the model and the buffers capture it
+ * into a CUDA graph on first use and replay it while the model description, pointers, sizes,
+ * damping and solver stay the same; 0 = launch kernel by kernel.  Covered: the KFAC factor,
+ * factorisation and natural-gradient calls (a thousand small dependent kernels), and on one GPU
+ * fitre_compute_cnn_gradient and fitre_cnn_hv (the last two gradient and the last four Hv
+ * argument sets are kept, so a CG loop alternating between two direction buffers replays).
+ * With a communicator the gradient and Hv passes launch directly, because their slices are
+ * all-reduced from a second stream under the sweep.  Same kernels and results either way.  No
  * counterpart in the reference. */
 int fitre_set_graphs(fitre_context *ctx, int on);
 
