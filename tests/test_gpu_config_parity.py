@@ -270,7 +270,7 @@ def test_vgg11_bn_256_kfac_step():
             e = G.rel(blk(got), ref)
             worst = max(worst, e / tol)
             assert e < tol, (l, e, kap)
-    print("KFAC step at 256 images: worst natural-gradient error / tolerance = %.3f" % worst)
+    print("KFAC step at 256 images: worst natural-gradient error / tolerance = %.2e" % worst)
     assert worst < 1.0
 
 
