@@ -41,8 +41,13 @@ constexpr int FP_LDA = FP_BM + 4;  // As[k][m]: (lane%4)*LDA + lane/4 hits 16 di
 constexpr int FP_LDB = FP_BK + 4;  // Bs[n][k]
 constexpr int FP_SMEM = 2 * (FP_BK * FP_LDA + FP_BN * FP_LDB) * (int)sizeof(double);
 
-template <int KS>  // KS = compile-time kernel size (0 = runtime)
+// KS = compile-time kernel size (0 = runtime); NT = 8-column MMA tiles per warp: 4 gives the
+// 128 x 64 block tile, 1 a 128 x 16 tile for layers with at most 16 output channels (LeNet, the
+// data gradient into a 3- or 6-channel input), which would otherwise spend 3/4 or more of their
+// tensor work on columns that do not exist.
+template <int KS, int NT>
 __global__ void __launch_bounds__(FP_THREADS, 2) conv_fprop_kernel(ConvArgs p) {
+    constexpr int BN = 16 * NT;
     extern __shared__ double smem[];
     double *As = smem;                           // [2][BK][LDA]
     double *Bs = smem + 2 * FP_BK * FP_LDA;      // [2][BN][LDB]
@@ -50,7 +55,7 @@ __global__ void __launch_bounds__(FP_THREADS, 2) conv_fprop_kernel(ConvArgs p) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int warp_m = warp & 3, warp_n = warp >> 2;
     const long m0 = (long)blockIdx.x * FP_BM;
-    const int c0 = blockIdx.y * FP_BN;
+    const int c0 = blockIdx.y * BN;
     const int k = KS ? KS : p.k, kk2 = k * k;
 
     // this thread gathers rows mm of the A tile for k-slots a_k0, a_k0 + 2, ...
@@ -70,7 +75,8 @@ __global__ void __launch_bounds__(FP_THREADS, 2) conv_fprop_kernel(ConvArgs p) {
     const long chan_stride = (long)p.N * p.W * p.H;
     // B tile: thread loads 4 consecutive k of column b_nn
     const int b_nn = tid >> 2, b_k0 = (tid & 3) * 4;
-    const bool b_cvalid = (c0 + b_nn) < p.Cout;
+    const bool b_loader = b_nn < BN;
+    const bool b_cvalid = b_loader && (c0 + b_nn) < p.Cout;
 
     const int nk = (p.K + FP_BK - 1) / FP_BK;
     const int iters = nk * p.nseg;
@@ -102,18 +108,20 @@ __global__ void __launch_bounds__(FP_THREADS, 2) conv_fprop_kernel(ConvArgs p) {
     };
     auto sstore = [&](int buf) {
         double *a = As + buf * FP_BK * FP_LDA;
-        double *b = Bs + buf * FP_BN * FP_LDB;
+        double *b = Bs + buf * BN * FP_LDB;
 #pragma unroll
         for (int r = 0; r < 8; ++r) a[(a_k0 + 2 * r) * FP_LDA + a_mm] = ra[r];
+        if (b_loader) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) b[b_nn * FP_LDB + b_k0 + e] = rb[e];
+            for (int e = 0; e < 4; ++e) b[b_nn * FP_LDB + b_k0 + e] = rb[e];
+        }
     };
 
-    double acc[4][4][2];
+    double acc[4][NT][2];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+        for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
     gload(0);
     sstore(0);
@@ -123,18 +131,18 @@ __global__ void __launch_bounds__(FP_THREADS, 2) conv_fprop_kernel(ConvArgs p) {
         const int buf = it & 1;
         if (it + 1 < iters) gload(it + 1);
         const double *a = As + buf * FP_BK * FP_LDA + warp_m * 32 + lr;
-        const double *b = Bs + buf * FP_BN * FP_LDB + (warp_n * 32 + lr) * FP_LDB;
+        const double *b = Bs + buf * BN * FP_LDB + (warp_n * 8 * NT + lr) * FP_LDB;
 #pragma unroll
         for (int k4 = 0; k4 < FP_BK / 4; ++k4) {
-            double fa[4], fb[4];
+            double fa[4], fb[NT];
 #pragma unroll
             for (int mi = 0; mi < 4; ++mi) fa[mi] = a[(k4 * 4 + lc) * FP_LDA + mi * 8];
 #pragma unroll
-            for (int ni = 0; ni < 4; ++ni) fb[ni] = b[ni * 8 * FP_LDB + k4 * 4 + lc];
+            for (int ni = 0; ni < NT; ++ni) fb[ni] = b[ni * 8 * FP_LDB + k4 * 4 + lc];
 #pragma unroll
             for (int mi = 0; mi < 4; ++mi)
 #pragma unroll
-                for (int ni = 0; ni < 4; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+                for (int ni = 0; ni < NT; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
         }
         if (it + 1 < iters) {
             sstore(buf ^ 1);
@@ -143,10 +151,10 @@ __global__ void __launch_bounds__(FP_THREADS, 2) conv_fprop_kernel(ConvArgs p) {
     }
 
 #pragma unroll
-    for (int ni = 0; ni < 4; ++ni)
+    for (int ni = 0; ni < NT; ++ni)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const int col = c0 + warp_n * 32 + ni * 8 + 2 * lc + e;
+            const int col = c0 + warp_n * 8 * NT + ni * 8 + 2 * lc + e;
             if (col >= p.Cout) continue;
             const double bv = p.bias ? p.bias[col] : 0.0;
 #pragma unroll
@@ -190,14 +198,18 @@ constexpr int WG_BQ = 64, WG_BN = 64, WG_BK = 16, WG_THREADS = 256;
 constexpr int WG_LD = WG_BK + 4;  // Sa[q][m], Sb[c][m]: (lane/4)*LD + lane%4 is conflict-free
 constexpr int WG_SMEM = 2 * (WG_BQ + WG_BN) * WG_LD * (int)sizeof(double);
 
-template <int KS>
+// NARROW (layers with at most 16 output channels): the block tile is 64 (q) x 16 (c), warps 4 x 2
+// with 16 x 8 tiles, instead of 64 x 64 with warps 2 x 4 and 32 x 16 tiles; the gather is the same
+// (columns past Cout are zeros that nobody multiplies any more).
+template <int KS, bool NARROW>
 __global__ void __launch_bounds__(WG_THREADS, 2) conv_wgrad_kernel(WgradArgs p) {
+    constexpr int MI = NARROW ? 2 : 4, NI = NARROW ? 1 : 2;
     extern __shared__ double smem[];
     double *Sa = smem;                          // [2][BQ][LD]
     double *Sb = smem + 2 * WG_BQ * WG_LD;      // [2][BN][LD]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int warp_q = warp & 1, warp_n = warp >> 1;  // warp tile 32 (q) x 16 (c)
-    const int q0 = blockIdx.x * WG_BQ, c0 = blockIdx.y * WG_BN;
+    const int warp_q = NARROW ? (warp & 3) : (warp & 1), warp_n = NARROW ? (warp >> 2) : (warp >> 1);
+    const int q0 = blockIdx.x * WG_BQ, c0 = blockIdx.y * (NARROW ? 16 : WG_BN);
     const long mbeg = (long)blockIdx.z * p.chunk;
     const long mend = min(p.M, mbeg + p.chunk);
     const int k = KS ? KS : p.k, kk2 = k * k;
@@ -264,11 +276,11 @@ __global__ void __launch_bounds__(WG_THREADS, 2) conv_wgrad_kernel(WgradArgs p) 
         }
     };
 
-    double acc[4][2][2];
+    double acc[MI][NI][2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < MI; ++i)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+        for (int j = 0; j < NI; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
     const int lr = lane >> 2, lc = lane & 3;
     if (iters > 0) {
@@ -279,19 +291,19 @@ __global__ void __launch_bounds__(WG_THREADS, 2) conv_wgrad_kernel(WgradArgs p) 
     for (int it = 0; it < iters; ++it) {
         const int buf = it & 1;
         if (it + 1 < iters) gload(it + 1);
-        const double *a = Sa + buf * WG_BQ * WG_LD + (warp_q * 32 + lr) * WG_LD + lc;
-        const double *b = Sb + buf * WG_BN * WG_LD + (warp_n * 16 + lr) * WG_LD + lc;
+        const double *a = Sa + buf * WG_BQ * WG_LD + (warp_q * 8 * MI + lr) * WG_LD + lc;
+        const double *b = Sb + buf * WG_BN * WG_LD + (warp_n * 8 * NI + lr) * WG_LD + lc;
 #pragma unroll
         for (int k4 = 0; k4 < WG_BK / 4; ++k4) {
-            double fa[4], fb[2];
+            double fa[MI], fb[NI];
 #pragma unroll
-            for (int mi = 0; mi < 4; ++mi) fa[mi] = a[mi * 8 * WG_LD + k4 * 4];
+            for (int mi = 0; mi < MI; ++mi) fa[mi] = a[mi * 8 * WG_LD + k4 * 4];
 #pragma unroll
-            for (int ni = 0; ni < 2; ++ni) fb[ni] = b[ni * 8 * WG_LD + k4 * 4];
+            for (int ni = 0; ni < NI; ++ni) fb[ni] = b[ni * 8 * WG_LD + k4 * 4];
 #pragma unroll
-            for (int mi = 0; mi < 4; ++mi)
+            for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
-                for (int ni = 0; ni < 2; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
+                for (int ni = 0; ni < NI; ++ni) dmma884(acc[mi][ni][0], acc[mi][ni][1], fa[mi], fb[ni]);
         }
         if (it + 1 < iters) {
             sstore(buf ^ 1);
@@ -300,14 +312,14 @@ __global__ void __launch_bounds__(WG_THREADS, 2) conv_wgrad_kernel(WgradArgs p) 
     }
     double *out = p.out + (long)blockIdx.z * p.K * p.Cout;
 #pragma unroll
-    for (int ni = 0; ni < 2; ++ni)
+    for (int ni = 0; ni < NI; ++ni)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const int col = c0 + warp_n * 16 + ni * 8 + 2 * lc + e;
+            const int col = c0 + warp_n * 8 * NI + ni * 8 + 2 * lc + e;
             if (col >= p.Cout) continue;
 #pragma unroll
-            for (int mi = 0; mi < 4; ++mi) {
-                const int row = q0 + warp_q * 32 + mi * 8 + lr;
+            for (int mi = 0; mi < MI; ++mi) {
+                const int row = q0 + warp_q * 8 * MI + mi * 8 + lr;
                 if (row < p.K) out[(long)col * p.K + row] = acc[mi][ni][e];
             }
         }
@@ -838,14 +850,19 @@ void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double 
     a.Wo = W + 2 * pad - k + 1;
     a.K = Cin * k * k;
     a.M = (long)N * a.Ho * a.Wo;
-    dim3 grid((unsigned)((a.M + FP_BM - 1) / FP_BM), (unsigned)((Cout + FP_BN - 1) / FP_BN));
+    const bool narrow = Cout <= 16;  // 128 x 16 block tile
+    const int bn = narrow ? 16 : FP_BN;
+    dim3 grid((unsigned)((a.M + FP_BM - 1) / FP_BM), (unsigned)((Cout + bn - 1) / bn));
     ProfScope prof(ctx, PROF_CONV_IGEMM, 2.0 * (double)a.M * a.K * Cout * nseg);
     if (k == 3) {
-        conv_fprop_kernel<3><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_fprop_kernel<3, 1><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        else conv_fprop_kernel<3, 4><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
     } else if (k == 5) {
-        conv_fprop_kernel<5><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_fprop_kernel<5, 1><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        else conv_fprop_kernel<5, 4><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
     } else {
-        conv_fprop_kernel<0><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_fprop_kernel<0, 1><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        else conv_fprop_kernel<0, 4><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
     }
     check_launch(ctx, "conv_fprop_kernel");
 }
@@ -904,12 +921,16 @@ void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, i
     a.out = S > 1 ? partials : dw;
     dim3 grid(tq, tn, S);
     ProfScope prof(ctx, PROF_CONV_WGRAD, 2.0 * (double)a.M * a.K * Cout * nseg);
+    const bool narrow = Cout <= 16;  // one 16-column tile (tn is 1 either way)
     if (k == 3) {
-        conv_wgrad_kernel<3><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_wgrad_kernel<3, true><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+        else conv_wgrad_kernel<3, false><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
     } else if (k == 5) {
-        conv_wgrad_kernel<5><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_wgrad_kernel<5, true><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+        else conv_wgrad_kernel<5, false><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
     } else {
-        conv_wgrad_kernel<0><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_wgrad_kernel<0, true><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
+        else conv_wgrad_kernel<0, false><<<grid, WG_THREADS, WG_SMEM, ctx->stream>>>(a);
     }
     check_launch(ctx, "conv_wgrad_kernel");
     if (S > 1) {
@@ -1036,12 +1057,18 @@ void gemm_init_attributes() {
     conv_tf32_init_attributes();
     conv_i8_init_attributes();
     kfac_init_attributes();
-    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
-    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
-    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
-    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
-    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
-    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<0, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<3, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<5, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_fprop_kernel<5, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<5, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(conv_wgrad_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
