@@ -347,46 +347,59 @@ constexpr int DG_BM = 64, DG_BN = 64, DG_BK = 16, DG_THREADS = 256;
 //   GEMM_K_LE_ROW: terms with k <= row only     (A lower triangular:   C = L * B)
 //   GEMM_LOWER_C:  tiles strictly above the diagonal of C are skipped (C symmetric, lower wanted)
 // The skipped terms are exact zeros, so results equal the plain product.
-__device__ __forceinline__ bool gemm_k_range(int kmode, int m0, int n0, int bm, int bn, int k, int &kt0, int &nk) {
+__device__ __forceinline__ bool gemm_k_range(int kmode, int m0, int n0, int bm, int bn, int k, int &kt0, int &nk,
+                                             int bk = DG_BK) {
     kt0 = 0;
-    nk = (k + DG_BK - 1) / DG_BK;
-    if (kmode == GEMM_K_LE_COL) nk = min(nk, (min(n0 + bn, k) + DG_BK - 1) / DG_BK);
-    else if (kmode == GEMM_K_GE_COL) kt0 = n0 / DG_BK;
-    else if (kmode == GEMM_K_LE_ROW) nk = min(nk, (min(m0 + bm, k) + DG_BK - 1) / DG_BK);
+    nk = (k + bk - 1) / bk;
+    if (kmode == GEMM_K_LE_COL) nk = min(nk, (min(n0 + bn, k) + bk - 1) / bk);
+    else if (kmode == GEMM_K_GE_COL) kt0 = n0 / bk;
+    else if (kmode == GEMM_K_LE_ROW) nk = min(nk, (min(m0 + bm, k) + bk - 1) / bk);
     else if (kmode == GEMM_LOWER_C && n0 >= m0 + bm) return false;
     return true;
 }
 constexpr int DG_LDA = DG_BM + 4, DG_LDB = DG_BN + 4;  // As[k][m], Bs[k][n]
+constexpr int DG_SMEM = 2 * 16 * (DG_LDA + DG_LDB) * (int)sizeof(double);
+constexpr int DG_SMEM_DEEP = 2 * 64 * (DG_LDA + DG_LDB) * (int)sizeof(double);
 
-template <bool TA, bool TB>
+// BK = depth of one k step.  16 for grids that fill the GPU (several resident blocks per SM hide
+// the operand fetch); 64 for grids of at most one block per SM with a long k loop (FC layers at
+// small batch, the couplings of the factorisation recursion), where a block is alone on its SM
+// and every step costs one round trip to L2 or HBM: four times fewer, four times longer steps,
+// each fetch hidden behind a full step of tensor work.  Terms are added in the same order
+// (groups of four k, ascending), so both depths return the same bits.
+template <bool TA, bool TB, int BK>
 __global__ void __launch_bounds__(DG_THREADS) dgemm_kernel(int m, int n, int k, double alpha,
                                                           const double *A, int lda,
                                                           const double *B, int ldb, double beta,
                                                           double *C, int ldc, int kmode) {
-    __shared__ double As[2][DG_BK * DG_LDA];
-    __shared__ double Bs[2][DG_BK * DG_LDB];
+    extern __shared__ double dg_smem[];
+    double *As = dg_smem;                        // [2][BK * DG_LDA], As[k][m]
+    double *Bs = dg_smem + 2 * BK * DG_LDA;      // [2][BK * DG_LDB], Bs[k][n]
+    constexpr int PER = BK / 4;                  // elements of each operand tile per thread
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int warp_m = warp & 1, warp_n = warp >> 1;  // warp tile 32 x 16
     const int m0 = blockIdx.x * DG_BM, n0 = blockIdx.y * DG_BN;
     int kt0, nk;
-    if (!gemm_k_range(kmode, m0, n0, DG_BM, DG_BN, k, kt0, nk)) return;
-    // loader roles: 1024 elements per operand tile, 4 per thread.  The fast thread index
+    if (!gemm_k_range(kmode, m0, n0, DG_BM, DG_BN, k, kt0, nk, BK)) return;
+    // loader roles: 64 * BK elements per operand tile, BK / 4 per thread.  The fast thread index
     // follows the contiguous direction of the operand in memory.
-    double ra[4], rb[4];
+    double ra[PER], rb[PER];
+    auto role = [&](bool along_k, int r, int &fast64, int &kk) {
+        if (!along_k) { fast64 = tid & 63; kk = (tid >> 6) + 4 * r; }
+        else          { kk = tid % BK; fast64 = tid / BK + (DG_THREADS / BK) * r; }
+    };
     auto gload = [&](int kt) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < PER; ++r) {
             int mm, kk;
-            if (!TA) { mm = tid & 63; kk = (tid >> 6) + 4 * r; }
-            else     { kk = tid & 15; mm = (tid >> 4) + 16 * r; }
-            const int gi = m0 + mm, gp = kt * DG_BK + kk;
+            role(TA, r, mm, kk);
+            const int gi = m0 + mm, gp = kt * BK + kk;
             double v = 0.0;
             if (gi < m && gp < k) v = TA ? A[gp + (long)gi * lda] : A[gi + (long)gp * lda];
             ra[r] = v;
             int nn, kb;
-            if (!TB) { kb = tid & 15; nn = (tid >> 4) + 16 * r; }
-            else     { nn = tid & 63; kb = (tid >> 6) + 4 * r; }
-            const int gj = n0 + nn, gq = kt * DG_BK + kb;
+            role(!TB, r, nn, kb);
+            const int gj = n0 + nn, gq = kt * BK + kb;
             double u = 0.0;
             if (gj < n && gq < k) u = TB ? B[gj + (long)gq * ldb] : B[gq + (long)gj * ldb];
             rb[r] = u;
@@ -394,15 +407,13 @@ __global__ void __launch_bounds__(DG_THREADS) dgemm_kernel(int m, int n, int k, 
     };
     auto sstore = [&](int buf) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < PER; ++r) {
             int mm, kk;
-            if (!TA) { mm = tid & 63; kk = (tid >> 6) + 4 * r; }
-            else     { kk = tid & 15; mm = (tid >> 4) + 16 * r; }
-            As[buf][kk * DG_LDA + mm] = ra[r];
+            role(TA, r, mm, kk);
+            As[buf * BK * DG_LDA + kk * DG_LDA + mm] = ra[r];
             int nn, kb;
-            if (!TB) { kb = tid & 15; nn = (tid >> 4) + 16 * r; }
-            else     { nn = tid & 63; kb = (tid >> 6) + 4 * r; }
-            Bs[buf][kb * DG_LDB + nn] = rb[r];
+            role(!TB, r, nn, kb);
+            Bs[buf * BK * DG_LDB + kb * DG_LDB + nn] = rb[r];
         }
     };
     double acc[4][2][2];
@@ -419,10 +430,10 @@ __global__ void __launch_bounds__(DG_THREADS) dgemm_kernel(int m, int n, int k, 
     for (int kt = kt0; kt < nk; ++kt) {
         const int buf = kt & 1;
         if (kt + 1 < nk) gload(kt + 1);
-        const double *a = As[buf] + warp_m * 32 + lr;
-        const double *b = Bs[buf] + warp_n * 16 + lr;
+        const double *a = As + buf * BK * DG_LDA + warp_m * 32 + lr;
+        const double *b = Bs + buf * BK * DG_LDB + warp_n * 16 + lr;
 #pragma unroll
-        for (int k4 = 0; k4 < DG_BK / 4; ++k4) {
+        for (int k4 = 0; k4 < BK / 4; ++k4) {
             double fa[4], fb[2];
 #pragma unroll
             for (int mi = 0; mi < 4; ++mi) fa[mi] = a[(k4 * 4 + lc) * DG_LDA + mi * 8];
@@ -965,14 +976,26 @@ void dgemm_structured(fitre_context *ctx, bool tA, bool tB, int m, int n, int k,
         return;
     }
     dim3 grid((m + DG_BM - 1) / DG_BM, (n + DG_BN - 1) / DG_BN);
-    if (!tA && !tB)
-        dgemm_kernel<false, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
-    else if (!tA && tB)
-        dgemm_kernel<false, true><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
-    else if (tA && !tB)
-        dgemm_kernel<true, false><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
-    else
-        dgemm_kernel<true, true><<<grid, DG_THREADS, 0, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kmode);
+    // at most one block per SM and a long k loop: the deep-step form (see dgemm_kernel)
+    // -- but not on the side streams, where several factorisations share the SMs and a block that
+    // takes 139 KB of shared memory keeps the others' blocks out
+    bool side = false;
+    for (cudaStream_t st : ctx->inv_streams) side = side || (st && st == ctx->stream);
+    const bool deep = !side && (long)grid.x * grid.y <= 148 && k >= 128;
+#define FITRE_DGEMM_LAUNCH(TA_, TB_)                                                                              \
+    do {                                                                                                          \
+        if (deep)                                                                                                 \
+            dgemm_kernel<TA_, TB_, 64><<<grid, DG_THREADS, DG_SMEM_DEEP, ctx->stream>>>(m, n, k, alpha, A, lda, B, \
+                                                                                        ldb, beta, C, ldc, kmode); \
+        else                                                                                                      \
+            dgemm_kernel<TA_, TB_, 16><<<grid, DG_THREADS, DG_SMEM, ctx->stream>>>(m, n, k, alpha, A, lda, B, ldb, \
+                                                                                   beta, C, ldc, kmode);          \
+    } while (0)
+    if (!tA && !tB) FITRE_DGEMM_LAUNCH(false, false);
+    else if (!tA && tB) FITRE_DGEMM_LAUNCH(false, true);
+    else if (tA && !tB) FITRE_DGEMM_LAUNCH(true, false);
+    else FITRE_DGEMM_LAUNCH(true, true);
+#undef FITRE_DGEMM_LAUNCH
     check_launch(ctx, "dgemm_kernel");
 }
 
@@ -1073,6 +1096,10 @@ void gemm_init_attributes() {
     FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(patch_syrk_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(syrk_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM));
+    FITRE_CUDA(cudaFuncSetAttribute(dgemm_kernel<false, false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_DEEP));
+    FITRE_CUDA(cudaFuncSetAttribute(dgemm_kernel<false, true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_DEEP));
+    FITRE_CUDA(cudaFuncSetAttribute(dgemm_kernel<true, false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_DEEP));
+    FITRE_CUDA(cudaFuncSetAttribute(dgemm_kernel<true, true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_DEEP));
     FITRE_CUDA(cudaFuncSetAttribute(dgemm_large_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DL_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(dgemm_large_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DL_SMEM));
     FITRE_CUDA(cudaFuncSetAttribute(dgemm_large_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DL_SMEM));

@@ -285,13 +285,23 @@ __device__ __forceinline__ double pool_gather(const double *dpool_plane, const d
         const int k = h / g.pk, l = w / g.pk;
         return (k < g.Hp && l < g.Wp) ? dpool_plane[l * g.Hp + k] / (double)(g.pk * g.pk) : 0.0;
     }
-    // windows k with k*ps - pp <= h < k*ps - pp + pk
-    int kmin = (h + g.pp - g.pk + g.ps) / g.ps;  // ceil((h + pp - pk + 1) / ps) for non-negative args
-    if (h + g.pp - g.pk + 1 <= 0) kmin = 0;
-    const int kmax = min((h + g.pp) / g.ps, g.Hp - 1);
-    int lmin = (w + g.pp - g.pk + g.ps) / g.ps;
-    if (w + g.pp - g.pk + 1 <= 0) lmin = 0;
-    const int lmax = min((w + g.pp) / g.ps, g.Wp - 1);
+    // windows k with k*ps - pp <= h < k*ps - pp + pk: kmin = ceil((h + pp - pk + 1) / ps) (0 when the
+    // numerator is not positive), kmax = floor((h + pp) / ps); stride 2, the usual case, by shifts
+    const int th = h + g.pp - g.pk + 1, tw = w + g.pp - g.pk + 1;
+    int kmin, kmax, lmin, lmax;
+    if (g.ps == 2) {
+        kmin = th <= 0 ? 0 : (th + 1) >> 1;
+        lmin = tw <= 0 ? 0 : (tw + 1) >> 1;
+        kmax = (h + g.pp) >> 1;
+        lmax = (w + g.pp) >> 1;
+    } else {
+        kmin = th <= 0 ? 0 : (th + g.ps - 1) / g.ps;
+        lmin = tw <= 0 ? 0 : (tw + g.ps - 1) / g.ps;
+        kmax = (h + g.pp) / g.ps;
+        lmax = (w + g.pp) / g.ps;
+    }
+    kmax = min(kmax, g.Hp - 1);
+    lmax = min(lmax, g.Wp - 1);
     const int me = w * g.H + h;
     double s = 0.0;
     if (map_plane) {
@@ -343,11 +353,22 @@ struct PlaneChan {   // per-channel bases shared by the pool/activation functors
     long cbase;      // c * rows
     long pbase;      // start of channel c in the pooled tensor
     unsigned hw, H, pw;
+    int sh_hw, sh_H;  // log2 of hw / H when they are powers of two (the usual planes), else -1
 };
+// (image, column, row) of element r of a channel block; shifts when the plane sizes allow
+__device__ __forceinline__ void plane_coords(const PlaneChan &p, unsigned r, unsigned &n, unsigned &w,
+                                             unsigned &h) {
+    n = p.sh_hw >= 0 ? r >> p.sh_hw : r / p.hw;
+    const unsigned rem = r - n * p.hw;
+    w = p.sh_H >= 0 ? rem >> p.sh_H : rem / p.H;
+    h = rem - w * p.H;
+}
 __device__ __forceinline__ PlaneChan plane_chan(int c, long rows, const PoolGeom &g) {
     PlaneChan p;
     p.hw = (unsigned)(g.H * g.W);
     p.H = (unsigned)g.H;
+    p.sh_hw = (p.hw & (p.hw - 1)) == 0 ? 31 - __clz(p.hw) : -1;
+    p.sh_H = (p.H & (p.H - 1)) == 0 ? 31 - __clz(p.H) : -1;
     p.pw = (unsigned)(g.Hp * g.Wp);
     p.cbase = (long)c * rows;
     p.pbase = g.type == FITRE_NO_POOL ? p.cbase : (long)c * (rows / p.hw) * p.pw;
@@ -365,8 +386,8 @@ struct PoolActBwdOp {  // dxP, dxA (+ sums: dA [, dA*zhat])
     __device__ Chan chan(int c) const { return plane_chan(c, rows, g); }
     template <int V>
     __device__ void run(const Chan &ch, unsigned r, double (&a)[NS > 0 ? NS : 1]) const {
-        const unsigned n = r / ch.hw, rem = r - n * ch.hw;
-        const unsigned w = rem / ch.H, h = rem - w * ch.H;
+        unsigned n, w, h;
+        plane_coords(ch, r, n, w, h);
         const long i = ch.cbase + r;
         const double *aplane = actv + ch.cbase + (long)n * ch.hw;
         const double *pplane = dpool + ch.pbase + (long)n * (g.type == FITRE_NO_POOL ? ch.hw : ch.pw);
@@ -478,8 +499,8 @@ struct RPoolActBwdOp {  // RdA = h' RdP + h'' Rzin dxP   (+ sums, see conv_post_
     template <int V>
     __device__ void run(const Chan &ch, unsigned r, double (&a)[NS > 0 ? NS : 1]) const {
         const PlaneChan &pc = ch.p;
-        const unsigned n = r / pc.hw, rem = r - n * pc.hw;
-        const unsigned w = rem / pc.H, h = rem - w * pc.H;
+        unsigned n, w, h;
+        plane_coords(pc, r, n, w, h);
         const long i = pc.cbase + r;
         const double *aplane = actv + pc.cbase + (long)n * pc.hw;
         const double *pplane = rdpool + pc.pbase + (long)n * (g.type == FITRE_NO_POOL ? pc.hw : pc.pw);
