@@ -46,7 +46,7 @@ constexpr int FP_SMEM = 2 * (FP_BK * FP_LDA + FP_BN * FP_LDB) * (int)sizeof(doub
 // data gradient into a 3- or 6-channel input), which would otherwise spend 3/4 or more of their
 // tensor work on columns that do not exist.
 template <int KS, int NT>
-__global__ void __launch_bounds__(FP_THREADS, 2) conv_fprop_kernel(ConvArgs p) {
+__global__ void __launch_bounds__(FP_THREADS, NT == 1 ? 3 : 2) conv_fprop_kernel(ConvArgs p) {
     constexpr int BN = 16 * NT;
     extern __shared__ double smem[];
     double *As = smem;                           // [2][BK][LDA]
@@ -333,6 +333,29 @@ __global__ void reduce_slabs_kernel(const double *partial, double *out, long n, 
         double s = 0.0;
         for (int k = 0; k < slabs; ++k) s += partial[(long)k * n + i];
         out[i] = alpha * s;
+    }
+}
+
+// The same sum for many slabs of a small output (LeNet's first layer: 296 slabs of 450 values):
+// eight warps share the slabs of 32 outputs, each adds its contiguous range in ascending order,
+// and the eight part sums are added in ascending order -- a fixed order, like the kernel above.
+__global__ void reduce_slabs_tall_kernel(const double *partial, double *out, long n, int slabs,
+                                         double alpha) {
+    __shared__ double part[8][33];
+    const int li = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const long i = blockIdx.x * 32L + li;
+    const int per = (slabs + 7) / 8;
+    const int k0 = g * per, k1 = min(slabs, k0 + per);
+    double s = 0.0;
+    if (i < n)
+        for (int k = k0; k < k1; ++k) s += partial[(long)k * n + i];
+    part[g][li] = s;
+    __syncthreads();
+    if (g == 0 && i < n) {
+        double t = 0.0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t += part[j][li];
+        out[i] = alpha * t;
     }
 }
 
@@ -861,18 +884,19 @@ void conv_fprop(fitre_context *ctx, int nseg, const ConvSeg *segs, const double 
     a.Wo = W + 2 * pad - k + 1;
     a.K = Cin * k * k;
     a.M = (long)N * a.Ho * a.Wo;
-    const bool narrow = Cout <= 16;  // 128 x 16 block tile
+    const bool narrow = Cout <= 16;  // 128 x 16 block tile: gather-bound, so three blocks per SM
     const int bn = narrow ? 16 : FP_BN;
+    constexpr int FP_SMEM_NARROW = 2 * (FP_BK * FP_LDA + 16 * FP_LDB) * (int)sizeof(double);
     dim3 grid((unsigned)((a.M + FP_BM - 1) / FP_BM), (unsigned)((Cout + bn - 1) / bn));
     ProfScope prof(ctx, PROF_CONV_IGEMM, 2.0 * (double)a.M * a.K * Cout * nseg);
     if (k == 3) {
-        if (narrow) conv_fprop_kernel<3, 1><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_fprop_kernel<3, 1><<<grid, FP_THREADS, FP_SMEM_NARROW, ctx->stream>>>(a);
         else conv_fprop_kernel<3, 4><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
     } else if (k == 5) {
-        if (narrow) conv_fprop_kernel<5, 1><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_fprop_kernel<5, 1><<<grid, FP_THREADS, FP_SMEM_NARROW, ctx->stream>>>(a);
         else conv_fprop_kernel<5, 4><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
     } else {
-        if (narrow) conv_fprop_kernel<0, 1><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
+        if (narrow) conv_fprop_kernel<0, 1><<<grid, FP_THREADS, FP_SMEM_NARROW, ctx->stream>>>(a);
         else conv_fprop_kernel<0, 4><<<grid, FP_THREADS, FP_SMEM, ctx->stream>>>(a);
     }
     check_launch(ctx, "conv_fprop_kernel");
@@ -947,7 +971,10 @@ void conv_wgrad(fitre_context *ctx, int nseg, const ConvSeg *segs, double *dw, i
     if (S > 1) {
         const long n = (long)a.K * Cout;
         int blocks = (int)std::min<long>((n + 255) / 256, 1184);
-        reduce_slabs_kernel<<<blocks, 256, 0, ctx->stream>>>(partials, dw, n, S, 1.0);
+        if (S >= 32 && n <= 32 * 1184)
+            reduce_slabs_tall_kernel<<<(unsigned)((n + 31) / 32), 256, 0, ctx->stream>>>(partials, dw, n, S, 1.0);
+        else
+            reduce_slabs_kernel<<<blocks, 256, 0, ctx->stream>>>(partials, dw, n, S, 1.0);
         check_launch(ctx, "reduce_slabs_kernel");
     }
 }

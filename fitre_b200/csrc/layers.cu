@@ -790,12 +790,15 @@ __global__ void dots_partial_kernel(long n, const double *a0, const double *b0, 
     }
     block_reduce_store<3>(acc, partials + 3 * blockIdx.x);
 }
+// One warp per dot product: lane l adds the partials of blocks l, l + 32, ... in ascending order,
+// then the 32 lane sums are folded by a fixed shuffle tree.
 __global__ void dots_final_kernel(const double *partials, int blocks, double *out) {
-    if (threadIdx.x < 3) {
-        double s = 0.0;
-        for (int b = 0; b < blocks; ++b) s += partials[3 * b + threadIdx.x];
-        out[threadIdx.x] = s;
-    }
+    const int which = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    double s = 0.0;
+    for (int b = lane; b < blocks; b += 32) s += partials[3 * b + which];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) out[which] = s;
 }
 
 int grid_for(long n) { return (int)std::max<long>(1, std::min<long>((n + kThreads - 1) / kThreads, 148 * 8)); }
@@ -1083,7 +1086,7 @@ void vec_dots(fitre_context *ctx, long n, const double *a0, const double *b0, co
     double *partials = ctx->dscal + 16;
     dots_partial_kernel<<<kDotBlocks, kThreads, 0, ctx->stream>>>(n, a0, b0, a1, b1, a2, b2, partials);
     check_launch(ctx, "dots_partial_kernel");
-    dots_final_kernel<<<1, 32, 0, ctx->stream>>>(partials, kDotBlocks, ctx->dscal + 8);
+    dots_final_kernel<<<1, 96, 0, ctx->stream>>>(partials, kDotBlocks, ctx->dscal + 8);
     check_launch(ctx, "dots_final_kernel");
     FITRE_CUDA(cudaMemcpyAsync(ctx->pinned + 8, ctx->dscal + 8, 3 * sizeof(double),
                                cudaMemcpyDeviceToHost, ctx->stream));
