@@ -17,6 +17,7 @@
 #include <cstring>
 #include <memory>
 #include <mutex>
+#include <climits>
 #include <thread>
 #include <vector>
 
@@ -33,8 +34,19 @@ enum { ncclSuccess = 0, ncclInProgress = 7 };
 enum { ncclChar = 0, ncclFloat64 = 8 };
 enum { ncclSum = 0 };
 
+// Leading fields of ncclConfig_t as published with NCCL 2.17 (nccl.h); the library reads `version`
+// and gives every field that a newer layout adds its default.
+struct CommConfig {
+    size_t size;
+    unsigned int magic, version;
+    int blocking, cgaClusterSize, minCTAs, maxCTAs;
+    const char *netName;
+};
+constexpr int kConfigUndef = INT_MIN;  // NCCL_CONFIG_UNDEF_INT
+
 struct Api {
     void *handle = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t *, int, ncclUniqueId, int, CommConfig *) = nullptr;  // optional
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
@@ -60,6 +72,7 @@ Api &api() {
     FITRE_REQUIRE(a.handle != nullptr, FITRE_ERR_COMM, "cannot load the NCCL library (libnccl.so.2)");
     a.GetUniqueId = (decltype(a.GetUniqueId))dlsym(a.handle, "ncclGetUniqueId");
     a.CommInitRank = (decltype(a.CommInitRank))dlsym(a.handle, "ncclCommInitRank");
+    a.CommInitRankConfig = (decltype(a.CommInitRankConfig))dlsym(a.handle, "ncclCommInitRankConfig");
     a.CommDestroy = (decltype(a.CommDestroy))dlsym(a.handle, "ncclCommDestroy");
     a.CommAbort = (decltype(a.CommAbort))dlsym(a.handle, "ncclCommAbort");
     a.CommGetAsyncError = (decltype(a.CommGetAsyncError))dlsym(a.handle, "ncclCommGetAsyncError");
@@ -322,14 +335,22 @@ namespace {
 // ncclCommInitRank blocks until every rank has joined.  It runs on a helper thread; the caller
 // waits for it at most comm_timeout_s seconds.  If the time runs out the job is abandoned: should
 // the set-up ever return, the helper aborts the communicator it got.
-ncclComm_t bounded_init(fitre_context *ctx, const ncclUniqueId &id, int rank, int world) {
+// max_ctas > 0 caps the thread blocks this communicator's kernels may occupy (ncclConfig_t's
+// maxCTAs) when the library has ncclCommInitRankConfig.
+ncclComm_t bounded_init(fitre_context *ctx, const ncclUniqueId &id, int rank, int world, int max_ctas = 0) {
     Api &a = api();
     auto job = std::make_shared<InitJob>();
     const int device = ctx->device;
-    std::thread([job, id, rank, world, device, &a]() {
+    std::thread([job, id, rank, world, device, max_ctas, &a]() {
         cudaSetDevice(device);
         ncclComm_t c = nullptr;
-        const ncclResult_t r = a.CommInitRank(&c, world, id, rank);
+        ncclResult_t r;
+        if (max_ctas > 0 && a.CommInitRankConfig) {
+            CommConfig cfg{sizeof(CommConfig), 0xcafebeefu, 21700u, kConfigUndef, kConfigUndef, 1, max_ctas, nullptr};
+            r = a.CommInitRankConfig(&c, world, id, rank, &cfg);
+        } else {
+            r = a.CommInitRank(&c, world, id, rank);
+        }
         std::unique_lock<std::mutex> lk(job->mu);
         job->result = r;
         job->comm = c;
@@ -383,7 +404,11 @@ void comm_init(fitre_context *ctx, const void *id128, int rank, int world) {
         FITRE_CUDA(cudaMemcpyAsync(&id2, dev, sizeof(id2), cudaMemcpyDeviceToHost, ctx->stream));
         stream_wait(ctx, ctx->stream);
         FITRE_CUDA(cudaMemsetAsync(dev, 0, sizeof(id2), ctx->stream));
-        ctx->comm->side = bounded_init(ctx, id2, rank, world);
+        // Its all-reduces run under the backward sweep, whose convolution kernels want every SM:
+        // a few thread blocks are enough for 74 MB per pass (FITRE_SIDE_COMM_CTAS, 0 = NCCL's choice).
+        int side_ctas = 4;
+        if (const char *e = std::getenv("FITRE_SIDE_COMM_CTAS")) side_ctas = std::atoi(e);
+        ctx->comm->side = bounded_init(ctx, id2, rank, world, side_ctas);
         FITRE_CUDA(cudaStreamCreateWithFlags(&ctx->comm->side_stream, cudaStreamNonBlocking));
         FITRE_CUDA(cudaEventCreateWithFlags(&ctx->comm->ev_done, cudaEventDisableTiming));
         peer_setup(ctx);
