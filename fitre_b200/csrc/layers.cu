@@ -251,7 +251,18 @@ struct PoolGeom {
     // pool_argmax_map_kernel so that the gather below compares one byte per covering window
     // instead of re-scanning the window's pk * pk activations
     const unsigned char *map;
+    // optional, instead of `map`, for pools with at most two windows over an element in either
+    // direction (ceil(pk / ps) <= 2): one byte per ELEMENT of the pool input, bit 2*dl + dk set
+    // when the window (kmin(h) + dk, lmin(w) + dl) has its arg-max at this element; filled by
+    // pool_winner_mask_kernel.  Three elements in four are zero and skip the gather altogether.
+    const unsigned char *emask;
 };
+// first window that covers coordinate x: ceil((x + pp - pk + 1) / ps), 0 when the numerator is <= 0
+__device__ __forceinline__ int first_window(int x, const PoolGeom &g) {
+    const int t = x + g.pp - g.pk + 1;
+    if (t <= 0) return 0;
+    return g.ps == 2 ? (t + 1) >> 1 : (t + g.ps - 1) / g.ps;
+}
 
 // arg-max of one pooling window, scan order of the backward kernel: column outer, row inner,
 // strict '>' (functions/dev_pool.cu:374-391).  Returns w*H + h of the winner.
@@ -277,6 +288,18 @@ __device__ __forceinline__ int window_argmax(const double *plane, const PoolGeom
 
 // errors arriving at element (h, w) of one plane through the pooling layer (gather form of
 // functions/dev_pool.cu:269-298,346-398 and the 1/k^2 scale of functions/cnn_backward.cu:471-473)
+__device__ __forceinline__ double pool_gather_masked(const double *dpool_plane, const PoolGeom &g, int h,
+                                                     int w, unsigned mask) {
+    if (!mask) return 0.0;
+    const int kmin = first_window(h, g), lmin = first_window(w, g);
+    double s = 0.0;  // same order as the scan below: l outer, k inner
+    if (mask & 1u) s += dpool_plane[lmin * g.Hp + kmin];
+    if (mask & 2u) s += dpool_plane[lmin * g.Hp + kmin + 1];
+    if (mask & 4u) s += dpool_plane[(lmin + 1) * g.Hp + kmin];
+    if (mask & 8u) s += dpool_plane[(lmin + 1) * g.Hp + kmin + 1];
+    return s;
+}
+
 __device__ __forceinline__ double pool_gather(const double *dpool_plane, const double *act_plane,
                                               const PoolGeom &g, int h, int w,
                                               const unsigned char *map_plane = nullptr) {
@@ -324,8 +347,17 @@ __device__ __forceinline__ double pool_gather(const double *dpool_plane, const d
 template <int V>
 __device__ __forceinline__ Pk<V> pool_gather_v(const double *dpool_plane, const double *act_plane,
                                                const PoolGeom &g, int h, int w, const Pk<V> &a,
-                                               const unsigned char *map_plane = nullptr) {
+                                               const unsigned char *map_plane = nullptr,
+                                               const unsigned char *elem_mask = nullptr) {
     Pk<V> out;
+    if (elem_mask) {  // elem_mask points at the byte of element (h, w); V == 2 reads both rows at once
+        unsigned m;
+        if (V == 2) m = *reinterpret_cast<const unsigned short *>(elem_mask);
+        else m = elem_mask[0];
+#pragma unroll
+        for (int e = 0; e < V; ++e) out.v[e] = pool_gather_masked(dpool_plane, g, h + e, w, (m >> (8 * e)) & 0xffu);
+        return out;
+    }
     if (V == 2 && g.type == FITRE_MAX_POOL && g.pk == 2 && g.ps == 2 && g.pp == 0 &&
         !(g.H & 1) && !(g.W & 1)) {
         const Pk<V> b = ldp<V>(act_plane + (w ^ 1) * g.H + h);  // the window's other column
@@ -393,7 +425,8 @@ struct PoolActBwdOp {  // dxP, dxA (+ sums: dA [, dA*zhat])
         const double *pplane = dpool + ch.pbase + (long)n * (g.type == FITRE_NO_POOL ? ch.hw : ch.pw);
         const Pk<V> av = ldp<V>(actv + i), zi = ldp<V>(zin + i);
         const unsigned char *mplane = g.map ? g.map + ch.pbase + (long)n * ch.pw : nullptr;
-        const Pk<V> dP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av, mplane);
+        const Pk<V> dP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av, mplane,
+                                          g.emask ? g.emask + i : nullptr);
         Pk<V> dA;
 #pragma unroll
         for (int e = 0; e < V; ++e) {
@@ -507,7 +540,8 @@ struct RPoolActBwdOp {  // RdA = h' RdP + h'' Rzin dxP   (+ sums, see conv_post_
         const Pk<V> av = ldp<V>(actv + i), zi = ldp<V>(zin + i), rzh = ldp<V>(rzin + i);
         const Pk<V> dp = ldp<V>(dxP + i);
         const unsigned char *mplane = g.map ? g.map + pc.pbase + (long)n * pc.pw : nullptr;
-        const Pk<V> RdP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av, mplane);
+        const Pk<V> RdP = pool_gather_v<V>(pplane, aplane, g, (int)h, (int)w, av, mplane,
+                                           g.emask ? g.emask + i : nullptr);
         Pk<V> RdA;
 #pragma unroll
         for (int e = 0; e < V; ++e)
@@ -581,6 +615,24 @@ __global__ void pool_argmax_map_kernel(const double *act, unsigned char *map, lo
             code = (w - (l * g.ps - g.pp)) * g.pk + (h - (k * g.ps - g.pp));
         }
         map[t] = (unsigned char)code;
+    }
+}
+
+// One thread per pooling window: sets, in the byte of the element that is the window's arg-max,
+// the bit that names this window among the (at most 2 x 2) windows over that element (see
+// PoolGeom::emask).  OR is order-independent, so the map is the same whatever the schedule.
+__global__ void pool_winner_mask_kernel(const double *act, unsigned char *emask, long planes, PoolGeom g) {
+    const long total = planes * g.Hp * g.Wp;
+    for (long t = blockIdx.x * (long)blockDim.x + threadIdx.x; t < total; t += (long)gridDim.x * blockDim.x) {
+        const long plane = t / (g.Hp * g.Wp);
+        const int rem = (int)(t - plane * (g.Hp * g.Wp));
+        const int l = rem / g.Hp, k = rem - l * g.Hp;
+        const int arg = window_argmax(act + plane * (long)(g.H * g.W), g, k, l);
+        if (arg < 0) continue;
+        const int w = arg / g.H, h = arg - w * g.H;
+        const int bit = 2 * (l - first_window(w, g)) + (k - first_window(h, g));
+        const long idx = plane * (long)(g.H * g.W) + arg;
+        atomicOr(reinterpret_cast<unsigned *>(emask + (idx & ~3L)), 1u << (8 * (int)(idx & 3) + bit));
     }
 }
 
@@ -816,6 +868,7 @@ bool vec2_ok(const ConvGeom &g, int N, std::initializer_list<const void *> ptrs)
 PoolGeom pool_geom(const ConvGeom &g) {
     PoolGeom p;
     p.map = nullptr;
+    p.emask = nullptr;
     p.type = g.poolType;
     p.pk = g.pk; p.ps = g.ps; p.pp = g.pp;
     p.H = g.Ho; p.W = g.Wo;
@@ -833,20 +886,32 @@ bool pool_wants_map(const ConvGeom &g) {
     const bool fast = g.pk == 2 && g.ps == 2 && g.pp == 0 && !(g.Ho & 1) && !(g.Wo & 1);
     return !fast;  // the 2/2/0 pool resolves its window from two loads
 }
+// at most two windows over an element in either direction: the per-element winner mask serves
+bool pool_mask_per_element(const ConvGeom &g) { return pool_wants_map(g) && (g.pk + g.ps - 1) / g.ps <= 2; }
 // fills the arg-max map of this layer's pooling windows and hands it to the gather
 void prepare_pool_map(fitre_context *ctx, const ConvGeom &g, int N, const double *act, unsigned char *map,
                       PoolGeom &pg) {
     if (!map || !pool_wants_map(g)) return;
     const long planes = (long)g.Cout * N;
+    if (pool_mask_per_element(g)) {
+        FITRE_CUDA(cudaMemsetAsync(map, 0, (size_t)pool_map_doubles(g, N) * sizeof(double), ctx->stream));
+        pool_winner_mask_kernel<<<grid_for(planes * g.Hp * g.Wp), kThreads, 0, ctx->stream>>>(act, map, planes, pg);
+        check_launch(ctx, "pool_winner_mask_kernel");
+        pg.emask = map;
+        return;
+    }
     pool_argmax_map_kernel<<<grid_for(planes * g.Hp * g.Wp), kThreads, 0, ctx->stream>>>(act, map, planes, pg);
     check_launch(ctx, "pool_argmax_map_kernel");
     pg.map = map;
 }
 }  // namespace
 
-// doubles of scratch the backward passes need for the arg-max map of layer g's pooling windows
+// doubles of scratch the backward passes need for the arg-max map of layer g's pooling: one byte
+// per element of the pool input (winner mask) or one per window (arg-max code)
 long pool_map_doubles(const ConvGeom &g, int N) {
-    return pool_wants_map(g) ? ((long)g.Cout * N * g.Hp * g.Wp + 7) / 8 : 0;
+    if (!pool_wants_map(g)) return 0;
+    const long bytes = pool_mask_per_element(g) ? (long)g.Cout * N * g.Ho * g.Wo : (long)g.Cout * N * g.Hp * g.Wp;
+    return (bytes + 7) / 8;
 }
 
 void add_channel_bias(fitre_context *ctx, double *x, const double *bias, long rows, int C) {
