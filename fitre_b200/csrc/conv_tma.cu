@@ -13,6 +13,7 @@
 //  * stages form a ring guarded by mbarriers (complete_tx); every wait is bounded and reports
 //    through an error word instead of spinning forever.
 // No cluster multicast is used anywhere (each CTA fetches its own tiles).
+#include <cstdlib>
 #include <cuda.h>
 
 #include <algorithm>
@@ -585,6 +586,15 @@ WgradPlan wgrad_plan(int N, int Cin, int H, int W, int k, int pad, int Cout) {
     const long tiles = (long)pl.tq * pl.tn;
     const double step_us = 8.3 * pl.BMT / 64.0;  // one BMT x 128 x 64 step with two CTAs per SM
     pl.splits = best_split(tiles, pl.tiles_total, 256, 8, step_us, (double)K * Cout * 8);
+    // One wave of equal blocks does not end together: a block whose neighbour on the SM has
+    // retired runs at twice the rate, and the slots it leaves stay empty.  Four times finer units
+    // (down to 8 steps each) let the block scheduler even that out; measured on VGG-11-BN at 512
+    // images 31.5 -> 32.6 TFLOP/s, 2x and 8x finer gave less.
+    {
+        int finer = pl.splits * 4;
+        while (finer > pl.splits && pl.tiles_total / finer < 8) --finer;
+        pl.splits = std::max(pl.splits, finer);
+    }
     pl.tiles_per_split = (pl.tiles_total + pl.splits - 1) / pl.splits;
     pl.splits = (pl.tiles_total + pl.tiles_per_split - 1) / pl.tiles_per_split;
     return pl;
