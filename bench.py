@@ -444,6 +444,51 @@ def bind_to_gpu_numa_node(gpu_index):
     return None
 
 
+def time_shared_results(ctx, model, api, hx, hy, hw, hv_in, hg, hh, n, world, rank, args, barrier, e0, e1,
+                        h2d, d2h):
+    """End to end like `e2e`, with gradient and Hv delivered once per node into a segment all ranks
+    share; checks afterwards that the shared vectors are the private-buffer results bit for bit."""
+    import torch
+    import torch.distributed as dist
+    P = model.pSize
+    shm = "/dev/shm/fitre_bench_%s" % os.environ.get("MASTER_PORT", "0")
+    if rank == 0:
+        np.memmap(shm, dtype=np.float64, mode="w+", shape=(2 * P,)).flush()
+    dist.barrier()
+    buf = np.memmap(shm, dtype=np.float64, mode="r+", shape=(2 * P,))
+    rt = torch.cuda.cudart()
+    rt.cudaHostRegister(buf.ctypes.data, buf.nbytes, 0)
+    ctx.set_host_results_shared(1)
+    try:
+        def host_step():
+            return api.gradientHvHost(ctx, model, hx, hy, hw, hv_in, n, 10, 0.0, buf[:P], buf[P:])
+        for _ in range(max(1, min(args.warmup, 3))):
+            host_step()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            host_step()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        same = bool(np.array_equal(np.asarray(buf[:P]), hg.numpy()) and np.array_equal(np.asarray(buf[P:]), hh.numpy()))
+    finally:
+        ctx.set_host_results_shared(0)
+        rt.cudaHostUnregister(buf.ctypes.data)
+        dist.barrier()
+        del buf
+        if rank == 0:
+            os.unlink(shm)
+    return {"value": world * n * args.steps / (ms * 1e-3), "unit": "images/s", "ms_per_step": ms / args.steps,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step_per_rank": d2h // world,
+            "results_equal_private_buffers": same,
+            "note": "gradient and Hv cross PCIe once per node: every rank copies its 1/%d share into a "
+                    "shared page-locked segment and all ranks read the whole vectors" % world}
+
+
 # ---- the benchmark ----------------------------------------------------------------------------
 def run_ours(args):
     import torch
@@ -541,6 +586,18 @@ def run_ours(args):
     h2d = 8 * (x.size + y.size + w.size + v.size)
     d2h = 8 * 2 * model.pSize
 
+    # ---- the same with ONE result buffer per node: the ranks' processes map and page-lock the same
+    # shared-memory segment, each copies its 1/world share of gradient and Hv, all find the whole
+    # vectors (fitre_set_host_results_shared).  Extra information; `e2e` above stays the figure with
+    # private buffers on every rank.
+    e2e_shared = None
+    if world > 1:
+        try:
+            e2e_shared = time_shared_results(ctx, model, api, hx, hy, hw, hv_in, hg, hh, n, world, rank, args,
+                                             barrier, e0, e1, h2d, d2h)
+        except Exception as e:  # noqa: BLE001 -- extra information must not take the headline down
+            e2e_shared = {"error": str(e)[:300]}
+
     # ---- the path's other configurations at this GPU count, and the sharded-parity check
     secondary, parity = {}, None
     if not args.no_secondary and args.precision == "fp64":
@@ -617,6 +674,8 @@ def run_ours(args):
         "per_gpu_algorithmic_tflops": (gpi + hpi) * n * args.steps / (ms * 1e-3) / 1e12,
         "algorithmic_mflop_per_image": {"gradient": gpi / 1e6, "hv": hpi / 1e6},
     }
+    if e2e_shared is not None:
+        line["e2e_node_shared_results"] = e2e_shared
     if world > 1:
         line["multi_gpu"] = {
             "host_binding": ("process bound to the %d cores next to its GPU" % numa_cores) if numa_cores else "none",

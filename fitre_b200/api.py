@@ -100,6 +100,11 @@ class Context:
         on an owner rank, which also forms that layer's slice of the natural gradient."""
         self.check(self.lib.fitre_set_kfac_distribution(self.h, int(mode)))
 
+    def set_host_results_shared(self, on):
+        """gradientHvHost's result buffers are one shared, page-locked segment on every rank:
+        each rank copies its share only (see fitre_set_host_results_shared)."""
+        self.check(self.lib.fitre_set_host_results_shared(self.h, int(bool(on))))
+
     def set_graphs(self, on):
         """CUDA-graph replay of the factor-inverse and natural-gradient launch sequences (default on)."""
         self.check(self.lib.fitre_set_graphs(self.h, int(bool(on))))

@@ -208,6 +208,12 @@ int fitre_set_kfac_distribution(fitre_context *ctx, int mode) {
 
 int fitre_get_kfac_solver(const fitre_context *ctx) { return ctx ? ctx->kfac_solver : -1; }
 
+int fitre_set_host_results_shared(fitre_context *ctx, int on) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    ctx->host_shared = on ? 1 : 0;
+    return FITRE_OK;
+}
+
 int fitre_set_graphs(fitre_context *ctx, int on) {
     if (!ctx) return FITRE_ERR_BAD_ARG;
     ctx->use_graphs = on ? 1 : 0;
@@ -589,7 +595,12 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         FITRE_REQUIRE(rc == FITRE_OK, rc, ctx->err);
         // the gradient call returned after a stream sync (loss read-back): g is complete and
         // travels back on the copy stream while the Hessian-vector product runs
-        FITRE_CUDA(cudaMemcpyAsync(gradient_host, g, sizeof(double) * m->pSize, cudaMemcpyDeviceToHost, cs));
+        {
+            long lo, hi;
+            host_share(ctx, 0, m->pSize, lo, hi);
+            FITRE_CUDA(cudaMemcpyAsync(gradient_host + lo, g + lo, sizeof(double) * (size_t)(hi - lo),
+                                       cudaMemcpyDeviceToHost, cs));
+        }
         FITRE_CUDA(cudaStreamWaitEvent(st, ctx->ev_up, 0));
         // finished slices of hv follow the gradient on the copy stream as the backward sweep completes
         // its layers (with ranks: as each layer's slice has been all-reduced on the side stream)
@@ -599,9 +610,20 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         const long sent_from = ctx->hv_host_dst ? ctx->hv_sent_from : m->pSize;
         ctx->hv_host_dst = nullptr;
         FITRE_REQUIRE(rc == FITRE_OK, rc, ctx->err);
-        if (sent_from > 0)
-            FITRE_CUDA(cudaMemcpyAsync(hv_host, hv, sizeof(double) * sent_from, cudaMemcpyDeviceToHost, st));
+        if (sent_from > 0) {
+            long lo, hi;
+            host_share(ctx, 0, sent_from, lo, hi);
+            if (hi > lo)
+                FITRE_CUDA(cudaMemcpyAsync(hv_host + lo, hv + lo, sizeof(double) * (size_t)(hi - lo),
+                                           cudaMemcpyDeviceToHost, st));
+        }
         FITRE_CUDA(cudaEventRecord(ctx->ev_down, cs));
+        if (ctx->host_shared && ctx->world > 1) {
+            // every rank wrote its share of the one buffer: a one-element all-reduce queued behind
+            // this rank's copies completes only when all ranks have queued theirs, i.e. sent their shares
+            FITRE_CUDA(cudaStreamWaitEvent(st, ctx->ev_down, 0));
+            comm_allreduce_sum(ctx, ctx->dscal + 3890, 1);
+        }
         stream_wait(ctx, st);
         FITRE_CUDA(cudaEventSynchronize(ctx->ev_down));
         if (loss_host) *loss_host = loss;

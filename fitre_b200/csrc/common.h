@@ -83,6 +83,7 @@ struct fitre_context {
     cudaEvent_t fwd_wait_event = nullptr, ev_w2 = nullptr, chunk_ev[24] = {};
     int fwd_wait_layer = -1;
     double *hv_host_dst = nullptr;
+    int host_shared = 0;                  // result buffers of the host entry point are shared by all ranks
     long hv_sent_from = 0;
     // set around a backward sweep whose result vector is a batch sum wanted on every rank: the
     // sweep then all-reduces each layer's finished slice while it computes the next layer
@@ -277,6 +278,16 @@ void conv_post_rop_forward(fitre_context *ctx, const ConvGeom &g, int N, const d
 // `pool_map` (pool_map_doubles(g, N) doubles of scratch, may be NULL): room for the arg-max map of
 // the layer's pooling windows, which the backward gather of a general max pool then reads
 long pool_map_doubles(const ConvGeom &g, int N);
+// The part [lo, hi) of a finished range [a, b) of a result vector that this rank sends to the
+// host: all of it, or its 1/world share when every rank's host buffer is the same memory.
+inline void host_share(const fitre_context *ctx, long a, long b, long &lo, long &hi) {
+    lo = a;
+    hi = b;
+    if (!ctx->host_shared || ctx->world <= 1) return;
+    const long len = b - a;
+    lo = a + len * ctx->rank / ctx->world;
+    hi = a + len * (ctx->rank + 1) / ctx->world;
+}
 const double *conv_post_backward(fitre_context *ctx, const ConvGeom &g, int N, const double *zl,
                                  double *dxl, const double *delta_pool, double *db,
                                  double *scratch, unsigned char *pool_map = nullptr);

@@ -248,8 +248,11 @@ static void send_finished_hv(fitre_context *ctx, const double *hv, long from, in
     if (!ev) FITRE_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     FITRE_CUDA(cudaEventRecord(ev, after));
     FITRE_CUDA(cudaStreamWaitEvent(ctx->copy_stream, ev, 0));
-    FITRE_CUDA(cudaMemcpyAsync(ctx->hv_host_dst + from, hv + from, sizeof(double) * (size_t)(ctx->hv_sent_from - from),
-                               cudaMemcpyDeviceToHost, ctx->copy_stream));
+    long lo, hi;
+    host_share(ctx, from, ctx->hv_sent_from, lo, hi);
+    if (hi > lo)
+        FITRE_CUDA(cudaMemcpyAsync(ctx->hv_host_dst + lo, hv + lo, sizeof(double) * (size_t)(hi - lo),
+                                   cudaMemcpyDeviceToHost, ctx->copy_stream));
     ctx->hv_sent_from = from;
 }
 

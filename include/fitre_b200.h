@@ -635,6 +635,15 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
                            const real *vector_host, int curBatchSize, int numClasses,
                            real weightDecay, real *loss_host, real *gradient_host,
                            real *hv_host);
+/* With ranks, gradient and hv are the same vectors on every rank, and on one node the ranks' host
+ * memory is one memory.  on = 1 tells fitre_gradient_hv_host that gradient_host and hv_host
+ * address the SAME physical buffers on every rank of the communicator (one shared-memory segment
+ * mapped, and page-locked, by every process): each rank then copies only its 1/world share of
+ * every finished slice, and the call returns once all ranks' shares have landed (a one-element
+ * all-reduce queued behind the copies is the barrier), so the node moves each result across
+ * PCIe once instead of `world` times.  loss_host stays private.  Default 0: every rank fills its
+ * own buffers.  No counterpart in the reference (one GPU, device-resident results). */
+int fitre_set_host_results_shared(fitre_context *ctx, int on);
 
 #ifdef __cplusplus
 }

@@ -181,7 +181,27 @@ def main():
         # Hessian-vector slices travel to the host as each layer's all-reduce completes)
         g_host, hv_host = np.zeros(model.pSize), np.zeros(model.pSize)
         loss_host = api.gradientHvHost(ctx, model, xs, ys, w, v, per, ncls, 0.0, g_host, hv_host)
+        # the same call with result buffers that are ONE shared, page-locked segment on all ranks:
+        # every rank copies its share of each finished slice only, and finds the whole vectors
+        P = model.pSize
+        shm = "/dev/shm/fitre_mr_%s" % os.environ.get("MASTER_PORT", "0")
+        if rank == 0:
+            np.memmap(shm, dtype=np.float64, mode="w+", shape=(2 * P,)).flush()
+        dist.barrier()
+        buf = np.memmap(shm, dtype=np.float64, mode="r+", shape=(2 * P,))
+        rt = torch.cuda.cudart()
+        rt.cudaHostRegister(buf.ctypes.data, buf.nbytes, 0)
+        ctx.set_host_results_shared(1)
+        loss_shared = api.gradientHvHost(ctx, model, xs, ys, w, v, per, ncls, 0.0, buf[:P], buf[P:])
+        ctx.set_host_results_shared(0)
+        g_shared, hv_shared = np.array(buf[:P]), np.array(buf[P:])
+        rt.cudaHostUnregister(buf.ctypes.data)
+        dist.barrier()
+        del buf
+        if rank == 0:
+            os.unlink(shm)
         np.savez(out, loss=loss64, gradient=g64, hv=hv, A=A.cpu().numpy(), peer_reduce=int(ctx.peer_reduce_enabled),
+                 loss_shared=loss_shared, gradient_shared=g_shared, hv_shared=hv_shared,
                  peer_launches=ctx.kernel_launches("peer_allreduce_kernel"),
                  loss_host=loss_host, gradient_host=g_host, hv_host=hv_host,
                  G=Gm.cpu().numpy(), Ainv=Ai.cpu().numpy(), Ginv=Gi.cpu().numpy(),
