@@ -459,6 +459,7 @@ def time_shared_results(ctx, model, api, hx, hy, hw, hv_in, hg, hh, n, world, ra
     rt = torch.cuda.cudart()
     rt.cudaHostRegister(buf.ctypes.data, buf.nbytes, 0)
     ctx.set_host_results_shared(1)
+    ctx.set_host_inputs_replicated(1)  # weights and direction are the same on every rank
     try:
         def host_step():
             return api.gradientHvHost(ctx, model, hx, hy, hw, hv_in, n, 10, 0.0, buf[:P], buf[P:])
@@ -477,16 +478,19 @@ def time_shared_results(ctx, model, api, hx, hy, hw, hv_in, hg, hh, n, world, ra
         same = bool(np.array_equal(np.asarray(buf[:P]), hg.numpy()) and np.array_equal(np.asarray(buf[P:]), hh.numpy()))
     finally:
         ctx.set_host_results_shared(0)
+        ctx.set_host_inputs_replicated(0)
         rt.cudaHostUnregister(buf.ctypes.data)
         dist.barrier()
         del buf
         if rank == 0:
             os.unlink(shm)
     return {"value": world * n * args.steps / (ms * 1e-3), "unit": "images/s", "ms_per_step": ms / args.steps,
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step_per_rank": d2h // world,
+            "h2d_bytes_per_step_per_rank": h2d - (world - 1) * d2h // world,
+            "d2h_bytes_per_step_per_rank": d2h // world,
             "results_equal_private_buffers": same,
-            "note": "gradient and Hv cross PCIe once per node: every rank copies its 1/%d share into a "
-                    "shared page-locked segment and all ranks read the whole vectors" % world}
+            "note": "weights, direction, gradient and Hv cross PCIe once per node: every rank uploads a 1/%d "
+                    "chunk of the replicated inputs (all-gathered over NVLink) and copies its share of the "
+                    "results into a page-locked segment that all ranks read" % world}
 
 
 # ---- the benchmark ----------------------------------------------------------------------------

@@ -31,7 +31,7 @@ SYMBOLS = [
     "fitre_kfac_factors_and_inverses_mem_required", "fitre_kfac_factors_and_inverses",
     "fitre_kfac_omega_z_begin", "fitre_kfac_lambda_delta_finish",
     "fitre_kfac_natural_gradient_mem_required", "fitre_compute_natural_gradient",
-    "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host", "fitre_set_host_results_shared",
+    "fitre_syrk_tn_static_scratch", "fitre_gradient_hv_host", "fitre_set_host_results_shared", "fitre_set_host_inputs_replicated",
     "fitre_init_batch_norm_data", "fitre_evaluate_cnn_model", "fitre_compute_accuracy",
     "fitre_select_column_matrix", "fitre_prepare_minibatch", "fitre_generalization_mem_required",
     "fitre_compute_generalization_errors", "fitre_trust_region_kfac_mem_required",
@@ -72,6 +72,7 @@ def load():
     sig("fitre_set_kfac_solver", i, vp, i)
     sig("fitre_set_graphs", i, vp, i)
     sig("fitre_set_host_results_shared", i, vp, i)
+    sig("fitre_set_host_inputs_replicated", i, vp, i)
     sig("fitre_set_kfac_distribution", i, vp, i)
     sig("fitre_get_kfac_solver", i, vp)
     sig("fitre_kfac_matrix_factor", i, vp, vp, vp, i, d, d)

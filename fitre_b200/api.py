@@ -105,6 +105,11 @@ class Context:
         each rank copies its share only (see fitre_set_host_results_shared)."""
         self.check(self.lib.fitre_set_host_results_shared(self.h, int(bool(on))))
 
+    def set_host_inputs_replicated(self, on):
+        """gradientHvHost's weights and vector hold the same values on every rank: each rank uploads
+        one chunk, the chunks are all-gathered on the device (see fitre_set_host_inputs_replicated)."""
+        self.check(self.lib.fitre_set_host_inputs_replicated(self.h, int(bool(on))))
+
     def set_graphs(self, on):
         """CUDA-graph replay of the factor-inverse and natural-gradient launch sequences (default on)."""
         self.check(self.lib.fitre_set_graphs(self.h, int(bool(on))))

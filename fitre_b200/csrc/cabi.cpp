@@ -214,6 +214,12 @@ int fitre_set_host_results_shared(fitre_context *ctx, int on) {
     return FITRE_OK;
 }
 
+int fitre_set_host_inputs_replicated(fitre_context *ctx, int on) {
+    if (!ctx) return FITRE_ERR_BAD_ARG;
+    ctx->host_replicated = on ? 1 : 0;
+    return FITRE_OK;
+}
+
 int fitre_set_graphs(fitre_context *ctx, int on) {
     if (!ctx) return FITRE_ERR_BAD_ARG;
     ctx->use_graphs = on ? 1 : 0;
@@ -532,7 +538,7 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         FITRE_REQUIRE(numClasses == m->fcLayer[m->lLayers - 1].out, FITRE_ERR_BAD_ARG,
                       "numClasses differs from the last layer");
         const CONV_LAYER &c0 = m->convLayer[0];
-        const long P = align32(m->pSize), Z = align32(m->zSize);
+        const long P = align32(m->pSize + 64), Z = align32(m->zSize);  // room for world equal chunks
         const long X = align32((long)n * c0.inChannels * c0.height * c0.width);
         const long Y = align32(n), PR = align32((long)n * numClasses);
         const long work = std::max(fitre_cnn_gradient_mem_required(m), fitre_cnn_hv_mem_required(m));
@@ -568,15 +574,34 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
         FITRE_CUDA(cudaMemcpyAsync(x, batch_host, sizeof(double) * (long)n * c0.inChannels * c0.height * c0.width,
                                    cudaMemcpyHostToDevice, st));
         FITRE_CUDA(cudaMemcpyAsync(y, labels_host, sizeof(double) * n, cudaMemcpyHostToDevice, st));
+        // The head of the weights goes up at once on every rank.  The rest, and the direction vector,
+        // travel on the copy stream underneath the first layers' compute: in full, or -- replicated
+        // inputs, i.e. the same weights and direction on every rank, as data parallelism has them --
+        // one of `world` equal chunks per rank, exchanged by an all-gather over NVLink queued on the
+        // copy stream, so that the node reads each vector from host memory once.
         FITRE_CUDA(cudaMemcpyAsync(w, weights_host, sizeof(double) * head, cudaMemcpyHostToDevice, st));
+        const bool gather = ctx->host_replicated && ctx->world > 1 && ctx->world <= 64 && comm_has_allgather();
+        auto upload = [&](double *dst, const double *src, long first, long count) {  // on the copy stream
+            if (count <= 0) return;
+            if (!gather) {
+                FITRE_CUDA(cudaMemcpyAsync(dst + first, src + first, sizeof(double) * (size_t)count,
+                                           cudaMemcpyHostToDevice, cs));
+                return;
+            }
+            const long chunk = (count + ctx->world - 1) / ctx->world;
+            const long lo = std::min<long>(count, (long)ctx->rank * chunk), hi = std::min<long>(count, lo + chunk);
+            if (hi > lo)
+                FITRE_CUDA(cudaMemcpyAsync(dst + first + lo, src + first + lo, sizeof(double) * (size_t)(hi - lo),
+                                           cudaMemcpyHostToDevice, cs));
+            comm_allgather_inplace(ctx, dst + first, (size_t)chunk, cs);
+        };
         if (head < m->pSize) {
-            FITRE_CUDA(cudaMemcpyAsync(w + head, weights_host + head, sizeof(double) * (m->pSize - head),
-                                       cudaMemcpyHostToDevice, cs));
+            upload(w, weights_host, head, m->pSize - head);
             FITRE_CUDA(cudaEventRecord(ctx->ev_w2, cs));
             ctx->fwd_wait_event = ctx->ev_w2;
             ctx->fwd_wait_layer = split_layer;
         }
-        FITRE_CUDA(cudaMemcpyAsync(v, vector_host, sizeof(double) * m->pSize, cudaMemcpyHostToDevice, cs));
+        upload(v, vector_host, 0, m->pSize);
         FITRE_CUDA(cudaEventRecord(ctx->ev_up, cs));
         DEVICE_DATASET data;
         std::memset(&data, 0, sizeof(data));

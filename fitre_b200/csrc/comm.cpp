@@ -147,6 +147,17 @@ void comm_allreduce_sum(fitre_context *ctx, double *dev_buf, size_t n) {
     ctx->launches += 1;  // NCCL's kernel; counted so the launch figure covers the whole step
 }
 
+bool comm_has_allgather() { return api().AllGather != nullptr; }
+
+bool comm_allgather_inplace(fitre_context *ctx, double *dev_buf, size_t chunk, cudaStream_t stream) {
+    if (ctx->world <= 1 || !ctx->comm || chunk == 0) return true;
+    if (!api().AllGather) return false;
+    check(api().AllGather(dev_buf + (size_t)ctx->rank * chunk, dev_buf, chunk, ncclFloat64, live_comm(ctx), stream),
+          "ncclAllGather");
+    ctx->launches += 1;
+    return true;
+}
+
 // sum over the ranks, result on `root` only (the buffers of the other ranks are left as they were)
 void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root) {
     if (ctx->world <= 1 || !ctx->comm || n == 0) return;

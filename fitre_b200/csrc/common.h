@@ -84,6 +84,7 @@ struct fitre_context {
     int fwd_wait_layer = -1;
     double *hv_host_dst = nullptr;
     int host_shared = 0;                  // result buffers of the host entry point are shared by all ranks
+    int host_replicated = 0;              // ... and its weights / vector inputs hold the same values on all ranks
     long hv_sent_from = 0;
     // set around a backward sweep whose result vector is a batch sum wanted on every rank: the
     // sweep then all-reduces each layer's finished slice while it computes the next layer
@@ -164,6 +165,10 @@ struct ProfScope {
 
 // ---- comm.cpp: all-reduce hooks (no-ops when world == 1) ----
 void comm_allreduce_sum(fitre_context *ctx, double *dev_buf, size_t n);
+// In place: every rank contributes dev_buf[rank * chunk, +chunk) and receives all world chunks.
+// False (nothing done) when the NCCL library at hand has no ncclAllGather.
+bool comm_allgather_inplace(fitre_context *ctx, double *dev_buf, size_t chunk, cudaStream_t stream);
+bool comm_has_allgather();
 void comm_reduce_sum(fitre_context *ctx, double *dev_buf, size_t n, int root);
 void comm_destroy(fitre_context *ctx);
 // all-reduce of a finished slice on the side communicator / stream; join = the context's stream

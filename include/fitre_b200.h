@@ -644,6 +644,14 @@ int fitre_gradient_hv_host(fitre_context *ctx, const CNN_MODEL *m, const real *b
  * PCIe once instead of `world` times.  loss_host stays private.  Default 0: every rank fills its
  * own buffers.  No counterpart in the reference (one GPU, device-resident results). */
 int fitre_set_host_results_shared(fitre_context *ctx, int on);
+/* The inputs' counterpart: on = 1 tells fitre_gradient_hv_host that weights_host and vector_host
+ * hold the same values on every rank (what data parallelism means: replicated parameters, one
+ * direction).  Each rank then uploads one of `world` equal chunks of either vector and the chunks
+ * are exchanged by an all-gather over NVLink, so the node reads each from host memory once.  All
+ * ranks must set it alike (the all-gather is a collective).  Batch and labels are per rank and
+ * travel as before.  Default 0.  Falls back to full uploads when the NCCL library has no
+ * ncclAllGather. */
+int fitre_set_host_inputs_replicated(fitre_context *ctx, int on);
 
 #ifdef __cplusplus
 }

@@ -193,8 +193,17 @@ def main():
         rt.cudaHostRegister(buf.ctypes.data, buf.nbytes, 0)
         ctx.set_host_results_shared(1)
         loss_shared = api.gradientHvHost(ctx, model, xs, ys, w, v, per, ncls, 0.0, buf[:P], buf[P:])
-        ctx.set_host_results_shared(0)
         g_shared, hv_shared = np.array(buf[:P]), np.array(buf[P:])
+        # ... and with the replicated inputs (weights, direction) uploaded one chunk per rank and
+        # all-gathered on the device
+        dist.barrier()
+        buf[:] = 0.0
+        dist.barrier()
+        ctx.set_host_inputs_replicated(1)
+        loss_gathered = api.gradientHvHost(ctx, model, xs, ys, w, v, per, ncls, 0.0, buf[:P], buf[P:])
+        ctx.set_host_inputs_replicated(0)
+        ctx.set_host_results_shared(0)
+        g_gathered, hv_gathered = np.array(buf[:P]), np.array(buf[P:])
         rt.cudaHostUnregister(buf.ctypes.data)
         dist.barrier()
         del buf
@@ -202,6 +211,7 @@ def main():
             os.unlink(shm)
         np.savez(out, loss=loss64, gradient=g64, hv=hv, A=A.cpu().numpy(), peer_reduce=int(ctx.peer_reduce_enabled),
                  loss_shared=loss_shared, gradient_shared=g_shared, hv_shared=hv_shared,
+                 loss_gathered=loss_gathered, gradient_gathered=g_gathered, hv_gathered=hv_gathered,
                  peer_launches=ctx.kernel_launches("peer_allreduce_kernel"),
                  loss_host=loss_host, gradient_host=g_host, hv_host=hv_host,
                  G=Gm.cpu().numpy(), Ainv=Ai.cpu().numpy(), Ginv=Gi.cpu().numpy(),

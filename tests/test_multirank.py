@@ -135,6 +135,10 @@ def test_two_gpu_cuda_matches_full_batch(tmp_path, builder):
         assert np.array_equal(res["gradient_shared"], res["gradient"])
         assert np.array_equal(res["hv_shared"], res["hv"])
         assert res["loss_shared"] == res["loss_host"]
+        # ... and with weights and direction uploaded one chunk per rank and all-gathered
+        assert np.array_equal(res["gradient_gathered"], res["gradient"])
+        assert np.array_equal(res["hv_gathered"], res["hv"])
+        assert res["loss_gathered"] == res["loss_host"]
         # 3xTF32 mode across ranks: stated tolerance 1e-3 against the fp64 full-batch result
         assert rel(res["gradient_x3"], g) < 1e-3 and rel(res["hv_x3"], hv) < 1e-3
 
