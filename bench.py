@@ -16,7 +16,10 @@ duration measured by CUDA events inside the timed region, on 1 GPU the CPU basel
 `secondary` the device-timed figures of the path's other configurations at the same GPU count
 (LeNet gradient + Hv + 10 Steihaug-CG iterations, AlexNet-BN gradient + Hv at a global batch of
 1024, the KFAC step at 256 images per GPU).  With more than one GPU, `multi_gpu_parity` holds
-the relative errors of a small sharded problem against the full-batch oracle.
+the relative errors of a small sharded problem against the full-batch oracle, and
+`e2e_node_shared_results` the end-to-end figure when the ranks of the node share one page-locked
+result segment and upload the replicated inputs in chunks (extra information; `e2e` keeps
+private buffers and full transfers on every rank).
 
 `--impl reference` times the same step on the host cores: the gradient and the Hessian-vector
 product by double backward as PyTorch computes them on the CPU (the operator of the
