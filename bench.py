@@ -455,9 +455,20 @@ def time_shared_results(ctx, model, api, hx, hy, hw, hv_in, hg, hh, n, world, ra
     import torch.distributed as dist
     P = model.pSize
     shm = "/dev/shm/fitre_bench_%s" % os.environ.get("MASTER_PORT", "0")
+    # rank 0 creates the segment if the node's shared-memory file system has room for it (touching a
+    # tmpfs mapping beyond its limit is a bus error, not an exception) and tells the others
+    ok = torch.zeros(1, dtype=torch.float64, device="cuda")
     if rank == 0:
-        np.memmap(shm, dtype=np.float64, mode="w+", shape=(2 * P,)).flush()
-    dist.barrier()
+        try:
+            st = os.statvfs("/dev/shm")
+            if st.f_bavail * st.f_frsize > 2 * P * 8 + (64 << 20):
+                np.memmap(shm, dtype=np.float64, mode="w+", shape=(2 * P,)).flush()
+                ok[0] = 1.0
+        except OSError:
+            pass
+    dist.broadcast(ok, 0)
+    if float(ok.item()) != 1.0:
+        return {"skipped": "no room for a %d MB segment in /dev/shm" % (2 * P * 8 >> 20)}
     buf = np.memmap(shm, dtype=np.float64, mode="r+", shape=(2 * P,))
     rt = torch.cuda.cudart()
     rt.cudaHostRegister(buf.ctypes.data, buf.nbytes, 0)
